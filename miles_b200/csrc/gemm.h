@@ -1,0 +1,46 @@
+// Host API of the tcgen05 bf16 GEMM family (dense, grouped-by-rows, grouped-by-contraction).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mb {
+
+enum GemmMode : int {
+  GEMM_DENSE = 0,          // C[M,N] = A . B^T
+  GEMM_GROUPED_ROWS = 1,   // every 128-row tile of A picks the B slab of its group (MoE fwd/dgrad)
+  GEMM_GROUPED_CONTR = 2,  // C_g[M,N] = sum over the rows of group g (MoE wgrad)
+};
+
+// Operand description. A "K-major" operand is a row-major [mn, k] matrix (contraction contiguous);
+// an "MN-major" operand is a row-major [k, mn] matrix (contraction strided).
+struct GemmOperand {
+  const void* ptr;
+  long long rows;  // outer extent of the row-major matrix in memory
+  long long cols;  // inner (contiguous) extent
+  long long ld;    // elements between rows
+  bool mn_major;
+};
+
+struct GemmProblem {
+  int mode;
+  int M, N, K;  // logical problem per group (K ignored in GEMM_GROUPED_CONTR)
+  GemmOperand a, b;
+  void* c;
+  long long ldc;
+  long long c_group_stride;  // elements between per-group outputs (mode 2)
+  bool out_fp32;
+  bool accumulate;           // C += A.B^T instead of C =
+  int num_groups;
+  const int* tile_group;     // mode 1: [ceil(M/128)] group per row tile
+  const int* num_m_tiles;    // mode 1: device scalar with the number of live row tiles
+  const int* group_offsets;  // mode 2: [num_groups+1] row offsets, multiples of 64
+  int* status;               // device status word (0 = ok); may be null
+  int block_n;               // 0 = choose, else 128 or 256
+  int max_ctas;              // 0 = all SMs
+};
+
+// Launches on `stream`. Returns 0 or a negative host-side error code (bad argument / driver error).
+int gemm_bf16_launch(const GemmProblem& p, cudaStream_t stream);
+const char* gemm_last_error();
+
+}  // namespace mb

@@ -1,0 +1,93 @@
+// C++ launchers of the non-GEMM sm_100a kernels. Pointers are device pointers; every launcher is
+// asynchronous on the given stream and performs no allocation.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mb {
+
+// ---- elementwise.cu
+void rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, float* rstd, int T, int H,
+                 float eps, cudaStream_t s);
+int rmsnorm_bwd_num_partials(int T);
+void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                 float* dw_partial, float* dw, bool accumulate_dw, int T, int H, cudaStream_t s);
+void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* q_out, void* k_out,
+                      float* q_rstd, float* k_rstd, void* k_cache, void* v_cache, const int* slot_mapping, int T,
+                      int Hq, int Hk, float theta, float eps, bool use_norm, cudaStream_t s);
+void qk_norm_rope_bwd(const void* dq, const void* dk, const void* dv, const void* qkv, const void* qw, const void* kw,
+                      const int* pos, const float* q_rstd, const float* k_rstd, void* dqkv, float* dqw, float* dkw,
+                      int T, int Hq, int Hk, float theta, bool use_norm, cudaStream_t s);
+void swiglu_fwd(const void* in, void* out, long long T, int I, cudaStream_t s);
+void swiglu_bwd(const void* dout, const void* in, void* din, long long T, int I, cudaStream_t s);
+void adam_step(void* p, float* master, const void* g, bool g_fp32, void* m, void* v, bool mv_bf16, long long n, float lr,
+               float b1, float b2, float eps, float wd, float bc1, float bc2, const float* grad_scale,
+               const float* skip_flag, cudaStream_t s);
+void sumsq(const void* g, bool g_fp32, long long n, float* out, cudaStream_t s);
+
+// ---- moe.cu
+// Router: softmax over E experts (fp32 logits), top-k, optional renormalisation of the k weights.
+// With `replay_ids` the expert choice is taken from it (rollout routing replay) and only the weights
+// are recomputed from the current logits.
+void moe_router_topk(const float* logits, const int* replay_ids, int* topk_ids, float* topk_w, float* probs_out,
+                     int T, int E, int K, bool renorm, cudaStream_t s);
+// Deterministic counting sort of the T*K (token, slot) pairs by expert. Rows of each expert are padded
+// to a multiple of 128; outputs: dest_row[T*K], row_src[max_rows] (-1 for padding), expert_offsets[E+1]
+// (padded), tile_group[max_rows/128], num_m_tiles[1], expert_counts[E].
+void moe_build_permutation(const int* topk_ids, int T, int K, int E, int max_rows, int* expert_counts,
+                           int* expert_offsets, int* dest_row, int* row_src, int* tile_group, int* num_m_tiles,
+                           cudaStream_t s);
+void moe_permute(const void* x, const int* row_src, const int* num_m_tiles, void* x_perm, int max_rows, int H, int K,
+                 cudaStream_t s);
+// out[t] = sum_k w[t,k] * y_perm[dest_row[t,k]]
+void moe_combine(const void* y_perm, const int* dest_row, const float* topk_w, void* out, int T, int K, int H,
+                 cudaStream_t s);
+// dy_perm[row] = w * dout[token]; dw[t,k] = <dout[t], y_perm[row]>; padding rows are zeroed.
+void moe_combine_bwd(const void* dout, const void* y_perm, const int* row_src, const int* num_m_tiles,
+                     const float* topk_w, void* dy_perm, float* dtopk_w, int max_rows, int K, int H, cudaStream_t s);
+// dx[t] = sum_k dx_perm[dest_row[t,k]]
+void moe_unpermute_sum(const void* dx_perm, const int* dest_row, void* dx, int T, int K, int H, cudaStream_t s);
+// Backward of softmax->topk->renorm wrt the router logits.
+void moe_router_bwd(const float* probs, const int* topk_ids, const float* topk_w, const float* dtopk_w, float* dlogits,
+                    int T, int E, int K, bool renorm, cudaStream_t s);
+
+// ---- logprob.cu
+// Row-wise online softmax statistics over bf16 or fp32 logits scaled by 1/temperature:
+// logprob of `target`, entropy, and (kept for the backward) row max and log-sum-exp.
+void logprob_entropy_fwd(const void* logits, bool fp32, const int* targets, float* logprob, float* entropy, float* lse,
+                         float* psum_x, int T, int V, long long ld, float inv_temp, cudaStream_t s);
+// dlogits = inv_temp * ( dlp * (onehot - p) - dH * p * (x - sum p x) ), written in the logits dtype (in place allowed).
+void logprob_entropy_bwd(const void* logits, bool fp32, const int* targets, const float* lse, const float* psum_x,
+                         const float* dlogprob, const float* dentropy, void* dlogits, int T, int V, long long ld,
+                         float inv_temp, cudaStream_t s);
+
+// ---- sampling.cu
+// Per-row temperature / top-k / top-p sampling with a counter-based RNG; returns the token and its
+// logprob under the temperature-scaled full distribution.
+void sample_rows(const void* logits, bool fp32, int T, int V, long long ld, const float* temperature, const int* top_k,
+                 const float* top_p, const unsigned long long* seeds, const int* step, int* out_token, float* out_logprob,
+                 cudaStream_t s);
+
+// ---- attention.cu
+void paged_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                            const int* seq_lens, void* out, float* scratch, int B, int Hq, int Hk, int page_size,
+                            int max_pages, int num_splits, float scale, cudaStream_t s);
+
+// ---- rl.cu
+void gae_reverse_scan(const float* rewards, const float* values, const int* cu_seqlens, float* adv, float* ret,
+                      int num_seqs, float gamma, float lam, cudaStream_t s);
+
+// ---- quant.cu
+void quant_mxfp8(const void* x, uint8_t* q, uint8_t* scales, long long rows, long long cols, cudaStream_t s);
+void dequant_mxfp8(const uint8_t* q, const uint8_t* scales, void* x, long long rows, long long cols, cudaStream_t s);
+void quant_nvfp4(const void* x, uint8_t* q, uint8_t* block_scales, const float* global_amax, long long rows,
+                 long long cols, cudaStream_t s);
+void dequant_nvfp4(const uint8_t* q, const uint8_t* block_scales, const float* global_amax, void* x, long long rows,
+                   long long cols, cudaStream_t s);
+void absmax(const void* x, long long n, float* out, cudaStream_t s);
+void quant_fp8_block128(const void* x, uint8_t* q, float* scales, long long rows, long long cols, bool ue8m0,
+                        cudaStream_t s);
+void fake_int4_quant(const void* x, void* y, long long rows, long long cols, int group_rows, int group_cols,
+                     bool symmetric, cudaStream_t s);
+
+}  // namespace mb
