@@ -1,0 +1,159 @@
+// Paged-KV decode attention (one query token per sequence, GQA), split over the KV length.
+//
+// Cache layout: k_cache / v_cache are [num_slots, Hk, 128] bf16 where slot = page * page_size + offset
+// and block_table[b, i] is the i-th page of sequence b. Grid = (B, Hk, splits); every CTA serves all
+// G = Hq/Hk query heads of one KV head over its slice of the context so that each K/V row is read from
+// HBM exactly once. Partial (max, sum, out) triples are merged by a second kernel.
+//
+// Reference counterpart: flashinfer's trtllm_mha decode backend selected by the B200 recipe
+// (scripts/run_qwen3_30b_a3b.py:311-324).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include "launchers.h"
+
+namespace mb {
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int D = 128;
+constexpr int WARPS = 4;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int G>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+              const int* __restrict__ block_table, const int* __restrict__ seq_lens, float* __restrict__ part_o,
+              float* __restrict__ part_ml, int Hq, int Hk, int page_size, int max_pages, int num_splits, float scale) {
+  const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int len = seq_lens[b];
+  const int per = (len + num_splits - 1) / num_splits;
+  const int t_lo = split * per;
+  const int t_hi = min(len, t_lo + per);
+
+  float qr[G][4];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(q + (static_cast<long long>(b) * Hq + h * G + g) * D + lane * 4);
+    const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(rb[0]), c = __bfloat1622float2(rb[1]);
+    qr[g][0] = a.x * scale; qr[g][1] = a.y * scale; qr[g][2] = c.x * scale; qr[g][3] = c.y * scale;
+  }
+  float m[G], l[G], acc[G][4];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -FLT_MAX;
+    l[g] = 0.f;
+    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+  }
+  const int* table = block_table + static_cast<long long>(b) * max_pages;
+  for (int t = t_lo + warp; t < t_hi; t += WARPS) {
+    const int page = table[t / page_size];
+    const long long slot = static_cast<long long>(page) * page_size + (t % page_size);
+    const long long off = (slot * Hk + h) * D + lane * 4;
+    const uint2 kraw = *reinterpret_cast<const uint2*>(k_cache + off);
+    const uint2 vraw = *reinterpret_cast<const uint2*>(v_cache + off);
+    const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&kraw);
+    const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&vraw);
+    const float2 k0 = __bfloat1622float2(kb[0]), k1 = __bfloat1622float2(kb[1]);
+    const float2 v0 = __bfloat1622float2(vb[0]), v1 = __bfloat1622float2(vb[1]);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s = qr[g][0] * k0.x + qr[g][1] * k0.y + qr[g][2] * k1.x + qr[g][3] * k1.y;
+      s = warp_sum(s);
+      const float nm = fmaxf(m[g], s);
+      const float corr = __expf(m[g] - nm);
+      const float p = __expf(s - nm);
+      l[g] = l[g] * corr + p;
+      acc[g][0] = acc[g][0] * corr + p * v0.x;
+      acc[g][1] = acc[g][1] * corr + p * v0.y;
+      acc[g][2] = acc[g][2] * corr + p * v1.x;
+      acc[g][3] = acc[g][3] * corr + p * v1.y;
+      m[g] = nm;
+    }
+  }
+  // merge the warps of this CTA through shared memory
+  __shared__ float sm_m[WARPS][G], sm_l[WARPS][G];
+  __shared__ float sm_o[WARPS][G][D];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) {
+      sm_m[warp][g] = m[g];
+      sm_l[warp][g] = l[g];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sm_o[warp][g][lane * 4 + i] = acc[g][i];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
+    const int g = idx / D, d = idx - g * D;
+    float gm = -FLT_MAX;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) gm = fmaxf(gm, sm_m[w][g]);
+    float gl = 0.f, go = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float c = sm_m[w][g] == -FLT_MAX ? 0.f : __expf(sm_m[w][g] - gm);
+      gl += sm_l[w][g] * c;
+      go += sm_o[w][g][d] * c;
+    }
+    const long long base = ((static_cast<long long>(b) * Hq + h * G + g) * num_splits + split);
+    part_o[base * D + d] = go;
+    if (d == 0) {
+      part_ml[base * 2] = gm;
+      part_ml[base * 2 + 1] = gl;
+    }
+  }
+}
+
+__global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    bf16* __restrict__ out, int num_splits) {
+  const long long bh = blockIdx.x;  // b * Hq + head
+  const int d = threadIdx.x;
+  float gm = -FLT_MAX;
+  for (int s = 0; s < num_splits; ++s) gm = fmaxf(gm, part_ml[(bh * num_splits + s) * 2]);
+  float gl = 0.f, go = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float mm = part_ml[(bh * num_splits + s) * 2];
+    const float c = mm == -FLT_MAX ? 0.f : __expf(mm - gm);
+    gl += part_ml[(bh * num_splits + s) * 2 + 1] * c;
+    go += part_o[(bh * num_splits + s) * D + d] * c;
+  }
+  out[bh * D + d] = __float2bfloat16(gl > 0.f ? go / gl : 0.f);
+}
+
+}  // namespace
+
+// scratch: fp32 [B*Hq*num_splits*(128+2)]
+void paged_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                            const int* seq_lens, void* out, float* scratch, int B, int Hq, int Hk, int page_size,
+                            int max_pages, int num_splits, float scale, cudaStream_t s) {
+  if (B <= 0) return;
+  float* part_o = scratch;
+  float* part_ml = scratch + static_cast<long long>(B) * Hq * num_splits * D;
+  dim3 grid(B, Hk, num_splits);
+  const int G = Hq / Hk;
+#define MB_DEC(GG)                                                                                                   \
+  decode_kernel<GG><<<grid, WARPS * 32, 0, s>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k_cache),      \
+                                                static_cast<const bf16*>(v_cache), block_table, seq_lens, part_o,     \
+                                                part_ml, Hq, Hk, page_size, max_pages, num_splits, scale)
+  switch (G) {
+    case 1: MB_DEC(1); break;
+    case 2: MB_DEC(2); break;
+    case 4: MB_DEC(4); break;
+    case 8: MB_DEC(8); break;
+    default: return;
+  }
+#undef MB_DEC
+  decode_merge_kernel<<<B * Hq, D, 0, s>>>(part_o, part_ml, static_cast<bf16*>(out), num_splits);
+}
+
+}  // namespace mb

@@ -56,10 +56,11 @@ void moe_router_bwd(const float* probs, const int* topk_ids, const float* topk_w
 // logprob of `target`, entropy, and (kept for the backward) row max and log-sum-exp.
 void logprob_entropy_fwd(const void* logits, bool fp32, const int* targets, float* logprob, float* entropy, float* lse,
                          float* psum_x, int T, int V, long long ld, float inv_temp, cudaStream_t s);
-// dlogits = inv_temp * ( dlp * (onehot - p) - dH * p * (x - sum p x) ), written in the logits dtype (in place allowed).
+// dlogits = inv_temp * ( dlp * (onehot - p) - dH * p * (x - sum p x) ), written as bf16 with row pitch ld_out
+// (in place is allowed for bf16 logits).
 void logprob_entropy_bwd(const void* logits, bool fp32, const int* targets, const float* lse, const float* psum_x,
                          const float* dlogprob, const float* dentropy, void* dlogits, int T, int V, long long ld,
-                         float inv_temp, cudaStream_t s);
+                         long long ld_out, float inv_temp, cudaStream_t s);
 
 // ---- sampling.cu
 // Per-row temperature / top-k / top-p sampling with a counter-based RNG; returns the token and its
@@ -87,7 +88,7 @@ void dequant_nvfp4(const uint8_t* q, const uint8_t* block_scales, const float* g
 void absmax(const void* x, long long n, float* out, cudaStream_t s);
 void quant_fp8_block128(const void* x, uint8_t* q, float* scales, long long rows, long long cols, bool ue8m0,
                         cudaStream_t s);
-void fake_int4_quant(const void* x, void* y, long long rows, long long cols, int group_rows, int group_cols,
-                     bool symmetric, cudaStream_t s);
+void fake_int4_quant(const void* x, void* y, void* scale, void* zero, long long rows, long long cols, int group_rows,
+                     int group_cols, bool symmetric, cudaStream_t s);
 
 }  // namespace mb

@@ -3,7 +3,7 @@
 // One CTA per row computes, in a single online-softmax sweep over the (bf16 or fp32) logits scaled by
 // 1/temperature: log-sum-exp, sum_v p_v x_v, the target's log-probability and the entropy
 // H = lse - sum_v p_v x_v. The [T, V] fp32 probabilities are never materialised. The backward pass
-// rewrites the logits buffer with dL/dlogits so the LM-head GEMMs can consume it directly.
+// writes dL/dlogits as bf16 (in place for bf16 logits) so the LM-head GEMMs can consume it directly.
 //
 // Reference counterparts: Megatron fused_vocab_parallel_cross_entropy and _VocabParallelEntropy
 // (miles/backends/training_utils/loss_hub/math_utils.py:280-299,397-433).
@@ -112,10 +112,10 @@ template <typename T, int THREADS>
 __global__ void logprob_bwd_kernel(const T* __restrict__ logits, const int* __restrict__ targets,
                                    const float* __restrict__ lse, const float* __restrict__ psumx,
                                    const float* __restrict__ dlogprob, const float* __restrict__ dentropy,
-                                   T* __restrict__ dlogits, int V, long long ld_, float inv_temp) {
+                                   bf16* __restrict__ dlogits, int V, long long ld_, long long ld_out, float inv_temp) {
   const long long row = blockIdx.x;
   const T* x = logits + row * ld_;
-  T* dx = dlogits + row * ld_;
+  bf16* dx = dlogits + row * ld_out;
   const float l = lse[row];
   const float px = psumx[row];
   const float dlp = dlogprob ? dlogprob[row] : 0.f;
@@ -127,8 +127,7 @@ __global__ void logprob_bwd_kernel(const T* __restrict__ logits, const int* __re
     float g = -dlp * p - dh * p * (xs - px);
     if (i == t) g += dlp;
     g *= inv_temp;
-    if constexpr (sizeof(T) == 2) dx[i] = __float2bfloat16(g);
-    else dx[i] = g;
+    dx[i] = __float2bfloat16(g);
   }
 }
 
@@ -147,17 +146,17 @@ void logprob_entropy_fwd(const void* logits, bool fp32, const int* targets, floa
 
 void logprob_entropy_bwd(const void* logits, bool fp32, const int* targets, const float* lse, const float* psum_x,
                          const float* dlogprob, const float* dentropy, void* dlogits, int T, int V, long long ld,
-                         float inv_temp, cudaStream_t s) {
+                         long long ld_out, float inv_temp, cudaStream_t s) {
   if (T <= 0) return;
   int bx = (V + 256 * 8 - 1) / (256 * 8);
   if (bx < 1) bx = 1;
   dim3 grid(T, bx);
   if (fp32)
     logprob_bwd_kernel<float, 256><<<grid, 256, 0, s>>>(static_cast<const float*>(logits), targets, lse, psum_x,
-                                                        dlogprob, dentropy, static_cast<float*>(dlogits), V, ld, inv_temp);
+                                                        dlogprob, dentropy, static_cast<bf16*>(dlogits), V, ld, ld_out, inv_temp);
   else
     logprob_bwd_kernel<bf16, 256><<<grid, 256, 0, s>>>(static_cast<const bf16*>(logits), targets, lse, psum_x, dlogprob,
-                                                       dentropy, static_cast<bf16*>(dlogits), V, ld, inv_temp);
+                                                       dentropy, static_cast<bf16*>(dlogits), V, ld, ld_out, inv_temp);
 }
 
 }  // namespace mb

@@ -217,13 +217,16 @@ std::vector<at::Tensor> logprob_entropy_fwd(const at::Tensor& logits, const at::
   return {lp, ent, lse, px};
 }
 
-void logprob_entropy_bwd(at::Tensor& logits, const at::Tensor& targets, const at::Tensor& lse, const at::Tensor& px,
-                         const c10::optional<at::Tensor>& dlp, const c10::optional<at::Tensor>& dent, double inv_temp) {
+// Returns dlogits as bf16 [T, V]; for bf16 logits the result overwrites the input buffer.
+at::Tensor logprob_entropy_bwd(at::Tensor& logits, const at::Tensor& targets, const at::Tensor& lse, const at::Tensor& px,
+                               const c10::optional<at::Tensor>& dlp, const c10::optional<at::Tensor>& dent, double inv_temp) {
   const c10::cuda::CUDAGuard guard(logits.device());
   const bool fp32 = logits.scalar_type() == at::kFloat;
+  at::Tensor out = fp32 ? at::empty(logits.sizes(), logits.options().dtype(at::kBFloat16)) : logits;
   mb::logprob_entropy_bwd(logits.data_ptr(), fp32, targets.data_ptr<int>(), lse.data_ptr<float>(), px.data_ptr<float>(),
-                          opt_ptr<float>(dlp), opt_ptr<float>(dent), logits.data_ptr(), logits.size(0), logits.size(1),
-                          logits.stride(0), inv_temp, cur_stream());
+                          opt_ptr<float>(dlp), opt_ptr<float>(dent), out.data_ptr(), logits.size(0), logits.size(1),
+                          logits.stride(0), out.stride(0), inv_temp, cur_stream());
+  return out;
 }
 
 }  // namespace

@@ -5,4 +5,139 @@
 
 #include "launchers.h"
 
-void register_more(pybind11::module_& m) {}
+namespace {
+
+cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+#define CHECK_BF16(t) TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kBFloat16 && (t).is_contiguous(), #t " must be a contiguous bf16 CUDA tensor")
+#define CHECK_F32(t) TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kFloat && (t).is_contiguous(), #t " must be a contiguous fp32 CUDA tensor")
+#define CHECK_I32(t) TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kInt && (t).is_contiguous(), #t " must be a contiguous int32 CUDA tensor")
+
+template <typename T>
+T* opt_ptr(const c10::optional<at::Tensor>& t) {
+  return t.has_value() ? static_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+// logits [B, V] (bf16/fp32) -> (token int32 [B], logprob fp32 [B]); per-row parameters are optional tensors.
+void sample_rows(const at::Tensor& logits, const c10::optional<at::Tensor>& temperature,
+                 const c10::optional<at::Tensor>& top_k, const c10::optional<at::Tensor>& top_p,
+                 const c10::optional<at::Tensor>& seeds, const c10::optional<at::Tensor>& step, at::Tensor& out_token,
+                 at::Tensor& out_logprob) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "logits must be 2-D with contiguous rows");
+  const bool fp32 = logits.scalar_type() == at::kFloat;
+  TORCH_CHECK(fp32 || logits.scalar_type() == at::kBFloat16, "logits must be bf16 or fp32");
+  CHECK_I32(out_token); CHECK_F32(out_logprob);
+  if (seeds.has_value()) TORCH_CHECK(seeds->scalar_type() == at::kLong && seeds->is_cuda(), "seeds must be int64 CUDA");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  mb::sample_rows(logits.data_ptr(), fp32, logits.size(0), logits.size(1), logits.stride(0), opt_ptr<float>(temperature),
+                  opt_ptr<int>(top_k), opt_ptr<float>(top_p),
+                  reinterpret_cast<const unsigned long long*>(opt_ptr<int64_t>(seeds)), opt_ptr<int>(step),
+                  out_token.data_ptr<int>(), out_logprob.data_ptr<float>(), cur_stream());
+}
+
+// q [B, Hq, 128]; caches [slots, Hk, 128]; block_table [B, max_pages]; out [B, Hq, 128]; scratch fp32.
+void paged_decode_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
+                            const at::Tensor& block_table, const at::Tensor& seq_lens, at::Tensor& out, at::Tensor& scratch,
+                            int64_t page_size, int64_t num_splits, double scale) {
+  CHECK_BF16(q); CHECK_BF16(k_cache); CHECK_BF16(v_cache); CHECK_I32(block_table); CHECK_I32(seq_lens); CHECK_BF16(out); CHECK_F32(scratch);
+  const int B = q.size(0), Hq = q.size(1), Hk = k_cache.size(1);
+  TORCH_CHECK(q.size(2) == 128 && k_cache.size(2) == 128, "head_dim must be 128");
+  const int G = Hq / Hk;
+  TORCH_CHECK(Hq % Hk == 0 && (G == 1 || G == 2 || G == 4 || G == 8), "unsupported GQA group size");
+  TORCH_CHECK(scratch.numel() >= static_cast<int64_t>(B) * Hq * num_splits * 130, "scratch too small");
+  const c10::cuda::CUDAGuard guard(q.device());
+  mb::paged_decode_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr<int>(),
+                             seq_lens.data_ptr<int>(), out.data_ptr(), scratch.data_ptr<float>(), B, Hq, Hk, page_size,
+                             block_table.size(1), num_splits, scale, cur_stream());
+}
+
+std::vector<at::Tensor> gae(const at::Tensor& rewards, const at::Tensor& values, const at::Tensor& cu, double gamma, double lam) {
+  CHECK_F32(rewards); CHECK_F32(values); CHECK_I32(cu);
+  const c10::cuda::CUDAGuard guard(rewards.device());
+  at::Tensor adv = at::zeros_like(rewards), ret = at::zeros_like(rewards);
+  mb::gae_reverse_scan(rewards.data_ptr<float>(), values.data_ptr<float>(), cu.data_ptr<int>(), adv.data_ptr<float>(),
+                       ret.data_ptr<float>(), cu.numel() - 1, gamma, lam, cur_stream());
+  return {adv, ret};
+}
+
+std::vector<at::Tensor> quant_mxfp8(const at::Tensor& x) {
+  CHECK_BF16(x);
+  const int64_t cols = x.size(-1), rows = x.numel() / cols;
+  TORCH_CHECK(cols % 32 == 0, "last dim must be a multiple of 32 for MXFP8");
+  const c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor q = at::empty(x.sizes(), x.options().dtype(at::kByte));
+  auto ssz = x.sizes().vec(); ssz.back() = cols / 32;
+  at::Tensor sc = at::empty(ssz, x.options().dtype(at::kByte));
+  mb::quant_mxfp8(x.data_ptr(), q.data_ptr<uint8_t>(), sc.data_ptr<uint8_t>(), rows, cols, cur_stream());
+  return {q, sc};
+}
+at::Tensor dequant_mxfp8(const at::Tensor& q, const at::Tensor& sc) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int64_t cols = q.size(-1), rows = q.numel() / cols;
+  at::Tensor x = at::empty(q.sizes(), q.options().dtype(at::kBFloat16));
+  mb::dequant_mxfp8(q.data_ptr<uint8_t>(), sc.data_ptr<uint8_t>(), x.data_ptr(), rows, cols, cur_stream());
+  return x;
+}
+at::Tensor absmax(const at::Tensor& x) {
+  CHECK_BF16(x);
+  const c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor out = at::zeros({1}, x.options().dtype(at::kFloat));
+  mb::absmax(x.data_ptr(), x.numel(), out.data_ptr<float>(), cur_stream());
+  return out;
+}
+// returns packed uint8 [.., cols/2], e4m3 block scales as uint8 [.., cols/16]; `global_amax` fp32 [1] on device
+std::vector<at::Tensor> quant_nvfp4(const at::Tensor& x, const at::Tensor& global_amax) {
+  CHECK_BF16(x); CHECK_F32(global_amax);
+  const int64_t cols = x.size(-1), rows = x.numel() / cols;
+  TORCH_CHECK(cols % 16 == 0, "last dim must be a multiple of 16 for NVFP4");
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto qsz = x.sizes().vec(); qsz.back() = cols / 2;
+  auto ssz = x.sizes().vec(); ssz.back() = cols / 16;
+  at::Tensor q = at::empty(qsz, x.options().dtype(at::kByte)), sc = at::empty(ssz, x.options().dtype(at::kByte));
+  mb::quant_nvfp4(x.data_ptr(), q.data_ptr<uint8_t>(), sc.data_ptr<uint8_t>(), global_amax.data_ptr<float>(), rows, cols, cur_stream());
+  return {q, sc};
+}
+at::Tensor dequant_nvfp4(const at::Tensor& q, const at::Tensor& sc, const at::Tensor& global_amax) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  auto xsz = q.sizes().vec(); xsz.back() *= 2;
+  at::Tensor x = at::empty(xsz, q.options().dtype(at::kBFloat16));
+  const int64_t cols = xsz.back(), rows = x.numel() / cols;
+  mb::dequant_nvfp4(q.data_ptr<uint8_t>(), sc.data_ptr<uint8_t>(), global_amax.data_ptr<float>(), x.data_ptr(), rows, cols, cur_stream());
+  return x;
+}
+std::vector<at::Tensor> quant_fp8_block128(const at::Tensor& x, bool ue8m0) {
+  CHECK_BF16(x);
+  TORCH_CHECK(x.dim() == 2, "expected a 2-D weight");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0), cols = x.size(1);
+  at::Tensor q = at::empty({rows, cols}, x.options().dtype(at::kByte));
+  at::Tensor sc = at::empty({(rows + 127) / 128, (cols + 127) / 128}, x.options().dtype(at::kFloat));
+  mb::quant_fp8_block128(x.data_ptr(), q.data_ptr<uint8_t>(), sc.data_ptr<float>(), rows, cols, ue8m0, cur_stream());
+  return {q, sc};
+}
+std::vector<at::Tensor> fake_int4_quant(const at::Tensor& x, int64_t gr, int64_t gc, bool sym) {
+  CHECK_BF16(x);
+  TORCH_CHECK(x.dim() == 2 && gr > 0 && gc > 0 && (gr * gc) % 32 == 0, "group must hold a multiple of 32 elements");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0), cols = x.size(1);
+  at::Tensor y = at::empty_like(x);
+  at::Tensor sc = at::empty({(rows + gr - 1) / gr, (cols + gc - 1) / gc}, x.options());
+  at::Tensor zp = at::zeros_like(sc);
+  mb::fake_int4_quant(x.data_ptr(), y.data_ptr(), sc.data_ptr(), zp.data_ptr(), rows, cols, gr, gc, sym, cur_stream());
+  return {y, sc, zp};
+}
+
+}  // namespace
+
+void register_more(pybind11::module_& m) {
+  m.def("sample_rows", &sample_rows);
+  m.def("paged_decode_attention", &paged_decode_attention);
+  m.def("gae", &gae);
+  m.def("quant_mxfp8", &quant_mxfp8);
+  m.def("dequant_mxfp8", &dequant_mxfp8);
+  m.def("absmax", &absmax);
+  m.def("quant_nvfp4", &quant_nvfp4);
+  m.def("dequant_nvfp4", &dequant_nvfp4);
+  m.def("quant_fp8_block128", &quant_fp8_block128);
+  m.def("fake_int4_quant", &fake_int4_quant);
+}

@@ -1,0 +1,373 @@
+"""Hand-scheduled sm_100a execution of the Qwen3 dense / MoE decoder (training and inference).
+
+There is no autograd graph and no tracing compiler on this path: forward and backward of a decoder
+layer are explicit sequences of kernel launches (tcgen05 GEMMs, fused norm / rope / swiglu / routing
+kernels), activations are recomputed layer by layer in the backward pass (only each layer's input is
+kept, the "full recompute" policy of the reference recipe scripts/run_qwen3_30b_a3b.py:168-175), and
+weight gradients are accumulated by the GEMM epilogue directly into the persistent flat gradient buffer
+(the role of Megatron's ``main_grad`` + gradient-accumulation fusion).
+
+The same object serves the rollout engine (prefill and paged-KV decode), so trainer and engine share
+kernels and reduction orders — the basis for trainer/rollout log-prob parity.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..ops import _ext
+from .config import ModelConfig
+from .params import ParamStore
+from .torch_impl import InferMeta
+
+
+def _flash_attn():
+    from flash_attn import flash_attn_varlen_func  # library attention (until the tcgen05 kernel lands for training)
+
+    return flash_attn_varlen_func
+
+
+@dataclass
+class MoeCtx:
+    ids: torch.Tensor
+    w: torch.Tensor
+    probs: torch.Tensor
+    offsets: torch.Tensor
+    dest: torch.Tensor
+    src: torch.Tensor
+    tile_group: torch.Tensor
+    num_tiles: torch.Tensor
+    max_rows: int
+
+
+class B200Qwen3:
+    def __init__(self, cfg: ModelConfig, store: ParamStore, ep=None):
+        assert cfg.head_dim == 128, "the sm_100a attention/rope kernels are specialised for head_dim 128"
+        self.cfg = cfg
+        self.store = store
+        self.ep = ep  # expert-parallel dispatcher (None = all experts local)
+        self.C = _ext.load(required=True)
+        self.dev = store.device
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.launches = 0  # number of this library's kernels launched (reported by the benchmark)
+        self._decode_scratch: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ GEMM helpers
+    def _gemm(self, a, b, out, a_mn=False, b_mn=False, acc=False):
+        self.C.gemm(a, b, out, a_mn, b_mn, acc, 0, self.status)
+        self.launches += 1
+        return out
+
+    def linear(self, x, w, out_dtype=torch.bfloat16):
+        out = torch.empty(x.shape[0], w.shape[0], dtype=out_dtype, device=x.device)
+        return self._gemm(x, w, out)
+
+    def linear_dgrad(self, dy, w):
+        dx = torch.empty(dy.shape[0], w.shape[1], dtype=torch.bfloat16, device=dy.device)
+        return self._gemm(dy, w, dx, False, True)
+
+    def linear_wgrad(self, dy, x, dw):
+        """dw [N,K] += dy[M,N]^T . x[M,K]"""
+        return self._gemm(dy, x, dw, True, True, True)
+
+    def check_status(self) -> None:
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(f"a miles_b200 kernel reported error status {code} (bounded wait expired)")
+
+    # ------------------------------------------------------------------ MoE block
+    def _route(self, h2, router_w, replay_ids):
+        cfg, C = self.cfg, self.C
+        logits = self.linear(h2, router_w, torch.float32)
+        rid = replay_ids.contiguous() if replay_ids is not None else None
+        ids, w, probs = C.moe_router_topk(logits, rid, cfg.moe_top_k, cfg.norm_topk_prob, True)
+        self.launches += 1
+        return ids, w, probs
+
+    def _permute_plan(self, ids, E_local) -> MoeCtx:
+        T, K = ids.shape
+        max_rows = ((T * K + 127) // 128 + min(E_local, T * K)) * 128
+        counts, offsets, dest, src, tg, nt = self.C.moe_build_permutation(ids, E_local, max_rows)
+        self.launches += 3
+        return MoeCtx(ids, None, None, offsets, dest, src, tg, nt, max_rows)
+
+    def _experts_fwd(self, xp, plan: MoeCtx, w1, w2, keep: bool):
+        C = self.C
+        I2 = w1.shape[1]
+        gu = torch.empty(plan.max_rows, I2, dtype=torch.bfloat16, device=xp.device)
+        C.grouped_gemm_rows(xp, w1, gu, plan.tile_group, plan.num_tiles, False, False, 0, self.status)
+        act = C.swiglu_fwd(gu)
+        yp = torch.empty(plan.max_rows, w2.shape[1], dtype=torch.bfloat16, device=xp.device)
+        C.grouped_gemm_rows(act, w2, yp, plan.tile_group, plan.num_tiles, False, False, 0, self.status)
+        self.launches += 3
+        return (gu, act, yp) if keep else (None, None, yp)
+
+    def moe_forward(self, i, h2, replay_ids=None, record=None, keep=False):
+        cfg, P, C = self.cfg, self.store.params, self.C
+        p = f"layers.{i}.moe."
+        ids, w, probs = self._route(h2, P[p + "router.weight"], replay_ids)
+        if record is not None:
+            record.append(ids)
+        if self.ep is not None:
+            return self.ep.moe_forward(self, i, h2, ids, w, probs, keep)
+        plan = self._permute_plan(ids, cfg.num_experts)
+        plan.w, plan.probs = w, probs
+        xp = C.moe_permute(h2, plan.src, plan.num_tiles, cfg.moe_top_k)
+        gu, act, yp = self._experts_fwd(xp, plan, P[p + "w1"], P[p + "w2"], keep)
+        y = C.moe_combine(yp, plan.dest, w, h2.shape[0], cfg.moe_top_k)
+        self.launches += 2
+        saved = (plan, xp, gu, act, yp) if keep else None
+        return y, saved
+
+    def moe_backward(self, i, h2, dy, saved):
+        """Returns dh2 (gradient wrt the normalised MoE input); accumulates router / expert weight grads."""
+        cfg, P, G, C = self.cfg, self.store.params, self.store.grads, self.C
+        p = f"layers.{i}.moe."
+        if self.ep is not None:
+            return self.ep.moe_backward(self, i, h2, dy, saved)
+        plan, xp, gu, act, yp = saved
+        w1, w2 = P[p + "w1"], P[p + "w2"]
+        dyp, dw = C.moe_combine_bwd(dy, yp, plan.src, plan.num_tiles, plan.w)
+        dxp = self._experts_bwd(dyp, xp, gu, act, plan, w1, w2, G[p + "w1"], G[p + "w2"])
+        dh2 = C.moe_combine(dxp, plan.dest, None, h2.shape[0], cfg.moe_top_k)
+        self.launches += 2
+        dh2 = self._router_bwd(i, h2, dh2, plan.probs, plan.ids, plan.w, dw)
+        return dh2
+
+    def _experts_bwd(self, dyp, xp, gu, act, plan, w1, w2, gw1, gw2):
+        C = self.C
+        dact = torch.empty_like(act)
+        C.grouped_gemm_rows(dyp, w2, dact, plan.tile_group, plan.num_tiles, True, False, 0, self.status)
+        C.grouped_gemm_contr(dyp, act, gw2, plan.offsets, True, 0, self.status)
+        dgu = C.swiglu_bwd(dact, gu)
+        dxp = torch.empty_like(xp)
+        C.grouped_gemm_rows(dgu, w1, dxp, plan.tile_group, plan.num_tiles, True, False, 0, self.status)
+        C.grouped_gemm_contr(dgu, xp, gw1, plan.offsets, True, 0, self.status)
+        self.launches += 5
+        return dxp
+
+    def _router_bwd(self, i, h2, dh2, probs, ids, w, dw):
+        cfg, P, G, C = self.cfg, self.store.params, self.store.grads, self.C
+        p = f"layers.{i}.moe."
+        dlogits = C.moe_router_bwd(probs, ids, w, dw, cfg.norm_topk_prob).to(torch.bfloat16)
+        self._gemm(dlogits, P[p + "router.weight"], dh2, False, True, True)
+        self.linear_wgrad(dlogits, h2, G[p + "router.weight"])
+        self.launches += 1
+        return dh2
+
+    # ------------------------------------------------------------------ layer forward / backward
+    def _attn_qkv(self, i, x, positions, meta: Optional[InferMeta], kv_cache):
+        cfg, P, C = self.cfg, self.store.params, self.C
+        p = f"layers.{i}."
+        h1, rstd1 = C.rmsnorm_fwd(x, None, P[p + "ln1.weight"], cfg.rms_eps)
+        qkv = self.linear(h1, P[p + "attn.qkv.weight"])
+        if cfg.qkv_bias:
+            qkv += P[p + "attn.qkv.bias"]
+        kc = vc = slots = None
+        if kv_cache is not None:
+            kc, vc = kv_cache[i]
+            slots = meta.slot_mapping
+        write_k = meta is None or meta.is_prefill
+        q, k, qr, kr = C.qk_norm_rope_fwd(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"), positions,
+                                          cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps, kc, vc, slots,
+                                          write_k)
+        self.launches += 2
+        return h1, rstd1, qkv, q, k, qr, kr
+
+    def _v_view(self, qkv):
+        cfg = self.cfg
+        return qkv.view(qkv.shape[0], cfg.num_q_heads + 2 * cfg.num_kv_heads, cfg.head_dim)[:, cfg.num_q_heads + cfg.num_kv_heads:]
+
+    def layer_forward(self, i, x, positions, cu, max_seqlen, meta: Optional[InferMeta] = None, kv_cache=None,
+                      replay_ids=None, record=None):
+        """Inference/no-grad forward of one layer: returns the layer output."""
+        cfg, P, C = self.cfg, self.store.params, self.C
+        p = f"layers.{i}."
+        h1, rstd1, qkv, q, k, _, _ = self._attn_qkv(i, x, positions, meta, kv_cache)
+        scale = cfg.head_dim ** -0.5
+        if meta is not None and not meta.is_prefill:
+            att = torch.empty_like(q)
+            B = q.shape[0]
+            splits = self._decode_splits(B, meta)
+            need = B * cfg.num_q_heads * splits * 130
+            if self._decode_scratch is None or self._decode_scratch.numel() < need:
+                self._decode_scratch = torch.empty(need, dtype=torch.float32, device=self.dev)
+            kc, vc = kv_cache[i]
+            C.paged_decode_attention(q, kc, vc, meta.block_table, meta.seq_lens, att, self._decode_scratch, meta.page_size,
+                                     splits, scale)
+            self.launches += 2
+        else:
+            att = _flash_attn()(q, k, self._v_view(qkv), cu, cu, max_seqlen, max_seqlen, softmax_scale=scale, causal=True)
+        o = self.linear(att.view(att.shape[0], -1), P[p + "attn.o.weight"])
+        h2, _, x2 = C.rmsnorm_fwd(o, x, P[p + "ln2.weight"], cfg.rms_eps)
+        self.launches += 1
+        if cfg.layer_is_moe(i):
+            y, _ = self.moe_forward(i, h2, replay_ids, record, keep=False)
+        else:
+            gu = self.linear(h2, P[p + "mlp.gate_up.weight"])
+            y = self.linear(C.swiglu_fwd(gu), P[p + "mlp.down.weight"])
+            self.launches += 1
+        return x2.add_(y)
+
+    def _decode_splits(self, B: int, meta: InferMeta) -> int:
+        ctas = B * self.cfg.num_kv_heads
+        return max(1, min(16, (148 * 4) // max(ctas, 1)))
+
+    def layer_backward(self, i, x, dy, positions, cu, max_seqlen, replay_ids=None):
+        """Recompute layer i from its input ``x`` and back-propagate ``dy``; returns dx."""
+        cfg, P, G, C = self.cfg, self.store.params, self.store.grads, self.C
+        p = f"layers.{i}."
+        scale = cfg.head_dim ** -0.5
+        # ---- recompute forward, keeping what the backward needs
+        h1, rstd1, qkv, q, k, qr, kr = self._attn_qkv(i, x, positions, None, None)
+        q_, k_, v_ = q.requires_grad_(True), k.requires_grad_(True), self._v_view(qkv).detach().requires_grad_(True)
+        with torch.enable_grad():
+            att = _flash_attn()(q_, k_, v_, cu, cu, max_seqlen, max_seqlen, softmax_scale=scale, causal=True)
+        att2 = att.detach().view(att.shape[0], -1)
+        o = self.linear(att2, P[p + "attn.o.weight"])
+        h2, rstd2, x2 = C.rmsnorm_fwd(o, x, P[p + "ln2.weight"], cfg.rms_eps)
+        self.launches += 1
+        is_moe = cfg.layer_is_moe(i)
+        if is_moe:
+            _, saved = self.moe_forward(i, h2, replay_ids, None, keep=True)
+        else:
+            gu = self.linear(h2, P[p + "mlp.gate_up.weight"])
+            act = C.swiglu_fwd(gu)
+            self.launches += 1
+        # ---- backward: MLP / MoE
+        if is_moe:
+            dh2 = self.moe_backward(i, h2, dy, saved)
+            del saved
+        else:
+            dact = self.linear_dgrad(dy, P[p + "mlp.down.weight"])
+            self.linear_wgrad(dy, act, G[p + "mlp.down.weight"])
+            dgu = C.swiglu_bwd(dact, gu)
+            dh2 = self.linear_dgrad(dgu, P[p + "mlp.gate_up.weight"])
+            self.linear_wgrad(dgu, h2, G[p + "mlp.gate_up.weight"])
+            self.launches += 1
+        # ---- ln2 (residual gradient dy flows straight through x2)
+        dx2 = C.rmsnorm_bwd(dh2, x2, P[p + "ln2.weight"], rstd2, dy, G[p + "ln2.weight"], True)
+        self.launches += 2
+        # ---- attention output projection
+        datt = self.linear_dgrad(dx2, P[p + "attn.o.weight"])
+        self.linear_wgrad(dx2, att2, G[p + "attn.o.weight"])
+        dq, dk, dv = torch.autograd.grad(att, (q_, k_, v_), datt.view_as(att))
+        dqkv = C.qk_norm_rope_bwd(dq.contiguous(), dk.contiguous(), dv.contiguous(), qkv, P.get(p + "attn.q_norm.weight"),
+                                  P.get(p + "attn.k_norm.weight"), positions, qr, kr, G.get(p + "attn.q_norm.weight"),
+                                  G.get(p + "attn.k_norm.weight"), cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta)
+        self.launches += 1
+        if cfg.qkv_bias:
+            G[p + "attn.qkv.bias"].add_(dqkv.float().sum(0).to(G[p + "attn.qkv.bias"].dtype))
+        dh1 = self.linear_dgrad(dqkv, P[p + "attn.qkv.weight"])
+        self.linear_wgrad(dqkv, h1, G[p + "attn.qkv.weight"])
+        dx = C.rmsnorm_bwd(dh1, x, P[p + "ln1.weight"], rstd1, dx2, G[p + "ln1.weight"], True)
+        self.launches += 2
+        return dx
+
+    # ------------------------------------------------------------------ whole-model passes
+    @torch.no_grad()
+    def forward_hidden(self, tokens, positions, cu_seqlens, meta: Optional[InferMeta] = None, kv_cache=None,
+                       replay: Optional[torch.Tensor] = None, record: Optional[list] = None, max_seqlen: int = 0,
+                       save_inputs: Optional[list] = None):
+        cfg, P, C = self.cfg, self.store.params, self.C
+        x = P["embed.weight"][tokens.long()]
+        if not max_seqlen and cu_seqlens is not None:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
+        moe_idx = 0
+        for i in range(cfg.num_layers):
+            if save_inputs is not None:
+                save_inputs.append(x)
+            rid = None
+            if cfg.layer_is_moe(i):
+                if replay is not None:
+                    rid = replay[:, moe_idx]
+                moe_idx += 1
+            x = self.layer_forward(i, x, positions, cu_seqlens, max_seqlen, meta, kv_cache, rid, record)
+        if save_inputs is not None:
+            save_inputs.append(x)
+        h, _ = C.rmsnorm_fwd(x, None, P["final_norm.weight"], cfg.rms_eps)
+        self.launches += 1
+        return h
+
+    @torch.no_grad()
+    def logits(self, hidden_rows, out_dtype=torch.float32):
+        return self.linear(hidden_rows.contiguous(), self.store.lm_head(), out_dtype)
+
+    @torch.no_grad()
+    def logprobs_entropy(self, hidden_rows, targets, inv_temp: float, chunk: int = 2048, keep_stats: bool = False):
+        C = self.C
+        n = hidden_rows.shape[0]
+        lp = torch.empty(n, dtype=torch.float32, device=self.dev)
+        ent = torch.empty_like(lp)
+        lse = torch.empty_like(lp) if keep_stats else None
+        px = torch.empty_like(lp) if keep_stats else None
+        tg = targets.to(torch.int32).contiguous()
+        for a in range(0, n, chunk):
+            b = min(a + chunk, n)
+            lg = self.logits(hidden_rows[a:b])
+            l1, e1, s1, p1 = C.logprob_entropy_fwd(lg, tg[a:b], inv_temp)
+            self.launches += 1
+            lp[a:b], ent[a:b] = l1, e1
+            if keep_stats:
+                lse[a:b], px[a:b] = s1, p1
+        return (lp, ent, lse, px) if keep_stats else (lp, ent)
+
+    @torch.no_grad()
+    def forward_logprobs(self, tokens, positions, cu_seqlens, row_index, targets, inv_temp, replay=None, record=None,
+                         max_seqlen: int = 0):
+        h = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, record=record, max_seqlen=max_seqlen)
+        return self.logprobs_entropy(h[row_index.long()], targets, inv_temp)
+
+    def forward_backward(self, tokens, positions, cu_seqlens, row_index, targets, inv_temp, loss_fn, replay=None,
+                         max_seqlen: int = 0, chunk: int = 2048):
+        """One micro-batch: forward, ``loss_fn(logprobs, entropy) -> (loss, metrics)``, backward into the grad buffers."""
+        cfg, P, G, C = self.cfg, self.store.params, self.store.grads, self.C
+        assert G, "allocate_grads() must be called before training"
+        if not max_seqlen:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
+        inputs: list[torch.Tensor] = []
+        h = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, max_seqlen=max_seqlen, save_inputs=inputs)
+        x_last = inputs.pop()  # input of the final norm
+        rows = row_index.long()
+        hr = h[rows].contiguous()
+        tg = targets.to(torch.int32).contiguous()
+        with torch.no_grad():
+            lp, ent, lse, px = self.logprobs_entropy(hr, tg, inv_temp, chunk, keep_stats=True)
+        lp_leaf, ent_leaf = lp.detach().requires_grad_(True), ent.detach().requires_grad_(True)
+        with torch.enable_grad():
+            loss, metrics = loss_fn(lp_leaf, ent_leaf)
+            grads = torch.autograd.grad(loss, (lp_leaf, ent_leaf), allow_unused=True)
+        dlp = grads[0].float().contiguous() if grads[0] is not None else torch.zeros_like(lp)
+        dent = grads[1].float().contiguous() if grads[1] is not None else None
+        with torch.no_grad():
+            # ---- LM head backward, chunked: recompute logits, turn them into dlogits in place
+            W = self.store.lm_head()
+            gW = G["embed.weight"] if cfg.tie_embeddings else G["lm_head.weight"]
+            dhr = torch.empty_like(hr)
+            for a in range(0, hr.shape[0], chunk):
+                b = min(a + chunk, hr.shape[0])
+                lg = self.logits(hr[a:b])
+                dl = C.logprob_entropy_bwd(lg, tg[a:b], lse[a:b].contiguous(), px[a:b].contiguous(), dlp[a:b].contiguous(),
+                                           dent[a:b].contiguous() if dent is not None else None, inv_temp)
+                del lg
+                self._gemm(dl, W, dhr[a:b], False, True)
+                self.linear_wgrad(dl, hr[a:b], gW)
+                self.launches += 1
+            dh = torch.zeros_like(h)
+            dh.index_add_(0, rows, dhr)
+            # ---- final norm
+            _, rstd = C.rmsnorm_fwd(x_last, None, P["final_norm.weight"], cfg.rms_eps)
+            dx = C.rmsnorm_bwd(dh, x_last, P["final_norm.weight"], rstd, None, G["final_norm.weight"], True)
+            self.launches += 3
+            del dh, dhr, h, hr
+            moe_layers = [i for i in range(cfg.num_layers) if cfg.layer_is_moe(i)]
+            for i in reversed(range(cfg.num_layers)):
+                rid = replay[:, moe_layers.index(i)] if (replay is not None and cfg.layer_is_moe(i)) else None
+                dx = self.layer_backward(i, inputs[i], dx, positions, cu_seqlens, max_seqlen, rid)
+                inputs[i] = None
+            # ---- embedding
+            G["embed.weight"].index_add_(0, tokens.long(), dx.to(G["embed.weight"].dtype))
+        return loss.detach(), metrics, lp.detach(), ent.detach()

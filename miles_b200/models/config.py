@@ -1,0 +1,199 @@
+"""Model shape configuration and presets for the Qwen3 dense / Qwen3-MoE families (and Qwen2/Llama-style
+dense models, which differ only in qk-norm and qkv bias).
+
+Preset shapes follow the reference's per-model argument files (scripts/models/qwen3-4B.py:6-22,
+scripts/models/qwen3-30B-A3B.py:14-42) and the HF ``config.json`` field names, which ``from_hf_config``
+reads (the reference cross-checks the same fields in miles/utils/arguments.py:3656-3707).
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+from typing import Any
+
+
+@dataclass
+class ModelConfig:
+    name: str = "qwen3-tiny"
+    num_layers: int = 2
+    hidden_size: int = 256
+    num_q_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 64
+    ffn_hidden_size: int = 768
+    vocab_size: int = 1024
+    rms_eps: float = 1e-6
+    rope_theta: float = 1e6
+    qk_norm: bool = True
+    qkv_bias: bool = False
+    tie_embeddings: bool = False
+    # MoE (num_experts == 0 -> dense MLP in every layer)
+    num_experts: int = 0
+    moe_top_k: int = 0
+    moe_ffn_hidden_size: int = 0
+    norm_topk_prob: bool = True
+    moe_layer_freq: int = 1  # every n-th layer is MoE (1 = all)
+    first_dense_layers: int = 0
+    max_position_embeddings: int = 40960
+    hf_architecture: str = "Qwen3ForCausalLM"
+    extra: dict[str, Any] = field(default_factory=dict)
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def q_dim(self) -> int:
+        return self.num_q_heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    @property
+    def qkv_dim(self) -> int:
+        return self.q_dim + 2 * self.kv_dim
+
+    def layer_is_moe(self, i: int) -> bool:
+        return self.is_moe and i >= self.first_dense_layers and ((i + 1) % self.moe_layer_freq == 0)
+
+    def num_params(self) -> int:
+        n = self.vocab_size * self.hidden_size * (1 if self.tie_embeddings else 2) + self.hidden_size
+        for i in range(self.num_layers):
+            n += 2 * self.hidden_size + self.qkv_dim * self.hidden_size + self.q_dim * self.hidden_size
+            if self.qk_norm:
+                n += 2 * self.head_dim
+            if self.qkv_bias:
+                n += self.qkv_dim
+            if self.layer_is_moe(i):
+                n += self.num_experts * self.hidden_size
+                n += self.num_experts * 3 * self.moe_ffn_hidden_size * self.hidden_size
+            else:
+                n += 3 * self.ffn_hidden_size * self.hidden_size
+        return n
+
+    def num_active_params(self) -> int:
+        if not self.is_moe:
+            return self.num_params()
+        n = self.num_params()
+        for i in range(self.num_layers):
+            if self.layer_is_moe(i):
+                n -= (self.num_experts - self.moe_top_k) * 3 * self.moe_ffn_hidden_size * self.hidden_size
+        return n
+
+    def to_dict(self) -> dict:
+        return asdict(self)
+
+    # ------------------------------------------------------------------ HF interop
+    def to_hf_config(self) -> dict:
+        cfg = {
+            "architectures": [self.hf_architecture],
+            "model_type": "qwen3_moe" if self.is_moe else "qwen3",
+            "hidden_size": self.hidden_size,
+            "num_hidden_layers": self.num_layers,
+            "num_attention_heads": self.num_q_heads,
+            "num_key_value_heads": self.num_kv_heads,
+            "head_dim": self.head_dim,
+            "intermediate_size": self.ffn_hidden_size,
+            "vocab_size": self.vocab_size,
+            "rms_norm_eps": self.rms_eps,
+            "rope_theta": self.rope_theta,
+            "tie_word_embeddings": self.tie_embeddings,
+            "attention_bias": self.qkv_bias,
+            "max_position_embeddings": self.max_position_embeddings,
+            "torch_dtype": "bfloat16",
+        }
+        if self.is_moe:
+            cfg.update({
+                "num_experts": self.num_experts,
+                "num_experts_per_tok": self.moe_top_k,
+                "moe_intermediate_size": self.moe_ffn_hidden_size,
+                "norm_topk_prob": self.norm_topk_prob,
+                "decoder_sparse_step": self.moe_layer_freq,
+                "mlp_only_layers": list(range(self.first_dense_layers)),
+            })
+        return cfg
+
+    @classmethod
+    def from_hf_config(cls, cfg: dict | str | Path, name: str | None = None) -> "ModelConfig":
+        if not isinstance(cfg, dict):
+            p = Path(cfg)
+            if p.is_dir():
+                p = p / "config.json"
+            cfg = json.loads(p.read_text())
+        arch = (cfg.get("architectures") or ["Qwen3ForCausalLM"])[0]
+        heads = cfg["num_attention_heads"]
+        head_dim = cfg.get("head_dim") or cfg["hidden_size"] // heads
+        is_qwen3 = "qwen3" in cfg.get("model_type", "qwen3").lower()
+        mlp_only = cfg.get("mlp_only_layers") or []
+        return cls(
+            name=name or cfg.get("_name_or_path", arch),
+            num_layers=cfg["num_hidden_layers"],
+            hidden_size=cfg["hidden_size"],
+            num_q_heads=heads,
+            num_kv_heads=cfg.get("num_key_value_heads", heads),
+            head_dim=head_dim,
+            ffn_hidden_size=cfg.get("intermediate_size", 0),
+            vocab_size=cfg["vocab_size"],
+            rms_eps=cfg.get("rms_norm_eps", 1e-6),
+            rope_theta=float(cfg.get("rope_theta", 1e6)),
+            qk_norm=is_qwen3,
+            qkv_bias=bool(cfg.get("attention_bias", not is_qwen3 and "qwen2" in cfg.get("model_type", ""))),
+            tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+            num_experts=cfg.get("num_experts", 0) or 0,
+            moe_top_k=cfg.get("num_experts_per_tok", 0) or 0,
+            moe_ffn_hidden_size=cfg.get("moe_intermediate_size", 0) or 0,
+            norm_topk_prob=bool(cfg.get("norm_topk_prob", True)),
+            moe_layer_freq=cfg.get("decoder_sparse_step", 1) or 1,
+            first_dense_layers=(max(mlp_only) + 1) if mlp_only else 0,
+            max_position_embeddings=cfg.get("max_position_embeddings", 40960),
+            hf_architecture=arch,
+        )
+
+
+def _dense(name, L, H, q, kv, ffn, tie, vocab=151936, hd=128, **kw) -> ModelConfig:
+    return ModelConfig(name=name, num_layers=L, hidden_size=H, num_q_heads=q, num_kv_heads=kv, head_dim=hd,
+                       ffn_hidden_size=ffn, vocab_size=vocab, tie_embeddings=tie, **kw)
+
+
+def _moe(name, L, H, q, kv, E, k, moe_ffn, vocab=151936, hd=128, **kw) -> ModelConfig:
+    return ModelConfig(name=name, num_layers=L, hidden_size=H, num_q_heads=q, num_kv_heads=kv, head_dim=hd,
+                       ffn_hidden_size=moe_ffn, vocab_size=vocab, num_experts=E, moe_top_k=k, moe_ffn_hidden_size=moe_ffn,
+                       hf_architecture="Qwen3MoeForCausalLM", **kw)
+
+
+PRESETS: dict[str, ModelConfig] = {
+    # CPU plumbing model of the tiny GRPO configuration
+    "qwen3-tiny": ModelConfig(),
+    "qwen3-tiny-moe": ModelConfig(name="qwen3-tiny-moe", num_experts=8, moe_top_k=2, moe_ffn_hidden_size=128,
+                                  hf_architecture="Qwen3MoeForCausalLM"),
+    # a small GPU smoke model with head_dim 128 (the kernels' native head size)
+    "qwen3-smoke": _dense("qwen3-smoke", 2, 512, 4, 2, 1024, False, vocab=4096),
+    "qwen3-smoke-moe": _moe("qwen3-smoke-moe", 2, 512, 8, 2, 16, 4, 256, vocab=4096),
+    "qwen3-0.6B": _dense("qwen3-0.6B", 28, 1024, 16, 8, 3072, True),
+    "qwen3-1.7B": _dense("qwen3-1.7B", 28, 2048, 16, 8, 6144, True),
+    "qwen3-4B": _dense("qwen3-4B", 36, 2560, 32, 8, 9728, True),
+    "qwen3-8B": _dense("qwen3-8B", 36, 4096, 32, 8, 12288, False),
+    "qwen3-14B": _dense("qwen3-14B", 40, 5120, 40, 8, 17408, False),
+    "qwen3-32B": _dense("qwen3-32B", 64, 5120, 64, 8, 25600, False),
+    "qwen3-30B-A3B": _moe("qwen3-30B-A3B", 48, 2048, 32, 4, 128, 8, 768),
+    "qwen3-235B-A22B": _moe("qwen3-235B-A22B", 94, 4096, 64, 4, 128, 8, 1536),
+    "qwen2.5-0.5B": _dense("qwen2.5-0.5B", 24, 896, 14, 2, 4864, True, hd=64, qk_norm=False, qkv_bias=True,
+                           rope_theta=1e6, hf_architecture="Qwen2ForCausalLM"),
+    "qwen2.5-7B": _dense("qwen2.5-7B", 28, 3584, 28, 4, 18944, False, vocab=152064, qk_norm=False, qkv_bias=True,
+                         hf_architecture="Qwen2ForCausalLM"),
+    "llama-3.1-8B": _dense("llama-3.1-8B", 32, 4096, 32, 8, 14336, False, vocab=128256, qk_norm=False,
+                           rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+}
+
+
+def get_config(name: str) -> ModelConfig:
+    if name in PRESETS:
+        import copy
+
+        return copy.deepcopy(PRESETS[name])
+    p = Path(name)
+    if p.exists():
+        return ModelConfig.from_hf_config(p)
+    raise KeyError(f"unknown model {name!r}; presets: {sorted(PRESETS)}")

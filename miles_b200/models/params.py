@@ -1,0 +1,183 @@
+"""Flat parameter storage shared by the trainer, the rollout engine and the weight-sync path.
+
+All parameters of one rank live in two contiguous buffers per dtype role — ``dense`` (everything that is
+replicated over expert-parallel ranks) and ``expert`` (the locally owned experts).  Every named parameter
+is a view into its buffer, so the optimizer, gradient reduction and weight hand-off operate on a handful
+of large flat tensors instead of thousands of small ones, and the trainer and a colocated engine can
+share the very same memory (weight sync then costs a version bump, not a copy).
+
+Native parameter names::
+
+    embed.weight [V,H]            final_norm.weight [H]         lm_head.weight [V,H] (absent when tied)
+    layers.i.ln1.weight [H]       layers.i.ln2.weight [H]
+    layers.i.attn.qkv.weight [(Hq+2Hk)D, H]   (+ attn.qkv.bias)  layers.i.attn.o.weight [H, Hq*D]
+    layers.i.attn.q_norm.weight [D]           layers.i.attn.k_norm.weight [D]
+    layers.i.mlp.gate_up.weight [2I,H]        layers.i.mlp.down.weight [H,I]
+    layers.i.moe.router.weight [E,H]          layers.i.moe.w1 [E_local,2I,H]   layers.i.moe.w2 [E_local,H,I]
+
+The fused layouts (q|k|v rows, gate|up rows) are what the fused kernels consume; ``hf_mapping`` converts
+to and from HuggingFace names, the role that megatron_to_hf/qwen3moe.py:6-117 plays in the reference.
+"""
+from __future__ import annotations
+
+import hashlib
+from collections import OrderedDict
+from dataclasses import dataclass
+from typing import Iterator, Optional
+
+import torch
+
+from .config import ModelConfig
+
+
+@dataclass
+class ParamSpec:
+    name: str
+    shape: tuple[int, ...]
+    group: str  # "dense" | "expert"
+    init: str  # "normal" | "ones" | "zeros"
+    offset: int = 0
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+
+def _align(n: int, a: int = 128) -> int:
+    return (n + a - 1) // a * a
+
+
+def build_specs(cfg: ModelConfig, ep_size: int = 1) -> list[ParamSpec]:
+    assert cfg.num_experts % ep_size == 0 or not cfg.is_moe, "experts must divide evenly over EP ranks"
+    H, D = cfg.hidden_size, cfg.head_dim
+    specs: list[ParamSpec] = [ParamSpec("embed.weight", (cfg.vocab_size, H), "dense", "normal")]
+    for i in range(cfg.num_layers):
+        p = f"layers.{i}."
+        specs.append(ParamSpec(p + "ln1.weight", (H,), "dense", "ones"))
+        specs.append(ParamSpec(p + "attn.qkv.weight", (cfg.qkv_dim, H), "dense", "normal"))
+        if cfg.qkv_bias:
+            specs.append(ParamSpec(p + "attn.qkv.bias", (cfg.qkv_dim,), "dense", "zeros"))
+        if cfg.qk_norm:
+            specs.append(ParamSpec(p + "attn.q_norm.weight", (D,), "dense", "ones"))
+            specs.append(ParamSpec(p + "attn.k_norm.weight", (D,), "dense", "ones"))
+        specs.append(ParamSpec(p + "attn.o.weight", (H, cfg.q_dim), "dense", "normal"))
+        specs.append(ParamSpec(p + "ln2.weight", (H,), "dense", "ones"))
+        if cfg.layer_is_moe(i):
+            el = cfg.num_experts // ep_size
+            I = cfg.moe_ffn_hidden_size
+            specs.append(ParamSpec(p + "moe.router.weight", (cfg.num_experts, H), "dense", "normal"))
+            specs.append(ParamSpec(p + "moe.w1", (el, 2 * I, H), "expert", "normal"))
+            specs.append(ParamSpec(p + "moe.w2", (el, H, I), "expert", "normal"))
+        else:
+            I = cfg.ffn_hidden_size
+            specs.append(ParamSpec(p + "mlp.gate_up.weight", (2 * I, H), "dense", "normal"))
+            specs.append(ParamSpec(p + "mlp.down.weight", (H, I), "dense", "normal"))
+    specs.append(ParamSpec("final_norm.weight", (H,), "dense", "ones"))
+    if not cfg.tie_embeddings:
+        specs.append(ParamSpec("lm_head.weight", (cfg.vocab_size, H), "dense", "normal"))
+    off = {"dense": 0, "expert": 0}
+    for s in specs:
+        s.offset = off[s.group]
+        off[s.group] += _align(s.numel)
+    return specs
+
+
+def _seed_for(seed: int, key: str) -> int:
+    h = hashlib.blake2b(f"{seed}:{key}".encode(), digest_size=8).digest()
+    return int.from_bytes(h, "little") & 0x7FFFFFFFFFFFFFFF
+
+
+class ParamStore:
+    """Owns the flat parameter (and optionally gradient) buffers of one rank."""
+
+    def __init__(self, cfg: ModelConfig, device: torch.device | str = "cpu", dtype: torch.dtype = torch.bfloat16,
+                 ep_size: int = 1, ep_rank: int = 0, init_std: float = 0.02, seed: int = 1234, init: bool = True,
+                 meta: bool = False):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.ep_size, self.ep_rank = ep_size, ep_rank
+        self.specs = build_specs(cfg, ep_size)
+        self.by_name = OrderedDict((s.name, s) for s in self.specs)
+        self.sizes = {g: sum(_align(s.numel) for s in self.specs if s.group == g) for g in ("dense", "expert")}
+        dev = torch.device("meta") if meta else self.device
+        self.flat = {g: torch.zeros(n, dtype=dtype, device=dev) for g, n in self.sizes.items()}
+        self.grad: dict[str, Optional[torch.Tensor]] = {"dense": None, "expert": None}
+        self.params: "OrderedDict[str, torch.Tensor]" = OrderedDict()
+        self.grads: "OrderedDict[str, torch.Tensor]" = OrderedDict()
+        for s in self.specs:
+            self.params[s.name] = self.flat[s.group][s.offset:s.offset + s.numel].view(s.shape)
+        self.version = 0
+        if init and not meta:
+            self.init_weights(init_std, seed)
+
+    # ------------------------------------------------------------------ init / access
+    @torch.no_grad()
+    def init_weights(self, std: float = 0.02, seed: int = 1234) -> None:
+        gen = torch.Generator(device=self.device)
+        el = self.cfg.num_experts // self.ep_size if self.cfg.is_moe else 0
+        for s in self.specs:
+            p = self.params[s.name]
+            if s.init == "ones":
+                p.fill_(1.0)
+            elif s.init == "zeros":
+                p.zero_()
+            elif s.group == "expert":
+                # one stream per *global* expert so that any EP factorisation builds the same model
+                for le in range(el):
+                    ge = self.ep_rank * el + le
+                    gen.manual_seed(_seed_for(seed, f"{s.name}:{ge}"))
+                    p[le].copy_(torch.empty(p[le].shape, dtype=torch.float32, device=self.device).normal_(0.0, std, generator=gen))
+            else:
+                gen.manual_seed(_seed_for(seed, s.name))
+                chunk = 1 << 26
+                flat = p.view(-1)
+                for a in range(0, flat.numel(), chunk):
+                    b = min(a + chunk, flat.numel())
+                    flat[a:b].copy_(torch.empty(b - a, dtype=torch.float32, device=self.device).normal_(0.0, std, generator=gen))
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        return self.params[name]
+
+    def named_parameters(self) -> Iterator[tuple[str, torch.Tensor]]:
+        return iter(self.params.items())
+
+    def lm_head(self) -> torch.Tensor:
+        return self.params["embed.weight"] if self.cfg.tie_embeddings else self.params["lm_head.weight"]
+
+    # ------------------------------------------------------------------ gradients
+    def allocate_grads(self, dtype: torch.dtype = torch.float32) -> None:
+        for g, n in self.sizes.items():
+            if self.grad[g] is None or self.grad[g].dtype != dtype:
+                self.grad[g] = torch.zeros(n, dtype=dtype, device=self.device)
+        self.grads.clear()
+        for s in self.specs:
+            self.grads[s.name] = self.grad[s.group][s.offset:s.offset + s.numel].view(s.shape)
+
+    def zero_grads(self) -> None:
+        for g in self.grad.values():
+            if g is not None:
+                g.zero_()
+
+    def free_grads(self) -> None:
+        self.grad = {"dense": None, "expert": None}
+        self.grads.clear()
+
+    def num_local_params(self) -> int:
+        return sum(s.numel for s in self.specs)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.flat.values())
+
+    @torch.no_grad()
+    def copy_from(self, other: "ParamStore") -> None:
+        for g in self.flat:
+            self.flat[g].copy_(other.flat[g].to(self.flat[g].dtype))
+        self.version = other.version
+
+    def checksum(self) -> dict[str, float]:
+        """Cheap per-group checksum used by the weight-update equality checks."""
+        return {g: float(t.float().abs().sum().item()) if t.numel() else 0.0 for g, t in self.flat.items()}

@@ -1,0 +1,142 @@
+"""Pure-PyTorch execution of the Qwen3 dense / MoE decoder over a ``ParamStore``.
+
+This is (a) the autograd oracle the hand-written sm_100a forward/backward is tested against, and (b) the
+compute path of the CPU/gloo configuration (tiny fp32 model, world size 2), for both the trainer and
+the rollout engine.  Layout conventions are shared with ``b200_impl``: packed tokens ``[T]`` with
+``cu_seqlens``, fused qkv / gate_up weights, rotate-half RoPE, softmax->top-k->renormalise routing.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from ..ops import reference as R
+from .config import ModelConfig
+from .params import ParamStore
+
+
+@dataclass
+class InferMeta:
+    """Attention metadata of one engine forward.
+
+    prefill: ``cu_seqlens`` over the packed new tokens, ``slot_mapping[t]`` = cache slot of token t.
+    decode : one token per sequence, ``block_table`` [B, max_pages], ``seq_lens`` [B] (including the new token).
+    """
+    is_prefill: bool
+    cu_seqlens: Optional[torch.Tensor] = None
+    max_seqlen: int = 0
+    slot_mapping: Optional[torch.Tensor] = None
+    block_table: Optional[torch.Tensor] = None
+    seq_lens: Optional[torch.Tensor] = None
+    page_size: int = 16
+    cu_list: list = field(default_factory=list)
+
+
+class TorchQwen3:
+    def __init__(self, cfg: ModelConfig, store: ParamStore, ep_group=None):
+        self.cfg = cfg
+        self.store = store
+        self.ep_group = ep_group
+        if store.ep_size != 1:
+            raise NotImplementedError("the PyTorch execution path keeps all experts on every rank")
+
+    # ------------------------------------------------------------------ blocks
+    def _attn_block(self, i, x, positions, cu, meta: Optional[InferMeta], kv_cache):
+        cfg, P = self.cfg, self.store.params
+        p = f"layers.{i}."
+        h = R.rmsnorm(x, P[p + "ln1.weight"], cfg.rms_eps)
+        qkv = F.linear(h, P[p + "attn.qkv.weight"], P.get(p + "attn.qkv.bias"))
+        q, k, v = R.qk_norm_rope(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"), positions,
+                                 cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rope_theta, cfg.rms_eps)
+        scale = cfg.head_dim ** -0.5
+        if meta is None or meta.is_prefill:
+            if kv_cache is not None:
+                kc, vc = kv_cache[i]
+                kc[meta.slot_mapping.long()] = k.to(kc.dtype)
+                vc[meta.slot_mapping.long()] = v.to(vc.dtype)
+            att = R.attention_varlen(q, k, v, cu, scale)
+        else:
+            kc, vc = kv_cache[i]
+            kc[meta.slot_mapping.long()] = k.to(kc.dtype)
+            vc[meta.slot_mapping.long()] = v.to(vc.dtype)
+            outs = []
+            ps = meta.page_size
+            for b in range(q.shape[0]):
+                L = int(meta.seq_lens[b])
+                pages = meta.block_table[b, : (L + ps - 1) // ps].long()
+                slots = (pages[:, None] * ps + torch.arange(ps, device=q.device)[None, :]).reshape(-1)[:L]
+                outs.append(R.attention_prefix(q[b:b + 1], kc[slots].to(q.dtype), vc[slots].to(q.dtype), L - 1, scale))
+            att = torch.cat(outs, 0)
+        o = F.linear(att.reshape(att.shape[0], -1), P[p + "attn.o.weight"])
+        return x + o
+
+    def _mlp_block(self, i, x, replay_ids=None, record=None):
+        cfg, P = self.cfg, self.store.params
+        p = f"layers.{i}."
+        h = R.rmsnorm(x, P[p + "ln2.weight"], cfg.rms_eps)
+        if cfg.layer_is_moe(i):
+            logits = F.linear(h.float(), P[p + "moe.router.weight"].float())
+            ids, w, _ = R.router_topk(logits, cfg.moe_top_k, cfg.norm_topk_prob, replay_ids)
+            if record is not None:
+                record.append(ids)
+            y = R.moe_experts(h, ids, w.to(h.dtype) if h.dtype != torch.float32 else w, P[p + "moe.w1"], P[p + "moe.w2"])
+        else:
+            y = F.linear(R.swiglu(F.linear(h, P[p + "mlp.gate_up.weight"])), P[p + "mlp.down.weight"])
+        return x + y
+
+    # ------------------------------------------------------------------ forward
+    def forward_hidden(self, tokens, positions, cu_seqlens, meta: Optional[InferMeta] = None, kv_cache=None,
+                       replay: Optional[torch.Tensor] = None, record: Optional[list] = None):
+        """tokens/positions [T] -> final-normed hidden [T,H]. ``replay`` is int32 [T, n_moe_layers, K]."""
+        cfg, P = self.cfg, self.store.params
+        x = F.embedding(tokens.long(), P["embed.weight"])
+        moe_idx = 0
+        for i in range(cfg.num_layers):
+            x = self._attn_block(i, x, positions, cu_seqlens, meta, kv_cache)
+            rid = None
+            if cfg.layer_is_moe(i):
+                if replay is not None:
+                    rid = replay[:, moe_idx]
+                moe_idx += 1
+            x = self._mlp_block(i, x, rid, record)
+        return R.rmsnorm(x, P["final_norm.weight"], cfg.rms_eps)
+
+    def logits(self, hidden_rows):
+        return F.linear(hidden_rows, self.store.lm_head())
+
+    def logprobs_entropy(self, hidden_rows, targets, inv_temp: float, chunk: int = 4096):
+        lps, ents = [], []
+        for a in range(0, hidden_rows.shape[0], chunk):
+            lp, ent = R.logprob_entropy(self.logits(hidden_rows[a:a + chunk]), targets[a:a + chunk], inv_temp)
+            lps.append(lp)
+            ents.append(ent)
+        if not lps:
+            z = hidden_rows.new_zeros((0,), dtype=torch.float32)
+            return z, z.clone()
+        return torch.cat(lps), torch.cat(ents)
+
+    # ------------------------------------------------------------------ trainer API (autograd)
+    def forward_logprobs(self, tokens, positions, cu_seqlens, row_index, targets, inv_temp, replay=None, record=None,
+                         with_grad: bool = False):
+        """Log-probs/entropy of ``targets`` predicted at packed rows ``row_index``."""
+        ctx = torch.enable_grad() if with_grad else torch.no_grad()
+        with ctx:
+            hidden = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, record=record)
+            return self.logprobs_entropy(hidden[row_index.long()], targets, inv_temp)
+
+    def set_requires_grad(self, flag: bool) -> None:
+        for t in self.store.flat.values():
+            t.requires_grad_(flag)
+        # views were created before requires_grad was set; rebuild them so autograd tracks them
+        for s in self.store.specs:
+            self.store.params[s.name] = self.store.flat[s.group][s.offset:s.offset + s.numel].view(s.shape)
+
+    def accumulate_autograd_grads(self) -> None:
+        """Move ``flat.grad`` produced by autograd into the persistent gradient buffers."""
+        for g, t in self.store.flat.items():
+            if t.grad is not None and self.store.grad[g] is not None:
+                self.store.grad[g].add_(t.grad.to(self.store.grad[g].dtype))
+                t.grad = None
