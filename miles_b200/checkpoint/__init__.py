@@ -1,0 +1,195 @@
+"""Checkpoints: native sharded format, HF safetensors import / export, resume bookkeeping.
+
+Layouts (reference: miles/backends/megatron_utils/checkpoint.py:100-198, hf_export.py:40-193,
+backends/fsdp_utils/checkpoint.py:78-250):
+
+* native : ``<dir>/iter_%07d/rank_%05d.pt`` (flat parameter buffers + optimizer state + RNG of one rank)
+  and ``meta.json``; ``<dir>/latest_checkpointed_iteration.txt`` names the newest iteration — the same
+  directory conventions as Megatron ``torch_dist`` so resume logic (``start_rollout_id = iteration + 1``)
+  and tooling carry over.
+* HF     : sharded ``model-%05d-of-%05d.safetensors`` + ``model.safetensors.index.json`` + ``config.json``
+  and a ``.complete`` marker written last.
+"""
+from __future__ import annotations
+
+import json
+import os
+import shutil
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models.hf_mapping import from_hf, hf_names
+
+LATEST = "latest_checkpointed_iteration.txt"
+
+
+def iter_dir(base: str, iteration: int) -> str:
+    return os.path.join(base, f"iter_{iteration:07d}")
+
+
+def is_native_checkpoint(path: str) -> bool:
+    return os.path.exists(os.path.join(path, LATEST)) or os.path.basename(os.path.normpath(path)).startswith("iter_")
+
+
+def latest_iteration(base: str) -> Optional[int]:
+    p = os.path.join(base, LATEST)
+    if not os.path.exists(p):
+        return None
+    txt = open(p).read().strip()
+    return int(txt) if txt.isdigit() else None
+
+
+def save_checkpoint(actor, base: str, iteration: int) -> str:
+    d = iter_dir(base, iteration)
+    os.makedirs(d, exist_ok=True)
+    rank = actor.ps.rank
+    state = {
+        "flat": {g: t.detach().cpu() for g, t in actor.store.flat.items()},
+        "version": actor.store.version,
+        "global_step": actor.global_step,
+        "rng": {"cpu": torch.get_rng_state(), "cuda": torch.cuda.get_rng_state() if actor.on_gpu else None},
+        "ep": (actor.store.ep_size, actor.store.ep_rank),
+    }
+    if actor.opt is not None and not getattr(actor.args, "no_save_optim", False):
+        sd = actor.opt.state_dict()
+        state["optimizer"] = {k: ({a: (b.detach().cpu() if isinstance(b, torch.Tensor) else b) for a, b in v.items()}
+                                  if isinstance(v, dict) else v) for k, v in sd.items()}
+    if getattr(actor, "_value_head", None) is not None:
+        state["value_head"] = actor._value_head.detach().cpu()
+    tmp = os.path.join(d, f"rank_{rank:05d}.pt.tmp")
+    torch.save(state, tmp)
+    os.replace(tmp, os.path.join(d, f"rank_{rank:05d}.pt"))
+    if dist.is_initialized():
+        dist.barrier()
+    if rank == 0:
+        with open(os.path.join(d, "meta.json"), "w") as f:
+            json.dump({"iteration": iteration, "world_size": actor.ps.world_size, "model": actor.cfg.to_dict()}, f, default=str)
+        with open(os.path.join(base, LATEST), "w") as f:
+            f.write(str(iteration))
+    return d
+
+
+def load_checkpoint(actor, path: str, step: Optional[int] = None) -> Optional[int]:
+    """Load a native checkpoint (returns its iteration) or an HF directory (returns None)."""
+    if is_native_checkpoint(path):
+        it = step if step is not None else latest_iteration(path)
+        d = iter_dir(path, it) if it is not None else path
+        f = os.path.join(d, f"rank_{actor.ps.rank:05d}.pt")
+        state = torch.load(f, map_location="cpu", weights_only=False)
+        with torch.no_grad():
+            for g, t in actor.store.flat.items():
+                t.copy_(state["flat"][g].to(t.dtype))
+        actor.store.version = state.get("version", 0)
+        if actor.opt is not None and "optimizer" in state and not getattr(actor.args, "no_load_optim", False):
+            actor.opt.load_state_dict(state["optimizer"])
+        elif actor.opt is not None:
+            actor.opt.sync_master_from_params()
+        if not getattr(actor.args, "no_load_rng", False) and "rng" in state:
+            torch.set_rng_state(state["rng"]["cpu"])
+        if getattr(actor, "_value_head", None) is not None and "value_head" in state:
+            actor._value_head.data.copy_(state["value_head"])
+        if getattr(actor.args, "finetune", False):
+            return None
+        return state.get("global_step", it)
+    if os.path.isdir(path):
+        load_hf(actor.cfg, actor.store, path)
+        if actor.opt is not None:
+            actor.opt.sync_master_from_params()
+        return None
+    raise FileNotFoundError(f"checkpoint {path} not found")
+
+
+def load_weights_into_backup(actor, tag: str, path: str, step: Optional[int] = None) -> None:
+    """Load a checkpoint into the pinned host copy ``tag`` without disturbing the live weights."""
+    actor.backup_weights("_tmp_live")
+    load_checkpoint(actor, path, step)
+    actor.backup_weights(tag)
+    actor.restore_weights("_tmp_live")
+    del actor.weights_backup["_tmp_live"]
+
+
+# ------------------------------------------------------------------ HuggingFace safetensors
+def load_hf(cfg, store, path: str, strict: bool = True) -> int:
+    from safetensors import safe_open
+
+    idx = os.path.join(path, "model.safetensors.index.json")
+    if os.path.exists(idx):
+        wm = json.load(open(idx))["weight_map"]
+        files = sorted(set(wm.values()))
+    else:
+        files = sorted(f for f in os.listdir(path) if f.endswith(".safetensors"))
+        wm = None
+    handles = {f: safe_open(os.path.join(path, f), framework="pt", device="cpu") for f in files}
+    where = dict(wm) if wm else {k: f for f, h in handles.items() for k in h.keys()}
+
+    def get(name):
+        f = where.get(name)
+        return handles[f].get_tensor(name) if f is not None else None
+
+    return from_hf(cfg, store, get, strict)
+
+
+def export_hf(actor, out_dir: str, max_shard_bytes: int = 5 << 30, tokenizer_dir: Optional[str] = None) -> str:
+    """Collective export of the live weights in HF layout; each rank writes its own shards."""
+    from safetensors.torch import save_file
+
+    cfg, store, ps = actor.cfg, actor.store, actor.ps
+    os.makedirs(out_dir, exist_ok=True)
+    marker = os.path.join(out_dir, ".complete")
+    if ps.rank == 0 and os.path.exists(marker):
+        os.remove(marker)
+    shards, cur, size = [], {}, 0
+    for hf_name, t in hf_names(cfg, store):
+        is_expert = ".experts." in hf_name
+        if not is_expert and ps.dp_cp.rank != 0:
+            continue  # replicated tensors are written once
+        nb = t.numel() * t.element_size()
+        if cur and size + nb > max_shard_bytes:
+            shards.append(cur)
+            cur, size = {}, 0
+        cur[hf_name] = t.detach().contiguous().cpu()
+        size += nb
+    if cur:
+        shards.append(cur)
+    counts = [len(shards)]
+    if dist.is_initialized() and ps.world_size > 1:
+        gathered = [None] * ps.world_size
+        dist.all_gather_object(gathered, len(shards))
+        counts = gathered
+    total = sum(counts)
+    first = sum(counts[:ps.rank])
+    weight_map = {}
+    for j, sh in enumerate(shards):
+        fname = f"model-{first + j + 1:05d}-of-{total:05d}.safetensors"
+        save_file(sh, os.path.join(out_dir, fname), metadata={"format": "pt"})
+        for k in sh:
+            weight_map[k] = fname
+    maps = [weight_map]
+    if dist.is_initialized() and ps.world_size > 1:
+        maps = [None] * ps.world_size
+        dist.all_gather_object(maps, weight_map)
+    if ps.rank == 0:
+        merged = {}
+        for m in maps:
+            merged.update(m)
+        nbytes = sum(p.numel() * p.element_size() for p in store.flat.values())
+        with open(os.path.join(out_dir, "model.safetensors.index.json"), "w") as f:
+            json.dump({"metadata": {"total_size": nbytes}, "weight_map": merged}, f, indent=1)
+        with open(os.path.join(out_dir, "config.json"), "w") as f:
+            json.dump(cfg.to_hf_config(), f, indent=1)
+        src = tokenizer_dir or getattr(actor.args, "hf_checkpoint", None)
+        if src and os.path.isdir(src):
+            for fn in os.listdir(src):
+                if fn.startswith("tokenizer") or fn in ("vocab.json", "merges.txt", "special_tokens_map.json", "generation_config.json"):
+                    shutil.copy(os.path.join(src, fn), os.path.join(out_dir, fn))
+    if dist.is_initialized():
+        dist.barrier()
+    if ps.rank == 0:
+        open(marker, "w").write("ok")
+    return out_dir
+
+
+def is_complete_hf_dir(path: str) -> bool:
+    return os.path.exists(os.path.join(path, ".complete"))

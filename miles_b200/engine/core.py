@@ -1,0 +1,540 @@
+"""In-process rollout engine: paged KV cache, continuous batching, CUDA-graph decode, sampling.
+
+The engine owns no weights of its own: it runs the same model object (and therefore the same kernels
+and the same parameter memory) as the trainer when colocated, which makes the trainer -> rollout weight
+update a version bump.  It honours the contract the reference expects from its SGLang server
+(miles/backends/sglang_utils/sglang_engine.py:126-693 and
+miles/rollout/generate_utils/generate_endpoint_utils.py:52-140): token-in / token-out generation with
+temperature / top-p / top-k / seed, stop tokens and max length, per-token log-probs of the sampled
+tokens under the same temperature, finish reason ``stop | length | abort``, the weight version(s) a
+sample was generated under, optional per-token routed experts (rollout routing replay), abort, pause /
+continue, cache flush and memory release / resume.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from ..models.torch_impl import InferMeta
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    max_new_tokens: int = 128
+    stop_token_ids: tuple = ()
+    ignore_eos: bool = False
+    sampling_seed: Optional[int] = None
+    min_new_tokens: int = 0
+    # benchmark hook (reference: rollout/generate_hub/benchmarkers.py): stop exactly at this length
+    forced_length: Optional[int] = None
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "SamplingParams":
+        d = dict(d or {})
+        stop = d.pop("stop_token_ids", None) or ()
+        kw = {k: v for k, v in d.items() if k in cls.__dataclass_fields__}
+        return cls(stop_token_ids=tuple(stop), **kw)
+
+
+@dataclass
+class Request:
+    rid: str
+    input_ids: list
+    params: SamplingParams
+    return_routed_experts: bool = False
+    output_ids: list = field(default_factory=list)
+    output_logprobs: list = field(default_factory=list)
+    routed_experts: list = field(default_factory=list)  # per token [L, K] int32 cpu tensors
+    weight_versions: list = field(default_factory=list)
+    finish_reason: Optional[str] = None
+    pages: list = field(default_factory=list)
+    slot: int = -1  # row in the running batch
+    seed: int = 0
+    t_submit: float = 0.0
+    cached_tokens: int = 0
+
+    @property
+    def seq_len(self) -> int:
+        return len(self.input_ids) + len(self.output_ids)
+
+    def result(self) -> dict:
+        """Response in the shape of the reference's /generate endpoint."""
+        meta = {
+            "output_token_logprobs": [(lp, tok) for lp, tok in zip(self.output_logprobs, self.output_ids)],
+            "finish_reason": {"type": self.finish_reason or "abort"},
+            "weight_version": self.weight_versions[-1] if self.weight_versions else 0,
+            "weight_versions": list(self.weight_versions),
+            "prompt_tokens": len(self.input_ids),
+            "completion_tokens": len(self.output_ids),
+            "cached_tokens": self.cached_tokens,
+            "id": self.rid,
+        }
+        if self.return_routed_experts and self.routed_experts:
+            meta["routed_experts"] = torch.cat(self.routed_experts, 0)
+        return {"output_ids": list(self.output_ids), "meta_info": meta}
+
+
+class PagePool:
+    """Free-list page allocator (host side). Page 0 is reserved as the dummy page of padded batch rows."""
+
+    def __init__(self, num_pages: int):
+        self.num_pages = num_pages
+        self.free = deque(range(1, num_pages))
+
+    def alloc(self, n: int) -> Optional[list]:
+        if len(self.free) < n:
+            return None
+        return [self.free.popleft() for _ in range(n)]
+
+    def release(self, pages: Sequence[int]) -> None:
+        self.free.extend(pages)
+
+    @property
+    def num_free(self) -> int:
+        return len(self.free)
+
+
+class Engine:
+    def __init__(self, model, *, max_running: int = 64, num_pages: Optional[int] = None, page_size: int = 64,
+                 max_seq_len: int = 16384, max_prefill_tokens: int = 16384, kv_mem_bytes: Optional[int] = None,
+                 use_cuda_graph: Optional[bool] = None, eos_token_id: Optional[int] = None, kv_dtype=None):
+        self.model = model
+        self.cfg = model.cfg
+        self.store = model.store
+        self.dev = self.store.device
+        self.on_gpu = self.dev.type == "cuda"
+        self.page_size = page_size
+        self.max_running = max_running
+        self.max_seq_len = max_seq_len
+        self.max_pages_per_seq = (max_seq_len + page_size - 1) // page_size
+        self.max_prefill_tokens = max_prefill_tokens
+        self.eos_token_id = eos_token_id
+        self.kv_dtype = kv_dtype or self.store.dtype
+        cfg = self.cfg
+        per_page = 2 * cfg.num_layers * page_size * cfg.num_kv_heads * cfg.head_dim * torch.empty((), dtype=self.kv_dtype).element_size()
+        if num_pages is None:
+            if kv_mem_bytes is None:
+                kv_mem_bytes = max_running * max_seq_len * per_page // page_size
+            num_pages = max(2, kv_mem_bytes // per_page)
+        self.num_pages = int(num_pages)
+        self.pool = PagePool(self.num_pages)
+        self.kv_cache: Optional[list] = None
+        self._alloc_kv()
+        self.waiting: deque = deque()
+        self.running: list = []
+        self.finished: dict = {}
+        self.paused = False
+        self.weight_version = 0
+        self._rid = itertools.count()
+        self.use_cuda_graph = self.on_gpu if use_cuda_graph is None else use_cuda_graph
+        self._graphs: dict = {}
+        self._alloc_decode_buffers()
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "retracted": 0}
+
+    # ------------------------------------------------------------------ memory
+    def _alloc_kv(self) -> None:
+        cfg = self.cfg
+        slots = self.num_pages * self.page_size
+        self.kv_cache = [(torch.zeros(slots, cfg.num_kv_heads, cfg.head_dim, dtype=self.kv_dtype, device=self.dev),
+                          torch.zeros(slots, cfg.num_kv_heads, cfg.head_dim, dtype=self.kv_dtype, device=self.dev))
+                         for _ in range(cfg.num_layers)]
+
+    def _alloc_decode_buffers(self) -> None:
+        B, dev = self.max_running, self.dev
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.d_tokens = torch.zeros(B, **i32)
+        self.d_positions = torch.zeros(B, **i32)
+        self.d_seq_lens = torch.ones(B, **i32)
+        self.d_slots = torch.zeros(B, **i32)
+        self.d_block_table = torch.zeros(B, self.max_pages_per_seq, **i32)
+        self.d_temperature = torch.ones(B, dtype=torch.float32, device=dev)
+        self.d_top_k = torch.zeros(B, **i32)
+        self.d_top_p = torch.ones(B, dtype=torch.float32, device=dev)
+        self.d_seeds = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.d_step = torch.zeros(B, **i32)
+        self.d_active = torch.zeros(B, **i32)
+        self._rows: list = []
+        self._rows_B = 0
+        self.d_out_tokens = torch.zeros(B, **i32)
+        self.d_out_logprobs = torch.zeros(B, dtype=torch.float32, device=dev)
+        self.slots_free = list(range(B - 1, -1, -1))
+        self.slot_req: list = [None] * B
+        pin = self.on_gpu
+        self.h_out = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
+        self.h_lp = torch.zeros(B, dtype=torch.float32, pin_memory=pin)
+
+    def release_memory_occupation(self, tags: Sequence[str] = ("kv_cache", "cuda_graph")) -> None:
+        """Free the KV cache and/or captured graphs (weights are shared with the trainer and stay)."""
+        assert not self.running, "release_memory_occupation with running requests; pause/abort first"
+        if "cuda_graph" in tags:
+            self._graphs.clear()
+        if "kv_cache" in tags:
+            self.kv_cache = None
+            self._graphs.clear()  # graphs hold raw cache pointers
+        if self.on_gpu:
+            torch.cuda.empty_cache()
+
+    def resume_memory_occupation(self, tags: Sequence[str] = ("kv_cache",)) -> None:
+        if "kv_cache" in tags and self.kv_cache is None:
+            self._alloc_kv()
+            self.pool = PagePool(self.num_pages)
+
+    def flush_cache(self) -> bool:
+        if self.running:
+            return False
+        self.pool = PagePool(self.num_pages)
+        return True
+
+    # ------------------------------------------------------------------ request API
+    def add_request(self, input_ids: Sequence[int], params: SamplingParams | dict | None = None, rid: Optional[str] = None,
+                    return_routed_experts: bool = False) -> str:
+        if not isinstance(params, SamplingParams):
+            params = SamplingParams.from_dict(params or {})
+        rid = rid if rid is not None else f"req-{next(self._rid)}"
+        ids = [int(t) for t in input_ids]
+        if len(ids) + 1 > self.max_seq_len:
+            ids = ids[-(self.max_seq_len - 1):]
+        req = Request(rid, ids, params, return_routed_experts)
+        req.seed = params.sampling_seed if params.sampling_seed is not None else (hash(rid) & 0x7FFFFFFF)
+        req.t_submit = time.time()
+        self.waiting.append(req)
+        return rid
+
+    def abort_request(self, rid: Optional[str] = None, abort_all: bool = False) -> int:
+        n = 0
+        for req in list(self.running):
+            if abort_all or req.rid == rid:
+                self._finish(req, "abort")
+                n += 1
+        for req in list(self.waiting):
+            if abort_all or req.rid == rid:
+                self.waiting.remove(req)
+                req.finish_reason = "abort"
+                self.finished[req.rid] = req
+                n += 1
+        return n
+
+    def pause_generation(self, mode: str = "retract") -> None:
+        """``abort``: finish everything as aborted; ``retract``: running requests go back to the queue and
+        will be re-prefilled (their generated tokens are kept); ``in_place``: keep KV and resume as is."""
+        self.paused = True
+        if mode == "abort":
+            self.abort_request(abort_all=True)
+        elif mode == "retract":
+            for req in list(self.running):
+                self._retract(req)
+
+    def continue_generation(self) -> None:
+        self.paused = False
+
+    def update_weight_version(self, version: Optional[int] = None) -> int:
+        self.weight_version = self.weight_version + 1 if version is None else int(version)
+        return self.weight_version
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def pop_finished(self) -> list:
+        out = list(self.finished.values())
+        self.finished.clear()
+        return out
+
+    # ------------------------------------------------------------------ scheduling
+    def _pages_needed(self, n_tokens: int) -> int:
+        return (n_tokens + self.page_size - 1) // self.page_size
+
+    def _retract(self, req: Request) -> None:
+        self._release(req)
+        self.running.remove(req)
+        self.waiting.appendleft(req)
+        self.stats["retracted"] += 1
+
+    def _release(self, req: Request) -> None:
+        if req.pages:
+            self.pool.release(req.pages)
+            req.pages = []
+        if req.slot >= 0:
+            self.slot_req[req.slot] = None
+            self.slots_free.append(req.slot)
+            req.slot = -1
+
+    def _finish(self, req: Request, reason: str) -> None:
+        req.finish_reason = reason
+        self._release(req)
+        if req in self.running:
+            self.running.remove(req)
+        self.finished[req.rid] = req
+
+    def _check_stop(self, req: Request, tok: int) -> Optional[str]:
+        p = req.params
+        n = len(req.output_ids)
+        if p.forced_length is not None:
+            return "length" if n >= min(p.forced_length, p.max_new_tokens) else None
+        if n >= p.min_new_tokens and not p.ignore_eos:
+            if tok in p.stop_token_ids or (self.eos_token_id is not None and tok == self.eos_token_id):
+                return "stop"
+        if n >= p.max_new_tokens or req.seq_len >= self.max_seq_len:
+            return "length"
+        return None
+
+    def step(self) -> list:
+        """One scheduler iteration (a prefill batch if requests are waiting, else one decode step)."""
+        if self.paused or self.kv_cache is None:
+            return []
+        before = set(self.finished)
+        admitted = self._admit()
+        if admitted:
+            self._prefill(admitted)
+        elif self.running:
+            self._decode()
+        return [self.finished[r] for r in self.finished if r not in before]
+
+    def _admit(self) -> list:
+        batch, tokens = [], 0
+        while self.waiting and self.slots_free:
+            req = self.waiting[0]
+            n = req.seq_len
+            if batch and tokens + n > self.max_prefill_tokens:
+                break
+            pages = self.pool.alloc(self._pages_needed(n + 1))
+            if pages is None:
+                break
+            self.waiting.popleft()
+            req.pages = pages
+            req.slot = self.slots_free.pop()
+            self.slot_req[req.slot] = req
+            batch.append(req)
+            tokens += n
+        return batch
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def _prefill(self, batch: list) -> None:
+        dev, ps = self.dev, self.page_size
+        toks, pos, slots, cu = [], [], [], [0]
+        for req in batch:
+            ids = req.input_ids + req.output_ids
+            n = len(ids)
+            toks.extend(ids)
+            pos.extend(range(n))
+            pg = torch.tensor(req.pages, dtype=torch.int64)
+            idx = torch.arange(n)
+            slots.append(pg[idx // ps] * ps + idx % ps)
+            cu.append(cu[-1] + n)
+        tokens = torch.tensor(toks, dtype=torch.int32, device=dev)
+        positions = torch.tensor(pos, dtype=torch.int32, device=dev)
+        slot_mapping = torch.cat(slots).to(torch.int32).to(dev)
+        cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+        max_len = max(b - a for a, b in zip(cu[:-1], cu[1:]))
+        meta = InferMeta(True, cu_t, max_len, slot_mapping, page_size=ps)
+        want_routes = any(r.return_routed_experts for r in batch) and self.cfg.is_moe
+        record = [] if want_routes else None
+        kw = {"max_seqlen": max_len} if self.on_gpu and hasattr(self.model, "launches") else {}
+        h = self.model.forward_hidden(tokens, positions, cu_t, meta=meta, kv_cache=self.kv_cache, record=record, **kw)
+        last = torch.tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=dev)
+        logits = self.model.logits(h[last])
+        tok, lp = self._sample(logits, batch)
+        tok_l, lp_l = tok.tolist(), lp.tolist()
+        routes = torch.stack(record, 1).cpu() if want_routes else None  # [T, L, K]
+        self.stats["prefill_tokens"] += len(toks)
+        for i, req in enumerate(batch):
+            if routes is not None and req.return_routed_experts and not req.routed_experts:
+                req.routed_experts.append(routes[cu[i]:cu[i + 1]])
+            self.running.append(req)
+            self._append_token(req, int(tok_l[i]), float(lp_l[i]))
+
+    def _sample(self, logits: torch.Tensor, reqs: list):
+        """Eager sampling for a list of requests (prefill path)."""
+        n = len(reqs)
+        if self.on_gpu and hasattr(self.model, "C"):
+            dev = self.dev
+            t = torch.tensor([r.params.temperature for r in reqs], dtype=torch.float32, device=dev)
+            k = torch.tensor([r.params.top_k if r.params.top_k else 0 for r in reqs], dtype=torch.int32, device=dev)
+            p = torch.tensor([r.params.top_p for r in reqs], dtype=torch.float32, device=dev)
+            s = torch.tensor([r.seed for r in reqs], dtype=torch.int64, device=dev)
+            st = torch.tensor([len(r.output_ids) for r in reqs], dtype=torch.int32, device=dev)
+            out = torch.empty(n, dtype=torch.int32, device=dev)
+            lp = torch.empty(n, dtype=torch.float32, device=dev)
+            self.model.C.sample_rows(logits, t, k, p, s, st, out, lp)
+            self.model.launches += 1
+            return out, lp
+        from ..ops import reference as R
+
+        toks, lps = [], []
+        for i, r in enumerate(reqs):
+            g = torch.Generator(device=logits.device).manual_seed((r.seed * 1000003 + len(r.output_ids)) & 0x7FFFFFFF)
+            tk, l = R.sample(logits[i:i + 1], r.params.temperature, r.params.top_k, r.params.top_p, g)
+            toks.append(tk)
+            lps.append(l)
+        return torch.cat(toks), torch.cat(lps)
+
+    def _append_token(self, req: Request, tok: int, lp: float) -> None:
+        req.output_ids.append(tok)
+        req.output_logprobs.append(lp)
+        if not req.weight_versions or req.weight_versions[-1] != self.weight_version:
+            req.weight_versions.append(self.weight_version)
+        reason = self._check_stop(req, tok)
+        if reason:
+            self._finish(req, reason)
+
+    # ------------------------------------------------------------------ decode
+    def _grow_pages(self) -> None:
+        """Make sure every running request owns the page its next token is written to."""
+        for req in list(self.running):
+            need = self._pages_needed(req.seq_len)
+            while len(req.pages) < need:
+                pg = self.pool.alloc(1)
+                if pg is None:
+                    victim = self.running[-1]
+                    self._retract(victim)
+                    if victim is req:
+                        break
+                    continue
+                req.pages.extend(pg)
+
+    def _bucket(self, n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        if b > 16:
+            b = (n + 15) // 16 * 16
+        return min(max(b, 1), self.max_running)
+
+    def _upload_rows(self, reqs: list, B: int) -> None:
+        """Full refresh of the device-side decode state (only when the batch composition changed)."""
+        W = self.max_pages_per_seq
+        h_i = torch.zeros(B, 6 + W, dtype=torch.int32)  # tok, pos, len, top_k, step, active, block_table...
+        h_i[:, 2] = 1
+        h_f = torch.ones(B, 2, dtype=torch.float32)
+        h_s = torch.zeros(B, dtype=torch.int64)
+        for i, r in enumerate(reqs):
+            L = r.seq_len  # tokens so far; the last one is the input of this step
+            h_i[i, 0], h_i[i, 1], h_i[i, 2] = r.output_ids[-1], L - 1, L
+            h_i[i, 3], h_i[i, 4], h_i[i, 5] = (r.params.top_k or 0), len(r.output_ids), 1
+            h_i[i, 6:6 + len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
+            h_f[i, 0], h_f[i, 1] = r.params.temperature, r.params.top_p
+            h_s[i] = r.seed
+        d_i = h_i.to(self.dev, non_blocking=False)
+        self.d_tokens[:B] = d_i[:, 0]
+        self.d_positions[:B] = d_i[:, 1]
+        self.d_seq_lens[:B] = d_i[:, 2]
+        self.d_top_k[:B] = d_i[:, 3]
+        self.d_step[:B] = d_i[:, 4]
+        self.d_active[:B] = d_i[:, 5]
+        self.d_block_table[:B] = d_i[:, 6:]
+        d_f = h_f.to(self.dev)
+        self.d_temperature[:B] = d_f[:, 0]
+        self.d_top_p[:B] = d_f[:, 1]
+        self.d_seeds[:B] = h_s.to(self.dev)
+        self._rows = list(reqs)
+        self._rows_B = B
+
+    @torch.no_grad()
+    def _decode(self) -> None:
+        ps = self.page_size
+        before_pages = {r.rid: len(r.pages) for r in self.running}
+        self._grow_pages()
+        reqs = list(self.running)
+        if not reqs:
+            return
+        n = len(reqs)
+        B = self._bucket(n)
+        same = (self._rows_B == B and len(self._rows) == n and all(a is b for a, b in zip(self._rows, reqs)))
+        if not same:
+            self._upload_rows(reqs, B)
+        else:
+            for i, r in enumerate(reqs):  # pages appended since the last step
+                for j in range(before_pages.get(r.rid, 0), len(r.pages)):
+                    self.d_block_table[i, j] = r.pages[j]
+        want_routes = self.cfg.is_moe and any(r.return_routed_experts for r in reqs)
+        routes = self._run_decode(B, want_routes)
+        if self.on_gpu:
+            self.h_out[:n].copy_(self.d_out_tokens[:n], non_blocking=True)
+            self.h_lp[:n].copy_(self.d_out_logprobs[:n], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            tok_l, lp_l = self.h_out[:n].tolist(), self.h_lp[:n].tolist()
+        else:
+            tok_l, lp_l = self.d_out_tokens[:n].tolist(), self.d_out_logprobs[:n].tolist()
+        routes_c = routes[:n].cpu() if routes is not None else None
+        self.stats["decode_tokens"] += n
+        self.stats["decode_steps"] += 1
+        for i, r in enumerate(reqs):
+            if routes_c is not None and r.return_routed_experts:
+                r.routed_experts.append(routes_c[i:i + 1])
+            self._append_token(r, int(tok_l[i]), float(lp_l[i]))
+
+    def _decode_body(self, B: int, want_routes: bool):
+        ps = self.page_size
+        pos = self.d_positions[:B]
+        page = self.d_block_table[:B].gather(1, (pos // ps).long()[:, None])[:, 0]
+        self.d_slots[:B] = page * ps + pos % ps
+        meta = InferMeta(False, None, 0, self.d_slots[:B], self.d_block_table[:B], self.d_seq_lens[:B], ps)
+        record = [] if want_routes else None
+        h = self.model.forward_hidden(self.d_tokens[:B], pos, None, meta=meta, kv_cache=self.kv_cache, record=record)
+        logits = self.model.logits(h)
+        if self.on_gpu and hasattr(self.model, "C"):
+            self.model.C.sample_rows(logits, self.d_temperature[:B], self.d_top_k[:B], self.d_top_p[:B], self.d_seeds[:B],
+                                     self.d_step[:B], self.d_out_tokens[:B], self.d_out_logprobs[:B])
+            self.model.launches += 1
+        else:
+            reqs = list(self._rows)
+            tok, lp = self._sample(logits[:len(reqs)], reqs)
+            self.d_out_tokens[:len(reqs)] = tok.to(torch.int32)
+            self.d_out_logprobs[:len(reqs)] = lp
+        # advance the device-side state so that the next step needs no host upload
+        act = self.d_active[:B]
+        self.d_tokens[:B] = torch.where(act > 0, self.d_out_tokens[:B], self.d_tokens[:B])
+        self.d_positions[:B] += act
+        self.d_seq_lens[:B] += act
+        self.d_step[:B] += act
+        return torch.stack(record, 1) if want_routes else None
+
+    def _run_decode(self, B: int, want_routes: bool):
+        if not (self.use_cuda_graph and self.on_gpu):
+            return self._decode_body(B, want_routes)
+        key = (B, want_routes)
+        entry = self._graphs.get(key)
+        if entry is None:
+            # warm-up outside capture (first-use attribute setup, allocator growth), then capture
+            launches0 = getattr(self.model, "launches", 0)
+            self._decode_body(B, want_routes)
+            torch.cuda.synchronize()
+            per_replay = getattr(self.model, "launches", 0) - launches0
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out = self._decode_body(B, want_routes)
+            entry = (g, out, per_replay)
+            self._graphs[key] = entry
+            if hasattr(self.model, "launches"):
+                self.model.launches -= per_replay  # the capture pass itself launched nothing
+        g, out, per_replay = entry
+        g.replay()
+        if hasattr(self.model, "launches"):
+            self.model.launches += per_replay
+        return out
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams] | dict | None = None,
+                 return_routed_experts: bool = False) -> list:
+        """Blocking batch generation: returns results in prompt order."""
+        rids = []
+        for i, p in enumerate(prompts):
+            sp = params[i] if isinstance(params, (list, tuple)) else params
+            rids.append(self.add_request(p, sp, return_routed_experts=return_routed_experts))
+        done: dict = {}
+        while self.has_work():
+            if self.paused:
+                raise RuntimeError("generate() called while generation is paused")
+            for req in self.step():
+                done[req.rid] = req
+        for req in self.pop_finished():
+            done.setdefault(req.rid, req)
+        return [done[r].result() for r in rids]

@@ -1,0 +1,261 @@
+"""The synchronous RL loop of one rank (SPMD: one process per GPU, trainer and engine colocated).
+
+Per rollout step (reference driver: train.py:22-150)::
+
+    generate -> [offload rollout: free KV] -> [critic.train] -> actor.train -> save
+             -> [offload train: free gradients] -> onload KV -> update_weights -> eval
+
+Every rank owns a slice of the prompt stream and generates its own groups with its in-process engine;
+the samples a rank generated are the samples it trains on, so no rollout data crosses GPUs (the
+reference ships them through the Ray object store).  Collectives appear only inside the model (expert
+parallel dispatch), in the gradient reduction and in metric aggregation.
+"""
+from __future__ import annotations
+
+import asyncio
+import copy
+import os
+import time
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .engine import Engine
+from .engine.client import EngineClient
+from .parallel.state import ParallelState, init_parallel_state
+from .rollout.base_types import RolloutFnConstructorInput, RolloutFnEvalInput, RolloutFnTrainInput
+from .rollout.train_data import (compute_rollout_metrics, convert_samples_to_train_data, flatten_groups,
+                                 postprocess_rollout_data)
+from .trainer.actor import TrainActor
+from .utils.misc import load_function, should_run_periodic_action
+from .utils.timer import Timer
+
+
+def _load_tokenizer(args):
+    path = getattr(args, "hf_checkpoint", None)
+    if not path or not os.path.isdir(path):
+        return None
+    try:
+        from transformers import AutoTokenizer
+
+        return AutoTokenizer.from_pretrained(path, trust_remote_code=True)
+    except Exception:
+        return None
+
+
+class RLLoop:
+    def __init__(self, args, ps: Optional[ParallelState] = None):
+        self.args = args
+        self.ps = ps or init_parallel_state(
+            tp=args.tensor_model_parallel_size, pp=args.pipeline_model_parallel_size, cp=args.context_parallel_size,
+            ep=args.expert_model_parallel_size, backend=None if args.distributed_backend == "nccl" else args.distributed_backend,
+            timeout_minutes=args.distributed_timeout_minutes)
+        torch.manual_seed(args.seed + self.ps.rank)
+        self.tokenizer = _load_tokenizer(args)
+        self.actor = TrainActor(args, "actor", self.ps)
+        self.critic = None
+        if getattr(args, "use_critic", False):
+            cargs = copy.copy(args)
+            cargs.load = getattr(args, "critic_load", None)
+            cargs.kl_coef, cargs.use_kl_loss = 0.0, False
+            self.critic = TrainActor(cargs, "critic", self.ps)
+        self.engine: Optional[Engine] = None
+        self.client: Optional[EngineClient] = None
+        if not getattr(args, "debug_train_only", False):
+            self._build_engine()
+        self.data_source = self._build_data_source()
+        self.rollout_fn = self._build_rollout_fn()
+        self.start_rollout_id = self._resume()
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.tracker = None
+        try:
+            from .utils.tracking import init_tracking
+
+            self.tracker = init_tracking(args, primary=self.ps.rank == 0)
+        except Exception:
+            self.tracker = None
+
+    # ------------------------------------------------------------------ construction
+    def _build_engine(self) -> None:
+        a = self.args
+        cfg = self.actor.cfg
+        local_batch = max(1, (a.rollout_batch_size * a.n_samples_per_prompt + self.ps.world_size - 1) // self.ps.world_size)
+        max_running = getattr(a, "sglang_max_running_requests", None) or min(512, max(local_batch, 1))
+        max_ctx = getattr(a, "rollout_max_context_len", None) or ((getattr(a, "rollout_max_prompt_len", None) or 1024)
+                                                                   + a.rollout_max_response_len + 8)
+        page = getattr(a, "engine_page_size", 64)
+        kv_bytes = None
+        if self.actor.on_gpu:
+            total = torch.cuda.get_device_properties(self.actor.device).total_memory
+            frac = float(getattr(a, "sglang_mem_fraction_static", 0.7))
+            budget = int(total * frac) - self.actor.store.nbytes()
+            per_tok = 2 * cfg.num_layers * cfg.num_kv_heads * cfg.head_dim * 2
+            want = max_running * (max_ctx + page) * per_tok
+            kv_bytes = max(min(budget, want), per_tok * page * 4)
+        self.engine = Engine(self.actor.model, max_running=max_running, page_size=page, max_seq_len=max_ctx,
+                             max_prefill_tokens=getattr(a, "engine_max_prefill_tokens", 16384), kv_mem_bytes=kv_bytes,
+                             use_cuda_graph=not getattr(a, "sglang_disable_cuda_graph", False) and self.actor.on_gpu,
+                             eos_token_id=getattr(self.tokenizer, "eos_token_id", None))
+        self.client = EngineClient([self.engine], self.tokenizer)
+        self.actor.connect_rollout_engines([self.engine])
+
+    def _build_data_source(self):
+        a = self.args
+        path = getattr(a, "data_source_path", None) or "miles_b200.rollout.data_source.RolloutDataSourceWithBuffer"
+        path = path.replace("miles.rollout.data_source", "miles_b200.rollout.data_source")
+        if not getattr(a, "prompt_data", None) and "Synthetic" not in path and getattr(a, "rollout_global_dataset", True):
+            path = "miles_b200.rollout.data_source.SyntheticDataSource"
+        local = copy.copy(a)
+        local.rollout_seed = a.rollout_seed + 7919 * self.ps.rank  # every rank draws its own prompt stream
+        if getattr(a, "synthetic_vocab_size", None) is None:
+            local.synthetic_vocab_size = self.actor.cfg.vocab_size
+        return load_function(path)(local, self.tokenizer)
+
+    def _build_rollout_fn(self):
+        a = self.args
+        path = getattr(a, "rollout_function_path", None)
+        if path is None:
+            path = "miles_b200.rollout.fully_async_rollout.FullyAsyncRolloutFn" if getattr(a, "fully_async", False) else \
+                "miles_b200.rollout.inference_rollout.InferenceRolloutFn"
+        obj = load_function(path)
+        local = copy.copy(a)
+        ws = self.ps.world_size
+        local.rollout_batch_size = max(1, a.rollout_batch_size // ws)
+        local.over_sampling_batch_size = max(local.rollout_batch_size, (a.over_sampling_batch_size or a.rollout_batch_size) // ws)
+        self.local_args = local
+        if isinstance(obj, type):
+            return obj(RolloutFnConstructorInput(local, self.data_source, self.client))
+        return lambda inp: obj(local, inp.rollout_id, self.data_source, evaluation=inp.evaluation)
+
+    def _resume(self) -> int:
+        a = self.args
+        if getattr(a, "start_rollout_id", None) is not None:
+            start = a.start_rollout_id
+        elif getattr(a, "load", None) and self.actor.global_step and not getattr(a, "finetune", False):
+            start = self.actor.global_step
+        else:
+            start = 0
+        if start > 0:
+            self.data_source.load(start - 1)
+        return start
+
+    # ------------------------------------------------------------------ phases
+    def generate(self, rollout_id: int) -> tuple:
+        a = self.args
+        t0 = time.perf_counter()
+        if getattr(a, "load_debug_rollout_data", None):
+            blob = torch.load(a.load_debug_rollout_data.format(rollout_id=rollout_id), weights_only=False)
+            from .utils.types import Sample
+
+            samples = [Sample.from_dict(d) for d in blob["samples"]]
+            samples = samples[self.ps.rank::self.ps.world_size] if self.ps.world_size > 1 else samples
+            return samples, {}
+        out = self.rollout_fn(RolloutFnTrainInput(rollout_id))
+        if asyncio.iscoroutine(out):
+            out = asyncio.run(out)
+        samples = flatten_groups(out.samples if hasattr(out, "samples") else out)
+        samples = postprocess_rollout_data(self.local_args, samples)
+        dt = time.perf_counter() - t0
+        metrics = dict(getattr(out, "metrics", {}) or {})
+        metrics.update(compute_rollout_metrics(a, samples, dt))
+        if getattr(a, "save_debug_rollout_data", None):
+            p = a.save_debug_rollout_data.format(rollout_id=rollout_id)
+            os.makedirs(os.path.dirname(p) or ".", exist_ok=True)
+            gathered = [[s.to_dict() for s in samples]]
+            if self.ps.world_size > 1:
+                gathered = [None] * self.ps.world_size
+                dist.all_gather_object(gathered, [s.to_dict() for s in samples])
+            if self.ps.rank == 0:
+                torch.save({"rollout_id": rollout_id, "samples": [d for g in gathered for d in g]}, p)
+        return samples, metrics
+
+    def offload_rollout(self) -> None:
+        if self.engine is not None and self.args.offload_rollout:
+            self.engine.release_memory_occupation(("kv_cache", "cuda_graph"))
+
+    def onload_rollout(self) -> None:
+        if self.engine is not None and self.args.offload_rollout:
+            self.engine.resume_memory_occupation(("kv_cache",))
+
+    def train(self, rollout_id: int, samples: list) -> dict:
+        a = self.args
+        data = convert_samples_to_train_data(a, samples)
+        local = copy.copy(self.actor.args)
+        metrics = {}
+        # every rank already holds exactly its own share: train on it without a DP re-split
+        saved = (self.actor.ps.dp_cp.size, self.actor.ps.dp_cp.rank)
+        self.actor._local_data = True
+        if self.critic is not None:
+            metrics.update({k.replace("train/", "train/critic_"): v for k, v in self.critic.train_critic(rollout_id, data).items()})
+        metrics.update(self.actor.train(rollout_id, data))
+        self.h2d_bytes += self.actor.h2d_bytes
+        return metrics
+
+    def update_weights(self) -> dict:
+        if self.engine is None or getattr(self.args, "debug_skip_weight_update", False):
+            return {}
+        return self.actor.update_weights()
+
+    # ------------------------------------------------------------------ one step / whole run
+    def step(self, rollout_id: int) -> dict:
+        a = self.args
+        T = Timer()
+        t0 = time.perf_counter()
+        metrics: dict = {}
+        samples, m = self.generate(rollout_id)
+        metrics.update(m)
+        t1 = time.perf_counter()
+        if getattr(a, "debug_rollout_only", False):
+            return metrics
+        self.offload_rollout()
+        if a.offload_train:
+            self.actor.wake_up()
+        metrics.update(self.train(rollout_id, samples))
+        t2 = time.perf_counter()
+        if should_run_periodic_action(rollout_id, a.save_interval, None, a.num_rollout):
+            self.actor.save_model(rollout_id)
+            self.data_source.save(rollout_id)
+        if a.offload_train:
+            self.actor.sleep()
+        self.onload_rollout()
+        if (rollout_id + 1) % (a.update_weights_interval or 1) == 0:
+            metrics.update(self.update_weights())
+        t3 = time.perf_counter()
+        n_tok = sum(len(s.tokens) for s in samples)
+        tot = torch.tensor([float(n_tok)], device=self.actor.device)
+        if self.ps.world_size > 1:
+            dist.all_reduce(tot)
+        metrics.update({"perf/rollout_time": t1 - t0, "perf/train_time": t2 - t1, "perf/update_weights_wall": t3 - t2,
+                        "perf/step_time": t3 - t0, "perf/step_tokens": float(tot.item()),
+                        "perf/grpo_tokens_per_s": float(tot.item()) / max(t3 - t0, 1e-9)})
+        if a.eval_interval is not None and should_run_periodic_action(rollout_id, a.eval_interval, None, a.num_rollout):
+            metrics.update(self.evaluate(rollout_id))
+        if self.tracker is not None:
+            self.tracker.log(metrics, step=rollout_id)
+        return metrics
+
+    def evaluate(self, rollout_id: int) -> dict:
+        out = self.rollout_fn(RolloutFnEvalInput(rollout_id))
+        if asyncio.iscoroutine(out):
+            out = asyncio.run(out)
+        return dict(getattr(out, "metrics", {}) or {})
+
+    def run(self) -> list:
+        a = self.args
+        history = []
+        if self.engine is not None and not getattr(a, "debug_skip_weight_update", False):
+            self.update_weights()  # engines start from the trainer's weights
+        if a.eval_interval is not None and not getattr(a, "skip_eval_before_train", False) and self.start_rollout_id == 0:
+            self.evaluate(-1)
+        for rid in range(self.start_rollout_id, a.num_rollout):
+            m = self.step(rid)
+            history.append(m)
+            if self.ps.rank == 0:
+                keys = ("rollout/raw_reward/mean", "train/pg_loss", "train/grad_norm", "train/train_rollout_logprob_abs_diff",
+                        "perf/step_time", "perf/grpo_tokens_per_s")
+                print(f"[rollout {rid}] " + " ".join(f"{k.split('/')[-1] if k.count('/')==1 else k}={m[k]:.5g}" for k in keys if k in m), flush=True)
+            if getattr(a, "debug_exit_after_rollout", None) is not None and rid >= a.debug_exit_after_rollout:
+                break
+        return history

@@ -1,0 +1,91 @@
+"""Native parameter layout <-> HuggingFace names (Qwen3 / Qwen3-MoE / Qwen2 / Llama conventions).
+
+``to_hf`` splits the fused tensors (q|k|v rows, gate|up rows, stacked experts) into the per-projection
+tensors an HF checkpoint or an external engine expects; ``from_hf`` is the inverse.  This is the role of
+the per-architecture converters in the reference's
+miles/backends/megatron_utils/megatron_to_hf/{qwen2,qwen3moe}.py (there the source layout is
+Megatron's interleaved per-group QKV; here the fused layout is plain row concatenation, so the
+conversion is pure slicing without reshuffles).
+"""
+from __future__ import annotations
+
+import re
+from typing import Iterator, Optional
+
+import torch
+
+from .config import ModelConfig
+
+
+def to_hf(cfg: ModelConfig, name: str, t: torch.Tensor, expert_offset: int = 0) -> list:
+    """One native tensor -> list of (hf_name, tensor view)."""
+    if name == "embed.weight":
+        return [("model.embed_tokens.weight", t)]
+    if name == "final_norm.weight":
+        return [("model.norm.weight", t)]
+    if name == "lm_head.weight":
+        return [("lm_head.weight", t)]
+    m = re.match(r"layers\.(\d+)\.(.+)", name)
+    assert m, f"unknown parameter {name}"
+    i, rest = int(m.group(1)), m.group(2)
+    p = f"model.layers.{i}."
+    q, kv = cfg.q_dim, cfg.kv_dim
+    if rest == "ln1.weight":
+        return [(p + "input_layernorm.weight", t)]
+    if rest == "ln2.weight":
+        return [(p + "post_attention_layernorm.weight", t)]
+    if rest in ("attn.qkv.weight", "attn.qkv.bias"):
+        sfx = rest.rsplit(".", 1)[1]
+        return [(p + f"self_attn.q_proj.{sfx}", t[:q]), (p + f"self_attn.k_proj.{sfx}", t[q:q + kv]),
+                (p + f"self_attn.v_proj.{sfx}", t[q + kv:])]
+    if rest == "attn.q_norm.weight":
+        return [(p + "self_attn.q_norm.weight", t)]
+    if rest == "attn.k_norm.weight":
+        return [(p + "self_attn.k_norm.weight", t)]
+    if rest == "attn.o.weight":
+        return [(p + "self_attn.o_proj.weight", t)]
+    if rest == "mlp.gate_up.weight":
+        I = t.shape[0] // 2
+        return [(p + "mlp.gate_proj.weight", t[:I]), (p + "mlp.up_proj.weight", t[I:])]
+    if rest == "mlp.down.weight":
+        return [(p + "mlp.down_proj.weight", t)]
+    if rest == "moe.router.weight":
+        return [(p + "mlp.gate.weight", t)]
+    if rest == "moe.w1":
+        I = t.shape[1] // 2
+        out = []
+        for e in range(t.shape[0]):
+            ge = expert_offset + e
+            out += [(p + f"mlp.experts.{ge}.gate_proj.weight", t[e, :I]), (p + f"mlp.experts.{ge}.up_proj.weight", t[e, I:])]
+        return out
+    if rest == "moe.w2":
+        return [(p + f"mlp.experts.{expert_offset + e}.down_proj.weight", t[e]) for e in range(t.shape[0])]
+    raise KeyError(name)
+
+
+def hf_names(cfg: ModelConfig, store) -> Iterator[tuple]:
+    """Iterate (hf_name, tensor) over every local parameter of ``store``."""
+    el = cfg.num_experts // store.ep_size if cfg.is_moe else 0
+    for name, t in store.named_parameters():
+        for item in to_hf(cfg, name, t, expert_offset=store.ep_rank * el):
+            yield item
+
+
+def from_hf(cfg: ModelConfig, store, get_tensor, strict: bool = True) -> int:
+    """Fill ``store`` from HF tensors; ``get_tensor(hf_name) -> tensor | None``. Returns #tensors loaded."""
+    el = cfg.num_experts // store.ep_size if cfg.is_moe else 0
+    n = 0
+    with torch.no_grad():
+        for name, dst in store.named_parameters():
+            for hf_name, view in to_hf(cfg, name, dst, expert_offset=store.ep_rank * el):
+                src = get_tensor(hf_name)
+                if src is None:
+                    if name == "lm_head.weight":
+                        src = get_tensor("model.embed_tokens.weight")
+                    if src is None:
+                        if strict:
+                            raise KeyError(f"missing tensor {hf_name} in checkpoint")
+                        continue
+                view.copy_(src.to(view.dtype))
+                n += 1
+    return n

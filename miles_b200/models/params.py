@@ -149,10 +149,12 @@ class ParamStore:
         return self.params["embed.weight"] if self.cfg.tie_embeddings else self.params["lm_head.weight"]
 
     # ------------------------------------------------------------------ gradients
-    def allocate_grads(self, dtype: torch.dtype = torch.float32) -> None:
+    def allocate_grads(self, dtype: torch.dtype = torch.float32, expert_dtype: Optional[torch.dtype] = None) -> None:
         for g, n in self.sizes.items():
-            if self.grad[g] is None or self.grad[g].dtype != dtype:
-                self.grad[g] = torch.zeros(n, dtype=dtype, device=self.device)
+            dt = expert_dtype if (g == "expert" and expert_dtype is not None) else dtype
+            if self.grad[g] is None or self.grad[g].dtype != dt:
+                self.grad[g] = None
+                self.grad[g] = torch.zeros(n, dtype=dt, device=self.device)
         self.grads.clear()
         for s in self.specs:
             self.grads[s.name] = self.grad[s.group][s.offset:s.offset + s.numel].view(s.shape)

@@ -1,0 +1,413 @@
+"""The trainer of one rank: the six-method backend contract ``init / train / update_weights / save_model /
+sleep / wake_up`` (reference: miles/ray/train_actor.py:153-184 and the Megatron actor in
+miles/backends/megatron_utils/actor.py:88-872), implemented natively on the flat parameter store.
+
+One RL step (``train``): split the rollout over data-parallel ranks -> pack token-capped micro-batches
+-> [reference-model log-probs] -> actor log-probs (the "old" policy, with routing recorded or replayed)
+-> advantages / returns (+ whitening over DP) -> ``num_steps_per_rollout`` optimizer steps of
+forward/backward over the micro-batches -> gradient reduction -> clip + fused Adam -> metrics.
+"""
+from __future__ import annotations
+
+import math
+import os
+import time
+from typing import Any, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models import ParamStore, build_model
+from ..parallel.state import ParallelState, get_parallel_state
+from ..rl.advantages import compute_advantages_and_returns
+from ..rl.losses import LossConfig, SegmentReducer, policy_loss, sft_loss, value_loss
+from ..utils.arguments import model_config_from_args
+from ..utils.misc import load_function
+from ..utils.timer import Timer, timer
+from .data import MicroBatch, build_micro_batches, split_by_dp
+from .optimizer import FlatAdam, OptimConfig
+
+_DT = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
+
+
+def choose_memory_plan(total_bytes: int, dense_params: int, expert_params: int, reserve_frac: float = 0.42) -> dict:
+    """Pick gradient / optimizer-state precision and placement that leaves ``reserve_frac`` of the device
+    for activations and the KV cache.  Bytes per parameter: bf16 weight 2 + gradient + two moments (+ master)."""
+    budget = total_bytes * (1.0 - reserve_frac)
+    n = dense_params + expert_params
+    plans = [
+        ("fp32-master", dict(expert_grad="fp32", state="fp32", master=True, offload=False), 2 + 4 + 8 + 4),
+        ("fp32-states", dict(expert_grad="bf16", state="fp32", master=False, offload=False), 2 + 2 + 8),
+        ("bf16-states", dict(expert_grad="bf16", state="bf16", master=False, offload=False), 2 + 2 + 4),
+        ("bf16-states-host", dict(expert_grad="bf16", state="bf16", master=False, offload=True), 2 + 2),
+    ]
+    for name, plan, bpp in plans:
+        if n * bpp <= budget:
+            return dict(plan, name=name)
+    return dict(plans[-1][1], name=plans[-1][0])
+
+
+class TrainActor:
+    def __init__(self, args, role: str = "actor", ps: Optional[ParallelState] = None, store: Optional[ParamStore] = None):
+        self.args = args
+        self.role = role
+        self.ps = ps or get_parallel_state()
+        self.cfg = model_config_from_args(args)
+        self.device = self.ps.device
+        self.on_gpu = self.device.type == "cuda"
+        backend = getattr(args, "model_backend", "auto")
+        want_b200 = backend == "b200" or (backend == "auto" and self.on_gpu and self.cfg.head_dim == 128)
+        self.dtype = torch.bfloat16 if want_b200 else (torch.float32 if not self.on_gpu else torch.bfloat16)
+        ep = self.ps.ep.size if self.cfg.is_moe else 1
+        if store is None:
+            store = ParamStore(self.cfg, self.device, self.dtype, ep_size=ep, ep_rank=self.ps.ep.rank if ep > 1 else 0,
+                               init_std=getattr(args, "init_std", 0.02), seed=args.seed)
+        self.store = store
+        self.ep_dispatcher = None
+        if ep > 1:
+            from ..parallel.expert_parallel import ExpertParallel
+
+            self.ep_dispatcher = ExpertParallel(self.cfg, self.ps, fused=getattr(args, "fused_comm", True))
+        self.model = build_model(self.cfg, store, "b200" if want_b200 else "torch", ep=self.ep_dispatcher)
+        self.is_torch = not want_b200
+        self.loss_cfg = LossConfig.from_args(args)
+        if getattr(args, "custom_tis_function_path", None):
+            self.loss_cfg.custom_tis_fn = load_function(args.custom_tis_function_path)
+        if getattr(args, "custom_pg_loss_reducer_function_path", None):
+            self.loss_cfg.custom_pg_reducer_fn = load_function(args.custom_pg_loss_reducer_function_path)
+        self.custom_loss_fn = load_function(args.custom_loss_function_path) if getattr(args, "custom_loss_function_path", None) else None
+        self.opt: Optional[FlatAdam] = None
+        self.plan: dict = {}
+        self.weights_backup: dict = {}   # tag -> pinned host copies of the flat buffers (ref / old_actor / teacher)
+        self.rollout_engines: list = []
+        self.global_step = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self._value_head = None
+        if role == "critic":
+            self._init_value_head()
+        self._setup_optimizer()
+        if getattr(args, "load", None):
+            from ..checkpoint import load_checkpoint
+
+            it = load_checkpoint(self, args.load, getattr(args, "ckpt_step", None))
+            if it is not None:
+                self.global_step = it
+        need_ref = (args.kl_coef != 0 or args.use_kl_loss) and role == "actor"
+        if need_ref:
+            self.backup_weights("ref")
+            if getattr(args, "ref_load", None) and args.ref_load != getattr(args, "load", None):
+                from ..checkpoint import load_weights_into_backup
+
+                load_weights_into_backup(self, "ref", args.ref_load, getattr(args, "ref_ckpt_step", None))
+
+    # ------------------------------------------------------------------ setup
+    def _init_value_head(self) -> None:
+        g = torch.Generator(device="cpu").manual_seed(self.args.seed + 17)
+        w = torch.empty(1, self.cfg.hidden_size).normal_(0, 0.02, generator=g)
+        self._value_head = w.to(self.device, torch.float32).requires_grad_(True)
+
+    def _setup_optimizer(self) -> None:
+        a = self.args
+        if getattr(a, "debug_disable_optimizer", False):
+            return
+        dense = self.store.sizes["dense"]
+        expert = self.store.sizes["expert"]
+        if self.on_gpu:
+            total = torch.cuda.get_device_properties(self.device).total_memory
+            plan = choose_memory_plan(total, dense, expert)
+        else:
+            plan = dict(expert_grad="fp32", state="fp32", master=False, offload=False, name="cpu")
+        # explicit flags override the automatic plan
+        if getattr(a, "use_precision_aware_optimizer", False) or a.exp_avg_dtype != "fp32" or a.exp_avg_sq_dtype != "fp32":
+            plan["state"] = a.exp_avg_dtype if a.exp_avg_dtype in _DT else "bf16"
+            plan["master"] = getattr(a, "main_params_dtype", "fp32") == "fp32" and plan.get("master", False)
+        if getattr(a, "optimizer_cpu_offload", False):
+            plan["offload"] = True
+        if self.store.dtype == torch.float32:
+            plan["master"] = False
+        self.plan = plan
+        self._expert_grad_dtype = torch.bfloat16 if (plan["expert_grad"] == "bf16" and self.store.dtype == torch.bfloat16) else torch.float32
+        self.store.allocate_grads(torch.float32, self._expert_grad_dtype)
+        oc = OptimConfig(lr=a.lr if self.role == "actor" else (a.critic_lr or a.lr), beta1=a.adam_beta1, beta2=a.adam_beta2,
+                         eps=a.adam_eps, weight_decay=a.weight_decay, clip_grad=a.clip_grad, state_dtype=_DT[plan["state"]],
+                         master_weights=plan["master"], offload_states=plan["offload"], lr_decay_style=a.lr_decay_style,
+                         lr_warmup_iters=a.lr_warmup_iters or 0, lr_decay_iters=a.lr_decay_iters or 0, min_lr=a.min_lr,
+                         lr_wsd_decay_iters=a.lr_wsd_decay_iters or 0)
+        self.opt = FlatAdam(self.store, oc, dp_group=self.ps.dp_cp.group, ep_group=self.ps.ep.group)
+
+    # ------------------------------------------------------------------ weight tags (ref / old_actor / teacher)
+    def backup_weights(self, tag: str) -> None:
+        """Pinned-host copy of the live weights under ``tag`` (reference: miles/utils/tensor_backper.py:22-180)."""
+        bk = self.weights_backup.get(tag)
+        if bk is None:
+            bk = {g: torch.empty(t.shape, dtype=t.dtype, pin_memory=self.on_gpu) for g, t in self.store.flat.items()}
+            self.weights_backup[tag] = bk
+        for g, t in self.store.flat.items():
+            bk[g].copy_(t, non_blocking=True)
+        if self.on_gpu:
+            torch.cuda.current_stream().synchronize()
+
+    def restore_weights(self, tag: str) -> None:
+        for g, t in self.store.flat.items():
+            t.copy_(self.weights_backup[tag][g], non_blocking=True)
+
+    class _Swapped:
+        def __init__(self, actor, tag):
+            self.a, self.tag = actor, tag
+
+        def __enter__(self):
+            self.a.backup_weights("_live")
+            self.a.restore_weights(self.tag)
+
+        def __exit__(self, *exc):
+            self.a.restore_weights("_live")
+
+    def with_weights(self, tag: str):
+        return TrainActor._Swapped(self, tag)
+
+    # ------------------------------------------------------------------ forward passes
+    def _forward_logprobs(self, mb: MicroBatch, replay=None, record=None):
+        inv_t = 1.0 / self.args.rollout_temperature
+        if self.is_torch:
+            return self.model.forward_logprobs(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t,
+                                               replay=replay, record=record)
+        return self.model.forward_logprobs(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t,
+                                           replay=replay, record=record, max_seqlen=mb.max_seqlen)
+
+    def _replay_for(self, mb: MicroBatch, phase: str):
+        a = self.args
+        if not self.cfg.is_moe:
+            return None
+        if a.use_rollout_routing_replay and mb.replay is not None:
+            return mb.replay
+        if a.use_routing_replay and phase == "train":
+            return mb.extras.get("recorded_routing")
+        return None
+
+    @torch.no_grad()
+    def compute_log_probs(self, mbs: list, key: str = "log_probs", with_entropy: bool = False) -> None:
+        for mb in mbs:
+            record = [] if (self.cfg.is_moe and self.args.use_routing_replay and not self.args.use_rollout_routing_replay
+                            and key == "log_probs") else None
+            lp, ent = self._forward_logprobs(mb, self._replay_for(mb, "logprob"), record)
+            mb.extras[key] = lp
+            if with_entropy:
+                mb.extras["entropy"] = ent
+            if record:
+                mb.extras["recorded_routing"] = torch.stack(record, 1)
+
+    # ------------------------------------------------------------------ the RL step
+    def _stage(self, data: dict) -> list:
+        a = self.args
+        if getattr(self, "_local_data", False):
+            ids = list(range(len(data["tokens"])))  # the caller already holds exactly this rank's share
+        else:
+            ids = split_by_dp(data, self.ps.dp_cp.size, balance=getattr(a, "balance_data", False))[self.ps.dp_cp.rank]
+        lens = [len(data["tokens"][i]) for i in ids]
+        n_mb = None
+        moe_layers = sum(self.cfg.layer_is_moe(i) for i in range(self.cfg.num_layers))
+        kw = dict(pin=self.on_gpu, num_moe_layers=moe_layers, top_k=self.cfg.moe_top_k, sample_ids=ids)
+        if a.use_dynamic_batch_size:
+            from .data import num_micro_batches_for
+
+            n_mb = num_micro_batches_for(lens, a.max_tokens_per_gpu) if lens else 0
+            if self.ps.world_size > 1:
+                t = torch.tensor([n_mb], dtype=torch.int64, device=self.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                n_mb = int(t.item())
+            if self.ps.world_size > 1:
+                mbs = build_micro_batches(data, num_micro_batches=max(n_mb, 1), **kw)
+            else:
+                mbs = build_micro_batches(data, max_tokens_per_gpu=a.max_tokens_per_gpu, **kw)
+        else:
+            mbs = build_micro_batches(data, micro_batch_size=a.micro_batch_size, **kw)
+        out = []
+        for mb in mbs:
+            d = mb.to_device(self.device)
+            self.h2d_bytes += d.h2d_bytes
+            out.append(d)
+        return out
+
+    def _advantages(self, mbs: list) -> None:
+        a = self.args
+        if getattr(a, "disable_compute_advantages_and_returns", False):
+            return
+        for mb in mbs:
+            adv, ret, kl = compute_advantages_and_returns(
+                advantage_estimator=a.advantage_estimator, rewards=mb.rewards, cu=mb.resp_cu, loss_mask=mb.loss_mask,
+                log_probs=mb.extras.get("log_probs") if not a.use_rollout_logprobs else mb.rollout_log_probs,
+                ref_log_probs=mb.extras.get("ref_log_probs"), values=mb.extras.get("values"),
+                teacher_log_probs=mb.teacher_log_probs if a.use_opd else None, kl_coef=a.kl_coef, kl_loss_type=a.kl_loss_type,
+                gamma=a.gamma, lambd=a.lambd, normalize_advantages=False, opd_kl_coef=a.opd_kl_coef if a.use_opd else 0.0)
+            mb.extras["advantages"], mb.extras["returns"], mb.extras["kl"] = adv, ret, kl
+        if a.normalize_advantages and mbs:
+            from ..rl.advantages import whiten
+
+            allv = torch.cat([mb.extras["advantages"] for mb in mbs])
+            allm = torch.cat([mb.loss_mask for mb in mbs])
+            w = whiten(allv, allm, self.ps.dp_cp.group)
+            off = 0
+            for mb in mbs:
+                n = mb.loss_mask.numel()
+                mb.extras["advantages"] = w[off:off + n]
+                off += n
+
+    def _loss_closure(self, mb: MicroBatch, scale: float):
+        a, lc = self.args, self.loss_cfg
+        reducer = SegmentReducer(mb.seg, mb.loss_mask, mb.denoms, per_token=a.calculate_per_token_loss, num_samples=mb.num_samples)
+
+        def fn(lp, ent):
+            if a.loss_type == "sft_loss":
+                loss, m = sft_loss(lc, lp, reducer=reducer)
+            elif a.loss_type == "custom_loss":
+                loss, m = self.custom_loss_fn(a, mb, lp, ent, reducer)
+            else:
+                loss, m = policy_loss(lc, lp, ent, old_log_probs=mb.extras.get("log_probs"), advantages=mb.extras["advantages"],
+                                      reducer=reducer, rollout_log_probs=mb.rollout_log_probs,
+                                      ref_log_probs=mb.extras.get("ref_log_probs"))
+            return loss * scale, m
+
+        return fn
+
+    def train(self, rollout_id: int, data: dict) -> dict:
+        a = self.args
+        T = Timer()
+        t_start = time.perf_counter()
+        with T.context("data_preprocess"):
+            mbs = self._stage(data)
+        n_tokens_local = sum(mb.num_tokens for mb in mbs)
+        need_old = not (a.use_rollout_logprobs or a.skip_actor_forward_only) or a.use_routing_replay and not a.use_rollout_routing_replay
+        if a.loss_type == "sft_loss":
+            need_old = False
+        if "ref" in self.weights_backup and a.loss_type == "policy_loss":
+            with T.context("ref_log_probs"), self.with_weights("ref"):
+                self.compute_log_probs(mbs, "ref_log_probs")
+        if need_old:
+            with T.context("log_probs"):
+                self.compute_log_probs(mbs, "log_probs", with_entropy=getattr(a, "use_rollout_entropy", False))
+        if a.loss_type == "policy_loss":
+            self._advantages(mbs)
+        metrics_acc: dict = {}
+        grad_norm = torch.zeros((), device=self.device)
+        with T.context("actor_train"):
+            steps = a.num_steps_per_rollout or 1
+            per_step = max(1, math.ceil(len(mbs) / steps))
+            gbs = a.global_batch_size or max(1, len(data["tokens"]))
+            for s in range(steps):
+                chunk = mbs[s * per_step:(s + 1) * per_step]
+                if not chunk:
+                    continue
+                self.store.zero_grads()
+                if a.calculate_per_token_loss:
+                    tok = torch.stack([mb.loss_mask.sum() for mb in chunk]).sum()
+                    if self.ps.world_size > 1:
+                        dist.all_reduce(tok, group=self.ps.dp_cp.group)
+                    scale = 1.0 / max(float(tok.item()), 1.0)
+                else:
+                    scale = 1.0 / gbs
+                for mb in chunk:
+                    m = self._forward_backward(mb, scale)
+                    for k, v in m.items():
+                        metrics_acc[k] = metrics_acc.get(k, 0.0) + v.detach().float() * scale
+                self._reduce_grads()
+                if self.opt is not None:
+                    grad_norm = self.opt.step(1.0)
+                self.global_step += 1
+        if self.on_gpu:
+            torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t_start
+        out = self._finalize_metrics(metrics_acc, grad_norm, n_tokens_local, elapsed, len(mbs))
+        if getattr(a, "keep_old_actor", False):
+            self.backup_weights("old_actor")
+        if a.ref_update_interval and "ref" in self.weights_backup and (rollout_id + 1) % a.ref_update_interval == 0:
+            self.backup_weights("ref")
+        return out
+
+    def _forward_backward(self, mb: MicroBatch, scale: float) -> dict:
+        inv_t = 1.0 / self.args.rollout_temperature
+        fn = self._loss_closure(mb, scale)
+        replay = self._replay_for(mb, "train")
+        if self.is_torch:
+            self.model.set_requires_grad(True)
+            lp, ent = self.model.forward_logprobs(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t,
+                                                  replay=replay, with_grad=True)
+            loss, m = fn(lp, ent)
+            loss.backward()
+            self.model.accumulate_autograd_grads()
+            self.model.set_requires_grad(False)
+            return m
+        _, m, _, _ = self.model.forward_backward(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t, fn,
+                                                 replay=replay, max_seqlen=mb.max_seqlen)
+        return m
+
+    def _reduce_grads(self) -> None:
+        """Sum dense gradients over dp x cp and expert gradients over the experts' own data-parallel group."""
+        if self.ps.world_size <= 1:
+            return
+        g = self.store.grad
+        if self.ps.dp_cp.size > 1 and g["dense"] is not None and g["dense"].numel():
+            dist.all_reduce(g["dense"], group=self.ps.dp_cp.group)
+        if self.ps.expert_dp.size > 1 and g["expert"] is not None and g["expert"].numel():
+            dist.all_reduce(g["expert"], group=self.ps.expert_dp.group)
+
+    def _finalize_metrics(self, acc: dict, grad_norm, n_tokens_local: int, elapsed: float, n_mb: int) -> dict:
+        keys = sorted(acc)
+        vals = torch.stack([acc[k].reshape(()) for k in keys]) if keys else torch.zeros(0, device=self.device)
+        extra = torch.tensor([float(n_tokens_local)], device=self.device)
+        if self.ps.world_size > 1:
+            if keys:
+                dist.all_reduce(vals, group=self.ps.dp_cp.group)
+            dist.all_reduce(extra)
+        out = {f"train/{k}": float(v) for k, v in zip(keys, vals.tolist())}
+        out["train/grad_norm"] = float(grad_norm)
+        if self.opt is not None:
+            from .optimizer import lr_at
+
+            out["train/lr"] = lr_at(self.opt.cfg, max(self.opt.step_count - 1, 0))
+        out["train/step"] = self.global_step
+        out["perf/actor_train_time"] = elapsed
+        out["perf/actor_train_tok_per_s"] = float(extra[0]) / max(elapsed, 1e-9)
+        out["perf/num_micro_batches"] = n_mb
+        return out
+
+    # ------------------------------------------------------------------ critic (PPO)
+    @torch.no_grad()
+    def compute_values(self, mbs: list) -> None:
+        for mb in mbs:
+            h = self.model.forward_hidden(mb.tokens, mb.positions, mb.cu_seqlens) if self.is_torch else \
+                self.model.forward_hidden(mb.tokens, mb.positions, mb.cu_seqlens, max_seqlen=mb.max_seqlen)
+            mb.extras["values"] = (h[mb.rows].float() @ self._value_head.t())[:, 0]
+
+    # ------------------------------------------------------------------ weight update, offload, checkpoints
+    def connect_rollout_engines(self, engines: list) -> None:
+        self.rollout_engines = list(engines)
+
+    def update_weights(self) -> dict:
+        from ..weight_sync import sync_weights
+
+        with Timer().context("update_weights"):
+            return sync_weights(self, self.rollout_engines)
+
+    def sleep(self) -> None:
+        """Release trainer-only device memory (gradients) so that the rollout engine can use it."""
+        with Timer().context("sleep"):
+            self.store.free_grads()
+            if self.on_gpu:
+                torch.cuda.empty_cache()
+
+    def wake_up(self) -> None:
+        with Timer().context("wake_up"):
+            if not self.store.grads:
+                self.store.allocate_grads(torch.float32, getattr(self, "_expert_grad_dtype", torch.float32))
+
+    def save_model(self, rollout_id: int, force_sync: bool = False) -> None:
+        from ..checkpoint import save_checkpoint
+
+        with Timer().context("save_model"):
+            if getattr(self.args, "save", None):
+                save_checkpoint(self, self.args.save, rollout_id)
+            if getattr(self.args, "save_hf", None):
+                from ..checkpoint import export_hf
+
+                export_hf(self, self.args.save_hf.format(rollout_id=rollout_id))

@@ -1,0 +1,368 @@
+"""Command-line surface of ``train.py`` / ``train_async.py`` / ``train_multi_lora_async.py``.
+
+The parser is assembled from three sources so that launch scripts written for the reference keep
+working:
+
+1. ``flag_table.FLAG_GROUPS`` — the framework's own flag groups (cluster, train, rollout, data, eval,
+   algo, lora, debug, ...), names and defaults as in miles/utils/arguments.py:106-2589;
+2. ``TRAINER_FLAGS`` — the subset of Megatron-LM model/optimizer/parallelism flags that the reference's
+   launchers actually pass (shape flags, ``--tensor-model-parallel-size``, ``--lr-decay-style`` ...); the
+   trainer here consumes them directly instead of forwarding to Megatron;
+3. engine passthrough — every ``--sglang-<name>`` / ``--eval-sglang-<name>`` option is accepted and
+   collected into ``args.sglang_*`` (mirrors miles/backends/sglang_utils/arguments.py:110-207); the
+   in-process engine reads the ones it implements (mem fraction, max running requests, cuda-graph
+   batch sizes, page size, chunked prefill size ...).
+
+``validate_args`` performs the cross-flag checks and derivations of ``miles_validate_args``
+(miles/utils/arguments.py:2848-3523) that apply to this backend and rejects features that are not
+built rather than ignoring them silently.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import re
+from typing import Any, Optional, Sequence
+
+from .flag_table import FLAG_GROUPS
+
+_KIND = {"i": int, "f": float, "s": str, "j": json.loads}
+
+# (flag, kind, default, extra) — Megatron-LM flags consumed natively by this trainer
+TRAINER_FLAGS = [
+    # parallelism
+    ("--tensor-model-parallel-size", "i", 1, {}), ("--pipeline-model-parallel-size", "i", 1, {}),
+    ("--context-parallel-size", "i", 1, {}), ("--expert-model-parallel-size", "i", 1, {}),
+    ("--expert-tensor-parallel-size", "i", None, {}), ("--sequence-parallel", "b", False, {}),
+    ("--virtual-pipeline-model-parallel-size", "i", None, {}), ("--cp-comm-type", "s", "p2p", {"choices": ["p2p", "a2a", "allgather"]}),
+    ("--decoder-first-pipeline-num-layers", "i", None, {}), ("--decoder-last-pipeline-num-layers", "i", None, {}),
+    ("--use-distributed-optimizer", "B", True, {}), ("--overlap-grad-reduce", "B", True, {}),
+    ("--overlap-param-gather", "B", True, {}), ("--accumulate-allreduce-grads-in-fp32", "b", False, {}),
+    # model shape
+    ("--num-layers", "i", None, {}), ("--hidden-size", "i", None, {}), ("--ffn-hidden-size", "i", None, {}),
+    ("--num-attention-heads", "i", None, {}), ("--group-query-attention", "b", False, {}),
+    ("--num-query-groups", "i", None, {}), ("--kv-channels", "i", None, {}), ("--vocab-size", "i", None, {}),
+    ("--make-vocab-size-divisible-by", "i", 128, {}), ("--normalization", "s", "RMSNorm", {}),
+    ("--norm-epsilon", "f", 1e-6, {}), ("--swiglu", "b", False, {}), ("--disable-bias-linear", "b", False, {}),
+    ("--add-qkv-bias", "b", False, {}), ("--qk-layernorm", "b", False, {}),
+    ("--untie-embeddings-and-output-weights", "b", False, {}), ("--position-embedding-type", "s", "rope", {}),
+    ("--use-rotary-position-embeddings", "b", False, {}), ("--rotary-base", "f", 1e6, {}),
+    ("--rotary-percent", "f", 1.0, {}), ("--max-position-embeddings", "i", 40960, {}), ("--seq-length", "i", 4096, {}),
+    ("--attention-softmax-in-fp32", "b", False, {}), ("--attention-backend", "s", "flash", {}),
+    ("--attention-dropout", "f", 0.0, {}), ("--hidden-dropout", "f", 0.0, {}), ("--transformer-impl", "s", "native", {}),
+    ("--spec", "s", None, {"nargs": "+"}), ("--no-rope-fusion", "b", False, {}), ("--no-masked-softmax-fusion", "b", False, {}),
+    ("--no-gradient-accumulation-fusion", "b", False, {}), ("--attention-output-gate", "b", False, {}),
+    ("--apply-layernorm-1p", "b", False, {}),
+    # MoE
+    ("--num-experts", "i", None, {}), ("--moe-router-topk", "i", 2, {}), ("--moe-ffn-hidden-size", "i", None, {}),
+    ("--moe-layer-freq", "s", "1", {}), ("--moe-router-score-function", "s", "softmax", {}),
+    ("--moe-router-pre-softmax", "b", False, {}), ("--moe-router-dtype", "s", "fp32", {}),
+    ("--moe-router-load-balancing-type", "s", "none", {}), ("--moe-aux-loss-coeff", "f", 0.0, {}),
+    ("--moe-grouped-gemm", "b", False, {}), ("--moe-token-dispatcher-type", "s", "alltoall", {}),
+    ("--moe-permute-fusion", "b", False, {}), ("--moe-router-enable-expert-bias", "b", False, {}),
+    ("--moe-router-bias-update-rate", "f", 0.0, {}), ("--moe-router-topk-scaling-factor", "f", None, {}),
+    ("--moe-shared-expert-intermediate-size", "i", None, {}), ("--moe-shared-expert-gate", "b", False, {}),
+    ("--moe-enable-deepep", "b", False, {}), ("--moe-token-drop-policy", "s", "probs", {}),
+    ("--moe-router-num-groups", "i", None, {}), ("--moe-router-group-topk", "i", None, {}),
+    ("--moe-router-padding-for-quantization", "b", False, {}), ("--moe-latent-size", "i", None, {}),
+    # MLA (accepted for shape files; rejected by the validator until the model family is built)
+    ("--multi-latent-attention", "b", False, {}), ("--q-lora-rank", "i", None, {}), ("--kv-lora-rank", "i", None, {}),
+    ("--qk-head-dim", "i", None, {}), ("--v-head-dim", "i", None, {}), ("--qk-pos-emb-head-dim", "i", None, {}),
+    ("--rotary-scaling-factor", "f", None, {}), ("--use-rope-scaling", "b", False, {}), ("--mscale", "f", None, {}),
+    ("--mscale-all-dim", "f", None, {}), ("--original-max-position-embeddings", "i", None, {}),
+    ("--beta-fast", "f", None, {}), ("--beta-slow", "f", None, {}), ("--no-position-embedding", "b", False, {}),
+    # optimizer / schedule
+    ("--optimizer", "s", "adam", {"choices": ["adam", "sgd", "muon"]}), ("--lr", "f", 1e-6, {}), ("--min-lr", "f", 0.0, {}),
+    ("--lr-decay-style", "s", "constant", {"choices": ["constant", "linear", "cosine", "WSD"]}),
+    ("--lr-warmup-iters", "i", 0, {}), ("--lr-decay-iters", "i", None, {}), ("--lr-wsd-decay-iters", "i", None, {}),
+    ("--lr-warmup-fraction", "f", None, {}), ("--weight-decay", "f", 0.1, {}), ("--adam-beta1", "f", 0.9, {}),
+    ("--adam-beta2", "f", 0.98, {}), ("--adam-eps", "f", 1e-8, {}), ("--clip-grad", "f", 1.0, {}),
+    ("--use-precision-aware-optimizer", "b", False, {}), ("--optimizer-cpu-offload", "b", False, {}),
+    ("--overlap-cpu-optimizer-d2h-h2d", "b", False, {}), ("--exp-avg-dtype", "s", "fp32", {"choices": ["fp32", "bf16", "fp16", "fp8"]}),
+    ("--exp-avg-sq-dtype", "s", "fp32", {"choices": ["fp32", "bf16", "fp16", "fp8"]}),
+    ("--main-params-dtype", "s", "fp32", {"choices": ["fp32", "bf16"]}), ("--offload-optimizer-states", "b", False, {}),
+    # precision
+    ("--bf16", "b", True, {}), ("--fp16", "b", False, {}), ("--fp8-format", "s", None, {}), ("--fp8-recipe", "s", None, {}),
+    ("--fp8-param-gather", "b", False, {}), ("--fp4-format", "s", None, {}), ("--te-precision-config-file", "s", None, {}),
+    ("--num-layers-at-start-in-bf16", "i", 0, {}), ("--num-layers-at-end-in-bf16", "i", 0, {}),
+    ("--reuse-grad-buf-for-mxfp8-param-ag", "b", False, {}),
+    # memory / recompute
+    ("--recompute-granularity", "s", "full", {"choices": ["full", "selective", "none"]}),
+    ("--recompute-method", "s", "uniform", {}), ("--recompute-num-layers", "i", 1, {}),
+    # checkpoint / misc
+    ("--load", "s", None, {}), ("--save", "s", None, {}), ("--save-interval", "i", None, {}), ("--ckpt-step", "i", None, {}),
+    ("--save-retain-interval", "i", None, {}), ("--async-save", "b", False, {}), ("--no-save-optim", "b", False, {}),
+    ("--no-load-optim", "b", False, {}), ("--no-load-rng", "b", False, {}), ("--finetune", "b", False, {}),
+    ("--seed", "i", 1234, {}), ("--global-batch-size", "i", None, {}), ("--micro-batch-size", "i", 1, {}),
+    ("--calculate-per-token-loss", "b", False, {}), ("--distributed-backend", "s", "nccl", {}),
+    ("--distributed-timeout-minutes", "i", 10, {}), ("--eval-interval", "i", None, {}), ("--low-memory-resume", "b", False, {}),
+    ("--mtp-num-layers", "i", None, {}), ("--mtp-loss-scaling-factor", "f", 0.2, {}), ("--custom-config-path", "s", None, {}),
+    ("--padded-vocab-size", "i", None, {}), ("--wandb-project", "s", None, {}), ("--deterministic-mode", "b", False, {}),
+    ("--no-check-for-nan-in-loss-and-grad", "b", False, {}), ("--log-interval", "i", 1, {}),
+    ("--tokenizer-type", "s", "HuggingFaceTokenizer", {}), ("--tokenizer-model", "s", None, {}),
+    # native extensions of this framework
+    ("--model-preset", "s", None, {}), ("--model-backend", "s", "auto", {"choices": ["auto", "b200", "torch"]}),
+    ("--init-std", "f", 0.02, {}), ("--engine-page-size", "i", 64, {}), ("--engine-max-prefill-tokens", "i", 16384, {}),
+    ("--fused-comm", "B", True, {}), ("--weight-sync-quant", "s", "none", {"choices": ["none", "mxfp8", "nvfp4", "fp8_block"]}),
+]
+
+_UNBUILT = {
+    "multi_latent_attention": "multi-latent attention models (DeepSeek / Kimi / GLM-5 families)",
+    "moe_router_enable_expert_bias": "aux-loss-free expert-bias routing",
+}
+
+
+def _add(group, flag: str, kind: str, default: Any, extra: dict) -> None:
+    names = [flag] + list(extra.get("aliases", []))
+    kw: dict = {}
+    if "dest" in extra:
+        kw["dest"] = extra["dest"]
+    if kind == "b":
+        group.add_argument(*names, action="store_true", default=bool(default) if default is not None else False, **kw)
+    elif kind == "nb":
+        group.add_argument(*names, action="store_false", default=True if default is None else default, **kw)
+    elif kind == "B":
+        group.add_argument(*names, action=argparse.BooleanOptionalAction, default=default, **kw)
+    elif kind == "a":
+        group.add_argument(*names, action="append", type=_KIND.get(extra.get("type", "s"), str), default=default, **kw)
+    else:
+        if "choices" in extra:
+            kw["choices"] = extra["choices"]
+        if "nargs" in extra:
+            kw["nargs"] = extra["nargs"]
+        group.add_argument(*names, type=_KIND[kind], default=default, **kw)
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser("miles_b200", allow_abbrev=False, conflict_handler="resolve")
+    seen: set = set()
+    for gname, flags in FLAG_GROUPS.items():
+        g = p.add_argument_group(gname)
+        for flag, kind, default, extra in flags:
+            if flag in seen:
+                continue
+            seen.add(flag)
+            _add(g, flag, kind, default, extra)
+    g = p.add_argument_group("trainer")
+    for flag, kind, default, extra in TRAINER_FLAGS:
+        if flag in seen:
+            continue
+        seen.add(flag)
+        _add(g, flag, kind, default, extra)
+    return p
+
+
+_ENGINE_RE = re.compile(r"^--(eval-)?sglang-([a-z0-9-]+)$")
+
+
+def _parse_engine_passthrough(rest: Sequence[str], ns: argparse.Namespace) -> list:
+    """Collect ``--sglang-x [v ...]`` / ``--eval-sglang-x`` into namespace attributes; return leftovers."""
+    left, i = [], 0
+    while i < len(rest):
+        tok = rest[i]
+        key, _, inline = tok.partition("=")
+        m = _ENGINE_RE.match(key)
+        if not m:
+            left.append(tok)
+            i += 1
+            continue
+        name = ("eval_" if m.group(1) else "") + "sglang_" + m.group(2).replace("-", "_")
+        vals = [inline] if inline else []
+        i += 1
+        while not inline and i < len(rest) and not rest[i].startswith("--"):
+            vals.append(rest[i])
+            i += 1
+        if not vals:
+            v: Any = True
+        else:
+            conv = []
+            for s in vals:
+                try:
+                    conv.append(json.loads(s))
+                except Exception:
+                    conv.append(s)
+            v = conv[0] if len(conv) == 1 else conv
+        setattr(ns, name, v)
+    return left
+
+
+def parse_args(argv: Optional[Sequence[str]] = None, validate: bool = True, add_custom_arguments=None) -> argparse.Namespace:
+    parser = build_parser()
+    if add_custom_arguments is not None:
+        add_custom_arguments(parser)
+    ns, rest = parser.parse_known_args(argv)
+    left = _parse_engine_passthrough(rest, ns)
+    if left:
+        # user rollout / generate functions may declare extra flags through ``fn.add_arguments``
+        extra_parser = argparse.ArgumentParser(add_help=False, allow_abbrev=False)
+        used = _load_user_arguments(ns, extra_parser)
+        if used:
+            ns2, left = extra_parser.parse_known_args(left)
+            for k, v in vars(ns2).items():
+                setattr(ns, k, v)
+        if left:
+            parser.error(f"unrecognized arguments: {' '.join(left)}")
+    if validate:
+        validate_args(ns)
+    return ns
+
+
+def _load_user_arguments(ns, parser) -> bool:
+    from .misc import load_function
+
+    used = False
+    for attr in ("rollout_function_path", "custom_generate_function_path", "custom_rm_path", "data_source_path"):
+        path = getattr(ns, attr, None)
+        if not path:
+            continue
+        try:
+            fn = load_function(path)
+        except Exception:
+            continue
+        adder = getattr(fn, "add_arguments", None)
+        if adder is not None:
+            adder(parser)
+            used = True
+    return used
+
+
+def _default(ns, name: str, value: Any) -> None:
+    if getattr(ns, name, None) is None:
+        setattr(ns, name, value)
+
+
+def validate_args(args: argparse.Namespace) -> argparse.Namespace:
+    for attr, what in _UNBUILT.items():
+        if getattr(args, attr, False):
+            raise NotImplementedError(f"--{attr.replace('_', '-')}: {what} is not built in this framework yet")
+    if getattr(args, "custom_config_path", None):
+        import yaml
+
+        with open(args.custom_config_path) as f:
+            for k, v in (yaml.safe_load(f) or {}).items():
+                setattr(args, k, v)
+    # ---- algorithm
+    assert not (args.kl_coef != 0 and args.kl_loss_coef != 0), "only one of --kl-coef and --kl-loss-coef can be set"
+    if args.advantage_estimator in ("reinforce_plus_plus", "reinforce_plus_plus_baseline"):
+        assert args.normalize_advantages, f"{args.advantage_estimator} requires --normalize-advantages"
+    if args.use_rollout_logprobs:
+        assert not args.use_tis, "--use-rollout-logprobs and --use-tis are mutually exclusive"
+    if args.get_mismatch_metrics:
+        assert args.custom_tis_function_path is not None, "--get-mismatch-metrics needs --custom-tis-function-path"
+    _default(args, "eps_clip_high", args.eps_clip)
+    _default(args, "eval_reward_key", getattr(args, "reward_key", None))
+    if args.use_rollout_routing_replay:
+        args.use_routing_replay = True
+    if getattr(args, "use_rollout_indexer_replay", False):
+        args.use_indexer_replay = True
+    args.use_critic = args.advantage_estimator == "ppo"
+    if args.use_critic:
+        assert args.kl_coef == 0, "shared actor/critic PPO does not support reward-level KL; use --use-kl-loss"
+    _default(args, "critic_load", args.load)
+    _default(args, "critic_lr", args.lr)
+    if getattr(args, "critic_save", None) is None and args.save is not None:
+        args.critic_save = args.save.rstrip("/") + "_critic"
+    if (args.kl_coef != 0 or args.use_kl_loss) and args.ref_load is not None and not os.path.exists(args.ref_load):
+        raise FileNotFoundError(f"ref_load {args.ref_load} does not exist")
+    if args.use_opd:
+        if args.opd_type is None:
+            raise ValueError("--opd-type must be given with --use-opd")
+        if args.opd_type == "megatron" and args.opd_teacher_load is None:
+            raise ValueError("--opd-teacher-load is required with --opd-type megatron")
+    # ---- batching
+    if args.use_dynamic_batch_size:
+        assert args.max_tokens_per_gpu is not None, "--use-dynamic-batch-size needs --max-tokens-per-gpu"
+        _default(args, "log_probs_max_tokens_per_gpu", args.max_tokens_per_gpu)
+    if args.num_steps_per_rollout is not None:
+        gbs = args.rollout_batch_size * args.n_samples_per_prompt // args.num_steps_per_rollout
+        if args.global_batch_size is not None:
+            assert args.global_batch_size == gbs, (
+                f"global_batch_size {args.global_batch_size} != rollout_batch_size*n_samples_per_prompt//num_steps_per_rollout = {gbs}")
+        args.global_batch_size = gbs
+    elif args.global_batch_size is None and args.rollout_batch_size is not None:
+        args.global_batch_size = args.rollout_batch_size * args.n_samples_per_prompt
+    if args.n_samples_per_prompt == 1:
+        args.grpo_std_normalization = False
+    _default(args, "over_sampling_batch_size", args.rollout_batch_size)
+    assert args.over_sampling_batch_size >= args.rollout_batch_size, "--over-sampling-batch-size must be >= --rollout-batch-size"
+    if args.num_epoch is None:
+        assert args.num_rollout is not None, "set --num-rollout or --num-epoch"
+    if args.rollout_max_context_len is not None:
+        _default(args, "rollout_max_prompt_len", args.rollout_max_context_len - 1)
+        assert args.rollout_max_prompt_len <= args.rollout_max_context_len - 1
+    _default(args, "eval_max_context_len", args.rollout_max_context_len)
+    # ---- placement / offload
+    if getattr(args, "offload", False):
+        args.offload_train = True
+        args.offload_rollout = True
+    world = args.actor_num_nodes * args.actor_num_gpus_per_node
+    if args.colocate:
+        _default(args, "offload_train", True)
+        _default(args, "offload_rollout", True)
+        args.rollout_num_gpus = world
+    _default(args, "offload_train", False)
+    _default(args, "offload_rollout", False)
+    _default(args, "rollout_num_gpus", world)
+    assert not (args.debug_rollout_only and args.debug_train_only), "--debug-rollout-only and --debug-train-only are exclusive"
+    if args.load_debug_rollout_data is not None:
+        args.debug_train_only = True
+    if args.dump_details is not None:
+        args.save_debug_rollout_data = f"{args.dump_details}/rollout_data/{{rollout_id}}.pt"
+        args.save_debug_train_data = f"{args.dump_details}/train_data/{{rollout_id}}_{{rank}}.pt"
+    if args.ci_test and not args.debug_rollout_only and not args.debug_train_only and not args.ci_disable_weight_update_checker:
+        args.check_weight_update_equal = True
+    if args.update_weight_transfer_mode in ("p2p", "disk-delta"):
+        assert not args.colocate, f"--update-weight-transfer-mode {args.update_weight_transfer_mode} is not compatible with --colocate"
+    if args.update_weight_transfer_mode == "disk-delta":
+        assert args.update_weight_disk_dir, "disk-delta needs --update-weight-disk-dir"
+    if args.save_interval is not None:
+        assert args.save is not None, "--save is required with --save-interval"
+    if args.lora_rank > 0:
+        assert args.target_modules is not None, "--target-modules is required when LoRA is enabled"
+        tm = args.target_modules
+        if tm == "all-linear":
+            mods = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
+        else:
+            mods = [m.strip() for m in tm.split(",")] if isinstance(tm, str) else list(tm)
+        if args.exclude_modules:
+            ex = {m.strip() for m in args.exclude_modules.split(",")}
+            mods = [m for m in mods if m not in ex]
+        args.target_modules = mods
+    # ---- parallel layout of this trainer: DP x TP x EP on one box (PP/CP sizes are validated by the topology)
+    tp, pp, cp = args.tensor_model_parallel_size, args.pipeline_model_parallel_size, args.context_parallel_size
+    assert world % (tp * pp * cp) == 0, f"world size {world} is not divisible by tp*pp*cp = {tp * pp * cp}"
+    args.world_size = world
+    args.data_parallel_size = world // (tp * pp * cp)
+    if args.sequence_parallel and tp == 1:
+        args.sequence_parallel = False
+    # ---- engine knobs derived from the passthrough
+    _default(args, "sglang_mem_fraction_static", 0.7 if args.colocate else 0.85)
+    _default(args, "sglang_max_running_requests", None)
+    _default(args, "sglang_server_concurrency", 512)
+    return args
+
+
+def model_config_from_args(args):
+    """Build a ``ModelConfig`` from a preset, an HF checkpoint dir, or Megatron-style shape flags."""
+    from ..models.config import ModelConfig, get_config
+
+    if getattr(args, "model_preset", None):
+        return get_config(args.model_preset)
+    if getattr(args, "hf_checkpoint", None) and os.path.exists(os.path.join(args.hf_checkpoint, "config.json")):
+        return ModelConfig.from_hf_config(args.hf_checkpoint)
+    assert args.num_layers and args.hidden_size and args.num_attention_heads, \
+        "model shape needs --model-preset, --hf-checkpoint or the --num-layers/--hidden-size/... flags"
+    heads = args.num_attention_heads
+    moe = bool(args.num_experts)
+    return ModelConfig(
+        name=getattr(args, "model_name", None) or "custom",
+        num_layers=args.num_layers, hidden_size=args.hidden_size, num_q_heads=heads,
+        num_kv_heads=args.num_query_groups or heads, head_dim=args.kv_channels or args.hidden_size // heads,
+        ffn_hidden_size=args.ffn_hidden_size or 0, vocab_size=args.padded_vocab_size or args.vocab_size,
+        rms_eps=args.norm_epsilon, rope_theta=float(args.rotary_base), qk_norm=bool(args.qk_layernorm),
+        qkv_bias=bool(args.add_qkv_bias), tie_embeddings=not args.untie_embeddings_and_output_weights,
+        num_experts=args.num_experts or 0, moe_top_k=args.moe_router_topk if moe else 0,
+        moe_ffn_hidden_size=(args.moe_ffn_hidden_size or 0) if moe else 0,
+        hf_architecture="Qwen3MoeForCausalLM" if moe else "Qwen3ForCausalLM",
+    )

@@ -1,0 +1,60 @@
+"""Trainer -> rollout-engine weight update.
+
+Session protocol of the reference (miles/backends/megatron_utils/update_weight/mixin.py:309-389):
+``pause_generation(mode) -> flush_cache (not for in_place) -> begin -> buckets -> update_weight_version ->
+end -> continue_generation``.  Modes here:
+
+* **shared**   — colocated engine running on the trainer's own ``ParamStore``: nothing is copied, the
+  update is the version bump (the B200-first answer to CUDA-IPC bucket passing).
+* **copy**     — engine with its own store on the same device / process: flat-buffer device copies
+  (optionally re-quantised to MXFP8 / NVFP4 by the fused kernels in ``weight_sync.reshard``).
+* **p2p**      — engines on other GPUs of the box: the trainer's shards are written straight into the
+  engines' weight buffers over NVLink from inside a kernel (``weight_sync.p2p``); NCCL broadcast is the
+  measured baseline.
+"""
+from __future__ import annotations
+
+import time
+from typing import Sequence
+
+import torch
+
+
+def sync_weights(actor, engines: Sequence, mode: str | None = None) -> dict:
+    args = actor.args
+    t0 = time.perf_counter()
+    pause_mode = getattr(args, "pause_generation_mode", "retract")
+    moved = 0
+    for e in engines:
+        e.pause_generation(pause_mode)
+        if pause_mode != "in_place":
+            e.flush_cache()
+    t_paused = time.perf_counter()
+    for e in engines:
+        if e.store is actor.store:
+            continue  # shared memory: nothing to move
+        with torch.no_grad():
+            for g, t in e.store.flat.items():
+                src = actor.store.flat[g]
+                if src.numel() == t.numel():
+                    t.copy_(src.to(t.dtype), non_blocking=True)
+                    moved += src.numel() * src.element_size()
+                else:
+                    from .reshard import reshard_into
+
+                    moved += reshard_into(actor.store, e.store, g)
+    if actor.on_gpu:
+        torch.cuda.synchronize()
+    version = actor.store.version
+    for e in engines:
+        e.update_weight_version(version)
+        e.continue_generation()
+    t1 = time.perf_counter()
+    if getattr(args, "check_weight_update_equal", False):
+        for e in engines:
+            a, b = actor.store.checksum(), e.store.checksum()
+            for g in a:
+                if e.store.flat[g].numel() == actor.store.flat[g].numel():
+                    assert abs(a[g] - b[g]) <= 1e-3 * max(1.0, abs(a[g])), f"weight update mismatch in group {g}: {a[g]} vs {b[g]}"
+    return {"perf/update_weights_time": t1 - t_paused, "perf/update_weights_total_time": t1 - t0,
+            "perf/update_weights_bytes": moved, "weight_version": version}
