@@ -2,6 +2,7 @@
 // asynchronous on the given stream and performs no allocation.
 #pragma once
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 
 namespace mb {
@@ -90,5 +91,27 @@ void quant_fp8_block128(const void* x, uint8_t* q, float* scales, long long rows
                         cudaStream_t s);
 void fake_int4_quant(const void* x, void* y, void* scale, void* zero, long long rows, long long cols, int group_rows,
                      int group_cols, bool symmetric, cudaStream_t s);
+
+// ---- ep_comm.cu: expert-parallel exchange over NVLink peer memory
+constexpr int kMaxPeers = 8;
+struct EpPeers {
+  void* xrecv[kMaxPeers];                 // peer receive regions [nranks][cap][H] bf16
+  int* meta[kMaxPeers];                   // per received row: (local expert, source slot)
+  int* counts[kMaxPeers];                 // [nranks] rows sent by each source
+  unsigned long long* flags[kMaxPeers];   // [nranks] dispatch arrival epochs
+  void* yback[kMaxPeers];                 // peer return regions [T*K][H] bf16
+  unsigned long long* flags2[kMaxPeers];  // [nranks] return arrival epochs
+  const int* send_counts;                 // local: true number of entries bound for each rank
+};
+void ep_dispatch(const void* x, const int* ids, const int* dest_row, const int* offsets, const EpPeers& peers, int me,
+                 int nranks, int experts_per_rank, int n_entries, int row_div, int H, int cap, unsigned long long* ctrl,
+                 int* status, cudaStream_t s);
+void ep_wait(const unsigned long long* flags, int nranks, unsigned long long* ctrl, int which, int* status, cudaStream_t s);
+void ep_return(const void* yp, const int* recv_dest_row, const int* meta, const int* counts, const EpPeers& peers, int me,
+               int nranks, int cap, int H, unsigned long long* ctrl, int* status, cudaStream_t s);
+int symm_alloc(size_t nbytes, void** ptr, char* handle64);
+int symm_open(const char* handle64, void** ptr);
+int symm_close(void* ptr);
+int symm_free(void* ptr);
 
 }  // namespace mb

@@ -164,7 +164,7 @@ std::vector<at::Tensor> moe_build_permutation(const at::Tensor& ids, int64_t E, 
   const int T = ids.size(0), K = ids.size(1);
   TORCH_CHECK(max_rows % 128 == 0, "max_rows must be a multiple of 128");
   auto o = ids.options();
-  at::Tensor counts = at::empty({E}, o), offsets = at::empty({E + 1}, o), dest = at::empty({T * K}, o);
+  at::Tensor counts = at::empty({E}, o), offsets = at::empty({E + 1}, o), dest = at::full({T * K}, -1, o);
   at::Tensor src = at::empty({max_rows}, o), tg = at::zeros({max_rows / 128}, o), nt = at::empty({1}, o);
   mb::moe_build_permutation(ids.data_ptr<int>(), T, K, E, max_rows, counts.data_ptr<int>(), offsets.data_ptr<int>(),
                             dest.data_ptr<int>(), src.data_ptr<int>(), tg.data_ptr<int>(), nt.data_ptr<int>(), cur_stream());

@@ -1,0 +1,95 @@
+// Bindings of the symmetric-memory allocator and the expert-parallel exchange kernels.
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include "launchers.h"
+
+namespace {
+
+cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+// Allocates device memory that peers can map; returns (address, 64-byte IPC handle).
+std::pair<int64_t, pybind11::bytes> symm_alloc(int64_t nbytes) {
+  void* p = nullptr;
+  char h[64];
+  const int rc = mb::symm_alloc(static_cast<size_t>(nbytes), &p, h);
+  TORCH_CHECK(rc == 0, "symm_alloc failed with CUDA error ", rc);
+  return {reinterpret_cast<int64_t>(p), pybind11::bytes(h, 64)};
+}
+int64_t symm_open(const std::string& handle) {
+  TORCH_CHECK(handle.size() == 64, "an IPC handle is 64 bytes");
+  void* p = nullptr;
+  const int rc = mb::symm_open(handle.data(), &p);
+  TORCH_CHECK(rc == 0, "symm_open failed with CUDA error ", rc);
+  return reinterpret_cast<int64_t>(p);
+}
+void symm_close(int64_t p) { mb::symm_close(reinterpret_cast<void*>(p)); }
+void symm_free(int64_t p) { mb::symm_free(reinterpret_cast<void*>(p)); }
+
+// A non-owning tensor over raw device memory.
+at::Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> shape, at::ScalarType dtype, int64_t device) {
+  auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, device);
+  return at::from_blob(reinterpret_cast<void*>(ptr), shape, [](void*) {}, opts);
+}
+
+mb::EpPeers make_peers(const std::vector<int64_t>& xrecv, const std::vector<int64_t>& meta, const std::vector<int64_t>& counts,
+                       const std::vector<int64_t>& flags, const std::vector<int64_t>& yback, const std::vector<int64_t>& flags2) {
+  mb::EpPeers p{};
+  const size_t n = xrecv.size();
+  TORCH_CHECK(n <= mb::kMaxPeers, "at most ", mb::kMaxPeers, " expert-parallel ranks");
+  for (size_t i = 0; i < n; ++i) {
+    p.xrecv[i] = reinterpret_cast<void*>(xrecv[i]);
+    p.meta[i] = reinterpret_cast<int*>(meta[i]);
+    p.counts[i] = reinterpret_cast<int*>(counts[i]);
+    p.flags[i] = reinterpret_cast<unsigned long long*>(flags[i]);
+    p.yback[i] = reinterpret_cast<void*>(yback[i]);
+    p.flags2[i] = reinterpret_cast<unsigned long long*>(flags2[i]);
+  }
+  return p;
+}
+
+void ep_dispatch(const at::Tensor& x, const at::Tensor& ids, const at::Tensor& dest_row, const at::Tensor& offsets,
+                 const at::Tensor& send_counts, const std::vector<int64_t>& xrecv, const std::vector<int64_t>& meta,
+                 const std::vector<int64_t>& counts, const std::vector<int64_t>& flags, const std::vector<int64_t>& yback,
+                 const std::vector<int64_t>& flags2, int64_t me, int64_t experts_per_rank, int64_t row_div, int64_t cap,
+                 at::Tensor& ctrl, at::Tensor& status) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.size(-1) % 8 == 0, "bad x");
+  const c10::cuda::CUDAGuard guard(x.device());
+  mb::EpPeers p = make_peers(xrecv, meta, counts, flags, yback, flags2);
+  p.send_counts = send_counts.data_ptr<int>();
+  mb::ep_dispatch(x.data_ptr(), ids.data_ptr<int>(), dest_row.data_ptr<int>(), offsets.data_ptr<int>(), p, me, xrecv.size(),
+                  experts_per_rank, ids.numel(), row_div, x.size(-1), cap,
+                  reinterpret_cast<unsigned long long*>(ctrl.data_ptr<int64_t>()), status.data_ptr<int>(), cur_stream());
+}
+
+void ep_wait(const at::Tensor& flags, int64_t nranks, at::Tensor& ctrl, int64_t which, at::Tensor& status) {
+  const c10::cuda::CUDAGuard guard(flags.device());
+  mb::ep_wait(reinterpret_cast<const unsigned long long*>(flags.data_ptr<int64_t>()), nranks,
+              reinterpret_cast<unsigned long long*>(ctrl.data_ptr<int64_t>()), which, status.data_ptr<int>(), cur_stream());
+}
+
+void ep_return(const at::Tensor& yp, const at::Tensor& recv_dest_row, const at::Tensor& meta_local, const at::Tensor& counts_local,
+               const std::vector<int64_t>& xrecv, const std::vector<int64_t>& meta, const std::vector<int64_t>& counts,
+               const std::vector<int64_t>& flags, const std::vector<int64_t>& yback, const std::vector<int64_t>& flags2,
+               int64_t me, int64_t cap, at::Tensor& ctrl, at::Tensor& status) {
+  TORCH_CHECK(yp.is_cuda() && yp.scalar_type() == at::kBFloat16 && yp.is_contiguous(), "bad yp");
+  const c10::cuda::CUDAGuard guard(yp.device());
+  mb::EpPeers p = make_peers(xrecv, meta, counts, flags, yback, flags2);
+  mb::ep_return(yp.data_ptr(), recv_dest_row.data_ptr<int>(), meta_local.data_ptr<int>(), counts_local.data_ptr<int>(), p, me,
+                xrecv.size(), cap, yp.size(-1), reinterpret_cast<unsigned long long*>(ctrl.data_ptr<int64_t>()),
+                status.data_ptr<int>(), cur_stream());
+}
+
+}  // namespace
+
+void register_comm(pybind11::module_& m) {
+  m.def("symm_alloc", &symm_alloc);
+  m.def("symm_open", &symm_open);
+  m.def("symm_close", &symm_close);
+  m.def("symm_free", &symm_free);
+  m.def("tensor_from_ptr", &tensor_from_ptr);
+  m.def("ep_dispatch", &ep_dispatch);
+  m.def("ep_wait", &ep_wait);
+  m.def("ep_return", &ep_return);
+}

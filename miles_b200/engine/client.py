@@ -77,7 +77,7 @@ class EngineClient:
         while self._futures:
             progressed = False
             for e in self.engines:
-                if e.has_work() and not e.paused:
+                if e.sync is not None or (e.has_work() and not e.paused):
                     for req in e.step():
                         self._resolve(req)
                     progressed = True
@@ -114,7 +114,7 @@ def decode_routed_experts(meta: dict):
     if raw is None:
         return None
     if isinstance(raw, str):
-        arr = np.frombuffer(base64.b64decode(raw), dtype=np.int32)
+        arr = np.frombuffer(base64.b64decode(raw), dtype=np.int32).copy()
         shp = meta.get("routed_experts_shape")
         return arr.reshape(shp) if shp else arr
     return np.asarray(raw, dtype=np.int32)

@@ -105,8 +105,13 @@ class PagePool:
 class Engine:
     def __init__(self, model, *, max_running: int = 64, num_pages: Optional[int] = None, page_size: int = 64,
                  max_seq_len: int = 16384, max_prefill_tokens: int = 16384, kv_mem_bytes: Optional[int] = None,
-                 use_cuda_graph: Optional[bool] = None, eos_token_id: Optional[int] = None, kv_dtype=None):
+                 use_cuda_graph: Optional[bool] = None, eos_token_id: Optional[int] = None, kv_dtype=None,
+                 sync=None, ep_decode=None):
         self.model = model
+        self.sync = sync            # lockstep agreement across expert-parallel ranks (None = independent engine)
+        self.ep_decode = ep_decode  # small expert-parallel exchange used by decode steps (graph friendly)
+        self.last_mode = 0
+        self._graph_pool = None
         self.cfg = model.cfg
         self.store = model.store
         self.dev = self.store.device
@@ -138,6 +143,8 @@ class Engine:
         self._graphs: dict = {}
         self._alloc_decode_buffers()
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "retracted": 0}
+        self.d2h_bytes = 0  # bytes read back from the device (sampled tokens, log-probs, routing)
+        self.h2d_bytes = 0
 
     # ------------------------------------------------------------------ memory
     def _alloc_kv(self) -> None:
@@ -286,16 +293,31 @@ class Engine:
         return None
 
     def step(self) -> list:
-        """One scheduler iteration (a prefill batch if requests are waiting, else one decode step)."""
-        if self.paused or self.kv_cache is None:
+        """One scheduler iteration: a prefill batch if requests can be admitted, else one decode step.
+
+        With ``sync`` every expert-parallel rank agrees on the kind of iteration (2 prefill, 1 decode, 0 idle);
+        ranks without matching work run a one-token dummy forward so that the MoE exchanges stay aligned."""
+        if self.kv_cache is None:
             return []
         before = set(self.finished)
-        admitted = self._admit()
-        if admitted:
+        admitted = [] if self.paused else self._admit()
+        local = 2 if admitted else (1 if (self.running and not self.paused) else 0)
+        mode = self.sync.agree(local) if self.sync is not None else local
+        self.last_mode = mode
+        if mode == 2:
             self._prefill(admitted)
-        elif self.running:
+        elif mode == 1:
             self._decode()
         return [self.finished[r] for r in self.finished if r not in before]
+
+    def drain(self) -> None:
+        """Keep stepping (with dummy work) until every rank of the lockstep group is idle."""
+        if self.sync is None:
+            return
+        while True:
+            self.step()
+            if self.last_mode == 0:
+                break
 
     def _admit(self) -> list:
         batch, tokens = [], 0
@@ -320,6 +342,8 @@ class Engine:
     def _prefill(self, batch: list) -> None:
         dev, ps = self.dev, self.page_size
         toks, pos, slots, cu = [], [], [], [0]
+        if not batch:  # lockstep dummy: one token written to the reserved page 0
+            toks, pos, slots, cu = [0], [0], [torch.zeros(1, dtype=torch.int64)], [0, 1]
         for req in batch:
             ids = req.input_ids + req.output_ids
             n = len(ids)
@@ -339,11 +363,15 @@ class Engine:
         record = [] if want_routes else None
         kw = {"max_seqlen": max_len} if self.on_gpu and hasattr(self.model, "launches") else {}
         h = self.model.forward_hidden(tokens, positions, cu_t, meta=meta, kv_cache=self.kv_cache, record=record, **kw)
+        if not batch:
+            return
         last = torch.tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=dev)
         logits = self.model.logits(h[last])
         tok, lp = self._sample(logits, batch)
         tok_l, lp_l = tok.tolist(), lp.tolist()
         routes = torch.stack(record, 1).cpu() if want_routes else None  # [T, L, K]
+        self.d2h_bytes += 8 * len(batch) + (routes.numel() * 4 if routes is not None else 0)
+        self.h2d_bytes += 12 * len(toks) + 4 * len(cu)
         self.stats["prefill_tokens"] += len(toks)
         for i, req in enumerate(batch):
             if routes is not None and req.return_routed_experts and not req.routed_experts:
@@ -389,6 +417,8 @@ class Engine:
     def _grow_pages(self) -> None:
         """Make sure every running request owns the page its next token is written to."""
         for req in list(self.running):
+            if req not in self.running:  # retracted as a victim earlier in this pass
+                continue
             need = self._pages_needed(req.seq_len)
             while len(req.pages) < need:
                 pg = self.pool.alloc(1)
@@ -442,11 +472,11 @@ class Engine:
         ps = self.page_size
         before_pages = {r.rid: len(r.pages) for r in self.running}
         self._grow_pages()
-        reqs = list(self.running)
-        if not reqs:
+        reqs = list(self.running) if not self.paused else []
+        if not reqs and self.sync is None:
             return
         n = len(reqs)
-        B = self._bucket(n)
+        B = self._bucket(max(n, 1))
         same = (self._rows_B == B and len(self._rows) == n and all(a is b for a, b in zip(self._rows, reqs)))
         if not same:
             self._upload_rows(reqs, B)
@@ -455,7 +485,16 @@ class Engine:
                 for j in range(before_pages.get(r.rid, 0), len(r.pages)):
                     self.d_block_table[i, j] = r.pages[j]
         want_routes = self.cfg.is_moe and any(r.return_routed_experts for r in reqs)
-        routes = self._run_decode(B, want_routes)
+        saved_ep = getattr(self.model, "ep", None)
+        if self.ep_decode is not None:
+            self.model.ep = self.ep_decode
+        try:
+            routes = self._run_decode(B, want_routes)
+        finally:
+            if self.ep_decode is not None:
+                self.model.ep = saved_ep
+        if n == 0:
+            return
         if self.on_gpu:
             self.h_out[:n].copy_(self.d_out_tokens[:n], non_blocking=True)
             self.h_lp[:n].copy_(self.d_out_logprobs[:n], non_blocking=True)
@@ -464,6 +503,7 @@ class Engine:
         else:
             tok_l, lp_l = self.d_out_tokens[:n].tolist(), self.d_out_logprobs[:n].tolist()
         routes_c = routes[:n].cpu() if routes is not None else None
+        self.d2h_bytes += 8 * n + (routes_c.numel() * 4 if routes_c is not None else 0)
         self.stats["decode_tokens"] += n
         self.stats["decode_steps"] += 1
         for i, r in enumerate(reqs):
@@ -509,12 +549,16 @@ class Engine:
             torch.cuda.synchronize()
             per_replay = getattr(self.model, "launches", 0) - launches0
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(g, pool=self._graph_pool):
                 out = self._decode_body(B, want_routes)
             entry = (g, out, per_replay)
             self._graphs[key] = entry
             if hasattr(self.model, "launches"):
-                self.model.launches -= per_replay  # the capture pass itself launched nothing
+                self.model.launches -= 2 * per_replay  # neither the warm-up nor the capture pass produced tokens
+            # the warm-up run advanced the device-side decode state; rewind it before the first real replay
+            self._upload_rows(list(self._rows), B)
         g, out, per_replay = entry
         g.replay()
         if hasattr(self.model, "launches"):
@@ -538,3 +582,19 @@ class Engine:
         for req in self.pop_finished():
             done.setdefault(req.rid, req)
         return [done[r].result() for r in rids]
+
+
+class LockstepSync:
+    """Agreement on the kind of engine iteration across expert-parallel ranks (MAX over a tiny CPU tensor)."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+
+        self.dist = dist
+        self.group = group
+        self.buf = torch.zeros(1, dtype=torch.int32)
+
+    def agree(self, mode: int) -> int:
+        self.buf[0] = mode
+        self.dist.all_reduce(self.buf, op=self.dist.ReduceOp.MAX, group=self.group)
+        return int(self.buf[0])

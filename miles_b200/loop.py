@@ -94,7 +94,14 @@ class RLLoop:
             per_tok = 2 * cfg.num_layers * cfg.num_kv_heads * cfg.head_dim * 2
             want = max_running * (max_ctx + page) * per_tok
             kv_bytes = max(min(budget, want), per_tok * page * 4)
-        self.engine = Engine(self.actor.model, max_running=max_running, page_size=page, max_seq_len=max_ctx,
+        sync = ep_decode = None
+        if self.actor.ep_dispatcher is not None:
+            from .engine.core import LockstepSync
+            from .parallel.expert_parallel import ExpertParallel
+
+            sync = LockstepSync(self.ps.gloo_world if self.ps.backend != "gloo" else None)
+            ep_decode = ExpertParallel(cfg, self.ps, fused=getattr(a, "fused_comm", True), max_tokens=max(max_running, 16))
+        self.engine = Engine(self.actor.model, sync=sync, ep_decode=ep_decode, max_running=max_running, page_size=page, max_seq_len=max_ctx,
                              max_prefill_tokens=getattr(a, "engine_max_prefill_tokens", 16384), kv_mem_bytes=kv_bytes,
                              use_cuda_graph=not getattr(a, "sglang_disable_cuda_graph", False) and self.actor.on_gpu,
                              eos_token_id=getattr(self.tokenizer, "eos_token_id", None))
@@ -155,6 +162,8 @@ class RLLoop:
         out = self.rollout_fn(RolloutFnTrainInput(rollout_id))
         if asyncio.iscoroutine(out):
             out = asyncio.run(out)
+        if self.engine is not None:
+            self.engine.drain()  # expert-parallel ranks keep serving dummy iterations until all are done
         samples = flatten_groups(out.samples if hasattr(out, "samples") else out)
         samples = postprocess_rollout_data(self.local_args, samples)
         dt = time.perf_counter() - t0

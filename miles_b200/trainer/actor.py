@@ -67,7 +67,9 @@ class TrainActor:
         if ep > 1:
             from ..parallel.expert_parallel import ExpertParallel
 
-            self.ep_dispatcher = ExpertParallel(self.cfg, self.ps, fused=getattr(args, "fused_comm", True))
+            max_tok = max(getattr(args, "max_tokens_per_gpu", None) or 0, getattr(args, "engine_max_prefill_tokens", 16384),
+                          (getattr(args, "rollout_max_context_len", None) or 0), 4096)
+            self.ep_dispatcher = ExpertParallel(self.cfg, self.ps, fused=getattr(args, "fused_comm", True), max_tokens=max_tok)
         self.model = build_model(self.cfg, store, "b200" if want_b200 else "torch", ep=self.ep_dispatcher)
         self.is_torch = not want_b200
         self.loss_cfg = LossConfig.from_args(args)

@@ -1,0 +1,100 @@
+"""Micro-batch packing, sequence balancing, sample conversion, flag surface."""
+import pytest
+import torch
+
+from miles_b200.rollout.train_data import convert_samples_to_train_data, pass_at_k, postprocess_rollout_data
+from miles_b200.trainer.data import build_micro_batches, pack_samples, split_by_dp
+from miles_b200.utils.arguments import build_parser, parse_args
+from miles_b200.utils.seqlen_balancing import first_fit_pack, karmarkar_karp
+from miles_b200.utils.types import Sample
+
+
+def _data():
+    return {
+        "tokens": [[1, 2, 3, 4, 5], [7, 8, 9], [4, 4, 4, 4, 4, 4, 4]],
+        "response_lengths": [2, 1, 4],
+        "loss_masks": [[1, 1], [1], [1, 0, 1, 1]],
+        "rewards": [1.0, -1.0, 0.5],
+        "rollout_log_probs": [[-0.1, -0.2], [-0.3], [-0.4, -0.5, -0.6, -0.7]],
+        "rollout_mask_sums": [2, 1, 3],
+    }
+
+
+def test_pack_samples_alignment():
+    mb = pack_samples(_data(), [0, 1, 2])
+    assert mb.tokens.tolist() == [1, 2, 3, 4, 5, 7, 8, 9, 4, 4, 4, 4, 4, 4, 4]
+    assert mb.positions.tolist() == [0, 1, 2, 3, 4, 0, 1, 2, 0, 1, 2, 3, 4, 5, 6]
+    assert mb.cu_seqlens.tolist() == [0, 5, 8, 15] and mb.max_seqlen == 7
+    # logits at rows predict the response tokens
+    assert mb.rows.tolist() == [2, 3, 6, 10, 11, 12, 13]
+    assert mb.targets.tolist() == [4, 5, 9, 4, 4, 4, 4]
+    assert mb.seg.tolist() == [0, 0, 1, 2, 2, 2, 2] and mb.resp_cu.tolist() == [0, 2, 3, 7]
+    assert mb.loss_mask.tolist() == [1, 1, 1, 1, 0, 1, 1] and mb.denoms.tolist() == [2, 1, 3]
+    assert torch.allclose(mb.rollout_log_probs, torch.tensor([-0.1, -0.2, -0.3, -0.4, -0.5, -0.6, -0.7]))
+
+
+def test_micro_batching_modes():
+    d = _data()
+    assert [m.sample_indices for m in build_micro_batches(d, max_tokens_per_gpu=8)] == [[0, 1], [2]]
+    assert [m.sample_indices for m in build_micro_batches(d, micro_batch_size=2)] == [[0, 1], [2]]
+    assert len(build_micro_batches(d, num_micro_batches=3)) == 3
+    assert split_by_dp(d, 2) == [[0, 2], [1]]
+
+
+def test_balancing():
+    L = [10, 9, 8, 7, 6, 5, 4, 3]
+    parts = karmarkar_karp(L, 2, equal_size=True)
+    sums = [sum(L[i] for i in p) for p in parts]
+    assert sorted(len(p) for p in parts) == [4, 4] and abs(sums[0] - sums[1]) <= 2
+    assert sorted(i for p in karmarkar_karp(L, 3) for i in p) == list(range(8))
+    bins = first_fit_pack([5, 4, 3, 9, 1], 9)
+    assert all(sum([5, 4, 3, 9, 1][i] for i in b) <= 9 for b in bins) and len(bins) == 3
+    with pytest.raises(ValueError):
+        karmarkar_karp([1, 2, 3], 2, equal_size=True)
+
+
+def _args(extra=()):
+    return parse_args(["--num-rollout", "2", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--model-preset", "qwen3-tiny",
+                       *extra])
+
+
+def test_convert_samples_and_postprocess():
+    args = _args()
+    ss = []
+    for g in range(2):
+        for j in range(2):
+            s = Sample(group_index=g, index=2 * g + j, tokens=[1, 2, 3, 4 + j], response_length=2, reward=float(j),
+                       rollout_log_probs=[-0.1, -0.2], status=Sample.Status.TRUNCATED if j else Sample.Status.COMPLETED)
+            ss.append(s)
+    d = convert_samples_to_train_data(args, ss)
+    assert d["raw_reward"] == [0.0, 1.0, 0.0, 1.0] and d["truncated"] == [0, 1, 0, 1]
+    assert abs(d["rewards"][0] + d["rewards"][1]) < 1e-6 and d["rewards"][1] > 0
+    assert d["loss_masks"] == [[1, 1]] * 4 and d["rollout_mask_sums"] == [2, 2, 2, 2]
+    ss[0].remove_sample = True
+    assert len(postprocess_rollout_data(args, ss)) == 3
+    assert pass_at_k(4, 0, 2) == 0.0 and pass_at_k(4, 4, 1) == 1.0 and abs(pass_at_k(4, 1, 1) - 0.25) < 1e-9
+
+
+def test_flag_surface_and_validation():
+    p = build_parser()
+    flags = {o for a in p._actions for o in a.option_strings}
+    for f in ("--advantage-estimator", "--eps-clip-high", "--use-rollout-routing-replay", "--update-weight-transfer-mode",
+              "--tensor-model-parallel-size", "--expert-model-parallel-size", "--max-tokens-per-gpu", "--use-tis", "--lora-rank",
+              "--save-hf", "--rollout-function-path", "--custom-rm-path", "--kl-loss-type", "--offload-train", "--no-offload-train",
+              "--moe-router-topk", "--num-query-groups", "--pause-generation-mode", "--max-weight-staleness", "--fully-async"):
+        assert f in flags, f
+    assert len(flags) > 480
+    a = _args(["--sglang-mem-fraction-static", "0.6", "--sglang-enable-metrics", "--eval-sglang-tp-size", "2", "--colocate"])
+    assert a.sglang_mem_fraction_static == 0.6 and a.sglang_enable_metrics is True and a.eval_sglang_tp_size == 2
+    assert a.global_batch_size == 4 and a.eps_clip_high == a.eps_clip and a.offload_train and a.offload_rollout
+    assert _args(["--use-rollout-routing-replay"]).use_routing_replay
+    with pytest.raises(AssertionError):
+        _args(["--kl-coef", "0.1", "--kl-loss-coef", "0.1"])
+    with pytest.raises(AssertionError):
+        _args(["--advantage-estimator", "reinforce_plus_plus"])
+    with pytest.raises(AssertionError):
+        _args(["--use-dynamic-batch-size"])
+    with pytest.raises(NotImplementedError):
+        _args(["--multi-latent-attention"])
+    with pytest.raises(SystemExit):
+        _args(["--definitely-not-a-flag"])

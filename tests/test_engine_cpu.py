@@ -1,0 +1,137 @@
+"""Rollout engine control flow on CPU (PyTorch op backend): continuous batching, stop conditions, abort,
+pause modes, retraction under page pressure, weight versions, async client routing."""
+import asyncio
+
+import pytest
+import torch
+
+from miles_b200.engine import Engine, SamplingParams
+from miles_b200.engine.client import EngineClient, decode_routed_experts
+from miles_b200.models import ParamStore, build_model, get_config
+
+
+def _engine(name="qwen3-tiny", **kw):
+    cfg = get_config(name)
+    st = ParamStore(cfg, "cpu", torch.float32, seed=11)
+    m = build_model(cfg, st)
+    kw.setdefault("max_running", 4)
+    kw.setdefault("page_size", 8)
+    kw.setdefault("max_seq_len", 128)
+    return cfg, m, Engine(m, **kw)
+
+
+def _prompts(cfg, lens, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+
+
+def test_continuous_batching_more_requests_than_slots_and_parity():
+    cfg, m, eng = _engine()
+    prompts = _prompts(cfg, [5, 17, 9, 30, 3, 12, 8])
+    sps = [SamplingParams(max_new_tokens=n, sampling_seed=i) for i, n in enumerate([4, 9, 1, 6, 12, 3, 7])]
+    res = eng.generate(prompts, sps)
+    assert [len(r["output_ids"]) for r in res] == [4, 9, 1, 6, 12, 3, 7]
+    assert all(r["meta_info"]["finish_reason"]["type"] == "length" for r in res)
+    assert eng.pool.num_free == eng.num_pages - 1 and not eng.running
+    for p, r in zip(prompts, res):
+        ids = p + r["output_ids"]
+        tok, pos, cu = torch.tensor(ids), torch.arange(len(ids)), torch.tensor([0, len(ids)])
+        lp, _ = m.forward_logprobs(tok, pos, cu, torch.arange(len(p) - 1, len(ids) - 1), tok[len(p):], 1.0)
+        elp = torch.tensor([x[0] for x in r["meta_info"]["output_token_logprobs"]])
+        assert torch.allclose(lp, elp, atol=1e-4)
+
+
+def test_sampling_is_seed_deterministic_and_greedy():
+    cfg, m, eng = _engine()
+    p = _prompts(cfg, [10])
+    a = eng.generate(p, SamplingParams(max_new_tokens=8, sampling_seed=5))[0]["output_ids"]
+    b = eng.generate(p, SamplingParams(max_new_tokens=8, sampling_seed=5))[0]["output_ids"]
+    c = eng.generate(p, SamplingParams(max_new_tokens=8, sampling_seed=6))[0]["output_ids"]
+    assert a == b and a != c
+    g1 = eng.generate(p, SamplingParams(max_new_tokens=5, temperature=0.0))[0]
+    ids = p[0] + g1["output_ids"]
+    tok = torch.tensor(ids)
+    h = m.forward_hidden(tok, torch.arange(len(ids)), torch.tensor([0, len(ids)]))
+    assert m.logits(h[len(p[0]) - 1:-1]).argmax(-1).tolist() == g1["output_ids"]
+
+
+def test_stop_tokens_and_forced_length():
+    cfg, m, eng = _engine()
+    p = _prompts(cfg, [6])
+    full = eng.generate(p, SamplingParams(max_new_tokens=20, sampling_seed=1))[0]["output_ids"]
+    stop = full[7]
+    first = full.index(stop)
+    r = eng.generate(p, SamplingParams(max_new_tokens=20, sampling_seed=1, stop_token_ids=(stop,)))[0]
+    assert r["output_ids"] == full[:first + 1] and r["meta_info"]["finish_reason"]["type"] == "stop"
+    r = eng.generate(p, SamplingParams(max_new_tokens=20, sampling_seed=1, stop_token_ids=(stop,), forced_length=11, ignore_eos=True))[0]
+    assert len(r["output_ids"]) == 11
+
+
+def test_abort_pause_modes_and_weight_versions():
+    cfg, m, eng = _engine()
+    prompts = _prompts(cfg, [8, 8, 8])
+    rids = [eng.add_request(p, SamplingParams(max_new_tokens=30, sampling_seed=i)) for i, p in enumerate(prompts)]
+    for _ in range(5):
+        eng.step()
+    assert eng.abort_request(rids[0]) == 1
+    eng.pause_generation("in_place")
+    assert eng.step() == [] and len(eng.running) == 2
+    eng.update_weight_version(3)
+    eng.continue_generation()
+    for _ in range(3):
+        eng.step()
+    eng.pause_generation("retract")
+    assert not eng.running and len(eng.waiting) == 2 and eng.flush_cache()
+    eng.update_weight_version(4)
+    eng.continue_generation()
+    while eng.has_work():
+        eng.step()
+    done = {r.rid: r for r in eng.pop_finished()}
+    assert done[rids[0]].finish_reason == "abort"
+    for rid in rids[1:]:
+        assert len(done[rid].output_ids) == 30
+        assert done[rid].weight_versions == [0, 3, 4]  # mixed versions are recorded per sample
+    eng.pause_generation("abort")
+    eng.continue_generation()
+
+
+def test_retraction_when_pages_run_out():
+    cfg, m, eng = _engine(num_pages=9, page_size=8, max_running=4)
+    prompts = _prompts(cfg, [14, 14, 14])
+    res = eng.generate(prompts, SamplingParams(max_new_tokens=24, sampling_seed=2))
+    assert all(len(r["output_ids"]) == 24 for r in res)
+    assert eng.stats["retracted"] > 0 and eng.pool.num_free == 8
+    solo = [Engine(m, max_running=1, page_size=8, max_seq_len=128).generate([p], SamplingParams(max_new_tokens=24, sampling_seed=2))[0]
+            for p in prompts]
+    # a retracted request is re-prefilled with its generated tokens and continues identically
+    assert [r["output_ids"] for r in res] == [r["output_ids"] for r in solo]
+
+
+def test_release_and_resume_memory():
+    cfg, m, eng = _engine()
+    p = _prompts(cfg, [7])
+    a = eng.generate(p, SamplingParams(max_new_tokens=4, sampling_seed=1))[0]["output_ids"]
+    eng.release_memory_occupation(("kv_cache", "cuda_graph"))
+    assert eng.kv_cache is None and eng.step() == []
+    eng.resume_memory_occupation(("kv_cache",))
+    assert eng.generate(p, SamplingParams(max_new_tokens=4, sampling_seed=1))[0]["output_ids"] == a
+
+
+def test_async_client_routes_to_least_loaded_engine_and_returns_routing():
+    cfg = get_config("qwen3-tiny-moe")
+    st = ParamStore(cfg, "cpu", torch.float32, seed=3)
+    m = build_model(cfg, st)
+    engines = [Engine(m, max_running=2, page_size=8, max_seq_len=64) for _ in range(2)]
+    client = EngineClient(engines)
+    prompts = _prompts(cfg, [6, 9, 4, 11])
+
+    async def run():
+        payloads = [{"input_ids": p, "sampling_params": {"max_new_tokens": 5, "sampling_seed": i}, "return_routed_experts": True}
+                    for i, p in enumerate(prompts)]
+        return await asyncio.gather(*[client.generate(pl) for pl in payloads])
+
+    outs = asyncio.run(run())
+    assert all(len(o["output_ids"]) == 5 for o in outs)
+    assert engines[0].stats["prefill_tokens"] > 0 and engines[1].stats["prefill_tokens"] > 0
+    re = decode_routed_experts(outs[1]["meta_info"])
+    assert re.shape == (9 + 5 - 1, 2, cfg.moe_top_k) and re.min() >= 0 and re.max() < cfg.num_experts
