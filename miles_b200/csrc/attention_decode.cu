@@ -157,3 +157,83 @@ void paged_decode_attention(const void* q, const void* k_cache, const void* v_ca
 }
 
 }  // namespace mb
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in noalloc.h): same kernels, split-KV partials in a fixed array that
+// is part of the library image instead of a caller-provided scratch tensor.
+#include <stdio.h>
+
+#include <mutex>
+
+#include "noalloc.h"
+
+namespace {
+
+// Partial outputs [B*Hq*splits][128] followed by partial (max, sum) pairs [B*Hq*splits][2].
+static __device__ __align__(256) float g_noalloc_scratch[MB_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_scratch_addr[kMaxDevices] = {nullptr};  // device address of the array, per device
+std::mutex g_scratch_mutex;
+thread_local char g_noalloc_err[256] = "";
+
+int noalloc_fail(int code, const char* msg) {
+  snprintf(g_noalloc_err, sizeof(g_noalloc_err), "%s", msg);
+  return code;
+}
+
+// In host code `g_noalloc_scratch` is only a handle of the symbol; the address kernels may use has to
+// be asked from the runtime, once per device, with that device current.
+int noalloc_scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return noalloc_fail(MB_NOALLOC_ERR_CUDA, "cudaGetDevice failed");
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      snprintf(g_noalloc_err, sizeof(g_noalloc_err), "cudaGetSymbolAddress(scratch) failed: %s", cudaGetErrorString(e));
+      return MB_NOALLOC_ERR_CUDA;
+    }
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return MB_NOALLOC_OK;
+}
+
+}  // namespace
+
+extern "C" const char* mb_noalloc_last_error(void) { return g_noalloc_err; }
+
+extern "C" int mb_paged_decode_attention_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                                 const int* block_table, const int* seq_lens, void* out, int B, int Hq,
+                                                 int Hk, int page_size, int max_pages, int num_splits, float scale,
+                                                 cudaStream_t stream) {
+  if (!q || !k_cache || !v_cache || !block_table || !seq_lens || !out)
+    return noalloc_fail(MB_NOALLOC_ERR_BAD_ARG, "null pointer argument");
+  if (B <= 0 || Hq <= 0 || Hk <= 0 || page_size <= 0 || max_pages <= 0 || num_splits <= 0)
+    return noalloc_fail(MB_NOALLOC_ERR_BAD_ARG, "extents must be positive");
+  if (Hq % Hk != 0) return noalloc_fail(MB_NOALLOC_ERR_BAD_ARG, "Hq must be a multiple of Hk");
+  const int G = Hq / Hk;
+  if (G != 1 && G != 2 && G != 4 && G != 8)
+    return noalloc_fail(MB_NOALLOC_ERR_BAD_ARG, "Hq / Hk must be 1, 2, 4 or 8");
+  const unsigned long long need = 130ull * static_cast<unsigned long long>(B) * Hq * num_splits;
+  if (need > MB_NOALLOC_SCRATCH_FLOATS) {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err),
+             "B*Hq*num_splits*130 = %llu floats exceed the built-in scratch of %u floats; lower num_splits or the batch",
+             need, MB_NOALLOC_SCRATCH_FLOATS);
+    return MB_NOALLOC_ERR_TOO_LARGE;
+  }
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch_for_current_device(&scratch);
+  if (rc != MB_NOALLOC_OK) return rc;
+  mb::paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, out, scratch, B, Hq, Hk, page_size, max_pages,
+                             num_splits, scale, stream);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err), "kernel launch failed: %s", cudaGetErrorString(e));
+    return MB_NOALLOC_ERR_CUDA;
+  }
+  return MB_NOALLOC_OK;
+}
