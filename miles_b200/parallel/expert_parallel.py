@@ -52,7 +52,7 @@ class ExpertParallel:
         self.ctrl = torch.zeros(8, dtype=torch.int64, device=self.dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.identity = torch.arange(self.max_entries, dtype=torch.int32, device=self.dev)
-        self.big_tiles = torch.full((1,), 1 << 24, dtype=torch.int32, device=self.dev)
+        self.big_tiles = torch.full((1,), 1 << 20, dtype=torch.int32, device=self.dev)
         self.pos_in_cap = torch.arange(cap, dtype=torch.int32, device=self.dev)[None, :]
         self._peers = (self.p_xrecv, self.p_meta, self.p_counts, self.p_flags, self.p_yback, self.p_flags2)
 
@@ -176,7 +176,7 @@ class ExpertParallel:
         p = f"layers.{i}.moe."
         ids, w, plan, order = saved["ids"], saved["w"], saved["plan"], saved["order"]
         T, K = ids.shape
-        big = torch.full((1,), 1 << 24, dtype=torch.int32, device=dy.device)
+        big = torch.full((1,), 1 << 20, dtype=torch.int32, device=dy.device)
         dy_slot, dw = C.moe_combine_bwd(dy, saved["yslot"], saved["ident"], big, w)
         dyr = self._exchange_nccl(dy_slot[order].contiguous(), saved["sc"], saved["rc"])
         dyp = C.moe_permute(dyr, plan.src, plan.num_tiles, 1)
