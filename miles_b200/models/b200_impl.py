@@ -293,6 +293,40 @@ class B200Qwen3:
         return h
 
     @torch.no_grad()
+    def _trunk_backward(self, inputs, x_last, h, rows, dhr, tokens, positions, cu_seqlens, max_seqlen, replay):
+        """Back-propagate ``dhr`` (gradient wrt the final-normed hidden rows) through the norm, layers and embedding."""
+        cfg, P, G, C = self.cfg, self.store.params, self.store.grads, self.C
+        dh = torch.zeros_like(h)
+        dh.index_add_(0, rows, dhr.to(h.dtype))
+        _, rstd = C.rmsnorm_fwd(x_last, None, P["final_norm.weight"], cfg.rms_eps)
+        dx = C.rmsnorm_bwd(dh, x_last, P["final_norm.weight"], rstd, None, G["final_norm.weight"], True)
+        self.launches += 3
+        del dh
+        moe_layers = [i for i in range(cfg.num_layers) if cfg.layer_is_moe(i)]
+        for i in reversed(range(cfg.num_layers)):
+            rid = replay[:, moe_layers.index(i)] if (replay is not None and cfg.layer_is_moe(i)) else None
+            dx = self.layer_backward(i, inputs[i], dx, positions, cu_seqlens, max_seqlen, rid)
+            inputs[i] = None
+        G["embed.weight"].index_add_(0, tokens.long(), dx.to(G["embed.weight"].dtype))
+
+    def forward_backward_hidden(self, tokens, positions, cu_seqlens, row_index, head_fn, replay=None, max_seqlen: int = 0):
+        """Generic head: ``head_fn(hidden_rows_fp32_leaf) -> (loss, metrics)`` (e.g. a value head); the trunk is
+        back-propagated with the gradient autograd computes for the hidden rows."""
+        assert self.store.grads, "allocate_grads() must be called before training"
+        if not max_seqlen:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
+        inputs: list = []
+        h = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, max_seqlen=max_seqlen, save_inputs=inputs)
+        x_last = inputs.pop()
+        rows = row_index.long()
+        leaf = h[rows].float().detach().requires_grad_(True)
+        with torch.enable_grad():
+            loss, metrics = head_fn(leaf)
+            loss.backward()
+        self._trunk_backward(inputs, x_last, h, rows, leaf.grad, tokens, positions, cu_seqlens, max_seqlen, replay)
+        return loss.detach(), metrics
+
+    @torch.no_grad()
     def logits(self, hidden_rows, out_dtype=torch.float32):
         return self.linear(hidden_rows.contiguous(), self.store.lm_head(), out_dtype)
 
@@ -356,18 +390,5 @@ class B200Qwen3:
                 self._gemm(dl, W, dhr[a:b], False, True)
                 self.linear_wgrad(dl, hr[a:b], gW)
                 self.launches += 1
-            dh = torch.zeros_like(h)
-            dh.index_add_(0, rows, dhr)
-            # ---- final norm
-            _, rstd = C.rmsnorm_fwd(x_last, None, P["final_norm.weight"], cfg.rms_eps)
-            dx = C.rmsnorm_bwd(dh, x_last, P["final_norm.weight"], rstd, None, G["final_norm.weight"], True)
-            self.launches += 3
-            del dh, dhr, h, hr
-            moe_layers = [i for i in range(cfg.num_layers) if cfg.layer_is_moe(i)]
-            for i in reversed(range(cfg.num_layers)):
-                rid = replay[:, moe_layers.index(i)] if (replay is not None and cfg.layer_is_moe(i)) else None
-                dx = self.layer_backward(i, inputs[i], dx, positions, cu_seqlens, max_seqlen, rid)
-                inputs[i] = None
-            # ---- embedding
-            G["embed.weight"].index_add_(0, tokens.long(), dx.to(G["embed.weight"].dtype))
+            self._trunk_backward(inputs, x_last, h, rows, dhr, tokens, positions, cu_seqlens, max_seqlen, replay)
         return loss.detach(), metrics, lp.detach(), ent.detach()

@@ -289,6 +289,10 @@ class TrainActor:
             with T.context("log_probs"):
                 self.compute_log_probs(mbs, "log_probs", with_entropy=getattr(a, "use_rollout_entropy", False))
         if a.loss_type == "policy_loss":
+            if data.get("values") is not None:
+                for mb in mbs:
+                    mb.extras["values"] = torch.cat([torch.as_tensor(data["values"][i], dtype=torch.float32)
+                                                     for i in mb.sample_indices]).to(self.device)
             self._advantages(mbs)
         metrics_acc: dict = {}
         grad_norm = torch.zeros((), device=self.device)
@@ -380,6 +384,63 @@ class TrainActor:
             h = self.model.forward_hidden(mb.tokens, mb.positions, mb.cu_seqlens) if self.is_torch else \
                 self.model.forward_hidden(mb.tokens, mb.positions, mb.cu_seqlens, max_seqlen=mb.max_seqlen)
             mb.extras["values"] = (h[mb.rows].float() @ self._value_head.t())[:, 0]
+
+    def train_critic(self, rollout_id: int, data: dict) -> dict:
+        """Critic step of shared actor/critic PPO: values -> GAE returns -> clipped value loss.
+        The values computed before the update are written back into ``data['values']`` for the actor."""
+        a = self.args
+        mbs = self._stage(data)
+        self.compute_values(mbs)
+        for mb in mbs:
+            adv, ret, _ = compute_advantages_and_returns(
+                advantage_estimator="ppo", rewards=mb.rewards, cu=mb.resp_cu, loss_mask=mb.loss_mask, values=mb.extras["values"],
+                kl_coef=0.0, gamma=a.gamma, lambd=a.lambd)
+            mb.extras["returns"] = ret
+        gbs = a.global_batch_size or max(1, len(data["tokens"]))
+        self.store.zero_grads()
+        if self._value_head.grad is not None:
+            self._value_head.grad = None
+        acc: dict = {}
+        for mb in mbs:
+            reducer = SegmentReducer(mb.seg, mb.loss_mask, mb.denoms, per_token=a.calculate_per_token_loss, num_samples=mb.num_samples)
+            old_v, ret = mb.extras["values"], mb.extras["returns"]
+
+            def head(hr, old_v=old_v, ret=ret, reducer=reducer):
+                v = (hr @ self._value_head.t())[:, 0]
+                loss, m = value_loss(self.loss_cfg, v, old_values=old_v, returns=ret, reducer=reducer)
+                return loss / gbs, m
+
+            if self.is_torch:
+                self.model.set_requires_grad(True)
+                with torch.enable_grad():
+                    h = self.model.forward_hidden(mb.tokens, mb.positions, mb.cu_seqlens)
+                    loss, m = head(h[mb.rows].float())
+                    loss.backward()
+                self.model.accumulate_autograd_grads()
+                self.model.set_requires_grad(False)
+            else:
+                _, m = self.model.forward_backward_hidden(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, head, max_seqlen=mb.max_seqlen)
+            for k, v in m.items():
+                acc[k] = acc.get(k, 0.0) + v.detach().float() / gbs
+        self._reduce_grads()
+        if self.ps.dp_cp.size > 1 and self._value_head.grad is not None:
+            dist.all_reduce(self._value_head.grad, group=self.ps.dp_cp.group)
+        gn = self.opt.step(1.0) if self.opt is not None else torch.zeros(())
+        with torch.no_grad():
+            if self._value_head.grad is not None:
+                self._value_head -= (a.critic_lr or a.lr) * self._value_head.grad
+                self._value_head.grad = None
+        self.global_step += 1
+        # hand the pre-update values to the actor in sample order
+        vals = [None] * len(data["tokens"])
+        for mb in mbs:
+            cu = mb.resp_cu.tolist()
+            v = mb.extras["values"].detach().cpu()
+            for j, i in enumerate(mb.sample_indices):
+                vals[i] = v[cu[j]:cu[j + 1]].tolist()
+        data["values"] = vals
+        out = self._finalize_metrics(acc, gn, sum(mb.num_tokens for mb in mbs), 0.0, len(mbs))
+        return {k: v for k, v in out.items() if k.startswith("train/")}
 
     # ------------------------------------------------------------------ weight update, offload, checkpoints
     def connect_rollout_engines(self, engines: list) -> None:
