@@ -81,7 +81,8 @@ void grouped_gemm_rows(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, 
   p.K = a.size(1);
   p.N = b_mn ? b.size(2) : b.size(1);
   TORCH_CHECK((b_mn ? b.size(1) : b.size(2)) == p.K, "contraction extents differ");
-  TORCH_CHECK(tile_group.numel() * 128 >= p.M, "tile_group is too short");
+  TORCH_CHECK(tile_group.dim() == 2 && tile_group.size(1) == 4 && num_m_tiles.numel() >= 1, "tile maps must be [tiles, 4] and [2]");
+  p.max_tiles = tile_group.size(0);
   TORCH_CHECK(c.dim() == 2 && c.size(0) == p.M && c.size(1) == p.N, "bad output shape");
   p.a = operand(a, false);
   at::Tensor b2 = b.view({b.size(0) * b.size(1), b.size(2)});

@@ -37,6 +37,7 @@ struct KArgs {
   int mode;
   int M, N, K;
   int num_groups;
+  int max_tiles;
   const int* tile_group;
   const int* num_m_tiles;
   const int* group_offsets;
@@ -54,6 +55,7 @@ struct Tile {
   int a_k0, b_k0;    // first contraction coordinate in each operand tensor
   int k_iters;
   int c_row0, c_col0;
+  int row_end;  // rows >= row_end are not stored
   long long c_base;
 };
 
@@ -63,7 +65,7 @@ __device__ __forceinline__ int num_tiles_of(const KArgs& p) {
   if (p.mode == GEMM_DENSE) return ((p.M + BLOCK_M - 1) / BLOCK_M) * n_tiles;
   if (p.mode == GEMM_GROUPED_ROWS) {
     int live = *p.num_m_tiles;
-    const int cap = (p.M + BLOCK_M - 1) / BLOCK_M;
+    const int cap = p.max_tiles;
     live = live < 0 ? 0 : (live > cap ? cap : live);
     return live * n_tiles;
   }
@@ -92,13 +94,16 @@ __device__ __forceinline__ Tile decode_tile(const KArgs& p, int t) {
     r.k_iters = (p.K + BLOCK_K - 1) / BLOCK_K;
     r.c_row0 = r.a_mn0;
     r.c_col0 = r.b_mn0;
+    r.row_end = p.M;
     r.c_base = 0;
   } else if (p.mode == GEMM_GROUPED_ROWS) {
     const int mt = t / n_tiles;
     const int nt = t - mt * n_tiles;
-    int g = p.tile_group[mt];
+    const int4 td = reinterpret_cast<const int4*>(p.tile_group)[mt];
+    int g = td.x;
     g = g < 0 ? 0 : (g >= p.num_groups ? p.num_groups - 1 : g);
-    r.a_mn0 = mt * BLOCK_M;
+    r.a_mn0 = td.y < 0 ? 0 : td.y;
+    r.row_end = min(p.M, r.a_mn0 + max(0, min(td.z, BLOCK_M)));
     r.a_k0 = 0;
     if (B_MN) {
       r.b_mn0 = nt * BLOCK_N;
@@ -126,6 +131,7 @@ __device__ __forceinline__ Tile decode_tile(const KArgs& p, int t) {
     r.k_iters = k_hi > k_lo ? (k_hi - k_lo + BLOCK_K - 1) / BLOCK_K : 0;
     r.c_row0 = r.a_mn0;
     r.c_col0 = r.b_mn0;
+    r.row_end = p.M;
     r.c_base = static_cast<long long>(g) * p.c_group_stride;
   }
   return r;
@@ -133,7 +139,7 @@ __device__ __forceinline__ Tile decode_tile(const KArgs& p, int t) {
 
 __device__ __forceinline__ void store_chunk(const KArgs& p, const Tile& t, int row, int col,
                                             const uint32_t (&acc)[32], bool zero) {
-  if (row >= p.M) return;
+  if (row >= t.row_end) return;
   const long long off = t.c_base + static_cast<long long>(row) * p.ldc + col;
   const bool full = (col + 32 <= p.N) && p.vec_ok;
   if (p.out_fp32) {
@@ -438,7 +444,7 @@ int make_map(CUtensorMap* map, const GemmOperand& op, int box_rows) {
 
 template <int BLOCK_N, bool A_MN, bool B_MN>
 int launch(const GemmProblem& p, const KArgs& ka, cudaStream_t stream) {
-  constexpr int STAGES = BLOCK_N == 256 ? 4 : 6;
+  constexpr int STAGES = BLOCK_N == 256 ? 4 : (BLOCK_N == 128 ? 6 : 8);
   constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 2;
   constexpr int SMEM = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 8 * (2 * STAGES + 5) + 1024;
   CUtensorMap ma, mb_;
@@ -456,7 +462,8 @@ int launch(const GemmProblem& p, const KArgs& ka, cudaStream_t stream) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long m_tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
   const long long n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
-  long long tiles = m_tiles * n_tiles * (p.mode == GEMM_GROUPED_CONTR ? p.num_groups : 1);
+  long long tiles = (p.mode == GEMM_GROUPED_ROWS ? static_cast<long long>(p.max_tiles) : m_tiles) * n_tiles *
+                    (p.mode == GEMM_GROUPED_CONTR ? p.num_groups : 1);
   int grid = static_cast<int>(tiles < sms ? tiles : sms);
   if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
   if (grid <= 0) return 0;
@@ -483,6 +490,7 @@ int gemm_bf16_launch(const GemmProblem& p, cudaStream_t stream) {
   ka.N = p.N;
   ka.K = p.K;
   ka.num_groups = p.num_groups;
+  ka.max_tiles = p.max_tiles;
   ka.tile_group = p.tile_group;
   ka.num_m_tiles = p.num_m_tiles;
   ka.group_offsets = p.group_offsets;
@@ -497,18 +505,27 @@ int gemm_bf16_launch(const GemmProblem& p, cudaStream_t stream) {
   ka.vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0 && p.ldc % vec == 0 && p.c_group_stride % vec == 0) ? 1 : 0;
 
   int bn = p.block_n;
+  const bool amn = p.a.mn_major, bmn = p.b.mn_major;
   if (bn == 0) {
-    int sms = 148;
-    const long long m_tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
+    const int sms = 148;
+    const long long m_tiles = p.mode == GEMM_GROUPED_ROWS ? p.max_tiles : (p.M + BLOCK_M - 1) / BLOCK_M;
     const long long groups = p.mode == GEMM_GROUPED_CONTR ? p.num_groups : 1;
-    const long long t256 = m_tiles * ((p.N + 255) / 256) * groups;
+    auto tiles = [&](int b) { return m_tiles * ((p.N + b - 1) / b) * groups; };
     // Prefer the 128x256 tile unless it leaves most SMs idle or wastes a large share of the tile.
     const bool waste256 = (p.N % 256) != 0 && (p.N % 256) <= 128;
-    bn = (t256 >= sms && !waste256) || (p.N >= 256 && t256 >= 2 * sms) ? 256 : 128;
+    bn = (tiles(256) >= sms && !waste256) || (p.N >= 256 && tiles(256) >= 2 * sms) ? 256 : 128;
     if (p.N <= 128) bn = 128;
+    // Skinny problems (decode projections): narrower tiles spread the weight stream over more SMs.
+    if (!amn && !bmn && tiles(bn) < sms) {
+      if (bn == 256 && tiles(128) <= sms) bn = 128;
+      if (bn == 128 && tiles(128) < sms / 2 && p.N >= 64) bn = 64;
+      if (bn == 64 && tiles(64) < sms / 2 && p.N >= 32) bn = 32;
+    }
   }
-  if (bn != 128 && bn != 256) return fail("block_n must be 128 or 256");
-  const bool amn = p.a.mn_major, bmn = p.b.mn_major;
+  if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return fail("block_n must be 32, 64, 128 or 256");
+  if ((bn == 32 || bn == 64) && (amn || bmn)) return fail("narrow tiles support K-major operands only");
+  if (bn == 32) return launch<32, false, false>(p, ka, stream);
+  if (bn == 64) return launch<64, false, false>(p, ka, stream);
 #define MB_DISPATCH(BN)                                                     \
   if (!amn && !bmn) return launch<BN, false, false>(p, ka, stream);         \
   if (!amn && bmn) return launch<BN, false, true>(p, ka, stream);           \

@@ -7,7 +7,7 @@ namespace mb {
 
 enum GemmMode : int {
   GEMM_DENSE = 0,          // C[M,N] = A . B^T
-  GEMM_GROUPED_ROWS = 1,   // every 128-row tile of A picks the B slab of its group (MoE fwd/dgrad)
+  GEMM_GROUPED_ROWS = 1,   // every row tile of A (<= 128 rows, listed in tile_group) picks the B slab of its group
   GEMM_GROUPED_CONTR = 2,  // C_g[M,N] = sum over the rows of group g (MoE wgrad)
 };
 
@@ -31,8 +31,9 @@ struct GemmProblem {
   bool out_fp32;
   bool accumulate;           // C += A.B^T instead of C =
   int num_groups;
-  const int* tile_group;     // mode 1: [ceil(M/128)] group per row tile
+  const int* tile_group;     // mode 1: [max_tiles][4] = {group, first row, rows to compute, 0} per row tile
   const int* num_m_tiles;    // mode 1: device scalar with the number of live row tiles
+  int max_tiles;             // mode 1: capacity of tile_group
   const int* group_offsets;  // mode 2: [num_groups+1] row offsets, multiples of 64
   int* status;               // device status word (0 = ok); may be null
   int block_n;               // 0 = choose, else 128 or 256

@@ -33,16 +33,17 @@ void sumsq(const void* g, bool g_fp32, long long n, float* out, cudaStream_t s);
 void moe_router_topk(const float* logits, const int* replay_ids, int* topk_ids, float* topk_w, float* probs_out,
                      int T, int E, int K, bool renorm, cudaStream_t s);
 // Deterministic counting sort of the T*K (token, slot) pairs by expert. Rows of each expert are padded
-// to a multiple of 128; outputs: dest_row[T*K], row_src[max_rows] (-1 for padding), expert_offsets[E+1]
-// (padded), tile_group[max_rows/128], num_m_tiles[1], expert_counts[E].
-void moe_build_permutation(const int* topk_ids, int T, int K, int E, int max_rows, int* expert_counts,
-                           int* expert_offsets, int* dest_row, int* row_src, int* tile_group, int* num_m_tiles,
-                           cudaStream_t s);
+// to a multiple of `align`; outputs: dest_row[T*K], row_src[max_rows] (-1 for padding), expert_offsets[E+1]
+// (padded), tile_group[max_tiles][4] = {expert, row0, rows, 0}, num_m_tiles[2] = {tiles, live rows},
+// expert_counts[E].
+void moe_build_permutation(const int* topk_ids, int T, int K, int E, int max_rows, int max_tiles, int align,
+                           int* expert_counts, int* expert_offsets, int* dest_row, int* row_src, int* tile_group,
+                           int* num_m_tiles, cudaStream_t s);
 void moe_permute(const void* x, const int* row_src, const int* num_m_tiles, void* x_perm, int max_rows, int H, int K,
                  cudaStream_t s);
-// out[t] = sum_k w[t,k] * y_perm[dest_row[t,k]]
-void moe_combine(const void* y_perm, const int* dest_row, const float* topk_w, void* out, int T, int K, int H,
-                 cudaStream_t s);
+// out[t] = (residual[t] +) sum_k w[t,k] * y_perm[dest_row[t,k]]
+void moe_combine(const void* y_perm, const int* dest_row, const float* topk_w, const void* residual, void* out, int T,
+                 int K, int H, cudaStream_t s);
 // dy_perm[row] = w * dout[token]; dw[t,k] = <dout[t], y_perm[row]>; padding rows are zeroed.
 void moe_combine_bwd(const void* dout, const void* y_perm, const int* row_src, const int* num_m_tiles,
                      const float* topk_w, void* dy_perm, float* dtopk_w, int max_rows, int K, int H, cudaStream_t s);

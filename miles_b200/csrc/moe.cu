@@ -4,7 +4,9 @@
 //                        table the expert choice comes from the rollout engine (rollout routing replay)
 //                        and only the gate weights are recomputed from the current logits.
 //   build_permutation  : deterministic counting sort of (token, slot) pairs by expert; each expert's rows
-//                        are padded to a multiple of 128 so that a GEMM row tile never straddles experts.
+//                        are padded to a multiple of `align` (64 for training so that the weight-gradient
+//                        contraction blocks stay inside one expert, 1 for inference) and cut into GEMM row
+//                        tiles of at most 128 rows that never straddle experts.
 //   permute / combine  : gather rows into expert order / weighted gather-sum back to token order, with
 //                        their backward passes. All gathers are index-driven (no atomics), so results are
 //                        bitwise reproducible.
@@ -194,24 +196,37 @@ __global__ void count_kernel(const int* __restrict__ ids, int n, int* __restrict
   }
 }
 
-// Pass 2: single CTA: padded exclusive scan, tile -> expert map, number of live tiles.
-__global__ void scan_kernel(const int* __restrict__ counts, int E, int max_rows, int* __restrict__ offsets,
-                            int* __restrict__ tile_group, int* __restrict__ num_m_tiles) {
+// Pass 2: single CTA: exclusive scan of the per-expert row counts padded to `align`, the list of GEMM row
+// tiles (expert, first row, rows to compute; a tile never straddles experts and is at most 128 rows), the
+// number of tiles and the number of live rows. tiles[t] = {expert, row0, rows, 0}; totals = {num tiles, live rows}.
+__global__ void scan_kernel(const int* __restrict__ counts, int E, int max_rows, int max_tiles, int align,
+                            int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ totals) {
+  extern __shared__ int tile_start[];  // [E+1]
   if (threadIdx.x == 0) {
-    int off = 0;
+    int off = 0, t = 0;
     for (int e = 0; e < E; ++e) {
       offsets[e] = off;
-      int padded = ((counts[e] + 127) / 128) * 128;
-      if (off + padded > max_rows) padded = max_rows - off > 0 ? ((max_rows - off) / 128) * 128 : 0;
+      tile_start[e] = t;
+      int padded = ((counts[e] + align - 1) / align) * align;
+      if (off + padded > max_rows) padded = max_rows - off > 0 ? ((max_rows - off) / align) * align : 0;
       off += padded;
+      t += (padded + 127) / 128;
     }
     offsets[E] = off;
-    *num_m_tiles = off / 128;
+    tile_start[E] = t < max_tiles ? t : max_tiles;
+    totals[0] = tile_start[E];
+    totals[1] = off;
   }
   __syncthreads();
   for (int e = 0; e < E; ++e) {
-    const int lo = offsets[e] / 128, hi = offsets[e + 1] / 128;
-    for (int t = lo + threadIdx.x; t < hi; t += blockDim.x) tile_group[t] = e;
+    const int rows_e = offsets[e + 1] - offsets[e];
+    for (int j = threadIdx.x; tile_start[e] + j < tile_start[e + 1] && tile_start[e] + j < max_tiles; j += blockDim.x) {
+      int* t = tiles + 4 * (tile_start[e] + j);
+      t[0] = e;
+      t[1] = offsets[e] + 128 * j;
+      t[2] = min(128, rows_e - 128 * j);
+      t[3] = 0;
+    }
   }
 }
 
@@ -253,6 +268,76 @@ __global__ void assign_kernel(const int* __restrict__ ids, int n, const int* __r
   }
 }
 
+// Single-CTA variant for small problems (decode steps): counts, scan, tile list and the stable assignment
+// in one launch. Also initialises row_src / dest_row, so the caller needs no memset or fill kernels.
+__global__ void __launch_bounds__(1024)
+build_small_kernel(const int* __restrict__ ids, int n, int E, int max_rows, int max_tiles, int align,
+                   int* __restrict__ counts_out, int* __restrict__ offsets, int* __restrict__ dest_row,
+                   int* __restrict__ row_src, int* __restrict__ tiles, int* __restrict__ totals) {
+  extern __shared__ int sm[];  // counts[E], off[E+1], tile_start[E+1]
+  int* cnt = sm;
+  int* off = sm + E;
+  int* tstart = off + E + 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) cnt[i] = 0;
+  for (int i = threadIdx.x; i < max_rows; i += blockDim.x) row_src[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+    else dest_row[i] = -1;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, t = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = o;
+      tstart[e] = t;
+      int padded = ((cnt[e] + align - 1) / align) * align;
+      if (o + padded > max_rows) padded = max_rows - o > 0 ? ((max_rows - o) / align) * align : 0;
+      o += padded;
+      t += (padded + 127) / 128;
+    }
+    off[E] = o;
+    tstart[E] = t < max_tiles ? t : max_tiles;
+    totals[0] = tstart[E];
+    totals[1] = o;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    offsets[e] = off[e];
+    if (e < E) counts_out[e] = cnt[e];
+  }
+  // tiles and stable ranks: one warp per expert
+  for (int e = warp; e < E; e += nwarps) {
+    const int rows_e = off[e + 1] - off[e];
+    for (int j = lane; tstart[e] + j < tstart[e + 1] && tstart[e] + j < max_tiles; j += 32) {
+      int* t = tiles + 4 * (tstart[e] + j);
+      t[0] = e;
+      t[1] = off[e] + 128 * j;
+      t[2] = min(128, rows_e - 128 * j);
+      t[3] = 0;
+    }
+    if (cnt[e] == 0) continue;
+    int base = 0;
+    for (int start = 0; start < n; start += 32) {
+      const int i = start + lane;
+      const bool hit = i < n && ids[i] == e;
+      const unsigned m = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const int rank = base + __popc(m & ((1u << lane) - 1u));
+        if (rank < rows_e) {
+          dest_row[i] = off[e] + rank;
+          row_src[off[e] + rank] = i;
+        } else {
+          dest_row[i] = -1;
+        }
+      }
+      base += __popc(m);
+    }
+  }
+}
+
 struct alignas(16) V8 {
   uint4 v;
 };
@@ -261,7 +346,7 @@ struct alignas(16) V8 {
 __global__ void permute_kernel(const bf16* __restrict__ x, const int* __restrict__ row_src,
                                const int* __restrict__ num_m_tiles, bf16* __restrict__ x_perm, int max_rows, int H,
                                int K) {
-  const int live_rows = min(*num_m_tiles * 128, max_rows);
+  const int live_rows = min(num_m_tiles[1], max_rows);
   const int vec_per_row = H / 8;
   const long long total = static_cast<long long>(live_rows) * vec_per_row;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
@@ -296,7 +381,8 @@ __device__ __forceinline__ uint4 pack8(const float (&a)[8]) {
 
 // out[t] = sum_k w[t,k] * y_perm[dest_row[t,k]]; with w == nullptr the weights are 1 (permute backward).
 __global__ void combine_kernel(const bf16* __restrict__ y_perm, const int* __restrict__ dest_row,
-                               const float* __restrict__ topk_w, bf16* __restrict__ out, int T, int K, int H) {
+                               const float* __restrict__ topk_w, const bf16* __restrict__ residual,
+                               bf16* __restrict__ out, int T, int K, int H) {
   const int vec_per_row = H / 8;
   const long long total = static_cast<long long>(T) * vec_per_row;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
@@ -304,6 +390,7 @@ __global__ void combine_kernel(const bf16* __restrict__ y_perm, const int* __res
     const int t = idx / vec_per_row;
     const int c = idx - static_cast<long long>(t) * vec_per_row;
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (residual) acc8(reinterpret_cast<const uint4*>(residual + static_cast<long long>(t) * H)[c], 1.f, a);
     for (int k = 0; k < K; ++k) {
       const int row = dest_row[static_cast<long long>(t) * K + k];
       if (row < 0) continue;
@@ -319,7 +406,7 @@ __global__ void combine_bwd_kernel(const bf16* __restrict__ dout, const bf16* __
                                    const int* __restrict__ row_src, const int* __restrict__ num_m_tiles,
                                    const float* __restrict__ topk_w, bf16* __restrict__ dy_perm,
                                    float* __restrict__ dtopk_w, int max_rows, int K, int H) {
-  const int live_rows = min(*num_m_tiles * 128, max_rows);
+  const int live_rows = min(num_m_tiles[1], max_rows);
   const int wpb = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < live_rows; row += gridDim.x * wpb) {
@@ -380,13 +467,20 @@ void moe_router_bwd(const float* probs, const int* topk_ids, const float* topk_w
                                                              renorm ? 1 : 0);
 }
 
-void moe_build_permutation(const int* topk_ids, int T, int K, int E, int max_rows, int* expert_counts,
-                           int* expert_offsets, int* dest_row, int* row_src, int* tile_group, int* num_m_tiles,
-                           cudaStream_t s) {
+void moe_build_permutation(const int* topk_ids, int T, int K, int E, int max_rows, int max_tiles, int align,
+                           int* expert_counts, int* expert_offsets, int* dest_row, int* row_src, int* tile_group,
+                           int* num_m_tiles, cudaStream_t s) {
   const int n = T * K;
+  if (n <= 4096 && max_rows <= 16384 && E <= 512) {
+    build_small_kernel<<<1, 1024, (3 * E + 2) * sizeof(int), s>>>(topk_ids, n, E, max_rows, max_tiles, align, expert_counts,
+                                                                   expert_offsets, dest_row, row_src, tile_group, num_m_tiles);
+    return;
+  }
+  cudaMemsetAsync(dest_row, 0xff, sizeof(int) * static_cast<size_t>(n), s);
   cudaMemsetAsync(row_src, 0xff, sizeof(int) * static_cast<size_t>(max_rows), s);
   count_kernel<<<E, 512, 0, s>>>(topk_ids, n, expert_counts);
-  scan_kernel<<<1, 256, 0, s>>>(expert_counts, E, max_rows, expert_offsets, tile_group, num_m_tiles);
+  scan_kernel<<<1, 256, (E + 1) * sizeof(int), s>>>(expert_counts, E, max_rows, max_tiles, align, expert_offsets, tile_group,
+                                                     num_m_tiles);
   assign_kernel<<<E, 512, 0, s>>>(topk_ids, n, expert_offsets, dest_row, row_src);
 }
 
@@ -397,15 +491,15 @@ void moe_permute(const void* x, const int* row_src, const int* num_m_tiles, void
       static_cast<const bf16*>(x), row_src, num_m_tiles, static_cast<bf16*>(x_perm), max_rows, H, K);
 }
 
-void moe_combine(const void* y_perm, const int* dest_row, const float* topk_w, void* out, int T, int K, int H,
-                 cudaStream_t s) {
+void moe_combine(const void* y_perm, const int* dest_row, const float* topk_w, const void* residual, void* out, int T,
+                 int K, int H, cudaStream_t s) {
   if (T <= 0) return;
   combine_kernel<<<grid_for(static_cast<long long>(T) * (H / 8), 256), 256, 0, s>>>(
-      static_cast<const bf16*>(y_perm), dest_row, topk_w, static_cast<bf16*>(out), T, K, H);
+      static_cast<const bf16*>(y_perm), dest_row, topk_w, static_cast<const bf16*>(residual), static_cast<bf16*>(out), T, K, H);
 }
 
 void moe_unpermute_sum(const void* dx_perm, const int* dest_row, void* dx, int T, int K, int H, cudaStream_t s) {
-  moe_combine(dx_perm, dest_row, nullptr, dx, T, K, H, s);
+  moe_combine(dx_perm, dest_row, nullptr, nullptr, dx, T, K, H, s);
 }
 
 void moe_combine_bwd(const void* dout, const void* y_perm, const int* row_src, const int* num_m_tiles,

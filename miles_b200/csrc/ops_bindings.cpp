@@ -157,17 +157,19 @@ at::Tensor moe_router_bwd(const at::Tensor& probs, const at::Tensor& ids, const 
   return dl;
 }
 
-// returns counts[E], offsets[E+1], dest_row[T*K], row_src[max_rows], tile_group[max_rows/128], num_m_tiles[1]
-std::vector<at::Tensor> moe_build_permutation(const at::Tensor& ids, int64_t E, int64_t max_rows) {
+// returns counts[E], offsets[E+1], dest_row[T*K], row_src[max_rows], tile_group[max_tiles,4], totals[2]
+std::vector<at::Tensor> moe_build_permutation(const at::Tensor& ids, int64_t E, int64_t max_rows, int64_t align) {
   CHECK_I32(ids);
   const c10::cuda::CUDAGuard guard(ids.device());
   const int T = ids.size(0), K = ids.size(1);
-  TORCH_CHECK(max_rows % 128 == 0, "max_rows must be a multiple of 128");
+  TORCH_CHECK(align >= 1 && max_rows >= 1, "bad permutation sizes");
+  const int64_t max_tiles = (max_rows + 127) / 128 + E;
   auto o = ids.options();
-  at::Tensor counts = at::empty({E}, o), offsets = at::empty({E + 1}, o), dest = at::full({T * K}, -1, o);
-  at::Tensor src = at::empty({max_rows}, o), tg = at::zeros({max_rows / 128}, o), nt = at::empty({1}, o);
-  mb::moe_build_permutation(ids.data_ptr<int>(), T, K, E, max_rows, counts.data_ptr<int>(), offsets.data_ptr<int>(),
-                            dest.data_ptr<int>(), src.data_ptr<int>(), tg.data_ptr<int>(), nt.data_ptr<int>(), cur_stream());
+  at::Tensor counts = at::empty({E}, o), offsets = at::empty({E + 1}, o), dest = at::empty({T * K}, o);
+  at::Tensor src = at::empty({max_rows}, o), tg = at::empty({max_tiles, 4}, o), nt = at::empty({2}, o);
+  mb::moe_build_permutation(ids.data_ptr<int>(), T, K, E, max_rows, max_tiles, align, counts.data_ptr<int>(),
+                            offsets.data_ptr<int>(), dest.data_ptr<int>(), src.data_ptr<int>(), tg.data_ptr<int>(),
+                            nt.data_ptr<int>(), cur_stream());
   return {counts, offsets, dest, src, tg, nt};
 }
 
@@ -181,12 +183,14 @@ at::Tensor moe_permute(const at::Tensor& x, const at::Tensor& row_src, const at:
   return xp;
 }
 
-at::Tensor moe_combine(const at::Tensor& y_perm, const at::Tensor& dest_row, const c10::optional<at::Tensor>& w, int64_t T, int64_t K) {
+at::Tensor moe_combine(const at::Tensor& y_perm, const at::Tensor& dest_row, const c10::optional<at::Tensor>& w, int64_t T, int64_t K,
+                       const c10::optional<at::Tensor>& residual) {
   CHECK_BF16(y_perm); CHECK_I32(dest_row);
   const c10::cuda::CUDAGuard guard(y_perm.device());
   const int H = y_perm.size(1);
   at::Tensor out = at::empty({T, H}, y_perm.options());
-  mb::moe_combine(y_perm.data_ptr(), dest_row.data_ptr<int>(), opt_ptr<float>(w), out.data_ptr(), T, K, H, cur_stream());
+  mb::moe_combine(y_perm.data_ptr(), dest_row.data_ptr<int>(), opt_ptr<float>(w), opt_ptr<void>(residual), out.data_ptr(), T, K, H,
+                  cur_stream());
   return out;
 }
 
@@ -246,7 +250,8 @@ void register_elementwise(pybind11::module_& m) {
   m.def("moe_router_bwd", &moe_router_bwd);
   m.def("moe_build_permutation", &moe_build_permutation);
   m.def("moe_permute", &moe_permute);
-  m.def("moe_combine", &moe_combine);
+  m.def("moe_combine", &moe_combine, pybind11::arg("y_perm"), pybind11::arg("dest_row"), pybind11::arg("w"), pybind11::arg("T"),
+        pybind11::arg("K"), pybind11::arg("residual") = c10::optional<at::Tensor>());
   m.def("moe_combine_bwd", &moe_combine_bwd);
   m.def("logprob_entropy_fwd", &logprob_entropy_fwd);
   m.def("logprob_entropy_bwd", &logprob_entropy_bwd);

@@ -87,10 +87,12 @@ class B200Qwen3:
         self.launches += 1
         return ids, w, probs
 
-    def _permute_plan(self, ids, E_local) -> MoeCtx:
+    def _permute_plan(self, ids, E_local, align: int = 1) -> MoeCtx:
+        """Expert-sorted row layout. ``align`` pads every expert's rows: 64 when weight gradients will be taken
+        (the wgrad contraction runs in 64-row blocks that must not straddle experts), 1 for inference."""
         T, K = ids.shape
-        max_rows = ((T * K + 127) // 128 + min(E_local, T * K)) * 128
-        counts, offsets, dest, src, tg, nt = self.C.moe_build_permutation(ids, E_local, max_rows)
+        max_rows = max(T * K + E_local * (align - 1), 1)
+        counts, offsets, dest, src, tg, nt = self.C.moe_build_permutation(ids, E_local, max_rows, align)
         self.launches += 3
         return MoeCtx(ids, None, None, offsets, dest, src, tg, nt, max_rows)
 
@@ -105,19 +107,19 @@ class B200Qwen3:
         self.launches += 3
         return (gu, act, yp) if keep else (None, None, yp)
 
-    def moe_forward(self, i, h2, replay_ids=None, record=None, keep=False):
+    def moe_forward(self, i, h2, replay_ids=None, record=None, keep=False, residual=None):
         cfg, P, C = self.cfg, self.store.params, self.C
         p = f"layers.{i}.moe."
         ids, w, probs = self._route(h2, P[p + "router.weight"], replay_ids)
         if record is not None:
             record.append(ids)
         if self.ep is not None:
-            return self.ep.moe_forward(self, i, h2, ids, w, probs, keep)
-        plan = self._permute_plan(ids, cfg.num_experts)
+            return self.ep.moe_forward(self, i, h2, ids, w, probs, keep, residual)
+        plan = self._permute_plan(ids, cfg.num_experts, 64 if keep else 1)
         plan.w, plan.probs = w, probs
         xp = C.moe_permute(h2, plan.src, plan.num_tiles, cfg.moe_top_k)
         gu, act, yp = self._experts_fwd(xp, plan, P[p + "w1"], P[p + "w2"], keep)
-        y = C.moe_combine(yp, plan.dest, w, h2.shape[0], cfg.moe_top_k)
+        y = C.moe_combine(yp, plan.dest, w, h2.shape[0], cfg.moe_top_k, residual)
         self.launches += 2
         saved = (plan, xp, gu, act, yp) if keep else None
         return y, saved
@@ -205,16 +207,16 @@ class B200Qwen3:
         h2, _, x2 = C.rmsnorm_fwd(o, x, P[p + "ln2.weight"], cfg.rms_eps)
         self.launches += 1
         if cfg.layer_is_moe(i):
-            y, _ = self.moe_forward(i, h2, replay_ids, record, keep=False)
-        else:
-            gu = self.linear(h2, P[p + "mlp.gate_up.weight"])
-            y = self.linear(C.swiglu_fwd(gu), P[p + "mlp.down.weight"])
-            self.launches += 1
+            y, _ = self.moe_forward(i, h2, replay_ids, record, keep=False, residual=x2)
+            return y
+        gu = self.linear(h2, P[p + "mlp.gate_up.weight"])
+        y = self.linear(C.swiglu_fwd(gu), P[p + "mlp.down.weight"])
+        self.launches += 1
         return x2.add_(y)
 
     def _decode_splits(self, B: int, meta: InferMeta) -> int:
         ctas = B * self.cfg.num_kv_heads
-        return max(1, min(16, (148 * 4) // max(ctas, 1)))
+        return max(1, min(16, (148 * 3) // max(ctas, 1)))
 
     def layer_backward(self, i, x, dy, positions, cu, max_seqlen, replay_ids=None):
         """Recompute layer i from its input ``x`` and back-propagate ``dy``; returns dx."""

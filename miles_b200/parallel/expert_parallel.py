@@ -52,7 +52,7 @@ class ExpertParallel:
         self.ctrl = torch.zeros(8, dtype=torch.int64, device=self.dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.identity = torch.arange(self.max_entries, dtype=torch.int32, device=self.dev)
-        self.big_tiles = torch.full((1,), 1 << 20, dtype=torch.int32, device=self.dev)
+        self.big_tiles = torch.tensor([1 << 20, 1 << 30], dtype=torch.int32, device=self.dev)
         self.pos_in_cap = torch.arange(cap, dtype=torch.int32, device=self.dev)[None, :]
         self._peers = (self.p_xrecv, self.p_meta, self.p_counts, self.p_flags, self.p_yback, self.p_flags2)
 
@@ -72,12 +72,12 @@ class ExpertParallel:
         C.ep_wait(self.flags, self.n, self.ctrl, 1, self.status)
         self.bytes_dispatched += rows.shape[-1] * 2 * ids_flat.numel()
 
-    def _recv_plan(self, model):
+    def _recv_plan(self, model, align: int = 1):
         """Group the received rows by local expert (rows beyond each source's count are ignored)."""
         n, cap = self.n, self.cap
         valid = self.pos_in_cap < self.counts[:, None]
         ids_recv = torch.where(valid, self.meta.view(n, cap, 2)[:, :, 0], torch.full_like(self.pos_in_cap, -1))
-        return model._permute_plan(ids_recv.reshape(n * cap, 1).contiguous(), self.el)
+        return model._permute_plan(ids_recv.reshape(n * cap, 1).contiguous(), self.el, align)
 
     def _return(self, rows_perm, plan, n_entries):
         C = self.C
@@ -88,13 +88,13 @@ class ExpertParallel:
     def _route(self, ids):
         T, K = ids.shape
         ids_rank = torch.div(ids, self.el, rounding_mode="floor").to(torch.int32).contiguous()
-        max_rows = ((T * K + 127) // 128 + self.n) * 128
-        counts_r, offsets_r, dest_r, _, _, _ = self.C.moe_build_permutation(ids_rank, self.n, max_rows)
+        counts_r, offsets_r, dest_r, _, _, _ = self.C.moe_build_permutation(ids_rank, self.n, T * K, 1)
         return counts_r, offsets_r, dest_r
 
-    def moe_forward(self, model, i, h2, ids, w, probs, keep: bool):
+    def moe_forward(self, model, i, h2, ids, w, probs, keep: bool, residual=None):
         if not self.fused:
-            return self._moe_forward_nccl(model, i, h2, ids, w, probs, keep)
+            y, saved = self._moe_forward_nccl(model, i, h2, ids, w, probs, keep)
+            return (y if residual is None else y.add_(residual)), saved
         cfg, P, C = self.cfg, model.store.params, self.C
         p = f"layers.{i}.moe."
         T, K = ids.shape
@@ -103,11 +103,11 @@ class ExpertParallel:
         route = self._route(ids)
         ids_flat = ids.reshape(-1)
         self._send(h2, ids_flat, route, K)
-        plan = self._recv_plan(model)
+        plan = self._recv_plan(model, 64 if keep else 1)
         xp = C.moe_permute(self.xrecv, plan.src, plan.num_tiles, 1)
         gu, act, yp = model._experts_fwd(xp, plan, P[p + "w1"], P[p + "w2"], keep)
         yslot = self._return(yp, plan, n_entries)
-        y = C.moe_combine(yslot, self.identity[:n_entries], w, T, K)
+        y = C.moe_combine(yslot, self.identity[:n_entries], w, T, K, residual)
         model.launches += 8
         saved = None
         if keep:
@@ -158,7 +158,7 @@ class ExpertParallel:
         order, sc, rc, le_recv = self._nccl_plan(ids)
         rows = h2[torch.div(order, K, rounding_mode="floor")]
         xr = self._exchange_nccl(rows.contiguous(), sc, rc)
-        plan = model._permute_plan(le_recv.contiguous(), self.el)
+        plan = model._permute_plan(le_recv.contiguous(), self.el, 64 if keep else 1)
         xp = C.moe_permute(xr, plan.src, plan.num_tiles, 1)
         gu, act, yp = model._experts_fwd(xp, plan, P[p + "w1"], P[p + "w2"], keep)
         yr = yp[plan.dest.long()]
@@ -176,7 +176,7 @@ class ExpertParallel:
         p = f"layers.{i}.moe."
         ids, w, plan, order = saved["ids"], saved["w"], saved["plan"], saved["order"]
         T, K = ids.shape
-        big = torch.full((1,), 1 << 20, dtype=torch.int32, device=dy.device)
+        big = torch.tensor([1 << 20, 1 << 30], dtype=torch.int32, device=dy.device)
         dy_slot, dw = C.moe_combine_bwd(dy, saved["yslot"], saved["ident"], big, w)
         dyr = self._exchange_nccl(dy_slot[order].contiguous(), saved["sc"], saved["rc"])
         dyp = C.moe_permute(dyr, plan.src, plan.num_tiles, 1)
