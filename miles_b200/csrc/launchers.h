@@ -76,6 +76,17 @@ void paged_decode_attention(const void* q, const void* k_cache, const void* v_ca
                             const int* seq_lens, void* out, float* scratch, int B, int Hq, int Hk, int page_size,
                             int max_pages, int num_splits, float scale, cudaStream_t s);
 
+// ---- attention_fwd.cu
+// Causal variable-length attention forward on tcgen05. q/k/v are bf16 [rows, heads, 128] views with row pitches
+// q_ld/k_ld/v_ld (elements); `tiles` is int32 [num_tiles][4] = {q_row0, q_rows (<=128), kv_row0, q_pos0}: the
+// tile covers query rows q_row0.. of the q tensor, whose sequence starts at row kv_row0 of k/v and whose first
+// query sits at position q_pos0 of that sequence. out bf16 [Tq, Hq, 128]; lse fp32 [Hq, Tq] (natural log) or
+// null. Returns 0, or -1 with flash_attn_last_error() set.
+int flash_attn_fwd(const void* q, long long q_ld, const void* k, long long k_ld, const void* v, long long v_ld,
+                   void* out, float* lse, const int* tiles, int num_tiles, long long Tq, long long Tkv, int Hq, int Hk,
+                   int head_dim, float scale, int* status, cudaStream_t stream);
+const char* flash_attn_last_error();
+
 // ---- rl.cu
 void gae_reverse_scan(const float* rewards, const float* values, const int* cu_seqlens, float* adv, float* ret,
                       int num_seqs, float gamma, float lam, cudaStream_t s);

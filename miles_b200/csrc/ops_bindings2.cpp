@@ -51,6 +51,29 @@ void paged_decode_attention(const at::Tensor& q, const at::Tensor& k_cache, cons
                              block_table.size(1), num_splits, scale, cur_stream());
 }
 
+// q [Tq, Hq, 128], k/v [Tkv, Hk, 128] (last dim contiguous, arbitrary row pitch); tiles int32 [n, 4].
+std::vector<at::Tensor> flash_attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& tiles,
+                                       double scale, const c10::optional<at::Tensor>& status) {
+  CHECK_I32(tiles);
+  for (const at::Tensor* t : {&q, &k, &v}) TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kBFloat16, "q/k/v must be bf16 CUDA tensors");
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && q.size(2) == 128 && k.size(2) == 128 && v.size(2) == 128,
+              "q/k/v must be [rows, heads, 128]");
+  TORCH_CHECK(q.stride(2) == 1 && k.stride(2) == 1 && v.stride(2) == 1 && q.stride(1) == 128 && k.stride(1) == 128 &&
+                  v.stride(1) == 128, "heads must be packed along each row");
+  TORCH_CHECK(tiles.is_contiguous() && tiles.dim() == 2 && tiles.size(1) == 4, "tiles must be contiguous [n, 4]");
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int64_t Tq = q.size(0), Hq = q.size(1), Hk = k.size(1);
+  at::Tensor out = at::empty({Tq, Hq, 128}, q.options());
+  at::Tensor lse = at::empty({Hq, Tq}, q.options().dtype(at::kFloat));
+  int* st = nullptr;
+  if (status.has_value()) { CHECK_I32((*status)); st = status->data_ptr<int>(); }
+  const int rc = mb::flash_attn_fwd(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                                    out.data_ptr(), lse.data_ptr<float>(), tiles.data_ptr<int>(), tiles.size(0), Tq,
+                                    k.size(0), Hq, Hk, 128, scale, st, cur_stream());
+  TORCH_CHECK(rc == 0, mb::flash_attn_last_error());
+  return {out, lse};
+}
+
 std::vector<at::Tensor> gae(const at::Tensor& rewards, const at::Tensor& values, const at::Tensor& cu, double gamma, double lam) {
   CHECK_F32(rewards); CHECK_F32(values); CHECK_I32(cu);
   const c10::cuda::CUDAGuard guard(rewards.device());
@@ -135,6 +158,7 @@ void register_more(pybind11::module_& m) {
   register_comm(m);
   m.def("sample_rows", &sample_rows);
   m.def("paged_decode_attention", &paged_decode_attention);
+  m.def("flash_attn_fwd", &flash_attn_fwd);
   m.def("gae", &gae);
   m.def("quant_mxfp8", &quant_mxfp8);
   m.def("dequant_mxfp8", &dequant_mxfp8);

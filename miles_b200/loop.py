@@ -63,6 +63,8 @@ class RLLoop:
         self.engine: Optional[Engine] = None
         self.client: Optional[EngineClient] = None
         if not getattr(args, "debug_train_only", False):
+            if args.offload_train:
+                self.actor.sleep()  # gradients are only needed inside train(); the KV cache gets the memory first
             self._build_engine()
         self.data_source = self._build_data_source()
         self.rollout_fn = self._build_rollout_fn()

@@ -18,15 +18,18 @@ from typing import Optional
 import torch
 
 from ..ops import _ext
+from ..ops.attention import TileCache
 from .config import ModelConfig
 from .params import ParamStore
 from .torch_impl import InferMeta
 
 
-def _flash_attn():
-    from flash_attn import flash_attn_varlen_func  # library attention (until the tcgen05 kernel lands for training)
+def _flash_attn_bwd():
+    # The attention backward still comes from the flash-attn library; it consumes the output and the
+    # log-sum-exp written by this package's tcgen05 forward kernel.
+    from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
 
-    return flash_attn_varlen_func
+    return _flash_attn_varlen_backward
 
 
 @dataclass
@@ -53,6 +56,13 @@ class B200Qwen3:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.launches = 0  # number of this library's kernels launched (reported by the benchmark)
         self._decode_scratch: Optional[torch.Tensor] = None
+        self._tiles = TileCache()
+
+    def attention(self, q, k, v, cu):
+        """Causal attention over packed sequences: returns (out [T, Hq, 128], lse [Hq, T])."""
+        out, lse = self.C.flash_attn_fwd(q, k, v, self._tiles.get(cu), self.cfg.head_dim ** -0.5, self.status)
+        self.launches += 1
+        return out, lse
 
     # ------------------------------------------------------------------ GEMM helpers
     def _gemm(self, a, b, out, a_mn=False, b_mn=False, acc=False):
@@ -202,7 +212,7 @@ class B200Qwen3:
                                      splits, scale)
             self.launches += 2
         else:
-            att = _flash_attn()(q, k, self._v_view(qkv), cu, cu, max_seqlen, max_seqlen, softmax_scale=scale, causal=True)
+            att, _ = self.attention(q, k, self._v_view(qkv), cu)
         o = self.linear(att.view(att.shape[0], -1), P[p + "attn.o.weight"])
         h2, _, x2 = C.rmsnorm_fwd(o, x, P[p + "ln2.weight"], cfg.rms_eps)
         self.launches += 1
@@ -225,10 +235,9 @@ class B200Qwen3:
         scale = cfg.head_dim ** -0.5
         # ---- recompute forward, keeping what the backward needs
         h1, rstd1, qkv, q, k, qr, kr = self._attn_qkv(i, x, positions, None, None)
-        q_, k_, v_ = q.requires_grad_(True), k.requires_grad_(True), self._v_view(qkv).detach().requires_grad_(True)
-        with torch.enable_grad():
-            att = _flash_attn()(q_, k_, v_, cu, cu, max_seqlen, max_seqlen, softmax_scale=scale, causal=True)
-        att2 = att.detach().view(att.shape[0], -1)
+        v = self._v_view(qkv)
+        att, lse = self.attention(q, k, v, cu)
+        att2 = att.view(att.shape[0], -1)
         o = self.linear(att2, P[p + "attn.o.weight"])
         h2, rstd2, x2 = C.rmsnorm_fwd(o, x, P[p + "ln2.weight"], cfg.rms_eps)
         self.launches += 1
@@ -256,8 +265,10 @@ class B200Qwen3:
         # ---- attention output projection
         datt = self.linear_dgrad(dx2, P[p + "attn.o.weight"])
         self.linear_wgrad(dx2, att2, G[p + "attn.o.weight"])
-        dq, dk, dv = torch.autograd.grad(att, (q_, k_, v_), datt.view_as(att))
-        dqkv = C.qk_norm_rope_bwd(dq.contiguous(), dk.contiguous(), dv.contiguous(), qkv, P.get(p + "attn.q_norm.weight"),
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        _flash_attn_bwd()(datt.view_as(att), q, k, v, att, lse, dq, dk, dv, cu, cu, max_seqlen, max_seqlen, 0.0, scale,
+                          True, -1, -1, 0.0, None, False, None, False)
+        dqkv = C.qk_norm_rope_bwd(dq, dk, dv, qkv, P.get(p + "attn.q_norm.weight"),
                                   P.get(p + "attn.k_norm.weight"), positions, qr, kr, G.get(p + "attn.q_norm.weight"),
                                   G.get(p + "attn.k_norm.weight"), cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta)
         self.launches += 1

@@ -89,6 +89,15 @@ class TrainActor:
         if role == "critic":
             self._init_value_head()
         self._setup_optimizer()
+        self.lora = None
+        if getattr(args, "lora_rank", 0) and args.lora_rank > 0 and role == "actor":
+            from ..lora import LoRAManager
+
+            self.lora = LoRAManager(self.store, args.lora_rank, args.lora_alpha or args.lora_rank, args.target_modules or "all-linear",
+                                    lr=args.lr, weight_decay=args.weight_decay, seed=args.seed, betas=(args.adam_beta1, args.adam_beta2))
+            self.opt = None  # base weights are frozen: only the adapters have optimizer state
+            if getattr(args, "lora_adapter_path", None):
+                self.lora.load(args.lora_adapter_path)
         if getattr(args, "load", None):
             from ..checkpoint import load_checkpoint
 
@@ -317,7 +326,10 @@ class TrainActor:
                     for k, v in m.items():
                         metrics_acc[k] = metrics_acc.get(k, 0.0) + v.detach().float() * scale
                 self._reduce_grads()
-                if self.opt is not None:
+                if self.lora is not None:
+                    self.lora.grads_from_weight_grads()
+                    grad_norm = self.lora.step(a.clip_grad)
+                elif self.opt is not None:
                     grad_norm = self.opt.step(1.0)
                 self.global_step += 1
         if self.on_gpu:
@@ -469,7 +481,9 @@ class TrainActor:
 
         with Timer().context("save_model"):
             if getattr(self.args, "save", None):
-                save_checkpoint(self, self.args.save, rollout_id)
+                d = save_checkpoint(self, self.args.save, rollout_id)
+                if self.lora is not None and self.ps.rank == 0:
+                    self.lora.save(os.path.join(d, "adapter"), getattr(self.args, "hf_checkpoint", None) or "")
             if getattr(self.args, "save_hf", None):
                 from ..checkpoint import export_hf
 

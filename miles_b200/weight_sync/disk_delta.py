@@ -1,0 +1,107 @@
+"""Disk-delta weight transfer: ship only what changed since the previous sync through a shared directory.
+
+The trainer keeps a CPU snapshot of the last synced weights; per sync it writes, for every tensor, either
+the byte-wise XOR against the snapshot or the new bytes (``--update-weight-delta-encoding xor|overwrite``),
+compressed (zlib here; the reference uses zstd) into per-rank ``model-NNNNN-of-MMMMM.delta`` files plus an
+index with ``version``, ``base_version``, ``encoding`` and a checksum per tensor; engines pull the index,
+apply the delta to their weights and bump the version.  Reference:
+miles/backends/megatron_utils/update_weight/update_weight_from_distributed/delta.py:32-378,
+miles/utils/disk_delta.py:21-87.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import zlib
+from typing import Optional
+
+import torch
+
+
+def _bytes(t: torch.Tensor) -> bytes:
+    return t.detach().contiguous().cpu().view(torch.uint8).numpy().tobytes()
+
+
+def checksum(b: bytes, kind: str = "sha1") -> str:
+    return hashlib.blake2b(b, digest_size=16).hexdigest() if kind == "blake2" else hashlib.sha1(b).hexdigest()
+
+
+class DiskDeltaWriter:
+    def __init__(self, directory: str, encoding: str = "xor", checksum_kind: str = "sha1", rank: int = 0, world: int = 1):
+        assert encoding in ("xor", "overwrite")
+        self.dir, self.encoding, self.ck = directory, encoding, checksum_kind
+        self.rank, self.world = rank, world
+        self.snapshot: dict = {}
+        self.version = 0
+        os.makedirs(directory, exist_ok=True)
+
+    def write(self, named_tensors, version: int) -> dict:
+        """Write the delta of ``named_tensors`` against the snapshot; returns this rank's index entry."""
+        vdir = os.path.join(self.dir, f"v{version:08d}")
+        os.makedirs(vdir, exist_ok=True)
+        fname = f"model-{self.rank + 1:05d}-of-{self.world:05d}.delta"
+        entries, blob, off = {}, bytearray(), 0
+        raw_total = 0
+        for name, t in named_tensors:
+            new = _bytes(t)
+            raw_total += len(new)
+            old = self.snapshot.get(name)
+            if self.encoding == "xor" and old is not None and len(old) == len(new):
+                a = torch.frombuffer(bytearray(new), dtype=torch.uint8)
+                b = torch.frombuffer(bytearray(old), dtype=torch.uint8)
+                payload, enc = (a ^ b).numpy().tobytes(), "xor"
+            else:
+                payload, enc = new, "overwrite"
+            comp = zlib.compress(payload, 1)
+            entries[name] = {"offset": off, "nbytes": len(comp), "raw_nbytes": len(new), "encoding": enc,
+                             "dtype": str(t.dtype).replace("torch.", ""), "shape": list(t.shape), "checksum": checksum(new, self.ck)}
+            blob += comp
+            off += len(comp)
+            self.snapshot[name] = new
+        tmp = os.path.join(vdir, fname + ".tmp")
+        with open(tmp, "wb") as f:
+            f.write(blob)
+        os.replace(tmp, os.path.join(vdir, fname))
+        idx = {"version": version, "base_version": self.version, "file": fname, "tensors": entries,
+               "raw_bytes": raw_total, "compressed_bytes": off, "checksum_kind": self.ck}
+        with open(os.path.join(vdir, f"index-{self.rank:05d}.json"), "w") as f:
+            json.dump(idx, f)
+        self.version = version
+        return idx
+
+
+class DiskDeltaReader:
+    def __init__(self, directory: str):
+        self.dir = directory
+        self.version = 0
+
+    def apply(self, version: int, params: dict, strict_base: bool = True) -> int:
+        """Apply every rank's delta of ``version`` onto ``params`` (name -> tensor). Returns #tensors updated."""
+        vdir = os.path.join(self.dir, f"v{version:08d}")
+        n = 0
+        for fn in sorted(os.listdir(vdir)):
+            if not fn.startswith("index-"):
+                continue
+            idx = json.load(open(os.path.join(vdir, fn)))
+            if strict_base and idx["base_version"] != self.version and any(e["encoding"] == "xor" for e in idx["tensors"].values()):
+                raise RuntimeError(f"delta v{version} is based on v{idx['base_version']} but this engine holds v{self.version}")
+            blob = open(os.path.join(vdir, idx["file"]), "rb").read()
+            for name, e in idx["tensors"].items():
+                if name not in params:
+                    continue
+                raw = zlib.decompress(blob[e["offset"]:e["offset"] + e["nbytes"]])
+                dst = params[name]
+                if e["encoding"] == "xor":
+                    cur = torch.frombuffer(bytearray(_bytes(dst)), dtype=torch.uint8)
+                    new = (cur ^ torch.frombuffer(bytearray(raw), dtype=torch.uint8)).numpy().tobytes()
+                else:
+                    new = raw
+                if checksum(new, idx.get("checksum_kind", "sha1")) != e["checksum"]:
+                    raise RuntimeError(f"checksum mismatch for {name} in delta v{version}")
+                t = torch.frombuffer(bytearray(new), dtype=torch.uint8).view(getattr(torch, e["dtype"])).reshape(e["shape"])
+                with torch.no_grad():
+                    dst.copy_(t.to(dst.device))
+                n += 1
+        self.version = version
+        return n
