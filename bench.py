@@ -126,6 +126,7 @@ def main() -> None:
     ]
     if not ns.no_routing_replay:
         flags += ["--use-rollout-routing-replay"]
+    t_start = time.perf_counter()
     args = parse_args(flags)
     args.synthetic_prompt_len = ns.prompt_len
     loop = RLLoop(args)
@@ -143,8 +144,15 @@ def main() -> None:
             n += loop.actor.opt.launches
         return n
 
+    def note(msg: str) -> None:  # progress on stderr; stdout carries only the JSON line
+        if rank == 0:
+            print(f"[bench +{time.perf_counter() - t_start:7.1f}s] {msg}", file=sys.stderr, flush=True)
+
+    note(f"initialised: plan={loop.actor.plan.get('name')} mem={torch.cuda.memory_allocated(dev) / 2**30:.1f} GiB")
     for i in range(ns.warmup):
-        loop.step(i)
+        m = loop.step(i)
+        note(f"warm-up step {i}: rollout {m.get('perf/rollout_time', 0):.1f}s train {m.get('perf/train_time', 0):.1f}s "
+             f"peak mem {torch.cuda.max_memory_allocated(dev) / 2**30:.1f} GiB")
     barrier()
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
     if rank == 0:
@@ -160,6 +168,7 @@ def main() -> None:
     for i in range(ns.warmup, ns.warmup + ns.steps):
         last = loop.step(i)
         tokens += last["perf/step_tokens"]
+        note(f"timed step {i}: rollout {last.get('perf/rollout_time', 0):.1f}s train {last.get('perf/train_time', 0):.1f}s")
     ev1.record()
     barrier()
     wall = time.perf_counter() - t0

@@ -106,8 +106,9 @@ class Engine:
     def __init__(self, model, *, max_running: int = 64, num_pages: Optional[int] = None, page_size: int = 64,
                  max_seq_len: int = 16384, max_prefill_tokens: int = 16384, kv_mem_bytes: Optional[int] = None,
                  use_cuda_graph: Optional[bool] = None, eos_token_id: Optional[int] = None, kv_dtype=None,
-                 sync=None, ep_decode=None):
+                 sync=None, ep_decode=None, kv_storage: Optional[torch.Tensor] = None):
         self.model = model
+        self.kv_storage = kv_storage  # caller-owned uint8 device buffer to carve the KV cache from (None = allocate)
         self.sync = sync            # lockstep agreement across expert-parallel ranks (None = independent engine)
         self.ep_decode = ep_decode  # small expert-parallel exchange used by decode steps (graph friendly)
         self.last_mode = 0
@@ -150,6 +151,17 @@ class Engine:
     def _alloc_kv(self) -> None:
         cfg = self.cfg
         slots = self.num_pages * self.page_size
+        if self.kv_storage is not None:
+            # The buffer is shared in time with another user (the trainer's expert gradients): its contents
+            # are undefined whenever a rollout starts, which is fine because every page is written by a
+            # prefill or decode step before any position of it is read.
+            per = slots * cfg.num_kv_heads * cfg.head_dim
+            esz = torch.empty((), dtype=self.kv_dtype).element_size()
+            assert self.kv_storage.numel() >= 2 * cfg.num_layers * per * esz, "kv_storage is too small"
+            flat = self.kv_storage[:2 * cfg.num_layers * per * esz].view(self.kv_dtype)
+            views = [flat[i * per:(i + 1) * per].view(slots, cfg.num_kv_heads, cfg.head_dim) for i in range(2 * cfg.num_layers)]
+            self.kv_cache = [(views[2 * i], views[2 * i + 1]) for i in range(cfg.num_layers)]
+            return
         self.kv_cache = [(torch.zeros(slots, cfg.num_kv_heads, cfg.head_dim, dtype=self.kv_dtype, device=self.dev),
                           torch.zeros(slots, cfg.num_kv_heads, cfg.head_dim, dtype=self.kv_dtype, device=self.dev))
                          for _ in range(cfg.num_layers)]

@@ -96,6 +96,10 @@ class RLLoop:
             per_tok = 2 * cfg.num_layers * cfg.num_kv_heads * cfg.head_dim * 2
             want = max_running * (max_ctx + page) * per_tok
             kv_bytes = max(min(budget, want), per_tok * page * 4)
+        kv_storage = None
+        if self.actor.on_gpu and getattr(a, "share_kv_grad_memory", True) and not getattr(a, "debug_rollout_only", False):
+            # rollout and training alternate in this loop: the KV cache borrows the bytes of the expert gradients
+            kv_storage = self.actor.lend_arena(kv_bytes)
         sync = ep_decode = None
         if self.actor.ep_dispatcher is not None:
             from .engine.core import LockstepSync
@@ -106,7 +110,7 @@ class RLLoop:
         self.engine = Engine(self.actor.model, sync=sync, ep_decode=ep_decode, max_running=max_running, page_size=page, max_seq_len=max_ctx,
                              max_prefill_tokens=getattr(a, "engine_max_prefill_tokens", 16384), kv_mem_bytes=kv_bytes,
                              use_cuda_graph=not getattr(a, "sglang_disable_cuda_graph", False) and self.actor.on_gpu,
-                             eos_token_id=getattr(self.tokenizer, "eos_token_id", None))
+                             eos_token_id=getattr(self.tokenizer, "eos_token_id", None), kv_storage=kv_storage)
         self.client = EngineClient([self.engine], self.tokenizer)
         self.actor.connect_rollout_engines([self.engine])
 

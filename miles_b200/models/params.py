@@ -149,10 +149,19 @@ class ParamStore:
         return self.params["embed.weight"] if self.cfg.tie_embeddings else self.params["lm_head.weight"]
 
     # ------------------------------------------------------------------ gradients
-    def allocate_grads(self, dtype: torch.dtype = torch.float32, expert_dtype: Optional[torch.dtype] = None) -> None:
+    def allocate_grads(self, dtype: torch.dtype = torch.float32, expert_dtype: Optional[torch.dtype] = None,
+                       expert_storage: Optional[torch.Tensor] = None) -> None:
+        """Flat gradient buffers per group. ``expert_storage`` (uint8) places the expert gradients in memory
+        the caller owns — the colocated loop lends the same bytes to the KV cache between training steps."""
         for g, n in self.sizes.items():
             dt = expert_dtype if (g == "expert" and expert_dtype is not None) else dtype
-            if self.grad[g] is None or self.grad[g].dtype != dt:
+            if g == "expert" and expert_storage is not None and n > 0:
+                nbytes = n * torch.empty((), dtype=dt).element_size()
+                assert expert_storage.dtype == torch.uint8 and expert_storage.numel() >= nbytes
+                self.grad[g] = None
+                self.grad[g] = expert_storage[:nbytes].view(dt)
+                self.grad[g].zero_()
+            elif self.grad[g] is None or self.grad[g].dtype != dt:
                 self.grad[g] = None
                 self.grad[g] = torch.zeros(n, dtype=dt, device=self.device)
         self.grads.clear()

@@ -1,6 +1,6 @@
 """Convert a HuggingFace safetensors checkpoint into the native sharded format (one file per rank).
 
-    python tools/convert_hf_to_native.py --hf-checkpoint /path/to/Qwen3-4B --save /ckpt/qwen3-4b --expert-model-parallel-size 1
+    python -m miles_b200.tools.convert_hf_to_native --hf-checkpoint /path/to/Qwen3-4B --save /ckpt/qwen3-4b --expert-model-parallel-size 1
 
 Writes ``<save>/iter_0000000/rank_%05d.pt`` and ``latest_checkpointed_iteration.txt`` so that
 ``--load <save>`` (or ``--ref-load``) starts from the converted weights.  Counterpart of the reference's
@@ -11,7 +11,6 @@ import json
 import os
 import sys
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import torch
 

@@ -1,6 +1,6 @@
 """Convert a native checkpoint (all ranks) into HuggingFace safetensors shards.
 
-    python tools/convert_native_to_hf.py --load /ckpt/run --ckpt-step 10 --output /export/hf
+    python -m miles_b200.tools.convert_native_to_hf --load /ckpt/run --ckpt-step 10 --output /export/hf
 
 Counterpart of the reference's tools/convert_torch_dist_to_hf.py.
 """
@@ -9,7 +9,6 @@ import json
 import os
 import sys
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import torch
 from safetensors.torch import save_file

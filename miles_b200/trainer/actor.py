@@ -80,6 +80,7 @@ class TrainActor:
         self.custom_loss_fn = load_function(args.custom_loss_function_path) if getattr(args, "custom_loss_function_path", None) else None
         self.opt: Optional[FlatAdam] = None
         self.plan: dict = {}
+        self.arena: Optional[torch.Tensor] = None  # see lend_arena()
         self.weights_backup: dict = {}   # tag -> pinned host copies of the flat buffers (ref / old_actor / teacher)
         self.rollout_engines: list = []
         self.global_step = 0
@@ -464,9 +465,28 @@ class TrainActor:
         with Timer().context("update_weights"):
             return sync_weights(self, self.rollout_engines)
 
+    def lend_arena(self, min_bytes: int) -> torch.Tensor:
+        """One device buffer that holds the expert gradients while training and is lent to the colocated
+        engine (KV cache) while rolling out. The two uses never overlap in the synchronous loop, the
+        addresses stay fixed (captured decode graphs remain valid), and nothing is freed or reallocated
+        between phases. Returns the uint8 buffer (at least ``min_bytes`` long)."""
+        n = self.store.sizes.get("expert", 0) * torch.empty((), dtype=self._expert_grad_dtype).element_size()
+        size = max(int(min_bytes), n, 256)
+        if self.arena is None or self.arena.numel() < size:
+            self.store.free_grads()
+            self.arena = None
+            if self.on_gpu:
+                torch.cuda.empty_cache()
+            self.arena = torch.empty(size, dtype=torch.uint8, device=self.device)
+            self.store.allocate_grads(torch.float32, self._expert_grad_dtype, expert_storage=self.arena)
+        return self.arena
+
     def sleep(self) -> None:
-        """Release trainer-only device memory (gradients) so that the rollout engine can use it."""
+        """Release trainer-only device memory (gradients) so that the rollout engine can use it. With a lent
+        arena the gradients already share their bytes with the KV cache and nothing has to move."""
         with Timer().context("sleep"):
+            if self.arena is not None:
+                return
             self.store.free_grads()
             if self.on_gpu:
                 torch.cuda.empty_cache()
@@ -474,7 +494,8 @@ class TrainActor:
     def wake_up(self) -> None:
         with Timer().context("wake_up"):
             if not self.store.grads:
-                self.store.allocate_grads(torch.float32, getattr(self, "_expert_grad_dtype", torch.float32))
+                self.store.allocate_grads(torch.float32, getattr(self, "_expert_grad_dtype", torch.float32),
+                                          expert_storage=self.arena)
 
     def save_model(self, rollout_id: int, force_sync: bool = False) -> None:
         from ..checkpoint import save_checkpoint
