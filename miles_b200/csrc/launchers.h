@@ -87,6 +87,19 @@ int flash_attn_fwd(const void* q, long long q_ld, const void* k, long long k_ld,
                    int head_dim, float scale, int* status, cudaStream_t stream);
 const char* flash_attn_last_error();
 
+// ---- decode_stream.cu / decode_small.cu (at most 8 tokens: persistent weight-streaming mma.sync kernel fed by
+// bulk asynchronous copies, RMSNorm folded in; `status` receives a code if a bounded wait gives up)
+void small_gemv(const void* x, int T, const void* norm_w, float eps, const void* W, int N, int K, const void* residual,
+                void* out, bool out_fp32, int* status, cudaStream_t s);
+void router_small(const float* logits, int T, int E, int K, bool renorm, int* topk_ids, float* topk_w, int* active,
+                  int* pair_count, int* pair_list, cudaStream_t s);
+// gu[pair, 2I] = W1[e] . norm(x[pair / K]) for the experts listed in `active` (count in active[0])
+void moe_small_up(const void* x, const void* norm_w, float eps, const void* W1, const int* active, const int* pair_count,
+                  const int* pair_list, int max_active, int H, int I, int K, void* gu, int* status, cudaStream_t s);
+// y[pair, H] = W2[e] . (silu(gu[pair, :I]) * gu[pair, I:])
+void moe_small_down(const void* gu, const void* W2, const int* active, const int* pair_count, const int* pair_list,
+                    int max_active, int H, int I, void* y, int* status, cudaStream_t s);
+
 // ---- rl.cu
 void gae_reverse_scan(const float* rewards, const float* values, const int* cu_seqlens, float* adv, float* ret,
                       int num_seqs, float gamma, float lam, cudaStream_t s);

@@ -74,6 +74,58 @@ std::vector<at::Tensor> flash_attn_fwd(const at::Tensor& q, const at::Tensor& k,
   return {out, lse};
 }
 
+// ---- small-batch decode kernels (T <= 8)
+void small_gemv(const at::Tensor& x, const c10::optional<at::Tensor>& norm_w, double eps, const at::Tensor& W,
+                const c10::optional<at::Tensor>& residual, at::Tensor& out, const c10::optional<at::Tensor>& status) {
+  CHECK_BF16(x); CHECK_BF16(W);
+  const int T = x.size(0), K = x.size(1), N = W.size(0);
+  TORCH_CHECK(T >= 1 && T <= 8 && W.size(1) == K && K % 32 == 0 && N % 16 == 0, "small_gemv: need 1 <= T <= 8, K % 32 == 0, N % 16 == 0");
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.size(0) == T && out.size(1) == N, "small_gemv: bad output shape");
+  const bool f32 = out.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || out.scalar_type() == at::kBFloat16, "small_gemv: output must be fp32 or bf16");
+  if (norm_w.has_value()) CHECK_BF16((*norm_w));
+  if (residual.has_value()) { CHECK_BF16((*residual)); TORCH_CHECK(residual->numel() == out.numel(), "small_gemv: residual shape"); }
+  const c10::cuda::CUDAGuard guard(x.device());
+  mb::small_gemv(x.data_ptr(), T, norm_w.has_value() ? norm_w->data_ptr() : nullptr, eps, W.data_ptr(), N, K,
+                 residual.has_value() ? residual->data_ptr() : nullptr, out.data_ptr(), f32,
+                 status.has_value() ? status->data_ptr<int>() : nullptr, cur_stream());
+}
+
+void router_small(const at::Tensor& logits, int64_t K, bool renorm, at::Tensor& ids, at::Tensor& w, at::Tensor& active,
+                  at::Tensor& pair_count, at::Tensor& pair_list) {
+  CHECK_F32(logits); CHECK_I32(ids); CHECK_F32(w); CHECK_I32(active); CHECK_I32(pair_count); CHECK_I32(pair_list);
+  const int T = logits.size(0), E = logits.size(1);
+  TORCH_CHECK(T >= 1 && T <= 8 && E <= 1024 && K <= 32 && K <= E, "router_small: unsupported shape");
+  TORCH_CHECK(ids.numel() >= T * K && w.numel() >= T * K && active.numel() >= E + 1 && pair_count.numel() >= E && pair_list.numel() >= 8 * E,
+              "router_small: output buffers too small");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  mb::router_small(logits.data_ptr<float>(), T, E, K, renorm, ids.data_ptr<int>(), w.data_ptr<float>(), active.data_ptr<int>(),
+                   pair_count.data_ptr<int>(), pair_list.data_ptr<int>(), cur_stream());
+}
+
+void moe_small_up(const at::Tensor& x, const at::Tensor& norm_w, double eps, const at::Tensor& W1, const at::Tensor& active,
+                  const at::Tensor& pair_count, const at::Tensor& pair_list, int64_t max_active, int64_t K, at::Tensor& act,
+                  const c10::optional<at::Tensor>& status) {
+  CHECK_BF16(x); CHECK_BF16(norm_w); CHECK_BF16(W1); CHECK_BF16(act);
+  const int H = x.size(1), I = W1.size(1) / 2;
+  TORCH_CHECK(W1.dim() == 3 && W1.size(2) == H && H % 32 == 0 && I % 8 == 0 && act.size(1) == 2 * I, "moe_small_up: unsupported shape");
+  TORCH_CHECK((2 * I) % 16 == 0, "moe_small_up: 2I must be a multiple of 16");
+  const c10::cuda::CUDAGuard guard(x.device());
+  mb::moe_small_up(x.data_ptr(), norm_w.data_ptr(), eps, W1.data_ptr(), active.data_ptr<int>(), pair_count.data_ptr<int>(),
+                   pair_list.data_ptr<int>(), max_active, H, I, K, act.data_ptr(),
+                   status.has_value() ? status->data_ptr<int>() : nullptr, cur_stream());
+}
+
+void moe_small_down(const at::Tensor& act, const at::Tensor& W2, const at::Tensor& active, const at::Tensor& pair_count,
+                    const at::Tensor& pair_list, int64_t max_active, at::Tensor& y, const c10::optional<at::Tensor>& status) {
+  CHECK_BF16(act); CHECK_BF16(W2); CHECK_BF16(y);
+  const int I = act.size(1) / 2, H = W2.size(1);
+  TORCH_CHECK(W2.dim() == 3 && W2.size(2) == I && H % 16 == 0 && I % 32 == 0 && y.size(1) == H, "moe_small_down: unsupported shape");
+  const c10::cuda::CUDAGuard guard(act.device());
+  mb::moe_small_down(act.data_ptr(), W2.data_ptr(), active.data_ptr<int>(), pair_count.data_ptr<int>(), pair_list.data_ptr<int>(),
+                     max_active, H, I, y.data_ptr(), status.has_value() ? status->data_ptr<int>() : nullptr, cur_stream());
+}
+
 std::vector<at::Tensor> gae(const at::Tensor& rewards, const at::Tensor& values, const at::Tensor& cu, double gamma, double lam) {
   CHECK_F32(rewards); CHECK_F32(values); CHECK_I32(cu);
   const c10::cuda::CUDAGuard guard(rewards.device());
@@ -159,6 +211,10 @@ void register_more(pybind11::module_& m) {
   m.def("sample_rows", &sample_rows);
   m.def("paged_decode_attention", &paged_decode_attention);
   m.def("flash_attn_fwd", &flash_attn_fwd);
+  m.def("small_gemv", &small_gemv);
+  m.def("router_small", &router_small);
+  m.def("moe_small_up", &moe_small_up);
+  m.def("moe_small_down", &moe_small_down);
   m.def("gae", &gae);
   m.def("quant_mxfp8", &quant_mxfp8);
   m.def("dequant_mxfp8", &dequant_mxfp8);

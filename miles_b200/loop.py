@@ -95,7 +95,15 @@ class RLLoop:
             budget = int(total * frac) - self.actor.store.nbytes()
             per_tok = 2 * cfg.num_layers * cfg.num_kv_heads * cfg.head_dim * 2
             want = max_running * (max_ctx + page) * per_tok
-            kv_bytes = max(min(budget, want), per_tok * page * 4)
+            # what is really free once weights, gradients and resident optimizer states are placed, keeping
+            # an eighth of the device for activations; expert gradients count as free (the arena is shared)
+            free_now = torch.cuda.mem_get_info(self.actor.device)[0]
+            lend = 0
+            if getattr(a, "share_kv_grad_memory", True) and self.actor.store.grad.get("expert") is not None:
+                g = self.actor.store.grad["expert"]
+                lend = g.numel() * g.element_size()
+            room = free_now + lend - total // 8
+            kv_bytes = max(min(budget, want, room), per_tok * page * 4)
         kv_storage = None
         if self.actor.on_gpu and getattr(a, "share_kv_grad_memory", True) and not getattr(a, "debug_rollout_only", False):
             # rollout and training alternate in this loop: the KV cache borrows the bytes of the expert gradients

@@ -57,6 +57,8 @@ class B200Qwen3:
         self.launches = 0  # number of this library's kernels launched (reported by the benchmark)
         self._decode_scratch: Optional[torch.Tensor] = None
         self._tiles = TileCache()
+        self._ident: Optional[torch.Tensor] = None
+        self.small_decode = True  # weight-streaming kernels for decode steps of at most SMALL_T rows
 
     def attention(self, q, k, v, cu):
         """Causal attention over packed sequences: returns (out [T, Hq, 128], lse [Hq, T])."""
@@ -198,6 +200,9 @@ class B200Qwen3:
         """Inference/no-grad forward of one layer: returns the layer output."""
         cfg, P, C = self.cfg, self.store.params, self.C
         p = f"layers.{i}."
+        if (meta is not None and not meta.is_prefill and x.shape[0] <= self.SMALL_T and replay_ids is None
+                and (self.ep is None or not cfg.layer_is_moe(i)) and self.small_decode):
+            return self._layer_forward_small(i, x, positions, meta, kv_cache, record)
         h1, rstd1, qkv, q, k, _, _ = self._attn_qkv(i, x, positions, meta, kv_cache)
         scale = cfg.head_dim ** -0.5
         if meta is not None and not meta.is_prefill:
@@ -223,6 +228,64 @@ class B200Qwen3:
         y = self.linear(C.swiglu_fwd(gu), P[p + "mlp.down.weight"])
         self.launches += 1
         return x2.add_(y)
+
+    SMALL_T = 8  # decode steps with at most this many rows take the weight-streaming kernels
+
+    def _layer_forward_small(self, i, x, positions, meta: InferMeta, kv_cache, record=None):
+        """Decode forward of one layer for at most 8 rows: 8-9 light launches instead of 14-15, the two RMSNorms
+        folded into the projections that consume them, no expert permutation (per-expert pair lists)."""
+        cfg, P, C = self.cfg, self.store.params, self.C
+        p = f"layers.{i}."
+        T, dev = x.shape[0], x.device
+        wqkv = P[p + "attn.qkv.weight"]
+        qkv = torch.empty(T, wqkv.shape[0], dtype=torch.bfloat16, device=dev)
+        C.small_gemv(x, P[p + "ln1.weight"], cfg.rms_eps, wqkv, None, qkv, self.status)
+        if cfg.qkv_bias:
+            qkv += P[p + "attn.qkv.bias"]
+        kc, vc = kv_cache[i]
+        q, _, _, _ = C.qk_norm_rope_fwd(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"), positions,
+                                        cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps, kc, vc,
+                                        meta.slot_mapping, False)
+        att = torch.empty_like(q)
+        splits = self._decode_splits(T, meta)
+        need = T * cfg.num_q_heads * splits * 130
+        if self._decode_scratch is None or self._decode_scratch.numel() < need:
+            self._decode_scratch = torch.empty(need, dtype=torch.float32, device=dev)
+        C.paged_decode_attention(q, kc, vc, meta.block_table, meta.seq_lens, att, self._decode_scratch, meta.page_size,
+                                 splits, cfg.head_dim ** -0.5)
+        x2 = torch.empty_like(x)
+        C.small_gemv(att.view(T, -1), None, cfg.rms_eps, P[p + "attn.o.weight"], x, x2, self.status)
+        self.launches += 6
+        ln2 = P[p + "ln2.weight"]
+        if cfg.layer_is_moe(i):
+            E, K = cfg.num_experts, cfg.moe_top_k
+            w1, w2 = P[p + "moe.w1"], P[p + "moe.w2"]
+            ids = torch.empty(T, K, dtype=torch.int32, device=dev)
+            w = torch.empty(T, K, dtype=torch.float32, device=dev)
+            lists = torch.empty(1 + E + E + 8 * E, dtype=torch.int32, device=dev)
+            active, pc, pl = lists[:1 + E], lists[1 + E:1 + 2 * E], lists[1 + 2 * E:]
+            logits = torch.empty(T, E, dtype=torch.float32, device=dev)
+            C.small_gemv(x2, ln2, cfg.rms_eps, P[p + "moe.router.weight"], None, logits, self.status)
+            C.router_small(logits, K, cfg.norm_topk_prob, ids, w, active, pc, pl)
+            if record is not None:
+                record.append(ids)
+            max_active = min(E, T * K)
+            act = torch.empty(T * K, w1.shape[1], dtype=torch.bfloat16, device=dev)  # gate | up; SwiGLU happens in the consumer
+            C.moe_small_up(x2, ln2, cfg.rms_eps, w1, active, pc, pl, max_active, K, act, self.status)
+            yp = torch.empty(T * K, x.shape[1], dtype=torch.bfloat16, device=dev)
+            C.moe_small_down(act, w2, active, pc, pl, max_active, yp, self.status)
+            if self._ident is None or self._ident.numel() < T * K:
+                self._ident = torch.arange(self.SMALL_T * K, dtype=torch.int32, device=dev)
+            y = C.moe_combine(yp, self._ident[:T * K], w, T, K, x2)
+            self.launches += 5
+            return y
+        wgu = P[p + "mlp.gate_up.weight"]
+        gu = torch.empty(T, wgu.shape[0], dtype=torch.bfloat16, device=dev)
+        C.small_gemv(x2, ln2, cfg.rms_eps, wgu, None, gu, self.status)
+        y = torch.empty_like(x)
+        C.small_gemv(C.swiglu_fwd(gu), None, cfg.rms_eps, P[p + "mlp.down.weight"], x2, y, self.status)
+        self.launches += 3
+        return y
 
     def _decode_splits(self, B: int, meta: InferMeta) -> int:
         ctas = B * self.cfg.num_kv_heads

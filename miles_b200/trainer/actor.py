@@ -30,9 +30,10 @@ from .optimizer import FlatAdam, OptimConfig
 _DT = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
 
 
-def choose_memory_plan(total_bytes: int, dense_params: int, expert_params: int, reserve_frac: float = 0.42) -> dict:
+def choose_memory_plan(total_bytes: int, dense_params: int, expert_params: int, reserve_frac: float = 0.30) -> dict:
     """Pick gradient / optimizer-state precision and placement that leaves ``reserve_frac`` of the device
-    for activations and the KV cache.  Bytes per parameter: bf16 weight 2 + gradient + two moments (+ master)."""
+    for activations and for the part of the KV cache that does not fit into the bytes it borrows from the
+    expert gradients.  Bytes per parameter: bf16 weight 2 + gradient + two moments (+ master)."""
     budget = total_bytes * (1.0 - reserve_frac)
     n = dense_params + expert_params
     plans = [

@@ -72,7 +72,8 @@ def main():
             dist.broadcast(rp, src=r)
             _, _, lp_r, _ = ref.forward_backward(b[0], b[1], b[2], b[3], b[4], 1.0, loss_fn_for(b[5]), replay=rp)
             lps[r] = lp_r
-        assert (lp - lps[ps.rank]).abs().max().item() < 2e-2, (lp - lps[ps.rank]).abs().max().item()
+        d = (lp - lps[ps.rank]).abs()
+        assert d.max().item() < 5e-2 and d.mean().item() < 5e-3, (d.max().item(), d.mean().item())  # bf16, different reduction order
         assert torch.allclose(lp0, lp, atol=1e-5)
         # expert gradients: the owner accumulates the contributions of every rank's tokens
         for s in store.specs:
