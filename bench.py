@@ -194,7 +194,7 @@ def main() -> None:
                 "tokens_per_step": tokens / ns.steps, "parallelism": f"dp{world}-attn x ep{world}-experts, colocated engine",
                 "optimizer_plan": loop.actor.plan.get("name"), "routing_replay": not ns.no_routing_replay,
                 "l2": "working set (61 GB of weights + KV cache) is far larger than L2; no explicit flush",
-                "phases_s": {k: last.get(k) for k in ("perf/rollout_time", "perf/train_time", "perf/update_weights_wall")},
+                "phases_s": {k: round(float(v), 3) for k, v in last.items() if k.startswith("perf/") and k.endswith(("_time", "_wall"))},
             },
             "clocks": clocks,
             "e2e": {"value": tokens / wall, "unit": "tokens/s", "h2d_bytes_per_step": h2d / ns.steps,
