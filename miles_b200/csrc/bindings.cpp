@@ -68,7 +68,8 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn, bo
 // a: [rows, K] rows grouped in 128-row tiles; b: [G, N, K] (K-major) or [G, K, N] (MN-major).
 void grouped_gemm_rows(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, const at::Tensor& tile_group,
                        const at::Tensor& num_m_tiles, bool b_mn, bool accumulate, int64_t block_n,
-                       const c10::optional<at::Tensor>& status) {
+                       const c10::optional<at::Tensor>& status, const c10::optional<at::Tensor>& row_ptrs,
+                       const c10::optional<at::Tensor>& sig_ctrl, const std::vector<int64_t>& sig_flags, int64_t sig_me) {
   check_bf16_2d(a, "a");
   TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 3 && b.is_contiguous(),
               "b must be a contiguous 3-D bf16 tensor");
@@ -94,6 +95,17 @@ void grouped_gemm_rows(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, 
   p.num_m_tiles = num_m_tiles.data_ptr<int>();
   p.status = status_ptr(status);
   p.block_n = static_cast<int>(block_n);
+  if (row_ptrs.has_value()) {  // scattered output: the epilogue stores each row at its own (possibly remote) address
+    TORCH_CHECK(row_ptrs->is_cuda() && row_ptrs->scalar_type() == at::kLong && row_ptrs->numel() >= p.M, "row_ptrs must be int64 [M]");
+    p.row_ptrs = reinterpret_cast<const unsigned long long*>(row_ptrs->data_ptr<int64_t>());
+    if (sig_ctrl.has_value()) {
+      TORCH_CHECK(sig_ctrl->scalar_type() == at::kLong && sig_ctrl->numel() >= 6 && sig_flags.size() <= 8, "bad signal arguments");
+      p.sig_ctrl = reinterpret_cast<unsigned long long*>(sig_ctrl->data_ptr<int64_t>());
+      for (size_t i = 0; i < sig_flags.size(); ++i) p.sig_flags[i] = reinterpret_cast<unsigned long long*>(sig_flags[i]);
+      p.sig_nranks = static_cast<int>(sig_flags.size());
+      p.sig_me = static_cast<int>(sig_me);
+    }
+  }
   TORCH_CHECK(mb::gemm_bf16_launch(p, cur_stream()) == 0, "grouped_gemm_rows: ", mb::gemm_last_error());
 }
 
@@ -131,7 +143,11 @@ void register_elementwise(pybind11::module_& m);  // ops_bindings.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM: c (+)= a . b^T with selectable operand majors");
-  m.def("grouped_gemm_rows", &grouped_gemm_rows, "MoE grouped GEMM over 128-row tiles tagged with a group id");
+  namespace py = pybind11;
+  m.def("grouped_gemm_rows", &grouped_gemm_rows, "MoE grouped GEMM over 128-row tiles tagged with a group id", py::arg("a"),
+        py::arg("b"), py::arg("c"), py::arg("tile_group"), py::arg("num_m_tiles"), py::arg("b_mn"), py::arg("accumulate"),
+        py::arg("block_n"), py::arg("status"), py::arg("row_ptrs") = py::none(), py::arg("sig_ctrl") = py::none(),
+        py::arg("sig_flags") = std::vector<int64_t>(), py::arg("sig_me") = 0);
   m.def("grouped_gemm_contr", &grouped_gemm_contr, "MoE weight-gradient GEMM (contraction over each group's rows)");
   register_elementwise(m);
 }

@@ -155,7 +155,30 @@ __global__ void ep_return_kernel(const uint4* __restrict__ yp, const int* __rest
   }
 }
 
+// Destination address of every expert-sorted row: row r holds receive-slot j = row_src[r] (source rank j / cap),
+// whose result belongs at yback[source][meta[j].y]. 0 marks padding rows. The grouped GEMM that produces the rows
+// stores them there directly (its epilogue is the return transfer).
+__global__ void ep_row_ptrs_kernel(const int* __restrict__ row_src, const int2* __restrict__ meta, EpPeers peers, int cap,
+                                   long long row_bytes, int max_rows, unsigned long long* __restrict__ out) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= max_rows) return;
+  const int j = row_src[r];
+  unsigned long long p = 0ull;
+  if (j >= 0) {
+    const int src = j / cap;
+    p = reinterpret_cast<unsigned long long>(peers.yback[src]) + static_cast<unsigned long long>(meta[j].y) * row_bytes;
+  }
+  out[r] = p;
+}
+
 }  // namespace
+
+void ep_row_ptrs(const int* row_src, const int* meta, const EpPeers& peers, int cap, int H, int max_rows,
+                 unsigned long long* out, cudaStream_t s) {
+  if (max_rows <= 0) return;
+  ep_row_ptrs_kernel<<<(max_rows + 255) / 256, 256, 0, s>>>(row_src, reinterpret_cast<const int2*>(meta), peers, cap,
+                                                            static_cast<long long>(H) * 2, max_rows, out);
+}
 
 void ep_dispatch(const void* x, const int* ids, const int* dest_row, const int* offsets, const EpPeers& peers, int me,
                  int nranks, int experts_per_rank, int n_entries, int row_div, int H, int cap, unsigned long long* ctrl,

@@ -48,6 +48,10 @@ struct KArgs {
   int out_fp32;
   int vec_ok;
   int* status;
+  const unsigned long long* row_ptrs;
+  unsigned long long* sig_ctrl;
+  unsigned long long* sig_flags[8];
+  int sig_nranks, sig_me;
 };
 
 struct Tile {
@@ -140,6 +144,24 @@ __device__ __forceinline__ Tile decode_tile(const KArgs& p, int t) {
 __device__ __forceinline__ void store_chunk(const KArgs& p, const Tile& t, int row, int col,
                                             const uint32_t (&acc)[32], bool zero) {
   if (row >= t.row_end) return;
+  if (p.row_ptrs) {
+    // scattered bf16 rows (possibly in a peer GPU's memory): N % 8 == 0 and 16-byte aligned rows are checked on the host
+    const unsigned long long base = p.row_ptrs[row];
+    if (base == 0ull) return;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(base) + col;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (col + 8 * i + 8 <= p.N) {
+        uint4 v;
+        v.x = zero ? 0u : pack_bf16(__uint_as_float(acc[8 * i + 0]), __uint_as_float(acc[8 * i + 1]));
+        v.y = zero ? 0u : pack_bf16(__uint_as_float(acc[8 * i + 2]), __uint_as_float(acc[8 * i + 3]));
+        v.z = zero ? 0u : pack_bf16(__uint_as_float(acc[8 * i + 4]), __uint_as_float(acc[8 * i + 5]));
+        v.w = zero ? 0u : pack_bf16(__uint_as_float(acc[8 * i + 6]), __uint_as_float(acc[8 * i + 7]));
+        *reinterpret_cast<uint4*>(dst + 8 * i) = v;
+      }
+    }
+    return;
+  }
   const long long off = t.c_base + static_cast<long long>(row) * p.ldc + col;
   const bool full = (col + 32 <= p.N) && p.vec_ok;
   if (p.out_fp32) {
@@ -389,6 +411,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       ++iter;
     }
+    if (p.row_ptrs) __threadfence_system();  // this thread's peer stores are visible before the CTA reports in
   }
 
   tc_fence_before();
@@ -396,6 +419,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (p.sig_ctrl && threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned long long done = atomicAdd(&p.sig_ctrl[5], 1ull);
+    if (done == gridDim.x - 1) {  // every CTA has stored and fenced: raise the return flags of this epoch
+      __threadfence_system();
+      const unsigned long long epoch = p.sig_ctrl[2] + 1;
+      for (int d = 0; d < p.sig_nranks; ++d)
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p.sig_flags[d] + p.sig_me), "l"(epoch) : "memory");
+      p.sig_ctrl[5] = 0;
+      p.sig_ctrl[2] = epoch;
+    }
   }
 }
 
@@ -500,6 +535,13 @@ int gemm_bf16_launch(const GemmProblem& p, cudaStream_t stream) {
   ka.accumulate = p.accumulate ? 1 : 0;
   ka.out_fp32 = p.out_fp32 ? 1 : 0;
   ka.status = p.status;
+  ka.row_ptrs = p.row_ptrs;
+  ka.sig_ctrl = p.row_ptrs ? p.sig_ctrl : nullptr;
+  for (int i = 0; i < 8; ++i) ka.sig_flags[i] = p.sig_flags[i];
+  ka.sig_nranks = p.sig_nranks;
+  ka.sig_me = p.sig_me;
+  if (p.row_ptrs && (p.out_fp32 || p.accumulate || p.N % 8 != 0 || p.mode == GEMM_GROUPED_CONTR))
+    return fail("scattered output needs bf16, no accumulation, N % 8 == 0 and a row-major problem");
   const int esz = p.out_fp32 ? 4 : 2;
   const int vec = 16 / esz;
   ka.vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0 && p.ldc % vec == 0 && p.c_group_stride % vec == 0) ? 1 : 0;

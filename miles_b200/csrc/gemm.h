@@ -38,6 +38,16 @@ struct GemmProblem {
   int* status;               // device status word (0 = ok); may be null
   int block_n;               // 0 = choose, else 128 or 256
   int max_ctas;              // 0 = all SMs
+  // Scattered output (bf16, no accumulate): row r of C is stored at byte address row_ptrs[r] (0 = drop the row)
+  // instead of c + r*ldc. The addresses may lie in other GPUs' memory mapped into this process: the epilogue then
+  // is the expert-parallel return transfer (plain 16-byte P2P stores, tile by tile, while later tiles compute).
+  const unsigned long long* row_ptrs;
+  // With row_ptrs: after every CTA has stored its tiles and fenced at system scope, the last CTA to finish writes
+  // epoch = sig_ctrl[2] + 1 to sig_flags[d][sig_me] for every rank d (release) and stores it to sig_ctrl[2];
+  // sig_ctrl[5] is the arrival counter (left at zero). Null sig_ctrl = no signalling.
+  unsigned long long* sig_ctrl;
+  unsigned long long* sig_flags[8];
+  int sig_nranks, sig_me;
 };
 
 // Launches on `stream`. Returns 0 or a negative host-side error code (bad argument / driver error).

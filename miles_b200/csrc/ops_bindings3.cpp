@@ -81,6 +81,18 @@ void ep_return(const at::Tensor& yp, const at::Tensor& recv_dest_row, const at::
                 status.data_ptr<int>(), cur_stream());
 }
 
+at::Tensor ep_row_ptrs(const at::Tensor& row_src, const at::Tensor& meta_local, const std::vector<int64_t>& xrecv,
+                       const std::vector<int64_t>& meta, const std::vector<int64_t>& counts, const std::vector<int64_t>& flags,
+                       const std::vector<int64_t>& yback, const std::vector<int64_t>& flags2, int64_t cap, int64_t H) {
+  TORCH_CHECK(row_src.is_cuda() && row_src.scalar_type() == at::kInt && row_src.is_contiguous(), "bad row_src");
+  const c10::cuda::CUDAGuard guard(row_src.device());
+  mb::EpPeers p = make_peers(xrecv, meta, counts, flags, yback, flags2);
+  at::Tensor out = at::empty({row_src.numel()}, row_src.options().dtype(at::kLong));
+  mb::ep_row_ptrs(row_src.data_ptr<int>(), meta_local.data_ptr<int>(), p, cap, H, row_src.numel(),
+                  reinterpret_cast<unsigned long long*>(out.data_ptr<int64_t>()), cur_stream());
+  return out;
+}
+
 }  // namespace
 
 void register_comm(pybind11::module_& m) {
@@ -92,4 +104,5 @@ void register_comm(pybind11::module_& m) {
   m.def("ep_dispatch", &ep_dispatch);
   m.def("ep_wait", &ep_wait);
   m.def("ep_return", &ep_return);
+  m.def("ep_row_ptrs", &ep_row_ptrs);
 }

@@ -108,14 +108,20 @@ class B200Qwen3:
         self.launches += 3
         return MoeCtx(ids, None, None, offsets, dest, src, tg, nt, max_rows)
 
-    def _experts_fwd(self, xp, plan: MoeCtx, w1, w2, keep: bool):
+    def _experts_fwd(self, xp, plan: MoeCtx, w1, w2, keep: bool, scatter=None):
+        """``scatter = (row_ptrs, ctrl, flag_ptrs, rank)``: the second GEMM stores every output row at its own
+        address (the expert-parallel return buffers of the ranks the tokens came from) and raises their flags."""
         C = self.C
         I2 = w1.shape[1]
         gu = torch.empty(plan.max_rows, I2, dtype=torch.bfloat16, device=xp.device)
         C.grouped_gemm_rows(xp, w1, gu, plan.tile_group, plan.num_tiles, False, False, 0, self.status)
         act = C.swiglu_fwd(gu)
-        yp = torch.empty(plan.max_rows, w2.shape[1], dtype=torch.bfloat16, device=xp.device)
-        C.grouped_gemm_rows(act, w2, yp, plan.tile_group, plan.num_tiles, False, False, 0, self.status)
+        yp = torch.empty(plan.max_rows if scatter is None else 1, w2.shape[1], dtype=torch.bfloat16, device=xp.device)
+        if scatter is None:
+            C.grouped_gemm_rows(act, w2, yp, plan.tile_group, plan.num_tiles, False, False, 0, self.status)
+        else:
+            C.grouped_gemm_rows(act, w2, yp.expand(plan.max_rows, -1), plan.tile_group, plan.num_tiles, False, False, 0,
+                                self.status, scatter[0], scatter[1], scatter[2], scatter[3])
         self.launches += 3
         return (gu, act, yp) if keep else (None, None, yp)
 
@@ -151,14 +157,19 @@ class B200Qwen3:
         dh2 = self._router_bwd(i, h2, dh2, plan.probs, plan.ids, plan.w, dw)
         return dh2
 
-    def _experts_bwd(self, dyp, xp, gu, act, plan, w1, w2, gw1, gw2):
+    def _experts_bwd(self, dyp, xp, gu, act, plan, w1, w2, gw1, gw2, scatter=None):
         C = self.C
         dact = torch.empty_like(act)
         C.grouped_gemm_rows(dyp, w2, dact, plan.tile_group, plan.num_tiles, True, False, 0, self.status)
         C.grouped_gemm_contr(dyp, act, gw2, plan.offsets, True, 0, self.status)
         dgu = C.swiglu_bwd(dact, gu)
-        dxp = torch.empty_like(xp)
-        C.grouped_gemm_rows(dgu, w1, dxp, plan.tile_group, plan.num_tiles, True, False, 0, self.status)
+        if scatter is None:
+            dxp = torch.empty_like(xp)
+            C.grouped_gemm_rows(dgu, w1, dxp, plan.tile_group, plan.num_tiles, True, False, 0, self.status)
+        else:  # the input-gradient rows go straight back to the ranks that own the tokens
+            dxp = torch.empty(1, xp.shape[1], dtype=xp.dtype, device=xp.device)
+            C.grouped_gemm_rows(dgu, w1, dxp.expand(xp.shape[0], -1), plan.tile_group, plan.num_tiles, True, False, 0,
+                                self.status, scatter[0], scatter[1], scatter[2], scatter[3])
         C.grouped_gemm_contr(dgu, xp, gw1, plan.offsets, True, 0, self.status)
         self.launches += 5
         return dxp

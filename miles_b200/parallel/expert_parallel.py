@@ -24,11 +24,14 @@ from .symm import SymmetricRegion
 
 
 class ExpertParallel:
-    def __init__(self, cfg, ps, fused: bool = True, max_tokens: int = 32768):
+    def __init__(self, cfg, ps, fused: bool = True, max_tokens: int = 32768, fused_epilogue: bool = True):
         self.cfg, self.ps = cfg, ps
         self.group, self.rank, self.n = ps.ep.group, ps.ep.rank, ps.ep.size
         self.el = cfg.num_experts // self.n
         self.fused = fused and ps.device.type == "cuda"
+        # the GEMM that produces the expert outputs (or input gradients) stores them straight into the source ranks'
+        # return buffers; off = a separate copy kernel after the GEMM (kept for comparison)
+        self.fused_epilogue = self.fused and fused_epilogue
         self.dev = ps.device
         self.C = _ext.load(required=True) if self.dev.type == "cuda" else None
         self.K, self.H = cfg.moe_top_k, cfg.hidden_size
@@ -79,6 +82,16 @@ class ExpertParallel:
         ids_recv = torch.where(valid, self.meta.view(n, cap, 2)[:, :, 0], torch.full_like(self.pos_in_cap, -1))
         return model._permute_plan(ids_recv.reshape(n * cap, 1).contiguous(), self.el, align)
 
+    def _scatter_args(self, plan):
+        """Arguments that turn the producing GEMM's epilogue into the return transfer (rows stored straight into the
+        source ranks' return regions over NVLink, flags raised by the last CTA)."""
+        ptrs = self.C.ep_row_ptrs(plan.src, self.meta, *self._peers, self.cap, self.H)
+        return ptrs, self.ctrl, self.p_flags2, self.rank
+
+    def _await_return(self, n_entries):
+        self.C.ep_wait(self.flags2, self.n, self.ctrl, 3, self.status)
+        return self.yback[:n_entries]
+
     def _return(self, rows_perm, plan, n_entries):
         C = self.C
         C.ep_return(rows_perm, plan.dest, self.meta, self.counts, *self._peers, self.rank, self.cap, self.ctrl, self.status)
@@ -105,8 +118,12 @@ class ExpertParallel:
         self._send(h2, ids_flat, route, K)
         plan = self._recv_plan(model, 64 if keep else 1)
         xp = C.moe_permute(self.xrecv, plan.src, plan.num_tiles, 1)
-        gu, act, yp = model._experts_fwd(xp, plan, P[p + "w1"], P[p + "w2"], keep)
-        yslot = self._return(yp, plan, n_entries)
+        if self.fused_epilogue:
+            gu, act, _ = model._experts_fwd(xp, plan, P[p + "w1"], P[p + "w2"], keep, scatter=self._scatter_args(plan))
+            yslot = self._await_return(n_entries)
+        else:
+            gu, act, yp = model._experts_fwd(xp, plan, P[p + "w1"], P[p + "w2"], keep)
+            yslot = self._return(yp, plan, n_entries)
         y = C.moe_combine(yslot, self.identity[:n_entries], w, T, K, residual)
         model.launches += 8
         saved = None
@@ -125,9 +142,14 @@ class ExpertParallel:
         dy_slot, dw = C.moe_combine_bwd(dy, saved["yslot"], self.identity[:n_entries], self.big_tiles, w)
         self._send(dy_slot, ids.reshape(-1), saved["route"], 1)
         dyp = C.moe_permute(self.xrecv, plan.src, plan.num_tiles, 1)
-        dxp = model._experts_bwd(dyp, saved["xp"], saved["gu"], saved["act"], plan, P[p + "w1"], P[p + "w2"],
-                                 G[p + "w1"], G[p + "w2"])
-        dslot = self._return(dxp, plan, n_entries)
+        if self.fused_epilogue:
+            model._experts_bwd(dyp, saved["xp"], saved["gu"], saved["act"], plan, P[p + "w1"], P[p + "w2"],
+                               G[p + "w1"], G[p + "w2"], scatter=self._scatter_args(plan))
+            dslot = self._await_return(n_entries)
+        else:
+            dxp = model._experts_bwd(dyp, saved["xp"], saved["gu"], saved["act"], plan, P[p + "w1"], P[p + "w2"],
+                                     G[p + "w1"], G[p + "w2"])
+            dslot = self._return(dxp, plan, n_entries)
         dh2 = C.moe_combine(dslot, self.identity[:n_entries], None, T, K)
         model.launches += 8
         return model._router_bwd(i, h2, dh2, saved["probs"], ids, w, dw)

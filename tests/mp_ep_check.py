@@ -25,7 +25,8 @@ def batch(cfg, lens, dev, seed):
 
 
 def main():
-    fused = sys.argv[1] == "fused"
+    mode = sys.argv[1]  # nccl | fused (GEMM epilogue stores into the peers) | fused_copy (separate return kernel)
+    fused = mode != "nccl"
     world = int(os.environ["WORLD_SIZE"])
     ps = init_parallel_state(ep=world)
     dev = ps.device
@@ -34,7 +35,7 @@ def main():
     # expert-parallel model
     store = ParamStore(cfg, dev, torch.bfloat16, ep_size=world, ep_rank=ps.ep.rank, init_std=0.05, seed=5)
     store.allocate_grads(torch.float32)
-    ep = ExpertParallel(cfg, ps, fused=fused, max_tokens=1024)
+    ep = ExpertParallel(cfg, ps, fused=fused, max_tokens=1024, fused_epilogue=(mode == "fused"))
     model = build_model(cfg, store, "b200", ep=ep)
     # single-rank oracle with all experts
     ref_store = ParamStore(cfg, dev, torch.bfloat16, init_std=0.05, seed=5)
@@ -89,7 +90,7 @@ def main():
         cos = torch.nn.functional.cosine_similarity(dense, ref_store.grad["dense"], dim=0).item()
         assert cos > 0.995, cos
     if ps.rank == 0:
-        print(f"EP_CHECK_OK fused={fused} world={world}")
+        print(f"EP_CHECK_OK mode={mode} world={world}")
     dist.barrier()
     dist.destroy_process_group()
 

@@ -18,7 +18,7 @@ def _run(mode: str, n: int):
     assert r.returncode == 0 and "EP_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
 
 
-@pytest.mark.parametrize("mode", ["nccl", "fused"])
+@pytest.mark.parametrize("mode", ["nccl", "fused", "fused_copy"])
 def test_expert_parallel_matches_single_rank(mode):
     n = torch.cuda.device_count()
     if n < 2:
