@@ -244,6 +244,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  const uint32_t stage_buf = (bar_base + 8u * (2 * STAGES + 5) + 15u) & ~15u;  // epilogue staging (BLOCK_N == 128 only)
+  (void)stage_buf;
   __shared__ int abort_flag_s;
   __shared__ uint32_t tmem_base_s;
   volatile int* abort_flag = &abort_flag_s;
@@ -399,12 +401,50 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + acc * BLOCK_N + (static_cast<uint32_t>(quad * 32) << 16);
+      if (BLOCK_N == 128 && p.row_ptrs) {
+        // Scattered rows (expert-parallel return): pass the warp's 32 x 128 block through shared memory so that
+        // every store instruction writes two whole 256-byte row segments instead of thirty-two 64-byte pieces;
+        // over NVLink the size of a write decides how much of the link carries payload.
+        const uint32_t stg = stage_buf + static_cast<uint32_t>(quad) * (32 * 256);
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        if (tl.c_col0 + c * 32 >= p.N) break;  // warp-uniform
-        tmem_ld_32x32(t_addr + c * 32, acc_regs);
-        tmem_ld_wait();
-        store_chunk(p, tl, row, tl.c_col0 + c * 32, acc_regs, false);
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_32x32(t_addr + c * 32, acc_regs);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t v0 = pack_bf16(__uint_as_float(acc_regs[8 * i + 0]), __uint_as_float(acc_regs[8 * i + 1]));
+            const uint32_t v1 = pack_bf16(__uint_as_float(acc_regs[8 * i + 2]), __uint_as_float(acc_regs[8 * i + 3]));
+            const uint32_t v2 = pack_bf16(__uint_as_float(acc_regs[8 * i + 4]), __uint_as_float(acc_regs[8 * i + 5]));
+            const uint32_t v3 = pack_bf16(__uint_as_float(acc_regs[8 * i + 6]), __uint_as_float(acc_regs[8 * i + 7]));
+            const uint32_t chunk = static_cast<uint32_t>(c * 4 + i) ^ static_cast<uint32_t>(lane & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + lane * 256 + chunk * 16), "r"(v0), "r"(v1),
+                         "r"(v2), "r"(v3)
+                         : "memory");
+          }
+        }
+        const unsigned long long my_ptr = (row < tl.row_end) ? p.row_ptrs[row] : 0ull;
+        __syncwarp();
+#pragma unroll 1
+        for (int it = 0; it < 16; ++it) {
+          const int rl = it * 2 + (lane >> 4);
+          const int ch = lane & 15;
+          const unsigned long long base = __shfl_sync(0xffffffffu, my_ptr, rl);
+          uint4 v;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                       : "r"(stg + rl * 256 + ((ch ^ (rl & 7)) * 16)));
+          const int col = tl.c_col0 + ch * 8;
+          if (base != 0ull && col + 8 <= p.N) *reinterpret_cast<uint4*>(base + static_cast<unsigned long long>(col) * 2) = v;
+        }
+        __syncwarp();
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / 32; ++c) {
+          if (tl.c_col0 + c * 32 >= p.N) break;  // warp-uniform
+          tmem_ld_32x32(t_addr + c * 32, acc_regs);
+          tmem_ld_wait();
+          store_chunk(p, tl, row, tl.c_col0 + c * 32, acc_regs, false);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -479,9 +519,11 @@ int make_map(CUtensorMap* map, const GemmOperand& op, int box_rows) {
 
 template <int BLOCK_N, bool A_MN, bool B_MN>
 int launch(const GemmProblem& p, const KArgs& ka, cudaStream_t stream) {
-  constexpr int STAGES = BLOCK_N == 256 ? 4 : (BLOCK_N == 128 ? 6 : 8);
+  // the 128-wide variant gives one pipeline stage to a 32 KB staging buffer for scattered (peer) output rows
+  constexpr int STAGES = BLOCK_N == 256 ? 4 : (BLOCK_N == 128 ? 5 : 8);
   constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 2;
-  constexpr int SMEM = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 8 * (2 * STAGES + 5) + 1024;
+  constexpr int SMEM = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 8 * (2 * STAGES + 5) + 1024 +
+                       (BLOCK_N == 128 ? 4 * 32 * 256 + 16 : 0);
   CUtensorMap ma, mb_;
   if (make_map(&ma, p.a, A_MN ? BLOCK_K : BLOCK_M)) return -1;
   if (make_map(&mb_, p.b, B_MN ? BLOCK_K : BLOCK_N)) return -1;
@@ -564,6 +606,7 @@ int gemm_bf16_launch(const GemmProblem& p, cudaStream_t stream) {
       if (bn == 64 && tiles(64) < sms / 2 && p.N >= 32) bn = 32;
     }
   }
+  if (p.row_ptrs) bn = 128;  // the staged scatter epilogue lives in the 128-wide variant
   if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return fail("block_n must be 32, 64, 128 or 256");
   if ((bn == 32 || bn == 64) && (amn || bmn)) return fail("narrow tiles support K-major operands only");
   if (bn == 32) return launch<32, false, false>(p, ka, stream);
