@@ -97,6 +97,7 @@ def main() -> None:
     ap.add_argument("--mean-response-len", type=float, default=2048.0)
     ap.add_argument("--max-tokens-per-gpu", type=int, default=32768)
     ap.add_argument("--no-routing-replay", action="store_true")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (dense models; the rest of the GPUs are data parallel)")
     ns = ap.parse_args()
     if ns.impl == "reference":
         reference_arm(ns)
@@ -111,7 +112,7 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     assert world == ns.gpus, f"--gpus {ns.gpus} but WORLD_SIZE={world}; launch with torchrun --nproc-per-node {ns.gpus}"
-    n_prompts = ns.prompts_per_gpu * world
+    n_prompts = ns.prompts_per_gpu * (world // ns.tp)
     flags = [
         "--model-preset", ns.model, "--num-rollout", str(ns.steps + ns.warmup),
         "--rollout-batch-size", str(n_prompts), "--n-samples-per-prompt", str(ns.samples_per_prompt),
@@ -120,7 +121,8 @@ def main() -> None:
         "--eps-clip", "0.2", "--eps-clip-high", "0.28", "--lr", "1e-6", "--weight-decay", "0.1", "--adam-beta1", "0.9",
         "--adam-beta2", "0.98", "--clip-grad", "1.0", "--use-dynamic-batch-size", "--max-tokens-per-gpu", str(ns.max_tokens_per_gpu),
         "--actor-num-nodes", "1", "--actor-num-gpus-per-node", str(world), "--colocate",
-        "--expert-model-parallel-size", str(world), "--recompute-granularity", "full",
+        "--expert-model-parallel-size", str(world if ns.tp == 1 else 1), "--tensor-model-parallel-size", str(ns.tp),
+        "--recompute-granularity", "full",
         "--custom-generate-function-path", "miles_b200.rollout.generate_hub.benchmarkers.generate",
         "--benchmark-mean-response-len", str(ns.mean_response_len), "--sglang-mem-fraction-static", "0.8",
     ]
@@ -191,7 +193,8 @@ def main() -> None:
                 "model": cfg.name, "params_b": round(cfg.num_params() / 1e9, 2), "global_batch": n_prompts * ns.samples_per_prompt,
                 "prompts": n_prompts, "samples_per_prompt": ns.samples_per_prompt, "seq_len": ns.prompt_len + ns.max_response_len,
                 "prompt_len": ns.prompt_len, "max_response_len": ns.max_response_len, "mean_response_len": ns.mean_response_len,
-                "tokens_per_step": tokens / ns.steps, "parallelism": f"dp{world}-attn x ep{world}-experts, colocated engine",
+                "tokens_per_step": tokens / ns.steps, "parallelism": (f"dp{world}-attn x ep{world}-experts, colocated engine" if ns.tp == 1 else
+                                                     f"tp{ns.tp} x dp{world // ns.tp}, colocated engine"),
                 "optimizer_plan": loop.actor.plan.get("name"), "routing_replay": not ns.no_routing_replay,
                 "l2": "working set (61 GB of weights + KV cache) is far larger than L2; no explicit flush",
                 "phases_s": {k: round(float(v), 3) for k, v in last.items() if k.startswith("perf/") and k.endswith(("_time", "_wall"))},

@@ -42,7 +42,8 @@ void fill_out(mb::GemmProblem& p, const at::Tensor& c) {
 }
 
 void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn, bool b_mn, bool accumulate,
-          int64_t block_n, const c10::optional<at::Tensor>& status) {
+          int64_t block_n, const c10::optional<at::Tensor>& status, const std::vector<int64_t>& dest,
+          const c10::optional<at::Tensor>& sig_ctrl, const std::vector<int64_t>& sig_flags, int64_t sig_me) {
   check_bf16_2d(a, "a");
   check_bf16_2d(b, "b");
   TORCH_CHECK(c.dim() == 2, "c must be 2-D");
@@ -62,6 +63,18 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn, bo
   p.accumulate = accumulate;
   p.status = status_ptr(status);
   p.block_n = static_cast<int>(block_n);
+  if (!dest.empty()) {  // replicated output: each destination receives the tile at the offset it has in c
+    TORCH_CHECK(dest.size() <= 8, "at most 8 destinations");
+    p.n_dest = static_cast<int>(dest.size());
+    for (size_t i = 0; i < dest.size(); ++i) p.dest[i] = reinterpret_cast<void*>(dest[i]);
+    if (sig_ctrl.has_value()) {
+      TORCH_CHECK(sig_ctrl->scalar_type() == at::kLong && sig_ctrl->numel() >= 6 && sig_flags.size() <= 8, "bad signal arguments");
+      p.sig_ctrl = reinterpret_cast<unsigned long long*>(sig_ctrl->data_ptr<int64_t>());
+      for (size_t i = 0; i < sig_flags.size(); ++i) p.sig_flags[i] = reinterpret_cast<unsigned long long*>(sig_flags[i]);
+      p.sig_nranks = static_cast<int>(sig_flags.size());
+      p.sig_me = static_cast<int>(sig_me);
+    }
+  }
   TORCH_CHECK(mb::gemm_bf16_launch(p, cur_stream()) == 0, "gemm: ", mb::gemm_last_error());
 }
 
@@ -142,8 +155,11 @@ void grouped_gemm_contr(const at::Tensor& a, const at::Tensor& b, at::Tensor& c,
 void register_elementwise(pybind11::module_& m);  // ops_bindings.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("gemm", &gemm, "bf16 tcgen05 GEMM: c (+)= a . b^T with selectable operand majors");
   namespace py = pybind11;
+  m.def("gemm", &gemm, "bf16 tcgen05 GEMM: c (+)= a . b^T with selectable operand majors", py::arg("a"), py::arg("b"),
+        py::arg("c"), py::arg("a_mn"), py::arg("b_mn"), py::arg("accumulate"), py::arg("block_n"), py::arg("status"),
+        py::arg("dest") = std::vector<int64_t>(), py::arg("sig_ctrl") = py::none(),
+        py::arg("sig_flags") = std::vector<int64_t>(), py::arg("sig_me") = 0);
   m.def("grouped_gemm_rows", &grouped_gemm_rows, "MoE grouped GEMM over 128-row tiles tagged with a group id", py::arg("a"),
         py::arg("b"), py::arg("c"), py::arg("tile_group"), py::arg("num_m_tiles"), py::arg("b_mn"), py::arg("accumulate"),
         py::arg("block_n"), py::arg("status"), py::arg("row_ptrs") = py::none(), py::arg("sig_ctrl") = py::none(),

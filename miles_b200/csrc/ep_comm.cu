@@ -171,7 +171,54 @@ __global__ void ep_row_ptrs_kernel(const int* __restrict__ row_src, const int2* 
   out[r] = p;
 }
 
+// out[i] = (residual[i] +) sum_d slots[d][i] in fp32, slots d = 0..n-1 at stride `slot_elems` (the tensor-parallel
+// partial sums pushed by the peers' GEMM epilogues). Fixed summation order: every rank gets bit-identical results.
+__global__ void sum_slots_kernel(const uint4* __restrict__ slots, long long slot_vecs, int n, const uint4* __restrict__ residual,
+                                 uint4* __restrict__ out, long long vecs) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int d = 0; d < n; ++d) {
+      const uint4 v = slots[d * slot_vecs + i];
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(b[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    if (residual) {
+      const uint4 v = residual[i];
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(b[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    out[i] = o;
+  }
+}
+
 }  // namespace
+
+void sum_slots(const void* slots, long long slot_elems, int n, const void* residual, void* out, long long elems,
+               cudaStream_t s) {
+  const long long vecs = elems / 8;
+  if (vecs <= 0) return;
+  long long blocks = (vecs + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  sum_slots_kernel<<<static_cast<int>(blocks), 256, 0, s>>>(static_cast<const uint4*>(slots), slot_elems / 8, n,
+                                                            static_cast<const uint4*>(residual), static_cast<uint4*>(out), vecs);
+}
 
 void ep_row_ptrs(const int* row_src, const int* meta, const EpPeers& peers, int cap, int H, int max_rows,
                  unsigned long long* out, cudaStream_t s) {

@@ -52,6 +52,8 @@ struct KArgs {
   unsigned long long* sig_ctrl;
   unsigned long long* sig_flags[8];
   int sig_nranks, sig_me;
+  void* dest[8];
+  int n_dest;
 };
 
 struct Tile {
@@ -401,7 +403,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + acc * BLOCK_N + (static_cast<uint32_t>(quad * 32) << 16);
-      if (BLOCK_N == 128 && p.row_ptrs) {
+      if (BLOCK_N == 128 && p.n_dest > 0) {
+        // Replicated tile (tensor-parallel partial sums): same staging, every row segment goes to each destination.
+        const uint32_t stg = stage_buf + static_cast<uint32_t>(quad) * (32 * 256);
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_32x32(t_addr + c * 32, acc_regs);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t v0 = pack_bf16(__uint_as_float(acc_regs[8 * i + 0]), __uint_as_float(acc_regs[8 * i + 1]));
+            const uint32_t v1 = pack_bf16(__uint_as_float(acc_regs[8 * i + 2]), __uint_as_float(acc_regs[8 * i + 3]));
+            const uint32_t v2 = pack_bf16(__uint_as_float(acc_regs[8 * i + 4]), __uint_as_float(acc_regs[8 * i + 5]));
+            const uint32_t v3 = pack_bf16(__uint_as_float(acc_regs[8 * i + 6]), __uint_as_float(acc_regs[8 * i + 7]));
+            const uint32_t chunk = static_cast<uint32_t>(c * 4 + i) ^ static_cast<uint32_t>(lane & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + lane * 256 + chunk * 16), "r"(v0), "r"(v1),
+                         "r"(v2), "r"(v3)
+                         : "memory");
+          }
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int it = 0; it < 16; ++it) {
+          const int rl = it * 2 + (lane >> 4);
+          const int ch = lane & 15;
+          uint4 v;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                       : "r"(stg + rl * 256 + ((ch ^ (rl & 7)) * 16)));
+          const int grow = tl.c_row0 + quad * 32 + rl;
+          const int col = tl.c_col0 + ch * 8;
+          if (grow < tl.row_end && col + 8 <= p.N) {
+            const long long off = static_cast<long long>(grow) * p.ldc + col;
+            for (int d = 0; d < p.n_dest; ++d) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.dest[d]) + off) = v;
+          }
+        }
+        __syncwarp();
+      } else if (BLOCK_N == 128 && p.row_ptrs) {
         // Scattered rows (expert-parallel return): pass the warp's 32 x 128 block through shared memory so that
         // every store instruction writes two whole 256-byte row segments instead of thirty-two 64-byte pieces;
         // over NVLink the size of a write decides how much of the link carries payload.
@@ -451,7 +489,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       ++iter;
     }
-    if (p.row_ptrs) __threadfence_system();  // this thread's peer stores are visible before the CTA reports in
+    if (p.row_ptrs || p.n_dest > 0) __threadfence_system();  // peer stores are visible before the CTA reports in
   }
 
   tc_fence_before();
@@ -578,7 +616,11 @@ int gemm_bf16_launch(const GemmProblem& p, cudaStream_t stream) {
   ka.out_fp32 = p.out_fp32 ? 1 : 0;
   ka.status = p.status;
   ka.row_ptrs = p.row_ptrs;
-  ka.sig_ctrl = p.row_ptrs ? p.sig_ctrl : nullptr;
+  ka.sig_ctrl = (p.row_ptrs || p.n_dest > 0) ? p.sig_ctrl : nullptr;
+  ka.n_dest = p.n_dest;
+  for (int i = 0; i < 8; ++i) ka.dest[i] = p.dest[i];
+  if (p.n_dest > 0 && (p.out_fp32 || p.accumulate || p.N % 8 != 0 || p.mode != GEMM_DENSE || p.n_dest > 8 || p.ldc % 8 != 0))
+    return fail("replicated output needs a dense bf16 problem without accumulation, N % 8 == 0 and ldc % 8 == 0");
   for (int i = 0; i < 8; ++i) ka.sig_flags[i] = p.sig_flags[i];
   ka.sig_nranks = p.sig_nranks;
   ka.sig_me = p.sig_me;
@@ -606,7 +648,7 @@ int gemm_bf16_launch(const GemmProblem& p, cudaStream_t stream) {
       if (bn == 64 && tiles(64) < sms / 2 && p.N >= 32) bn = 32;
     }
   }
-  if (p.row_ptrs) bn = 128;  // the staged scatter epilogue lives in the 128-wide variant
+  if (p.row_ptrs || p.n_dest > 0) bn = 128;  // the staged scatter epilogue lives in the 128-wide variant
   if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return fail("block_n must be 32, 64, 128 or 256");
   if ((bn == 32 || bn == 64) && (amn || bmn)) return fail("narrow tiles support K-major operands only");
   if (bn == 32) return launch<32, false, false>(p, ka, stream);

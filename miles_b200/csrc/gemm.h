@@ -48,6 +48,12 @@ struct GemmProblem {
   unsigned long long* sig_ctrl;
   unsigned long long* sig_flags[8];
   int sig_nranks, sig_me;
+  // Replicated output (bf16, no accumulate): the tile is stored at the same offset into each of dest[0..n_dest)
+  // instead of c. With dest[d] = slot `me` of rank d's partial-sum buffer this turns a row-parallel projection into
+  // GEMM + all-gather of partial sums in one kernel (a tensor-parallel all-reduce once the slots are added up);
+  // signalling as above.
+  void* dest[8];
+  int n_dest;
 };
 
 // Launches on `stream`. Returns 0 or a negative host-side error code (bad argument / driver error).

@@ -132,6 +132,8 @@ void ep_dispatch(const void* x, const int* ids, const int* dest_row, const int* 
                  int nranks, int experts_per_rank, int n_entries, int row_div, int H, int cap, unsigned long long* ctrl,
                  int* status, cudaStream_t s);
 void ep_wait(const unsigned long long* flags, int nranks, unsigned long long* ctrl, int which, int* status, cudaStream_t s);
+void sum_slots(const void* slots, long long slot_elems, int n, const void* residual, void* out, long long elems,
+               cudaStream_t s);
 void ep_row_ptrs(const int* row_src, const int* meta, const EpPeers& peers, int cap, int H, int max_rows,
                  unsigned long long* out, cudaStream_t s);
 void ep_return(const void* yp, const int* recv_dest_row, const int* meta, const int* counts, const EpPeers& peers, int me,

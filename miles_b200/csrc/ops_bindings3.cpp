@@ -93,6 +93,17 @@ at::Tensor ep_row_ptrs(const at::Tensor& row_src, const at::Tensor& meta_local, 
   return out;
 }
 
+// slots: [n, slot_elems] bf16 (contiguous); out/residual: the first `out.numel()` elements of a slot's layout.
+void sum_slots(const at::Tensor& slots, const c10::optional<at::Tensor>& residual, at::Tensor& out) {
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kBFloat16 && slots.is_contiguous() && slots.dim() == 2, "bad slots");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.numel() % 8 == 0 && out.numel() <= slots.size(1) &&
+                  slots.size(1) % 8 == 0, "bad out");
+  if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && residual->numel() == out.numel() && residual->scalar_type() == at::kBFloat16, "bad residual");
+  const c10::cuda::CUDAGuard guard(slots.device());
+  mb::sum_slots(slots.data_ptr(), slots.size(1), slots.size(0), residual.has_value() ? residual->data_ptr() : nullptr,
+                out.data_ptr(), out.numel(), cur_stream());
+}
+
 }  // namespace
 
 void register_comm(pybind11::module_& m) {
@@ -105,4 +116,5 @@ void register_comm(pybind11::module_& m) {
   m.def("ep_wait", &ep_wait);
   m.def("ep_return", &ep_return);
   m.def("ep_row_ptrs", &ep_row_ptrs);
+  m.def("sum_slots", &sum_slots);
 }

@@ -51,7 +51,9 @@ class RLLoop:
             tp=args.tensor_model_parallel_size, pp=args.pipeline_model_parallel_size, cp=args.context_parallel_size,
             ep=args.expert_model_parallel_size, backend=None if args.distributed_backend == "nccl" else args.distributed_backend,
             timeout_minutes=args.distributed_timeout_minutes)
-        torch.manual_seed(args.seed + self.ps.rank)
+        # ranks of one tensor-parallel group are one data-parallel replica: same seeds, same prompts, same samples
+        self.n_rep, self.rep = self.ps.dp_cp.size, self.ps.dp_cp.rank
+        torch.manual_seed(args.seed + self.rep)
         self.tokenizer = _load_tokenizer(args)
         self.actor = TrainActor(args, "actor", self.ps)
         self.critic = None
@@ -83,7 +85,7 @@ class RLLoop:
     def _build_engine(self) -> None:
         a = self.args
         cfg = self.actor.cfg
-        local_batch = max(1, (a.rollout_batch_size * a.n_samples_per_prompt + self.ps.world_size - 1) // self.ps.world_size)
+        local_batch = max(1, (a.rollout_batch_size * a.n_samples_per_prompt + self.n_rep - 1) // self.n_rep)
         max_running = getattr(a, "sglang_max_running_requests", None) or min(512, max(local_batch, 1))
         max_ctx = getattr(a, "rollout_max_context_len", None) or ((getattr(a, "rollout_max_prompt_len", None) or 1024)
                                                                    + a.rollout_max_response_len + 8)
@@ -129,7 +131,7 @@ class RLLoop:
         if not getattr(a, "prompt_data", None) and "Synthetic" not in path and getattr(a, "rollout_global_dataset", True):
             path = "miles_b200.rollout.data_source.SyntheticDataSource"
         local = copy.copy(a)
-        local.rollout_seed = a.rollout_seed + 7919 * self.ps.rank  # every rank draws its own prompt stream
+        local.rollout_seed = a.rollout_seed + 7919 * self.rep  # every data-parallel replica draws its own prompt stream
         if getattr(a, "synthetic_vocab_size", None) is None:
             local.synthetic_vocab_size = self.actor.cfg.vocab_size
         return load_function(path)(local, self.tokenizer)
@@ -142,7 +144,7 @@ class RLLoop:
                 "miles_b200.rollout.inference_rollout.InferenceRolloutFn"
         obj = load_function(path)
         local = copy.copy(a)
-        ws = self.ps.world_size
+        ws = self.n_rep
         local.rollout_batch_size = max(1, a.rollout_batch_size // ws)
         local.over_sampling_batch_size = max(local.rollout_batch_size, (a.over_sampling_batch_size or a.rollout_batch_size) // ws)
         self.local_args = local
@@ -171,7 +173,7 @@ class RLLoop:
             from .utils.types import Sample
 
             samples = [Sample.from_dict(d) for d in blob["samples"]]
-            samples = samples[self.ps.rank::self.ps.world_size] if self.ps.world_size > 1 else samples
+            samples = samples[self.rep::self.n_rep] if self.n_rep > 1 else samples
             return samples, {}
         out = self.rollout_fn(RolloutFnTrainInput(rollout_id))
         if asyncio.iscoroutine(out):
@@ -248,8 +250,8 @@ class RLLoop:
         t3 = time.perf_counter()
         n_tok = sum(len(s.tokens) for s in samples)
         tot = torch.tensor([float(n_tok)], device=self.actor.device)
-        if self.ps.world_size > 1:
-            dist.all_reduce(tot)
+        if self.n_rep > 1:
+            dist.all_reduce(tot, group=self.ps.dp_cp.group)  # one count per data-parallel replica
         metrics.update({"perf/rollout_time": t1 - t0, "perf/train_time": t2 - t1, "perf/update_weights_wall": t3 - t2,
                         "perf/step_time": t3 - t0, "perf/step_tokens": float(tot.item()),
                         "perf/grpo_tokens_per_s": float(tot.item()) / max(t3 - t0, 1e-9)})

@@ -46,11 +46,13 @@ class MoeCtx:
 
 
 class B200Qwen3:
-    def __init__(self, cfg: ModelConfig, store: ParamStore, ep=None):
+    def __init__(self, cfg: ModelConfig, store: ParamStore, ep=None, tp=None):
         assert cfg.head_dim == 128, "the sm_100a attention/rope kernels are specialised for head_dim 128"
-        self.cfg = cfg
+        self.cfg = store.cfg  # under tensor parallelism: this rank's view (local head counts, local FFN width)
         self.store = store
         self.ep = ep  # expert-parallel dispatcher (None = all experts local)
+        self.tp = tp if (tp is not None and tp.n > 1) else None  # tensor-parallel exchange (None = not sharded)
+        assert not (self.tp is not None and ep is not None), "tensor parallel attention with expert parallel MoE is not supported"
         self.C = _ext.load(required=True)
         self.dev = store.device
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
@@ -212,7 +214,7 @@ class B200Qwen3:
         cfg, P, C = self.cfg, self.store.params, self.C
         p = f"layers.{i}."
         if (meta is not None and not meta.is_prefill and x.shape[0] <= self.SMALL_T and replay_ids is None
-                and (self.ep is None or not cfg.layer_is_moe(i)) and self.small_decode):
+                and (self.ep is None or not cfg.layer_is_moe(i)) and self.small_decode and self.tp is None):
             return self._layer_forward_small(i, x, positions, meta, kv_cache, record)
         h1, rstd1, qkv, q, k, _, _ = self._attn_qkv(i, x, positions, meta, kv_cache)
         scale = cfg.head_dim ** -0.5
@@ -229,16 +231,41 @@ class B200Qwen3:
             self.launches += 2
         else:
             att, _ = self.attention(q, k, self._v_view(qkv), cu)
-        o = self.linear(att.view(att.shape[0], -1), P[p + "attn.o.weight"])
-        h2, _, x2 = C.rmsnorm_fwd(o, x, P[p + "ln2.weight"], cfg.rms_eps)
-        self.launches += 1
+        h2, _, x2 = self._o_proj_ln2(i, att.view(att.shape[0], -1), x)
         if cfg.layer_is_moe(i):
             y, _ = self.moe_forward(i, h2, replay_ids, record, keep=False, residual=x2)
             return y
         gu = self.linear(h2, P[p + "mlp.gate_up.weight"])
-        y = self.linear(C.swiglu_fwd(gu), P[p + "mlp.down.weight"])
         self.launches += 1
-        return x2.add_(y)
+        return self._row_parallel(C.swiglu_fwd(gu), P[p + "mlp.down.weight"], x2)
+
+    def _row_parallel(self, a, w, residual):
+        """``residual + a @ w^T`` for a row-parallel weight: under tensor parallelism the GEMM epilogue pushes the
+        partial sums to the peers and the slots are added in rank order (one fused GEMM + all-reduce)."""
+        if self.tp is not None:
+            self.launches += 3
+            return self.tp.linear_allreduce(a, w, residual=residual, gemm_status=self.status)
+        y = self.linear(a, w)
+        return y.add_(residual) if residual is not None else y
+
+    def _o_proj_ln2(self, i, att2, x):
+        """Attention output projection, residual add and the second RMSNorm: returns (h2, rstd2, x2)."""
+        cfg, P, C = self.cfg, self.store.params, self.C
+        p = f"layers.{i}."
+        self.launches += 1
+        if self.tp is not None:
+            x2 = self._row_parallel(att2, P[p + "attn.o.weight"], x)
+            h2, rstd2 = C.rmsnorm_fwd(x2, None, P[p + "ln2.weight"], cfg.rms_eps)
+            return h2, rstd2, x2
+        o = self.linear(att2, P[p + "attn.o.weight"])
+        return C.rmsnorm_fwd(o, x, P[p + "ln2.weight"], cfg.rms_eps)
+
+    def _col_parallel_dgrad(self, dy, w):
+        """Input gradient of a column-parallel weight: partial over the tensor-parallel ranks, so all-reduced."""
+        if self.tp is not None:
+            self.launches += 3
+            return self.tp.linear_allreduce(dy, w, b_mn=True, gemm_status=self.status)
+        return self.linear_dgrad(dy, w)
 
     SMALL_T = 8  # decode steps with at most this many rows take the weight-streaming kernels
 
@@ -312,9 +339,7 @@ class B200Qwen3:
         v = self._v_view(qkv)
         att, lse = self.attention(q, k, v, cu)
         att2 = att.view(att.shape[0], -1)
-        o = self.linear(att2, P[p + "attn.o.weight"])
-        h2, rstd2, x2 = C.rmsnorm_fwd(o, x, P[p + "ln2.weight"], cfg.rms_eps)
-        self.launches += 1
+        h2, rstd2, x2 = self._o_proj_ln2(i, att2, x)
         is_moe = cfg.layer_is_moe(i)
         if is_moe:
             _, saved = self.moe_forward(i, h2, replay_ids, None, keep=True)
@@ -330,7 +355,7 @@ class B200Qwen3:
             dact = self.linear_dgrad(dy, P[p + "mlp.down.weight"])
             self.linear_wgrad(dy, act, G[p + "mlp.down.weight"])
             dgu = C.swiglu_bwd(dact, gu)
-            dh2 = self.linear_dgrad(dgu, P[p + "mlp.gate_up.weight"])
+            dh2 = self._col_parallel_dgrad(dgu, P[p + "mlp.gate_up.weight"])
             self.linear_wgrad(dgu, h2, G[p + "mlp.gate_up.weight"])
             self.launches += 1
         # ---- ln2 (residual gradient dy flows straight through x2)
@@ -348,7 +373,7 @@ class B200Qwen3:
         self.launches += 1
         if cfg.qkv_bias:
             G[p + "attn.qkv.bias"].add_(dqkv.float().sum(0).to(G[p + "attn.qkv.bias"].dtype))
-        dh1 = self.linear_dgrad(dqkv, P[p + "attn.qkv.weight"])
+        dh1 = self._col_parallel_dgrad(dqkv, P[p + "attn.qkv.weight"])
         self.linear_wgrad(dqkv, h1, G[p + "attn.qkv.weight"])
         dx = C.rmsnorm_bwd(dh1, x, P[p + "ln1.weight"], rstd1, dx2, G[p + "ln1.weight"], True)
         self.launches += 2

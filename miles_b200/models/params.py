@@ -85,6 +85,67 @@ def build_specs(cfg: ModelConfig, ep_size: int = 1) -> list[ParamSpec]:
     return specs
 
 
+# ---------------------------------------------------------------------------------------------- tensor parallel
+TP_SHARDED = ("attn.qkv.weight", "attn.qkv.bias", "attn.o.weight", "mlp.gate_up.weight", "mlp.down.weight")
+
+
+def tp_local_config(cfg: ModelConfig, tp: int) -> ModelConfig:
+    """The per-rank view of the model under tensor parallelism: heads and the dense FFN width are divided, the rest
+    (hidden size, experts, vocabulary) stays. Every shape of the store and of the kernels follows from it."""
+    if tp == 1:
+        return cfg
+    assert cfg.num_q_heads % tp == 0 and cfg.num_kv_heads % tp == 0, "tensor parallel size must divide the head counts"
+    assert cfg.is_moe or cfg.ffn_hidden_size % tp == 0
+    import copy
+
+    c = copy.copy(cfg)
+    c.num_q_heads, c.num_kv_heads = cfg.num_q_heads // tp, cfg.num_kv_heads // tp
+    if cfg.ffn_hidden_size:
+        c.ffn_hidden_size = cfg.ffn_hidden_size // tp
+    return c
+
+
+def is_tp_sharded(name: str) -> bool:
+    return name.endswith(TP_SHARDED)
+
+
+def tp_slice(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, rank: int) -> torch.Tensor:
+    """Rank ``rank``'s shard of a full (global-config) tensor. qkv: the rank's q heads, k heads and v heads; o and
+    down: the matching input columns; gate_up: the rank's gate rows followed by its up rows."""
+    if tp == 1 or not is_tp_sharded(name):
+        return full
+    D = cfg.head_dim
+    if name.endswith(("attn.qkv.weight", "attn.qkv.bias")):
+        q, kv = cfg.q_dim, cfg.kv_dim
+        ql, kl = q // tp, kv // tp
+        parts = [full[rank * ql:(rank + 1) * ql], full[q + rank * kl:q + (rank + 1) * kl],
+                 full[q + kv + rank * kl:q + kv + (rank + 1) * kl]]
+        return torch.cat(parts, 0)
+    if name.endswith("attn.o.weight"):
+        ql = cfg.q_dim // tp
+        return full[:, rank * ql:(rank + 1) * ql]
+    if name.endswith("mlp.gate_up.weight"):
+        I = cfg.ffn_hidden_size
+        il = I // tp
+        return torch.cat([full[rank * il:(rank + 1) * il], full[I + rank * il:I + (rank + 1) * il]], 0)
+    il = cfg.ffn_hidden_size // tp  # mlp.down.weight
+    return full[:, rank * il:(rank + 1) * il]
+
+
+def tp_merge(cfg: ModelConfig, name: str, shards: list) -> torch.Tensor:
+    """Inverse of :func:`tp_slice` for the list of all ranks' shards (rank order)."""
+    tp = len(shards)
+    if tp == 1 or not is_tp_sharded(name):
+        return shards[0]
+    if name.endswith(("attn.qkv.weight", "attn.qkv.bias")):
+        ql, kl = cfg.q_dim // tp, cfg.kv_dim // tp
+        return torch.cat([s[:ql] for s in shards] + [s[ql:ql + kl] for s in shards] + [s[ql + kl:] for s in shards], 0)
+    if name.endswith(("attn.o.weight", "mlp.down.weight")):
+        return torch.cat(shards, 1)
+    il = cfg.ffn_hidden_size // tp
+    return torch.cat([s[:il] for s in shards] + [s[il:] for s in shards], 0)
+
+
 def _seed_for(seed: int, key: str) -> int:
     h = hashlib.blake2b(f"{seed}:{key}".encode(), digest_size=8).digest()
     return int.from_bytes(h, "little") & 0x7FFFFFFFFFFFFFFF
@@ -95,7 +156,12 @@ class ParamStore:
 
     def __init__(self, cfg: ModelConfig, device: torch.device | str = "cpu", dtype: torch.dtype = torch.bfloat16,
                  ep_size: int = 1, ep_rank: int = 0, init_std: float = 0.02, seed: int = 1234, init: bool = True,
-                 meta: bool = False):
+                 meta: bool = False, tp_size: int = 1, tp_rank: int = 0):
+        """``cfg`` is the global model; with ``tp_size > 1`` the store holds this rank's shard (``self.cfg`` becomes
+        the local view, ``self.global_cfg`` keeps the full model for conversions)."""
+        self.global_cfg = cfg
+        self.tp_size, self.tp_rank = tp_size, tp_rank
+        cfg = tp_local_config(cfg, tp_size)
         self.cfg = cfg
         self.device = torch.device(device)
         self.dtype = dtype
@@ -118,6 +184,8 @@ class ParamStore:
     @torch.no_grad()
     def init_weights(self, std: float = 0.02, seed: int = 1234) -> None:
         gen = torch.Generator(device=self.device)
+        if self.tp_size > 1:
+            self._gshapes = {g.name: g.shape for g in build_specs(self.global_cfg, self.ep_size)}
         el = self.cfg.num_experts // self.ep_size if self.cfg.is_moe else 0
         for s in self.specs:
             p = self.params[s.name]
@@ -131,6 +199,22 @@ class ParamStore:
                     ge = self.ep_rank * el + le
                     gen.manual_seed(_seed_for(seed, f"{s.name}:{ge}"))
                     p[le].copy_(torch.empty(p[le].shape, dtype=torch.float32, device=self.device).normal_(0.0, std, generator=gen))
+            elif self.tp_size > 1 and is_tp_sharded(s.name):
+                # draw the full tensor of the global model and keep this rank's shard: any TP factorisation builds
+                # the same model
+                gshape = next(g.shape for g in build_specs(self.global_cfg, self.ep_size) if g.name == s.name) \
+                    if not hasattr(self, "_gshapes") else self._gshapes[s.name]
+                gen.manual_seed(_seed_for(seed, s.name))
+                n = 1
+                for d in gshape:
+                    n *= d
+                full = torch.empty(n, dtype=torch.float32, device=self.device)
+                chunk = 1 << 26
+                for a in range(0, n, chunk):
+                    b = min(a + chunk, n)
+                    full[a:b].normal_(0.0, std, generator=gen)
+                p.copy_(tp_slice(self.global_cfg, s.name, full.view(gshape), self.tp_size, self.tp_rank))
+                del full
             else:
                 gen.manual_seed(_seed_for(seed, s.name))
                 chunk = 1 << 26

@@ -60,10 +60,19 @@ class TrainActor:
         want_b200 = backend == "b200" or (backend == "auto" and self.on_gpu and self.cfg.head_dim == 128)
         self.dtype = torch.bfloat16 if want_b200 else (torch.float32 if not self.on_gpu else torch.bfloat16)
         ep = self.ps.ep.size if self.cfg.is_moe else 1
+        tp = self.ps.tp.size
         if store is None:
             store = ParamStore(self.cfg, self.device, self.dtype, ep_size=ep, ep_rank=self.ps.ep.rank if ep > 1 else 0,
-                               init_std=getattr(args, "init_std", 0.02), seed=args.seed)
+                               init_std=getattr(args, "init_std", 0.02), seed=args.seed, tp_size=tp, tp_rank=self.ps.tp.rank)
         self.store = store
+        self.tp_exchange = None
+        if tp > 1:
+            from ..parallel.tensor_parallel import TensorParallel
+
+            assert want_b200, "tensor parallelism needs the sm_100a model path"
+            max_tok = max(getattr(args, "max_tokens_per_gpu", None) or 0, getattr(args, "engine_max_prefill_tokens", 16384), 4096)
+            self.tp_exchange = TensorParallel(self.ps.tp.group, self.ps.tp.rank, tp, self.device, self.cfg.hidden_size, max_tok,
+                                              fused=getattr(args, "fused_comm", True))
         self.ep_dispatcher = None
         if ep > 1:
             from ..parallel.expert_parallel import ExpertParallel
@@ -71,7 +80,7 @@ class TrainActor:
             max_tok = max(getattr(args, "max_tokens_per_gpu", None) or 0, getattr(args, "engine_max_prefill_tokens", 16384),
                           (getattr(args, "rollout_max_context_len", None) or 0), 4096)
             self.ep_dispatcher = ExpertParallel(self.cfg, self.ps, fused=getattr(args, "fused_comm", True), max_tokens=max_tok)
-        self.model = build_model(self.cfg, store, "b200" if want_b200 else "torch", ep=self.ep_dispatcher)
+        self.model = build_model(self.cfg, store, "b200" if want_b200 else "torch", ep=self.ep_dispatcher, tp=self.tp_exchange)
         self.is_torch = not want_b200
         self.loss_cfg = LossConfig.from_args(args)
         if getattr(args, "custom_tis_function_path", None):
@@ -147,7 +156,8 @@ class TrainActor:
                          master_weights=plan["master"], offload_states=plan["offload"], lr_decay_style=a.lr_decay_style,
                          lr_warmup_iters=a.lr_warmup_iters or 0, lr_decay_iters=a.lr_decay_iters or 0, min_lr=a.min_lr,
                          lr_wsd_decay_iters=a.lr_wsd_decay_iters or 0)
-        self.opt = FlatAdam(self.store, oc, dp_group=self.ps.dp_cp.group, ep_group=self.ps.ep.group)
+        self.opt = FlatAdam(self.store, oc, dp_group=self.ps.dp_cp.group, ep_group=self.ps.ep.group,
+                            tp_group=self.ps.tp.group if self.ps.tp.size > 1 else None)
 
     # ------------------------------------------------------------------ weight tags (ref / old_actor / teacher)
     def backup_weights(self, tag: str) -> None:
@@ -365,6 +375,14 @@ class TrainActor:
         """Sum dense gradients over dp x cp and expert gradients over the experts' own data-parallel group."""
         if self.ps.world_size <= 1:
             return
+        if self.ps.tp.size > 1:
+            # q/k norm weights are shared by all heads: each tensor-parallel rank holds the sum over its own heads
+            names = [n for n in self.store.grads if n.endswith(("attn.q_norm.weight", "attn.k_norm.weight"))]
+            if names:
+                buf = torch.stack([self.store.grads[n].float() for n in names])
+                dist.all_reduce(buf, group=self.ps.tp.group)
+                for n, row in zip(names, buf):
+                    self.store.grads[n].copy_(row)
         g = self.store.grad
         if self.ps.dp_cp.size > 1 and g["dense"] is not None and g["dense"].numel():
             dist.all_reduce(g["dense"], group=self.ps.dp_cp.group)

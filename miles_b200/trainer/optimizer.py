@@ -66,9 +66,10 @@ def lr_at(cfg: OptimConfig, step: int) -> float:
 
 
 class FlatAdam:
-    def __init__(self, store: ParamStore, cfg: OptimConfig, dp_group=None, ep_group=None):
+    def __init__(self, store: ParamStore, cfg: OptimConfig, dp_group=None, ep_group=None, tp_group=None):
         self.store, self.cfg = store, cfg
         self.dp_group, self.ep_group = dp_group, ep_group
+        self.tp_group = tp_group  # tensor-parallel shards count once each in the global gradient norm
         self.dev = store.device
         self.on_gpu = self.dev.type == "cuda"
         self.step_count = 0
@@ -130,6 +131,18 @@ class FlatAdam:
                 self._sumsq(gr, self.norm_buf[i:i + 1])
         if self.ep_group is not None and dist.is_initialized() and dist.get_world_size(self.ep_group) > 1:
             dist.all_reduce(self.norm_buf[1:2], group=self.ep_group)
+        if self.tp_group is not None and dist.is_initialized() and dist.get_world_size(self.tp_group) > 1:
+            # dense = replicated tensors (identical on every tensor-parallel rank, counted once) + sharded ones
+            # (each rank holds a different part): sum the sharded part over the group
+            from ..models.params import is_tp_sharded
+
+            sharded = torch.zeros(1, dtype=torch.float32, device=self.dev)
+            for name, g in self.store.grads.items():
+                if is_tp_sharded(name):
+                    sharded += g.float().pow(2).sum()
+            total_sharded = sharded.clone()
+            dist.all_reduce(total_sharded, group=self.tp_group)
+            self.norm_buf[0:1] += total_sharded - sharded
         total = self.norm_buf.sum().sqrt()
         self.last_grad_norm = total
         return total
