@@ -185,7 +185,7 @@ def main() -> None:
     if rank == 0:
         cfg = loop.actor.cfg
         out = {
-            "metric": "GRPO tokens/s/step (prompt+response tokens / (rollout + logprob + train + weight sync)), Qwen3-30B-A3B",
+            "metric": f"GRPO tokens/s/step (prompt+response tokens / (rollout + logprob + train + weight sync)), {cfg.name}",
             "value": tokens / dev_s, "unit": "tokens/s", "n_gpus": world, "steps": ns.steps, "warmup": ns.warmup,
             "ms_per_step": dev_s * 1e3 / ns.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (uniform random 1024-token prompts, random-init weights, forced log-normal response lengths)",
@@ -196,7 +196,7 @@ def main() -> None:
                 "tokens_per_step": tokens / ns.steps, "parallelism": (f"dp{world}-attn x ep{world}-experts, colocated engine" if ns.tp == 1 else
                                                      f"tp{ns.tp} x dp{world // ns.tp}, colocated engine"),
                 "optimizer_plan": loop.actor.plan.get("name"), "routing_replay": not ns.no_routing_replay,
-                "l2": "working set (61 GB of weights + KV cache) is far larger than L2; no explicit flush",
+                "l2": f"working set ({cfg.num_params() * 2 / 1e9:.0f} GB of weights + KV cache) is far larger than L2; no explicit flush",
                 "phases_s": {k: round(float(v), 3) for k, v in last.items() if k.startswith("perf/") and k.endswith(("_time", "_wall"))},
             },
             "clocks": clocks,

@@ -141,8 +141,10 @@ def export_hf(actor, out_dir: str, max_shard_bytes: int = 5 << 30, tokenizer_dir
     if ps.rank == 0 and os.path.exists(marker):
         os.remove(marker)
     shards, cur, size = [], {}, 0
-    for hf_name, t in hf_names(cfg, store):
+    for hf_name, t in hf_names(cfg, store, tp_group=ps.tp.group if ps.tp.size > 1 else None):
         is_expert = ".experts." in hf_name
+        if ps.tp.size > 1 and ps.tp.rank != 0:
+            continue  # the gathered tensors are identical on every tensor-parallel rank
         if not is_expert and ps.dp_cp.rank != 0:
             continue  # replicated tensors are written once
         nb = t.numel() * t.element_size()

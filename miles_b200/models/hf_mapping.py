@@ -63,21 +63,51 @@ def to_hf(cfg: ModelConfig, name: str, t: torch.Tensor, expert_offset: int = 0) 
     raise KeyError(name)
 
 
-def hf_names(cfg: ModelConfig, store) -> Iterator[tuple]:
-    """Iterate (hf_name, tensor) over every local parameter of ``store``."""
+def hf_names(cfg: ModelConfig, store, tp_group=None) -> Iterator[tuple]:
+    """Iterate (hf_name, tensor) over every local parameter of ``store``. Under tensor parallelism the sharded
+    tensors are gathered over ``tp_group`` first (a collective: every rank of the group must iterate), which is
+    the all-gather the reference performs per parameter (update_weight/common.py:189-221)."""
+    from .params import is_tp_sharded, tp_merge
+
+    gcfg = getattr(store, "global_cfg", cfg)
+    tp = getattr(store, "tp_size", 1)
     el = cfg.num_experts // store.ep_size if cfg.is_moe else 0
     for name, t in store.named_parameters():
-        for item in to_hf(cfg, name, t, expert_offset=store.ep_rank * el):
+        if tp > 1 and is_tp_sharded(name):
+            import torch.distributed as dist
+
+            parts = [torch.empty_like(t) for _ in range(tp)]
+            dist.all_gather(parts, t.contiguous(), group=tp_group)
+            t = tp_merge(gcfg, name, parts)
+        for item in to_hf(gcfg, name, t, expert_offset=store.ep_rank * el):
             yield item
 
 
 def from_hf(cfg: ModelConfig, store, get_tensor, strict: bool = True) -> int:
     """Fill ``store`` from HF tensors; ``get_tensor(hf_name) -> tensor | None``. Returns #tensors loaded."""
+    from .params import build_specs, is_tp_sharded, tp_slice
+
+    gcfg = getattr(store, "global_cfg", cfg)
+    tp = getattr(store, "tp_size", 1)
+    gshapes = {s.name: s.shape for s in build_specs(gcfg, store.ep_size)} if tp > 1 else {}
     el = cfg.num_experts // store.ep_size if cfg.is_moe else 0
     n = 0
     with torch.no_grad():
         for name, dst in store.named_parameters():
-            for hf_name, view in to_hf(cfg, name, dst, expert_offset=store.ep_rank * el):
+            if tp > 1 and is_tp_sharded(name):
+                # assemble the full tensor of the global model on the host, keep this rank's shard
+                full = torch.empty(gshapes[name], dtype=dst.dtype)
+                for hf_name, view in to_hf(gcfg, name, full):
+                    src = get_tensor(hf_name)
+                    if src is None:
+                        if strict:
+                            raise KeyError(f"missing tensor {hf_name} in checkpoint")
+                        continue
+                    view.copy_(src.to(view.dtype))
+                    n += 1
+                dst.copy_(tp_slice(gcfg, name, full, tp, store.tp_rank))
+                continue
+            for hf_name, view in to_hf(gcfg, name, dst, expert_offset=store.ep_rank * el):
                 src = get_tensor(hf_name)
                 if src is None:
                     if name == "lm_head.weight":
