@@ -41,8 +41,35 @@ def _newest_header() -> float:
 
 def sources() -> tuple[list[Path], list[Path]]:
     cu = sorted(p for p in CSRC.rglob("*.cu") if "build" not in p.parts)
-    cpp = sorted(p for p in CSRC.rglob("*.cpp") if "build" not in p.parts)
+    cpp = sorted(p for p in CSRC.rglob("*.cpp") if "build" not in p.parts and "native" not in p.parts)
     return cu, cpp
+
+
+# ---------------------------------------------------------------------------------------------- host-only module
+NATIVE_DIR = CSRC / "native"
+NATIVE_TARGET = PKG / "_native.so"
+
+
+def native_needs_build() -> bool:
+    if not NATIVE_TARGET.exists():
+        return True
+    t = NATIVE_TARGET.stat().st_mtime
+    return any(s.stat().st_mtime > t for s in NATIVE_DIR.glob("*.cpp"))
+
+
+def build_native(verbose: bool = False, force: bool = False) -> Path:
+    """`miles_b200/_native.so`: scheduler / page pool, quorum store, router table. Plain C++17 + pybind11."""
+    if not force and not native_needs_build():
+        return NATIVE_TARGET
+    import pybind11
+
+    srcs = sorted(NATIVE_DIR.glob("*.cpp"))
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-isystem", pybind11.get_include(),
+           "-isystem", sysconfig.get_paths()["include"], *map(str, srcs), "-o", str(NATIVE_TARGET)]
+    if verbose:
+        print(f"[miles_b200] building {NATIVE_TARGET.name} from {len(srcs)} files", file=sys.stderr)
+    _run(cmd)
+    return NATIVE_TARGET
 
 
 def needs_build() -> bool:
@@ -101,6 +128,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
                 f"-L{_cuda_home() / 'lib64'}", "-lcudart", f"-Wl,-rpath,{torch_lib}",
                 f"-Wl,-rpath,{_cuda_home() / 'lib64'}"]
         _run(link)
+    build_native(verbose=verbose, force=force)
     return TARGET
 
 

@@ -153,6 +153,7 @@ void grouped_gemm_contr(const at::Tensor& a, const at::Tensor& b, at::Tensor& c,
 }  // namespace
 
 void register_elementwise(pybind11::module_& m);  // ops_bindings.cpp
+void register_vmm(pybind11::module_& m);          // vmm_allocator.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   namespace py = pybind11;
@@ -166,4 +167,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("sig_flags") = std::vector<int64_t>(), py::arg("sig_me") = 0);
   m.def("grouped_gemm_contr", &grouped_gemm_contr, "MoE weight-gradient GEMM (contraction over each group's rows)");
   register_elementwise(m);
+  register_vmm(m);
 }

@@ -82,24 +82,13 @@ class Request:
         return {"output_ids": list(self.output_ids), "meta_info": meta}
 
 
-class PagePool:
-    """Free-list page allocator (host side). Page 0 is reserved as the dummy page of padded batch rows."""
+def PagePool(num_pages: int):
+    """KV page pool: the C++ free-list allocator of ``csrc/native/engine_core.cpp`` (page 0 is reserved as the
+    dummy page of padded batch rows; ``alloc(n)`` returns a list of page ids or ``None``, ``release(pages)``,
+    ``num_free``)."""
+    from ..ops import _native
 
-    def __init__(self, num_pages: int):
-        self.num_pages = num_pages
-        self.free = deque(range(1, num_pages))
-
-    def alloc(self, n: int) -> Optional[list]:
-        if len(self.free) < n:
-            return None
-        return [self.free.popleft() for _ in range(n)]
-
-    def release(self, pages: Sequence[int]) -> None:
-        self.free.extend(pages)
-
-    @property
-    def num_free(self) -> int:
-        return len(self.free)
+    return _native.load().PagePool(int(num_pages))
 
 
 class Engine:

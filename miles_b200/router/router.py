@@ -15,11 +15,14 @@ from typing import Optional
 
 
 class MilesRouter:
+    """Worker bookkeeping (in-flight counts, consecutive failures, quarantine) lives in the C++ ``RouterTable``
+    (``csrc/native/control_plane.cpp``); this class adds the policies and the HTTP transport."""
+
     def __init__(self, timeout: float = 600.0, max_connections: int = 1024, failure_threshold: int = 3,
                  health_interval: float = 5.0, policy: str = "least_inflight"):
-        self.workers: dict = {}          # url -> in-flight count
-        self.failures: dict = {}
-        self.dead: set = set()
+        from ..ops import _native
+
+        self.table = _native.load().RouterTable(failure_threshold)
         self.timeout, self.max_connections = timeout, max_connections
         self.failure_threshold, self.health_interval = failure_threshold, health_interval
         self.policy = policy
@@ -29,39 +32,51 @@ class MilesRouter:
 
     # ------------------------------------------------------------------ membership
     def add_worker(self, url: str) -> None:
-        url = url.rstrip("/")
-        self.workers.setdefault(url, 0)
-        self.failures[url] = 0
-        self.dead.discard(url)
+        self.table.add(url.rstrip("/"))
 
     def remove_worker(self, url: str) -> None:
-        url = url.rstrip("/")
-        self.workers.pop(url, None)
-        self.failures.pop(url, None)
-        self.dead.discard(url)
+        self.table.remove(url.rstrip("/"))
+
+    @property
+    def workers(self) -> dict:
+        """url -> requests in flight."""
+        return {u: v[0] for u, v in self.table.snapshot().items()}
+
+    @property
+    def dead(self) -> set:
+        return {u for u, v in self.table.snapshot().items() if v[2]}
 
     def live_workers(self) -> list:
-        return [u for u in self.workers if u not in self.dead]
+        return list(self.table.urls(True))
 
     # ------------------------------------------------------------------ selection
-    def pick(self, routing_key: Optional[str] = None) -> str:
+    def acquire(self, routing_key: Optional[str] = None) -> str:
+        """Choose a worker for one request and count it in flight; pair with :meth:`release`."""
+        if self.policy == "least_inflight" or (self.policy == "consistent_hashing" and not routing_key):
+            url = self.table.acquire()
+            if not url:
+                raise RuntimeError("no healthy worker")
+            return url
         live = self.live_workers()
         if not live:
             raise RuntimeError("no healthy worker")
         if self.policy == "round_robin":
             return live[next(self._rr) % len(live)]
-        if self.policy == "consistent_hashing" and routing_key:
-            ring = sorted(live, key=lambda u: hashlib.md5((u + "|" + routing_key).encode()).hexdigest())
-            return ring[0]
-        return min(live, key=lambda u: self.workers[u])
+        ring = sorted(live, key=lambda u: hashlib.md5((u + "|" + routing_key).encode()).hexdigest())
+        return ring[0]
+
+    def release(self, url: str, ok: bool) -> None:
+        self.table.release(url, ok)
+
+    def pick(self, routing_key: Optional[str] = None) -> str:
+        """Like :meth:`acquire` but without keeping the request counted (inspection, tests)."""
+        url = self.acquire(routing_key)
+        if self.policy == "least_inflight" or (self.policy == "consistent_hashing" and not routing_key):
+            self.table.cancel(url)
+        return url
 
     def mark_result(self, url: str, ok: bool) -> None:
-        if ok:
-            self.failures[url] = 0
-            return
-        self.failures[url] = self.failures.get(url, 0) + 1
-        if self.failures[url] >= self.failure_threshold:
-            self.dead.add(url)
+        self.table.report_health(url, ok)
 
     # ------------------------------------------------------------------ transport
     async def _http(self):
@@ -72,33 +87,28 @@ class MilesRouter:
         return self._client
 
     async def forward(self, method: str, path: str, body: bytes, headers: dict):
-        url = self.pick(headers.get("x-smg-routing-key"))
-        self.workers[url] += 1
+        url = self.acquire(headers.get("x-smg-routing-key"))
+        ok = False
         try:
             c = await self._http()
             r = await c.request(method, url + path, content=body, headers={"content-type": headers.get("content-type", "application/json")})
-            self.mark_result(url, r.status_code < 500)
+            ok = r.status_code < 500
             return r.status_code, r.content, r.headers.get("content-type", "application/json")
-        except Exception:
-            self.mark_result(url, False)
-            raise
         finally:
-            if url in self.workers:
-                self.workers[url] -= 1
+            self.release(url, ok)
 
     async def health_loop(self) -> None:
         while True:
             c = await self._http()
-            for url in list(self.workers):
+            for url in list(self.table.urls(False)):
                 try:
                     r = await c.get(url + "/health", timeout=5.0)
                     ok = r.status_code == 200
                 except Exception:
                     ok = False
-                if ok and url in self.dead:
-                    self.dead.discard(url)
-                    self.failures[url] = 0
-                elif not ok:
+                if ok:
+                    self.table.readmit(url)
+                else:
                     self.mark_result(url, False)
             await asyncio.sleep(self.health_interval)
 

@@ -130,9 +130,12 @@ def test_router_policies_and_quarantine():
     r = MilesRouter(failure_threshold=2)
     for u in ("http://a", "http://b", "http://c"):
         r.add_worker(u)
-    r.workers["http://a"] = 5
-    r.workers["http://b"] = 1
-    r.workers["http://c"] = 3
+    for _ in range(9):  # least-inflight spreads them 3 / 3 / 3; finishing some leaves a = 3, b = 1, c = 2
+        r.acquire()
+    for u, n in (("http://b", 2), ("http://c", 1)):
+        for _ in range(n):
+            r.release(u, True)
+    assert r.workers == {"http://a": 3, "http://b": 1, "http://c": 2}
     assert r.pick() == "http://b"
     r.mark_result("http://b", False)
     assert r.pick() == "http://b"
