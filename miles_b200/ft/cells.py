@@ -85,11 +85,17 @@ class TrainCell:
 
 
 class TrainGroup:
-    def __init__(self, num_cells: int, actor_factory: Callable[[int], list], max_retries: int = 30):
+    def __init__(self, num_cells: int, actor_factory: Callable[[int], list], max_retries: int = 30,
+                 heartbeat_timeout: float = 60.0):
         self.cells = [TrainCell(i, actor_factory) for i in range(num_cells)]
         self.max_retries = max_retries
         self.quorum_id = 0
         self.events: list = []
+        # membership as the participants would see it through the C++ quorum store (csrc/native/control_plane.cpp):
+        # members that stop heartbeating drop out after `heartbeat_timeout` even if nobody reports them
+        from ..ops import _native
+
+        self.store = _native.load().QuorumStore(timeout_s=heartbeat_timeout)
 
     def alive_cells(self) -> list:
         return [c for c in self.cells if c.alive]
@@ -115,6 +121,11 @@ class TrainGroup:
             except BaseException:
                 continue
         members = [c.index for c in survivors] + [c.index for c in pending if c.state == CellState.ALLOCATED_UNINITIALIZED]
+        for c in self.cells:
+            if c.index in members:
+                self.store.heartbeat(f"cell-{c.index}")
+            else:
+                self.store.evict(f"cell-{c.index}")
         for c in survivors:
             try:
                 c.execute("reconfigure", quorum_id=self.quorum_id, members=members)

@@ -74,7 +74,7 @@ def _targets(store: ParamStore, modules: Sequence[str]) -> list:
 
 class LoRAManager:
     def __init__(self, store: ParamStore, rank: int, alpha: float, target_modules: Sequence[str] | str = "all-linear",
-                 lr: float = 1e-4, weight_decay: float = 0.0, seed: int = 0, betas=(0.9, 0.999)):
+                 lr: float = 1e-4, weight_decay: float = 0.0, seed: int = 0, betas=(0.9, 0.999), base: Optional[dict] = None):
         assert rank > 0
         mods = ALL_LINEAR if target_modules in ("all-linear", None) else list(target_modules)
         self.store, self.rank, self.alpha = store, rank, float(alpha)
@@ -89,8 +89,12 @@ class LoRAManager:
             a = torch.empty(rank, w.shape[1]).uniform_(-1, 1, generator=g) * math.sqrt(3.0 / w.shape[1])
             self.A.append(a.to(dev).requires_grad_(False))
             self.B.append(torch.zeros(w.shape[0], rank, device=dev))
-        # frozen base copies of the targeted tensors only
-        self.base = {n: store.params[n].detach().clone() for n in {t.native for t in self.targets}}
+        # frozen base copies of the targeted tensors only (several adapters on one model share one set: ``base``)
+        need = {t.native for t in self.targets}
+        self.base = base if base is not None else {}
+        for n in need:
+            if n not in self.base:
+                self.base[n] = store.params[n].detach().clone()
         self.opt = torch.optim.AdamW([p for p in self.A + self.B], lr=lr, weight_decay=weight_decay, betas=betas)
         for p in self.A + self.B:
             p.grad = torch.zeros_like(p)
