@@ -1,0 +1,123 @@
+"""Context parallelism: how a packed batch is cut along the sequence and put back together.
+
+Zigzag layout (the default of the reference, needed for a balanced causal load): every sample is split into
+``2 * cp`` chunks and rank ``r`` owns chunks ``r`` and ``2 * cp - 1 - r``, so each rank holds an early and a late
+piece of every sample. All-gather layout (``--allgather-cp``): the concatenated batch is padded to a multiple of
+``cp`` and every rank owns one contiguous piece.
+
+Forward attention under context parallelism gathers K and V over the group (they are ``num_kv_heads / num_q_heads``
+of the activation bytes under GQA) and runs the tcgen05 attention kernel on the local queries with tile
+descriptors that carry each query chunk's position inside its sequence (``build_cp_tiles``); per-token outputs
+(log-probs, entropy, values) are put back in sample order with ``gather_per_token``. The backward pass of the
+attention under context parallelism is not implemented here: training runs with cp = 1, log-prob / reference /
+critic forwards may use cp > 1.
+
+Reference: miles/backends/training_utils/cp_utils.py:19-67,195-303 (zigzag slicing, all_gather_with_cp),
+data.py:198-235 (all-gather mode).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+def zigzag_bounds(n: int, cp: int, rank: int) -> list:
+    """[(start, end)] of the two chunks of a length-``n`` sample owned by ``rank`` (chunk sizes differ by at most 1)."""
+    parts = 2 * cp
+    base, rem = divmod(n, parts)
+    starts = [i * base + min(i, rem) for i in range(parts + 1)]
+    a, b = rank, parts - 1 - rank
+    return [(starts[a], starts[a + 1]), (starts[b], starts[b + 1])]
+
+
+def zigzag_slice(x: torch.Tensor, lens: Sequence[int], cp: int, rank: int) -> torch.Tensor:
+    """Rows of a packed ``[T, ...]`` tensor owned by ``rank`` (samples stay in order, early chunk before late chunk)."""
+    if cp == 1:
+        return x
+    out, s0 = [], 0
+    for n in lens:
+        for a, b in zigzag_bounds(n, cp, rank):
+            out.append(x[s0 + a:s0 + b])
+        s0 += n
+    return torch.cat(out, 0)
+
+
+def zigzag_positions(lens: Sequence[int], cp: int, rank: int) -> torch.Tensor:
+    """Position of every local token inside its sample (what RoPE and the causal mask need)."""
+    out = []
+    for n in lens:
+        for a, b in zigzag_bounds(n, cp, rank):
+            out.append(torch.arange(a, b, dtype=torch.int32))
+    return torch.cat(out) if out else torch.zeros(0, dtype=torch.int32)
+
+
+def unzigzag(parts: Sequence[torch.Tensor], lens: Sequence[int], cp: int) -> torch.Tensor:
+    """Inverse of :func:`zigzag_slice`: ``parts[r]`` are rank ``r``'s rows; returns the packed tensor in sample order."""
+    if cp == 1:
+        return parts[0]
+    cursors = [0] * cp
+    out = []
+    for n in lens:
+        chunks = {}
+        for r in range(cp):
+            for idx, (a, b) in zip((r, 2 * cp - 1 - r), zigzag_bounds(n, cp, r)):
+                chunks[idx] = parts[r][cursors[r]:cursors[r] + (b - a)]
+                cursors[r] += b - a
+        out.extend(chunks[i] for i in range(2 * cp))
+    return torch.cat(out, 0)
+
+
+def contiguous_bounds(total: int, cp: int, rank: int, multiple: int = 1) -> tuple:
+    """All-gather layout: (start, end, padded_total) of the rank's piece of the concatenated batch."""
+    unit = cp * multiple
+    padded = (total + unit - 1) // unit * unit
+    per = padded // cp
+    return rank * per, min(total, (rank + 1) * per), padded
+
+
+def build_cp_tiles(lens: Sequence[int], cp: int, rank: int, tile: int = 128) -> torch.Tensor:
+    """Tile table for the attention kernel on a zigzag shard: int32 ``[n, 4]`` rows ``{q_row0, q_rows, kv_row0,
+    q_pos0}`` where q rows index the local query tensor and kv rows the gathered (sample-order) K / V."""
+    rows, q0, kv0 = [], 0, 0
+    for n in lens:
+        for a, b in zigzag_bounds(n, cp, rank):
+            for c in range(a, b, tile):
+                rows.append((q0 + (c - a), min(tile, b - c), kv0, c))
+            q0 += b - a
+        kv0 += n
+    rows.sort(key=lambda r: -(r[3] + r[1]))
+    return torch.tensor(rows, dtype=torch.int32).view(-1, 4)
+
+
+def gather_kv(k_local: torch.Tensor, v_local: torch.Tensor, lens: Sequence[int], cp: int, group) -> tuple:
+    """All-gather the zigzag shards of K and V over the group and put them in sample order."""
+    if cp == 1:
+        return k_local, v_local
+    sizes = [sum(b - a for n in lens for a, b in zigzag_bounds(n, cp, r)) for r in range(cp)]
+    out = []
+    for t in (k_local, v_local):
+        parts = [torch.empty((s,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device) for s in sizes]
+        dist.all_gather(parts, t.contiguous(), group=group)
+        out.append(unzigzag(parts, lens, cp))
+    return out[0], out[1]
+
+
+def gather_per_token(x_local: torch.Tensor, lens: Sequence[int], cp: int, rank: int, group=None) -> torch.Tensor:
+    """Per-token values of all ranks in sample order. Each rank scatters its rows into a zero tensor of the full
+    length and the group sums them (one all-reduce; differentiable in the reference's sense: every row has exactly
+    one non-zero contributor)."""
+    if cp == 1:
+        return x_local
+    total = sum(lens)
+    full = torch.zeros((total,) + tuple(x_local.shape[1:]), dtype=x_local.dtype, device=x_local.device)
+    s0, cur = 0, 0
+    for n in lens:
+        for a, b in zigzag_bounds(n, cp, rank):
+            full[s0 + a:s0 + b] = x_local[cur:cur + (b - a)]
+            cur += b - a
+        s0 += n
+    if group is not None or dist.is_initialized():
+        dist.all_reduce(full, group=group)
+    return full

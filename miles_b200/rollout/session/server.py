@@ -1,0 +1,121 @@
+"""OpenAI-compatible session proxy: ``POST /sessions/{id}/v1/chat/completions`` keeps the exact token sequence of
+an agent conversation across turns (token in, token out) and ``GET /sessions/{id}/sample`` returns the assembled
+training sample (tokens, loss mask, rollout log-probs).
+
+An agent framework talks to this endpoint as if it were a chat model. Each request carries the whole conversation
+so far; the server renders only the messages it has not seen yet (through the tokenizer's chat template, as a
+delta against the previous rendering), appends them to the session's trajectory with loss mask 0, asks the
+engine to continue from the session's token ids, appends the sampled ids with their log-probs and answers with
+the decoded text.
+
+Reference: miles/rollout/session/core.py:244-453, sessions.py:26-116.
+"""
+
+import threading
+import time
+import uuid
+from typing import Callable, Optional
+
+from .trajectory import LinearTrajectory
+
+
+class SessionStore:
+    def __init__(self, tokenizer, generate: Callable, max_sessions: int = 4096):
+        """``generate(input_ids, sampling_params) -> dict`` with ``output_ids``, ``output_token_logprobs`` (floats),
+        ``finish_reason`` and optionally ``weight_version`` (a blocking call into the engine client)."""
+        self.tok, self.generate = tokenizer, generate
+        self.max_sessions = max_sessions
+        self._lock = threading.Lock()
+        self.sessions: dict = {}
+        self._rendered: dict = {}  # session id -> text of the conversation rendered so far (for delta rendering)
+
+    def get(self, sid: str) -> LinearTrajectory:
+        with self._lock:
+            if sid not in self.sessions:
+                if len(self.sessions) >= self.max_sessions:
+                    raise RuntimeError("too many open sessions")
+                self.sessions[sid] = LinearTrajectory(sid)
+                self._rendered[sid] = ""
+            return self.sessions[sid]
+
+    def close(self, sid: str) -> Optional[LinearTrajectory]:
+        with self._lock:
+            self._rendered.pop(sid, None)
+            return self.sessions.pop(sid, None)
+
+    # ------------------------------------------------------------------ rendering
+    def _render(self, messages: list, add_generation_prompt: bool) -> str:
+        if hasattr(self.tok, "apply_chat_template"):
+            return self.tok.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt)
+        text = "".join(f"<|{m['role']}|>{m.get('content') or ''}<|end|>" for m in messages)
+        return text + ("<|assistant|>" if add_generation_prompt else "")
+
+    def _encode(self, text: str) -> list:
+        return list(self.tok.encode(text, add_special_tokens=False)) if text else []
+
+    def chat(self, sid: str, messages: list, sampling_params: dict) -> dict:
+        traj = self.get(sid)
+        if len(messages) < traj.num_messages:
+            raise ValueError("the request holds fewer messages than the session: a session only moves forward")
+        full = self._render(messages, add_generation_prompt=True)
+        seen = self._rendered[sid]
+        if not full.startswith(seen):
+            raise ValueError("the conversation does not extend the session's history (token-in-token-out would break)")
+        delta = full[len(seen):]
+        new_ids = self._encode(delta)
+        if new_ids:
+            role = messages[-1]["role"] if messages else "user"
+            traj.append_context(role, new_ids)
+        out = self.generate(list(traj.tokens), dict(sampling_params))
+        ids = list(out["output_ids"])
+        lps = [float(x[0]) if isinstance(x, (list, tuple)) else float(x) for x in out.get("output_token_logprobs", [0.0] * len(ids))]
+        traj.append_generation(ids, lps, out.get("weight_version"), out.get("finish_reason"))
+        text = self.tok.decode(ids, skip_special_tokens=True) if hasattr(self.tok, "decode") else ""
+        # what the next request will contain for this turn is the assistant message as text; remember the rendering
+        # of the history *with* the sampled ids decoded exactly, so that the next delta starts after them
+        self._rendered[sid] = full + (self.tok.decode(ids, skip_special_tokens=False) if hasattr(self.tok, "decode") else "")
+        traj.num_messages = len(messages) + 1
+        return {"text": text, "ids": ids, "finish_reason": out.get("finish_reason", "stop")}
+
+
+def build_session_app(store: SessionStore, model_name: str = "policy"):
+    from fastapi import FastAPI, HTTPException, Request
+
+    app = FastAPI(title="miles_b200 session server")
+
+    async def _chat(sid: str, req: Request):
+        body = await req.json()
+        sp = {"temperature": body.get("temperature", 1.0), "top_p": body.get("top_p", 1.0),
+              "max_new_tokens": body.get("max_tokens") or body.get("max_completion_tokens") or 1024}
+        if body.get("stop"):
+            sp["stop"] = body["stop"]
+        try:
+            out = store.chat(sid, body.get("messages", []), sp)
+        except ValueError as e:
+            raise HTTPException(409, str(e))
+        except RuntimeError as e:
+            raise HTTPException(503, str(e))
+        fr = out["finish_reason"]
+        fr = fr.get("type") if isinstance(fr, dict) else fr
+        return {"id": "chatcmpl-" + uuid.uuid4().hex[:24], "object": "chat.completion", "created": int(time.time()),
+                "model": body.get("model", model_name),
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": out["text"]},
+                             "finish_reason": "length" if fr == "length" else "stop"}],
+                "usage": {"completion_tokens": len(out["ids"])}}
+
+    app.post("/sessions/{sid}/v1/chat/completions")(_chat)
+
+    @app.get("/sessions/{sid}/sample")
+    async def sample(sid: str):
+        if sid not in store.sessions:
+            raise HTTPException(404, "unknown session")
+        return store.sessions[sid].to_sample_dict()
+
+    @app.delete("/sessions/{sid}")
+    async def close(sid: str):
+        t = store.close(sid)
+        if t is None:
+            raise HTTPException(404, "unknown session")
+        return t.to_sample_dict()
+
+    return app

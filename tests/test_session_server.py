@@ -1,0 +1,59 @@
+"""Token-in-token-out session proxy: exact token history across turns, loss masks, conflict detection."""
+import pytest
+
+from miles_b200.rollout.session import SessionStore, build_session_app
+
+
+class _Tok:
+    """Character-level tokenizer: decode(encode(x)) == x, which makes the delta rendering easy to check."""
+
+    def encode(self, text, add_special_tokens=False):
+        return [ord(c) for c in text]
+
+    def decode(self, ids, skip_special_tokens=True):
+        return "".join(chr(i) for i in ids)
+
+
+def _store():
+    calls = []
+
+    def generate(input_ids, sp):
+        calls.append(list(input_ids))
+        reply = f"r{len(calls)}"
+        return {"output_ids": [ord(c) for c in reply], "output_token_logprobs": [(-0.5, 0)] * len(reply),
+                "finish_reason": {"type": "stop"}, "weight_version": 3}
+
+    return SessionStore(_Tok(), generate), calls
+
+
+def test_two_turns_keep_exact_history_and_masks():
+    from fastapi.testclient import TestClient
+
+    store, calls = _store()
+    c = TestClient(build_session_app(store))
+    m1 = [{"role": "user", "content": "hi"}]
+    r1 = c.post("/sessions/s1/v1/chat/completions", json={"messages": m1, "max_tokens": 8}).json()
+    assert r1["choices"][0]["message"]["content"] == "r1"
+    m2 = m1 + [{"role": "assistant", "content": "r1"}, {"role": "tool", "content": "42"}]
+    r2 = c.post("/sessions/s1/v1/chat/completions", json={"messages": m2}).json()
+    assert r2["choices"][0]["message"]["content"] == "r2"
+    # the second call continued from the exact ids of turn one (prompt + sampled ids), not from re-rendered text
+    assert calls[1][:len(calls[0]) + 2] == calls[0] + [ord("r"), ord("1")]
+    s = c.get("/sessions/s1/sample").json()
+    text = "".join(chr(i) for i in s["tokens"])
+    assert text.startswith("<|user|>hi<|end|><|assistant|>r1") and text.endswith("r2")
+    resp = s["tokens"][len(s["tokens"]) - s["response_length"]:]
+    trained = "".join(chr(t) for t, m in zip(resp, s["loss_mask"]) if m)
+    assert trained == "r1r2" and len(s["rollout_log_probs"]) == s["response_length"]
+    assert s["weight_versions"] == [3]
+    assert c.delete("/sessions/s1").status_code == 200 and c.get("/sessions/s1/sample").status_code == 404
+
+
+def test_rewritten_history_is_rejected():
+    from fastapi.testclient import TestClient
+
+    store, _ = _store()
+    c = TestClient(build_session_app(store))
+    c.post("/sessions/s/v1/chat/completions", json={"messages": [{"role": "user", "content": "a"}]})
+    bad = [{"role": "user", "content": "changed"}, {"role": "assistant", "content": "r1"}, {"role": "user", "content": "b"}]
+    assert c.post("/sessions/s/v1/chat/completions", json={"messages": bad}).status_code == 409

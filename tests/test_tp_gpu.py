@@ -30,3 +30,14 @@ def test_tensor_parallel_model_matches_single_rank(mode):
            "--master-port", "29743", os.path.join(here, "mp_tp_model_check.py"), mode]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "TP_MODEL_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_context_parallel_attention_forward():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29745", os.path.join(here, "mp_cp_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "CP_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
