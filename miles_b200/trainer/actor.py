@@ -306,8 +306,10 @@ class TrainActor:
         if "ref" in self.weights_backup and a.loss_type == "policy_loss":
             with T.context("ref_log_probs"), self.with_weights("ref"):
                 self.compute_log_probs(mbs, "ref_log_probs")
+        for k in ("train_log_probs", "train_fwd_bwd", "train_optimizer"):
+            T.reset(k)
         if need_old:
-            with T.context("log_probs"):
+            with T.context("log_probs"), T.cuda_span("train_log_probs"):
                 self.compute_log_probs(mbs, "log_probs", with_entropy=getattr(a, "use_rollout_entropy", False))
         if a.loss_type == "policy_loss":
             if data.get("values") is not None:
@@ -333,21 +335,26 @@ class TrainActor:
                     scale = 1.0 / max(float(tok.item()), 1.0)
                 else:
                     scale = 1.0 / gbs
-                for mb in chunk:
-                    m = self._forward_backward(mb, scale)
-                    for k, v in m.items():
-                        metrics_acc[k] = metrics_acc.get(k, 0.0) + v.detach().float() * scale
-                self._reduce_grads()
-                if self.lora is not None:
-                    self.lora.grads_from_weight_grads()
-                    grad_norm = self.lora.step(a.clip_grad)
-                elif self.opt is not None:
-                    grad_norm = self.opt.step(1.0)
+                with T.cuda_span("train_fwd_bwd"):
+                    for mb in chunk:
+                        m = self._forward_backward(mb, scale)
+                        for k, v in m.items():
+                            metrics_acc[k] = metrics_acc.get(k, 0.0) + v.detach().float() * scale
+                    self._reduce_grads()
+                with T.cuda_span("train_optimizer"):
+                    if self.lora is not None:
+                        self.lora.grads_from_weight_grads()
+                        grad_norm = self.lora.step(a.clip_grad)
+                    elif self.opt is not None:
+                        grad_norm = self.opt.step(1.0)
                 self.global_step += 1
         if self.on_gpu:
             torch.cuda.synchronize()
         elapsed = time.perf_counter() - t_start
+        T.flush_cuda()
         out = self._finalize_metrics(metrics_acc, grad_norm, n_tokens_local, elapsed, len(mbs))
+        for k in ("train_log_probs", "train_fwd_bwd", "train_optimizer"):
+            out[f"perf/{k}_time"] = float(T.log_dict().get(k, 0.0))
         if getattr(a, "keep_old_actor", False):
             self.backup_weights("old_actor")
         if a.ref_update_interval and "ref" in self.weights_backup and (rollout_id + 1) % a.ref_update_interval == 0:
