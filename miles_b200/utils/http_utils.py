@@ -1,0 +1,62 @@
+"""Shared async HTTP client with bounded retries (rollout functions, remote reward models, router registration).
+
+Reference: miles/utils/http_utils.py (368 lines: shared httpx client, post/get with retries).
+"""
+from __future__ import annotations
+
+import asyncio
+import random
+from typing import Any, Optional
+
+_client = None
+_limits = {"max_connections": 1024, "timeout": 600.0}
+
+
+def configure(max_connections: int = 1024, timeout: float = 600.0) -> None:
+    global _client
+    _limits.update(max_connections=max_connections, timeout=timeout)
+    _client = None
+
+
+def client():
+    global _client
+    if _client is None:
+        import httpx
+
+        _client = httpx.AsyncClient(timeout=_limits["timeout"], limits=httpx.Limits(max_connections=_limits["max_connections"]))
+    return _client
+
+
+async def request(method: str, url: str, payload: Optional[dict] = None, max_retries: int = 5, base_delay: float = 0.5,
+                  retry_on=(500, 502, 503, 504), transport=None) -> Any:
+    """JSON request with exponential back-off and jitter. ``transport(method, url, payload) -> (status, json)`` replaces
+    the network in tests. Raises the last error when every attempt failed."""
+    last: Optional[BaseException] = None
+    for attempt in range(max_retries + 1):
+        try:
+            if transport is not None:
+                status, body = await transport(method, url, payload)
+            else:
+                r = await client().request(method, url, json=payload)
+                status, body = r.status_code, (r.json() if r.content else None)
+            if status in retry_on:
+                raise RuntimeError(f"{method} {url} -> HTTP {status}")
+            if status >= 400:
+                raise ValueError(f"{method} {url} -> HTTP {status}: {body}")
+            return body
+        except ValueError:
+            raise  # the request itself is wrong: retrying cannot help
+        except Exception as e:  # noqa: BLE001 - network errors of any kind are retried
+            last = e
+            if attempt == max_retries:
+                break
+            await asyncio.sleep(base_delay * (2 ** attempt) * (0.5 + random.random() / 2))
+    raise last if last is not None else RuntimeError("request failed")
+
+
+async def post(url: str, payload: Optional[dict] = None, **kw) -> Any:
+    return await request("POST", url, payload, **kw)
+
+
+async def get(url: str, **kw) -> Any:
+    return await request("GET", url, None, **kw)
