@@ -274,41 +274,74 @@ __global__ void __launch_bounds__(1024)
 build_small_kernel(const int* __restrict__ ids, int n, int E, int max_rows, int max_tiles, int align,
                    int* __restrict__ counts_out, int* __restrict__ offsets, int* __restrict__ dest_row,
                    int* __restrict__ row_src, int* __restrict__ tiles, int* __restrict__ totals) {
-  extern __shared__ int sm[];  // counts[E], off[E+1], tile_start[E+1]
+  extern __shared__ int sm[];  // counts[E], off[E+1], tile_start[E+1], ids[n]
   int* cnt = sm;
   int* off = sm + E;
   int* tstart = off + E + 1;
+  int* sid = tstart + E + 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   for (int i = threadIdx.x; i < E; i += blockDim.x) cnt[i] = 0;
   for (int i = threadIdx.x; i < max_rows; i += blockDim.x) row_src[i] = -1;
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {  // the only global read of the ids
     const int e = ids[i];
+    sid[i] = e;
     if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
     else dest_row[i] = -1;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int o = 0, t = 0;
-    for (int e = 0; e < E; ++e) {
-      off[e] = o;
-      tstart[e] = t;
-      int padded = ((cnt[e] + align - 1) / align) * align;
-      if (o + padded > max_rows) padded = max_rows - o > 0 ? ((max_rows - o) / align) * align : 0;
-      o += padded;
-      t += (padded + 127) / 128;
+  if (warp == 0) {
+    // Exclusive scans by one warp: lane l owns experts [l*per, (l+1)*per). First the padded row offsets, clamped to
+    // the capacity (offsets are multiples of `align`, so clamping both ends of an expert's range equals shrinking the
+    // expert that overflows and giving the later ones nothing), then the 128-row tile starts of the clamped ranges.
+    const int per = (E + 31) / 32;
+    const int e0 = lane * per, e1 = min(E, e0 + per);
+    const int cap = (max_rows / align) * align;
+    int local = 0;
+    for (int e = e0; e < e1; ++e) local += ((cnt[e] + align - 1) / align) * align;
+    int incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
     }
-    off[E] = o;
-    tstart[E] = t < max_tiles ? t : max_tiles;
-    totals[0] = tstart[E];
-    totals[1] = o;
+    int run = incl - local;
+    int tl = 0;
+    for (int e = e0; e < e1; ++e) {
+      const int s0 = min(run, cap);
+      run += ((cnt[e] + align - 1) / align) * align;
+      const int s1 = min(run, cap);
+      off[e] = s0;
+      tl += (s1 - s0 + 127) / 128;
+      tstart[e] = s1 - s0;  // rows of the expert for now; turned into a tile start below
+    }
+    const int total_rows = min(__shfl_sync(0xffffffffu, incl, 31), cap);
+    int tincl = tl;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, tincl, o);
+      if (lane >= o) tincl += v;
+    }
+    int trun = tincl - tl;
+    for (int e = e0; e < e1; ++e) {
+      const int rows = tstart[e];
+      tstart[e] = trun;
+      trun += (rows + 127) / 128;
+    }
+    const int total_tiles = __shfl_sync(0xffffffffu, tincl, 31);
+    if (lane == 0) {
+      off[E] = total_rows;
+      tstart[E] = total_tiles < max_tiles ? total_tiles : max_tiles;
+      totals[0] = tstart[E];
+      totals[1] = total_rows;
+    }
   }
   __syncthreads();
   for (int e = threadIdx.x; e <= E; e += blockDim.x) {
     offsets[e] = off[e];
     if (e < E) counts_out[e] = cnt[e];
   }
-  // tiles and stable ranks: one warp per expert
+  // tiles and stable ranks: one warp per expert, ids read from shared memory
   for (int e = warp; e < E; e += nwarps) {
     const int rows_e = off[e + 1] - off[e];
     for (int j = lane; tstart[e] + j < tstart[e + 1] && tstart[e] + j < max_tiles; j += 32) {
@@ -322,7 +355,7 @@ build_small_kernel(const int* __restrict__ ids, int n, int E, int max_rows, int 
     int base = 0;
     for (int start = 0; start < n; start += 32) {
       const int i = start + lane;
-      const bool hit = i < n && ids[i] == e;
+      const bool hit = i < n && sid[i] == e;
       const unsigned m = __ballot_sync(0xffffffffu, hit);
       if (hit) {
         const int rank = base + __popc(m & ((1u << lane) - 1u));
@@ -334,6 +367,7 @@ build_small_kernel(const int* __restrict__ ids, int n, int E, int max_rows, int 
         }
       }
       base += __popc(m);
+      if (base >= cnt[e]) break;  // all entries of this expert placed (warp-uniform)
     }
   }
 }
@@ -472,7 +506,7 @@ void moe_build_permutation(const int* topk_ids, int T, int K, int E, int max_row
                            int* num_m_tiles, cudaStream_t s) {
   const int n = T * K;
   if (n <= 4096 && max_rows <= 16384 && E <= 512) {
-    build_small_kernel<<<1, 1024, (3 * E + 2) * sizeof(int), s>>>(topk_ids, n, E, max_rows, max_tiles, align, expert_counts,
+    build_small_kernel<<<1, n <= 1024 ? 256 : 1024, (3 * E + 2 + n) * sizeof(int), s>>>(topk_ids, n, E, max_rows, max_tiles, align, expert_counts,
                                                                    expert_offsets, dest_row, row_src, tile_group, num_m_tiles);
     return;
   }

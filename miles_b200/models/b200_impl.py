@@ -214,8 +214,15 @@ class B200Qwen3:
         cfg, P, C = self.cfg, self.store.params, self.C
         p = f"layers.{i}."
         if (meta is not None and not meta.is_prefill and x.shape[0] <= self.SMALL_T and replay_ids is None
-                and (self.ep is None or not cfg.layer_is_moe(i)) and self.small_decode and self.tp is None):
-            return self._layer_forward_small(i, x, positions, meta, kv_cache, record)
+                and self.small_decode and self.tp is None):
+            if self.ep is None or not cfg.layer_is_moe(i):
+                return self._layer_forward_small(i, x, positions, meta, kv_cache, record)
+            # expert-parallel MoE: the attention half still takes the light kernels, the experts go through the exchange
+            x2 = self._attn_small(i, x, positions, meta, kv_cache)
+            h2, _ = C.rmsnorm_fwd(x2, None, P[p + "ln2.weight"], cfg.rms_eps)
+            self.launches += 1
+            y, _ = self.moe_forward(i, h2, replay_ids, record, keep=False, residual=x2)
+            return y
         h1, rstd1, qkv, q, k, _, _ = self._attn_qkv(i, x, positions, meta, kv_cache)
         scale = cfg.head_dim ** -0.5
         if meta is not None and not meta.is_prefill:
@@ -269,9 +276,9 @@ class B200Qwen3:
 
     SMALL_T = 8  # decode steps with at most this many rows take the weight-streaming kernels
 
-    def _layer_forward_small(self, i, x, positions, meta: InferMeta, kv_cache, record=None):
-        """Decode forward of one layer for at most 8 rows: 8-9 light launches instead of 14-15, the two RMSNorms
-        folded into the projections that consume them, no expert permutation (per-expert pair lists)."""
+    def _attn_small(self, i, x, positions, meta: InferMeta, kv_cache):
+        """Attention half of a decode layer for at most 8 rows: returns ``x + attention(x)`` (RMSNorm folded into the
+        qkv projection, residual folded into the output projection)."""
         cfg, P, C = self.cfg, self.store.params, self.C
         p = f"layers.{i}."
         T, dev = x.shape[0], x.device
@@ -294,6 +301,15 @@ class B200Qwen3:
         x2 = torch.empty_like(x)
         C.small_gemv(att.view(T, -1), None, cfg.rms_eps, P[p + "attn.o.weight"], x, x2, self.status)
         self.launches += 6
+        return x2
+
+    def _layer_forward_small(self, i, x, positions, meta: InferMeta, kv_cache, record=None):
+        """Decode forward of one layer for at most 8 rows: 8-9 light launches instead of 14-15, the two RMSNorms
+        folded into the projections that consume them, no expert permutation (per-expert pair lists)."""
+        cfg, P, C = self.cfg, self.store.params, self.C
+        p = f"layers.{i}."
+        T, dev = x.shape[0], x.device
+        x2 = self._attn_small(i, x, positions, meta, kv_cache)
         ln2 = P[p + "ln2.weight"]
         if cfg.layer_is_moe(i):
             E, K = cfg.num_experts, cfg.moe_top_k
