@@ -1,0 +1,101 @@
+"""Collects what the dashboard shows: step metrics (a tracking sink), trajectory life-cycle events (a lifecycle
+sink) and periodic GPU samples (utilisation, memory, power, SM clock through NVML; read-only)."""
+from __future__ import annotations
+
+import threading
+import time
+from typing import Callable, Optional
+
+from .store import EventStore
+
+
+def _nvml_sampler() -> Optional[Callable[[], list]]:
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        n = pynvml.nvmlDeviceGetCount()
+        handles = [pynvml.nvmlDeviceGetHandleByIndex(i) for i in range(n)]
+    except Exception:  # noqa: BLE001 - no driver on this host
+        return None
+
+    def sample() -> list:
+        out = []
+        for i, h in enumerate(handles):
+            try:
+                u = pynvml.nvmlDeviceGetUtilizationRates(h)
+                m = pynvml.nvmlDeviceGetMemoryInfo(h)
+                out.append({"gpu": i, "util": u.gpu, "mem_used": m.used, "mem_total": m.total,
+                            "power_w": pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0,
+                            "sm_mhz": pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)})
+            except Exception:  # noqa: BLE001
+                continue
+        return out
+
+    return sample
+
+
+class Collector:
+    def __init__(self, store: EventStore, gpu_interval: float = 5.0, gpu_sampler: Optional[Callable[[], list]] = None):
+        self.store = store
+        self.gpu_interval = gpu_interval
+        self._sampler = gpu_sampler if gpu_sampler is not None else _nvml_sampler()
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+
+    # sinks -----------------------------------------------------------------------------------------------
+    def log_metrics(self, metrics: dict, step: int) -> None:
+        self.store.append("metrics", {"step": step, **{k: v for k, v in metrics.items() if isinstance(v, (int, float))}})
+
+    def on_lifecycle(self, rec: dict) -> None:
+        self.store.append("trajectories", rec, t=rec.get("t"))
+
+    def sample_gpus_once(self) -> int:
+        if self._sampler is None:
+            return 0
+        rows = self._sampler()
+        for r in rows:
+            self.store.append("gpus", r)
+        return len(rows)
+
+    # background sampling ---------------------------------------------------------------------------------
+    def start(self) -> None:
+        if self._sampler is None or self._thread is not None:
+            return
+
+        def loop():
+            while not self._stop.wait(self.gpu_interval):
+                self.sample_gpus_once()
+
+        self._thread = threading.Thread(target=loop, daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+
+
+def advisories(store: EventStore, window: int = 20) -> list:
+    """Plain-language hints from the recent history (each rule is a few lines: easy to read, easy to extend)."""
+    out = []
+    ms = store.tail("metrics", window)
+    if ms:
+        last = ms[-1]
+        ro, tr = last.get("perf/rollout_time"), last.get("perf/train_time")
+        if ro and tr and ro > 3 * tr:
+            out.append({"rule": "rollout_bound", "text": f"rollout takes {ro:.1f}s against {tr:.1f}s of training: "
+                        "consider the fully-asynchronous driver or a larger rollout batch per GPU"})
+        d = last.get("train/train_rollout_logprob_abs_diff")
+        if d is not None and d > 0.05:
+            out.append({"rule": "train_rollout_mismatch", "text": f"trainer/rollout log-prob difference {d:.3f} is high: "
+                        "check routing replay (MoE) and importance-sampling correction"})
+        trunc = last.get("rollout/truncated_ratio")
+        if trunc is not None and trunc > 0.3:
+            out.append({"rule": "truncation", "text": f"{trunc:.0%} of the responses hit the length limit"})
+        norms = [m.get("train/grad_norm") for m in ms if m.get("train/grad_norm") is not None]
+        if len(norms) >= 5 and norms[-1] > 10 * (sum(norms[:-1]) / len(norms[:-1]) + 1e-9):
+            out.append({"rule": "grad_spike", "text": f"gradient norm {norms[-1]:.2f} is more than 10x its recent mean"})
+    gs = store.tail("gpus", 64)
+    low = [g for g in gs if g.get("sm_mhz") and g.get("util", 0) > 80 and g["sm_mhz"] < 1000]
+    if low:
+        out.append({"rule": "low_clocks", "text": f"GPU {low[-1]['gpu']} runs at {low[-1]['sm_mhz']} MHz under load"})
+    return out
