@@ -1,0 +1,44 @@
+"""Submission pacing (group vs sample back-fill) and the true-on-policy contract report."""
+import asyncio
+
+from miles_b200.models import get_config
+from miles_b200.rollout.submission import SubmissionPacer
+from miles_b200.true_on_policy import check, explain
+
+
+def test_group_pacing_counts_groups():
+    p = SubmissionPacer("group", 4)
+    assert p.may_submit(pending_groups=1, group_budget=2) and not p.may_submit(2, 2)
+
+
+def test_sample_backfill_admits_a_group_once_enough_samples_finished():
+    async def run():
+        p = SubmissionPacer("sample", group_size=4)
+        p.submitted([[0] * 4, [0] * 4])
+        assert not p.may_submit(pending_groups=2, group_budget=2)  # 8 in flight, budget 8
+        slow = asyncio.ensure_future(asyncio.sleep(10))
+        for _ in range(3):
+            p.sample_finished()
+        assert not p.may_submit(2, 2)  # 5 in flight + 4 > 8
+        asyncio.get_event_loop().call_later(0.01, p.sample_finished)
+        done, rest = await p.wait({slow})
+        assert not done and rest == {slow}  # woken by the sample, not by a group
+        assert p.may_submit(2, 2)  # 4 in flight + 4 <= 8
+        slow.cancel()
+        p.submitted([[0] * 4])
+        assert p.may_submit(pending_groups=0, group_budget=1) and p.samples_in_flight == 0  # stale count dropped
+
+    asyncio.run(run())
+
+
+def test_contract_names_what_breaks_bit_equality():
+    class A:
+        use_rollout_routing_replay = False
+        sglang_quantization = None
+
+    rep = check(A(), get_config("qwen3-30B-A3B"))
+    assert {c.key for c in rep.broken} == {"routing", "attention", "batch_invariance"} and not rep.bitwise_expected
+    A.use_rollout_routing_replay = True
+    assert "routing" in {c.key for c in check(A(), get_config("qwen3-30B-A3B")).satisfied}
+    assert "routing" in {c.key for c in check(A(), get_config("qwen3-4B")).satisfied}
+    assert "broken: attention" in explain(rep)
