@@ -45,18 +45,24 @@ class CIHistoryBackend(JsonlBackend):
 
 
 class DashboardBackend(TrackingBackend):
-    """Hourly-partitioned append-only JSONL store read by the dashboard API."""
+    """Feeds the run dashboard (``miles_b200/dashboard``): step metrics, trajectory life-cycle events and periodic
+    read-only GPU samples go to its partitioned JSONL store."""
     name = "dashboard"
 
     def __init__(self, root: str):
+        from ..dashboard import Collector, EventStore
+        from . import lifecycle
+
         self.root = root
-        os.makedirs(root, exist_ok=True)
+        self.collector = Collector(EventStore(root))
+        lifecycle.add_sink(self.collector.on_lifecycle)
+        self.collector.start()
 
     def log(self, metrics: dict, step: int) -> None:
-        part = time.strftime("%Y%m%d-%H", time.gmtime())
-        with open(os.path.join(self.root, f"metrics-{part}.jsonl"), "a") as f:
-            f.write(json.dumps({"step": step, "ts": time.time(), "metrics": {k: v for k, v in metrics.items()
-                                                                               if isinstance(v, (int, float))}}) + "\n")
+        self.collector.log_metrics(metrics, step)
+
+    def finish(self) -> None:
+        self.collector.stop()
 
 
 class WandbBackend(TrackingBackend):
