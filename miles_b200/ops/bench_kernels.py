@@ -1,0 +1,106 @@
+"""Micro-benchmarks of single kernels (CUDA events, warm-up, L2-exceeding operands), also the small cases that
+profiler captures are taken on.
+
+    python -m miles_b200.ops.bench_kernels gemm --m 8192 --n 8192 --k 8192
+    python -m miles_b200.ops.bench_kernels attn --seqs 4 --len 8192
+    python -m miles_b200.ops.bench_kernels gemv --t 4 --n 49152 --k 2048
+    python -m miles_b200.ops.bench_kernels decode_attn --batch 64 --ctx 1500
+
+Each prints one JSON line with the time per launch and the achieved TFLOP/s or TB/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def _time(fn, iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn", "gemv", "decode_attn"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--t", type=int, default=4)
+    ap.add_argument("--seqs", type=int, default=4)
+    ap.add_argument("--len", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=1500)
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hk", type=int, default=4)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--library", action="store_true", help="also time the library kernel for the same problem")
+    ns = ap.parse_args()
+    from miles_b200.ops import _ext
+
+    C = _ext.load(required=True)
+    dev = "cuda"
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = {"what": ns.what}
+    if ns.what == "gemm":
+        a = torch.randn(ns.m, ns.k, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(ns.n, ns.k, device=dev, dtype=torch.bfloat16)
+        c = torch.empty(ns.m, ns.n, device=dev, dtype=torch.bfloat16)
+        ms = _time(lambda: C.gemm(a, b, c, False, False, False, 0, status), ns.iters)
+        fl = 2.0 * ns.m * ns.n * ns.k
+        out.update(shape=[ns.m, ns.n, ns.k], ms=ms, tflops=fl / ms / 1e9)
+        if ns.library:
+            ml = _time(lambda: torch.matmul(a, b.t(), out=c), ns.iters)
+            out.update(library_ms=ml, library_tflops=fl / ml / 1e9)
+    elif ns.what == "attn":
+        from miles_b200.ops.attention import build_tiles
+
+        lens = [ns.len] * ns.seqs
+        T = sum(lens)
+        qkv = torch.randn(T, ns.hq + 2 * ns.hk, 128, device=dev, dtype=torch.bfloat16)
+        q, k, v = qkv[:, :ns.hq], qkv[:, ns.hq:ns.hq + ns.hk], qkv[:, ns.hq + ns.hk:]
+        tiles = build_tiles(lens).to(dev)
+        ms = _time(lambda: C.flash_attn_fwd(q, k, v, tiles, 128 ** -0.5, status), ns.iters)
+        fl = sum(4.0 * 128 * ns.hq * (n * (n + 1) / 2) for n in lens)
+        out.update(lens=lens, ms=ms, tflops=fl / ms / 1e9)
+        if ns.library:
+            from flash_attn import flash_attn_varlen_func
+
+            cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+            ml = _time(lambda: flash_attn_varlen_func(q, k, v, cu, cu, ns.len, ns.len, softmax_scale=128 ** -0.5, causal=True), ns.iters)
+            out.update(library_ms=ml, library_tflops=fl / ml / 1e9)
+    elif ns.what == "gemv":
+        x = torch.randn(ns.t, ns.k, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(ns.n, ns.k, device=dev, dtype=torch.bfloat16)
+        y = torch.empty(ns.t, ns.n, device=dev, dtype=torch.bfloat16)
+        ms = _time(lambda: C.small_gemv(x, None, 1e-6, w, None, y, status), ns.iters)
+        out.update(shape=[ns.t, ns.n, ns.k], ms=ms, tbps=ns.n * ns.k * 2 / ms / 1e9)
+    else:
+        page, B, ctx = 64, ns.batch, ns.ctx
+        pages_per = (ctx + page - 1) // page
+        slots = B * pages_per * page + page
+        kc = torch.randn(slots, ns.hk, 128, device=dev, dtype=torch.bfloat16)
+        vc = torch.randn(slots, ns.hk, 128, device=dev, dtype=torch.bfloat16)
+        q = torch.randn(B, ns.hq, 128, device=dev, dtype=torch.bfloat16)
+        o = torch.empty_like(q)
+        bt = (1 + torch.arange(B * pages_per, dtype=torch.int32, device=dev)).view(B, pages_per)
+        sl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+        splits = max(1, min(16, (148 * 3) // max(B * ns.hk, 1)))
+        scratch = torch.empty(B * ns.hq * splits * 130, dtype=torch.float32, device=dev)
+        ms = _time(lambda: C.paged_decode_attention(q, kc, vc, bt, sl, o, scratch, page, splits, 128 ** -0.5), ns.iters)
+        out.update(batch=B, ctx=ctx, splits=splits, ms=ms, tbps=2.0 * B * ctx * ns.hk * 128 * 2 / ms / 1e9)
+    out["status"] = int(status.item())
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
