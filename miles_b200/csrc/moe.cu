@@ -506,7 +506,7 @@ void moe_build_permutation(const int* topk_ids, int T, int K, int E, int max_row
                            int* num_m_tiles, cudaStream_t s) {
   const int n = T * K;
   if (n <= 4096 && max_rows <= 16384 && E <= 512) {
-    build_small_kernel<<<1, n <= 1024 ? 256 : 1024, (3 * E + 2 + n) * sizeof(int), s>>>(topk_ids, n, E, max_rows, max_tiles, align, expert_counts,
+    build_small_kernel<<<1, n <= 128 ? 256 : 1024, (3 * E + 2 + n) * sizeof(int), s>>>(topk_ids, n, E, max_rows, max_tiles, align, expert_counts,
                                                                    expert_offsets, dest_row, row_src, tile_group, num_m_tiles);
     return;
   }

@@ -117,4 +117,9 @@ void register_comm(pybind11::module_& m) {
   m.def("ep_return", &ep_return);
   m.def("ep_row_ptrs", &ep_row_ptrs);
   m.def("sum_slots", &sum_slots);
+  // Per-context preference for a large shared-memory carve-out: decode alternates kernels that use ~200 KB of shared
+  // memory with kernels that use none, and without a common preference the SM re-partitions L1 / shared memory in between.
+  m.def("device_prefer_shared_memory", [](bool on) {
+    return static_cast<int>(cudaDeviceSetCacheConfig(on ? cudaFuncCachePreferShared : cudaFuncCachePreferNone));
+  });
 }

@@ -95,8 +95,9 @@ class Engine:
     def __init__(self, model, *, max_running: int = 64, num_pages: Optional[int] = None, page_size: int = 64,
                  max_seq_len: int = 16384, max_prefill_tokens: int = 16384, kv_mem_bytes: Optional[int] = None,
                  use_cuda_graph: Optional[bool] = None, eos_token_id: Optional[int] = None, kv_dtype=None,
-                 sync=None, ep_decode=None, kv_storage: Optional[torch.Tensor] = None):
+                 sync=None, ep_decode=None, kv_storage: Optional[torch.Tensor] = None, overlap_decode: bool = True):
         self.model = model
+        self.overlap_decode = overlap_decode  # keep one decode step in flight while the host reads the previous one
         self.kv_storage = kv_storage  # caller-owned uint8 device buffer to carve the KV cache from (None = allocate)
         self.sync = sync            # lockstep agreement across expert-parallel ranks (None = independent engine)
         self.ep_decode = ep_decode  # small expert-parallel exchange used by decode steps (graph friendly)
@@ -176,11 +177,16 @@ class Engine:
         self.slots_free = list(range(B - 1, -1, -1))
         self.slot_req: list = [None] * B
         pin = self.on_gpu
-        self.h_out = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
-        self.h_lp = torch.zeros(B, dtype=torch.float32, pin_memory=pin)
+        # two generations of result buffers: one decode step may be in flight while the previous one is read
+        self.h_out = torch.zeros(2, B, dtype=torch.int32, pin_memory=pin)
+        self.h_lp = torch.zeros(2, B, dtype=torch.float32, pin_memory=pin)
+        self._h_routes: list = [None, None]
+        self._parity = 0
+        self._pending: Optional[dict] = None
 
     def release_memory_occupation(self, tags: Sequence[str] = ("kv_cache", "cuda_graph")) -> None:
         """Free the KV cache and/or captured graphs (weights are shared with the trainer and stay)."""
+        self._drain_pending()
         assert not self.running, "release_memory_occupation with running requests; pause/abort first"
         if "cuda_graph" in tags:
             self._graphs.clear()
@@ -217,6 +223,7 @@ class Engine:
         return rid
 
     def abort_request(self, rid: Optional[str] = None, abort_all: bool = False) -> int:
+        self._drain_pending()
         n = 0
         for req in list(self.running):
             if abort_all or req.rid == rid:
@@ -233,6 +240,7 @@ class Engine:
     def pause_generation(self, mode: str = "retract") -> None:
         """``abort``: finish everything as aborted; ``retract``: running requests go back to the queue and
         will be re-prefilled (their generated tokens are kept); ``in_place``: keep KV and resume as is."""
+        self._drain_pending()
         self.paused = True
         if mode == "abort":
             self.abort_request(abort_all=True)
@@ -248,7 +256,7 @@ class Engine:
         return self.weight_version
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._pending is not None)
 
     def pop_finished(self) -> list:
         out = list(self.finished.values())
@@ -302,7 +310,7 @@ class Engine:
             return []
         before = set(self.finished)
         admitted = [] if self.paused else self._admit()
-        local = 2 if admitted else (1 if (self.running and not self.paused) else 0)
+        local = 2 if admitted else (1 if ((self.running and not self.paused) or self._pending is not None) else 0)
         mode = self.sync.agree(local) if self.sync is not None else local
         self.last_mode = mode
         if mode == 2:
@@ -380,16 +388,20 @@ class Engine:
             self.running.append(req)
             self._append_token(req, int(tok_l[i]), float(lp_l[i]))
 
-    def _sample(self, logits: torch.Tensor, reqs: list):
-        """Eager sampling for a list of requests (prefill path)."""
+    def _sample(self, logits: torch.Tensor, reqs: list, steps: Optional[list] = None):
+        """Eager sampling for a list of requests (prefill path). ``steps``: per-request sampling step counters (the
+        number of tokens generated so far); decode passes the device-side counters because a look-ahead step runs
+        before the host has appended the previous token."""
         n = len(reqs)
+        if steps is None:
+            steps = [len(r.output_ids) for r in reqs]
         if self.on_gpu and hasattr(self.model, "C"):
             dev = self.dev
             t = torch.tensor([r.params.temperature for r in reqs], dtype=torch.float32, device=dev)
             k = torch.tensor([r.params.top_k if r.params.top_k else 0 for r in reqs], dtype=torch.int32, device=dev)
             p = torch.tensor([r.params.top_p for r in reqs], dtype=torch.float32, device=dev)
             s = torch.tensor([r.seed for r in reqs], dtype=torch.int64, device=dev)
-            st = torch.tensor([len(r.output_ids) for r in reqs], dtype=torch.int32, device=dev)
+            st = torch.tensor(steps, dtype=torch.int32, device=dev)
             out = torch.empty(n, dtype=torch.int32, device=dev)
             lp = torch.empty(n, dtype=torch.float32, device=dev)
             self.model.C.sample_rows(logits, t, k, p, s, st, out, lp)
@@ -399,7 +411,7 @@ class Engine:
 
         toks, lps = [], []
         for i, r in enumerate(reqs):
-            g = torch.Generator(device=logits.device).manual_seed((r.seed * 1000003 + len(r.output_ids)) & 0x7FFFFFFF)
+            g = torch.Generator(device=logits.device).manual_seed((r.seed * 1000003 + int(steps[i])) & 0x7FFFFFFF)
             tk, l = R.sample(logits[i:i + 1], r.params.temperature, r.params.top_k, r.params.top_p, g)
             toks.append(tk)
             lps.append(l)
@@ -468,18 +480,37 @@ class Engine:
         self._rows = list(reqs)
         self._rows_B = B
 
+    # ------------------------------------------------------------------ decode: launch / process, one step in flight
+    def _grow_pages_ahead(self, lookahead: int) -> bool:
+        """Pages for ``lookahead`` more positions of every running request, without retracting anybody.
+        False if the pool cannot provide them (pages obtained so far stay with their requests)."""
+        for req in self.running:
+            need = self._pages_needed(req.seq_len + lookahead)
+            while len(req.pages) < need:
+                pg = self.pool.alloc(1)
+                if pg is None:
+                    return False
+                req.pages.extend(pg)
+        return True
+
     @torch.no_grad()
-    def _decode(self) -> None:
-        ps = self.page_size
+    def _launch_decode(self, lookahead: int) -> Optional[dict]:
+        """Enqueue one decode step for the running set and the copies of its results into pinned host buffers.
+        ``lookahead = 1``: the step *after* the one still in flight (same batch, device-side state already advances
+        inside the captured step), launched before the host has looked at the previous step's tokens."""
         before_pages = {r.rid: len(r.pages) for r in self.running}
-        self._grow_pages()
+        if lookahead == 0:
+            self._grow_pages()
+        elif not self._grow_pages_ahead(lookahead):
+            return None
         reqs = list(self.running) if not self.paused else []
         if not reqs and self.sync is None:
-            return
+            return None
         n = len(reqs)
         B = self._bucket(max(n, 1))
         same = (self._rows_B == B and len(self._rows) == n and all(a is b for a, b in zip(self._rows, reqs)))
         if not same:
+            assert lookahead == 0, "a look-ahead step never changes the batch"
             self._upload_rows(reqs, B)
         else:
             for i, r in enumerate(reqs):  # pages appended since the last step
@@ -495,22 +526,77 @@ class Engine:
             if self.ep_decode is not None:
                 self.model.ep = saved_ep
         if n == 0:
-            return
+            return None
+        par = self._parity
+        self._parity ^= 1
+        pend = {"reqs": reqs, "n": n, "parity": par, "event": None, "routes": None}
         if self.on_gpu:
-            self.h_out[:n].copy_(self.d_out_tokens[:n], non_blocking=True)
-            self.h_lp[:n].copy_(self.d_out_logprobs[:n], non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            tok_l, lp_l = self.h_out[:n].tolist(), self.h_lp[:n].tolist()
+            self.h_out[par, :n].copy_(self.d_out_tokens[:n], non_blocking=True)
+            self.h_lp[par, :n].copy_(self.d_out_logprobs[:n], non_blocking=True)
+            if routes is not None:
+                hr = self._h_routes[par]
+                if hr is None or hr.shape[0] < n or hr.shape[1:] != routes.shape[1:]:
+                    hr = torch.empty((self.max_running,) + tuple(routes.shape[1:]), dtype=routes.dtype, pin_memory=True)
+                    self._h_routes[par] = hr
+                hr[:n].copy_(routes[:n], non_blocking=True)
+                pend["routes"] = hr
+            ev = torch.cuda.Event()
+            ev.record()
+            pend["event"] = ev
         else:
-            tok_l, lp_l = self.d_out_tokens[:n].tolist(), self.d_out_logprobs[:n].tolist()
-        routes_c = routes[:n].cpu() if routes is not None else None
-        self.d2h_bytes += 8 * n + (routes_c.numel() * 4 if routes_c is not None else 0)
-        self.stats["decode_tokens"] += n
+            self.h_out[par, :n] = self.d_out_tokens[:n]
+            self.h_lp[par, :n] = self.d_out_logprobs[:n]
+            pend["routes"] = routes[:n].clone() if routes is not None else None
+        return pend
+
+    def _process_decode(self, pend: dict) -> None:
+        """Read one step's sampled tokens on the host and advance the requests (a request that finished, was
+        retracted or aborted after the step was launched ignores its row)."""
+        if pend["event"] is not None:
+            pend["event"].synchronize()
+        n, par = pend["n"], pend["parity"]
+        tok_l, lp_l = self.h_out[par, :n].tolist(), self.h_lp[par, :n].tolist()
+        routes_c = pend["routes"]
+        self.d2h_bytes += 8 * n + (routes_c[:n].numel() * 4 if routes_c is not None else 0)
         self.stats["decode_steps"] += 1
-        for i, r in enumerate(reqs):
+        for i, r in enumerate(pend["reqs"]):
+            if r.finish_reason is not None or r.slot < 0:
+                continue
             if routes_c is not None and r.return_routed_experts:
-                r.routed_experts.append(routes_c[i:i + 1])
+                r.routed_experts.append(routes_c[i:i + 1].clone())
+            self.stats["decode_tokens"] += 1
             self._append_token(r, int(tok_l[i]), float(lp_l[i]))
+
+    def _can_look_ahead(self, pend: dict) -> bool:
+        if not self.overlap_decode or self.sync is not None or self.paused or self.waiting:
+            return False
+        reqs = pend["reqs"]
+        if len(reqs) != len(self.running) or any(a is not b for a, b in zip(reqs, self.running)):
+            return False
+        for r in reqs:  # a request that is certain to stop at the step in flight ends the speculation
+            p = r.params
+            limit = p.max_new_tokens if p.forced_length is None else min(p.forced_length, p.max_new_tokens)
+            if len(r.output_ids) + 1 >= limit or r.seq_len + 2 >= self.max_seq_len:
+                return False
+        return True
+
+    def _drain_pending(self) -> None:
+        if self._pending is not None:
+            pend, self._pending = self._pending, None
+            self._process_decode(pend)
+
+    @torch.no_grad()
+    def _decode(self) -> None:
+        """One decode step becomes visible to the host per call, while the next one is already running: the host
+        work between steps (reading tokens, stop checks, page bookkeeping) no longer leaves the GPU idle."""
+        pend, self._pending = self._pending, None
+        if pend is None:
+            pend = self._launch_decode(0)
+            if pend is None:
+                return
+        nxt = self._launch_decode(1) if self._can_look_ahead(pend) else None
+        self._process_decode(pend)
+        self._pending = nxt
 
     def _decode_body(self, B: int, want_routes: bool):
         ps = self.page_size
@@ -527,7 +613,7 @@ class Engine:
             self.model.launches += 1
         else:
             reqs = list(self._rows)
-            tok, lp = self._sample(logits[:len(reqs)], reqs)
+            tok, lp = self._sample(logits[:len(reqs)], reqs, steps=self.d_step[:len(reqs)].tolist())
             self.d_out_tokens[:len(reqs)] = tok.to(torch.int32)
             self.d_out_logprobs[:len(reqs)] = lp
         # advance the device-side state so that the next step needs no host upload

@@ -135,3 +135,23 @@ def test_async_client_routes_to_least_loaded_engine_and_returns_routing():
     assert engines[0].stats["prefill_tokens"] > 0 and engines[1].stats["prefill_tokens"] > 0
     re = decode_routed_experts(outs[1]["meta_info"])
     assert re.shape == (9 + 5 - 1, 2, cfg.moe_top_k) and re.min() >= 0 and re.max() < cfg.num_experts
+
+
+def test_overlapped_decode_matches_step_by_step_and_handles_unforeseen_stops():
+    """One decode step in flight while the host reads the previous one: same tokens as the strictly sequential
+    engine, also when a stop token ends a request after the next step was already launched."""
+    cfg, m, seq = _engine(overlap_decode=False)
+    _, _, ovl = _engine(overlap_decode=True)
+    prompts = _prompts(cfg, [9, 21, 5, 14], seed=4)
+    base = seq.generate(prompts, SamplingParams(max_new_tokens=20, sampling_seed=5))
+    # pick a token that some request produces mid-way and make it a stop token
+    stop = base[1]["output_ids"][7]
+    sp = SamplingParams(max_new_tokens=20, sampling_seed=5, stop_token_ids=[stop])
+    steps0 = seq.stats["decode_steps"]
+    a = seq.generate(prompts, sp)
+    b = ovl.generate(prompts, sp)
+    assert [r["output_ids"] for r in a] == [r["output_ids"] for r in b]
+    assert [r["meta_info"]["finish_reason"]["type"] for r in a] == [r["meta_info"]["finish_reason"]["type"] for r in b]
+    assert any(r["meta_info"]["finish_reason"]["type"] == "stop" for r in b)
+    assert ovl._pending is None and not ovl.running and ovl.pool.num_free == ovl.num_pages - 1
+    assert ovl.stats["decode_steps"] >= seq.stats["decode_steps"] - steps0  # speculated steps whose rows were dropped count too
