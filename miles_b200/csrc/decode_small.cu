@@ -163,6 +163,80 @@ __global__ void __launch_bounds__(1024) small_gemv_kernel(const bf16* __restrict
 }
 
 
+// ---------------------------------------------------------------------------------------------- small_gemv, 9..64 tokens
+// Same scheme with G groups of 8 token columns: the weight fragments of a chunk are loaded once and multiplied with
+// every group (G MMAs per fragment pair), the activations come from L1/L2. Used for the dense projections of decode
+// steps with up to 64 rows, where a 128-row tcgen05 tile is mostly padding and its fixed cost (tensor-map prefetch,
+// TMEM allocation, pipeline fill) is a multiple of the 3-6 us the weights take to stream.
+template <int G>
+__global__ void __launch_bounds__(256) small_gemv_multi_kernel(const bf16* __restrict__ x, int T, const bf16* __restrict__ W,
+                                                               int N, int K, const bf16* __restrict__ residual,
+                                                               void* __restrict__ out, int out_fp32) {
+  __shared__ float red[8][16][TOK * G];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int r = lane >> 2, c = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  int k_begin, k_end;
+  k_range(K, warp, nwarps, k_begin, k_end);
+  float acc[G][4];
+#pragma unroll
+  for (int g = 0; g < G; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+  const bf16* w0 = W + static_cast<long long>(n0 + r) * K;
+  const bf16* w1 = W + static_cast<long long>(n0 + r + 8) * K;
+  constexpr int UNROLL = 4;
+  int k = k_begin + c * 8;
+  for (; k + (UNROLL - 1) * 32 < k_end; k += UNROLL * 32) {
+    uint4 a0[UNROLL], a1[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      a0[u] = ldg16_stream(w0 + k + u * 32);
+      a1[u] = ldg16_stream(w1 + k + u * 32);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const int t = g * TOK + r;
+        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+        if (t < T) xv = ldg16(x + static_cast<long long>(t) * K + k + u * 32);
+        mma16816(acc[g], a0[u].x, a1[u].x, a0[u].y, a1[u].y, xv.x, xv.y);
+        mma16816(acc[g], a0[u].z, a1[u].z, a0[u].w, a1[u].w, xv.z, xv.w);
+      }
+    }
+  }
+  for (; k < k_end; k += 32) {
+    const uint4 a0 = ldg16_stream(w0 + k), a1 = ldg16_stream(w1 + k);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int t = g * TOK + r;
+      uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+      if (t < T) xv = ldg16(x + static_cast<long long>(t) * K + k);
+      mma16816(acc[g], a0.x, a1.x, a0.y, a1.y, xv.x, xv.y);
+      mma16816(acc[g], a0.z, a1.z, a0.w, a1.w, xv.z, xv.w);
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    red[warp][r][g * TOK + 2 * c] = acc[g][0];
+    red[warp][r][g * TOK + 2 * c + 1] = acc[g][1];
+    red[warp][r + 8][g * TOK + 2 * c] = acc[g][2];
+    red[warp][r + 8][g * TOK + 2 * c + 1] = acc[g][3];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 16 * TOK * G; i += blockDim.x) {
+    const int row = i / (TOK * G), t = i - row * (TOK * G);
+    if (t >= T) continue;
+    float v = 0.f;
+    for (int w = 0; w < nwarps; ++w) v += red[w][row][t];
+    const long long o = static_cast<long long>(t) * N + n0 + row;
+    if (residual) v += __bfloat162float(residual[o]);
+    if (out_fp32)
+      static_cast<float*>(out)[o] = v;
+    else
+      static_cast<bf16*>(out)[o] = __float2bfloat16(v);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- router_small
 // One CTA of 8 warps over the fp32 router logits [T, E] (a small_gemv with the norm folded in produces them).
 // Outputs: topk_ids[T,K], topk_w[T,K], and for the MoE kernels the compact list of active experts with, per
@@ -245,6 +319,18 @@ __global__ void __launch_bounds__(256) router_small_kernel(const float* __restri
 
 void small_gemv_direct(const void* x, int T, const void* norm_w, float eps, const void* W, int N, int K,
                        const void* residual, void* out, bool out_fp32, cudaStream_t s) {
+  if (T > TOK) {  // 9..64 rows: token groups (no folded norm on this path)
+    int warps = (K + 255) / 256;
+    warps = warps < 4 ? 4 : (warps > 8 ? 8 : warps);
+    const bf16* xb = static_cast<const bf16*>(x);
+    const bf16* wb = static_cast<const bf16*>(W);
+    const bf16* rb = static_cast<const bf16*>(residual);
+    const int f32 = out_fp32 ? 1 : 0;
+    if (T <= 16) small_gemv_multi_kernel<2><<<N / 16, 32 * warps, 0, s>>>(xb, T, wb, N, K, rb, out, f32);
+    else if (T <= 32) small_gemv_multi_kernel<4><<<N / 16, 32 * warps, 0, s>>>(xb, T, wb, N, K, rb, out, f32);
+    else small_gemv_multi_kernel<8><<<N / 16, 32 * warps, 0, s>>>(xb, T, wb, N, K, rb, out, f32);
+    return;
+  }
   const int threads = 32 * (warps_for(K) < 4 ? 4 : warps_for(K));  // the epilogue needs 128 threads
   if (norm_w)
     small_gemv_kernel<true><<<N / 16, threads, 0, s>>>(static_cast<const bf16*>(x), T, static_cast<const bf16*>(norm_w),

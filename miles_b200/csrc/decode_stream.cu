@@ -383,7 +383,7 @@ void small_gemv(const void* x, int T, const void* norm_w, float eps, const void*
   a.out_fp32 = out_fp32 ? 1 : 0;
   a.residual = static_cast<const bf16*>(residual);
   a.status = status;
-  if (static_cast<long long>(N) * K * 2 < (48ll << 20)) {  // small matrix: the direct kernel starts faster
+  if (T > TOK || static_cast<long long>(N) * K * 2 < (48ll << 20)) {  // small matrix or 9..64 rows: the direct kernels
     small_gemv_direct(x, T, norm_w, eps, W, N, K, residual, out, out_fp32, s);
     return;
   }

@@ -79,7 +79,8 @@ void small_gemv(const at::Tensor& x, const c10::optional<at::Tensor>& norm_w, do
                 const c10::optional<at::Tensor>& residual, at::Tensor& out, const c10::optional<at::Tensor>& status) {
   CHECK_BF16(x); CHECK_BF16(W);
   const int T = x.size(0), K = x.size(1), N = W.size(0);
-  TORCH_CHECK(T >= 1 && T <= 8 && W.size(1) == K && K % 32 == 0 && N % 16 == 0, "small_gemv: need 1 <= T <= 8, K % 32 == 0, N % 16 == 0");
+  TORCH_CHECK(T >= 1 && T <= 64 && W.size(1) == K && K % 32 == 0 && N % 16 == 0, "small_gemv: need 1 <= T <= 64, K % 32 == 0, N % 16 == 0");
+  TORCH_CHECK(T <= 8 || !norm_w.has_value(), "small_gemv: the folded RMSNorm is available for at most 8 rows");
   TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.size(0) == T && out.size(1) == N, "small_gemv: bad output shape");
   const bool f32 = out.scalar_type() == at::kFloat;
   TORCH_CHECK(f32 || out.scalar_type() == at::kBFloat16, "small_gemv: output must be fp32 or bf16");

@@ -232,3 +232,22 @@ def test_small_decode_kernels_vs_fp32(ext, T):
     a = (torch.nn.functional.silu(act[:, :I].float()) * act[:, I:].float()).to(torch.bfloat16)
     ref_y = torch.einsum("pi,phi->ph", a.float(), W2[flat].float())
     assert _rel(yp, ref_y) < 1e-2
+
+
+@pytest.mark.parametrize("T", [9, 16, 33, 64])
+def test_small_gemv_token_groups_vs_fp32(ext, T):
+    """Dense projections of decode steps with 9..64 rows: token groups of 8 share the weight fragments."""
+    torch.manual_seed(20 + T)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for N, K in ((5120, 2048), (2048, 4096), (128, 2048)):
+        x = torch.randn(T, K, device=DEV, dtype=torch.bfloat16)
+        W = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.03
+        res = torch.randn(T, N, device=DEV, dtype=torch.bfloat16)
+        ref = x.float() @ W.float().t()
+        out = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+        ext.small_gemv(x, None, 0.0, W, None, out, status)
+        assert _rel(out, ref) < 1e-2
+        out32 = torch.empty(T, N, device=DEV, dtype=torch.float32)
+        ext.small_gemv(x, None, 0.0, W, res, out32, status)
+        assert _rel(out32, ref + res.float()) < 2e-3
+    assert status.item() == 0
