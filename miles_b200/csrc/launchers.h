@@ -138,6 +138,22 @@ void ep_row_ptrs(const int* row_src, const int* meta, const EpPeers& peers, int 
                  unsigned long long* out, cudaStream_t s);
 void ep_return(const void* yp, const int* recv_dest_row, const int* meta, const int* counts, const EpPeers& peers, int me,
                int nranks, int cap, int H, unsigned long long* ctrl, int* status, cudaStream_t s);
+
+// ---- dp_adam.cu (gradient reduce-scatter + partitioned Adam + parameter all-gather over peer memory)
+struct DpPeers {
+  void* grad[kMaxPeers];                  // fp32 flat gradient buffers of all data-parallel ranks
+  void* param[kMaxPeers];                 // bf16 flat parameter buffers
+  unsigned long long* flags[kMaxPeers];   // [nranks] "gradients final" epochs
+  unsigned long long* flags2[kMaxPeers];  // [nranks] "parameters pushed" epochs
+};
+void peer_signal(const DpPeers& peers, int me, int nranks, unsigned long long* ctrl, int which, bool second, cudaStream_t s);
+int dp_reduce_shard_blocks(long long shard_elems);
+void dp_reduce_shard(const DpPeers& peers, int nranks, long long lo, long long shard_elems, float* reduced, float* partial,
+                     cudaStream_t s);
+void dp_adam_push(const DpPeers& peers, int me, int nranks, long long lo, long long n, const float* reduced, float* master,
+                  void* m, void* v, bool mv_bf16, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                  const float* grad_scale, const float* skip_flag, cudaStream_t s);
+
 int symm_alloc(size_t nbytes, void** ptr, char* handle64);
 int symm_open(const char* handle64, void** ptr);
 int symm_close(void* ptr);

@@ -1,4 +1,5 @@
 // Bindings of the symmetric-memory allocator and the expert-parallel exchange kernels.
+#include <cmath>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
@@ -104,6 +105,55 @@ void sum_slots(const at::Tensor& slots, const c10::optional<at::Tensor>& residua
                 out.data_ptr(), out.numel(), cur_stream());
 }
 
+mb::DpPeers make_dp_peers(const std::vector<int64_t>& grad, const std::vector<int64_t>& param, const std::vector<int64_t>& flags,
+                          const std::vector<int64_t>& flags2) {
+  mb::DpPeers p{};
+  TORCH_CHECK(grad.size() <= mb::kMaxPeers && grad.size() == param.size(), "at most ", mb::kMaxPeers, " data-parallel ranks");
+  for (size_t i = 0; i < grad.size(); ++i) {
+    p.grad[i] = reinterpret_cast<void*>(grad[i]);
+    p.param[i] = reinterpret_cast<void*>(param[i]);
+    p.flags[i] = reinterpret_cast<unsigned long long*>(flags[i]);
+    p.flags2[i] = reinterpret_cast<unsigned long long*>(flags2[i]);
+  }
+  return p;
+}
+
+void peer_signal(const std::vector<int64_t>& grad, const std::vector<int64_t>& param, const std::vector<int64_t>& flags,
+                 const std::vector<int64_t>& flags2, int64_t me, at::Tensor& ctrl, int64_t which, bool second) {
+  const c10::cuda::CUDAGuard guard(ctrl.device());
+  mb::peer_signal(make_dp_peers(grad, param, flags, flags2), me, grad.size(),
+                  reinterpret_cast<unsigned long long*>(ctrl.data_ptr<int64_t>()), which, second, cur_stream());
+}
+
+// reduced: fp32 [shard]; returns the per-block partial sums of squares (add them up in order for a reproducible norm)
+at::Tensor dp_reduce_shard(const std::vector<int64_t>& grad, const std::vector<int64_t>& param, const std::vector<int64_t>& flags,
+                           const std::vector<int64_t>& flags2, int64_t lo, at::Tensor& reduced) {
+  TORCH_CHECK(reduced.is_cuda() && reduced.scalar_type() == at::kFloat && reduced.is_contiguous(), "bad reduced buffer");
+  TORCH_CHECK(lo % 8 == 0 && reduced.numel() % 8 == 0, "shard bounds must be multiples of 8 elements");
+  const c10::cuda::CUDAGuard guard(reduced.device());
+  const int blocks = mb::dp_reduce_shard_blocks(reduced.numel());
+  at::Tensor partial = at::zeros({blocks}, reduced.options());
+  mb::dp_reduce_shard(make_dp_peers(grad, param, flags, flags2), grad.size(), lo, reduced.numel(), reduced.data_ptr<float>(),
+                      partial.data_ptr<float>(), cur_stream());
+  return partial;
+}
+
+void dp_adam_push(const std::vector<int64_t>& grad, const std::vector<int64_t>& param, const std::vector<int64_t>& flags,
+                  const std::vector<int64_t>& flags2, int64_t me, int64_t lo, const at::Tensor& reduced,
+                  const c10::optional<at::Tensor>& master, at::Tensor& m, at::Tensor& v, double lr, double b1, double b2, double eps,
+                  double wd, int64_t step, const at::Tensor& grad_scale, const at::Tensor& skip_flag) {
+  const int64_t n = reduced.numel();
+  TORCH_CHECK(lo % 8 == 0 && n % 8 == 0 && m.numel() == n && v.numel() == n, "piece bounds must be multiples of 8 elements");
+  TORCH_CHECK(m.scalar_type() == v.scalar_type() && (m.scalar_type() == at::kFloat || m.scalar_type() == at::kBFloat16), "bad moment dtype");
+  const c10::cuda::CUDAGuard guard(reduced.device());
+  const float bc1 = 1.0f - static_cast<float>(std::pow(b1, static_cast<double>(step)));
+  const float bc2 = 1.0f - static_cast<float>(std::pow(b2, static_cast<double>(step)));
+  mb::dp_adam_push(make_dp_peers(grad, param, flags, flags2), me, grad.size(), lo, n, reduced.data_ptr<float>(),
+                   master.has_value() ? master->data_ptr<float>() : nullptr, m.data_ptr(), v.data_ptr(),
+                   m.scalar_type() == at::kBFloat16, lr, b1, b2, eps, wd, bc1, bc2, grad_scale.data_ptr<float>(),
+                   skip_flag.data_ptr<float>(), cur_stream());
+}
+
 }  // namespace
 
 void register_comm(pybind11::module_& m) {
@@ -117,6 +167,9 @@ void register_comm(pybind11::module_& m) {
   m.def("ep_return", &ep_return);
   m.def("ep_row_ptrs", &ep_row_ptrs);
   m.def("sum_slots", &sum_slots);
+  m.def("peer_signal", &peer_signal);
+  m.def("dp_reduce_shard", &dp_reduce_shard);
+  m.def("dp_adam_push", &dp_adam_push);
   // Per-context preference for a large shared-memory carve-out: decode alternates kernels that use ~200 KB of shared
   // memory with kernels that use none, and without a common preference the SM re-partitions L1 / shared memory in between.
   m.def("device_prefer_shared_memory", [](bool on) {

@@ -239,6 +239,10 @@ class ParamStore:
         the caller owns — the colocated loop lends the same bytes to the KV cache between training steps."""
         for g, n in self.sizes.items():
             dt = expert_dtype if (g == "expert" and expert_dtype is not None) else dtype
+            pinned = getattr(self, "_pinned_grads", {}).get(g)
+            if pinned is not None:
+                self.grad[g] = pinned
+                continue
             if g == "expert" and expert_storage is not None and n > 0:
                 nbytes = n * torch.empty((), dtype=dt).element_size()
                 assert expert_storage.dtype == torch.uint8 and expert_storage.numel() >= nbytes
@@ -251,6 +255,28 @@ class ParamStore:
         self.grads.clear()
         for s in self.specs:
             self.grads[s.name] = self.grad[s.group][s.offset:s.offset + s.numel].view(s.shape)
+
+    def rebind_flat(self, group: str, tensor: torch.Tensor) -> None:
+        """Move a flat parameter buffer to caller-provided storage (same size and dtype, contents already copied):
+        every named parameter of the group becomes a view of the new buffer."""
+        assert tensor.numel() == self.flat[group].numel() and tensor.dtype == self.flat[group].dtype
+        self.flat[group] = tensor
+        for s in self.specs:
+            if s.group == group:
+                self.params[s.name] = tensor[s.offset:s.offset + s.numel].view(s.shape)
+
+    def pin_grad_storage(self, group: str, tensor: torch.Tensor) -> None:
+        """Keep the group's gradients in caller-provided storage from now on (survives free / allocate cycles)."""
+        assert tensor.numel() == self.sizes[group]
+        if not hasattr(self, "_pinned_grads"):
+            self._pinned_grads = {}
+        self._pinned_grads[group] = tensor
+        had = bool(self.grads)
+        self.grad[group] = tensor
+        if had:
+            for s in self.specs:
+                if s.group == group:
+                    self.grads[s.name] = tensor[s.offset:s.offset + s.numel].view(s.shape)
 
     def zero_grads(self) -> None:
         for g in self.grad.values():

@@ -156,8 +156,16 @@ class TrainActor:
                          master_weights=plan["master"], offload_states=plan["offload"], lr_decay_style=a.lr_decay_style,
                          lr_warmup_iters=a.lr_warmup_iters or 0, lr_decay_iters=a.lr_decay_iters or 0, min_lr=a.min_lr,
                          lr_wsd_decay_iters=a.lr_wsd_decay_iters or 0)
+        dense_shard = None
+        if (self.on_gpu and self.ps.dp_cp.size > 1 and self.ps.tp.size == 1 and self.store.dtype == torch.bfloat16
+                and getattr(a, "fused_comm", True) and getattr(a, "use_distributed_optimizer", True) and self.ps.dp_cp.size <= 8):
+            from ..parallel.dp_optimizer import ShardedDenseAdam
+
+            # replicated parameters: reduce-scatter + Adam on the owned range + all-gather as peer-memory kernels
+            dense_shard = ShardedDenseAdam(self.store, self.ps.dp_cp.group, self.ps.dp_cp.rank, self.ps.dp_cp.size, self.device, oc)
+        self.dense_shard = dense_shard
         self.opt = FlatAdam(self.store, oc, dp_group=self.ps.dp_cp.group, ep_group=self.ps.ep.group,
-                            tp_group=self.ps.tp.group if self.ps.tp.size > 1 else None)
+                            tp_group=self.ps.tp.group if self.ps.tp.size > 1 else None, dense_shard=dense_shard)
 
     # ------------------------------------------------------------------ weight tags (ref / old_actor / teacher)
     def backup_weights(self, tag: str) -> None:
@@ -391,8 +399,8 @@ class TrainActor:
                 for n, row in zip(names, buf):
                     self.store.grads[n].copy_(row)
         g = self.store.grad
-        if self.ps.dp_cp.size > 1 and g["dense"] is not None and g["dense"].numel():
-            dist.all_reduce(g["dense"], group=self.ps.dp_cp.group)
+        if self.ps.dp_cp.size > 1 and g["dense"] is not None and g["dense"].numel() and getattr(self, "dense_shard", None) is None:
+            dist.all_reduce(g["dense"], group=self.ps.dp_cp.group)  # with the partitioned optimizer the step itself reduces
         if self.ps.expert_dp.size > 1 and g["expert"] is not None and g["expert"].numel():
             dist.all_reduce(g["expert"], group=self.ps.expert_dp.group)
 

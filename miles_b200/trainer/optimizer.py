@@ -66,7 +66,7 @@ def lr_at(cfg: OptimConfig, step: int) -> float:
 
 
 class FlatAdam:
-    def __init__(self, store: ParamStore, cfg: OptimConfig, dp_group=None, ep_group=None, tp_group=None):
+    def __init__(self, store: ParamStore, cfg: OptimConfig, dp_group=None, ep_group=None, tp_group=None, dense_shard=None):
         self.store, self.cfg = store, cfg
         self.dp_group, self.ep_group = dp_group, ep_group
         self.tp_group = tp_group  # tensor-parallel shards count once each in the global gradient norm
@@ -80,9 +80,16 @@ class FlatAdam:
             self.C = _ext.load(required=True)
         self.launches = 0
         self.state: dict = {}
+        # replicated parameters partitioned over the data-parallel ranks (parallel/dp_optimizer.py): this rank holds
+        # states for its range only and the step runs as peer-memory kernels instead of all-reduce + replicated Adam
+        self.dense_shard = dense_shard
         for g, flat in store.flat.items():
             n = flat.numel()
             if n == 0:
+                continue
+            if g == "dense" and dense_shard is not None:
+                self.state[g] = {"offload": False, "sharded": True, "m": dense_shard.m, "v": dense_shard.v,
+                                 "master": dense_shard.master}
                 continue
             off = cfg.offload_states and g == "expert" and self.on_gpu
             st: dict = {"offload": off}
@@ -127,6 +134,12 @@ class FlatAdam:
         self.norm_buf.zero_()
         for i, g in enumerate(("dense", "expert")):
             gr = self.store.grad.get(g)
+            if g == "dense" and self.dense_shard is not None:
+                ss = self.dense_shard.reduce().reshape(1)  # the reduce-scatter; the shards' sums of squares add up
+                dist.all_reduce(ss, group=self.dp_group)
+                self.norm_buf[0:1] = ss
+                self.launches += 3
+                continue
             if gr is not None and gr.numel():
                 self._sumsq(gr, self.norm_buf[i:i + 1])
         if self.ep_group is not None and dist.is_initialized() and dist.get_world_size(self.ep_group) > 1:
@@ -189,6 +202,10 @@ class FlatAdam:
             flat, grad = self.store.flat[g], self.store.grad[g]
             if st["offload"]:
                 self._step_offloaded(g, st, flat, grad, lr)
+                continue
+            if st.get("sharded"):
+                self.dense_shard.apply(self.segments[g], lr, self.step_count, self.grad_scale, self.skip_flag)
+                self.launches += len(self.segments[g]) + 2
                 continue
             for a, b, wd in self.segments[g]:
                 b = min(b, flat.numel())
@@ -277,5 +294,7 @@ class FlatAdam:
 
     def sync_master_from_params(self) -> None:
         for g, st in self.state.items():
-            if st.get("master") is not None:
+            if st.get("sharded"):
+                self.dense_shard.sync_master_from_params()
+            elif st.get("master") is not None:
                 st["master"].copy_(self.store.flat[g].float())
