@@ -77,8 +77,9 @@ class B200Qwen3:
     def linear(self, x, w, out_dtype=torch.bfloat16):
         out = torch.empty(x.shape[0], w.shape[0], dtype=out_dtype, device=x.device)
         T, (N, K) = x.shape[0], w.shape
-        if T <= 64 and self.small_decode and N % 16 == 0 and K % 32 == 0 and N * K * 2 < (48 << 20) and x.is_contiguous():
+        if T <= 32 and self.small_decode and N % 16 == 0 and K % 32 == 0 and N * K * 2 < (48 << 20) and x.is_contiguous():
             # a few rows against a small weight matrix (decode projections): the weight-streaming mma.sync kernel
+            # (measured: faster than the narrow tcgen05 tiles up to 32 rows, slower at 64)
             self.C.small_gemv(x, None, 0.0, w, None, out, self.status)
             self.launches += 1
             return out
