@@ -305,6 +305,13 @@ class TrainActor:
         a = self.args
         T = Timer()
         t_start = time.perf_counter()
+        dump = getattr(a, "save_debug_train_data", None)
+        if dump:
+            # per-step training inputs of this rank, for replay with --load-debug-rollout-data style tooling
+            path = dump.format(rollout_id=rollout_id, rank=self.ps.rank)
+            os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+            torch.save({"rollout_id": rollout_id, "rank": self.ps.rank,
+                        "data": {k: v for k, v in data.items() if isinstance(v, (list, tuple, int, float, str, torch.Tensor))}}, path)
         with T.context("data_preprocess"):
             mbs = self._stage(data)
         n_tokens_local = sum(mb.num_tokens for mb in mbs)
