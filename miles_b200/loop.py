@@ -106,23 +106,59 @@ class RLLoop:
                 lend = g.numel() * g.element_size()
             room = free_now + lend - total // 8
             kv_bytes = max(min(budget, want, room), per_tok * page * 4)
+        replicate = self.actor.ep_dispatcher is not None and self._replicate_experts_fits(kv_bytes)
+        if replicate:
+            kv_bytes = max(min(kv_bytes, room - self._replica_bytes()), per_tok * page * 4)
         kv_storage = None
         if self.actor.on_gpu and getattr(a, "share_kv_grad_memory", True) and not getattr(a, "debug_rollout_only", False):
             # rollout and training alternate in this loop: the KV cache borrows the bytes of the expert gradients
             kv_storage = self.actor.lend_arena(kv_bytes)
         sync = ep_decode = None
-        if self.actor.ep_dispatcher is not None:
+        engine_model = self.actor.model
+        self.rollout_store = None
+        if replicate:
+            # Rollout on a full replica of the experts: decode is bound by the weights it streams, not by capacity,
+            # and a B200 holds all experts of this model many times over. Every rank then generates independently
+            # with the single-GPU kernels (no dispatch / return per layer, no lockstep dummy steps); training stays
+            # expert parallel, and the weight update all-gathers the updated expert shares into the replica.
+            from .models import ParamStore, build_model
+
+            self.rollout_store = ParamStore(cfg, self.actor.device, self.actor.store.dtype, ep_size=1, init=False,
+                                            share_dense=self.actor.store)
+            engine_model = build_model(cfg, self.rollout_store, "b200")
+        elif self.actor.ep_dispatcher is not None:
             from .engine.core import LockstepSync
             from .parallel.expert_parallel import ExpertParallel
 
             sync = LockstepSync(self.ps.gloo_world if self.ps.backend != "gloo" else None)
             ep_decode = ExpertParallel(cfg, self.ps, fused=getattr(a, "fused_comm", True), max_tokens=max(max_running, 16))
-        self.engine = Engine(self.actor.model, sync=sync, ep_decode=ep_decode, max_running=max_running, page_size=page, max_seq_len=max_ctx,
+        self.engine = Engine(engine_model, sync=sync, ep_decode=ep_decode, max_running=max_running, page_size=page, max_seq_len=max_ctx,
                              max_prefill_tokens=getattr(a, "engine_max_prefill_tokens", 16384), kv_mem_bytes=kv_bytes,
                              use_cuda_graph=not getattr(a, "sglang_disable_cuda_graph", False) and self.actor.on_gpu,
                              eos_token_id=getattr(self.tokenizer, "eos_token_id", None), kv_storage=kv_storage)
         self.client = EngineClient([self.engine], self.tokenizer)
         self.actor.connect_rollout_engines([self.engine])
+
+    def _replica_bytes(self) -> int:
+        cfg = self.actor.cfg
+        moe_layers = sum(cfg.layer_is_moe(i) for i in range(cfg.num_layers))
+        return moe_layers * cfg.num_experts * 3 * cfg.hidden_size * cfg.moe_ffn_hidden_size * 2
+
+    def _replicate_experts_fits(self, kv_bytes) -> bool:
+        """A full copy of the experts for the rollout engine, if asked for (default) and if it fits next to the
+        trainer's state, the KV cache and an activation reserve."""
+        a = self.args
+        if not self.actor.on_gpu or getattr(a, "rollout_replicate_experts", True) is False or self.ps.tp.size > 1:
+            return False
+        replica = self._replica_bytes()
+        free_now, total = torch.cuda.mem_get_info(self.actor.device)
+        g = self.actor.store.grad.get("expert")
+        lend = g.numel() * g.element_size() if (g is not None and getattr(a, "share_kv_grad_memory", True)) else 0
+        need = replica + max((kv_bytes or 0) // 2 - lend, 0) + total // 8  # at least half of the wanted KV pool must remain
+        ok = torch.tensor([1.0 if free_now >= need else 0.0], device=self.actor.device)
+        if self.ps.world_size > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)  # all ranks take the same path
+        return bool(ok.item() > 0)
 
     def _build_data_source(self):
         a = self.args

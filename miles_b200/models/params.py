@@ -156,7 +156,7 @@ class ParamStore:
 
     def __init__(self, cfg: ModelConfig, device: torch.device | str = "cpu", dtype: torch.dtype = torch.bfloat16,
                  ep_size: int = 1, ep_rank: int = 0, init_std: float = 0.02, seed: int = 1234, init: bool = True,
-                 meta: bool = False, tp_size: int = 1, tp_rank: int = 0):
+                 meta: bool = False, tp_size: int = 1, tp_rank: int = 0, share_dense: Optional["ParamStore"] = None):
         """``cfg`` is the global model; with ``tp_size > 1`` the store holds this rank's shard (``self.cfg`` becomes
         the local view, ``self.global_cfg`` keeps the full model for conversions)."""
         self.global_cfg = cfg
@@ -170,7 +170,12 @@ class ParamStore:
         self.by_name = OrderedDict((s.name, s) for s in self.specs)
         self.sizes = {g: sum(_align(s.numel) for s in self.specs if s.group == g) for g in ("dense", "expert")}
         dev = torch.device("meta") if meta else self.device
-        self.flat = {g: torch.zeros(n, dtype=dtype, device=dev) for g, n in self.sizes.items()}
+        # ``share_dense``: the replicated parameters are the other store's very buffer (a rollout replica that holds
+        # all experts next to a trainer that holds its expert-parallel share)
+        if share_dense is not None:
+            assert share_dense.sizes["dense"] == self.sizes["dense"] and share_dense.dtype == dtype
+        self.flat = {g: (share_dense.flat[g] if (share_dense is not None and g == "dense") else torch.zeros(n, dtype=dtype, device=dev))
+                     for g, n in self.sizes.items()}
         self.grad: dict[str, Optional[torch.Tensor]] = {"dense": None, "expert": None}
         self.params: "OrderedDict[str, torch.Tensor]" = OrderedDict()
         self.grads: "OrderedDict[str, torch.Tensor]" = OrderedDict()

@@ -30,11 +30,12 @@ from .optimizer import FlatAdam, OptimConfig
 _DT = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
 
 
-def choose_memory_plan(total_bytes: int, dense_params: int, expert_params: int, reserve_frac: float = 0.30) -> dict:
+def choose_memory_plan(total_bytes: int, dense_params: int, expert_params: int, reserve_frac: float = 0.30,
+                       extra_resident_bytes: int = 0) -> dict:
     """Pick gradient / optimizer-state precision and placement that leaves ``reserve_frac`` of the device
     for activations and for the part of the KV cache that does not fit into the bytes it borrows from the
     expert gradients.  Bytes per parameter: bf16 weight 2 + gradient + two moments (+ master)."""
-    budget = total_bytes * (1.0 - reserve_frac)
+    budget = total_bytes * (1.0 - reserve_frac) - extra_resident_bytes  # e.g. the rollout engine's full expert replica
     n = dense_params + expert_params
     plans = [
         ("fp32-master", dict(expert_grad="fp32", state="fp32", master=True, offload=False), 2 + 4 + 8 + 4),
@@ -137,7 +138,13 @@ class TrainActor:
         expert = self.store.sizes["expert"]
         if self.on_gpu:
             total = torch.cuda.get_device_properties(self.device).total_memory
-            plan = choose_memory_plan(total, dense, expert)
+            extra = 0
+            if (self.cfg.is_moe and self.ps.ep.size > 1 and self.role == "actor" and self.ps.tp.size == 1
+                    and getattr(a, "rollout_replicate_experts", True) is not False and not getattr(a, "debug_train_only", False)):
+                # the colocated engine will hold all experts (see RLLoop._build_engine): leave room for the part this
+                # rank does not train
+                extra = (expert * self.ps.ep.size - expert) * 2
+            plan = choose_memory_plan(total, dense, expert, extra_resident_bytes=extra)
         else:
             plan = dict(expert_grad="fp32", state="fp32", master=False, offload=False, name="cpu")
         # explicit flags override the automatic plan

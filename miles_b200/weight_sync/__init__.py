@@ -36,6 +36,13 @@ def sync_weights(actor, engines: Sequence, mode: str | None = None) -> dict:
         with torch.no_grad():
             for g, t in e.store.flat.items():
                 src = actor.store.flat[g]
+                if src.data_ptr() == t.data_ptr() and src.numel() == t.numel():
+                    continue  # this group is shared
+                if g == "expert" and e.store.ep_size == 1 and actor.store.ep_size > 1:
+                    from .reshard import gather_experts_into
+
+                    moved += gather_experts_into(actor.store, e.store, actor.ps.ep.group)
+                    continue
                 if src.numel() == t.numel():
                     t.copy_(src.to(t.dtype), non_blocking=True)
                     moved += src.numel() * src.element_size()

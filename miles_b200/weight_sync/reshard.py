@@ -20,3 +20,19 @@ def reshard_into(src_store, dst_store, group: str) -> int:
         dst.copy_(src.to(dst.dtype), non_blocking=True)
         moved += dst.numel() * dst.element_size()
     return moved
+
+
+def gather_experts_into(src_store, dst_store, ep_group) -> int:
+    """Trainer holds ``E / ep`` experts per rank, the rollout replica all ``E``: every expert tensor of the replica
+    is the all-gather of the ranks' shares along the expert dimension (contiguous chunks, no staging copy).
+    Returns the bytes received by this rank."""
+    import torch.distributed as dist
+
+    moved = 0
+    for s in dst_store.specs:
+        if s.group != "expert":
+            continue
+        dst, src = dst_store.params[s.name], src_store.params[s.name]
+        dist.all_gather_into_tensor(dst, src.contiguous(), group=ep_group)
+        moved += (dst.numel() - src.numel()) * dst.element_size()
+    return moved
