@@ -37,6 +37,7 @@ class OptimConfig:
     state_dtype: torch.dtype = torch.float32
     master_weights: bool = True
     offload_states: bool = False          # keep moments (and master) of the expert group in pinned host memory
+    offload_resident_frac: float = 0.0    # share of the offloaded moments that stays on the device after all (no stream)
     offload_chunk_elems: int = 1 << 27    # 128 Mi elements per streamed chunk
     # LR schedule (in optimizer steps)
     lr_decay_style: str = "constant"
@@ -96,8 +97,14 @@ class FlatAdam:
             if off:
                 ce = cfg.offload_chunk_elems
                 st["chunks"] = [(a, min(a + ce, n)) for a in range(0, n, ce)]
-                st["m"] = [torch.zeros(b - a, dtype=cfg.state_dtype).pin_memory() for a, b in st["chunks"]]
-                st["v"] = [torch.zeros(b - a, dtype=cfg.state_dtype).pin_memory() for a, b in st["chunks"]]
+                # spread the chunks that stay on the device evenly among the streamed ones, so that their updates
+                # fill the time the copy engines need for the next streamed chunk
+                fr = min(max(cfg.offload_resident_frac, 0.0), 1.0)
+                res = [int((i + 1) * fr) > int(i * fr) for i in range(len(st["chunks"]))]
+                mk = lambda k, on_dev: (torch.zeros(k, dtype=cfg.state_dtype, device=self.dev) if on_dev
+                                        else torch.zeros(k, dtype=cfg.state_dtype).pin_memory())
+                st["m"] = [mk(b - a, r) for (a, b), r in zip(st["chunks"], res)]
+                st["v"] = [mk(b - a, r) for (a, b), r in zip(st["chunks"], res)]
                 st["master"] = None
             else:
                 st["m"] = torch.zeros(n, dtype=cfg.state_dtype, device=self.dev)
@@ -233,7 +240,13 @@ class FlatAdam:
         start = torch.cuda.Event()
         start.record(main)
         es = torch.empty((), dtype=c.state_dtype).element_size()
-        for i, (a, b) in enumerate(st["chunks"]):
+        streamed = [k for k, t in enumerate(st["m"]) if not t.is_cuda]
+        order = {k: j for j, k in enumerate(streamed)}
+        for k, (a, b) in enumerate(st["chunks"]):
+            if st["m"][k].is_cuda:  # resident chunk: plain update, overlaps the copies of the streamed ones
+                self._adam_region(flat[a:b], None, grad[a:b], st["m"][k], st["v"][k], lr, wd, self.step_count)
+                continue
+            i = order[k]
             dm, dv = st["stage"][i % nbuf]
             n = b - a
             with torch.cuda.stream(s_in):
@@ -241,29 +254,30 @@ class FlatAdam:
                     s_in.wait_event(ev_out[i - nbuf])  # staging buffer drained
                 else:
                     s_in.wait_event(start)
-                dm[:n].copy_(st["m"][i], non_blocking=True)
-                dv[:n].copy_(st["v"][i], non_blocking=True)
+                dm[:n].copy_(st["m"][k], non_blocking=True)
+                dv[:n].copy_(st["v"][k], non_blocking=True)
                 ev_in[i].record(s_in)
             main.wait_event(ev_in[i])
             self._adam_region(flat[a:b], None, grad[a:b], dm[:n], dv[:n], lr, wd, self.step_count)
             ev_cmp[i].record(main)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_cmp[i])
-                st["m"][i].copy_(dm[:n], non_blocking=True)
-                st["v"][i].copy_(dv[:n], non_blocking=True)
+                st["m"][k].copy_(dm[:n], non_blocking=True)
+                st["v"][k].copy_(dv[:n], non_blocking=True)
                 ev_out[i].record(s_out)
             self.h2d_bytes += 2 * n * es
             self.d2h_bytes += 2 * n * es
-        main.wait_event(ev_out[-1])
-        if len(ev_out) > 1:
-            main.wait_event(ev_out[-2])
+        if streamed:
+            main.wait_event(ev_out[len(streamed) - 1])
+            if len(streamed) > 1:
+                main.wait_event(ev_out[len(streamed) - 2])
 
     # ------------------------------------------------------------------ checkpoint
     def state_dict(self) -> dict:
         out = {"step": self.step_count}
         for g, st in self.state.items():
             if st["offload"]:
-                out[g] = {"m": torch.cat([t for t in st["m"]]), "v": torch.cat([t for t in st["v"]]), "master": None}
+                out[g] = {"m": torch.cat([t.cpu() for t in st["m"]]), "v": torch.cat([t.cpu() for t in st["v"]]), "master": None}
             else:
                 out[g] = {"m": st["m"], "v": st["v"], "master": st["master"]}
         return out
