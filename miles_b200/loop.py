@@ -138,6 +138,15 @@ class RLLoop:
                              eos_token_id=getattr(self.tokenizer, "eos_token_id", None), kv_storage=kv_storage)
         self.client = EngineClient([self.engine], self.tokenizer)
         self.actor.connect_rollout_engines([self.engine])
+        if self.actor.on_gpu and self.actor.opt is not None and self.actor.plan.get("offload"):
+            # everything resident is allocated now: whatever is left beyond the activation reserve takes moments back
+            # from host memory (less to stream per optimizer step)
+            free_now, total = torch.cuda.mem_get_info(self.actor.device)
+            spare = free_now - total // 6
+            t = torch.tensor([float(max(spare, 0))], device=self.actor.device)
+            if self.ps.world_size > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            self.actor.opt.promote_offloaded(int(t.item()))
 
     def _replica_bytes(self) -> int:
         cfg = self.actor.cfg

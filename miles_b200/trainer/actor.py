@@ -45,13 +45,8 @@ def choose_memory_plan(total_bytes: int, dense_params: int, expert_params: int, 
     ]
     for name, plan, bpp in plans:
         if n * bpp <= budget:
-            out = dict(plan, name=name)
-            if plan["offload"]:
-                # whatever the budget still allows stays on the device: only the rest of the moments is streamed
-                moments = max(expert_params * 4, 1)
-                out["resident_frac"] = max(0.0, min(1.0, 0.9 * (budget - n * bpp) / moments))
-            return out
-    return dict(plans[-1][1], name=plans[-1][0], resident_frac=0.0)
+            return dict(plan, name=name)
+    return dict(plans[-1][1], name=plans[-1][0])
 
 
 class TrainActor:
@@ -166,7 +161,7 @@ class TrainActor:
         oc = OptimConfig(lr=a.lr if self.role == "actor" else (a.critic_lr or a.lr), beta1=a.adam_beta1, beta2=a.adam_beta2,
                          eps=a.adam_eps, weight_decay=a.weight_decay, clip_grad=a.clip_grad, state_dtype=_DT[plan["state"]],
                          master_weights=plan["master"], offload_states=plan["offload"],
-                         offload_resident_frac=float(plan.get("resident_frac", 0.0)), lr_decay_style=a.lr_decay_style,
+ lr_decay_style=a.lr_decay_style,
                          lr_warmup_iters=a.lr_warmup_iters or 0, lr_decay_iters=a.lr_decay_iters or 0, min_lr=a.min_lr,
                          lr_wsd_decay_iters=a.lr_wsd_decay_iters or 0)
         dense_shard = None

@@ -272,6 +272,31 @@ class FlatAdam:
             if len(streamed) > 1:
                 main.wait_event(ev_out[len(streamed) - 2])
 
+    def promote_offloaded(self, max_bytes: int) -> int:
+        """Move evenly spaced chunks of the host-resident moments to the device, up to ``max_bytes``. Called once
+        everything else (engine, KV cache, exchange buffers) is allocated, with what is then really free minus the
+        activation reserve: the streamed volume shrinks by what fits. Returns the bytes moved."""
+        moved = 0
+        for st in self.state.values():
+            if not st.get("offload"):
+                continue
+            host = [k for k, t in enumerate(st["m"]) if not t.is_cuda]
+            if not host:
+                continue
+            per = 2 * st["m"][host[0]].numel() * st["m"][host[0]].element_size()
+            take = min(len(host), int(max(max_bytes - moved, 0) // max(per, 1)))
+            if take <= 0:
+                continue
+            stride = len(host) / take
+            for j in range(take):
+                k = host[min(len(host) - 1, int(j * stride))]
+                if st["m"][k].is_cuda:
+                    continue
+                st["m"][k] = st["m"][k].to(self.dev)
+                st["v"][k] = st["v"][k].to(self.dev)
+                moved += 2 * st["m"][k].numel() * st["m"][k].element_size()
+        return moved
+
     # ------------------------------------------------------------------ checkpoint
     def state_dict(self) -> dict:
         out = {"step": self.step_count}
