@@ -142,7 +142,7 @@ class RLLoop:
             # everything resident is allocated now: whatever is left beyond the activation reserve takes moments back
             # from host memory (less to stream per optimizer step)
             free_now, total = torch.cuda.mem_get_info(self.actor.device)
-            spare = free_now - total // 6
+            spare = free_now - total // 5
             t = torch.tensor([float(max(spare, 0))], device=self.actor.device)
             if self.ps.world_size > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MIN)
