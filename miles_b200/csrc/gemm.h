@@ -56,6 +56,34 @@ struct GemmProblem {
   int n_dest;
 };
 
+// Block-scaled GEMM (gemm_mx.cu): C[M,N] (bf16) = alpha * A . B^T, both operands K-major packed values with
+// scale-factor atoms (see sf_swizzle). kind 0 = MXFP8 (K % 128 == 0), kind 1 = NVFP4 (K % 256 == 0, two values per byte).
+struct MxGemmProblem {
+  int kind;
+  int mode;  // GEMM_DENSE or GEMM_GROUPED_ROWS (row tiles start on 128-row boundaries; B holds num_groups slabs of N rows)
+  int M, N, K;
+  const void* a;
+  long long a_rows, a_pitch_bytes;
+  const void* b;
+  long long b_rows, b_pitch_bytes;
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  void* c;
+  long long ldc;
+  float alpha;
+  int num_groups;
+  const int* tile_group;
+  const int* num_m_tiles;
+  int max_tiles;
+  int* status;
+  int block_n;  // 0 = choose, else 128 or 256
+};
+int gemm_mx_launch(const MxGemmProblem& p, cudaStream_t stream);
+const char* gemm_mx_last_error();
+// Row-major scale factors [rows, S] -> 512-byte atoms [ceil(rows/128)][ceil(S/4)] in the layout the block-scaled MMA
+// reads from TMEM; `out` must be zero-filled and hold ceil(rows/128) * ceil(S/4) * 512 bytes.
+void sf_swizzle(const uint8_t* in, uint8_t* out, long long rows, int S, cudaStream_t s);
+
 // Launches on `stream`. Returns 0 or a negative host-side error code (bad argument / driver error).
 int gemm_bf16_launch(const GemmProblem& p, cudaStream_t stream);
 const char* gemm_last_error();

@@ -206,9 +206,11 @@ std::vector<at::Tensor> fake_int4_quant(const at::Tensor& x, int64_t gr, int64_t
 }  // namespace
 
 void register_comm(pybind11::module_& m);  // ops_bindings3.cpp
+void register_mx(pybind11::module_& m);    // ops_bindings4.cpp
 
 void register_more(pybind11::module_& m) {
   register_comm(m);
+  register_mx(m);
   m.def("sample_rows", &sample_rows);
   m.def("paged_decode_attention", &paged_decode_attention);
   m.def("flash_attn_fwd", &flash_attn_fwd);

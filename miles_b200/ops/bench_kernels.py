@@ -2,6 +2,7 @@
 profiler captures are taken on.
 
     python -m miles_b200.ops.bench_kernels gemm --m 8192 --n 8192 --k 8192
+    python -m miles_b200.ops.bench_kernels gemm_mx --kind mxfp8 --m 8192 --n 8192 --k 8192
     python -m miles_b200.ops.bench_kernels attn --seqs 4 --len 8192
     python -m miles_b200.ops.bench_kernels gemv --t 4 --n 49152 --k 2048
     python -m miles_b200.ops.bench_kernels decode_attn --batch 64 --ctx 1500
@@ -31,7 +32,7 @@ def _time(fn, iters: int, warmup: int = 3) -> float:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "gemv", "decode_attn"])
+    ap.add_argument("what", choices=["gemm", "gemm_mx", "attn", "gemv", "decode_attn"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -43,6 +44,8 @@ def main() -> None:
     ap.add_argument("--hq", type=int, default=32)
     ap.add_argument("--hk", type=int, default=4)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--kind", default="mxfp8", choices=["mxfp8", "nvfp4"])
     ap.add_argument("--library", action="store_true", help="also time the library kernel for the same problem")
     ns = ap.parse_args()
     from miles_b200.ops import _ext
@@ -61,6 +64,14 @@ def main() -> None:
         if ns.library:
             ml = _time(lambda: torch.matmul(a, b.t(), out=c), ns.iters)
             out.update(library_ms=ml, library_tflops=fl / ml / 1e9)
+    elif ns.what == "gemm_mx":
+        from miles_b200.ops.mx_gemm import KINDS, quantize_operand
+
+        a = quantize_operand(torch.randn(ns.m, ns.k, device=dev, dtype=torch.bfloat16), ns.kind)
+        b = quantize_operand(torch.randn(ns.n, ns.k, device=dev, dtype=torch.bfloat16), ns.kind)
+        ms = _time(lambda: C.gemm_mx(a.q, a.atoms, b.q, b.atoms, KINDS[ns.kind], 1.0, 0, None, None, status, ns.block_n), ns.iters)
+        fl = 2.0 * ns.m * ns.n * ns.k
+        out.update(kind=ns.kind, shape=[ns.m, ns.n, ns.k], ms=ms, tflops=fl / ms / 1e9, status=int(status))
     elif ns.what == "attn":
         from miles_b200.ops.attention import build_tiles
 
