@@ -69,8 +69,18 @@ template <int BN>
 __device__ __forceinline__ MxTile mx_decode(const MxArgs& p, int t) {
   MxTile r;
   const int n_tiles = (p.N + BN - 1) / BN;
-  const int mt = t / n_tiles, nt = t - mt * n_tiles;
+  int mt = t / n_tiles, nt = t - mt * n_tiles;
   if (p.mode == GEMM_DENSE) {
+    // bands of 8 row tiles, column tiles outermost within a band: CTAs running together share B tiles in L2
+    constexpr int BAND = 8;
+    const int m_tiles = (p.M + BM - 1) / BM;
+    const int per_band = BAND * n_tiles;
+    const int band = t / per_band;
+    const int first_m = band * BAND;
+    const int band_rows = (m_tiles - first_m) < BAND ? (m_tiles - first_m) : BAND;
+    const int in_band = t - band * per_band;
+    mt = first_m + in_band % band_rows;
+    nt = in_band / band_rows;
     r.a_row0 = mt * BM;
     r.b_row0 = nt * BN;
     r.row_end = p.M;
