@@ -98,6 +98,7 @@ def main() -> None:
     ap.add_argument("--max-tokens-per-gpu", type=int, default=32768)
     ap.add_argument("--no-routing-replay", action="store_true")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (dense models; the rest of the GPUs are data parallel)")
+    ap.add_argument("--pp", type=int, default=1, help="pipeline-parallel size (experts are then not expert parallel)")
     ns = ap.parse_args()
     if ns.impl == "reference":
         reference_arm(ns)
@@ -121,7 +122,8 @@ def main() -> None:
         "--eps-clip", "0.2", "--eps-clip-high", "0.28", "--lr", "1e-6", "--weight-decay", "0.1", "--adam-beta1", "0.9",
         "--adam-beta2", "0.98", "--clip-grad", "1.0", "--use-dynamic-batch-size", "--max-tokens-per-gpu", str(ns.max_tokens_per_gpu),
         "--actor-num-nodes", "1", "--actor-num-gpus-per-node", str(world), "--colocate",
-        "--expert-model-parallel-size", str(world if ns.tp == 1 else 1), "--tensor-model-parallel-size", str(ns.tp),
+        "--expert-model-parallel-size", str(world if (ns.tp == 1 and ns.pp == 1) else 1), "--tensor-model-parallel-size", str(ns.tp),
+        "--pipeline-model-parallel-size", str(ns.pp),
         "--recompute-granularity", "full",
         "--custom-generate-function-path", "miles_b200.rollout.generate_hub.benchmarkers.generate",
         "--benchmark-mean-response-len", str(ns.mean_response_len), "--sglang-mem-fraction-static", "0.8",
@@ -193,7 +195,8 @@ def main() -> None:
                 "model": cfg.name, "params_b": round(cfg.num_params() / 1e9, 2), "global_batch": n_prompts * ns.samples_per_prompt,
                 "prompts": n_prompts, "samples_per_prompt": ns.samples_per_prompt, "seq_len": ns.prompt_len + ns.max_response_len,
                 "prompt_len": ns.prompt_len, "max_response_len": ns.max_response_len, "mean_response_len": ns.mean_response_len,
-                "tokens_per_step": tokens / ns.steps, "parallelism": (f"dp{world}-attn x ep{world}-experts, colocated engine" if ns.tp == 1 else
+                "tokens_per_step": tokens / ns.steps, "parallelism": (f"pp{ns.pp} x dp{world // ns.pp}, colocated engine" if ns.pp > 1 else
+                                                     f"dp{world}-attn x ep{world}-experts, colocated engine" if ns.tp == 1 else
                                                      f"tp{ns.tp} x dp{world // ns.tp}, colocated engine"),
                 "optimizer_plan": loop.actor.plan.get("name"), "routing_replay": not ns.no_routing_replay,
                 "l2": f"working set ({cfg.num_params() * 2 / 1e9:.0f} GB of weights + KV cache) is far larger than L2; no explicit flush",

@@ -147,6 +147,8 @@ def export_hf(actor, out_dir: str, max_shard_bytes: int = 5 << 30, tokenizer_dir
             continue  # the gathered tensors are identical on every tensor-parallel rank
         if not is_expert and ps.dp_cp.rank != 0:
             continue  # replicated tensors are written once
+        if hf_name == "model.embed_tokens.weight" and ps.pp.size > 1 and ps.pp.rank != 0:
+            continue  # a tied embedding also lives on the last pipeline stage (as its LM head)
         nb = t.numel() * t.element_size()
         if cur and size + nb > max_shard_bytes:
             shards.append(cur)

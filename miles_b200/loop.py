@@ -52,7 +52,10 @@ class RLLoop:
             ep=args.expert_model_parallel_size, backend=None if args.distributed_backend == "nccl" else args.distributed_backend,
             timeout_minutes=args.distributed_timeout_minutes)
         # ranks of one tensor-parallel group are one data-parallel replica: same seeds, same prompts, same samples
-        self.n_rep, self.rep = self.ps.dp_cp.size, self.ps.dp_cp.rank
+        # the stages of a pipeline each run their own engine on a full copy of the model and pool their samples
+        # before training, so they count as rollout replicas too
+        self.n_rep = self.ps.dp_cp.size * self.ps.pp.size
+        self.rep = self.ps.dp_cp.rank * self.ps.pp.size + self.ps.pp.rank
         torch.manual_seed(args.seed + self.rep)
         self.tokenizer = _load_tokenizer(args)
         self.actor = TrainActor(args, "actor", self.ps)
@@ -106,9 +109,18 @@ class RLLoop:
                 lend = g.numel() * g.element_size()
             room = free_now + lend - total // 8
             kv_bytes = max(min(budget, want, room), per_tok * page * 4)
-        replicate = self.actor.ep_dispatcher is not None and self._replicate_experts_fits(kv_bytes)
+        pipelined = self.ps.pp.size > 1
+        replicate = not pipelined and self.actor.ep_dispatcher is not None and self._replicate_experts_fits(kv_bytes)
         if replicate:
             kv_bytes = max(min(kv_bytes, room - self._replica_bytes()), per_tok * page * 4)
+        if pipelined:
+            assert self.actor.ep_dispatcher is None and self.ps.tp.size == 1, \
+                "the colocated engine of a pipelined trainer is built for tp = ep = 1"
+            from .models import build_specs
+
+            full_bytes = sum(sp.numel for sp in build_specs(cfg)) * 2
+            if kv_bytes is not None:
+                kv_bytes = max(min(kv_bytes, room - full_bytes), per_tok * page * 4)
         kv_storage = None
         if self.actor.on_gpu and getattr(a, "share_kv_grad_memory", True) and not getattr(a, "debug_rollout_only", False):
             # rollout and training alternate in this loop: the KV cache borrows the bytes of the expert gradients
@@ -126,6 +138,13 @@ class RLLoop:
             self.rollout_store = ParamStore(cfg, self.actor.device, self.actor.store.dtype, ep_size=1, init=False,
                                             share_dense=self.actor.store)
             engine_model = build_model(cfg, self.rollout_store, "b200")
+        elif pipelined:
+            # the trainer's stage holds part of the layers; the engine decodes on a copy of the whole model that the
+            # weight update fills stage by stage (broadcasts inside the pipeline group)
+            from .models import ParamStore, build_model
+
+            self.rollout_store = ParamStore(cfg, self.actor.device, self.actor.store.dtype, init=False)
+            engine_model = build_model(cfg, self.rollout_store, "b200" if not self.actor.is_torch else "torch")
         elif self.actor.ep_dispatcher is not None:
             from .engine.core import LockstepSync
             from .parallel.expert_parallel import ExpertParallel
@@ -227,6 +246,24 @@ class RLLoop:
             self.engine.drain()  # expert-parallel ranks keep serving dummy iterations until all are done
         samples = flatten_groups(out.samples if hasattr(out, "samples") else out)
         samples = postprocess_rollout_data(self.local_args, samples)
+        if self.ps.pp.size > 1:
+            # every stage trains on the samples of all the stages of its pipeline
+            pooled = [None] * self.ps.pp.size
+            dist.all_gather_object(pooled, [s.to_dict() for s in samples], group=self.ps.pp.group)
+            from .utils.types import Sample
+
+            samples, gmap = [], {}
+            for part_id, part in enumerate(pooled):
+                for d in part:
+                    smp = Sample.from_dict(d)
+                    # every stage's data source numbers its groups and samples from zero: make them distinct again
+                    if smp.group_index is not None:
+                        smp.group_index = gmap.setdefault((part_id, smp.group_index), len(gmap))
+                    if smp.index is not None:
+                        smp.index = smp.index * self.ps.pp.size + part_id
+                    if smp.rollout_id is not None:
+                        smp.rollout_id = smp.rollout_id * self.ps.pp.size + part_id
+                    samples.append(smp)
         dt = time.perf_counter() - t0
         metrics = dict(getattr(out, "metrics", {}) or {})
         metrics.update(compute_rollout_metrics(a, samples, dt))
@@ -295,7 +332,7 @@ class RLLoop:
         t3 = time.perf_counter()
         n_tok = sum(len(s.tokens) for s in samples)
         tot = torch.tensor([float(n_tok)], device=self.actor.device)
-        if self.n_rep > 1:
+        if self.ps.dp_cp.size > 1:
             dist.all_reduce(tot, group=self.ps.dp_cp.group)  # one count per data-parallel replica
         metrics.update({"perf/rollout_time": t1 - t0, "perf/train_time": t2 - t1, "perf/update_weights_wall": t3 - t2,
                         "perf/step_time": t3 - t0, "perf/step_tokens": float(tot.item()),

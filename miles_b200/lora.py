@@ -41,7 +41,7 @@ def _targets(store: ParamStore, modules: Sequence[str]) -> list:
     cfg = store.cfg
     out = []
     q, kv = cfg.q_dim, cfg.kv_dim
-    for i in range(cfg.num_layers):
+    for i in range(*getattr(store, "layer_range", (0, cfg.num_layers))):
         p, hp = f"layers.{i}.", f"model.layers.{i}."
         att = {"q_proj": (0, q), "k_proj": (q, q + kv), "v_proj": (q + kv, q + 2 * kv)}
         for m, (a, b) in att.items():

@@ -406,13 +406,17 @@ class B200Qwen3:
     @torch.no_grad()
     def forward_hidden(self, tokens, positions, cu_seqlens, meta: Optional[InferMeta] = None, kv_cache=None,
                        replay: Optional[torch.Tensor] = None, record: Optional[list] = None, max_seqlen: int = 0,
-                       save_inputs: Optional[list] = None):
+                       save_inputs: Optional[list] = None, x_in: Optional[torch.Tensor] = None):
+        """Runs this pipeline stage's layers (all of them without pipeline parallelism). The first stage embeds
+        ``tokens``, later stages continue from ``x_in``; every stage but the last returns the raw hidden states that
+        the next stage consumes, the last one applies the final norm."""
         cfg, P, C = self.cfg, self.store.params, self.C
-        x = P["embed.weight"][tokens.long()]
+        lo, hi = self.store.layer_range
+        x = P["embed.weight"][tokens.long()] if self.store.is_first_stage else x_in
         if not max_seqlen and cu_seqlens is not None:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
-        moe_idx = 0
-        for i in range(cfg.num_layers):
+        moe_idx = sum(cfg.layer_is_moe(j) for j in range(lo))  # replay columns are indexed over the whole model
+        for i in range(lo, hi):
             if save_inputs is not None:
                 save_inputs.append(x)
             rid = None
@@ -423,6 +427,8 @@ class B200Qwen3:
             x = self.layer_forward(i, x, positions, cu_seqlens, max_seqlen, meta, kv_cache, rid, record)
         if save_inputs is not None:
             save_inputs.append(x)
+        if not self.store.is_last_stage:
+            return x
         h, _ = C.rmsnorm_fwd(x, None, P["final_norm.weight"], cfg.rms_eps)
         self.launches += 1
         return h
@@ -437,21 +443,34 @@ class B200Qwen3:
         dx = C.rmsnorm_bwd(dh, x_last, P["final_norm.weight"], rstd, None, G["final_norm.weight"], True)
         self.launches += 3
         del dh
-        moe_layers = [i for i in range(cfg.num_layers) if cfg.layer_is_moe(i)]
-        for i in reversed(range(cfg.num_layers)):
-            rid = replay[:, moe_layers.index(i)] if (replay is not None and cfg.layer_is_moe(i)) else None
-            dx = self.layer_backward(i, inputs[i], dx, positions, cu_seqlens, max_seqlen, rid)
-            inputs[i] = None
-        G["embed.weight"].index_add_(0, tokens.long(), dx.to(G["embed.weight"].dtype))
+        return self.layers_backward(inputs, dx, tokens, positions, cu_seqlens, max_seqlen, replay)
 
-    def forward_backward_hidden(self, tokens, positions, cu_seqlens, row_index, head_fn, replay=None, max_seqlen: int = 0):
+    @torch.no_grad()
+    def layers_backward(self, inputs, dx, tokens, positions, cu_seqlens, max_seqlen, replay):
+        """Backward through this stage's layers: ``inputs[j]`` is the saved input of local layer ``j``, ``dx`` the
+        gradient of the stage's output. Returns the gradient of the stage's input (on the first stage it has been
+        added into the embedding gradient) and keeps it in ``self.last_dx_in``."""
+        cfg, G = self.cfg, self.store.grads
+        lo, hi = self.store.layer_range
+        moe_layers = [i for i in range(cfg.num_layers) if cfg.layer_is_moe(i)]
+        for i in reversed(range(lo, hi)):
+            rid = replay[:, moe_layers.index(i)] if (replay is not None and cfg.layer_is_moe(i)) else None
+            dx = self.layer_backward(i, inputs[i - lo], dx, positions, cu_seqlens, max_seqlen, rid)
+            inputs[i - lo] = None
+        if self.store.is_first_stage:
+            G["embed.weight"].index_add_(0, tokens.long(), dx.to(G["embed.weight"].dtype))
+        self.last_dx_in = dx
+        return dx
+
+    def forward_backward_hidden(self, tokens, positions, cu_seqlens, row_index, head_fn, replay=None, max_seqlen: int = 0,
+                                x_in: Optional[torch.Tensor] = None):
         """Generic head: ``head_fn(hidden_rows_fp32_leaf) -> (loss, metrics)`` (e.g. a value head); the trunk is
         back-propagated with the gradient autograd computes for the hidden rows."""
         assert self.store.grads, "allocate_grads() must be called before training"
         if not max_seqlen:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
         inputs: list = []
-        h = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, max_seqlen=max_seqlen, save_inputs=inputs)
+        h = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, max_seqlen=max_seqlen, save_inputs=inputs, x_in=x_in)
         x_last = inputs.pop()
         rows = row_index.long()
         leaf = h[rows].float().detach().requires_grad_(True)
@@ -486,19 +505,21 @@ class B200Qwen3:
 
     @torch.no_grad()
     def forward_logprobs(self, tokens, positions, cu_seqlens, row_index, targets, inv_temp, replay=None, record=None,
-                         max_seqlen: int = 0):
-        h = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, record=record, max_seqlen=max_seqlen)
+                         max_seqlen: int = 0, x_in: Optional[torch.Tensor] = None):
+        h = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, record=record, max_seqlen=max_seqlen, x_in=x_in)
         return self.logprobs_entropy(h[row_index.long()], targets, inv_temp)
 
     def forward_backward(self, tokens, positions, cu_seqlens, row_index, targets, inv_temp, loss_fn, replay=None,
-                         max_seqlen: int = 0, chunk: int = 2048):
-        """One micro-batch: forward, ``loss_fn(logprobs, entropy) -> (loss, metrics)``, backward into the grad buffers."""
+                         max_seqlen: int = 0, chunk: int = 2048, x_in: Optional[torch.Tensor] = None):
+        """One micro-batch: forward, ``loss_fn(logprobs, entropy) -> (loss, metrics)``, backward into the grad buffers.
+        On the last pipeline stage ``x_in`` is the activation received from the previous stage and ``self.last_dx_in``
+        afterwards holds the gradient to send back."""
         cfg, P, G, C = self.cfg, self.store.params, self.store.grads, self.C
         assert G, "allocate_grads() must be called before training"
         if not max_seqlen:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
         inputs: list[torch.Tensor] = []
-        h = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, max_seqlen=max_seqlen, save_inputs=inputs)
+        h = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, max_seqlen=max_seqlen, save_inputs=inputs, x_in=x_in)
         x_last = inputs.pop()  # input of the final norm
         rows = row_index.long()
         hr = h[rows].contiguous()

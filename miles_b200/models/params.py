@@ -50,11 +50,18 @@ def _align(n: int, a: int = 128) -> int:
     return (n + a - 1) // a * a
 
 
-def build_specs(cfg: ModelConfig, ep_size: int = 1) -> list[ParamSpec]:
+def build_specs(cfg: ModelConfig, ep_size: int = 1, layers: Optional[tuple] = None, first: bool = True,
+                last: bool = True) -> list[ParamSpec]:
+    """All parameters of the model, or of one pipeline stage: ``layers = (lo, hi)`` keeps those decoder layers,
+    ``first`` / ``last`` say whether the stage holds the embedding / the final norm and LM head (with tied embeddings
+    the last stage holds a copy of the embedding as its LM head). Names always carry the global layer index."""
     assert cfg.num_experts % ep_size == 0 or not cfg.is_moe, "experts must divide evenly over EP ranks"
     H, D = cfg.hidden_size, cfg.head_dim
-    specs: list[ParamSpec] = [ParamSpec("embed.weight", (cfg.vocab_size, H), "dense", "normal")]
-    for i in range(cfg.num_layers):
+    lo, hi = layers if layers is not None else (0, cfg.num_layers)
+    specs: list[ParamSpec] = []
+    if first or (last and cfg.tie_embeddings):
+        specs.append(ParamSpec("embed.weight", (cfg.vocab_size, H), "dense", "normal"))
+    for i in range(lo, hi):
         p = f"layers.{i}."
         specs.append(ParamSpec(p + "ln1.weight", (H,), "dense", "ones"))
         specs.append(ParamSpec(p + "attn.qkv.weight", (cfg.qkv_dim, H), "dense", "normal"))
@@ -75,9 +82,10 @@ def build_specs(cfg: ModelConfig, ep_size: int = 1) -> list[ParamSpec]:
             I = cfg.ffn_hidden_size
             specs.append(ParamSpec(p + "mlp.gate_up.weight", (2 * I, H), "dense", "normal"))
             specs.append(ParamSpec(p + "mlp.down.weight", (H, I), "dense", "normal"))
-    specs.append(ParamSpec("final_norm.weight", (H,), "dense", "ones"))
-    if not cfg.tie_embeddings:
-        specs.append(ParamSpec("lm_head.weight", (cfg.vocab_size, H), "dense", "normal"))
+    if last:
+        specs.append(ParamSpec("final_norm.weight", (H,), "dense", "ones"))
+        if not cfg.tie_embeddings:
+            specs.append(ParamSpec("lm_head.weight", (cfg.vocab_size, H), "dense", "normal"))
     off = {"dense": 0, "expert": 0}
     for s in specs:
         s.offset = off[s.group]
@@ -156,17 +164,25 @@ class ParamStore:
 
     def __init__(self, cfg: ModelConfig, device: torch.device | str = "cpu", dtype: torch.dtype = torch.bfloat16,
                  ep_size: int = 1, ep_rank: int = 0, init_std: float = 0.02, seed: int = 1234, init: bool = True,
-                 meta: bool = False, tp_size: int = 1, tp_rank: int = 0, share_dense: Optional["ParamStore"] = None):
+                 meta: bool = False, tp_size: int = 1, tp_rank: int = 0, share_dense: Optional["ParamStore"] = None,
+                 pp_size: int = 1, pp_rank: int = 0, pp_first_layers: Optional[int] = None,
+                 pp_last_layers: Optional[int] = None):
         """``cfg`` is the global model; with ``tp_size > 1`` the store holds this rank's shard (``self.cfg`` becomes
-        the local view, ``self.global_cfg`` keeps the full model for conversions)."""
+        the local view, ``self.global_cfg`` keeps the full model for conversions). With ``pp_size > 1`` it holds the
+        decoder layers ``self.layer_range`` of pipeline stage ``pp_rank`` (plus embedding / head on the end stages)."""
         self.global_cfg = cfg
         self.tp_size, self.tp_rank = tp_size, tp_rank
+        self.pp_size, self.pp_rank = pp_size, pp_rank
+        from ..parallel.pipeline_parallel import stage_layers
+
+        self.layer_range = stage_layers(cfg.num_layers, pp_size, pp_rank, pp_first_layers, pp_last_layers)
+        self.is_first_stage, self.is_last_stage = pp_rank == 0, pp_rank == pp_size - 1
         cfg = tp_local_config(cfg, tp_size)
         self.cfg = cfg
         self.device = torch.device(device)
         self.dtype = dtype
         self.ep_size, self.ep_rank = ep_size, ep_rank
-        self.specs = build_specs(cfg, ep_size)
+        self.specs = build_specs(cfg, ep_size, self.layer_range, self.is_first_stage, self.is_last_stage)
         self.by_name = OrderedDict((s.name, s) for s in self.specs)
         self.sizes = {g: sum(_align(s.numel) for s in self.specs if s.group == g) for g in ("dense", "expert")}
         dev = torch.device("meta") if meta else self.device

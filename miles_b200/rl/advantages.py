@@ -131,11 +131,11 @@ def discounted_returns_flat(token_rewards: torch.Tensor, cu: torch.Tensor, gamma
 
 
 def whiten(values: torch.Tensor, mask: torch.Tensor, group: Optional["dist.ProcessGroup"] = None,
-           shift_mean: bool = True, eps: float = 1e-8) -> torch.Tensor:
+           shift_mean: bool = True, eps: float = 1e-8, reduce: bool = True) -> torch.Tensor:
     """Masked whitening with statistics all-reduced over ``group`` (3 floats), Bessel-corrected."""
     m = mask.to(values.dtype)
     stats = torch.stack([(values * m).sum(), (values * values * m).sum(), m.sum()]).float()
-    if dist.is_available() and dist.is_initialized():
+    if reduce and dist.is_available() and dist.is_initialized():
         dist.all_reduce(stats, op=dist.ReduceOp.SUM, group=group)
     s, ss, n = stats[0], stats[1], stats[2]
     if float(n) == 0:

@@ -64,8 +64,17 @@ class TrainActor:
         tp = self.ps.tp.size
         if store is None:
             store = ParamStore(self.cfg, self.device, self.dtype, ep_size=ep, ep_rank=self.ps.ep.rank if ep > 1 else 0,
-                               init_std=getattr(args, "init_std", 0.02), seed=args.seed, tp_size=tp, tp_rank=self.ps.tp.rank)
+                               init_std=getattr(args, "init_std", 0.02), seed=args.seed, tp_size=tp, tp_rank=self.ps.tp.rank,
+                               pp_size=self.ps.pp.size, pp_rank=self.ps.pp.rank,
+                               pp_first_layers=getattr(args, "decoder_first_pipeline_num_layers", None),
+                               pp_last_layers=getattr(args, "decoder_last_pipeline_num_layers", None))
         self.store = store
+        self.pipe = None
+        if self.ps.pp.size > 1:
+            from ..parallel.pipeline_parallel import PipeGroup, PipelineSchedule
+
+            assert want_b200, "pipeline parallelism needs the sm_100a model path"
+            self.pipe = PipelineSchedule(PipeGroup(self.ps.pp.group, self.ps.pp.rank, self.ps.pp.size, self.ps.pp.ranks), self.device)
         self.tp_exchange = None
         if tp > 1:
             from ..parallel.tensor_parallel import TensorParallel
@@ -173,7 +182,8 @@ class TrainActor:
             dense_shard = ShardedDenseAdam(self.store, self.ps.dp_cp.group, self.ps.dp_cp.rank, self.ps.dp_cp.size, self.device, oc)
         self.dense_shard = dense_shard
         self.opt = FlatAdam(self.store, oc, dp_group=self.ps.dp_cp.group, ep_group=self.ps.ep.group,
-                            tp_group=self.ps.tp.group if self.ps.tp.size > 1 else None, dense_shard=dense_shard)
+                            tp_group=self.ps.tp.group if self.ps.tp.size > 1 else None, dense_shard=dense_shard,
+                            pp_group=self.ps.pp.group if self.ps.pp.size > 1 else None)
 
     # ------------------------------------------------------------------ weight tags (ref / old_actor / teacher)
     def backup_weights(self, tag: str) -> None:
@@ -226,6 +236,8 @@ class TrainActor:
 
     @torch.no_grad()
     def compute_log_probs(self, mbs: list, key: str = "log_probs", with_entropy: bool = False) -> None:
+        if self.pipe is not None:
+            return self._compute_log_probs_pipelined(mbs, key, with_entropy)
         for mb in mbs:
             record = [] if (self.cfg.is_moe and self.args.use_routing_replay and not self.args.use_rollout_routing_replay
                             and key == "log_probs") else None
@@ -235,6 +247,88 @@ class TrainActor:
                 mb.extras["entropy"] = ent
             if record:
                 mb.extras["recorded_routing"] = torch.stack(record, 1)
+
+    # ------------------------------------------------------------------ pipeline parallel passes
+    def _act_meta(self, mbs: list):
+        H = self.cfg.hidden_size
+        return lambda i: ((mbs[i].tokens.shape[0], H), self.store.dtype)
+
+    @torch.no_grad()
+    def _compute_log_probs_pipelined(self, mbs: list, key: str, with_entropy: bool) -> None:
+        """Forward-only pipeline; the last stage's log-probs (and entropies, recorded routing) are then shared with
+        the other stages so that every stage runs the same advantage / bookkeeping code."""
+        a, pp, cfg = self.args, self.ps.pp, self.cfg
+        inv_t = 1.0 / a.rollout_temperature
+        want_record = cfg.is_moe and a.use_routing_replay and not a.use_rollout_routing_replay and key == "log_probs"
+        records: dict = {}
+        results: dict = {}
+
+        def fwd(i, x_in):
+            mb = mbs[i]
+            rec = [] if want_record else None
+            records[i] = rec
+            replay = self._replay_for(mb, "logprob")
+            if self.store.is_last_stage:
+                results[i] = self.model.forward_logprobs(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t,
+                                                         replay=replay, record=rec, max_seqlen=mb.max_seqlen, x_in=x_in)
+                return None
+            return self.model.forward_hidden(mb.tokens, mb.positions, mb.cu_seqlens, replay=replay, record=rec,
+                                             max_seqlen=mb.max_seqlen, x_in=x_in)
+
+        self.pipe.run_forward_only(len(mbs), self._act_meta(mbs), fwd)
+        src = pp.ranks[-1]
+        lo = self.store.layer_range[0]
+        moe_before = sum(cfg.layer_is_moe(j) for j in range(lo))
+        n_moe = sum(cfg.layer_is_moe(j) for j in range(cfg.num_layers))
+        for i, mb in enumerate(mbs):
+            n = mb.targets.shape[0]
+            buf = torch.stack(results[i][:2]) if self.store.is_last_stage else torch.empty(2, n, dtype=torch.float32, device=self.device)
+            dist.broadcast(buf, src=src, group=pp.group)
+            mb.extras[key] = buf[0].contiguous()
+            if with_entropy:
+                mb.extras["entropy"] = buf[1].contiguous()
+            if want_record:
+                full = torch.zeros(mb.tokens.shape[0], n_moe, cfg.moe_top_k, dtype=torch.int32, device=self.device)
+                if records[i]:
+                    full[:, moe_before:moe_before + len(records[i])] = torch.stack(records[i], 1).to(torch.int32)
+                dist.all_reduce(full, group=pp.group)  # stages hold disjoint layers: the sum is the concatenation
+                mb.extras["recorded_routing"] = full
+
+    def _forward_backward_pipelined(self, chunk: list, scale: float, metrics_acc: dict) -> None:
+        """1F1B over the micro-batches of one optimizer step. Intermediate stages keep the per-layer inputs of their
+        in-flight micro-batches (at most `stages after this one + 1`); the last stage runs forward, loss and backward
+        of a micro-batch back to back."""
+        inv_t = 1.0 / self.args.rollout_temperature
+        saved: dict = {}
+        last = self.store.is_last_stage
+
+        def fwd(i, x_in):
+            mb = chunk[i]
+            if last:
+                saved[i] = x_in
+                return None
+            inputs: list = []
+            y = self.model.forward_hidden(mb.tokens, mb.positions, mb.cu_seqlens, replay=self._replay_for(mb, "train"),
+                                          max_seqlen=mb.max_seqlen, save_inputs=inputs, x_in=x_in)
+            inputs.pop()  # the stage output itself
+            saved[i] = inputs
+            return y
+
+        def bwd(i, dy):
+            mb = chunk[i]
+            replay = self._replay_for(mb, "train")
+            if last:
+                _, m, _, _ = self.model.forward_backward(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t,
+                                                         self._loss_closure(mb, scale), replay=replay, max_seqlen=mb.max_seqlen,
+                                                         x_in=saved.pop(i))
+                for k, v in m.items():
+                    metrics_acc[k] = metrics_acc.get(k, 0.0) + v.detach().float() * scale
+                return self.model.last_dx_in
+            return self.model.layers_backward(saved.pop(i), dy, mb.tokens, mb.positions, mb.cu_seqlens, mb.max_seqlen, replay)
+
+        self.pipe.run_1f1b(len(chunk), self._act_meta(chunk), fwd, bwd)
+        if self.cfg.tie_embeddings and (self.store.is_first_stage or last):
+            pass  # reduced in _reduce_grads (all stages take part in the collective)
 
     # ------------------------------------------------------------------ the RL step
     def _stage(self, data: dict) -> list:
@@ -285,7 +379,7 @@ class TrainActor:
 
             allv = torch.cat([mb.extras["advantages"] for mb in mbs])
             allm = torch.cat([mb.loss_mask for mb in mbs])
-            w = whiten(allv, allm, self.ps.dp_cp.group)
+            w = whiten(allv, allm, self.ps.dp_cp.group, reduce=self.ps.dp_cp.size > 1)
             off = 0
             for mb in mbs:
                 n = mb.loss_mask.numel()
@@ -353,16 +447,19 @@ class TrainActor:
                 self.store.zero_grads()
                 if a.calculate_per_token_loss:
                     tok = torch.stack([mb.loss_mask.sum() for mb in chunk]).sum()
-                    if self.ps.world_size > 1:
+                    if self.ps.dp_cp.size > 1:  # a size-1 axis has no group object, and None would mean the whole world
                         dist.all_reduce(tok, group=self.ps.dp_cp.group)
                     scale = 1.0 / max(float(tok.item()), 1.0)
                 else:
                     scale = 1.0 / gbs
                 with T.cuda_span("train_fwd_bwd"):
-                    for mb in chunk:
-                        m = self._forward_backward(mb, scale)
-                        for k, v in m.items():
-                            metrics_acc[k] = metrics_acc.get(k, 0.0) + v.detach().float() * scale
+                    if self.pipe is not None:
+                        self._forward_backward_pipelined(chunk, scale, metrics_acc)
+                    else:
+                        for mb in chunk:
+                            m = self._forward_backward(mb, scale)
+                            for k, v in m.items():
+                                metrics_acc[k] = metrics_acc.get(k, 0.0) + v.detach().float() * scale
                     self._reduce_grads()
                 with T.cuda_span("train_optimizer"):
                     if self.lora is not None:
@@ -413,6 +510,14 @@ class TrainActor:
                 dist.all_reduce(buf, group=self.ps.tp.group)
                 for n, row in zip(names, buf):
                     self.store.grads[n].copy_(row)
+        if self.ps.pp.size > 1 and self.cfg.tie_embeddings:
+            # the first stage's embedding and the last stage's LM head are one parameter: both need the summed gradient
+            H = self.cfg.hidden_size
+            ge = self.store.grads.get("embed.weight")
+            buf = ge.float() if ge is not None else torch.zeros(self.cfg.vocab_size, H, dtype=torch.float32, device=self.device)
+            dist.all_reduce(buf, group=self.ps.pp.group)
+            if ge is not None:
+                ge.copy_(buf)
         g = self.store.grad
         if self.ps.dp_cp.size > 1 and g["dense"] is not None and g["dense"].numel() and getattr(self, "dense_shard", None) is None:
             dist.all_reduce(g["dense"], group=self.ps.dp_cp.group)  # with the partitioned optimizer the step itself reduces
@@ -424,10 +529,16 @@ class TrainActor:
         vals = torch.stack([acc[k].reshape(()) for k in keys]) if keys else torch.zeros(0, device=self.device)
         extra = torch.tensor([float(n_tokens_local)], device=self.device)
         if self.ps.world_size > 1:
-            if keys:
+            if keys and self.ps.dp_cp.size > 1:
                 dist.all_reduce(vals, group=self.ps.dp_cp.group)
             dist.all_reduce(extra)
+            extra = extra / (self.ps.tp.size * self.ps.pp.size)  # ranks of one replica staged the same tokens
         out = {f"train/{k}": float(v) for k, v in zip(keys, vals.tolist())}
+        if self.ps.pp.size > 1:
+            # only the last stage computes the loss: every stage reports its metrics
+            box = [out]
+            dist.broadcast_object_list(box, src=self.ps.pp.ranks[-1], group=self.ps.pp.group)
+            out = dict(box[0])
         out["train/grad_norm"] = float(grad_norm)
         if self.opt is not None:
             from .optimizer import lr_at

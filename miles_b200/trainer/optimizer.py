@@ -67,10 +67,12 @@ def lr_at(cfg: OptimConfig, step: int) -> float:
 
 
 class FlatAdam:
-    def __init__(self, store: ParamStore, cfg: OptimConfig, dp_group=None, ep_group=None, tp_group=None, dense_shard=None):
+    def __init__(self, store: ParamStore, cfg: OptimConfig, dp_group=None, ep_group=None, tp_group=None, dense_shard=None,
+                 pp_group=None):
         self.store, self.cfg = store, cfg
         self.dp_group, self.ep_group = dp_group, ep_group
         self.tp_group = tp_group  # tensor-parallel shards count once each in the global gradient norm
+        self.pp_group = pp_group  # pipeline stages hold disjoint layers: their squared norms add up
         self.dev = store.device
         self.on_gpu = self.dev.type == "cuda"
         self.step_count = 0
@@ -163,6 +165,8 @@ class FlatAdam:
             total_sharded = sharded.clone()
             dist.all_reduce(total_sharded, group=self.tp_group)
             self.norm_buf[0:1] += total_sharded - sharded
+        if self.pp_group is not None and dist.is_initialized() and dist.get_world_size(self.pp_group) > 1:
+            dist.all_reduce(self.norm_buf, group=self.pp_group)
         total = self.norm_buf.sum().sqrt()
         self.last_grad_norm = total
         return total

@@ -34,6 +34,11 @@ def sync_weights(actor, engines: Sequence, mode: str | None = None) -> dict:
         if e.store is actor.store:
             continue  # shared memory: nothing to move
         with torch.no_grad():
+            if getattr(actor.store, "pp_size", 1) > 1 and getattr(e.store, "pp_size", 1) == 1:
+                from .reshard import gather_stages_into
+
+                moved += gather_stages_into(actor.store, e.store, actor.ps.pp)
+                continue
             for g, t in e.store.flat.items():
                 src = actor.store.flat[g]
                 if src.data_ptr() == t.data_ptr() and src.numel() == t.numel():

@@ -52,3 +52,14 @@ def test_partitioned_optimizer_matches_allreduce_adam():
            "--master-port", "29747", os.path.join(here, "mp_dp_adam_check.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "DP_ADAM_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_pipeline_parallel_model_matches_single_rank():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29749", os.path.join(here, "mp_pp_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "PP_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
