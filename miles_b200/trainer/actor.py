@@ -173,6 +173,17 @@ class TrainActor:
  lr_decay_style=a.lr_decay_style,
                          lr_warmup_iters=a.lr_warmup_iters or 0, lr_decay_iters=a.lr_decay_iters or 0, min_lr=a.min_lr,
                          lr_wsd_decay_iters=a.lr_wsd_decay_iters or 0)
+        if getattr(a, "optimizer", "adam") == "muon":
+            from .muon import Muon, MuonConfig
+
+            self.dense_shard = None
+            self.opt = Muon(self.store, oc, MuonConfig(momentum=getattr(a, "muon_momentum", 0.95), nesterov=not getattr(a, "muon_no_nesterov", False),
+                                                       ns_steps=getattr(a, "muon_num_ns_steps", 5), scale_mode=getattr(a, "muon_scale_mode", "spectral"),
+                                                       extra_scale=getattr(a, "muon_extra_scale_factor", 1.0),
+                                                       split_qkv=not getattr(a, "muon_no_split_qkv", False)),
+                            ep_group=self.ps.ep.group, tp_group=self.ps.tp.group if self.ps.tp.size > 1 else None,
+                            pp_group=self.ps.pp.group if self.ps.pp.size > 1 else None)
+            return
         dense_shard = None
         if (self.on_gpu and self.ps.dp_cp.size > 1 and self.ps.tp.size == 1 and self.store.dtype == torch.bfloat16
                 and getattr(a, "fused_comm", True) and getattr(a, "use_distributed_optimizer", True) and self.ps.dp_cp.size <= 8):

@@ -73,6 +73,9 @@ TRAINER_FLAGS = [
     ("--mscale-all-dim", "f", None, {}), ("--original-max-position-embeddings", "i", None, {}),
     ("--beta-fast", "f", None, {}), ("--beta-slow", "f", None, {}), ("--no-position-embedding", "b", False, {}),
     # optimizer / schedule
+    ("--muon-momentum", "f", 0.95, {}), ("--muon-num-ns-steps", "i", 5, {}), ("--muon-extra-scale-factor", "f", 1.0, {}),
+    ("--muon-scale-mode", "s", "spectral", {"choices": ["spectral", "unit_rms_norm"]}),
+    ("--muon-no-nesterov", "b", False, {}), ("--muon-no-split-qkv", "b", False, {}),
     ("--optimizer", "s", "adam", {"choices": ["adam", "sgd", "muon"]}), ("--lr", "f", 1e-6, {}), ("--min-lr", "f", 0.0, {}),
     ("--lr-decay-style", "s", "constant", {"choices": ["constant", "linear", "cosine", "WSD"]}),
     ("--lr-warmup-iters", "i", 0, {}), ("--lr-decay-iters", "i", None, {}), ("--lr-wsd-decay-iters", "i", None, {}),
