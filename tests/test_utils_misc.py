@@ -70,3 +70,130 @@ def test_lifecycle_sinks_do_not_raise():
     lifecycle.attempt_end(3, status="completed")
     assert [r["event"] for r in seen] == ["attempt_start", "attempt_end"] and seen[1]["status"] == "completed"
     lifecycle.clear_sinks()
+
+
+def test_dp_schedule_keeps_rollouts_together_and_balances_ranks():
+    import random
+
+    from miles_b200.utils.dp_schedule import build_dp_schedule
+
+    random.seed(0)
+    lens = [random.randint(50, 900) for _ in range(40)]
+    rids = [i // 2 for i in range(40)]  # 20 rollouts of two samples each
+    s = build_dp_schedule(lens, rids, dp_size=4, global_batch_size=8, max_tokens_per_gpu=1500, balance=True,
+                          allow_partial_step=True)
+    assert s.num_rollouts == [8, 8, 4]
+    seen = sorted(i for p in s.partitions for i in p)
+    assert seen == list(range(40))  # every sample is scheduled exactly once
+    # every rank has the same number of micro-batches per step, and no micro-batch exceeds the token budget
+    assert all(len(m) == sum(s.num_microbatches) for m in s.micro_batches)
+    for rank in range(4):
+        part, mbs = s.for_rank(rank)
+        for mb in mbs:
+            assert sum(lens[part[j]] for j in mb) <= 1500
+    # the samples of a rollout are trained in the same step
+    step_of = {}
+    for rank in range(4):
+        part, mbs = s.for_rank(rank)
+        k = 0
+        for step, n in enumerate(s.num_microbatches):
+            for mb in mbs[k:k + n]:
+                for j in mb:
+                    step_of[part[j]] = step
+            k += n
+    assert all(step_of[2 * r] == step_of[2 * r + 1] for r in range(20))
+    # without the partial step the trailing rollouts are dropped
+    s2 = build_dp_schedule(lens, rids, dp_size=4, global_batch_size=8, max_tokens_per_gpu=1500)
+    assert s2.num_rollouts == [8, 8] and len({i for p in s2.partitions for i in p}) == 32
+    # fixed micro-batch size must divide evenly
+    import pytest
+
+    with pytest.raises(ValueError):
+        build_dp_schedule(lens[:12], list(range(12)), dp_size=4, global_batch_size=12, micro_batch_size=5)
+    s3 = build_dp_schedule(lens[:16], list(range(16)), dp_size=4, global_batch_size=16, micro_batch_size=2)
+    assert s3.num_microbatches == [2]
+
+
+def test_deployment_plan_and_validation(tmp_path):
+    from types import SimpleNamespace as NS
+
+    import pytest
+    import yaml
+
+    from miles_b200.engine.deployment import Deployment
+
+    spec = {"sglang": [
+        {"name": "actor", "server_groups": [
+            {"worker_type": "prefill", "num_gpus": 2, "num_gpus_per_engine": 1},
+            {"worker_type": "decode", "num_gpus": 4, "num_gpus_per_engine": 2, "overrides": {"max_running_requests": 256}}]},
+        {"name": "reward", "model_path": "/ckpt/rm", "overrides": {"mem_fraction_static": 0.5}, "server_groups": [
+            {"worker_type": "placeholder", "num_gpus": 1}, {"worker_type": "regular", "num_gpus": 1}]}]}
+    p = tmp_path / "dep.yaml"
+    p.write_text(yaml.safe_dump(spec))
+    args = NS(hf_checkpoint="/ckpt/a", rollout_num_gpus_per_engine=1)
+    dep = Deployment.from_yaml(str(p)).resolve(args)
+    assert dep.total_num_gpus == 8 and dep.has_pd_disaggregation
+    assert dep.updatable_model().name == "actor"
+    plan = dep.plan()
+    assert [(e.model, e.worker_type, e.gpu_ids) for e in plan] == [
+        ("actor", "prefill", [0]), ("actor", "prefill", [1]), ("actor", "decode", [2, 3]), ("actor", "decode", [4, 5]),
+        ("reward", "regular", [7])]  # GPU 6 is the placeholder
+    assert plan[2].overrides == {"max_running_requests": 256} and plan[-1].overrides == {"mem_fraction_static": 0.5}
+    assert not plan[-1].update_weights
+    with pytest.raises(ValueError):
+        Deployment.from_dict({"sglang": [{"name": "a", "server_groups": [{"worker_type": "prefill", "num_gpus": 1}]}]}).resolve(args)
+    with pytest.raises(ValueError):
+        Deployment.from_dict({"sglang": [{"name": "a", "server_groups": [{"worker_type": "regular", "num_gpus": 3, "num_gpus_per_engine": 2}]}]}).resolve(args)
+    with pytest.raises(ValueError):
+        Deployment.from_dict({"sglang": [{"name": "a", "server_groups": [{"worker_type": "bogus", "num_gpus": 1}]}]})
+    d2 = Deployment.from_args(NS(rollout_num_gpus=8, rollout_num_gpus_per_engine=2, prefill_num_servers=1)).resolve(args)
+    assert [g.worker_type for g in d2.models[0].server_groups] == ["prefill", "decode"] and len(d2.plan()) == 4
+
+
+def test_env_report_round_trip():
+    from miles_b200.utils import env_report as E
+
+    rep = E.collect()
+    d = E.decode("worker log prefix " + E.encode(rep))
+    assert d["python"] == rep.python and "torch" in d["packages"]
+    assert E.decode("no report here") is None
+    other = dict(d, python="0.0")
+    assert ("python", d["python"], "0.0") in E.diff(d, other)
+
+
+def test_eval_dispatcher_runs_in_background_and_skips_when_busy(tmp_path):
+    import asyncio
+    import os
+
+    from miles_b200.rollout.eval_dispatch import CheckpointEvalFn, EvalDispatcher, EvalSkip, is_checkpoint_eval_fn
+
+    class MyEval(CheckpointEvalFn):
+        async def evaluate_checkpoint(self, checkpoint_dir, rollout_id):
+            if rollout_id == 7:
+                raise EvalSkip("no data")
+            assert os.path.exists(os.path.join(checkpoint_dir, "w.bin"))
+            await asyncio.sleep(0.05)
+            return {"eval/score": float(rollout_id)}
+
+    assert is_checkpoint_eval_fn(MyEval) and not is_checkpoint_eval_fn(int)
+
+    async def export(rid, d):
+        os.makedirs(d, exist_ok=True)
+        open(os.path.join(d, "w.bin"), "wb").write(b"x")
+
+    seen = []
+
+    async def main():
+        disp = EvalDispatcher(MyEval(None), export_fn=export, on_result=lambda r, m: seen.append((r, m)))
+        assert await disp.dispatch(1, str(tmp_path / "e1"))
+        assert disp.busy
+        assert not await disp.dispatch(2, str(tmp_path / "e2"))          # one evaluation at a time
+        assert await disp.dispatch(3, str(tmp_path / "e3"), force=True)  # waits for #1, then runs
+        assert await disp.dispatch(7, str(tmp_path / "e7"), force=True)
+        await disp.drain()
+        return disp
+
+    disp = asyncio.run(main())
+    assert [r for r, _ in seen] == [1, 3, 7] and disp.skipped == [2]
+    assert seen[0][1]["eval/score"] == 1.0 and seen[2][1]["eval/skipped"] == 1.0
+    assert not os.path.exists(tmp_path / "e1")  # snapshots are removed once evaluated
