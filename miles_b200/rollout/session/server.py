@@ -20,7 +20,7 @@ from .trajectory import LinearTrajectory
 
 
 class SessionStore:
-    def __init__(self, tokenizer, generate: Callable, max_sessions: int = 4096):
+    def __init__(self, tokenizer, generate: Callable, max_sessions: int = 4096, tito: bool = False, family: Optional[str] = None):
         """``generate(input_ids, sampling_params) -> dict`` with ``output_ids``, ``output_token_logprobs`` (floats),
         ``finish_reason`` and optionally ``weight_version`` (a blocking call into the engine client)."""
         self.tok, self.generate = tokenizer, generate
@@ -28,6 +28,11 @@ class SessionStore:
         self._lock = threading.Lock()
         self.sessions: dict = {}
         self._rendered: dict = {}  # session id -> text of the conversation rendered so far (for delta rendering)
+        self.tito = None
+        if tito:
+            from .tito import TitoTokenizer
+
+            self.tito = TitoTokenizer(tokenizer, family)
 
     def get(self, sid: str) -> LinearTrajectory:
         with self._lock:
@@ -53,10 +58,30 @@ class SessionStore:
     def _encode(self, text: str) -> list:
         return list(self.tok.encode(text, add_special_tokens=False)) if text else []
 
+    def _chat_tito(self, traj, messages: list, sampling_params: dict) -> dict:
+        """Token-level path: nothing already in the trajectory is rendered again; a later request contributes only
+        its messages after the ones the session has seen (the assistant message among them is the turn the session
+        generated itself and is skipped)."""
+        if not traj.tokens:
+            traj.append_context(messages[-1]["role"] if messages else "user", self.tito.initial(messages))
+        else:
+            new = [m for m in messages[traj.num_messages:] if m.get("role") != "assistant"]
+            last = traj.turns[-1]
+            traj.append_context(new[-1]["role"] if new else "user", self.tito.continuation(traj.tokens[last.start:last.end], new))
+        out = self.generate(list(traj.tokens), dict(sampling_params))
+        ids = list(out["output_ids"])
+        lps = [float(x[0]) if isinstance(x, (list, tuple)) else float(x) for x in out.get("output_token_logprobs", [0.0] * len(ids))]
+        traj.append_generation(ids, lps, out.get("weight_version"), out.get("finish_reason"))
+        traj.num_messages = len(messages) + 1
+        text = self.tok.decode(ids, skip_special_tokens=True) if hasattr(self.tok, "decode") else ""
+        return {"text": text, "ids": ids, "finish_reason": out.get("finish_reason", "stop")}
+
     def chat(self, sid: str, messages: list, sampling_params: dict) -> dict:
         traj = self.get(sid)
         if len(messages) < traj.num_messages:
             raise ValueError("the request holds fewer messages than the session: a session only moves forward")
+        if getattr(self, "tito", None) is not None:
+            return self._chat_tito(traj, messages, sampling_params)
         full = self._render(messages, add_generation_prompt=True)
         seen = self._rendered[sid]
         if not full.startswith(seen):

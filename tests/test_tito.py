@@ -1,0 +1,121 @@
+"""Token-in-token-out tokenisation and tree trajectories (toy tokenizer whose merges would cross turn boundaries)."""
+from miles_b200.rollout.session.tito import FAMILIES, TitoTokenizer, TreeTrajectory
+
+
+class ToyTokenizer:
+    """Specials are single tokens; ordinary text is tokenised greedily in pairs of characters, so the split of a
+    text depends on where it starts: exactly the effect that breaks re-tokenisation across boundaries."""
+    chat_template = None
+    name_or_path = "toy"
+    SPECIALS = ["<|im_start|>", "<|im_end|>"]
+
+    def __init__(self):
+        self.vocab, self.inv = {}, []
+
+    def _id(self, s):
+        if s not in self.vocab:
+            self.vocab[s] = len(self.inv)
+            self.inv.append(s)
+        return self.vocab[s]
+
+    def encode(self, text, add_special_tokens=False):
+        out, i = [], 0
+        while i < len(text):
+            sp = next((s for s in self.SPECIALS if text.startswith(s, i)), None)
+            if sp:
+                out.append(self._id(sp))
+                i += len(sp)
+                continue
+            j = min([text.find(s, i) for s in self.SPECIALS if text.find(s, i) >= 0] + [len(text)])
+            chunk = text[i:j]
+            out += [self._id(chunk[k:k + 2]) for k in range(0, len(chunk), 2)]
+            i = j
+        return out
+
+    def decode(self, ids, skip_special_tokens=False):
+        return "".join(self.inv[i] for i in ids)
+
+
+def test_incremental_ids_equal_full_rendering_when_turns_are_closed():
+    tok = ToyTokenizer()
+    t = TitoTokenizer(tok, "chatml")
+    msgs = [{"role": "system", "content": "sys"}, {"role": "user", "content": "hello"}]
+    traj = t.initial(msgs)
+    assert tok.decode(traj) == "<|im_start|>system\nsys<|im_end|>\n<|im_start|>user\nhello<|im_end|>\n<|im_start|>assistant\n"
+    gen = tok.encode("abc<|im_end|>")  # engine output, closed turn
+    traj += gen
+    new = [{"role": "tool", "content": "result"}]
+    traj += t.continuation(gen, new)
+    msgs2 = msgs + [{"role": "assistant", "content": "abc"}] + new
+    assert t.consistent_with_template(traj, msgs2) is True
+
+
+def test_boundary_fix_closes_an_open_turn_without_touching_generated_tokens():
+    tok = ToyTokenizer()
+    t = TitoTokenizer(tok, "chatml")
+    traj = t.initial([{"role": "user", "content": "q"}])
+    gen = tok.encode("abc")  # stopped by length: no end-of-turn token; "abc" tokenises as "ab","c"
+    n0 = len(traj)
+    traj += gen
+    cont = t.continuation(gen, [{"role": "user", "content": "next"}])
+    traj += cont
+    assert traj[n0:n0 + len(gen)] == gen  # the sampled ids are kept as they are
+    assert tok.decode(cont).startswith("<|im_end|>\n<|im_start|>user\nnext<|im_end|>\n<|im_start|>assistant\n")
+    # a naive re-tokenisation of the text would merge differently: "c" + "\n" etc. The fix is tokenised on its own
+    assert cont[:2] == tok.encode("<|im_end|>") + tok.encode("\n")
+    assert t.boundary_fix(tok.encode("abc<|im_end|>")) == tok.encode("\n")
+
+
+def test_history_rewriting_family_is_not_compared_with_the_template():
+    t = TitoTokenizer(ToyTokenizer(), "qwen3")
+    assert FAMILIES["qwen3"].rewrites_history and t.consistent_with_template([1, 2], []) is None
+
+
+def test_tree_trajectory_branches_at_the_common_prefix():
+    tr = TreeTrajectory("s1")
+    tr.append([1, 2, 3], generated=False)
+    tr.append([10, 11], generated=True, log_probs=[-0.1, -0.2])
+    tr.append([4, 5], generated=False)
+    tr.append([12], generated=True, log_probs=[-0.3])
+    assert tr.tokens_to() == [1, 2, 3, 10, 11, 4, 5, 12]
+    # a request whose history is the first 4 tokens followed by something else: branch inside the first node
+    m = tr.seek([1, 2, 3, 10, 99])
+    assert m == 4
+    tr.append([99, 98], generated=False)
+    tr.append([13, 14], generated=True, log_probs=[-0.4, -0.5])
+    samples = tr.to_sample_dicts()
+    toks = sorted(s["tokens"] for s in samples)
+    assert toks == [[1, 2, 3, 10, 11, 4, 5, 12], [1, 2, 3, 10, 99, 98, 13, 14]]
+    for s in samples:
+        assert len(s["loss_mask"]) == s["response_length"] == len(s["tokens"]) - 3
+        assert s["rollout_id_key"] == "s1"
+    b = next(s for s in samples if s["tokens"][-1] == 14)
+    assert b["loss_mask"] == [1, 0, 0, 1, 1] and b["rollout_log_probs"][0] == -0.1
+    # seeking the full first path lands on its leaf and extends it
+    assert tr.seek([1, 2, 3, 10, 11, 4, 5, 12]) == 8
+    tr.append([6], generated=False)
+    assert tr.tokens_to()[-2:] == [12, 6]
+
+
+def test_session_store_token_level_mode():
+    from miles_b200.rollout.session.server import SessionStore
+
+    tok = ToyTokenizer()
+    outs = iter([tok.encode("abc"), tok.encode("done<|im_end|>")])
+
+    def gen(ids, sp):
+        o = next(outs)
+        return {"output_ids": o, "output_token_logprobs": [-0.5] * len(o), "finish_reason": "stop", "weight_version": 3}
+
+    st = SessionStore(tok, gen, tito=True, family="chatml")
+    m1 = [{"role": "user", "content": "q"}]
+    r1 = st.chat("s", m1, {})
+    assert r1["text"] == "abc"
+    m2 = m1 + [{"role": "assistant", "content": "abc"}, {"role": "tool", "content": "t"}]
+    st.chat("s", m2, {})
+    traj = st.sessions["s"]
+    text = tok.decode(traj.tokens)
+    assert text == ("<|im_start|>user\nq<|im_end|>\n<|im_start|>assistant\nabc<|im_end|>\n<|im_start|>tool\nt<|im_end|>\n"
+                    "<|im_start|>assistant\ndone<|im_end|>")
+    d = traj.to_sample_dict()
+    assert sum(d["loss_mask"]) == len(tok.encode("abc")) + len(tok.encode("done<|im_end|>"))
