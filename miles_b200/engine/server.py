@@ -154,6 +154,10 @@ def build_app(engine: Engine, tokenizer=None, model_path: str = ""):
             return {"success": True, "checksum": engine.store.checksum()}
         raise HTTPException(400, f"unknown action {action!r}")
 
+    from .server_extra import register_extra
+
+    register_extra(app, engine, snapshot)
+
     @app.get("/metrics")
     async def metrics():
         s = engine.stats

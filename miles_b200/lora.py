@@ -181,3 +181,25 @@ class LoRAManager:
     def adapter_tensors(self):
         """(hf name, tensor) pairs of the adapter only — what an external engine would load."""
         return list(self.state_dict().items())
+
+
+@torch.no_grad()
+def merge_adapter_into(store: ParamStore, tensors: dict, scale: float = 1.0) -> int:
+    """Add ``scale * B @ A`` of a PEFT-named adapter (``...<module>.lora_A.weight`` / ``lora_B.weight``) into the
+    weights of ``store``; a negative ``scale`` takes the same adapter out again. Returns the number of modules merged.
+    Engines use it to serve an adapter without a second set of GEMMs."""
+    by_module = {t.hf_module: t for t in _targets(store, ALL_LINEAR)}
+    n = 0
+    for key, a in tensors.items():
+        if not key.endswith("lora_A.weight"):
+            continue
+        mod = key[:-len(".lora_A.weight")]
+        mod = mod[len("base_model.model."):] if mod.startswith("base_model.model.") else mod
+        b = tensors.get(key.replace("lora_A.weight", "lora_B.weight"))
+        t = by_module.get(mod)
+        if b is None or t is None:
+            continue
+        w = LoRAManager._slice(store.params[t.native], t)
+        w.add_((scale * (b.to(w.device).float() @ a.to(w.device).float())).to(w.dtype))
+        n += 1
+    return n

@@ -105,3 +105,15 @@ class DiskDeltaReader:
                 n += 1
         self.version = version
         return n
+
+
+def apply_delta_dir(store, path: str) -> int:
+    """Apply one published version directory (``.../v%08d``) to a parameter store; the store remembers the version
+    it holds so that an XOR delta is only applied on top of its base."""
+    path = path.rstrip("/")
+    version = int(os.path.basename(path).lstrip("v"))
+    reader = getattr(store, "_delta_reader", None)
+    if reader is None or reader.dir != os.path.dirname(path):
+        reader = DiskDeltaReader(os.path.dirname(path))
+        store._delta_reader = reader
+    return reader.apply(version, store.params)

@@ -1,0 +1,104 @@
+"""Weight update over a dedicated process group (gloo, two processes) and the engine endpoints around it."""
+import socket
+
+import torch
+import torch.multiprocessing as mp
+
+from miles_b200.models import ParamStore, get_config
+from miles_b200.weight_sync.broadcast import (bucket_header, destroy_update_group, init_update_group, iter_buckets,
+                                              receive_bucket, send_bucket)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_iter_buckets_respects_the_byte_limit():
+    ts = [(f"t{i}", torch.zeros(n)) for i, n in enumerate([10, 10, 100, 5, 5, 5])]
+    bs = list(iter_buckets(ts, 100))  # 100 bytes = 25 floats
+    assert [[n for n, _ in b] for b in bs] == [["t0", "t1"], ["t2"], ["t3", "t4", "t5"]]
+
+
+def _proc(rank, port, q_hdr, ret):
+    cfg = get_config("qwen3-tiny")
+    init_update_group("127.0.0.1", port, rank, 2, "w", backend="gloo", timeout_s=60)
+    if rank == 0:  # trainer
+        src = ParamStore(cfg, "cpu", torch.float32, seed=1)
+        for bucket in iter_buckets(src.params.items(), 1 << 20):
+            q_hdr.put(bucket_header(bucket, "w"))
+            send_bucket(bucket, "w")
+        q_hdr.put(None)
+        ret[0] = src.checksum()
+    else:          # engine
+        dst = ParamStore(cfg, "cpu", torch.float32, seed=2)
+        n = 0
+        while True:
+            hdr = q_hdr.get()
+            if hdr is None:
+                break
+            n += receive_bucket(hdr, dst)
+        ret[1] = (dst.checksum(), n, len(dst.params))
+    assert destroy_update_group("w")
+
+
+def test_broadcast_update_between_two_processes():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    ps = [ctx.Process(target=_proc, args=(r, port, q, ret)) for r in range(2)]
+    for p in ps:
+        p.start()
+    for p in ps:
+        p.join(120)
+        assert p.exitcode == 0
+    (chk, n, total) = ret[1]
+    assert n == total and chk == ret[0]
+
+
+def test_engine_endpoints_adapters_profile_and_layout(tmp_path):
+    from fastapi.testclient import TestClient
+
+    from miles_b200.engine import Engine
+    from miles_b200.engine.server import build_app
+    from miles_b200.lora import LoRAManager
+    from miles_b200.models import build_model
+    from miles_b200.weight_sync.disk_delta import DiskDeltaWriter
+    from miles_b200.weight_sync.registry import put_bucket
+
+    cfg = get_config("qwen3-tiny")
+    st = ParamStore(cfg, "cpu", torch.float32, seed=11)
+    eng = Engine(build_model(cfg, st), max_running=2, page_size=8, max_seq_len=64)
+    c = TestClient(build_app(eng))
+    assert c.get("/parallelism_config").json()["tp_size"] == 1
+    # adapter round trip: load changes the weights, unload restores them
+    other = ParamStore(cfg, "cpu", torch.float32, seed=11)
+    lm = LoRAManager(other, 4, 8, "all-linear", lr=1e-3, weight_decay=0.0, seed=3)
+    for b in lm.B:
+        b.data.normal_(0, 0.05)
+    before = {g: t.clone() for g, t in st.flat.items()}
+    bid = put_bucket(lm.adapter_tensors())
+    r = c.post("/load_lora_adapter_from_tensors", json={"lora_name": "a1", "bucket_id": bid, "scaling": lm.scale})
+    assert r.status_code == 200 and r.json()["loaded_adapters"] == ["a1"]
+    assert not torch.equal(st.flat["dense"], before["dense"])
+    lm.merge()
+    assert torch.allclose(st.flat["dense"], other.flat["dense"], atol=1e-5)  # same result as the trainer-side merge
+    assert c.post("/unload_lora_adapter", json={"lora_name": "a1"}).status_code == 200
+    assert torch.allclose(st.flat["dense"], before["dense"], atol=1e-5)
+    assert c.post("/unload_lora_adapter", json={"lora_name": "a1"}).status_code == 404
+    # profile
+    assert c.post("/start_profile", json={"output_dir": str(tmp_path), "activities": ["CPU"]}).status_code == 200
+    assert c.post("/start_profile", json={}).status_code == 409
+    tr = c.post("/stop_profile").json()["trace"]
+    import os
+
+    assert os.path.exists(tr)
+    # pull a published delta
+    new = ParamStore(cfg, "cpu", torch.float32, seed=99)
+    w = DiskDeltaWriter(str(tmp_path / "delta"), encoding="overwrite")
+    w.write(list(new.params.items()), version=1)
+    r = c.post("/pull_weights", json={"path": str(tmp_path / "delta" / "v00000001"), "weight_version": 1})
+    assert r.status_code == 200 and r.json()["num_tensors"] == len(new.params)
+    assert torch.equal(st.flat["dense"], new.flat["dense"]) and eng.weight_version == 1
