@@ -98,6 +98,8 @@ def main() -> None:
     ap.add_argument("--max-tokens-per-gpu", type=int, default=32768)
     ap.add_argument("--no-routing-replay", action="store_true")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (dense models; the rest of the GPUs are data parallel)")
+    ap.add_argument("--rollout-quantization", default="none", choices=["none", "mxfp8", "nvfp4"],
+                    help="serve the rollout from block-scaled copies of the weights (not the headline configuration)")
     ap.add_argument("--pp", type=int, default=1, help="pipeline-parallel size (experts are then not expert parallel)")
     ns = ap.parse_args()
     if ns.impl == "reference":
@@ -130,6 +132,8 @@ def main() -> None:
     ]
     if not ns.no_routing_replay:
         flags += ["--use-rollout-routing-replay"]
+    if ns.rollout_quantization != "none":
+        flags += ["--rollout-quantization", ns.rollout_quantization]
     t_start = time.perf_counter()
     args = parse_args(flags)
     args.synthetic_prompt_len = ns.prompt_len
@@ -190,7 +194,7 @@ def main() -> None:
             "metric": f"GRPO tokens/s/step (prompt+response tokens / (rollout + logprob + train + weight sync)), {cfg.name}",
             "value": tokens / dev_s, "unit": "tokens/s", "n_gpus": world, "steps": ns.steps, "warmup": ns.warmup,
             "ms_per_step": dev_s * 1e3 / ns.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic (uniform random 1024-token prompts, random-init weights, forced log-normal response lengths)",
+            "dtype": "bf16" if ns.rollout_quantization == "none" else f"bf16 training, {ns.rollout_quantization} rollout GEMMs", "data": "synthetic (uniform random 1024-token prompts, random-init weights, forced log-normal response lengths)",
             "config": {
                 "model": cfg.name, "params_b": round(cfg.num_params() / 1e9, 2), "global_batch": n_prompts * ns.samples_per_prompt,
                 "prompts": n_prompts, "samples_per_prompt": ns.samples_per_prompt, "seq_len": ns.prompt_len + ns.max_response_len,

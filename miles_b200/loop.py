@@ -151,6 +151,14 @@ class RLLoop:
 
             sync = LockstepSync(self.ps.gloo_world if self.ps.backend != "gloo" else None)
             ep_decode = ExpertParallel(cfg, self.ps, fused=getattr(a, "fused_comm", True), max_tokens=max(max_running, 16))
+        quant = getattr(a, "rollout_quantization", "none")
+        if quant != "none" and self.actor.on_gpu and not self.actor.is_torch:
+            if engine_model is self.actor.model:
+                # the trainer keeps multiplying bf16 weights: the engine gets a model object of its own on the same store
+                from .models import build_model
+
+                engine_model = build_model(cfg, self.actor.store, "b200", ep=self.actor.ep_dispatcher, tp=self.actor.tp_exchange)
+            engine_model.enable_block_scaled(quant)
         self.engine = Engine(engine_model, sync=sync, ep_decode=ep_decode, max_running=max_running, page_size=page, max_seq_len=max_ctx,
                              max_prefill_tokens=getattr(a, "engine_max_prefill_tokens", 16384), kv_mem_bytes=kv_bytes,
                              use_cuda_graph=not getattr(a, "sglang_disable_cuda_graph", False) and self.actor.on_gpu,

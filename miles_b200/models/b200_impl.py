@@ -43,6 +43,7 @@ class MoeCtx:
     tile_group: torch.Tensor
     num_tiles: torch.Tensor
     max_rows: int
+    align: int = 1
 
 
 class B200Qwen3:
@@ -74,9 +75,44 @@ class B200Qwen3:
         self.launches += 1
         return out
 
+    # ------------------------------------------------------------------ block-scaled inference weights
+    MX_SUFFIXES = ("attn.qkv.weight", "attn.o.weight", "mlp.gate_up.weight", "mlp.down.weight", "moe.w1", "moe.w2")
+
+    def enable_block_scaled(self, kind: str) -> int:
+        """Serve the projections and experts from MXFP8 / NVFP4 copies of the weights (`csrc/gemm_mx.cu`) whenever
+        more than 32 rows are multiplied; the few-row decode kernels keep streaming the bf16 weights. Meant for a
+        model object that only the rollout engine uses. Call again (or `refresh_block_scaled`) after a weight update.
+        Returns the number of tensors quantised."""
+        from ..ops.mx_gemm import quantize_operand
+
+        step = 128 if kind == "mxfp8" else 256
+        self.mx_kind, self.mx = kind, {}
+        for name, w in self.store.params.items():
+            if not name.endswith(self.MX_SUFFIXES):
+                continue
+            w2 = w.reshape(-1, w.shape[-1])
+            if w2.shape[1] % step or w2.shape[0] % 128:
+                continue
+            self.mx[w.data_ptr()] = quantize_operand(w2, kind)
+        return len(self.mx)
+
+    def refresh_block_scaled(self) -> None:
+        if getattr(self, "mx", None):
+            self.enable_block_scaled(self.mx_kind)
+
+    def _mx_linear(self, x, wq, tile_group=None, num_tiles=None, n: int = 0):
+        from ..ops.mx_gemm import mx_linear, quantize_operand
+
+        xq = quantize_operand(x, self.mx_kind)
+        self.launches += 3
+        return mx_linear(xq, wq, self.status, tile_group, num_tiles, n)
+
     def linear(self, x, w, out_dtype=torch.bfloat16):
-        out = torch.empty(x.shape[0], w.shape[0], dtype=out_dtype, device=x.device)
         T, (N, K) = x.shape[0], w.shape
+        mx = getattr(self, "mx", None)
+        if mx and T > 32 and out_dtype == torch.bfloat16 and w.data_ptr() in mx:
+            return self._mx_linear(x.contiguous(), mx[w.data_ptr()])
+        out = torch.empty(x.shape[0], w.shape[0], dtype=out_dtype, device=x.device)
         if T <= 32 and self.small_decode and N % 16 == 0 and K % 32 == 0 and N * K * 2 < (48 << 20) and x.is_contiguous():
             # a few rows against a small weight matrix (decode projections): the weight-streaming mma.sync kernel
             # (measured: faster than the narrow tcgen05 tiles up to 32 rows, slower at 64)
@@ -115,13 +151,22 @@ class B200Qwen3:
         max_rows = max(T * K + E_local * (align - 1), 1)
         counts, offsets, dest, src, tg, nt = self.C.moe_build_permutation(ids, E_local, max_rows, align)
         self.launches += 3
-        return MoeCtx(ids, None, None, offsets, dest, src, tg, nt, max_rows)
+        ctx = MoeCtx(ids, None, None, offsets, dest, src, tg, nt, max_rows)
+        ctx.align = align
+        return ctx
 
     def _experts_fwd(self, xp, plan: MoeCtx, w1, w2, keep: bool, scatter=None):
         """``scatter = (row_ptrs, ctrl, flag_ptrs, rank)``: the second GEMM stores every output row at its own
         address (the expert-parallel return buffers of the ranks the tokens came from) and raises their flags."""
         C = self.C
         I2 = w1.shape[1]
+        mx = getattr(self, "mx", None)
+        if mx and not keep and scatter is None and w1.data_ptr() in mx and w2.data_ptr() in mx and plan.align == 128:
+            gu = self._mx_linear(xp, mx[w1.data_ptr()], plan.tile_group, plan.num_tiles, I2)
+            act = C.swiglu_fwd(gu)
+            yp = self._mx_linear(act, mx[w2.data_ptr()], plan.tile_group, plan.num_tiles, w2.shape[1])
+            self.launches += 1
+            return None, None, yp
         gu = torch.empty(plan.max_rows, I2, dtype=torch.bfloat16, device=xp.device)
         C.grouped_gemm_rows(xp, w1, gu, plan.tile_group, plan.num_tiles, False, False, 0, self.status)
         act = C.swiglu_fwd(gu)
@@ -142,7 +187,8 @@ class B200Qwen3:
             record.append(ids)
         if self.ep is not None:
             return self.ep.moe_forward(self, i, h2, ids, w, probs, keep, residual)
-        plan = self._permute_plan(ids, cfg.num_experts, 64 if keep else 1)
+        use_mx = bool(getattr(self, "mx", None)) and not keep and h2.shape[0] > 32
+        plan = self._permute_plan(ids, cfg.num_experts, 64 if keep else (128 if use_mx else 1))
         plan.w, plan.probs = w, probs
         xp = C.moe_permute(h2, plan.src, plan.num_tiles, cfg.moe_top_k)
         gu, act, yp = self._experts_fwd(xp, plan, P[p + "w1"], P[p + "w2"], keep)

@@ -73,6 +73,7 @@ TRAINER_FLAGS = [
     ("--mscale-all-dim", "f", None, {}), ("--original-max-position-embeddings", "i", None, {}),
     ("--beta-fast", "f", None, {}), ("--beta-slow", "f", None, {}), ("--no-position-embedding", "b", False, {}),
     # optimizer / schedule
+    ("--rollout-quantization", "s", "none", {"choices": ["none", "mxfp8", "nvfp4"]}),
     ("--muon-momentum", "f", 0.95, {}), ("--muon-num-ns-steps", "i", 5, {}), ("--muon-extra-scale-factor", "f", 1.0, {}),
     ("--muon-scale-mode", "s", "spectral", {"choices": ["spectral", "unit_rms_norm"]}),
     ("--muon-no-nesterov", "b", False, {}), ("--muon-no-split-qkv", "b", False, {}),

@@ -55,6 +55,10 @@ def sync_weights(actor, engines: Sequence, mode: str | None = None) -> dict:
                     from .reshard import reshard_into
 
                     moved += reshard_into(actor.store, e.store, g)
+    for e in engines:
+        refresh = getattr(getattr(e, "model", None), "refresh_block_scaled", None)
+        if refresh is not None:
+            refresh()  # engines that serve MXFP8 / NVFP4 copies re-quantise from the weights that just arrived
     if actor.on_gpu:
         torch.cuda.synchronize()
     version = actor.store.version

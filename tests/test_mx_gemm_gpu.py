@@ -80,3 +80,45 @@ def test_mx_gemm_grouped_rows(kind, block_n):
     for gi, r0, nr, _ in tiles:
         ref = xa[r0:r0 + nr] @ wb[gi * N:(gi + 1) * N].t()
         assert (y[r0:r0 + nr] - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3, (kind, gi)
+
+
+@pytest.mark.parametrize("kind", ["mxfp8", "nvfp4"])
+@pytest.mark.parametrize("preset", ["qwen3-smoke", "qwen3-smoke-moe"])
+def test_model_forward_with_block_scaled_weights(preset, kind):
+    """The inference forward with quantised projections / experts stays close to the bf16 forward."""
+    from miles_b200.models import ParamStore, build_model, get_config
+
+    cfg = get_config(preset)
+    store = ParamStore(cfg, "cuda", torch.bfloat16, init_std=0.05, seed=5)
+    model = build_model(cfg, store, "b200")
+    g = torch.Generator().manual_seed(1)
+    lens = [150, 90]
+    T = sum(lens)
+    tokens = torch.randint(0, cfg.vocab_size, (T,), generator=g).cuda().int()
+    pos = torch.cat([torch.arange(l) for l in lens]).cuda().int()
+    cu = torch.tensor([0, 150, 240], dtype=torch.int32, device="cuda")
+    rows = torch.arange(0, T - 1).cuda()
+    tg = tokens[(rows + 1).long()]
+    lp_ref, _ = model.forward_logprobs(tokens, pos, cu, rows, tg, 1.0)
+    n = model.enable_block_scaled(kind)
+    assert n >= 4 * cfg.num_layers
+    calls = {"n": 0}
+    orig = model._mx_linear
+
+    def counted(*a, **k):
+        calls["n"] += 1
+        return orig(*a, **k)
+
+    model._mx_linear = counted
+    lp_q, _ = model.forward_logprobs(tokens, pos, cu, rows, tg, 1.0)
+    model.check_status()
+    assert calls["n"] >= 4 * cfg.num_layers
+    assert torch.isfinite(lp_q).all()
+    d = (lp_q - lp_ref).abs()
+    lim = 0.08 if kind == "mxfp8" else 0.35
+    assert d.mean().item() < lim, (preset, kind, d.mean().item(), d.max().item())
+    # a weight update is picked up by refresh
+    store.params["layers.0.attn.o.weight"].mul_(0.5)
+    model.refresh_block_scaled()
+    lp_u, _ = model.forward_logprobs(tokens, pos, cu, rows, tg, 1.0)
+    assert (lp_u - lp_q).abs().max().item() > 0
