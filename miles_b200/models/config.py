@@ -183,6 +183,24 @@ PRESETS: dict[str, ModelConfig] = {
                            rope_theta=1e6, hf_architecture="Qwen2ForCausalLM"),
     "qwen2.5-7B": _dense("qwen2.5-7B", 28, 3584, 28, 4, 18944, False, vocab=152064, qk_norm=False, qkv_bias=True,
                          hf_architecture="Qwen2ForCausalLM"),
+    "qwen2.5-1.5B": _dense("qwen2.5-1.5B", 28, 1536, 12, 2, 8960, True, qk_norm=False, qkv_bias=True, rope_theta=1e6,
+                           hf_architecture="Qwen2ForCausalLM"),
+    "qwen2.5-3B": _dense("qwen2.5-3B", 36, 2048, 16, 2, 11008, True, qk_norm=False, qkv_bias=True, rope_theta=1e6,
+                         hf_architecture="Qwen2ForCausalLM"),
+    "qwen2.5-14B": _dense("qwen2.5-14B", 48, 5120, 40, 8, 13824, False, vocab=152064, qk_norm=False, qkv_bias=True, rope_theta=1e6,
+                          hf_architecture="Qwen2ForCausalLM"),
+    "qwen2.5-32B": _dense("qwen2.5-32B", 64, 5120, 40, 8, 27648, False, vocab=152064, qk_norm=False, qkv_bias=True, rope_theta=1e6,
+                          hf_architecture="Qwen2ForCausalLM"),
+    "qwen2.5-72B": _dense("qwen2.5-72B", 80, 8192, 64, 8, 29568, False, vocab=152064, qk_norm=False, qkv_bias=True, rope_theta=1e6,
+                          hf_architecture="Qwen2ForCausalLM"),
+    "llama-3.2-1B": _dense("llama-3.2-1B", 16, 2048, 32, 8, 8192, True, vocab=128256, hd=64, qk_norm=False,
+                           rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+    "llama-3.2-3B": _dense("llama-3.2-3B", 28, 3072, 24, 8, 8192, True, vocab=128256, qk_norm=False,
+                           rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+    "llama-3.1-70B": _dense("llama-3.1-70B", 80, 8192, 64, 8, 28672, False, vocab=128256, qk_norm=False,
+                            rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+    "mistral-7B": _dense("mistral-7B", 32, 4096, 32, 8, 14336, False, vocab=32768, qk_norm=False,
+                         rope_theta=1e6, rms_eps=1e-5, hf_architecture="MistralForCausalLM"),
     "llama-3.1-8B": _dense("llama-3.1-8B", 32, 4096, 32, 8, 14336, False, vocab=128256, qk_norm=False,
                            rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
 }
