@@ -349,6 +349,37 @@ def validate_args(args: argparse.Namespace) -> argparse.Namespace:
     return args
 
 
+def hf_validate_args(args, hf_config: dict) -> None:
+    """When both an HF checkpoint and explicit shape flags are given they must describe the same model: compares
+    every shape flag that was set against ``config.json`` and reports all mismatches at once
+    (reference: miles/utils/arguments.py:3656-3707)."""
+    cfg = dict(hf_config.get("text_config", hf_config))  # multimodal configs nest the language model
+    rope = cfg.get("rope_parameters")
+    if isinstance(rope, dict) and "rope_theta" not in cfg:
+        theta = rope.get("rope_theta") or next((v["rope_theta"] for v in rope.values() if isinstance(v, dict) and "rope_theta" in v), None)
+        if theta is not None:
+            cfg["rope_theta"] = theta
+    same = lambda a, b: a == b
+    close = lambda a, b: abs(float(a) - float(b)) <= 1e-12 + 1e-6 * abs(float(b))
+    table = [("hidden_size", "hidden_size", same), ("num_attention_heads", "num_attention_heads", same),
+             ("num_key_value_heads", "num_query_groups", same), ("num_hidden_layers", "num_layers", same),
+             ("intermediate_size", "ffn_hidden_size", same), ("moe_intermediate_size", "moe_ffn_hidden_size", same),
+             ("num_experts", "num_experts", same), ("num_experts_per_tok", "moe_router_topk", same),
+             ("tie_word_embeddings", "untie_embeddings_and_output_weights", lambda h, a: bool(h) != bool(a)),
+             ("rms_norm_eps", "norm_epsilon", close), ("rope_theta", "rotary_base", close), ("head_dim", "kv_channels", same)]
+    errors = []
+    for hf_key, flag, ok in table:
+        have = getattr(args, flag, None)
+        if hf_key not in cfg or have is None:
+            continue
+        if flag == "untie_embeddings_and_output_weights" and not getattr(args, "num_layers", None):
+            continue  # a store_true flag is only meaningful when the shape was given by flags at all
+        if not ok(cfg[hf_key], have):
+            errors.append(f"{hf_key}={cfg[hf_key]!r} in the checkpoint config but --{flag.replace('_', '-')} is {have!r}")
+    if errors:
+        raise AssertionError("model shape flags contradict the HF checkpoint: " + "; ".join(errors))
+
+
 def model_config_from_args(args):
     """Build a ``ModelConfig`` from a preset, an HF checkpoint dir, or Megatron-style shape flags."""
     from ..models.config import ModelConfig, get_config
@@ -356,6 +387,10 @@ def model_config_from_args(args):
     if getattr(args, "model_preset", None):
         return get_config(args.model_preset)
     if getattr(args, "hf_checkpoint", None) and os.path.exists(os.path.join(args.hf_checkpoint, "config.json")):
+        import json
+
+        with open(os.path.join(args.hf_checkpoint, "config.json")) as f:
+            hf_validate_args(args, json.load(f))
         return ModelConfig.from_hf_config(args.hf_checkpoint)
     assert args.num_layers and args.hidden_size and args.num_attention_heads, \
         "model shape needs --model-preset, --hf-checkpoint or the --num-layers/--hidden-size/... flags"

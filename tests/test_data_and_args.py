@@ -98,3 +98,25 @@ def test_flag_surface_and_validation():
         _args(["--multi-latent-attention"])
     with pytest.raises(SystemExit):
         _args(["--definitely-not-a-flag"])
+
+
+def test_hf_validate_args_reports_all_mismatches():
+    from types import SimpleNamespace as NS
+
+    import pytest
+
+    from miles_b200.utils.arguments import hf_validate_args
+
+    hf = {"hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 4, "num_hidden_layers": 48,
+          "moe_intermediate_size": 768, "num_experts": 128, "num_experts_per_tok": 8, "rms_norm_eps": 1e-6,
+          "rope_parameters": {"rope_theta": 1e6}, "tie_word_embeddings": False}
+    ok = NS(hidden_size=2048, num_attention_heads=32, num_query_groups=4, num_layers=48, ffn_hidden_size=None,
+            moe_ffn_hidden_size=768, num_experts=128, moe_router_topk=8, norm_epsilon=1e-6, rotary_base=1000000,
+            untie_embeddings_and_output_weights=True, kv_channels=None)
+    hf_validate_args(ok, hf)
+    hf_validate_args(NS(), {"text_config": hf})  # nothing set: nothing to compare
+    bad = NS(**{**vars(ok), "num_layers": 24, "rotary_base": 10000, "untie_embeddings_and_output_weights": False})
+    with pytest.raises(AssertionError) as e:
+        hf_validate_args(bad, hf)
+    msg = str(e.value)
+    assert "num_hidden_layers" in msg and "rope_theta" in msg and "tie_word_embeddings" in msg
