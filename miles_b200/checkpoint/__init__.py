@@ -61,6 +61,9 @@ def save_checkpoint(actor, base: str, iteration: int) -> str:
     tmp = os.path.join(d, f"rank_{rank:05d}.pt.tmp")
     torch.save(state, tmp)
     os.replace(tmp, os.path.join(d, f"rank_{rank:05d}.pt"))
+    from ..utils.ci_checks import save_model_hashes
+
+    save_model_hashes(actor.args, actor.store, actor.ps, iteration)
     if dist.is_initialized():
         dist.barrier()
     if rank == 0:
@@ -90,6 +93,10 @@ def load_checkpoint(actor, path: str, step: Optional[int] = None) -> Optional[in
             torch.set_rng_state(state["rng"]["cpu"])
         if getattr(actor, "_value_head", None) is not None and "value_head" in state:
             actor._value_head.data.copy_(state["value_head"])
+        from ..utils.ci_checks import check_model_hashes
+
+        if it is not None:
+            check_model_hashes(actor.args, actor.store, actor.ps, it)
         if getattr(actor.args, "finetune", False):
             return None
         return state.get("global_step", it)

@@ -478,6 +478,10 @@ class TrainActor:
                         grad_norm = self.lora.step(a.clip_grad)
                     elif self.opt is not None:
                         grad_norm = self.opt.step(1.0)
+                if getattr(a, "ci_test", False):
+                    from ..utils.ci_checks import check_grad_norm
+
+                    check_grad_norm(a, float(grad_norm), rollout_id, s, self.role, self.ps.rank)
                 self.global_step += 1
         if self.on_gpu:
             torch.cuda.synchronize()

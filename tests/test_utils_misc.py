@@ -197,3 +197,37 @@ def test_eval_dispatcher_runs_in_background_and_skips_when_busy(tmp_path):
     assert [r for r, _ in seen] == [1, 3, 7] and disp.skipped == [2]
     assert seen[0][1]["eval/score"] == 1.0 and seen[2][1]["eval/skipped"] == 1.0
     assert not os.path.exists(tmp_path / "e1")  # snapshots are removed once evaluated
+
+
+def test_ci_checks_hashes_kl_gate_and_grad_norm(tmp_path):
+    from types import SimpleNamespace as NS
+
+    import pytest
+    import torch
+
+    from miles_b200.models import ParamStore, get_config
+    from miles_b200.parallel.state import ParallelState
+    from miles_b200.utils import ci_checks as C
+
+    cfg = get_config("qwen3-tiny")
+    st = ParamStore(cfg, "cpu", torch.float32, seed=1)
+    h = C.model_hashes_by_layer(st)
+    assert set(h) >= {"layer0000", "layer0001", "embed", "final_norm"}
+    ps = ParallelState()
+    args = NS(ci_test=True, ci_save_model_hash=True, ci_check_model_hash=True, save=str(tmp_path), load=str(tmp_path))
+    assert C.save_model_hashes(args, st, ps, 3)
+    C.check_model_hashes(args, st, ps, 3)
+    st.params["layers.1.ln1.weight"][0] += 1
+    with pytest.raises(AssertionError) as e:
+        C.check_model_hashes(args, st, ps, 3)
+    assert "layer0001" in str(e.value)
+    C.check_first_step_kl(args, {"train/ppo_kl": 0.0, "train/pg_clipfrac": 0.0}, 0, 5)
+    with pytest.raises(AssertionError):
+        C.check_first_step_kl(args, {"train/ppo_kl": 1e-3, "train/pg_clipfrac": 0.0}, 0, 5)
+    C.check_first_step_kl(args, {"train/ppo_kl": 1e-3, "train/pg_clipfrac": 0.1}, 1, 5)  # later steps may be off-policy
+    a2 = NS(ci_save_grad_norm=str(tmp_path / "gn_{role}_{rollout_id}_{step_id}.pt"), ci_load_grad_norm=None)
+    C.check_grad_norm(a2, 2.0, 0, 0)
+    a3 = NS(ci_save_grad_norm=None, ci_load_grad_norm=a2.ci_save_grad_norm)
+    C.check_grad_norm(a3, 2.03, 0, 0)
+    with pytest.raises(AssertionError):
+        C.check_grad_norm(a3, 2.5, 0, 0)
