@@ -490,6 +490,11 @@ class TrainActor:
         out = self._finalize_metrics(metrics_acc, grad_norm, n_tokens_local, elapsed, len(mbs))
         for k in ("train_log_probs", "train_fwd_bwd", "train_optimizer"):
             out[f"perf/{k}_time"] = float(T.log_dict().get(k, 0.0))
+        if getattr(a, "ci_test", False) and (a.num_steps_per_rollout or 1) == 1 and not a.use_rollout_logprobs:
+            from ..utils.ci_checks import check_first_step_kl
+
+            # one optimizer step per rollout: the whole rollout was trained with the weights that computed its log-probs
+            check_first_step_kl(a, out, 0, self.global_step - 1)
         if getattr(a, "keep_old_actor", False):
             self.backup_weights("old_actor")
         if a.ref_update_interval and "ref" in self.weights_backup and (rollout_id + 1) % a.ref_update_interval == 0:
