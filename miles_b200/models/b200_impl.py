@@ -100,10 +100,10 @@ class B200Qwen3:
         if getattr(self, "mx", None):
             self.enable_block_scaled(self.mx_kind)
 
-    def _mx_linear(self, x, wq, tile_group=None, num_tiles=None, n: int = 0):
+    def _mx_linear(self, x, wq, tile_group=None, num_tiles=None, n: int = 0, amax=None):
         from ..ops.mx_gemm import mx_linear, quantize_operand
 
-        xq = quantize_operand(x, self.mx_kind)
+        xq = quantize_operand(x, self.mx_kind, amax)
         self.launches += 3
         return mx_linear(xq, wq, self.status, tile_group, num_tiles, n)
 
@@ -162,7 +162,8 @@ class B200Qwen3:
         I2 = w1.shape[1]
         mx = getattr(self, "mx", None)
         if mx and not keep and scatter is None and w1.data_ptr() in mx and w2.data_ptr() in mx and plan.align == 128:
-            gu = self._mx_linear(xp, mx[w1.data_ptr()], plan.tile_group, plan.num_tiles, I2)
+            # rows of xp past the live tiles are never written: the per-tensor scale of NVFP4 must not look at them
+            gu = self._mx_linear(xp, mx[w1.data_ptr()], plan.tile_group, plan.num_tiles, I2, getattr(plan, "amax_in", None))
             act = C.swiglu_fwd(gu)
             yp = self._mx_linear(act, mx[w2.data_ptr()], plan.tile_group, plan.num_tiles, w2.shape[1])
             self.launches += 1
@@ -191,6 +192,8 @@ class B200Qwen3:
         plan = self._permute_plan(ids, cfg.num_experts, 64 if keep else (128 if use_mx else 1))
         plan.w, plan.probs = w, probs
         xp = C.moe_permute(h2, plan.src, plan.num_tiles, cfg.moe_top_k)
+        if use_mx and self.mx_kind == "nvfp4":
+            plan.amax_in = C.absmax(h2.contiguous())  # the permuted rows hold exactly these values
         gu, act, yp = self._experts_fwd(xp, plan, P[p + "w1"], P[p + "w2"], keep)
         y = C.moe_combine(yp, plan.dest, w, h2.shape[0], cfg.moe_top_k, residual)
         self.launches += 2

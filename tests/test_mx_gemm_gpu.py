@@ -115,8 +115,12 @@ def test_model_forward_with_block_scaled_weights(preset, kind):
     assert calls["n"] >= 4 * cfg.num_layers
     assert torch.isfinite(lp_q).all()
     d = (lp_q - lp_ref).abs()
-    lim = 0.08 if kind == "mxfp8" else 0.35
+    # format noise only (a wrong operand or scale gives differences of several nats on this random model, whose
+    # log-probs spread over ~8 nats): E4M3 keeps ~3 % per element, E2M1 ~12 %
+    lim = 0.25 if kind == "mxfp8" else 1.0
     assert d.mean().item() < lim, (preset, kind, d.mean().item(), d.max().item())
+    corr = torch.corrcoef(torch.stack([lp_q, lp_ref]))[0, 1].item()
+    assert corr > (0.98 if kind == "mxfp8" else 0.85), (preset, kind, corr)
     # a weight update is picked up by refresh
     store.params["layers.0.attn.o.weight"].mul_(0.5)
     model.refresh_block_scaled()
