@@ -71,6 +71,7 @@ struct MxGemmProblem {
   void* c;
   long long ldc;
   float alpha;
+  const float* alpha_dev;  // optional device scalar multiplied into alpha
   int num_groups;
   const int* tile_group;
   const int* num_m_tiles;

@@ -48,6 +48,7 @@ struct MxArgs {
   __nv_bfloat16* c;
   long long ldc;
   float alpha;
+  const float* alpha_dev;  // optional device scalar multiplied into alpha (keeps per-tensor scales off the host)
   long long b_rows;
   int* status;
 };
@@ -314,6 +315,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     int iter = 0;
     bool ok = true;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(p.c) & 15) == 0 && p.ldc % 8 == 0;
+    const float alpha = p.alpha_dev ? p.alpha * __ldg(p.alpha_dev) : p.alpha;
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
       const MxTile tl = mx_decode<BN>(p, t);
       const int row = tl.a_row0 + quad * 32 + lane;
@@ -338,16 +340,16 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 v;
-              v.x = pack_bf16(__uint_as_float(r[8 * i + 0]) * p.alpha, __uint_as_float(r[8 * i + 1]) * p.alpha);
-              v.y = pack_bf16(__uint_as_float(r[8 * i + 2]) * p.alpha, __uint_as_float(r[8 * i + 3]) * p.alpha);
-              v.z = pack_bf16(__uint_as_float(r[8 * i + 4]) * p.alpha, __uint_as_float(r[8 * i + 5]) * p.alpha);
-              v.w = pack_bf16(__uint_as_float(r[8 * i + 6]) * p.alpha, __uint_as_float(r[8 * i + 7]) * p.alpha);
+              v.x = pack_bf16(__uint_as_float(r[8 * i + 0]) * alpha, __uint_as_float(r[8 * i + 1]) * alpha);
+              v.y = pack_bf16(__uint_as_float(r[8 * i + 2]) * alpha, __uint_as_float(r[8 * i + 3]) * alpha);
+              v.z = pack_bf16(__uint_as_float(r[8 * i + 4]) * alpha, __uint_as_float(r[8 * i + 5]) * alpha);
+              v.w = pack_bf16(__uint_as_float(r[8 * i + 6]) * alpha, __uint_as_float(r[8 * i + 7]) * alpha);
               *reinterpret_cast<uint4*>(dst + 8 * i) = v;
             }
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (col + i < p.N) dst[i] = __float2bfloat16(__uint_as_float(r[i]) * p.alpha);
+              if (col + i < p.N) dst[i] = __float2bfloat16(__uint_as_float(r[i]) * alpha);
           }
         }
       }
@@ -446,6 +448,7 @@ int launch_mx(const MxGemmProblem& q, cudaStream_t stream) {
   ka.c = static_cast<__nv_bfloat16*>(q.c);
   ka.ldc = q.ldc;
   ka.alpha = q.alpha;
+  ka.alpha_dev = q.alpha_dev;
   ka.b_rows = q.b_rows;
   ka.status = q.status;
   int dev = 0, sms = 0;

@@ -23,7 +23,8 @@ at::Tensor sf_swizzle(const at::Tensor& scales) {
 // a: uint8 [M, K or K/2]; b: uint8 [N, ...] (dense) or [G*N, ...] (grouped rows); sfa / sfb: atoms from sf_swizzle.
 at::Tensor gemm_mx(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb, int64_t kind,
                    double alpha, int64_t n, const c10::optional<at::Tensor>& tile_group,
-                   const c10::optional<at::Tensor>& num_m_tiles, const c10::optional<at::Tensor>& status, int64_t block_n) {
+                   const c10::optional<at::Tensor>& num_m_tiles, const c10::optional<at::Tensor>& status, int64_t block_n,
+                   const c10::optional<at::Tensor>& alpha_dev) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kByte && b.scalar_type() == at::kByte, "operands are uint8 CUDA tensors");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == b.size(1), "operands are [rows, packed K] with equal K");
   TORCH_CHECK(sfa.is_contiguous() && sfb.is_contiguous() && sfa.scalar_type() == at::kByte && sfb.scalar_type() == at::kByte, "scale atoms are contiguous uint8");
@@ -53,6 +54,10 @@ at::Tensor gemm_mx(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor&
   p.c = out.data_ptr();
   p.ldc = p.N;
   p.alpha = static_cast<float>(alpha);
+  if (alpha_dev.has_value()) {
+    TORCH_CHECK(alpha_dev->is_cuda() && alpha_dev->scalar_type() == at::kFloat && alpha_dev->numel() >= 1, "alpha_dev is a CUDA float scalar");
+    p.alpha_dev = alpha_dev->data_ptr<float>();
+  }
   if (grouped) {
     TORCH_CHECK(num_m_tiles.has_value() && tile_group->scalar_type() == at::kInt && tile_group->is_contiguous(), "grouped mode needs int32 tile_group and num_m_tiles");
     p.tile_group = tile_group->data_ptr<int>();
@@ -72,5 +77,5 @@ void register_mx(pybind11::module_& m) {
   m.def("sf_swizzle", &sf_swizzle);
   m.def("gemm_mx", &gemm_mx, pybind11::arg("a"), pybind11::arg("sfa"), pybind11::arg("b"), pybind11::arg("sfb"),
         pybind11::arg("kind"), pybind11::arg("alpha") = 1.0, pybind11::arg("n") = 0, pybind11::arg("tile_group") = pybind11::none(),
-        pybind11::arg("num_m_tiles") = pybind11::none(), pybind11::arg("status") = pybind11::none(), pybind11::arg("block_n") = 0);
+        pybind11::arg("num_m_tiles") = pybind11::none(), pybind11::arg("status") = pybind11::none(), pybind11::arg("block_n") = 0, pybind11::arg("alpha_dev") = pybind11::none());
 }

@@ -64,6 +64,9 @@ def mx_linear(x: MxOperand, w: MxOperand, status: Optional[torch.Tensor] = None,
     C = _ext.load(required=True)
     if x.kind != w.kind:
         raise ValueError("both operands must use the same block-scaled format")
-    alpha = float(torch.as_tensor(x.decode_scale).reshape(-1)[0]) * float(torch.as_tensor(w.decode_scale).reshape(-1)[0]) \
-        if x.kind == "nvfp4" else 1.0
-    return C.gemm_mx(x.q, x.atoms, w.q, w.atoms, KINDS[x.kind], alpha, n, tile_group, num_m_tiles, status, block_n)
+    alpha_dev = None
+    if x.kind == "nvfp4":
+        # the product of the two per-tensor scales stays on the device: no host round trip, usable under graph capture
+        alpha_dev = (torch.as_tensor(x.decode_scale, device=x.q.device).reshape(-1)[:1].float()
+                     * torch.as_tensor(w.decode_scale, device=x.q.device).reshape(-1)[:1].float())
+    return C.gemm_mx(x.q, x.atoms, w.q, w.atoms, KINDS[x.kind], 1.0, n, tile_group, num_m_tiles, status, block_n, alpha_dev)
