@@ -89,12 +89,16 @@ class TorchQwen3:
 
     # ------------------------------------------------------------------ forward
     def forward_hidden(self, tokens, positions, cu_seqlens, meta: Optional[InferMeta] = None, kv_cache=None,
-                       replay: Optional[torch.Tensor] = None, record: Optional[list] = None):
-        """tokens/positions [T] -> final-normed hidden [T,H]. ``replay`` is int32 [T, n_moe_layers, K]."""
+                       replay: Optional[torch.Tensor] = None, record: Optional[list] = None,
+                       x_in: Optional[torch.Tensor] = None):
+        """tokens/positions [T] -> final-normed hidden [T,H]. ``replay`` is int32 [T, n_moe_layers, K]. Under
+        pipeline parallelism this runs the stage's layers: later stages start from ``x_in``, every stage but the last
+        returns the raw hidden states for the next one."""
         cfg, P = self.cfg, self.store.params
-        x = F.embedding(tokens.long(), P["embed.weight"])
-        moe_idx = 0
-        for i in range(cfg.num_layers):
+        lo, hi = getattr(self.store, "layer_range", (0, cfg.num_layers))
+        x = F.embedding(tokens.long(), P["embed.weight"]) if getattr(self.store, "is_first_stage", True) else x_in
+        moe_idx = sum(cfg.layer_is_moe(j) for j in range(lo))
+        for i in range(lo, hi):
             x = self._attn_block(i, x, positions, cu_seqlens, meta, kv_cache)
             rid = None
             if cfg.layer_is_moe(i):
@@ -102,6 +106,8 @@ class TorchQwen3:
                     rid = replay[:, moe_idx]
                 moe_idx += 1
             x = self._mlp_block(i, x, rid, record)
+        if not getattr(self.store, "is_last_stage", True):
+            return x
         return R.rmsnorm(x, P["final_norm.weight"], cfg.rms_eps)
 
     def logits(self, hidden_rows):
@@ -120,11 +126,11 @@ class TorchQwen3:
 
     # ------------------------------------------------------------------ trainer API (autograd)
     def forward_logprobs(self, tokens, positions, cu_seqlens, row_index, targets, inv_temp, replay=None, record=None,
-                         with_grad: bool = False):
+                         with_grad: bool = False, x_in: Optional[torch.Tensor] = None, max_seqlen: int = 0):
         """Log-probs/entropy of ``targets`` predicted at packed rows ``row_index``."""
         ctx = torch.enable_grad() if with_grad else torch.no_grad()
         with ctx:
-            hidden = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, record=record)
+            hidden = self.forward_hidden(tokens, positions, cu_seqlens, replay=replay, record=record, x_in=x_in)
             return self.logprobs_entropy(hidden[row_index.long()], targets, inv_temp)
 
     def set_requires_grad(self, flag: bool) -> None:

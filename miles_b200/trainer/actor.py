@@ -73,7 +73,6 @@ class TrainActor:
         if self.ps.pp.size > 1:
             from ..parallel.pipeline_parallel import PipeGroup, PipelineSchedule
 
-            assert want_b200, "pipeline parallelism needs the sm_100a model path"
             self.pipe = PipelineSchedule(PipeGroup(self.ps.pp.group, self.ps.pp.rank, self.ps.pp.size, self.ps.pp.ranks), self.device)
         self.tp_exchange = None
         if tp > 1:
@@ -283,8 +282,8 @@ class TrainActor:
                 results[i] = self.model.forward_logprobs(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t,
                                                          replay=replay, record=rec, max_seqlen=mb.max_seqlen, x_in=x_in)
                 return None
-            return self.model.forward_hidden(mb.tokens, mb.positions, mb.cu_seqlens, replay=replay, record=rec,
-                                             max_seqlen=mb.max_seqlen, x_in=x_in)
+            kw = {} if self.is_torch else {"max_seqlen": mb.max_seqlen}
+            return self.model.forward_hidden(mb.tokens, mb.positions, mb.cu_seqlens, replay=replay, record=rec, x_in=x_in, **kw)
 
         self.pipe.run_forward_only(len(mbs), self._act_meta(mbs), fwd)
         src = pp.ranks[-1]
@@ -312,6 +311,8 @@ class TrainActor:
         inv_t = 1.0 / self.args.rollout_temperature
         saved: dict = {}
         last = self.store.is_last_stage
+        if self.is_torch:
+            return self._forward_backward_pipelined_autograd(chunk, scale, metrics_acc)
 
         def fwd(i, x_in):
             mb = chunk[i]
@@ -340,6 +341,45 @@ class TrainActor:
         self.pipe.run_1f1b(len(chunk), self._act_meta(chunk), fwd, bwd)
         if self.cfg.tie_embeddings and (self.store.is_first_stage or last):
             pass  # reduced in _reduce_grads (all stages take part in the collective)
+
+    def _forward_backward_pipelined_autograd(self, chunk: list, scale: float, metrics_acc: dict) -> None:
+        """The same schedule for the PyTorch model: a stage keeps the autograd graph of its in-flight micro-batches
+        and back-propagates the gradient it receives (the last stage: its loss)."""
+        inv_t = 1.0 / self.args.rollout_temperature
+        saved: dict = {}
+        last, first = self.store.is_last_stage, self.store.is_first_stage
+        model = self.model
+        model.set_requires_grad(True)
+
+        def fwd(i, x_in):
+            mb = chunk[i]
+            leaf = None if first else x_in.detach().requires_grad_(True)
+            if last:
+                saved[i] = leaf
+                return None
+            with torch.enable_grad():
+                y = model.forward_hidden(mb.tokens, mb.positions, mb.cu_seqlens, replay=self._replay_for(mb, "train"), x_in=leaf)
+            saved[i] = (leaf, y)
+            return y.detach()
+
+        def bwd(i, dy):
+            mb = chunk[i]
+            if last:
+                leaf = saved.pop(i)
+                lp, ent = model.forward_logprobs(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t,
+                                                 replay=self._replay_for(mb, "train"), with_grad=True, x_in=leaf)
+                loss, m = self._loss_closure(mb, scale)(lp, ent)
+                loss.backward()
+                for k, v in m.items():
+                    metrics_acc[k] = metrics_acc.get(k, 0.0) + v.detach().float() * scale
+            else:
+                leaf, y = saved.pop(i)
+                y.backward(dy)
+            model.accumulate_autograd_grads()
+            return None if leaf is None else leaf.grad
+
+        self.pipe.run_1f1b(len(chunk), self._act_meta(chunk), fwd, bwd)
+        model.set_requires_grad(False)
 
     # ------------------------------------------------------------------ the RL step
     def _stage(self, data: dict) -> list:

@@ -69,3 +69,34 @@ def test_gloo_world_size_2(tmp_path):
     b = torch.load(tmp_path / "r1.pt", weights_only=False)["hist"]
     assert a[0]["train/grad_norm"] == pytest.approx(b[0]["train/grad_norm"], rel=1e-5)
     assert a[1]["train/pg_loss"] == pytest.approx(b[1]["train/pg_loss"], abs=1e-6)
+
+
+def _pp_worker(rank: int, world: int, port: int, out_dir: str):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    from miles_b200.loop import RLLoop
+
+    args = parse_args(BASE + ["--num-rollout", "2", "--actor-num-gpus-per-node", str(world), "--distributed-backend", "gloo",
+                              "--pipeline-model-parallel-size", str(world)])
+    loop = RLLoop(args)
+    st = loop.actor.store
+    assert st.layer_range == (rank, rank + 1)  # the tiny model has two layers: one per stage
+    assert ("embed.weight" in st.params) == (rank == 0) and ("final_norm.weight" in st.params) == (rank == world - 1)
+    hist = loop.run()
+    # the engine decodes on a full-model replica that the weight update filled from both stages
+    rs = loop.rollout_store
+    assert rs is not None and rs.layer_range == (0, 2)
+    for name, p in st.params.items():
+        assert torch.equal(rs.params[name], p), name
+    both = [None, None]
+    dist.all_gather_object(both, {k: v for k, v in hist[-1].items() if k.startswith("train/")})
+    assert both[0] == both[1], "stages report different training metrics"
+    assert all(m["train/train_rollout_logprob_abs_diff"] < 1e-5 for m in hist)
+    assert all(m["perf/step_tokens"] == 32 * 48 for m in hist)  # one pipeline = one replica: all its samples, counted once
+    assert all(m["train/grad_norm"] > 0 for m in hist)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_gloo_pipeline_parallel_two_stages(tmp_path):
+    port = 29000 + (os.getpid() * 7) % 2000
+    mp.spawn(_pp_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
