@@ -254,24 +254,11 @@ class RLLoop:
             self.engine.drain()  # expert-parallel ranks keep serving dummy iterations until all are done
         samples = flatten_groups(out.samples if hasattr(out, "samples") else out)
         samples = postprocess_rollout_data(self.local_args, samples)
-        if self.ps.pp.size > 1:
-            # every stage trains on the samples of all the stages of its pipeline
-            pooled = [None] * self.ps.pp.size
-            dist.all_gather_object(pooled, [s.to_dict() for s in samples], group=self.ps.pp.group)
-            from .utils.types import Sample
-
-            samples, gmap = [], {}
-            for part_id, part in enumerate(pooled):
-                for d in part:
-                    smp = Sample.from_dict(d)
-                    # every stage's data source numbers its groups and samples from zero: make them distinct again
-                    if smp.group_index is not None:
-                        smp.group_index = gmap.setdefault((part_id, smp.group_index), len(gmap))
-                    if smp.index is not None:
-                        smp.index = smp.index * self.ps.pp.size + part_id
-                    if smp.rollout_id is not None:
-                        smp.rollout_id = smp.rollout_id * self.ps.pp.size + part_id
-                    samples.append(smp)
+        # the ranks of a context-parallel group and the stages of a pipeline train on the same samples: each of
+        # them generated a share with its own engine, now they pool them
+        for axis in (self.ps.cp, self.ps.pp):
+            if axis.size > 1:
+                samples = self._pool_samples(samples, axis)
         dt = time.perf_counter() - t0
         metrics = dict(getattr(out, "metrics", {}) or {})
         metrics.update(compute_rollout_metrics(a, samples, dt))
@@ -285,6 +272,25 @@ class RLLoop:
             if self.ps.rank == 0:
                 torch.save({"rollout_id": rollout_id, "samples": [d for g in gathered for d in g]}, p)
         return samples, metrics
+
+    def _pool_samples(self, samples: list, axis) -> list:
+        from .utils.types import Sample
+
+        pooled = [None] * axis.size
+        dist.all_gather_object(pooled, [s.to_dict() for s in samples], group=axis.group)
+        out, gmap = [], {}
+        for part_id, part in enumerate(pooled):
+            for d in part:
+                smp = Sample.from_dict(d)
+                # every rank's data source numbers its groups and samples from zero: make them distinct again
+                if smp.group_index is not None:
+                    smp.group_index = gmap.setdefault((part_id, smp.group_index), len(gmap))
+                if smp.index is not None:
+                    smp.index = smp.index * axis.size + part_id
+                if smp.rollout_id is not None:
+                    smp.rollout_id = smp.rollout_id * axis.size + part_id
+                out.append(smp)
+        return out
 
     def offload_rollout(self) -> None:
         if self.engine is not None and self.args.offload_rollout:
@@ -340,8 +346,8 @@ class RLLoop:
         t3 = time.perf_counter()
         n_tok = sum(len(s.tokens) for s in samples)
         tot = torch.tensor([float(n_tok)], device=self.actor.device)
-        if self.ps.dp_cp.size > 1:
-            dist.all_reduce(tot, group=self.ps.dp_cp.group)  # one count per data-parallel replica
+        if self.ps.dp.size > 1:
+            dist.all_reduce(tot, group=self.ps.dp.group)  # one count per replica (its cp / pp / tp ranks hold the same samples)
         metrics.update({"perf/rollout_time": t1 - t0, "perf/train_time": t2 - t1, "perf/update_weights_wall": t3 - t2,
                         "perf/step_time": t3 - t0, "perf/step_tokens": float(tot.item()),
                         "perf/grpo_tokens_per_s": float(tot.item()) / max(t3 - t0, 1e-9)})

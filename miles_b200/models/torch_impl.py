@@ -40,6 +40,7 @@ class TorchQwen3:
         self.cfg = cfg
         self.store = store
         self.ep_group = ep_group
+        self.cp_ctx = None  # (sample lengths, cp size, cp rank, group) while a context-parallel micro-batch is processed
         if store.ep_size != 1:
             raise NotImplementedError("the PyTorch execution path keeps all experts on every rank")
 
@@ -57,7 +58,14 @@ class TorchQwen3:
                 kc, vc = kv_cache[i]
                 kc[meta.slot_mapping.long()] = k.to(kc.dtype)
                 vc[meta.slot_mapping.long()] = v.to(vc.dtype)
-            att = R.attention_varlen(q, k, v, cu, scale)
+            if self.cp_ctx is not None and meta is None:
+                from ..parallel.context_parallel import attention_zigzag, gather_kv_autograd
+
+                lens, cp, rank, group = self.cp_ctx
+                kf, vf = gather_kv_autograd(k, v, lens, cp, rank, group)
+                att = attention_zigzag(q, kf, vf, lens, cp, rank, scale)
+            else:
+                att = R.attention_varlen(q, k, v, cu, scale)
         else:
             kc, vc = kv_cache[i]
             kc[meta.slot_mapping.long()] = k.to(kc.dtype)

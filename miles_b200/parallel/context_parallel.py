@@ -8,9 +8,14 @@ piece of every sample. All-gather layout (``--allgather-cp``): the concatenated 
 Forward attention under context parallelism gathers K and V over the group (they are ``num_kv_heads / num_q_heads``
 of the activation bytes under GQA) and runs the tcgen05 attention kernel on the local queries with tile
 descriptors that carry each query chunk's position inside its sequence (``build_cp_tiles``); per-token outputs
-(log-probs, entropy, values) are put back in sample order with ``gather_per_token``. The backward pass of the
-attention under context parallelism is not implemented here: training runs with cp = 1, log-prob / reference /
-critic forwards may use cp > 1.
+(log-probs, entropy, values) are put back in sample order with ``gather_per_token``.
+
+Training under context parallelism (second half of this file): a micro-batch is cut with ``MicroBatch.cp_shard``
+(local tokens, the response entries whose logit row is local, whole-sample denominators), K and V are gathered with
+a differentiable gather (``gather_kv_autograd``: its backward is the reduce-scatter of dK / dV, written as an
+all-reduce so that every backend can run it), per-token losses stay local and the ranks' partial losses add up in
+the gradient all-reduce over dp x cp. The PyTorch model path runs this end to end (``attention_zigzag``); on the
+sm_100a path the context-parallel attention has a forward kernel path only, so training there runs with cp = 1.
 
 Reference: miles/backends/training_utils/cp_utils.py:19-67,195-303 (zigzag slicing, all_gather_with_cp),
 data.py:198-235 (all-gather mode).
@@ -121,3 +126,75 @@ def gather_per_token(x_local: torch.Tensor, lens: Sequence[int], cp: int, rank: 
     if group is not None or dist.is_initialized():
         dist.all_reduce(full, group=group)
     return full
+
+
+# ---------------------------------------------------------------------------------------------- training under CP
+class _GatherRows(torch.autograd.Function):
+    """All-gather of per-rank row blocks of different sizes with a gradient: forward scatters the local rows into a
+    zero tensor of the total size and sums over the group (any backend can do that), backward sums the gradient of
+    the full tensor over the group and keeps the local rows' share (the gradient a reduce-scatter would deliver)."""
+
+    @staticmethod
+    def forward(ctx, x, sizes, rank, group):
+        ctx.sizes, ctx.rank, ctx.group = sizes, rank, group
+        off = sum(sizes[:rank])
+        full = x.new_zeros((sum(sizes),) + tuple(x.shape[1:]))
+        full[off:off + sizes[rank]] = x
+        dist.all_reduce(full, group=group)
+        return full
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        off = sum(ctx.sizes[:ctx.rank])
+        return g[off:off + ctx.sizes[ctx.rank]], None, None, None
+
+
+def gather_kv_autograd(k_local: torch.Tensor, v_local: torch.Tensor, lens: Sequence[int], cp: int, rank: int, group) -> tuple:
+    """K and V of all ranks in sample order, differentiable (see ``_GatherRows``)."""
+    sizes = [sum(b - a for n in lens for a, b in zigzag_bounds(n, cp, r)) for r in range(cp)]
+    out = []
+    for t in (k_local, v_local):
+        full = _GatherRows.apply(t, sizes, rank, group)
+        parts, off = [], 0
+        for s in sizes:
+            parts.append(full[off:off + s])
+            off += s
+        out.append(unzigzag(parts, lens, cp))
+    return out[0], out[1]
+
+
+def attention_zigzag(q_local: torch.Tensor, k_full: torch.Tensor, v_full: torch.Tensor, lens: Sequence[int], cp: int, rank: int,
+                     scale: float) -> torch.Tensor:
+    """Causal attention of the local (zigzag) queries against the gathered keys / values, in plain PyTorch ops
+    (autograd path of the PyTorch model; the sm_100a path uses the tile table of ``build_cp_tiles``)."""
+    Hq, Hk = q_local.shape[1], k_full.shape[1]
+    G = Hq // Hk
+    outs, q0, s0 = [], 0, 0
+    for n in lens:
+        for a, b in zigzag_bounds(n, cp, rank):
+            if b > a:
+                qs = q_local[q0:q0 + (b - a)].transpose(0, 1).float()                        # [Hq, Lq, D]
+                ks = k_full[s0:s0 + b].transpose(0, 1).float().repeat_interleave(G, dim=0)   # keys 0 .. b-1 of the sample
+                vs = v_full[s0:s0 + b].transpose(0, 1).float().repeat_interleave(G, dim=0)
+                att = torch.matmul(qs, ks.transpose(1, 2)) * scale
+                qpos = torch.arange(a, b, device=q_local.device)[:, None]
+                kpos = torch.arange(0, b, device=q_local.device)[None, :]
+                att = att.masked_fill(kpos > qpos, float("-inf"))
+                outs.append(torch.matmul(torch.softmax(att, dim=-1), vs).transpose(0, 1).to(q_local.dtype))
+            q0 += b - a
+        s0 += n
+    return torch.cat(outs, 0) if outs else q_local.new_zeros(q_local.shape)
+
+
+def local_index_map(lens: Sequence[int], cp: int, rank: int) -> torch.Tensor:
+    """int64 [sum(lens)]: index of every packed token inside the rank's local token list, -1 if another rank owns it."""
+    idx = torch.full((sum(lens),), -1, dtype=torch.int64)
+    cur, s0 = 0, 0
+    for n in lens:
+        for a, b in zigzag_bounds(n, cp, rank):
+            idx[s0 + a:s0 + b] = torch.arange(cur, cur + (b - a))
+            cur += b - a
+        s0 += n
+    return idx

@@ -226,8 +226,21 @@ class TrainActor:
         return TrainActor._Swapped(self, tag)
 
     # ------------------------------------------------------------------ forward passes
+    def _set_cp(self, mb: MicroBatch) -> None:
+        """Tell the model how the micro-batch is cut along the sequence (context parallelism)."""
+        cp = mb.extras.get("cp")
+        if cp is None:
+            if hasattr(self.model, "cp_ctx"):
+                self.model.cp_ctx = None
+            return
+        if not self.is_torch:
+            raise NotImplementedError("training under context parallelism runs on the PyTorch model path; the sm_100a "
+                                      "path has the context-parallel attention forward only")
+        self.model.cp_ctx = (cp[0], cp[1], cp[2], self.ps.cp.group)
+
     def _forward_logprobs(self, mb: MicroBatch, replay=None, record=None):
         inv_t = 1.0 / self.args.rollout_temperature
+        self._set_cp(mb)
         if self.is_torch:
             return self.model.forward_logprobs(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t,
                                                replay=replay, record=record)
@@ -387,7 +400,8 @@ class TrainActor:
         if getattr(self, "_local_data", False):
             ids = list(range(len(data["tokens"])))  # the caller already holds exactly this rank's share
         else:
-            ids = split_by_dp(data, self.ps.dp_cp.size, balance=getattr(a, "balance_data", False))[self.ps.dp_cp.rank]
+            # the ranks of one context-parallel group work on the same samples (each on its share of the tokens)
+            ids = split_by_dp(data, self.ps.dp.size, balance=getattr(a, "balance_data", False))[self.ps.dp.rank]
         lens = [len(data["tokens"][i]) for i in ids]
         n_mb = None
         moe_layers = sum(self.cfg.layer_is_moe(i) for i in range(self.cfg.num_layers))
@@ -407,8 +421,12 @@ class TrainActor:
         else:
             mbs = build_micro_batches(data, micro_batch_size=a.micro_batch_size, **kw)
         out = []
+        cp = self.ps.cp.size
+        if cp > 1:
+            assert a.advantage_estimator in ("grpo", "reinforce_plus_plus_baseline") or a.loss_type == "sft_loss", \
+                "context parallelism supports estimators whose per-token terms need no other rank's tokens"
         for mb in mbs:
-            d = mb.to_device(self.device)
+            d = mb.cp_shard(cp, self.ps.cp.rank).to_device(self.device)
             self.h2d_bytes += d.h2d_bytes
             out.append(d)
         return out
@@ -545,6 +563,7 @@ class TrainActor:
         inv_t = 1.0 / self.args.rollout_temperature
         fn = self._loss_closure(mb, scale)
         replay = self._replay_for(mb, "train")
+        self._set_cp(mb)
         if self.is_torch:
             self.model.set_requires_grad(True)
             lp, ent = self.model.forward_logprobs(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t,

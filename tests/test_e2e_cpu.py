@@ -100,3 +100,43 @@ def _pp_worker(rank: int, world: int, port: int, out_dir: str):
 def test_gloo_pipeline_parallel_two_stages(tmp_path):
     port = 29000 + (os.getpid() * 7) % 2000
     mp.spawn(_pp_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+
+
+def _cp_worker(rank: int, world: int, port: int, out_dir: str):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import copy
+
+    from miles_b200.loop import RLLoop
+    from miles_b200.parallel.state import ParallelState
+    from miles_b200.rollout.train_data import convert_samples_to_train_data
+    from miles_b200.trainer.actor import TrainActor
+
+    args = parse_args(BASE + ["--num-rollout", "1", "--actor-num-gpus-per-node", str(world), "--distributed-backend", "gloo",
+                              "--context-parallel-size", str(world)])
+    loop = RLLoop(args)
+    assert loop.ps.cp.size == world and loop.ps.dp.size == 1
+    # a single-process trainer with the same initial weights trains on the same pooled samples
+    solo = TrainActor(copy.copy(args), "actor", ParallelState())
+    for g in solo.store.flat:
+        assert torch.equal(solo.store.flat[g], loop.actor.store.flat[g])
+    loop.update_weights()
+    samples, _ = loop.generate(0)
+    assert len(samples) == 32  # both ranks' shares, pooled
+    if args.offload_train:
+        loop.actor.wake_up()  # what RLLoop.step does before training
+    m = loop.train(0, samples)
+    solo._local_data = True
+    m0 = solo.train(0, convert_samples_to_train_data(args, samples))
+    # the context-parallel step is the single-process step: same loss terms, same gradient norm, same new weights
+    for k in ("train/pg_loss", "train/grad_norm", "train/train_rollout_logprob_abs_diff"):
+        assert abs(m[k] - m0[k]) <= 1e-5 * max(1.0, abs(m0[k])), (k, m[k], m0[k])
+    for g in solo.store.flat:
+        assert torch.allclose(solo.store.flat[g], loop.actor.store.flat[g], atol=1e-6), g
+    assert m["train/train_rollout_logprob_abs_diff"] < 1e-5
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_gloo_context_parallel_training_matches_single_process(tmp_path):
+    port = 31000 + (os.getpid() * 13) % 2000
+    mp.spawn(_cp_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
