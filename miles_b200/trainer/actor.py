@@ -288,6 +288,7 @@ class TrainActor:
 
         def fwd(i, x_in):
             mb = mbs[i]
+            self._set_cp(mb)
             rec = [] if want_record else None
             records[i] = rec
             replay = self._replay_for(mb, "logprob")
@@ -366,6 +367,7 @@ class TrainActor:
 
         def fwd(i, x_in):
             mb = chunk[i]
+            self._set_cp(mb)
             leaf = None if first else x_in.detach().requires_grad_(True)
             if last:
                 saved[i] = leaf
@@ -377,6 +379,7 @@ class TrainActor:
 
         def bwd(i, dy):
             mb = chunk[i]
+            self._set_cp(mb)
             if last:
                 leaf = saved.pop(i)
                 lp, ent = model.forward_logprobs(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t,
