@@ -4,13 +4,18 @@ Session protocol of the reference (miles/backends/megatron_utils/update_weight/m
 ``pause_generation(mode) -> flush_cache (not for in_place) -> begin -> buckets -> update_weight_version ->
 end -> continue_generation``.  Modes here:
 
-* **shared**   — colocated engine running on the trainer's own ``ParamStore``: nothing is copied, the
-  update is the version bump (the B200-first answer to CUDA-IPC bucket passing).
-* **copy**     — engine with its own store on the same device / process: flat-buffer device copies
-  (optionally re-quantised to MXFP8 / NVFP4 by the fused kernels in ``weight_sync.reshard``).
-* **p2p**      — engines on other GPUs of the box: the trainer's shards are written straight into the
-  engines' weight buffers over NVLink from inside a kernel (``weight_sync.p2p``); NCCL broadcast is the
-  measured baseline.
+* **shared**    — colocated engine running on the trainer's own ``ParamStore``: nothing is copied, the update is
+  the version bump (the B200-first answer to CUDA-IPC bucket passing).
+* **copy**      — engine with its own store in the same process: flat-buffer device copies; an engine that holds all
+  experts next to an expert-parallel trainer receives them by all-gather (``reshard.gather_experts_into``), an engine
+  next to a pipelined trainer by per-stage broadcasts (``reshard.gather_stages_into``); engines that serve MXFP8 /
+  NVFP4 copies re-quantise afterwards.
+* **broadcast** — engines in other processes: ``broadcast.BroadcastWeightUpdater`` (a process group that exists only
+  for weight updates; buckets announced over HTTP, tensors broadcast from the trainer's source rank).
+* **disk**      — ``disk_delta``: versioned XOR / overwrite deltas that engines pull.
+
+Writing the trainer's shards straight into the buffers of engines on other GPUs of the box from inside a kernel
+(peer stores over NVLink) is not built; the broadcast mode covers those engines.
 """
 from __future__ import annotations
 
