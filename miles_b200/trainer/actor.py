@@ -106,6 +106,7 @@ class TrainActor:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._value_head = None
+        self.cell_group = None  # ft.indep_dp.ReconfigurableGroup when this trainer is one cell of several
         if role == "critic":
             self._init_value_head()
         self._setup_optimizer()
@@ -533,6 +534,15 @@ class TrainActor:
                             for k, v in m.items():
                                 metrics_acc[k] = metrics_acc.get(k, 0.0) + v.detach().float() * scale
                     self._reduce_grads()
+                    if getattr(self, "cell_group", None) is not None:
+                        from ..ft.indep_dp import cross_cell_grad_sync
+
+                        # independent data-parallel cells: average over the cells, and apply the step only if every
+                        # cell got through it (a discarded step leaves weights and optimizer state untouched)
+                        if not cross_cell_grad_sync(self, self.cell_group):
+                            self.discarded_steps = getattr(self, "discarded_steps", 0) + 1
+                            self.store.zero_grads()
+                            continue
                 with T.cuda_span("train_optimizer"):
                     if self.lora is not None:
                         self.lora.grads_from_weight_grads()
