@@ -50,7 +50,7 @@ class RLLoop:
         self.ps = ps or init_parallel_state(
             tp=args.tensor_model_parallel_size, pp=args.pipeline_model_parallel_size, cp=args.context_parallel_size,
             ep=args.expert_model_parallel_size, backend=None if args.distributed_backend == "nccl" else args.distributed_backend,
-            timeout_minutes=args.distributed_timeout_minutes)
+            timeout_minutes=args.distributed_timeout_minutes, cp_comm_type=getattr(args, "cp_comm_type", "p2p"))
         # ranks of one tensor-parallel group are one data-parallel replica: same seeds, same prompts, same samples
         # the stages of a pipeline each run their own engine on a full copy of the model and pool their samples
         # before training, so they count as rollout replicas too

@@ -198,3 +198,50 @@ def local_index_map(lens: Sequence[int], cp: int, rank: int) -> torch.Tensor:
             cur += b - a
         s0 += n
     return idx
+
+
+# ---------------------------------------------------------------------------------------------- Ulysses (all-to-all)
+class _AllToAllRows(torch.autograd.Function):
+    """``all_to_all_single`` over dim 0 with per-peer row counts; the gradient travels the same way back."""
+
+    @staticmethod
+    def forward(ctx, x, in_splits, out_splits, group):
+        ctx.in_splits, ctx.out_splits, ctx.group = in_splits, out_splits, group
+        out = x.new_empty((sum(out_splits),) + tuple(x.shape[1:]))
+        dist.all_to_all_single(out, x.contiguous(), out_splits, in_splits, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        gx = g.new_empty((sum(ctx.in_splits),) + tuple(g.shape[1:]))
+        dist.all_to_all_single(gx, g.contiguous(), ctx.in_splits, ctx.out_splits, group=ctx.group)
+        return gx, None, None, None
+
+
+def _local_sizes(lens: Sequence[int], cp: int) -> list:
+    return [sum(b - a for n in lens for a, b in zigzag_bounds(n, cp, r)) for r in range(cp)]
+
+
+def heads_to_sequence(x_local: torch.Tensor, lens: Sequence[int], cp: int, rank: int, group) -> torch.Tensor:
+    """``[T_local, H, D]`` (this rank's tokens, all heads) -> ``[T, H / cp, D]`` (all tokens in sample order, this
+    rank's share of the heads): the first all-to-all of Ulysses-style context parallelism."""
+    T, H, D = x_local.shape
+    assert H % cp == 0, "the all-to-all layout needs the head count to divide by the context-parallel size"
+    sizes = _local_sizes(lens, cp)
+    send = x_local.view(T, cp, H // cp, D).transpose(0, 1).reshape(cp * T, H // cp, D)  # block j goes to rank j
+    got = _AllToAllRows.apply(send, [T] * cp, sizes, group)
+    parts, off = [], 0
+    for s in sizes:
+        parts.append(got[off:off + s])
+        off += s
+    return unzigzag(parts, lens, cp)
+
+
+def sequence_to_heads(y_full: torch.Tensor, lens: Sequence[int], cp: int, rank: int, group) -> torch.Tensor:
+    """Inverse of :func:`heads_to_sequence` for the attention output."""
+    sizes = _local_sizes(lens, cp)
+    send = torch.cat([zigzag_slice(y_full, lens, cp, r) for r in range(cp)], 0)  # block r: rank r's tokens, my heads
+    T = sizes[rank]
+    got = _AllToAllRows.apply(send, sizes, [T] * cp, group)                     # block j: my tokens, rank j's heads
+    Hs, D = y_full.shape[1], y_full.shape[2]
+    return got.view(cp, T, Hs, D).transpose(0, 1).reshape(T, cp * Hs, D)

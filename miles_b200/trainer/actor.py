@@ -237,7 +237,7 @@ class TrainActor:
         if not self.is_torch:
             raise NotImplementedError("training under context parallelism runs on the PyTorch model path; the sm_100a "
                                       "path has the context-parallel attention forward only")
-        self.model.cp_ctx = (cp[0], cp[1], cp[2], self.ps.cp.group)
+        self.model.cp_ctx = (cp[0], cp[1], cp[2], self.ps.cp.group, getattr(self.ps, "cp_comm_type", "p2p"))
 
     def _forward_logprobs(self, mb: MicroBatch, replay=None, record=None):
         inv_t = 1.0 / self.args.rollout_temperature

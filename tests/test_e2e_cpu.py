@@ -102,7 +102,7 @@ def test_gloo_pipeline_parallel_two_stages(tmp_path):
     mp.spawn(_pp_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
 
 
-def _cp_worker(rank: int, world: int, port: int, out_dir: str):
+def _cp_worker(rank: int, world: int, port: int, out_dir: str, comm: str = "p2p"):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     import copy
 
@@ -112,9 +112,9 @@ def _cp_worker(rank: int, world: int, port: int, out_dir: str):
     from miles_b200.trainer.actor import TrainActor
 
     args = parse_args(BASE + ["--num-rollout", "1", "--actor-num-gpus-per-node", str(world), "--distributed-backend", "gloo",
-                              "--context-parallel-size", str(world)])
+                              "--context-parallel-size", str(world), "--cp-comm-type", comm])
     loop = RLLoop(args)
-    assert loop.ps.cp.size == world and loop.ps.dp.size == 1
+    assert loop.ps.cp.size == world and loop.ps.dp.size == 1 and loop.ps.cp_comm_type == comm
     # a single-process trainer with the same initial weights trains on the same pooled samples
     solo = TrainActor(copy.copy(args), "actor", ParallelState())
     for g in solo.store.flat:
@@ -137,9 +137,10 @@ def _cp_worker(rank: int, world: int, port: int, out_dir: str):
     dist.destroy_process_group()
 
 
-def test_gloo_context_parallel_training_matches_single_process(tmp_path):
-    port = 31000 + (os.getpid() * 13) % 2000
-    mp.spawn(_cp_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+@pytest.mark.parametrize("comm", ["p2p", "a2a"])
+def test_gloo_context_parallel_training_matches_single_process(tmp_path, comm):
+    port = 31000 + (os.getpid() * 13) % 2000 + (7 if comm == "a2a" else 0)
+    mp.spawn(_cp_worker, args=(2, port, str(tmp_path), comm), nprocs=2, join=True)
 
 
 def _pp_cp_worker(rank: int, world: int, port: int, out_dir: str):
