@@ -101,13 +101,13 @@ class RLLoop:
             per_tok = 2 * cfg.num_layers * cfg.num_kv_heads * cfg.head_dim * 2
             want = max_running * (max_ctx + page) * per_tok
             # what is really free once weights, gradients and resident optimizer states are placed, keeping
-            # an eighth of the device for activations; expert gradients count as free (the arena is shared)
+            # a seventh of the device for activations; expert gradients count as free (the arena is shared)
             free_now = torch.cuda.mem_get_info(self.actor.device)[0]
             lend = 0
             if getattr(a, "share_kv_grad_memory", True) and self.actor.store.grad.get("expert") is not None:
                 g = self.actor.store.grad["expert"]
                 lend = g.numel() * g.element_size()
-            room = free_now + lend - total // 8
+            room = free_now + lend - total // 7
             kv_bytes = max(min(budget, want, room), per_tok * page * 4)
         pipelined = self.ps.pp.size > 1
         replicate = not pipelined and self.actor.ep_dispatcher is not None and self._replicate_experts_fits(kv_bytes)
@@ -190,7 +190,7 @@ class RLLoop:
         free_now, total = torch.cuda.mem_get_info(self.actor.device)
         g = self.actor.store.grad.get("expert")
         lend = g.numel() * g.element_size() if (g is not None and getattr(a, "share_kv_grad_memory", True)) else 0
-        need = replica + max((kv_bytes or 0) // 2 - lend, 0) + total // 8  # at least half of the wanted KV pool must remain
+        need = replica + max((kv_bytes or 0) // 2 - lend, 0) + total // 7  # at least half of the wanted KV pool must remain
         ok = torch.tensor([1.0 if free_now >= need else 0.0], device=self.actor.device)
         if self.ps.world_size > 1:
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)  # all ranks take the same path
