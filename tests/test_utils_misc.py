@@ -231,3 +231,35 @@ def test_ci_checks_hashes_kl_gate_and_grad_norm(tmp_path):
     C.check_grad_norm(a3, 2.03, 0, 0)
     with pytest.raises(AssertionError):
         C.check_grad_norm(a3, 2.5, 0, 0)
+
+
+def test_launch_command_and_processing_helpers(capsys):
+    import base64
+    import io
+
+    from miles_b200.utils.launch import TrainJob, convert_checkpoint, execute_train
+    from miles_b200.utils.processing_utils import apply_chat_template, decode_image, image_to_data_url
+
+    job = TrainJob(num_gpus=4, args=["--model-preset", "qwen3-4B", "--colocate"], master_port=29601, env={"NCCL_DEBUG": "WARN"})
+    cmd = job.command()
+    assert cmd[1:3] == ["-m", "torch.distributed.run"] and "--nproc-per-node=4" in cmd and cmd[-3:] == ["--model-preset", "qwen3-4B", "--colocate"]
+    env = job.environment({})
+    assert env["NCCL_DEBUG"] == "WARN" and env["CUDA_DEVICE_MAX_CONNECTIONS"] == "1" and env["NCCL_NVLS_ENABLE"] in ("0", "1")
+    assert execute_train(job, dry_run=True) == 0 and "train.py" in capsys.readouterr().out
+    assert convert_checkpoint("a", "b", "native_to_hf", dry_run=True) == 0
+
+    class Tok:
+        def apply_chat_template(self, messages, tokenize, add_generation_prompt, **kw):
+            return ("T" if kw.get("tools") else "") + "|".join(m["content"] for m in messages) + (">" if add_generation_prompt else "")
+
+    assert apply_chat_template(Tok(), [{"role": "user", "content": "hi"}], tools=[{"name": "f"}]) == "Thi>"
+    from PIL import Image
+
+    img = Image.new("RGB", (4, 3), (255, 0, 0))
+    url = image_to_data_url(img)
+    back = decode_image(url)
+    assert back.size == (4, 3) and back.getpixel((0, 0)) == (255, 0, 0)
+    buf = io.BytesIO()
+    img.save(buf, format="PNG")
+    assert decode_image(buf.getvalue()).size == (4, 3)
+    assert decode_image(base64.b64encode(buf.getvalue()).decode()).size == (4, 3)
