@@ -58,20 +58,64 @@ class Collector:
             self.store.append("gpus", r)
         return len(rows)
 
+    def add_engine(self, url: str) -> None:
+        """Scrape this engine's ``/metrics`` (Prometheus text) with every sampling tick."""
+        self.__dict__.setdefault("_engines", []).append(url.rstrip("/"))
+
+    def scrape_engines_once(self, fetch: Optional[Callable[[str], str]] = None) -> int:
+        n = 0
+        for url in self.__dict__.get("_engines", []):
+            try:
+                text = fetch(url + "/metrics") if fetch is not None else _http_get(url + "/metrics")
+            except Exception as e:  # an engine that does not answer is itself a data point
+                self.store.append("engines", {"engine": url, "up": 0, "error": repr(e)[:120]})
+                continue
+            rec = {"engine": url, "up": 1}
+            rec.update(parse_prometheus(text))
+            self.store.append("engines", rec)
+            n += 1
+        return n
+
     # background sampling ---------------------------------------------------------------------------------
     def start(self) -> None:
-        if self._sampler is None or self._thread is not None:
+        if (self._sampler is None and not self.__dict__.get("_engines")) or self._thread is not None:
             return
 
         def loop():
             while not self._stop.wait(self.gpu_interval):
                 self.sample_gpus_once()
+                self.scrape_engines_once()
 
         self._thread = threading.Thread(target=loop, daemon=True)
         self._thread.start()
 
     def stop(self) -> None:
         self._stop.set()
+
+
+def _http_get(url: str, timeout: float = 2.0) -> str:
+    import urllib.request
+
+    with urllib.request.urlopen(url, timeout=timeout) as r:
+        return r.read().decode()
+
+
+def parse_prometheus(text: str) -> dict:
+    """``name{labels} value`` lines -> {name: value} (labels dropped, comments skipped, last sample wins)."""
+    out = {}
+    for line in text.splitlines():
+        line = line.strip()
+        if not line or line.startswith("#"):
+            continue
+        parts = line.rsplit(" ", 1)
+        if len(parts) != 2:
+            continue
+        name = parts[0].split("{", 1)[0].strip()
+        try:
+            out[name] = float(parts[1])
+        except ValueError:
+            continue
+    return out
 
 
 def advisories(store: EventStore, window: int = 20) -> list:
@@ -94,6 +138,14 @@ def advisories(store: EventStore, window: int = 20) -> list:
         norms = [m.get("train/grad_norm") for m in ms if m.get("train/grad_norm") is not None]
         if len(norms) >= 5 and norms[-1] > 10 * (sum(norms[:-1]) / len(norms[:-1]) + 1e-9):
             out.append({"rule": "grad_spike", "text": f"gradient norm {norms[-1]:.2f} is more than 10x its recent mean"})
+    es = store.tail("engines", 16)
+    down = sorted({e["engine"] for e in es[-4:] if not e.get("up")})
+    if down:
+        out.append({"rule": "engine_down", "text": "no answer from " + ", ".join(down)})
+    queued = [e for e in es[-4:] if e.get("miles_b200:num_queue_reqs", 0) > 4 * max(e.get("miles_b200:num_running_reqs", 0), 1)]
+    if queued:
+        out.append({"rule": "engine_queue", "text": f"{queued[-1]['engine']} queues {int(queued[-1]['miles_b200:num_queue_reqs'])} requests: "
+                    "raise --sglang-max-running-requests or add engines"})
     gs = store.tail("gpus", 64)
     low = [g for g in gs if g.get("sm_mhz") and g.get("util", 0) > 80 and g["sm_mhz"] < 1000]
     if low:

@@ -35,3 +35,24 @@ def test_collector_and_advisories_and_http(tmp_path):
     assert set(app.get("/api/streams").json()) == {"gpus", "metrics", "trajectories"}
     assert len(app.get("/api/metrics?limit=3").json()) == 3
     assert any(a["rule"] == "grad_spike" for a in app.get("/api/advisories").json())
+
+
+def test_engine_scrape_and_advisories(tmp_path):
+    from miles_b200.dashboard.collector import Collector, advisories, parse_prometheus
+    from miles_b200.dashboard.store import EventStore
+
+    text = '# HELP x\nmiles_b200:num_running_reqs 2\nmiles_b200:num_queue_reqs{engine="0"} 40\nbad line\n'
+    assert parse_prometheus(text) == {"miles_b200:num_running_reqs": 2.0, "miles_b200:num_queue_reqs": 40.0}
+    st = EventStore(str(tmp_path))
+    col = Collector(st, gpu_sampler=lambda: [])
+    col.add_engine("http://e0/")
+    col.add_engine("http://e1")
+
+    def fetch(url):
+        if "e1" in url:
+            raise OSError("refused")
+        return text
+
+    assert col.scrape_engines_once(fetch) == 1
+    rules = {a["rule"] for a in advisories(st)}
+    assert {"engine_down", "engine_queue"} <= rules
