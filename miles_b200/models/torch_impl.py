@@ -62,16 +62,17 @@ class TorchQwen3:
                 from ..parallel.context_parallel import attention_zigzag, gather_kv_autograd
 
                 lens, cp, rank, group = self.cp_ctx[:4]
+                layout = self.cp_ctx[5] if len(self.cp_ctx) > 5 else "zigzag"
                 if len(self.cp_ctx) > 4 and self.cp_ctx[4] == "a2a":
                     # Ulysses: trade the sequence shard for a head shard, attend over whole sequences, trade back
                     from ..parallel.context_parallel import heads_to_sequence, sequence_to_heads
 
-                    qf, kf, vf = (heads_to_sequence(t, lens, cp, rank, group) for t in (q, k, v))
+                    qf, kf, vf = (heads_to_sequence(t, lens, cp, rank, group, layout) for t in (q, k, v))
                     full_cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32, device=q.device)
-                    att = sequence_to_heads(R.attention_varlen(qf, kf, vf, full_cu, scale), lens, cp, rank, group)
+                    att = sequence_to_heads(R.attention_varlen(qf, kf, vf, full_cu, scale), lens, cp, rank, group, layout)
                 else:
-                    kf, vf = gather_kv_autograd(k, v, lens, cp, rank, group)
-                    att = attention_zigzag(q, kf, vf, lens, cp, rank, scale)
+                    kf, vf = gather_kv_autograd(k, v, lens, cp, rank, group, layout)
+                    att = attention_zigzag(q, kf, vf, lens, cp, rank, scale, layout)
             else:
                 att = R.attention_varlen(q, k, v, cu, scale)
         else:

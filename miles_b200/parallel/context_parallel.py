@@ -37,40 +37,57 @@ def zigzag_bounds(n: int, cp: int, rank: int) -> list:
     return [(starts[a], starts[a + 1]), (starts[b], starts[b + 1])]
 
 
-def zigzag_slice(x: torch.Tensor, lens: Sequence[int], cp: int, rank: int) -> torch.Tensor:
+def segments(lens: Sequence[int], cp: int, rank: int, layout: str = "zigzag") -> list:
+    """Per sample, the ``(start, end)`` pieces of it that ``rank`` owns. ``zigzag``: an early and a late chunk of every
+    sample; ``allgather``: the intersection of the sample with the rank's contiguous piece of the concatenated batch
+    (possibly none)."""
+    if layout == "zigzag":
+        return [zigzag_bounds(n, cp, rank) for n in lens]
+    lo, hi, _ = contiguous_bounds(sum(lens), cp, rank)
+    out, s0 = [], 0
+    for n in lens:
+        a, b = max(lo, s0) - s0, min(hi, s0 + n) - s0
+        out.append([(a, b)] if b > a else [])
+        s0 += n
+    return out
+
+
+def zigzag_slice(x: torch.Tensor, lens: Sequence[int], cp: int, rank: int, layout: str = "zigzag") -> torch.Tensor:
     """Rows of a packed ``[T, ...]`` tensor owned by ``rank`` (samples stay in order, early chunk before late chunk)."""
     if cp == 1:
         return x
     out, s0 = [], 0
-    for n in lens:
-        for a, b in zigzag_bounds(n, cp, rank):
+    for n, segs in zip(lens, segments(lens, cp, rank, layout)):
+        for a, b in segs:
             out.append(x[s0 + a:s0 + b])
         s0 += n
-    return torch.cat(out, 0)
+    return torch.cat(out, 0) if out else x[:0]
 
 
-def zigzag_positions(lens: Sequence[int], cp: int, rank: int) -> torch.Tensor:
+def zigzag_positions(lens: Sequence[int], cp: int, rank: int, layout: str = "zigzag") -> torch.Tensor:
     """Position of every local token inside its sample (what RoPE and the causal mask need)."""
     out = []
-    for n in lens:
-        for a, b in zigzag_bounds(n, cp, rank):
+    for segs in segments(lens, cp, rank, layout):
+        for a, b in segs:
             out.append(torch.arange(a, b, dtype=torch.int32))
     return torch.cat(out) if out else torch.zeros(0, dtype=torch.int32)
 
 
-def unzigzag(parts: Sequence[torch.Tensor], lens: Sequence[int], cp: int) -> torch.Tensor:
+def unzigzag(parts: Sequence[torch.Tensor], lens: Sequence[int], cp: int, layout: str = "zigzag") -> torch.Tensor:
     """Inverse of :func:`zigzag_slice`: ``parts[r]`` are rank ``r``'s rows; returns the packed tensor in sample order."""
     if cp == 1:
         return parts[0]
     cursors = [0] * cp
+    segs = [segments(lens, cp, r, layout) for r in range(cp)]
     out = []
-    for n in lens:
-        chunks = {}
+    for si in range(len(lens)):
+        chunks = []
         for r in range(cp):
-            for idx, (a, b) in zip((r, 2 * cp - 1 - r), zigzag_bounds(n, cp, r)):
-                chunks[idx] = parts[r][cursors[r]:cursors[r] + (b - a)]
+            for a, b in segs[r][si]:
+                chunks.append((a, parts[r][cursors[r]:cursors[r] + (b - a)]))
                 cursors[r] += b - a
-        out.extend(chunks[i] for i in range(2 * cp))
+        chunks.sort(key=lambda t: t[0])
+        out.extend(c for _, c in chunks)
     return torch.cat(out, 0)
 
 
@@ -151,9 +168,10 @@ class _GatherRows(torch.autograd.Function):
         return g[off:off + ctx.sizes[ctx.rank]], None, None, None
 
 
-def gather_kv_autograd(k_local: torch.Tensor, v_local: torch.Tensor, lens: Sequence[int], cp: int, rank: int, group) -> tuple:
+def gather_kv_autograd(k_local: torch.Tensor, v_local: torch.Tensor, lens: Sequence[int], cp: int, rank: int, group,
+                       layout: str = "zigzag") -> tuple:
     """K and V of all ranks in sample order, differentiable (see ``_GatherRows``)."""
-    sizes = [sum(b - a for n in lens for a, b in zigzag_bounds(n, cp, r)) for r in range(cp)]
+    sizes = _local_sizes(lens, cp, layout)
     out = []
     for t in (k_local, v_local):
         full = _GatherRows.apply(t, sizes, rank, group)
@@ -161,19 +179,19 @@ def gather_kv_autograd(k_local: torch.Tensor, v_local: torch.Tensor, lens: Seque
         for s in sizes:
             parts.append(full[off:off + s])
             off += s
-        out.append(unzigzag(parts, lens, cp))
+        out.append(unzigzag(parts, lens, cp, layout))
     return out[0], out[1]
 
 
 def attention_zigzag(q_local: torch.Tensor, k_full: torch.Tensor, v_full: torch.Tensor, lens: Sequence[int], cp: int, rank: int,
-                     scale: float) -> torch.Tensor:
+                     scale: float, layout: str = "zigzag") -> torch.Tensor:
     """Causal attention of the local (zigzag) queries against the gathered keys / values, in plain PyTorch ops
     (autograd path of the PyTorch model; the sm_100a path uses the tile table of ``build_cp_tiles``)."""
     Hq, Hk = q_local.shape[1], k_full.shape[1]
     G = Hq // Hk
     outs, q0, s0 = [], 0, 0
-    for n in lens:
-        for a, b in zigzag_bounds(n, cp, rank):
+    for n, segs in zip(lens, segments(lens, cp, rank, layout)):
+        for a, b in segs:
             if b > a:
                 qs = q_local[q0:q0 + (b - a)].transpose(0, 1).float()                        # [Hq, Lq, D]
                 ks = k_full[s0:s0 + b].transpose(0, 1).float().repeat_interleave(G, dim=0)   # keys 0 .. b-1 of the sample
@@ -188,12 +206,12 @@ def attention_zigzag(q_local: torch.Tensor, k_full: torch.Tensor, v_full: torch.
     return torch.cat(outs, 0) if outs else q_local.new_zeros(q_local.shape)
 
 
-def local_index_map(lens: Sequence[int], cp: int, rank: int) -> torch.Tensor:
+def local_index_map(lens: Sequence[int], cp: int, rank: int, layout: str = "zigzag") -> torch.Tensor:
     """int64 [sum(lens)]: index of every packed token inside the rank's local token list, -1 if another rank owns it."""
     idx = torch.full((sum(lens),), -1, dtype=torch.int64)
     cur, s0 = 0, 0
-    for n in lens:
-        for a, b in zigzag_bounds(n, cp, rank):
+    for n, segs in zip(lens, segments(lens, cp, rank, layout)):
+        for a, b in segs:
             idx[s0 + a:s0 + b] = torch.arange(cur, cur + (b - a))
             cur += b - a
         s0 += n
@@ -218,29 +236,29 @@ class _AllToAllRows(torch.autograd.Function):
         return gx, None, None, None
 
 
-def _local_sizes(lens: Sequence[int], cp: int) -> list:
-    return [sum(b - a for n in lens for a, b in zigzag_bounds(n, cp, r)) for r in range(cp)]
+def _local_sizes(lens: Sequence[int], cp: int, layout: str = "zigzag") -> list:
+    return [sum(b - a for segs in segments(lens, cp, r, layout) for a, b in segs) for r in range(cp)]
 
 
-def heads_to_sequence(x_local: torch.Tensor, lens: Sequence[int], cp: int, rank: int, group) -> torch.Tensor:
+def heads_to_sequence(x_local: torch.Tensor, lens: Sequence[int], cp: int, rank: int, group, layout: str = "zigzag") -> torch.Tensor:
     """``[T_local, H, D]`` (this rank's tokens, all heads) -> ``[T, H / cp, D]`` (all tokens in sample order, this
     rank's share of the heads): the first all-to-all of Ulysses-style context parallelism."""
     T, H, D = x_local.shape
     assert H % cp == 0, "the all-to-all layout needs the head count to divide by the context-parallel size"
-    sizes = _local_sizes(lens, cp)
+    sizes = _local_sizes(lens, cp, layout)
     send = x_local.view(T, cp, H // cp, D).transpose(0, 1).reshape(cp * T, H // cp, D)  # block j goes to rank j
     got = _AllToAllRows.apply(send, [T] * cp, sizes, group)
     parts, off = [], 0
     for s in sizes:
         parts.append(got[off:off + s])
         off += s
-    return unzigzag(parts, lens, cp)
+    return unzigzag(parts, lens, cp, layout)
 
 
-def sequence_to_heads(y_full: torch.Tensor, lens: Sequence[int], cp: int, rank: int, group) -> torch.Tensor:
+def sequence_to_heads(y_full: torch.Tensor, lens: Sequence[int], cp: int, rank: int, group, layout: str = "zigzag") -> torch.Tensor:
     """Inverse of :func:`heads_to_sequence` for the attention output."""
-    sizes = _local_sizes(lens, cp)
-    send = torch.cat([zigzag_slice(y_full, lens, cp, r) for r in range(cp)], 0)  # block r: rank r's tokens, my heads
+    sizes = _local_sizes(lens, cp, layout)
+    send = torch.cat([zigzag_slice(y_full, lens, cp, r, layout) for r in range(cp)], 0)  # block r: rank r's tokens, my heads
     T = sizes[rank]
     got = _AllToAllRows.apply(send, sizes, [T] * cp, group)                     # block j: my tokens, rank j's heads
     Hs, D = y_full.shape[1], y_full.shape[2]

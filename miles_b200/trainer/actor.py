@@ -237,7 +237,7 @@ class TrainActor:
         if not self.is_torch:
             raise NotImplementedError("training under context parallelism runs on the PyTorch model path; the sm_100a "
                                       "path has the context-parallel attention forward only")
-        self.model.cp_ctx = (cp[0], cp[1], cp[2], self.ps.cp.group, getattr(self.ps, "cp_comm_type", "p2p"))
+        self.model.cp_ctx = (cp[0], cp[1], cp[2], self.ps.cp.group, getattr(self.ps, "cp_comm_type", "p2p"), cp[3])
 
     def _forward_logprobs(self, mb: MicroBatch, replay=None, record=None):
         inv_t = 1.0 / self.args.rollout_temperature
@@ -430,7 +430,7 @@ class TrainActor:
             assert a.advantage_estimator in ("grpo", "reinforce_plus_plus_baseline") or a.loss_type == "sft_loss", \
                 "context parallelism supports estimators whose per-token terms need no other rank's tokens"
         for mb in mbs:
-            d = mb.cp_shard(cp, self.ps.cp.rank).to_device(self.device)
+            d = mb.cp_shard(cp, self.ps.cp.rank, "allgather" if getattr(a, "allgather_cp", False) else "zigzag").to_device(self.device)
             self.h2d_bytes += d.h2d_bytes
             out.append(d)
         return out

@@ -47,33 +47,34 @@ class MicroBatch:
     def num_samples(self) -> int:
         return int(self.cu_seqlens.numel() - 1)
 
-    def cp_shard(self, cp: int, rank: int) -> "MicroBatch":
+    def cp_shard(self, cp: int, rank: int, layout: str = "zigzag") -> "MicroBatch":
         """This rank's share of the micro-batch under context parallelism (zigzag layout): the local tokens with
         their positions and routing rows, and the response entries whose logit row is local. Per-sample quantities
         (rewards, loss denominators) stay whole, so per-sample means still divide by the sample's full token count
         and the ranks' partial losses add up. ``extras["cp"] = (lens, cp, rank)`` tells the model how to attend."""
         if cp == 1:
             return self
-        from ..parallel.context_parallel import local_index_map, zigzag_positions, zigzag_slice
+        from ..parallel.context_parallel import local_index_map, segments, zigzag_positions, zigzag_slice
 
         lens = (self.cu_seqlens[1:] - self.cu_seqlens[:-1]).tolist()
-        lmap = local_index_map(lens, cp, rank).to(self.rows.device)
+        lmap = local_index_map(lens, cp, rank, layout).to(self.rows.device)
         loc = lmap[self.rows]
         keep = loc >= 0
         f = lambda t: None if t is None else t[keep]
         seg = self.seg[keep]
         counts = torch.zeros(len(lens), dtype=torch.int64, device=seg.device).index_add_(0, seg, torch.ones_like(seg))
         resp_cu = torch.cat([counts.new_zeros(1), counts.cumsum(0)])
-        local_lens = [sum(b - a for a, b in _bounds(n, cp, rank)) for n in lens]
+        local_lens = [sum(b - a for a, b in segs) for segs in segments(lens, cp, rank, layout)]
         cu = torch.tensor([0] + list(torch.tensor(local_lens).cumsum(0).tolist()), dtype=torch.int32, device=self.cu_seqlens.device)
         mb = MicroBatch(
-            tokens=zigzag_slice(self.tokens, lens, cp, rank), positions=zigzag_positions(lens, cp, rank).to(self.positions.device),
+            tokens=zigzag_slice(self.tokens, lens, cp, rank, layout),
+            positions=zigzag_positions(lens, cp, rank, layout).to(self.positions.device),
             cu_seqlens=cu, max_seqlen=max(local_lens) if local_lens else 0, rows=loc[keep], targets=self.targets[keep], seg=seg,
             resp_cu=resp_cu, loss_mask=self.loss_mask[keep], rewards=self.rewards, denoms=self.denoms,
             sample_indices=self.sample_indices, rollout_log_probs=f(self.rollout_log_probs), teacher_log_probs=f(self.teacher_log_probs),
-            replay=None if self.replay is None else zigzag_slice(self.replay, lens, cp, rank),
+            replay=None if self.replay is None else zigzag_slice(self.replay, lens, cp, rank, layout),
             extras={k: (v[keep] if isinstance(v, torch.Tensor) and v.shape[:1] == keep.shape else v) for k, v in self.extras.items()})
-        mb.extras["cp"] = (lens, cp, rank)
+        mb.extras["cp"] = (lens, cp, rank, layout)
         return mb
 
     def to_device(self, device, non_blocking: bool = True) -> "MicroBatch":
@@ -91,12 +92,6 @@ class MicroBatch:
         mb = MicroBatch(**kw)
         mb.h2d_bytes = nbytes
         return mb
-
-
-def _bounds(n: int, cp: int, rank: int):
-    from ..parallel.context_parallel import zigzag_bounds
-
-    return zigzag_bounds(n, cp, rank)
 
 
 def _pin(t: torch.Tensor, pin: bool) -> torch.Tensor:

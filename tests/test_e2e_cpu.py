@@ -112,9 +112,10 @@ def _cp_worker(rank: int, world: int, port: int, out_dir: str, comm: str = "p2p"
     from miles_b200.trainer.actor import TrainActor
 
     args = parse_args(BASE + ["--num-rollout", "1", "--actor-num-gpus-per-node", str(world), "--distributed-backend", "gloo",
-                              "--context-parallel-size", str(world), "--cp-comm-type", comm])
+                              "--context-parallel-size", str(world), "--cp-comm-type", comm.split("+")[0]]
+                      + (["--allgather-cp"] if comm.endswith("+allgather") else []))
     loop = RLLoop(args)
-    assert loop.ps.cp.size == world and loop.ps.dp.size == 1 and loop.ps.cp_comm_type == comm
+    assert loop.ps.cp.size == world and loop.ps.dp.size == 1 and loop.ps.cp_comm_type == comm.split("+")[0]
     # a single-process trainer with the same initial weights trains on the same pooled samples
     solo = TrainActor(copy.copy(args), "actor", ParallelState())
     for g in solo.store.flat:
@@ -137,9 +138,9 @@ def _cp_worker(rank: int, world: int, port: int, out_dir: str, comm: str = "p2p"
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("comm", ["p2p", "a2a"])
+@pytest.mark.parametrize("comm", ["p2p", "a2a", "p2p+allgather"])
 def test_gloo_context_parallel_training_matches_single_process(tmp_path, comm):
-    port = 31000 + (os.getpid() * 13) % 2000 + (7 if comm == "a2a" else 0)
+    port = 31000 + (os.getpid() * 13) % 2000 + {"p2p": 0, "a2a": 7, "p2p+allgather": 14}[comm]
     mp.spawn(_cp_worker, args=(2, port, str(tmp_path), comm), nprocs=2, join=True)
 
 
