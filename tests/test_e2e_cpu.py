@@ -46,6 +46,7 @@ def test_single_process_grpo_steps(tmp_path):
 
 def _worker(rank: int, world: int, port: int, out_dir: str):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(2)  # several ranks share the host cores
     from miles_b200.loop import RLLoop
 
     args = parse_args(BASE + ["--num-rollout", "2", "--actor-num-gpus-per-node", str(world), "--distributed-backend", "gloo"])
@@ -73,6 +74,7 @@ def test_gloo_world_size_2(tmp_path):
 
 def _pp_worker(rank: int, world: int, port: int, out_dir: str):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(2)  # several ranks share the host cores
     from miles_b200.loop import RLLoop
 
     args = parse_args(BASE + ["--num-rollout", "2", "--actor-num-gpus-per-node", str(world), "--distributed-backend", "gloo",
@@ -104,6 +106,7 @@ def test_gloo_pipeline_parallel_two_stages(tmp_path):
 
 def _cp_worker(rank: int, world: int, port: int, out_dir: str, comm: str = "p2p"):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(2)  # several ranks share the host cores
     import copy
 
     from miles_b200.loop import RLLoop
@@ -146,6 +149,7 @@ def test_gloo_context_parallel_training_matches_single_process(tmp_path, comm):
 
 def _pp_cp_worker(rank: int, world: int, port: int, out_dir: str):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(2)  # several ranks share the host cores
     from miles_b200.loop import RLLoop
 
     args = parse_args(BASE + ["--num-rollout", "1", "--actor-num-gpus-per-node", str(world), "--distributed-backend", "gloo",

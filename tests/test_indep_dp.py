@@ -38,6 +38,7 @@ def _actor(seed):
 
 
 def _cell(cell, ports, ret):
+    torch.set_num_threads(2)  # several ranks share the host cores
     g = ReconfigurableGroup("gloo", timeout_s=30)
     act = _actor(seed=7)
     # quorum 1: three cells average their gradients

@@ -42,6 +42,7 @@ def _inputs():
 
 
 def _worker(rank, world, port, ret):
+    torch.set_num_threads(2)  # several ranks share the host cores
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     pg = PipeGroup(None, rank, world, list(range(world)))
     W = _weights(world)[rank].clone().requires_grad_(True)

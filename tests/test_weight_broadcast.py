@@ -22,6 +22,7 @@ def test_iter_buckets_respects_the_byte_limit():
 
 
 def _proc(rank, port, q_hdr, ret):
+    torch.set_num_threads(2)  # several ranks share the host cores
     cfg = get_config("qwen3-tiny")
     init_update_group("127.0.0.1", port, rank, 2, "w", backend="gloo", timeout_s=60)
     if rank == 0:  # trainer
