@@ -119,3 +119,48 @@ def test_session_store_token_level_mode():
                     "<|im_start|>assistant\ndone<|im_end|>")
     d = traj.to_sample_dict()
     assert sum(d["loss_mask"]) == len(tok.encode("abc")) + len(tok.encode("done<|im_end|>"))
+
+
+async def _toy_agent(chat, sample, args):
+    """Two tool rounds: ask, read the 'tool', answer."""
+    msgs = [{"role": "user", "content": sample.prompt}]
+    a1 = await chat(msgs)
+    msgs += [{"role": "assistant", "content": a1["content"]}, {"role": "tool", "content": "42"}]
+    a2 = await chat(msgs, max_tokens=8)
+    return {"answer": a2["content"], "turns": 2}
+
+
+def test_agentic_generate_builds_a_masked_multi_turn_sample():
+    import asyncio
+    from types import SimpleNamespace as NS
+
+    from miles_b200.rollout.base_types import GenerateFnInput
+    from miles_b200.rollout.generate_hub import agentic
+    from miles_b200.utils.types import Sample
+
+    tok = ToyTokenizer()
+    outs = iter([tok.encode("call"), tok.encode("done<|im_end|>")])
+    seen = []
+
+    class Client:
+        async def generate(self, payload):
+            seen.append(payload)
+            o = next(outs)
+            return {"output_ids": o, "text": tok.decode(o), "meta_info": {
+                "output_token_logprobs": [(-0.25, t) for t in o], "finish_reason": {"type": "stop"}, "weight_version": 7}}
+
+    args = NS(custom_agent_function_path="tests.test_tito._toy_agent", tito_family="chatml", use_rollout_routing_replay=False)
+    state = NS(args=args, client=Client(), tokenizer=tok)
+    sample = Sample(index=0, prompt="q?")
+    inp = GenerateFnInput(state=state, sample=sample, sampling_params={"max_new_tokens": 64, "temperature": 1.0}, evaluation=False)
+    out = asyncio.run(agentic.generate(inp)).samples
+    text = tok.decode(out.tokens)
+    assert text == ("<|im_start|>user\nq?<|im_end|>\n<|im_start|>assistant\ncall<|im_end|>\n<|im_start|>tool\n42<|im_end|>\n"
+                    "<|im_start|>assistant\ndone<|im_end|>")
+    n_gen = len(tok.encode("call")) + len(tok.encode("done<|im_end|>"))
+    assert sum(out.loss_mask) == n_gen and len(out.loss_mask) == out.response_length == len(out.rollout_log_probs)
+    assert out.metadata["agent_result"] == {"answer": "done", "turns": 2} or out.metadata["agent_result"]["turns"] == 2
+    assert out.weight_versions == [7] and out.status == Sample.Status.COMPLETED
+    # the second request continued from the exact tokens of the first turn, and honoured the per-call token cap
+    assert seen[1]["input_ids"][:len(seen[0]["input_ids"])] == seen[0]["input_ids"]
+    assert seen[1]["sampling_params"]["max_new_tokens"] == 8
