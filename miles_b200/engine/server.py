@@ -9,8 +9,6 @@
 ``/weights_checker``, ``/metrics``.  The engine loop runs as an asyncio task of the same process, so the
 server needs no scheduler or detokenizer subprocesses.
 """
-from __future__ import annotations
-
 import asyncio
 import time
 from typing import Any, Optional

@@ -7,8 +7,6 @@ method).  ``MiniFTController`` polls cell health, suspends unhealthy cells and r
 back-off.  Reference: miles/utils/ft_utils/control_server/server.py:1-156, mini_ft_controller.py:1-221;
 flags ``--control-server-port``, ``--mini-ft-controller-*``.
 """
-from __future__ import annotations
-
 import time
 from typing import Callable, Optional
 

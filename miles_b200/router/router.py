@@ -6,8 +6,6 @@ quarantines a worker after ``failure_threshold`` consecutive failures (it is re-
 Reference: miles/router/router.py:34-236 (``--use-miles-router``, ``--miles-router-*`` flags).
 Policies: ``least_inflight`` (default), ``round_robin``, ``consistent_hashing`` on a routing key header.
 """
-from __future__ import annotations
-
 import asyncio
 import hashlib
 import itertools

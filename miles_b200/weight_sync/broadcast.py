@@ -190,3 +190,40 @@ class BroadcastWeightUpdater:
             e.post("/update_weight_version", {"new_version": version})
             e.post("/continue_generation", {})
         return {"perf/update_weights_time": time.perf_counter() - t0, "perf/update_weights_bytes": moved, "weight_version": version}
+
+
+class HttpEngineHandle:
+    """What ``BroadcastWeightUpdater`` needs from an engine in another process: blocking and background POSTs to its
+    HTTP surface (`engine/server.py`). Background requests run on a small thread pool, because the engine answers
+    ``/init_weights_update_group`` and ``/update_weights_from_distributed`` only once the trainer's side of the
+    collective has started."""
+
+    def __init__(self, base_url: str, timeout_s: float = 300.0, workers: int = 2):
+        from concurrent.futures import ThreadPoolExecutor
+
+        self.base = base_url.rstrip("/")
+        self.timeout_s = timeout_s
+        self._pool = ThreadPoolExecutor(max_workers=workers)
+
+    def post(self, path: str, payload: Optional[dict] = None) -> dict:
+        import json
+        import urllib.request
+
+        req = urllib.request.Request(self.base + path, data=json.dumps(payload or {}).encode(),
+                                     headers={"Content-Type": "application/json"}, method="POST")
+        with urllib.request.urlopen(req, timeout=self.timeout_s) as r:
+            body = r.read().decode()
+        return json.loads(body) if body else {}
+
+    def post_async(self, path: str, payload: Optional[dict] = None):
+        return self._pool.submit(self.post, path, payload)
+
+    def get(self, path: str) -> dict:
+        import json
+        import urllib.request
+
+        with urllib.request.urlopen(self.base + path, timeout=self.timeout_s) as r:
+            return json.loads(r.read().decode())
+
+    def close(self) -> None:
+        self._pool.shutdown(wait=False)

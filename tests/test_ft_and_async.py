@@ -204,3 +204,50 @@ def test_math_and_misc_rewards():
     a.rm_type = "deterministic_random"
     s = Sample(prompt="p", response="r")
     assert asyncio.run(async_rm(a, s)) == asyncio.run(async_rm(a, s))
+
+
+def test_control_server_and_router_over_http():
+    """The JSON-body endpoints answer through a real HTTP stack (request objects are resolved by the framework)."""
+    from fastapi.testclient import TestClient
+
+    from miles_b200.ft.cells import TrainGroup
+    from miles_b200.ft.control_server import build_control_app
+    from miles_b200.router.router import MilesRouter, build_router_app
+
+    class Actor:
+        def __init__(self):
+            self.faults = []
+
+        def init(self):
+            return 0
+
+        def inject_fault(self, kind):
+            self.faults.append(kind)
+
+    actors = {}
+
+    def factory(i):
+        actors[i] = Actor()
+        return [actors[i]]
+
+    group = TrainGroup(2, factory)
+    group.init()
+    c = TestClient(build_control_app(group))
+    cells = c.get("/api/v1/cells").json()
+    name = (cells["items"] if isinstance(cells, dict) else cells)[0]["metadata"]["name"]
+    r = c.patch(f"/api/v1/cells/{name}", json={"spec": {"suspend": True}})
+    assert r.status_code == 200
+    r = c.post(f"/api/v1/cells/{name}/inject-fault", json={"type": "exception"})
+    assert r.status_code == 200 and "delivered" in r.json()
+    assert c.post(f"/api/v1/cells/{name}/inject-fault", json={"type": "segfault"}).status_code == 400  # host-side faults only
+
+    router = MilesRouter(health_interval=3600)
+
+    async def fake_forward(method, path, body, headers):
+        return 200, b'{"echo": "' + path.encode() + b'"}', "application/json"
+
+    router.forward = fake_forward
+    rc = TestClient(build_router_app(router))
+    assert rc.post("/add_worker", params={"url": "http://w0"}).status_code == 200
+    r = rc.post("/generate", json={"input_ids": [1, 2]})
+    assert r.status_code == 200 and r.json() == {"echo": "/generate"}

@@ -103,3 +103,61 @@ def test_engine_endpoints_adapters_profile_and_layout(tmp_path):
     r = c.post("/pull_weights", json={"path": str(tmp_path / "delta" / "v00000001"), "weight_version": 1})
     assert r.status_code == 200 and r.json()["num_tensors"] == len(new.params)
     assert torch.equal(st.flat["dense"], new.flat["dense"]) and eng.weight_version == 1
+
+
+def _serve(port, ready):
+    torch.set_num_threads(2)
+    from miles_b200.engine import Engine
+    from miles_b200.engine.server import serve
+    from miles_b200.models import build_model
+
+    cfg = get_config("qwen3-tiny")
+    st = ParamStore(cfg, "cpu", torch.float32, seed=2)  # starts from other weights than the trainer
+    eng = Engine(build_model(cfg, st), max_running=2, page_size=8, max_seq_len=64)
+    ready.set()
+    serve(eng, port=port)
+
+
+def test_updater_drives_an_engine_server_in_another_process():
+    """The whole disaggregated path: HTTP announcements + broadcasts on a dedicated gloo group."""
+    import time
+    from types import SimpleNamespace as NS
+
+    from miles_b200.weight_sync.broadcast import BroadcastWeightUpdater, HttpEngineHandle
+
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    ready = ctx.Event()
+    srv = ctx.Process(target=_serve, args=(port, ready), daemon=True)
+    srv.start()
+    try:
+        assert ready.wait(120)
+        h = HttpEngineHandle(f"http://127.0.0.1:{port}", timeout_s=60)
+        for _ in range(100):  # the HTTP server comes up a moment after the engine is built
+            try:
+                h.get("/health")
+                break
+            except Exception:
+                time.sleep(0.2)
+        cfg = get_config("qwen3-tiny")
+        src = ParamStore(cfg, "cpu", torch.float32, seed=1)
+        src.version = 4
+        actor = NS(store=src, on_gpu=False, args=NS(pause_generation_mode="retract"), ps=None)
+        before = h.post("/weights_checker", {"action": "checksum"})["checksum"]
+        up = BroadcastWeightUpdater(actor, [h], group_name="w-http", buffer_bytes=1 << 20, backend="gloo")
+        m = up.update()
+        after = h.post("/weights_checker", {"action": "checksum"})["checksum"]
+        want = src.checksum()
+        assert before != after and all(abs(after[g] - want[g]) <= 1e-3 * max(1.0, abs(want[g])) for g in want)
+        assert h.get("/get_weight_version")["weight_version"] == 4 and m["perf/update_weights_bytes"] > 0
+        # a second update reuses the group
+        src.flat["dense"].add_(0.25)
+        src.version = 5
+        up.update()
+        after2 = h.post("/weights_checker", {"action": "checksum"})["checksum"]
+        assert abs(after2["dense"] - src.checksum()["dense"]) <= 1e-3 * abs(src.checksum()["dense"])
+        up.disconnect()
+        h.close()
+    finally:
+        srv.terminate()
+        srv.join(10)
