@@ -157,6 +157,15 @@ def test_updater_drives_an_engine_server_in_another_process():
         after2 = h.post("/weights_checker", {"action": "checksum"})["checksum"]
         assert abs(after2["dense"] - src.checksum()["dense"]) <= 1e-3 * abs(src.checksum()["dense"])
         up.disconnect()
+        # the generation endpoints answer over the same HTTP surface, with the weights that just arrived
+        assert h.get("/health_generate")["status"] == "ok"
+        out = h.post("/generate", {"input_ids": [1, 2, 3, 4], "sampling_params": {"max_new_tokens": 5, "temperature": 0.0},
+                                   "return_logprob": True})
+        assert len(out["output_ids"]) == 5 and len(out["meta_info"]["output_token_logprobs"]) == 5
+        assert out["meta_info"]["weight_version"] == 5 and out["meta_info"]["finish_reason"]["type"] == "length"
+        assert h.post("/pause_generation", {"mode": "abort"})["success"] and h.post("/continue_generation", {})["success"]
+        info = h.get("/server_info")
+        assert info["stats"]["decode_tokens"] >= 4 and info["stats"]["prefill_tokens"] >= 4  # the first token comes out of the prefill
         h.close()
     finally:
         srv.terminate()
