@@ -67,7 +67,10 @@ class RLLoop:
             self.critic = TrainActor(cargs, "critic", self.ps)
         self.engine: Optional[Engine] = None
         self.client: Optional[EngineClient] = None
-        if not getattr(args, "debug_train_only", False):
+        self.weight_updater = None
+        if getattr(args, "rollout_engine_urls", None) and not getattr(args, "debug_train_only", False):
+            self._connect_remote_engines([u for u in args.rollout_engine_urls.split(",") if u])
+        elif not getattr(args, "debug_train_only", False):
             if args.offload_train:
                 self.actor.sleep()  # gradients are only needed inside train(); the KV cache gets the memory first
             self._build_engine()
@@ -174,6 +177,19 @@ class RLLoop:
             if self.ps.world_size > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MIN)
             self.actor.opt.promote_offloaded(int(t.item()))
+
+    def _connect_remote_engines(self, urls: list) -> None:
+        """Disaggregated mode: the engines run in other processes (`engine/server.py`). Generation goes over HTTP, the
+        weight update over a process group of its own that the trainer's first rank and the engines join."""
+        from .engine.remote import RemoteEngineClient
+        from .weight_sync.broadcast import BroadcastWeightUpdater, HttpEngineHandle
+
+        self.client = RemoteEngineClient(urls, self.tokenizer)
+        self.rollout_store = None
+        if self.ps.rank == 0:
+            handles = [HttpEngineHandle(u) for u in urls]
+            self.weight_updater = BroadcastWeightUpdater(
+                self.actor, handles, buffer_bytes=int(getattr(self.args, "update_weight_buffer_size", None) or (512 << 20)))
 
     def _replica_bytes(self) -> int:
         cfg = self.actor.cfg
@@ -315,7 +331,14 @@ class RLLoop:
         return metrics
 
     def update_weights(self) -> dict:
-        if self.engine is None or getattr(self.args, "debug_skip_weight_update", False):
+        if getattr(self.args, "debug_skip_weight_update", False):
+            return {}
+        if getattr(self.args, "rollout_engine_urls", None):
+            out = self.weight_updater.update() if self.weight_updater is not None else {}
+            if self.ps.world_size > 1:
+                dist.barrier()  # nobody generates with the old weights while the first rank is still sending
+            return out
+        if self.engine is None:
             return {}
         return self.actor.update_weights()
 
@@ -366,7 +389,7 @@ class RLLoop:
     def run(self) -> list:
         a = self.args
         history = []
-        if self.engine is not None and not getattr(a, "debug_skip_weight_update", False):
+        if (self.engine is not None or getattr(a, "rollout_engine_urls", None)) and not getattr(a, "debug_skip_weight_update", False):
             self.update_weights()  # engines start from the trainer's weights
         if a.eval_interval is not None and not getattr(a, "skip_eval_before_train", False) and self.start_rollout_id == 0:
             self.evaluate(-1)

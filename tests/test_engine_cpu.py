@@ -155,3 +155,42 @@ def test_overlapped_decode_matches_step_by_step_and_handles_unforeseen_stops():
     assert any(r["meta_info"]["finish_reason"]["type"] == "stop" for r in b)
     assert ovl._pending is None and not ovl.running and ovl.pool.num_free == ovl.num_pages - 1
     assert ovl.stats["decode_steps"] >= seq.stats["decode_steps"] - steps0  # speculated steps whose rows were dropped count too
+
+
+def test_remote_client_balances_and_fans_out():
+    from miles_b200.engine.remote import RemoteEngineClient
+
+    calls = []
+    gate = asyncio.Event()
+
+    async def transport(method, url, payload):
+        calls.append((method, url))
+        if url.endswith("/generate"):
+            await gate.wait()
+            return 200, {"output_ids": [1], "meta_info": {"finish_reason": {"type": "stop"}}}
+        if url.endswith("/get_weight_version"):
+            return 200, {"weight_version": 3}
+        if url.endswith("/health_generate"):
+            if "e1" in url:
+                raise OSError("down")
+            return 200, {"status": "ok"}
+        return 200, {"success": True}
+
+    async def main():
+        c = RemoteEngineClient(["http://e0/", "http://e1"], transport=transport, max_retries=0)
+        tasks = [asyncio.ensure_future(c.generate({"input_ids": [1]})) for _ in range(4)]
+        await asyncio.sleep(0.01)
+        assert c.inflight == {"http://e0": 2, "http://e1": 2}  # least in flight
+        same = [c._pick("session-a") for _ in range(3)]
+        assert len(set(same)) == 1  # a session sticks to its engine
+        gate.set()
+        outs = await asyncio.gather(*tasks)
+        assert all(o["output_ids"] == [1] for o in outs) and c.inflight == {"http://e0": 0, "http://e1": 0}
+        await c.pause_generation("abort")
+        await c.continue_generation()
+        assert await c.weight_versions() == [3, 3]
+        assert await c.health() == {"http://e0": True, "http://e1": False}
+        return c
+
+    asyncio.run(main())
+    assert sum(u.endswith("/pause_generation") for _, u in calls) == 2

@@ -170,3 +170,44 @@ def test_updater_drives_an_engine_server_in_another_process():
     finally:
         srv.terminate()
         srv.join(10)
+
+
+def test_disaggregated_loop_generates_remotely_and_broadcasts_weights():
+    """`--rollout-engine-urls`: the trainer process has no engine; it generates over HTTP and pushes weights through
+    the dedicated group. On-policy parity (trainer vs rollout log-probs) proves the engine got the right weights."""
+    import time
+
+    from miles_b200.loop import RLLoop
+    from miles_b200.utils.arguments import parse_args
+    from miles_b200.weight_sync.broadcast import HttpEngineHandle
+
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    ready = ctx.Event()
+    srv = ctx.Process(target=_serve, args=(port, ready), daemon=True)
+    srv.start()
+    try:
+        assert ready.wait(120)
+        h = HttpEngineHandle(f"http://127.0.0.1:{port}", timeout_s=60)
+        for _ in range(100):
+            try:
+                h.get("/health")
+                break
+            except Exception:
+                time.sleep(0.2)
+        args = parse_args(["--model-preset", "qwen3-tiny", "--num-rollout", "2", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2",
+                           "--rollout-max-response-len", "8", "--rollout-max-prompt-len", "16", "--rm-type", "parity", "--lr", "1e-3",
+                           "--actor-num-nodes", "1", "--actor-num-gpus-per-node", "1", "--rollout-engine-urls", f"http://127.0.0.1:{port}",
+                           "--micro-batch-size", "4"])
+        loop = RLLoop(args)
+        assert loop.engine is None and loop.weight_updater is not None
+        hist = loop.run()
+        assert len(hist) == 2 and all(m["train/train_rollout_logprob_abs_diff"] < 1e-5 for m in hist)
+        assert h.get("/get_weight_version")["weight_version"] == loop.actor.store.version
+        want = loop.actor.store.checksum()
+        got = h.post("/weights_checker", {"action": "checksum"})["checksum"]
+        assert all(abs(got[g] - want[g]) <= 1e-3 * max(1.0, abs(want[g])) for g in want)
+        loop.weight_updater.disconnect()
+    finally:
+        srv.terminate()
+        srv.join(10)
