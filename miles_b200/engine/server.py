@@ -172,3 +172,52 @@ def serve(engine: Engine, host: str = "127.0.0.1", port: int = 30000, tokenizer=
     import uvicorn
 
     uvicorn.run(build_app(engine, tokenizer, model_path), host=host, port=port, log_level="warning")
+
+
+def main(argv=None) -> None:
+    """``python -m miles_b200.engine.server --model-preset qwen3-4B --port 30000``: one engine process on this GPU
+    (or on the CPU with the PyTorch model), ready to be driven over HTTP and to join a trainer's weight-update group."""
+    import argparse
+
+    import torch
+
+    from ..models import ParamStore, build_model, get_config
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--model-preset", default=None)
+    ap.add_argument("--hf-checkpoint", default=None)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=30000)
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--max-running-requests", type=int, default=64)
+    ap.add_argument("--page-size", type=int, default=64)
+    ap.add_argument("--context-length", type=int, default=9224)
+    ap.add_argument("--mem-fraction-static", type=float, default=0.85)
+    ap.add_argument("--quantization", default="none", choices=["none", "mxfp8", "nvfp4"])
+    ap.add_argument("--seed", type=int, default=1234)
+    ns = ap.parse_args(argv)
+    cfg = get_config(ns.model_preset or ns.hf_checkpoint)
+    on_gpu = ns.device.startswith("cuda")
+    dtype = torch.bfloat16 if on_gpu else torch.float32
+    store = ParamStore(cfg, ns.device, dtype, seed=ns.seed)
+    tokenizer = None
+    if ns.hf_checkpoint:
+        from ..checkpoint import load_hf
+        from ..utils.processing_utils import load_tokenizer
+
+        load_hf(cfg, store, ns.hf_checkpoint)
+        tokenizer = load_tokenizer(ns.hf_checkpoint)
+    model = build_model(cfg, store, "b200" if (on_gpu and cfg.head_dim == 128) else "torch")
+    if ns.quantization != "none" and hasattr(model, "enable_block_scaled"):
+        model.enable_block_scaled(ns.quantization)
+    kv_bytes = None
+    if on_gpu:
+        free, total = torch.cuda.mem_get_info()
+        kv_bytes = max(int(free - (1.0 - ns.mem_fraction_static) * total), 1 << 28)
+    engine = Engine(model, max_running=ns.max_running_requests, page_size=ns.page_size, max_seq_len=ns.context_length,
+                    kv_mem_bytes=kv_bytes, use_cuda_graph=on_gpu, eos_token_id=getattr(tokenizer, "eos_token_id", None))
+    serve(engine, ns.host, ns.port, tokenizer, ns.hf_checkpoint or ns.model_preset or "")
+
+
+if __name__ == "__main__":
+    main()

@@ -211,3 +211,33 @@ def test_disaggregated_loop_generates_remotely_and_broadcasts_weights():
     finally:
         srv.terminate()
         srv.join(10)
+
+
+def test_engine_server_cli_starts_and_answers():
+    import subprocess
+    import sys
+    import time
+
+    from miles_b200.weight_sync.broadcast import HttpEngineHandle
+
+    port = _free_port()
+    p = subprocess.Popen([sys.executable, "-m", "miles_b200.engine.server", "--model-preset", "qwen3-tiny", "--device", "cpu", "--port", str(port),
+                          "--max-running-requests", "2", "--page-size", "8", "--context-length", "64"],
+                         env=dict(__import__("os").environ, OMP_NUM_THREADS="2"))
+    try:
+        h = HttpEngineHandle(f"http://127.0.0.1:{port}", timeout_s=30)
+        ok = False
+        for _ in range(300):
+            try:
+                ok = h.get("/health")["status"] == "ok"
+                break
+            except Exception:
+                assert p.poll() is None, "the server process exited"
+                time.sleep(0.2)
+        assert ok
+        out = h.post("/generate", {"input_ids": [5, 6, 7], "sampling_params": {"max_new_tokens": 3, "temperature": 0.0}})
+        assert len(out["output_ids"]) == 3
+        assert h.get("/parallelism_config")["tp_size"] == 1
+    finally:
+        p.terminate()
+        p.wait(10)
