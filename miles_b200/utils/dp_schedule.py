@@ -13,7 +13,8 @@ Rules (reference: miles/utils/dp_schedule.py:31-155):
   ``dp_size * microbatch_group`` (``microbatch_group`` > 1 under interleaved pipeline stages);
   fixed batching cuts chunks of ``micro_batch_size`` samples and requires that multiple;
 * micro-batches go to ranks round-robin, or by Karmarkar-Karp on their token counts (``balance``) with the same
-  number of micro-batches per rank.
+  number of micro-batches per rank; with ``workload_fn`` (sequence length -> cost, e.g. forward FLOPs, which grow
+  faster than linearly through attention) packing and distribution balance that cost instead of tokens.
 """
 from __future__ import annotations
 
@@ -56,7 +57,8 @@ def _split_to(bins: list, target: int, lengths: Sequence[int]) -> None:
 
 def build_dp_schedule(total_lengths: Sequence[int], rollout_ids: Sequence[int], *, dp_size: int, global_batch_size: int,
                       max_tokens_per_gpu: Optional[int] = None, micro_batch_size: Optional[int] = None, cp_size: int = 1,
-                      microbatch_group: int = 1, balance: bool = False, allow_partial_step: bool = False) -> DpSchedule:
+                      microbatch_group: int = 1, balance: bool = False, allow_partial_step: bool = False,
+                      workload_fn=None) -> DpSchedule:
     dynamic = max_tokens_per_gpu is not None
     if not dynamic and micro_batch_size is None:
         raise ValueError("either max_tokens_per_gpu (dynamic batching) or micro_batch_size is required")
@@ -82,7 +84,17 @@ def build_dp_schedule(total_lengths: Sequence[int], rollout_ids: Sequence[int], 
         lens = [total_lengths[i] for i in samples]
         if len(samples) < dp_size:
             raise ValueError(f"a step of {n_roll} rollouts has {len(samples)} samples, fewer than the {dp_size} ranks")
-        if dynamic:
+        cost = [float(workload_fn(n)) for n in lens] if workload_fn is not None else None
+        if dynamic and cost is not None:
+            # cost-balanced packing: as many micro-batches as the token budget asks for, equalised by cost
+            n_bins = max(1, -(-sum(lens) // (max_tokens_per_gpu * cp_size)))
+            bins = [[i] for i in range(len(lens))] if n_bins >= len(lens) else karmarkar_karp(cost, n_bins, equal_size=False)
+            bins = [b for b in bins if b]
+            target = max((len(bins) + align - 1) // align * align, align)
+            _split_to(bins, target, lens)
+            if len(bins) != target:
+                raise ValueError(f"{len(samples)} samples cannot fill {target} micro-batches (multiple of {align})")
+        elif dynamic:
             bins = first_fit_pack(lens, max_tokens_per_gpu * cp_size, decreasing=True)
             target = max((len(bins) + align - 1) // align * align, align)
             _split_to(bins, target, lens)
@@ -93,8 +105,9 @@ def build_dp_schedule(total_lengths: Sequence[int], rollout_ids: Sequence[int], 
             if len(bins) % align:
                 raise ValueError(f"{len(bins)} micro-batches of {micro_batch_size} samples are not a multiple of {align}")
         out.num_microbatches.append(len(bins) // dp_size)
-        if balance:
-            owner = karmarkar_karp([sum(lens[i] for i in b) for b in bins], dp_size, equal_size=True)
+        if balance or cost is not None:
+            w = cost if cost is not None else lens
+            owner = karmarkar_karp([sum(w[i] for i in b) for b in bins], dp_size, equal_size=True)
         else:
             owner = [list(range(r, len(bins), dp_size)) for r in range(dp_size)]
         for rank, ids in enumerate(owner):

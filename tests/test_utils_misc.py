@@ -263,3 +263,20 @@ def test_launch_command_and_processing_helpers(capsys):
     img.save(buf, format="PNG")
     assert decode_image(buf.getvalue()).size == (4, 3)
     assert decode_image(base64.b64encode(buf.getvalue()).decode()).size == (4, 3)
+
+
+def test_dp_schedule_balances_by_workload():
+    import random
+
+    from miles_b200.utils.dp_schedule import build_dp_schedule
+
+    random.seed(1)
+    lens = [random.choice([64, 128, 256, 2048, 4096]) for _ in range(32)]
+    cost = lambda n: n * 1000 + n * n  # attention makes long sequences disproportionately expensive
+    s = build_dp_schedule(lens, list(range(32)), dp_size=4, global_batch_size=32, max_tokens_per_gpu=8192, workload_fn=cost)
+    assert sorted(i for p in s.partitions for i in p) == list(range(32))
+    per_rank = [sum(cost(lens[i]) for i in p) for p in s.partitions]
+    s0 = build_dp_schedule(lens, list(range(32)), dp_size=4, global_batch_size=32, max_tokens_per_gpu=8192)
+    per_rank0 = [sum(cost(lens[i]) for i in p) for p in s0.partitions]
+    assert max(per_rank) / min(per_rank) <= max(per_rank0) / min(per_rank0) + 1e-9
+    assert all(len(m) == s.num_microbatches[0] for m in s.micro_batches)
