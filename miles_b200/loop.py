@@ -186,10 +186,12 @@ class RLLoop:
 
         self.client = RemoteEngineClient(urls, self.tokenizer)
         self.rollout_store = None
-        if self.ps.rank == 0:
-            handles = [HttpEngineHandle(u) for u in urls]
+        sender = self.ps.rank == 0
+        if sender or self.actor.store.ep_size > 1:
+            handles = [HttpEngineHandle(u) for u in urls] if sender else []
             self.weight_updater = BroadcastWeightUpdater(
-                self.actor, handles, buffer_bytes=int(getattr(self.args, "update_weight_buffer_size", None) or (512 << 20)))
+                self.actor, handles, buffer_bytes=int(getattr(self.args, "update_weight_buffer_size", None) or (512 << 20)),
+                is_sender=sender)
 
     def _replica_bytes(self) -> int:
         cfg = self.actor.cfg

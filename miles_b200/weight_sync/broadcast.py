@@ -119,7 +119,10 @@ class BroadcastWeightUpdater:
 
     def __init__(self, actor, engines: Sequence, group_name: str = "miles-weights", buffer_bytes: int = 512 << 20,
                  backend: Optional[str] = None, master_address: str = "127.0.0.1", master_port: Optional[int] = None,
-                 engine_world_sizes: Optional[Sequence[int]] = None):
+                 engine_world_sizes: Optional[Sequence[int]] = None, is_sender: bool = True):
+        # with an expert-parallel trainer every rank builds an updater (the expert gather is a collective of the
+        # trainer's own group) but only the sender talks to the engines
+        self.is_sender = is_sender
         self.actor, self.engines, self.group_name = actor, list(engines), group_name
         self.buffer_bytes = buffer_bytes
         self.backend = backend or ("nccl" if actor.on_gpu else "gloo")
@@ -168,6 +171,9 @@ class BroadcastWeightUpdater:
     def update(self) -> dict:
         import time
 
+        if not self.is_sender:
+            self._named()  # take part in the gathers, send nothing
+            return {}
         if not self.connected:
             self.connect()
         t0 = time.perf_counter()
