@@ -115,7 +115,9 @@ class RLLoop:
         pipelined = self.ps.pp.size > 1
         replicate = not pipelined and self.actor.ep_dispatcher is not None and self._replicate_experts_fits(kv_bytes)
         if replicate:
-            kv_bytes = max(min(kv_bytes, room - self._replica_bytes()), per_tok * page * 4)
+            # the worst case (every sequence at the full context length) almost never happens and the engine retracts
+            # requests when the pool runs dry: with the replica resident, size the pool for 65 % of that worst case
+            kv_bytes = max(min(kv_bytes, room - self._replica_bytes(), int(0.65 * want)), per_tok * page * 4)
         if pipelined:
             assert self.actor.ep_dispatcher is None and self.ps.tp.size == 1, \
                 "the colocated engine of a pipelined trainer is built for tp = ep = 1"
