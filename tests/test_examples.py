@@ -1,0 +1,23 @@
+"""Every flag that a launch recipe passes exists in the parser (recipes cannot silently rot)."""
+import glob
+import os
+import re
+
+from miles_b200.utils.arguments import build_parser
+
+LAUNCHER_FLAGS = {"--nnodes", "--nproc-per-node", "--master-addr", "--master-port"}
+SERVER_FLAGS = {"--port", "--device", "--max-running-requests", "--page-size", "--context-length", "--host", "--quantization",
+                "--mem-fraction-static"}
+
+
+def test_example_flags_are_known():
+    known = set()
+    for a in build_parser()._actions:
+        known.update(a.option_strings)
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
+    files = sorted(glob.glob(os.path.join(root, "*.sh")))
+    assert len(files) >= 8
+    for f in files:
+        flags = set(re.findall(r"(?<![\w-])(--[a-z][a-z0-9-]+)", open(f).read()))
+        unknown = sorted(x for x in flags - known - LAUNCHER_FLAGS - SERVER_FLAGS if not x.startswith("--sglang-"))
+        assert not unknown, (os.path.basename(f), unknown)
