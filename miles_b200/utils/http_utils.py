@@ -18,12 +18,22 @@ def configure(max_connections: int = 1024, timeout: float = 600.0) -> None:
     _client = None
 
 
+_client_loop = None
+
+
 def client():
-    global _client
-    if _client is None:
+    """The shared client of the running event loop (connections belong to a loop: a client made under an earlier
+    ``asyncio.run`` is replaced, not reused)."""
+    global _client, _client_loop
+    try:
+        loop = asyncio.get_running_loop()
+    except RuntimeError:
+        loop = None
+    if _client is None or _client_loop is not loop:
         import httpx
 
         _client = httpx.AsyncClient(timeout=_limits["timeout"], limits=httpx.Limits(max_connections=_limits["max_connections"]))
+        _client_loop = loop
     return _client
 
 

@@ -241,3 +241,41 @@ def test_engine_server_cli_starts_and_answers():
     finally:
         p.terminate()
         p.wait(10)
+
+
+def test_fleet_brings_up_a_deployment_and_restarts_an_engine():
+    import asyncio
+    from types import SimpleNamespace as NS
+
+    from miles_b200.engine.deployment import Deployment
+    from miles_b200.engine.fleet import Fleet
+    from miles_b200.engine.remote import RemoteEngineClient
+
+    dep = Deployment.from_dict({"sglang": [
+        {"name": "actor", "overrides": {"max_running_requests": 2, "page_size": 8, "context_length": 64},
+         "server_groups": [{"worker_type": "regular", "num_gpus": 2, "num_gpus_per_engine": 1}]}]}).resolve(
+        NS(hf_checkpoint=None, rollout_num_gpus_per_engine=1))
+    fleet = Fleet(dep, model_preset="qwen3-tiny", base_port=_free_port(), device="cpu", env={"OMP_NUM_THREADS": "2"})
+    # the two engines get consecutive ports: make sure the second is free too
+    fleet.start(wait_s=120)
+    try:
+        urls = fleet.urls("actor")
+        assert len(urls) == 2 and fleet.updatable_urls() == urls
+        client = RemoteEngineClient(urls, max_retries=1)
+
+        async def run():
+            outs = await asyncio.gather(*[client.generate({"input_ids": [1, 2, 3], "sampling_params": {"max_new_tokens": 2, "temperature": 0.0}})
+                                          for _ in range(4)])
+            return outs, await client.health()
+
+        outs, health = asyncio.run(run())
+        assert all(len(o["output_ids"]) == 2 for o in outs) and all(health.values())
+        pid = fleet.engines[0].proc.pid
+        fleet.engines[0].proc.kill()
+        fleet.engines[0].proc.wait(10)
+        assert not fleet.engines[0].alive()
+        fleet.restart(0, wait_s=120)
+        assert fleet.engines[0].alive() and fleet.engines[0].proc.pid != pid
+        assert all(asyncio.run(RemoteEngineClient(urls, max_retries=1).health()).values())
+    finally:
+        fleet.stop()
