@@ -28,6 +28,15 @@ class EngineProcess:
     def url(self) -> str:
         return f"http://127.0.0.1:{self.port}"
 
+    def health_generate(self, timeout: float = 30.0) -> bool:
+        """One real token through the engine (what the health monitor probes)."""
+        import json
+
+        if not self.alive():
+            return False
+        with urllib.request.urlopen(self.url + "/health_generate", timeout=timeout) as r:
+            return json.loads(r.read().decode()).get("status") in ("ok", "paused")
+
     def alive(self) -> bool:
         return self.proc.poll() is None
 
@@ -101,6 +110,27 @@ class Fleet:
         self.engines[index] = self._spawn(old.placement, old.port)
         self.wait_healthy(wait_s)
         return self.engines[index]
+
+    def monitor(self, interval: float = 10.0, timeout: float = 30.0, recover: bool = True, on_recovered=None):
+        """A `ft.health.HealthMonitor` over the fleet: an engine that fails its probe is killed and, with ``recover``,
+        replaced by a fresh process (``on_recovered(index, url)`` lets the caller reconnect it to the weight-update
+        group and push the current weights)."""
+        from ..ft.health import HealthMonitor
+
+        mon: list = []
+
+        def kill(i: int) -> None:
+            e = self.engines[i]
+            if e.alive():
+                e.proc.kill()
+            if recover:
+                new = self.restart(i)
+                mon[0].mark_recovered(i, new)
+                if on_recovered is not None:
+                    on_recovered(i, new.url)
+
+        mon.append(HealthMonitor(self.engines, kill, interval=interval, timeout=timeout))
+        return mon[0]
 
     def stop(self) -> None:
         for e in self.engines:

@@ -277,5 +277,13 @@ def test_fleet_brings_up_a_deployment_and_restarts_an_engine():
         fleet.restart(0, wait_s=120)
         assert fleet.engines[0].alive() and fleet.engines[0].proc.pid != pid
         assert all(asyncio.run(RemoteEngineClient(urls, max_retries=1).health()).values())
+        # the health monitor finds a dead engine, replaces it and reports the recovery
+        recovered = []
+        mon = fleet.monitor(recover=True, on_recovered=lambda i, u: recovered.append((i, u)))
+        assert mon.check_all() == []
+        fleet.engines[1].proc.kill()
+        fleet.engines[1].proc.wait(10)
+        assert mon.check_all() == [1] and recovered == [(1, urls[1])]
+        assert fleet.engines[1].alive() and mon.check_all() == []
     finally:
         fleet.stop()
