@@ -123,6 +123,7 @@ class BroadcastWeightUpdater:
         # with an expert-parallel trainer every rank builds an updater (the expert gather is a collective of the
         # trainer's own group) but only the sender talks to the engines
         self.is_sender = is_sender
+        self._base_name, self._generation = group_name, 0
         self.actor, self.engines, self.group_name = actor, list(engines), group_name
         self.buffer_bytes = buffer_bytes
         self.backend = backend or ("nccl" if actor.on_gpu else "gloo")
@@ -149,11 +150,26 @@ class BroadcastWeightUpdater:
             h.result()
         self.connected = True
 
-    def disconnect(self) -> None:
-        for e in self.engines:
-            e.post("/destroy_weights_update_group", {"group_name": self.group_name})
+    def disconnect(self, skip: Sequence[int] = ()) -> None:
+        for i, e in enumerate(self.engines):
+            if i in skip:
+                continue
+            try:
+                e.post("/destroy_weights_update_group", {"group_name": self.group_name})
+            except Exception:
+                pass  # an engine that is gone has no group left to destroy
         destroy_update_group(self.group_name)
         self.connected = False
+
+    def replace_engine(self, index: int, engine) -> None:
+        """A recovered engine took the place of a dead one: the old group (which still counts the dead process) is
+        dropped and the next update builds a new one, under a new name and port, with the current engines."""
+        if self.connected:
+            self.disconnect(skip=(index,))
+        self.engines[index] = engine
+        self._generation += 1
+        self.group_name = f"{self._base_name}-g{self._generation}"
+        self.master_port = None
 
     def _named(self):
         store = self.actor.store

@@ -277,13 +277,36 @@ def test_fleet_brings_up_a_deployment_and_restarts_an_engine():
         fleet.restart(0, wait_s=120)
         assert fleet.engines[0].alive() and fleet.engines[0].proc.pid != pid
         assert all(asyncio.run(RemoteEngineClient(urls, max_retries=1).health()).values())
-        # the health monitor finds a dead engine, replaces it and reports the recovery
+        # weights go to both engines; then the health monitor finds a dead engine, replaces it, the updater reconnects
+        # and the fresh engine receives the current weights like the survivor
+        from miles_b200.weight_sync.broadcast import BroadcastWeightUpdater, HttpEngineHandle
+
+        src = ParamStore(get_config("qwen3-tiny"), "cpu", torch.float32, seed=1)
+        src.version = 3
+        actor = NS(store=src, on_gpu=False, args=NS(pause_generation_mode="retract"), ps=None)
+        handles = [HttpEngineHandle(u, timeout_s=60) for u in urls]
+        up = BroadcastWeightUpdater(actor, handles, group_name="fleet-w", buffer_bytes=1 << 20, backend="gloo")
+        up.update()
         recovered = []
-        mon = fleet.monitor(recover=True, on_recovered=lambda i, u: recovered.append((i, u)))
+
+        def on_recovered(i, u):
+            recovered.append((i, u))
+            up.replace_engine(i, HttpEngineHandle(u, timeout_s=60))
+
+        mon = fleet.monitor(recover=True, on_recovered=on_recovered)
         assert mon.check_all() == []
         fleet.engines[1].proc.kill()
         fleet.engines[1].proc.wait(10)
         assert mon.check_all() == [1] and recovered == [(1, urls[1])]
         assert fleet.engines[1].alive() and mon.check_all() == []
+        src.flat["dense"].mul_(1.01)
+        src.version = 4
+        up.update()
+        want = src.checksum()
+        for hnd in up.engines:
+            got = hnd.post("/weights_checker", {"action": "checksum"})["checksum"]
+            assert all(abs(got[g] - want[g]) <= 1e-3 * max(1.0, abs(want[g])) for g in want)
+            assert hnd.get("/get_weight_version")["weight_version"] == 4
+        up.disconnect()
     finally:
         fleet.stop()
