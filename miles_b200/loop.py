@@ -68,6 +68,9 @@ class RLLoop:
         self.engine: Optional[Engine] = None
         self.client: Optional[EngineClient] = None
         self.weight_updater = None
+        self.fleet = None
+        if getattr(args, "launch_rollout_fleet", False) and not getattr(args, "debug_train_only", False):
+            args.rollout_engine_urls = self._launch_fleet()
         if getattr(args, "rollout_engine_urls", None) and not getattr(args, "debug_train_only", False):
             self._connect_remote_engines([u for u in args.rollout_engine_urls.split(",") if u])
         elif not getattr(args, "debug_train_only", False):
@@ -179,6 +182,29 @@ class RLLoop:
             if self.ps.world_size > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MIN)
             self.actor.opt.promote_offloaded(int(t.item()))
+
+    def _launch_fleet(self) -> str:
+        """Start the rollout engines this job asks for (``--sglang-config`` file, or ``--rollout-num-gpus`` /
+        ``--rollout-num-gpus-per-engine``) on the GPUs after the trainer's, from the first rank; every rank learns the
+        URLs. The engines stop with the job."""
+        import atexit
+
+        a = self.args
+        box = [None]
+        if self.ps.rank == 0:
+            from .engine.deployment import Deployment
+            from .engine.fleet import Fleet
+
+            dep = Deployment.from_yaml(a.sglang_config) if getattr(a, "sglang_config", None) else Deployment.from_args(a)
+            dep.resolve(a)
+            dev = getattr(a, "rollout_fleet_device", None)
+            self.fleet = Fleet(dep, model_preset=getattr(a, "model_preset", None), base_port=a.rollout_fleet_base_port, device=dev,
+                               first_gpu=0 if (dev or "").startswith("cpu") else self.ps.world_size).start()
+            atexit.register(self.fleet.stop)
+            box[0] = ",".join(self.fleet.updatable_urls() or self.fleet.urls())
+        if self.ps.world_size > 1:
+            dist.broadcast_object_list(box, src=0)
+        return box[0]
 
     def _connect_remote_engines(self, urls: list) -> None:
         """Disaggregated mode: the engines run in other processes (`engine/server.py`). Generation goes over HTTP, the

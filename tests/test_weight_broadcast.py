@@ -310,3 +310,23 @@ def test_fleet_brings_up_a_deployment_and_restarts_an_engine():
         up.disconnect()
     finally:
         fleet.stop()
+
+
+def test_loop_launches_its_own_fleet():
+    from miles_b200.loop import RLLoop
+    from miles_b200.utils.arguments import parse_args
+
+    args = parse_args(["--model-preset", "qwen3-tiny", "--num-rollout", "1", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2",
+                       "--rollout-max-response-len", "8", "--rollout-max-prompt-len", "16", "--rm-type", "parity", "--lr", "1e-3",
+                       "--actor-num-nodes", "1", "--actor-num-gpus-per-node", "1", "--micro-batch-size", "4",
+                       "--launch-rollout-fleet", "--rollout-fleet-device", "cpu", "--rollout-fleet-base-port", str(_free_port()),
+                       "--rollout-num-gpus", "1", "--rollout-num-gpus-per-engine", "1"])
+    loop = RLLoop(args)
+    try:
+        assert loop.fleet is not None and len(loop.fleet.engines) == 1 and loop.engine is None
+        hist = loop.run()
+        assert hist[0]["train/train_rollout_logprob_abs_diff"] < 1e-5
+    finally:
+        if loop.weight_updater is not None and loop.weight_updater.connected:
+            loop.weight_updater.disconnect()
+        loop.fleet.stop()
