@@ -9,6 +9,9 @@ Two modes, selected like in the reference (train_async.py:22-129, miles/utils/ar
   weight update uses ``--pause-generation-mode in_place|retract`` so that in-flight requests survive and
   record mixed weight versions; stale groups are filtered by ``--max-weight-staleness``.
 
+With engines in other processes (``--rollout-engine-urls`` / ``--launch-rollout-fleet``) the next rollout is generated
+on a background thread while the current one trains, and is collected before the weights change.
+
 On one process per GPU the producer is advanced cooperatively: the trainer yields to the rollout
 function between micro-batches (``pump``), which interleaves engine iterations with training kernels on
 the same device; samples generated under older weights are corrected by TIS when enabled.
@@ -37,6 +40,31 @@ class AsyncRLLoop(RLLoop):
         args.offload_rollout = False
         super().__init__(args, ps)
         self._prefetched = None
+        self._bg = None  # (thread, result box) of a generation that runs while the trainer trains (remote engines only)
+
+    # ------------------------------------------------------------------ overlap with engines in other processes
+    def _start_background_generation(self, rollout_id: int) -> None:
+        import threading
+
+        box: dict = {}
+
+        def run():
+            try:
+                box["out"] = self._generate_now(rollout_id)
+            except BaseException as e:  # surfaces in the training thread when the result is collected
+                box["err"] = e
+
+        th = threading.Thread(target=run, daemon=True)
+        th.start()
+        self._bg = (th, box)
+
+    def _collect_background_generation(self):
+        th, box = self._bg
+        self._bg = None
+        th.join()
+        if "err" in box:
+            raise box["err"]
+        return box["out"]
 
     def _generate_now(self, rollout_id: int):
         t0 = time.perf_counter()
@@ -63,15 +91,22 @@ class AsyncRLLoop(RLLoop):
         fully = getattr(a, "fully_async", False) and hasattr(self.rollout_fn, "pump")
         if fully:
             self.rollout_fn.pump(0.0)
+        remote = self.engine is None and self.client is not None
+        if remote and rollout_id + 1 < a.num_rollout:
+            # the engines are other processes: the next rollout is generated while this one trains, and is drained
+            # before the weights change (below)
+            self._start_background_generation(rollout_id + 1)
         metrics.update(self.train(rollout_id, samples))
         t2 = time.perf_counter()
         if should_run_periodic_action(rollout_id, a.save_interval, None, a.num_rollout):
             self.actor.save_model(rollout_id)
             self.data_source.save(rollout_id)
+        if self._bg is not None:
+            self._prefetched = self._collect_background_generation()  # in-flight generation ends before the update
         if (rollout_id + 1) % (a.update_weights_interval or 1) == 0:
             metrics.update(self.update_weights())
         # start the next rollout right away (one-step-async prefetch); with fully-async this mostly drains the buffer
-        if rollout_id + 1 < a.num_rollout:
+        if self._prefetched is None and rollout_id + 1 < a.num_rollout:
             self._prefetched = self._generate_now(rollout_id + 1)
         t3 = time.perf_counter()
         metrics.update({"perf/train_wait_time": t1 - t0, "perf/train_time": t2 - t1, "perf/step_time": t3 - t0,

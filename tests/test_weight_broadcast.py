@@ -330,3 +330,28 @@ def test_loop_launches_its_own_fleet():
         if loop.weight_updater is not None and loop.weight_updater.connected:
             loop.weight_updater.disconnect()
         loop.fleet.stop()
+
+
+def test_async_loop_overlaps_generation_with_training_on_remote_engines():
+    from miles_b200.async_loop import AsyncRLLoop
+    from miles_b200.utils.arguments import parse_args
+
+    args = parse_args(["--model-preset", "qwen3-tiny", "--num-rollout", "3", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2",
+                       "--rollout-max-response-len", "8", "--rollout-max-prompt-len", "16", "--rm-type", "parity", "--lr", "1e-3",
+                       "--actor-num-nodes", "1", "--actor-num-gpus-per-node", "1", "--micro-batch-size", "4",
+                       "--launch-rollout-fleet", "--rollout-fleet-device", "cpu", "--rollout-fleet-base-port", str(_free_port()),
+                       "--rollout-num-gpus", "1", "--rollout-num-gpus-per-engine", "1", "--use-tis"])
+    loop = AsyncRLLoop(args)
+    started = []
+    orig = loop._start_background_generation
+    loop._start_background_generation = lambda rid: (started.append(rid), orig(rid))[1]
+    try:
+        hist = loop.run()
+        assert len(hist) == 3 and started == [1, 2]  # rollouts 1 and 2 were generated while 0 and 1 trained
+        # a rollout generated during step i used the weights of before step i: one version behind, never more
+        assert all(m["train/train_rollout_logprob_abs_diff"] < 0.5 for m in hist)
+        assert hist[0]["train/train_rollout_logprob_abs_diff"] < 1e-5
+    finally:
+        if loop.weight_updater is not None and loop.weight_updater.connected:
+            loop.weight_updater.disconnect()
+        loop.fleet.stop()
