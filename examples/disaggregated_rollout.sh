@@ -1,7 +1,9 @@
 #!/usr/bin/env bash
 # Trainer and rollout engines on different GPUs of the box: engines are `miles_b200.engine.server` processes, the
 # trainer generates over HTTP and pushes weights through a process group of its own (NCCL between the GPUs).
-# GPUs 0..TRAIN-1 train (data parallel), GPUs TRAIN..7 serve.
+# GPUs 0..TRAIN-1 train (data parallel), GPUs TRAIN..7 serve. (`--launch-rollout-fleet --rollout-num-gpus N` makes the
+# trainer start and stop the engine processes itself; this script starts them by hand to show the pieces.)
+# With train_async.py the next rollout is generated while the current one trains.
 set -euo pipefail
 TRAIN=${TRAIN:-4}
 MODEL=${MODEL:-qwen3-4B}
