@@ -93,6 +93,29 @@ class Fleet:
                     raise TimeoutError(f"{len(pending)} engines did not come up within {wait_s:.0f} s")
                 time.sleep(0.3)
 
+    def start_router(self, port: int, model: Optional[str] = None, policy: str = "least_inflight", wait_s: float = 60.0) -> str:
+        """One router process in front of the engines of ``model`` (all engines if None); returns its URL. Generation
+        requests go through it, weight updates still address the engines themselves."""
+        cmd = [sys.executable, "-m", "miles_b200.router.router", "--port", str(port), "--policy", policy]
+        for u in self.urls(model):
+            cmd += ["--worker", u]
+        proc = subprocess.Popen(cmd, env=dict(os.environ, **self.env))
+        self.__dict__.setdefault("routers", []).append(proc)
+        url = f"http://127.0.0.1:{port}"
+        deadline = time.time() + wait_s
+        while True:
+            if proc.poll() is not None:
+                raise RuntimeError(f"the router exited with code {proc.returncode}")
+            try:
+                with urllib.request.urlopen(url + "/list_workers", timeout=2.0) as r:
+                    if r.status == 200:
+                        return url
+            except Exception:
+                pass
+            if time.time() > deadline:
+                raise TimeoutError("the router did not come up")
+            time.sleep(0.2)
+
     def urls(self, model: Optional[str] = None, worker_type: Optional[str] = None) -> list:
         return [e.url for e in self.engines if (model is None or e.placement.model == model)
                 and (worker_type is None or e.placement.worker_type == worker_type)]
@@ -134,6 +157,9 @@ class Fleet:
         return mon[0]
 
     def stop(self) -> None:
+        for r in self.__dict__.get("routers", []):
+            if r.poll() is None:
+                r.terminate()
         for e in self.engines:
             if e.alive():
                 e.proc.terminate()

@@ -144,3 +144,27 @@ def build_router_app(router: MilesRouter):
         return Response(content=content, status_code=status, media_type=ctype)
 
     return app
+
+
+def main(argv=None) -> None:
+    """``python -m miles_b200.router.router --port 3000 --worker http://127.0.0.1:30000 --worker ...``"""
+    import argparse
+
+    import uvicorn
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=3000)
+    ap.add_argument("--worker", action="append", default=[])
+    ap.add_argument("--policy", default="least_inflight", choices=["least_inflight", "round_robin", "consistent_hashing"])
+    ap.add_argument("--failure-threshold", type=int, default=3)
+    ap.add_argument("--health-interval", type=float, default=5.0)
+    ns = ap.parse_args(argv)
+    router = MilesRouter(failure_threshold=ns.failure_threshold, health_interval=ns.health_interval, policy=ns.policy)
+    for w in ns.worker:
+        router.add_worker(w)
+    uvicorn.run(build_router_app(router), host=ns.host, port=ns.port, log_level="warning")
+
+
+if __name__ == "__main__":
+    main()

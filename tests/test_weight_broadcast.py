@@ -270,6 +270,20 @@ def test_fleet_brings_up_a_deployment_and_restarts_an_engine():
 
         outs, health = asyncio.run(run())
         assert all(len(o["output_ids"]) == 2 for o in outs) and all(health.values())
+        # the same requests through a router process in front of both engines
+        rurl = fleet.start_router(_free_port(), "actor")
+        via = RemoteEngineClient([rurl], max_retries=1)
+
+        async def routed():
+            return await asyncio.gather(*[via.generate({"input_ids": [4, 5], "sampling_params": {"max_new_tokens": 2, "temperature": 0.0}})
+                                          for _ in range(4)])
+
+        assert all(len(o["output_ids"]) == 2 for o in asyncio.run(routed()))
+        import json
+        import urllib.request
+
+        with urllib.request.urlopen(rurl + "/list_workers", timeout=5) as r:
+            assert sorted(json.loads(r.read().decode())["urls"]) == sorted(urls)
         pid = fleet.engines[0].proc.pid
         fleet.engines[0].proc.kill()
         fleet.engines[0].proc.wait(10)
