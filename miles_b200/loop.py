@@ -202,8 +202,13 @@ class RLLoop:
                                first_gpu=0 if (dev or "").startswith("cpu") else self.ps.world_size).start()
             atexit.register(self.fleet.stop)
             box[0] = ",".join(self.fleet.updatable_urls() or self.fleet.urls())
+            if getattr(a, "use_miles_router", False):
+                # generation goes through one router process; weight updates still address the engines themselves
+                box.append(self.fleet.start_router(a.rollout_fleet_base_port + len(self.fleet.engines) + 1))
         if self.ps.world_size > 1:
+            box = box + [None] * (2 - len(box))
             dist.broadcast_object_list(box, src=0)
+        self.router_url = box[1] if len(box) > 1 else None
         return box[0]
 
     def _connect_remote_engines(self, urls: list) -> None:
@@ -212,7 +217,8 @@ class RLLoop:
         from .engine.remote import RemoteEngineClient
         from .weight_sync.broadcast import BroadcastWeightUpdater, HttpEngineHandle
 
-        self.client = RemoteEngineClient(urls, self.tokenizer)
+        router = getattr(self, "router_url", None) or getattr(self.args, "rollout_router_url", None)
+        self.client = RemoteEngineClient([router] if router else urls, self.tokenizer)
         self.rollout_store = None
         sender = self.ps.rank == 0
         if sender or self.actor.store.ep_size > 1:

@@ -334,10 +334,11 @@ def test_loop_launches_its_own_fleet():
                        "--rollout-max-response-len", "8", "--rollout-max-prompt-len", "16", "--rm-type", "parity", "--lr", "1e-3",
                        "--actor-num-nodes", "1", "--actor-num-gpus-per-node", "1", "--micro-batch-size", "4",
                        "--launch-rollout-fleet", "--rollout-fleet-device", "cpu", "--rollout-fleet-base-port", str(_free_port()),
-                       "--rollout-num-gpus", "1", "--rollout-num-gpus-per-engine", "1"])
+                       "--rollout-num-gpus", "1", "--rollout-num-gpus-per-engine", "1", "--use-miles-router"])
     loop = RLLoop(args)
     try:
         assert loop.fleet is not None and len(loop.fleet.engines) == 1 and loop.engine is None
+        assert loop.router_url is not None and loop.client.urls == [loop.router_url]  # requests go through the router
         hist = loop.run()
         assert hist[0]["train/train_rollout_logprob_abs_diff"] < 1e-5
     finally:
