@@ -43,7 +43,9 @@ class EngineProcess:
 
 class Fleet:
     def __init__(self, deployment: Deployment, model_preset: Optional[str] = None, base_port: int = 30000,
-                 device: Optional[str] = None, extra_args: Optional[list] = None, env: Optional[dict] = None, first_gpu: int = 0):
+                 device: Optional[str] = None, extra_args: Optional[list] = None, env: Optional[dict] = None, first_gpu: int = 0,
+                 ports: Optional[list] = None):
+        self.ports = list(ports) if ports else None  # explicit port per engine (default: base_port, base_port + 1, ...)
         self.first_gpu = first_gpu  # GPUs below this index belong to the trainer
         self.deployment, self.model_preset, self.base_port = deployment, model_preset, base_port
         self.device, self.extra_args, self.env = device, list(extra_args or []), dict(env or {})
@@ -71,7 +73,7 @@ class Fleet:
 
     def start(self, wait_s: float = 300.0) -> "Fleet":
         for i, pl in enumerate(self.deployment.plan(self.first_gpu)):
-            self.engines.append(self._spawn(pl, self.base_port + i))
+            self.engines.append(self._spawn(pl, self.ports[i] if self.ports else self.base_port + i))
         self.wait_healthy(wait_s)
         return self
 

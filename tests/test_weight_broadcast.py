@@ -255,8 +255,7 @@ def test_fleet_brings_up_a_deployment_and_restarts_an_engine():
         {"name": "actor", "overrides": {"max_running_requests": 2, "page_size": 8, "context_length": 64},
          "server_groups": [{"worker_type": "regular", "num_gpus": 2, "num_gpus_per_engine": 1}]}]}).resolve(
         NS(hf_checkpoint=None, rollout_num_gpus_per_engine=1))
-    fleet = Fleet(dep, model_preset="qwen3-tiny", base_port=_free_port(), device="cpu", env={"OMP_NUM_THREADS": "2"})
-    # the two engines get consecutive ports: make sure the second is free too
+    fleet = Fleet(dep, model_preset="qwen3-tiny", ports=[_free_port(), _free_port()], device="cpu", env={"OMP_NUM_THREADS": "2"})
     fleet.start(wait_s=120)
     try:
         urls = fleet.urls("actor")
