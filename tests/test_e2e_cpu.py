@@ -175,3 +175,26 @@ def _pp_cp_worker(rank: int, world: int, port: int, out_dir: str):
 def test_gloo_pipeline_and_context_parallel_together(tmp_path):
     port = 33000 + (os.getpid() * 17) % 2000
     mp.spawn(_pp_cp_worker, args=(4, port, str(tmp_path)), nprocs=4, join=True)
+
+
+def test_ci_checks_run_inside_the_loop(tmp_path):
+    """--ci-test: on-policy gate after every step, weight hashes written with the checkpoint and verified on resume."""
+    from miles_b200.loop import RLLoop
+
+    common = BASE + ["--actor-num-gpus-per-node", "1", "--ci-test", "--ci-save-model-hash", "--ci-check-model-hash",
+                     "--save", str(tmp_path / "ckpt"), "--save-interval", "1"]
+    loop = RLLoop(parse_args(common + ["--num-rollout", "1"]))
+    loop.run()
+    hashes = list((tmp_path / "ckpt").rglob("model_hash_*.json"))
+    assert len(hashes) == 1
+    loop2 = RLLoop(parse_args(common + ["--num-rollout", "2", "--load", str(tmp_path / "ckpt")]))  # verifies the hashes while loading
+    assert loop2.start_rollout_id == 1
+    # a tampered checkpoint is caught
+    import json
+
+    h = json.loads(hashes[0].read_text())
+    k = sorted(h)[0]
+    h[k] = "0" * 64
+    hashes[0].write_text(json.dumps(h))
+    with pytest.raises(AssertionError):
+        RLLoop(parse_args(common + ["--num-rollout", "2", "--load", str(tmp_path / "ckpt")]))
