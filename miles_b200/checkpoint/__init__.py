@@ -48,7 +48,8 @@ def save_checkpoint(actor, base: str, iteration: int) -> str:
     state = {
         "flat": {g: t.detach().cpu() for g, t in actor.store.flat.items()},
         "version": actor.store.version,
-        "global_step": actor.global_step,
+        "global_step": actor.global_step,  # optimizer steps taken (drives the LR schedule and metrics)
+        "rollout_id": iteration,           # the rollout this checkpoint was written after (the directory name)
         "rng": {"cpu": torch.get_rng_state(), "cuda": torch.cuda.get_rng_state() if actor.on_gpu else None},
         "ep": (actor.store.ep_size, actor.store.ep_rank),
     }
@@ -75,7 +76,10 @@ def save_checkpoint(actor, base: str, iteration: int) -> str:
 
 
 def load_checkpoint(actor, path: str, step: Optional[int] = None) -> Optional[int]:
-    """Load a native checkpoint (returns its iteration) or an HF directory (returns None)."""
+    """Load a native checkpoint or an HF directory. A native checkpoint returns the rollout id it was written
+    after (the ``iter_`` number; training resumes at the next one) and restores ``actor.global_step``, the count of
+    optimizer steps, which differs from the rollout id whenever a rollout takes several optimizer steps. An HF
+    directory, or ``--finetune``, returns None (start from rollout 0)."""
     if is_native_checkpoint(path):
         it = step if step is not None else latest_iteration(path)
         d = iter_dir(path, it) if it is not None else path
@@ -99,7 +103,9 @@ def load_checkpoint(actor, path: str, step: Optional[int] = None) -> Optional[in
             check_model_hashes(actor.args, actor.store, actor.ps, it)
         if getattr(actor.args, "finetune", False):
             return None
-        return state.get("global_step", it)
+        actor.global_step = int(state.get("global_step", 0) or 0)
+        rid = state.get("rollout_id", it)
+        return int(rid) if rid is not None else None
     if os.path.isdir(path):
         load_hf(actor.cfg, actor.store, path)
         if actor.opt is not None:

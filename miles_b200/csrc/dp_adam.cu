@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256) dp_adam_push_kernel(DpPeers peers, int me
     uint4 packed = reinterpret_cast<const uint4*>(own)[lo8 + i];
     if (!skip) {
       const bf16* pw = reinterpret_cast<const bf16*>(&packed);
-      bf16 nw[8];
+      __align__(16) bf16 nw[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const long long e = i * 8 + j;

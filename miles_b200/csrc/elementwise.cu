@@ -370,30 +370,147 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __r
 }
 
 // ------------------------------------------------------------------ fused Adam(W)
-// One flat buffer per call. Parameter is bf16 with an optional fp32 master copy; the gradient is bf16
-// or fp32; moments are fp32 or bf16. `found_inf`/`grad_scale` are read from device memory so that the
-// clip coefficient computed by a previous kernel never travels through the host.
+// One flat buffer per call. The parameter is bf16; its fp32 master copy is kept in one of two forms:
+//   * `master` (fp32 array), or
+//   * `lo` (16-bit array): the master is split over the bf16 weight itself and a signed 16-bit remainder,
+//         master_bits = (weight_bits << 16) + lo,     weight_bits = (master_bits + 0x8000) >> 16,
+//     so the weight the GEMMs read is the master rounded to nearest (ties away from zero) and the pair
+//     reconstructs every fp32 bit. An update far below half a bf16 ulp therefore accumulates in `lo`
+//     instead of being rounded away; memory per parameter is 4 bytes instead of 6.
+// With neither, the update is applied to the bf16 value itself (only sensible for large learning rates).
+// The gradient is bf16 or fp32; moments are fp32 or bf16. `skip_flag` / `grad_scale` are read from device
+// memory so that the clip coefficient computed by a previous kernel never travels through the host.
+// Eight elements per thread, 128-bit loads and stores; the host launcher handles a ragged tail.
+template <typename T>
+__device__ __forceinline__ void adam_load8(const T* p, float (&o)[8]);
+template <>
+__device__ __forceinline__ void adam_load8<bf16>(const bf16* p, float (&o)[8]) {
+  load8(p, o);
+}
+template <>
+__device__ __forceinline__ void adam_load8<float>(const float* p, float (&o)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
+  o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <typename T>
+__device__ __forceinline__ void adam_store8(T* p, const float (&o)[8]);
+template <>
+__device__ __forceinline__ void adam_store8<bf16>(bf16* p, const float (&o)[8]) {
+  store8(p, o);
+}
+template <>
+__device__ __forceinline__ void adam_store8<float>(float* p, const float (&o)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(o[4], o[5], o[6], o[7]);
+}
+
+struct AdamScalars {
+  float lr, b1, b2, eps, wd, bc1, bc2;
+};
+
+__device__ __forceinline__ float adam_update(float w, float grad, float& mi, float& vi, const AdamScalars& a) {
+  mi = a.b1 * mi + (1.f - a.b1) * grad;
+  vi = a.b2 * vi + (1.f - a.b2) * grad * grad;
+  const float upd = (mi / a.bc1) / (sqrtf(vi / a.bc2) + a.eps);
+  return w - a.lr * (upd + a.wd * w);
+}
+
+__device__ __forceinline__ float split_join(unsigned short hi, short lo) {
+  return __uint_as_float((static_cast<unsigned>(hi) << 16) + static_cast<unsigned>(static_cast<int>(lo)));
+}
+__device__ __forceinline__ void split_cut(float w, unsigned short& hi, short& lo) {
+  const unsigned bits = __float_as_uint(w);
+  const unsigned h = (bits + 0x8000u) >> 16;
+  hi = static_cast<unsigned short>(h);
+  lo = static_cast<short>(static_cast<int>(bits - (h << 16)));
+}
+
 template <typename GT, typename MT>
-__global__ void adam_kernel(bf16* __restrict__ p, float* __restrict__ master, const GT* __restrict__ g,
-                            MT* __restrict__ m, MT* __restrict__ v, long long n, float lr, float b1, float b2,
-                            float eps, float wd, float bc1, float bc2, const float* __restrict__ grad_scale,
-                            const float* __restrict__ skip_flag) {
+__global__ void adam_kernel(bf16* __restrict__ p, float* __restrict__ master, short* __restrict__ lo,
+                            const GT* __restrict__ g, MT* __restrict__ m, MT* __restrict__ v, long long n,
+                            AdamScalars a, const float* __restrict__ grad_scale, const float* __restrict__ skip_flag) {
   if (skip_flag && *skip_flag != 0.f) return;
   const float gs = grad_scale ? *grad_scale : 1.f;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const float grad = static_cast<float>(g[i]) * gs;
-    float w = master ? master[i] : __bfloat162float(p[i]);
-    float mi = static_cast<float>(m[i]);
-    float vi = static_cast<float>(v[i]);
-    mi = b1 * mi + (1.f - b1) * grad;
-    vi = b2 * vi + (1.f - b2) * grad * grad;
-    const float upd = (mi / bc1) / (sqrtf(vi / bc2) + eps);
-    w = w - lr * (upd + wd * w);
+  const long long n8 = n / 8;
+  for (long long i8 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i8 < n8;
+       i8 += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long i = i8 * 8;
+    float gr[8], mi[8], vi[8], w[8];
+    adam_load8<GT>(g + i, gr);
+    adam_load8<MT>(m + i, mi);
+    adam_load8<MT>(v + i, vi);
+    uint4 pw = *reinterpret_cast<const uint4*>(p + i);
+    unsigned short* ph = reinterpret_cast<unsigned short*>(&pw);
+    uint4 lw;
+    short* pl = reinterpret_cast<short*>(&lw);
+    if (master) {
+      adam_load8<float>(master + i, w);
+    } else if (lo) {
+      lw = *reinterpret_cast<const uint4*>(lo + i);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = split_join(ph[j], pl[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = __uint_as_float(static_cast<unsigned>(ph[j]) << 16);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w[j] = adam_update(w[j], gr[j] * gs, mi[j], vi[j], a);
+    adam_store8<MT>(m + i, mi);
+    adam_store8<MT>(v + i, vi);
+    if (master) {
+      adam_store8<float>(master + i, w);
+      store8(p + i, w);
+    } else if (lo) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) split_cut(w[j], ph[j], pl[j]);
+      *reinterpret_cast<uint4*>(p + i) = pw;
+      *reinterpret_cast<uint4*>(lo + i) = lw;
+    } else {
+      store8(p + i, w);
+    }
+  }
+  // ragged tail (fewer than eight elements): first threads of block 0
+  if (blockIdx.x == 0 && threadIdx.x < n - n8 * 8) {
+    const long long i = n8 * 8 + threadIdx.x;
+    float mi = static_cast<float>(m[i]), vi = static_cast<float>(v[i]);
+    unsigned short hi = reinterpret_cast<unsigned short*>(p)[i];
+    float w = master ? master[i] : (lo ? split_join(hi, lo[i]) : __uint_as_float(static_cast<unsigned>(hi) << 16));
+    w = adam_update(w, static_cast<float>(g[i]) * gs, mi, vi, a);
     m[i] = static_cast<MT>(mi);
     v[i] = static_cast<MT>(vi);
-    if (master) master[i] = w;
-    p[i] = __float2bfloat16(w);
+    if (master) {
+      master[i] = w;
+      p[i] = __float2bfloat16(w);
+    } else if (lo) {
+      short l;
+      split_cut(w, hi, l);
+      reinterpret_cast<unsigned short*>(p)[i] = hi;
+      lo[i] = l;
+    } else {
+      p[i] = __float2bfloat16(w);
+    }
+  }
+}
+
+// master[i] = join(p[i], lo[i]) (fp32 view of a split master, for checkpoints and checks)
+__global__ void split_master_join_kernel(const bf16* __restrict__ p, const short* __restrict__ lo, float* __restrict__ out,
+                                         long long n) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    out[i] = split_join(reinterpret_cast<const unsigned short*>(p)[i], lo[i]);
+}
+// (p[i], lo[i]) = cut(master[i])
+__global__ void split_master_cut_kernel(const float* __restrict__ master, bf16* __restrict__ p, short* __restrict__ lo,
+                                        long long n) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    unsigned short hi;
+    short l;
+    split_cut(master[i], hi, l);
+    reinterpret_cast<unsigned short*>(p)[i] = hi;
+    lo[i] = l;
   }
 }
 
@@ -477,20 +594,30 @@ void swiglu_bwd(const void* dout, const void* in, void* din, long long T, int I,
                                                                static_cast<bf16*>(din), T, I);
 }
 
-void adam_step(void* p, float* master, const void* g, bool g_fp32, void* m, void* v, bool mv_bf16, long long n, float lr,
-               float b1, float b2, float eps, float wd, float bc1, float bc2, const float* grad_scale,
+void adam_step(void* p, float* master, void* lo, const void* g, bool g_fp32, void* m, void* v, bool mv_bf16, long long n,
+               float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, const float* grad_scale,
                const float* skip_flag, cudaStream_t s) {
   if (n <= 0) return;
-  const int grid = grid_for(n, 256, 148 * 16);
+  const int grid = grid_for((n + 7) / 8, 256, 148 * 8);
   bf16* pp = static_cast<bf16*>(p);
+  const AdamScalars a{lr, b1, b2, eps, wd, bc1, bc2};
 #define MB_ADAM(GT, MT)                                                                                            \
-  adam_kernel<GT, MT><<<grid, 256, 0, s>>>(pp, master, static_cast<const GT*>(g), static_cast<MT*>(m),              \
-                                           static_cast<MT*>(v), n, lr, b1, b2, eps, wd, bc1, bc2, grad_scale, skip_flag)
+  adam_kernel<GT, MT><<<grid, 256, 0, s>>>(pp, master, static_cast<short*>(lo), static_cast<const GT*>(g),          \
+                                           static_cast<MT*>(m), static_cast<MT*>(v), n, a, grad_scale, skip_flag)
   if (g_fp32 && !mv_bf16) MB_ADAM(float, float);
   else if (g_fp32 && mv_bf16) MB_ADAM(float, bf16);
   else if (!g_fp32 && !mv_bf16) MB_ADAM(bf16, float);
   else MB_ADAM(bf16, bf16);
 #undef MB_ADAM
+}
+
+void split_master_join(const void* p, const void* lo, float* out, long long n, cudaStream_t s) {
+  if (n <= 0) return;
+  split_master_join_kernel<<<grid_for(n, 256), 256, 0, s>>>(static_cast<const bf16*>(p), static_cast<const short*>(lo), out, n);
+}
+void split_master_cut(const float* master, void* p, void* lo, long long n, cudaStream_t s) {
+  if (n <= 0) return;
+  split_master_cut_kernel<<<grid_for(n, 256), 256, 0, s>>>(master, static_cast<bf16*>(p), static_cast<short*>(lo), n);
 }
 
 void sumsq(const void* g, bool g_fp32, long long n, float* out, cudaStream_t s) {

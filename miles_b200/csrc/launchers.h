@@ -21,9 +21,13 @@ void qk_norm_rope_bwd(const void* dq, const void* dk, const void* dv, const void
                       int T, int Hq, int Hk, float theta, bool use_norm, cudaStream_t s);
 void swiglu_fwd(const void* in, void* out, long long T, int I, cudaStream_t s);
 void swiglu_bwd(const void* dout, const void* in, void* din, long long T, int I, cudaStream_t s);
-void adam_step(void* p, float* master, const void* g, bool g_fp32, void* m, void* v, bool mv_bf16, long long n, float lr,
-               float b1, float b2, float eps, float wd, float bc1, float bc2, const float* grad_scale,
+// Fused Adam(W) on a bf16 flat buffer. The fp32 master is `master` (fp32 array), or the pair (p, lo) with `lo` a
+// signed 16-bit remainder per element (see elementwise.cu), or absent. Pointers 16-byte aligned.
+void adam_step(void* p, float* master, void* lo, const void* g, bool g_fp32, void* m, void* v, bool mv_bf16, long long n,
+               float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, const float* grad_scale,
                const float* skip_flag, cudaStream_t s);
+void split_master_join(const void* p, const void* lo, float* out, long long n, cudaStream_t s);
+void split_master_cut(const float* master, void* p, void* lo, long long n, cudaStream_t s);
 void sumsq(const void* g, bool g_fp32, long long n, float* out, cudaStream_t s);
 
 // ---- moe.cu

@@ -113,16 +113,45 @@ at::Tensor swiglu_bwd(const at::Tensor& dout, const at::Tensor& in) {
 
 void adam_step(at::Tensor& p, const c10::optional<at::Tensor>& master, const at::Tensor& g, at::Tensor& m, at::Tensor& v,
                double lr, double b1, double b2, double eps, double wd, int64_t step,
-               const c10::optional<at::Tensor>& grad_scale, const c10::optional<at::Tensor>& skip_flag) {
+               const c10::optional<at::Tensor>& grad_scale, const c10::optional<at::Tensor>& skip_flag,
+               const c10::optional<at::Tensor>& lo) {
   CHECK_BF16(p);
   TORCH_CHECK(g.is_cuda() && g.is_contiguous() && g.numel() == p.numel(), "bad gradient");
   TORCH_CHECK(m.scalar_type() == v.scalar_type() && m.numel() == p.numel() && v.numel() == p.numel(), "bad moments");
+  TORCH_CHECK(m.is_cuda() && v.is_cuda() && m.is_contiguous() && v.is_contiguous(), "moments must be contiguous device tensors");
+  void* lo_ptr = nullptr;
+  if (lo.has_value() && lo->defined()) {
+    TORCH_CHECK(lo->is_cuda() && lo->is_contiguous() && lo->scalar_type() == at::kShort && lo->numel() == p.numel(),
+                "lo must be an int16 device tensor of the parameter's size");
+    TORCH_CHECK(!(master.has_value() && master->defined()), "pass either master or lo");
+    lo_ptr = lo->data_ptr();
+  }
+  auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  TORCH_CHECK(aligned(p.data_ptr()) && aligned(g.data_ptr()) && aligned(m.data_ptr()) && aligned(v.data_ptr()) &&
+              aligned(lo_ptr) && aligned(opt_ptr<float>(master)), "adam_step needs 16-byte aligned buffers");
   const c10::cuda::CUDAGuard guard(p.device());
   const float bc1 = 1.f - std::pow(static_cast<float>(b1), static_cast<float>(step));
   const float bc2 = 1.f - std::pow(static_cast<float>(b2), static_cast<float>(step));
-  mb::adam_step(p.data_ptr(), opt_ptr<float>(master), g.data_ptr(), g.scalar_type() == at::kFloat, m.data_ptr(),
+  mb::adam_step(p.data_ptr(), opt_ptr<float>(master), lo_ptr, g.data_ptr(), g.scalar_type() == at::kFloat, m.data_ptr(),
                 v.data_ptr(), m.scalar_type() == at::kBFloat16, p.numel(), lr, b1, b2, eps, wd, bc1, bc2,
                 opt_ptr<float>(grad_scale), opt_ptr<float>(skip_flag), cur_stream());
+}
+
+at::Tensor split_master_join(const at::Tensor& p, const at::Tensor& lo) {
+  CHECK_BF16(p);
+  TORCH_CHECK(lo.is_cuda() && lo.is_contiguous() && lo.scalar_type() == at::kShort && lo.numel() == p.numel(), "bad lo");
+  const c10::cuda::CUDAGuard guard(p.device());
+  at::Tensor out = at::empty(p.sizes(), p.options().dtype(at::kFloat));
+  mb::split_master_join(p.data_ptr(), lo.data_ptr(), out.data_ptr<float>(), p.numel(), cur_stream());
+  return out;
+}
+
+void split_master_cut(const at::Tensor& master, at::Tensor& p, at::Tensor& lo) {
+  CHECK_BF16(p); CHECK_F32(master);
+  TORCH_CHECK(lo.is_cuda() && lo.is_contiguous() && lo.scalar_type() == at::kShort && lo.numel() == p.numel() &&
+              master.numel() == p.numel(), "bad lo / master");
+  const c10::cuda::CUDAGuard guard(p.device());
+  mb::split_master_cut(master.data_ptr<float>(), p.data_ptr(), lo.data_ptr(), p.numel(), cur_stream());
 }
 
 void sumsq(const at::Tensor& g, at::Tensor& out) {
@@ -244,7 +273,11 @@ void register_elementwise(pybind11::module_& m) {
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
-  m.def("adam_step", &adam_step);
+  m.def("adam_step", &adam_step, pybind11::arg("p"), pybind11::arg("master"), pybind11::arg("g"), pybind11::arg("m"), pybind11::arg("v"), pybind11::arg("lr"),
+        pybind11::arg("b1"), pybind11::arg("b2"), pybind11::arg("eps"), pybind11::arg("wd"), pybind11::arg("step"), pybind11::arg("grad_scale") = pybind11::none(),
+        pybind11::arg("skip_flag") = pybind11::none(), pybind11::arg("lo") = pybind11::none());
+  m.def("split_master_join", &split_master_join);
+  m.def("split_master_cut", &split_master_cut);
   m.def("sumsq", &sumsq);
   m.def("moe_router_topk", &moe_router_topk);
   m.def("moe_router_bwd", &moe_router_bwd);

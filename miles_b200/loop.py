@@ -236,7 +236,9 @@ class RLLoop:
         """A full copy of the experts for the rollout engine, if asked for (default) and if it fits next to the
         trainer's state, the KV cache and an activation reserve."""
         a = self.args
-        if not self.actor.on_gpu or getattr(a, "rollout_replicate_experts", True) is False or self.ps.tp.size > 1:
+        from .trainer.actor import replica_wanted
+
+        if not self.actor.on_gpu or not replica_wanted(a, self.ps.ep.size) or self.ps.tp.size > 1:
             return False
         replica = self._replica_bytes()
         free_now, total = torch.cuda.mem_get_info(self.actor.device)
@@ -280,8 +282,8 @@ class RLLoop:
         a = self.args
         if getattr(a, "start_rollout_id", None) is not None:
             start = a.start_rollout_id
-        elif getattr(a, "load", None) and self.actor.global_step and not getattr(a, "finetune", False):
-            start = self.actor.global_step
+        elif getattr(a, "load", None) and self.actor.loaded_rollout_id is not None and not getattr(a, "finetune", False):
+            start = self.actor.loaded_rollout_id + 1  # the checkpoint was written after that rollout
         else:
             start = 0
         if start > 0:

@@ -30,23 +30,53 @@ from .optimizer import FlatAdam, OptimConfig
 _DT = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
 
 
-def choose_memory_plan(total_bytes: int, dense_params: int, expert_params: int, reserve_frac: float = 0.30,
-                       extra_resident_bytes: int = 0) -> dict:
-    """Pick gradient / optimizer-state precision and placement that leaves ``reserve_frac`` of the device
-    for activations and for the part of the KV cache that does not fit into the bytes it borrows from the
-    expert gradients.  Bytes per parameter: bf16 weight 2 + gradient + two moments (+ master)."""
-    budget = total_bytes * (1.0 - reserve_frac) - extra_resident_bytes  # e.g. the rollout engine's full expert replica
-    n = dense_params + expert_params
-    plans = [
-        ("fp32-master", dict(expert_grad="fp32", state="fp32", master=True, offload=False), 2 + 4 + 8 + 4),
-        ("fp32-states", dict(expert_grad="bf16", state="fp32", master=False, offload=False), 2 + 2 + 8),
-        ("bf16-states", dict(expert_grad="bf16", state="bf16", master=False, offload=False), 2 + 2 + 4),
-        ("bf16-states-host", dict(expert_grad="bf16", state="bf16", master=False, offload=True), 2 + 2),
-    ]
-    for name, plan, bpp in plans:
-        if n * bpp <= budget:
-            return dict(plan, name=name)
-    return dict(plans[-1][1], name=plans[-1][0])
+EP_ENGINE_MIN_RANKS = 99  # expert-parallel groups of at least this many ranks serve the rollout expert parallel too
+
+
+def replica_wanted(args, ep_size: int) -> bool:
+    """Whether the colocated engine of an expert-parallel trainer serves from a full copy of the experts.
+    ``--rollout-replicate-experts`` / ``--no-rollout-replicate-experts`` decide; by default small groups (two ranks)
+    take the replica and larger ones the expert-parallel engine, which shares the expert weight stream."""
+    v = getattr(args, "rollout_replicate_experts", None)
+    if v is None:
+        return ep_size < EP_ENGINE_MIN_RANKS
+    return bool(v)
+
+
+def choose_memory_plan(total_bytes: int, dense_params: int, expert_params: int, reserve_frac: float = 0.22,
+                       extra_resident_bytes: int = 0, kv_bytes: int = 0, dp_size: int = 1) -> dict:
+    """Where the optimizer state of the expert group lives. The numerics are the same at every size:
+    bf16 weights whose fp32 master is kept as (bf16 weight, signed 16-bit remainder), fp32 Adam moments, fp32
+    gradient accumulation for the replicated parameters and bf16 for the experts (that buffer shares its bytes
+    with the KV cache of the colocated engine). Per expert parameter that is 2 B of weight on the device and 10 B
+    of optimizer state; the plan keeps the share of those 10 B that fits next to everything else on the device
+    and streams the rest through pinned host memory every optimizer step.
+
+    ``reserve_frac`` of the device is left for activations, exchange buffers and the allocator;
+    ``extra_resident_bytes`` is whatever else will stay resident (e.g. a full expert replica for the engine);
+    ``kv_bytes`` the KV pool the engine will want (it shares the expert-gradient arena, so the larger of the two
+    counts); the replicated parameters' state is partitioned over ``dp_size`` ranks."""
+    state = expert_params * 10
+    dense = dense_params * (2 + 4) + dense_params * 10 // max(dp_size, 1)
+    resident = dense + expert_params * 2 + max(int(kv_bytes), expert_params * 2) + int(extra_resident_bytes)
+    room = int(total_bytes * (1.0 - reserve_frac)) - resident
+    plan = dict(expert_grad="bf16", state="fp32", master=True, offload=False, resident_frac=1.0, name="fp32-master")
+    if state > room:
+        frac = max(0.0, min(1.0, room / max(state, 1)))
+        frac = int(frac * 64) / 64.0  # whole chunks, rounded down
+        plan.update(offload=True, resident_frac=frac, name="fp32-master, %d%% of the expert state streamed from host" % round(100 * (1 - frac)))
+    return plan
+
+
+def wanted_kv_bytes(args, cfg, n_rep: int) -> int:
+    """The KV pool a colocated engine asks for: every running request at the full context length."""
+    local_batch = max(1, (args.rollout_batch_size * args.n_samples_per_prompt + n_rep - 1) // n_rep)
+    max_running = getattr(args, "sglang_max_running_requests", None) or min(512, max(local_batch, 1))
+    max_ctx = getattr(args, "rollout_max_context_len", None) or ((getattr(args, "rollout_max_prompt_len", None) or 1024)
+                                                                  + args.rollout_max_response_len + 8)
+    page = getattr(args, "engine_page_size", 64)
+    per_tok = 2 * cfg.num_layers * cfg.num_kv_heads * cfg.head_dim * 2
+    return int(max_running * (max_ctx + page) * per_tok)
 
 
 class TrainActor:
@@ -103,6 +133,7 @@ class TrainActor:
         self.weights_backup: dict = {}   # tag -> pinned host copies of the flat buffers (ref / old_actor / teacher)
         self.rollout_engines: list = []
         self.global_step = 0
+        self.loaded_rollout_id: Optional[int] = None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._value_head = None
@@ -122,9 +153,9 @@ class TrainActor:
         if getattr(args, "load", None):
             from ..checkpoint import load_checkpoint
 
-            it = load_checkpoint(self, args.load, getattr(args, "ckpt_step", None))
-            if it is not None:
-                self.global_step = it
+            # the rollout id the checkpoint was written after (None: weights only, start from rollout 0);
+            # load_checkpoint restores global_step (optimizer steps) itself
+            self.loaded_rollout_id = load_checkpoint(self, args.load, getattr(args, "ckpt_step", None))
         need_ref = (args.kl_coef != 0 or args.use_kl_loss) and role == "actor"
         if need_ref:
             self.backup_weights("ref")
@@ -148,20 +179,33 @@ class TrainActor:
         if self.on_gpu:
             total = torch.cuda.get_device_properties(self.device).total_memory
             extra = 0
-            if (self.cfg.is_moe and self.ps.ep.size > 1 and self.role == "actor" and self.ps.tp.size == 1
-                    and getattr(a, "rollout_replicate_experts", True) is not False and not getattr(a, "debug_train_only", False)):
+            colocated = self.role == "actor" and not getattr(a, "debug_train_only", False) and not getattr(a, "rollout_engine_urls", None)
+            if (self.cfg.is_moe and self.ps.ep.size > 1 and colocated and self.ps.tp.size == 1
+                    and replica_wanted(a, self.ps.ep.size)):
                 # the colocated engine will hold all experts (see RLLoop._build_engine): leave room for the part this
                 # rank does not train
                 extra = (expert * self.ps.ep.size - expert) * 2
-            plan = choose_memory_plan(total, dense, expert, extra_resident_bytes=extra)
+            kv = 0
+            if colocated:
+                kv = min(wanted_kv_bytes(a, self.cfg, self.ps.dp_cp.size * self.ps.pp.size),
+                         int(total * float(getattr(a, "sglang_mem_fraction_static", 0.7))))
+            plan = choose_memory_plan(total, dense, expert, extra_resident_bytes=extra, kv_bytes=kv, dp_size=self.ps.dp_cp.size)
         else:
-            plan = dict(expert_grad="fp32", state="fp32", master=False, offload=False, name="cpu")
+            plan = dict(expert_grad="fp32", state="fp32", master=False, offload=False, resident_frac=1.0, name="cpu")
         # explicit flags override the automatic plan
         if getattr(a, "use_precision_aware_optimizer", False) or a.exp_avg_dtype != "fp32" or a.exp_avg_sq_dtype != "fp32":
             plan["state"] = a.exp_avg_dtype if a.exp_avg_dtype in _DT else "bf16"
-            plan["master"] = getattr(a, "main_params_dtype", "fp32") == "fp32" and plan.get("master", False)
-        if getattr(a, "optimizer_cpu_offload", False):
-            plan["offload"] = True
+            plan["name"] += f", {plan['state']} moments"
+        if getattr(a, "main_params_dtype", "fp32") != "fp32":
+            plan["master"] = False
+            plan["name"] += ", no fp32 master"
+        if getattr(a, "optimizer_cpu_offload", False) or getattr(a, "offload_optimizer_states", False):
+            plan["offload"], plan["resident_frac"] = True, 0.0
+        if getattr(a, "accumulate_allreduce_grads_in_fp32", False) and self.on_gpu and self.cfg.is_moe:
+            # fp32 accumulation for the experts too, when twice the bytes still fit beside the rest
+            total = torch.cuda.get_device_properties(self.device).total_memory
+            if expert * 4 + expert * 2 + dense * 6 + (expert * 10 if not plan["offload"] else 0) < 0.7 * total:
+                plan["expert_grad"] = "fp32"
         if self.store.dtype == torch.float32:
             plan["master"] = False
         self.plan = plan
@@ -170,7 +214,8 @@ class TrainActor:
         oc = OptimConfig(lr=a.lr if self.role == "actor" else (a.critic_lr or a.lr), beta1=a.adam_beta1, beta2=a.adam_beta2,
                          eps=a.adam_eps, weight_decay=a.weight_decay, clip_grad=a.clip_grad, state_dtype=_DT[plan["state"]],
                          master_weights=plan["master"], offload_states=plan["offload"],
- lr_decay_style=a.lr_decay_style,
+                         offload_resident_frac=plan.get("resident_frac", 0.0) if plan["offload"] else 0.0,
+                         lr_decay_style=a.lr_decay_style,
                          lr_warmup_iters=a.lr_warmup_iters or 0, lr_decay_iters=a.lr_decay_iters or 0, min_lr=a.min_lr,
                          lr_wsd_decay_iters=a.lr_wsd_decay_iters or 0)
         if getattr(a, "optimizer", "adam") == "muon":

@@ -35,8 +35,8 @@ class OptimConfig:
     weight_decay: float = 0.1
     clip_grad: float = 1.0
     state_dtype: torch.dtype = torch.float32
-    master_weights: bool = True
-    offload_states: bool = False          # keep moments (and master) of the expert group in pinned host memory
+    master_weights: bool = True           # fp32 master copy of bf16 parameters (on the GPU: bf16 weight + 16-bit remainder)
+    offload_states: bool = False          # keep moments and master remainder of the expert group in pinned host memory
     offload_resident_frac: float = 0.0    # share of the offloaded moments that stays on the device after all (no stream)
     offload_chunk_elems: int = 1 << 27    # 128 Mi elements per streamed chunk
     # LR schedule (in optimizer steps)
@@ -96,6 +96,9 @@ class FlatAdam:
                 continue
             off = cfg.offload_states and g == "expert" and self.on_gpu
             st: dict = {"offload": off}
+            # split master: the bf16 weight is the upper half of the fp32 master, `lo` the signed 16-bit remainder
+            # (starts at zero: the initial master is the bf16 weight itself)
+            split = cfg.master_weights and flat.dtype == torch.bfloat16 and self.on_gpu
             if off:
                 ce = cfg.offload_chunk_elems
                 st["chunks"] = [(a, min(a + ce, n)) for a in range(0, n, ce)]
@@ -103,15 +106,22 @@ class FlatAdam:
                 # fill the time the copy engines need for the next streamed chunk
                 fr = min(max(cfg.offload_resident_frac, 0.0), 1.0)
                 res = [int((i + 1) * fr) > int(i * fr) for i in range(len(st["chunks"]))]
-                mk = lambda k, on_dev: (torch.zeros(k, dtype=cfg.state_dtype, device=self.dev) if on_dev
-                                        else torch.zeros(k, dtype=cfg.state_dtype).pin_memory())
+
+                def mk(k, on_dev, dt=cfg.state_dtype):
+                    if on_dev:
+                        return torch.zeros(k, dtype=dt, device=self.dev)
+                    return torch.empty(k, dtype=dt, pin_memory=True).zero_()  # pinned directly: no pageable detour
+
                 st["m"] = [mk(b - a, r) for (a, b), r in zip(st["chunks"], res)]
                 st["v"] = [mk(b - a, r) for (a, b), r in zip(st["chunks"], res)]
                 st["master"] = None
+                # the 16-bit remainder of the split fp32 master travels with the moments of its chunk
+                st["lo"] = [mk(b - a, r, torch.int16) for (a, b), r in zip(st["chunks"], res)] if split else None
             else:
                 st["m"] = torch.zeros(n, dtype=cfg.state_dtype, device=self.dev)
                 st["v"] = torch.zeros(n, dtype=cfg.state_dtype, device=self.dev)
-                st["master"] = flat.float().clone() if (cfg.master_weights and flat.dtype != torch.float32) else None
+                st["lo"] = torch.zeros(n, dtype=torch.int16, device=self.dev) if split else None
+                st["master"] = flat.float().clone() if (cfg.master_weights and flat.dtype != torch.float32 and not split) else None
             self.state[g] = st
         # weight decay applies to matrices only (norm weights and biases are exempt)
         self.segments = {g: [] for g in store.flat}
@@ -182,10 +192,10 @@ class FlatAdam:
         self.grad_scale.copy_((coef * extra_scale).reshape(1))
 
     # ------------------------------------------------------------------ update
-    def _adam_region(self, p, master, g, m, v, lr, wd, step):
+    def _adam_region(self, p, master, g, m, v, lr, wd, step, lo=None):
         c = self.cfg
         if self.C is not None and p.dtype == torch.bfloat16:
-            self.C.adam_step(p, master, g, m, v, lr, c.beta1, c.beta2, c.eps, wd, step, self.grad_scale, self.skip_flag)
+            self.C.adam_step(p, master, g, m, v, lr, c.beta1, c.beta2, c.eps, wd, step, self.grad_scale, self.skip_flag, lo)
             self.launches += 1
             return
         if float(self.skip_flag.item()) != 0.0:
@@ -221,7 +231,8 @@ class FlatAdam:
             for a, b, wd in self.segments[g]:
                 b = min(b, flat.numel())
                 self._adam_region(flat[a:b], st["master"][a:b] if st["master"] is not None else None, grad[a:b],
-                                  st["m"][a:b], st["v"][a:b], lr, wd, self.step_count)
+                                  st["m"][a:b], st["v"][a:b], lr, wd, self.step_count,
+                                  st["lo"][a:b] if st.get("lo") is not None else None)
         self.store.version += 1
         return self.last_grad_norm * grad_scale
 
@@ -234,8 +245,10 @@ class FlatAdam:
         main = torch.cuda.current_stream()
         ce = max(b - a for a, b in st["chunks"])
         nbuf = 3
+        has_lo = st.get("lo") is not None
         if "stage" not in st:
-            st["stage"] = [(torch.empty(ce, dtype=c.state_dtype, device=self.dev), torch.empty(ce, dtype=c.state_dtype, device=self.dev))
+            st["stage"] = [(torch.empty(ce, dtype=c.state_dtype, device=self.dev), torch.empty(ce, dtype=c.state_dtype, device=self.dev),
+                            torch.empty(ce, dtype=torch.int16, device=self.dev) if has_lo else None)
                            for _ in range(nbuf)]
         ev_in = [torch.cuda.Event() for _ in st["chunks"]]
         ev_cmp = [torch.cuda.Event() for _ in st["chunks"]]
@@ -248,10 +261,11 @@ class FlatAdam:
         order = {k: j for j, k in enumerate(streamed)}
         for k, (a, b) in enumerate(st["chunks"]):
             if st["m"][k].is_cuda:  # resident chunk: plain update, overlaps the copies of the streamed ones
-                self._adam_region(flat[a:b], None, grad[a:b], st["m"][k], st["v"][k], lr, wd, self.step_count)
+                self._adam_region(flat[a:b], None, grad[a:b], st["m"][k], st["v"][k], lr, wd, self.step_count,
+                                  st["lo"][k] if has_lo else None)
                 continue
             i = order[k]
-            dm, dv = st["stage"][i % nbuf]
+            dm, dv, dl = st["stage"][i % nbuf]
             n = b - a
             with torch.cuda.stream(s_in):
                 if i >= nbuf:
@@ -260,17 +274,21 @@ class FlatAdam:
                     s_in.wait_event(start)
                 dm[:n].copy_(st["m"][k], non_blocking=True)
                 dv[:n].copy_(st["v"][k], non_blocking=True)
+                if has_lo:
+                    dl[:n].copy_(st["lo"][k], non_blocking=True)
                 ev_in[i].record(s_in)
             main.wait_event(ev_in[i])
-            self._adam_region(flat[a:b], None, grad[a:b], dm[:n], dv[:n], lr, wd, self.step_count)
+            self._adam_region(flat[a:b], None, grad[a:b], dm[:n], dv[:n], lr, wd, self.step_count, dl[:n] if has_lo else None)
             ev_cmp[i].record(main)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_cmp[i])
                 st["m"][k].copy_(dm[:n], non_blocking=True)
                 st["v"][k].copy_(dv[:n], non_blocking=True)
+                if has_lo:
+                    st["lo"][k].copy_(dl[:n], non_blocking=True)
                 ev_out[i].record(s_out)
-            self.h2d_bytes += 2 * n * es
-            self.d2h_bytes += 2 * n * es
+            self.h2d_bytes += n * (2 * es + (2 if has_lo else 0))
+            self.d2h_bytes += n * (2 * es + (2 if has_lo else 0))
         if streamed:
             main.wait_event(ev_out[len(streamed) - 1])
             if len(streamed) > 1:
@@ -287,7 +305,7 @@ class FlatAdam:
             host = [k for k, t in enumerate(st["m"]) if not t.is_cuda]
             if not host:
                 continue
-            per = 2 * st["m"][host[0]].numel() * st["m"][host[0]].element_size()
+            per = st["m"][host[0]].numel() * (2 * st["m"][host[0]].element_size() + (2 if st.get("lo") is not None else 0))
             take = min(len(host), int(max(max_bytes - moved, 0) // max(per, 1)))
             if take <= 0:
                 continue
@@ -298,7 +316,9 @@ class FlatAdam:
                     continue
                 st["m"][k] = st["m"][k].to(self.dev)
                 st["v"][k] = st["v"][k].to(self.dev)
-                moved += 2 * st["m"][k].numel() * st["m"][k].element_size()
+                if st.get("lo") is not None:
+                    st["lo"][k] = st["lo"][k].to(self.dev)
+                moved += per
         return moved
 
     # ------------------------------------------------------------------ checkpoint
@@ -306,10 +326,28 @@ class FlatAdam:
         out = {"step": self.step_count}
         for g, st in self.state.items():
             if st["offload"]:
-                out[g] = {"m": torch.cat([t.cpu() for t in st["m"]]), "v": torch.cat([t.cpu() for t in st["v"]]), "master": None}
+                out[g] = {"m": torch.cat([t.cpu() for t in st["m"]]), "v": torch.cat([t.cpu() for t in st["v"]]), "master": None,
+                          "lo": torch.cat([t.cpu() for t in st["lo"]]) if st.get("lo") is not None else None}
             else:
-                out[g] = {"m": st["m"], "v": st["v"], "master": st["master"]}
+                out[g] = {"m": st["m"], "v": st["v"], "master": st["master"], "lo": st.get("lo")}
         return out
+
+    def master_fp32(self, g: str) -> torch.Tensor:
+        """The fp32 master values of group ``g`` as one tensor (a copy; for checkpoints, exports and checks)."""
+        st, flat = self.state[g], self.store.flat[g]
+        if st.get("sharded"):
+            return flat.float()
+        if st.get("master") is not None:
+            return st["master"].clone()
+        lo = st.get("lo")
+        if lo is None:
+            return flat.float()
+        if isinstance(lo, list):
+            out = torch.empty(flat.numel(), dtype=torch.float32, device=self.dev)
+            for (a, b), l in zip(st["chunks"], lo):
+                out[a:b] = self.C.split_master_join(flat[a:b], l.to(self.dev, non_blocking=True))
+            return out
+        return self.C.split_master_join(flat, lo)
 
     def load_state_dict(self, sd: dict) -> None:
         self.step_count = int(sd.get("step", 0))
@@ -318,14 +356,26 @@ class FlatAdam:
                 continue
             src = sd[g]
             if st["offload"]:
-                for (a, b), m, v in zip(st["chunks"], st["m"], st["v"]):
+                for k, ((a, b), m, v) in enumerate(zip(st["chunks"], st["m"], st["v"])):
                     m.copy_(src["m"][a:b])
                     v.copy_(src["v"][a:b])
+                    if st.get("lo") is not None:
+                        if src.get("lo") is not None:
+                            st["lo"][k].copy_(src["lo"][a:b])
+                        else:
+                            st["lo"][k].zero_()
             else:
                 st["m"].copy_(src["m"])
                 st["v"].copy_(src["v"])
                 if st["master"] is not None and src.get("master") is not None:
                     st["master"].copy_(src["master"])
+                if st.get("lo") is not None:
+                    if src.get("lo") is not None:
+                        st["lo"].copy_(src["lo"])
+                    elif src.get("master") is not None:  # a checkpoint written with a plain fp32 master
+                        self.C.split_master_cut(src["master"].to(self.dev).float().contiguous(), self.store.flat[g], st["lo"])
+                    else:
+                        st["lo"].zero_()
 
     def reset_state(self) -> None:
         for st in self.state.values():
@@ -341,3 +391,6 @@ class FlatAdam:
                 self.dense_shard.sync_master_from_params()
             elif st.get("master") is not None:
                 st["master"].copy_(self.store.flat[g].float())
+            elif st.get("lo") is not None:  # the master becomes the bf16 weight itself: remainder zero
+                for t in (st["lo"] if isinstance(st["lo"], list) else [st["lo"]]):
+                    t.zero_()

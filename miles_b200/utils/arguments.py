@@ -113,7 +113,7 @@ TRAINER_FLAGS = [
     ("--init-std", "f", 0.02, {}), ("--engine-page-size", "i", 64, {}), ("--engine-max-prefill-tokens", "i", 16384, {}),
     ("--fused-comm", "B", True, {}), ("--weight-sync-quant", "s", "none", {"choices": ["none", "mxfp8", "nvfp4", "fp8_block"]}),
     # rollout on a full replica of the experts (all-gathered at every weight update) instead of an expert-parallel engine
-    ("--rollout-replicate-experts", "B", True, {}), ("--share-kv-grad-memory", "B", True, {}),
+    ("--rollout-replicate-experts", "B", None, {}), ("--share-kv-grad-memory", "B", True, {}),
 ]
 
 _UNBUILT = {

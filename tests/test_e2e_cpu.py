@@ -44,6 +44,28 @@ def test_single_process_grpo_steps(tmp_path):
     assert loop2.actor.opt.step_count == 2
 
 
+def test_resume_counts_rollouts_not_optimizer_steps(tmp_path):
+    """Two optimizer steps per rollout: the checkpoint written after rollout 1 holds four optimizer steps, and a
+    resumed run continues at rollout 2 with the prompt stream where it stopped (not at "rollout 4")."""
+    from miles_b200.loop import RLLoop
+
+    common = BASE + ["--actor-num-gpus-per-node", "1", "--num-steps-per-rollout", "2", "--save", str(tmp_path / "ckpt"),
+                     "--save-interval", "1"]
+    loop = RLLoop(parse_args(common + ["--num-rollout", "2"]))
+    loop.run()
+    assert loop.actor.global_step == 4 and loop.actor.opt.step_count == 4
+    loop2 = RLLoop(parse_args(common + ["--num-rollout", "3", "--load", str(tmp_path / "ckpt")]))
+    assert loop2.start_rollout_id == 2
+    assert loop2.actor.global_step == 4 and loop2.actor.opt.step_count == 4
+    # the data source continues where the first run stopped: same next prompts as an uninterrupted run would draw
+    ref = RLLoop(parse_args(common + ["--num-rollout", "3"]))
+    for rid in range(2):
+        ref.data_source.get_samples(ref.local_args.rollout_batch_size)
+    a = ref.data_source.get_samples(1)
+    b = loop2.data_source.get_samples(1)
+    assert a[0][0].prompt == b[0][0].prompt or a[0][0].tokens == b[0][0].tokens
+
+
 def _worker(rank: int, world: int, port: int, out_dir: str):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.set_num_threads(2)  # several ranks share the host cores
