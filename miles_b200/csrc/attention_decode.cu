@@ -27,93 +27,6 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-template <int G>
-__global__ void __launch_bounds__(WARPS * 32)
-decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-              const int* __restrict__ block_table, const int* __restrict__ seq_lens, float* __restrict__ part_o,
-              float* __restrict__ part_ml, int Hq, int Hk, int page_size, int max_pages, int num_splits, float scale) {
-  const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int len = seq_lens[b];
-  const int per = (len + num_splits - 1) / num_splits;
-  const int t_lo = split * per;
-  const int t_hi = min(len, t_lo + per);
-
-  float qr[G][4];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(q + (static_cast<long long>(b) * Hq + h * G + g) * D + lane * 4);
-    const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    const float2 a = __bfloat1622float2(rb[0]), c = __bfloat1622float2(rb[1]);
-    qr[g][0] = a.x * scale; qr[g][1] = a.y * scale; qr[g][2] = c.x * scale; qr[g][3] = c.y * scale;
-  }
-  float m[G], l[G], acc[G][4];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -FLT_MAX;
-    l[g] = 0.f;
-    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
-  }
-  const int* table = block_table + static_cast<long long>(b) * max_pages;
-  for (int t = t_lo + warp; t < t_hi; t += WARPS) {
-    const int page = table[t / page_size];
-    const long long slot = static_cast<long long>(page) * page_size + (t % page_size);
-    const long long off = (slot * Hk + h) * D + lane * 4;
-    const uint2 kraw = *reinterpret_cast<const uint2*>(k_cache + off);
-    const uint2 vraw = *reinterpret_cast<const uint2*>(v_cache + off);
-    const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&kraw);
-    const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&vraw);
-    const float2 k0 = __bfloat1622float2(kb[0]), k1 = __bfloat1622float2(kb[1]);
-    const float2 v0 = __bfloat1622float2(vb[0]), v1 = __bfloat1622float2(vb[1]);
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float s = qr[g][0] * k0.x + qr[g][1] * k0.y + qr[g][2] * k1.x + qr[g][3] * k1.y;
-      s = warp_sum(s);
-      const float nm = fmaxf(m[g], s);
-      const float corr = __expf(m[g] - nm);
-      const float p = __expf(s - nm);
-      l[g] = l[g] * corr + p;
-      acc[g][0] = acc[g][0] * corr + p * v0.x;
-      acc[g][1] = acc[g][1] * corr + p * v0.y;
-      acc[g][2] = acc[g][2] * corr + p * v1.x;
-      acc[g][3] = acc[g][3] * corr + p * v1.y;
-      m[g] = nm;
-    }
-  }
-  // merge the warps of this CTA through shared memory
-  __shared__ float sm_m[WARPS][G], sm_l[WARPS][G];
-  __shared__ float sm_o[WARPS][G][D];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    if (lane == 0) {
-      sm_m[warp][g] = m[g];
-      sm_l[warp][g] = l[g];
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) sm_o[warp][g][lane * 4 + i] = acc[g][i];
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
-    const int g = idx / D, d = idx - g * D;
-    float gm = -FLT_MAX;
-#pragma unroll
-    for (int w = 0; w < WARPS; ++w) gm = fmaxf(gm, sm_m[w][g]);
-    float gl = 0.f, go = 0.f;
-#pragma unroll
-    for (int w = 0; w < WARPS; ++w) {
-      const float c = sm_m[w][g] == -FLT_MAX ? 0.f : __expf(sm_m[w][g] - gm);
-      gl += sm_l[w][g] * c;
-      go += sm_o[w][g][d] * c;
-    }
-    const long long base = ((static_cast<long long>(b) * Hq + h * G + g) * num_splits + split);
-    part_o[base * D + d] = go;
-    if (d == 0) {
-      part_ml[base * 2] = gm;
-      part_ml[base * 2 + 1] = gl;
-    }
-  }
-}
-
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int num_splits) {
   const long long bh = blockIdx.x;  // b * Hq + head
@@ -165,13 +78,20 @@ __global__ void __launch_bounds__(WARPS * 32)
 decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                   const int* __restrict__ block_table, const int* __restrict__ seq_lens, float* __restrict__ part_o,
                   float* __restrict__ part_ml, bf16* __restrict__ out, int Hq, int Hk, int page_size, int max_pages,
-                  int num_splits, float scale) {
+                  int num_splits, float scale, long long num_slots, int* __restrict__ status) {
   extern __shared__ __align__(16) unsigned char dsm[];
   bf16* Ks = reinterpret_cast<bf16*>(dsm);            // [2][TOK][LDS]
   bf16* Vs = Ks + 2 * STAGE_ELEMS;                    // [2][TOK][LDS]
   const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int len = seq_lens[b];
+  // The length and the page ids come from device memory the caller filled: a length beyond the block-table row is
+  // clamped, and a page outside the cache is read as zeros (status 9) instead of being dereferenced.
+  int len = seq_lens[b];
+  const long long row_cap = static_cast<long long>(max_pages) * page_size;
+  if (len < 0 || len > row_cap) {
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, 8);
+    len = len < 0 ? 0 : static_cast<int>(row_cap);
+  }
   int per = (len + num_splits - 1) / num_splits;
   per = (per + TOK - 1) / TOK * TOK;
   const int t_lo = split * per;
@@ -204,9 +124,17 @@ decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
       const int piece = threadIdx.x + i * (WARPS * 32);
       const int r = piece >> 4, c16 = piece & 15;
       const int t = base + r;
-      const bool ok = t < t_hi;
+      bool ok = t < t_hi;
       long long slot = 0;
-      if (ok) slot = static_cast<long long>(table[t / page_size]) * page_size + (t % page_size);
+      if (ok) {
+        const long long page = table[t / page_size];
+        if (page < 0 || (num_slots > 0 && (page + 1) * page_size > num_slots)) {
+          ok = false;
+          if (c16 == 0 && status) atomicCAS(status, 0, 9);
+        } else {
+          slot = page * page_size + (t % page_size);
+        }
+      }
       const long long off = (slot * Hk + h) * D + c16 * 8;
       const uint32_t dk = static_cast<uint32_t>(__cvta_generic_to_shared(Ks + stage * STAGE_ELEMS + r * LDS + c16 * 8));
       const uint32_t dv = static_cast<uint32_t>(__cvta_generic_to_shared(Vs + stage * STAGE_ELEMS + r * LDS + c16 * 8));
@@ -328,36 +256,42 @@ decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
 
 }  // namespace
 
-// scratch: fp32 [B*Hq*num_splits*(128+2)]
-void paged_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                            const int* seq_lens, void* out, float* scratch, int B, int Hq, int Hk, int page_size,
-                            int max_pages, int num_splits, float scale, cudaStream_t s) {
-  if (B <= 0) return;
+// scratch: fp32 [B*Hq*num_splits*(128+2)]. `num_slots` = rows of the cache (0: page ids are not range-checked);
+// `status` (may be null) receives 8 for a length beyond the block-table row, 9 for a page outside the cache.
+// Returns the error of this call's own launches (cudaSuccess = 0), not whatever an earlier call left behind.
+int paged_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                           const int* seq_lens, void* out, float* scratch, int B, int Hq, int Hk, int page_size,
+                           int max_pages, int num_splits, float scale, cudaStream_t s, long long num_slots, int* status) {
+  if (B <= 0) return 0;
   float* part_o = scratch;
   float* part_ml = scratch + static_cast<long long>(B) * Hq * num_splits * D;
-  dim3 grid(B, Hk, num_splits);
+  const dim3 grid(B, Hk, num_splits);
   const int G = Hq / Hk;
   constexpr int SMEM = 4 * STAGE_ELEMS * 2;  // K and V, two stages each
-#define MB_DEC(GG)                                                                                                   \
-  do {                                                                                                               \
-    static bool attr_done = false;                                                                                   \
-    if (!attr_done) {                                                                                                \
-      cudaFuncSetAttribute(decode_mma_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);                \
-      attr_done = true;                                                                                              \
-    }                                                                                                                \
-    decode_mma_kernel<GG><<<grid, WARPS * 32, SMEM, s>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k_cache), \
-                                                         static_cast<const bf16*>(v_cache), block_table, seq_lens, part_o, \
-                                                         part_ml, static_cast<bf16*>(out), Hq, Hk, page_size, max_pages, num_splits, scale); \
-  } while (0)
+  const bf16 *qp = static_cast<const bf16*>(q), *kp = static_cast<const bf16*>(k_cache), *vp = static_cast<const bf16*>(v_cache);
+  bf16* op = static_cast<bf16*>(out);
+  void* args[] = {&qp, &kp, &vp, &block_table, &seq_lens, &part_o, &part_ml, &op, &Hq, &Hk, &page_size, &max_pages,
+                  &num_splits, &scale, &num_slots, &status};
+  const void* fn = nullptr;
   switch (G) {
-    case 1: MB_DEC(1); break;
-    case 2: MB_DEC(2); break;
-    case 4: MB_DEC(4); break;
-    case 8: MB_DEC(8); break;
-    default: return;
+    case 1: fn = reinterpret_cast<const void*>(&decode_mma_kernel<1>); break;
+    case 2: fn = reinterpret_cast<const void*>(&decode_mma_kernel<2>); break;
+    case 4: fn = reinterpret_cast<const void*>(&decode_mma_kernel<4>); break;
+    case 8: fn = reinterpret_cast<const void*>(&decode_mma_kernel<8>); break;
+    default: return static_cast<int>(cudaErrorInvalidValue);
   }
-#undef MB_DEC
-  if (num_splits > 1) decode_merge_kernel<<<B * Hq, D, 0, s>>>(part_o, part_ml, static_cast<bf16*>(out), num_splits);
+  // The attribute belongs to the (function, device) pair; setting it costs a table lookup, so it is set on every
+  // call rather than remembered per process (a second device would otherwise launch with the 48 KB default).
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaLaunchKernel(fn, grid, dim3(WARPS * 32), args, SMEM, s);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (num_splits > 1) {
+    const float *po = part_o, *pm = part_ml;
+    void* margs[] = {&po, &pm, &op, &num_splits};
+    e = cudaLaunchKernel(reinterpret_cast<const void*>(&decode_merge_kernel), dim3(B * Hq), dim3(D), margs, 0, s);
+  }
+  return static_cast<int>(e);
 }
 
 }  // namespace mb
@@ -413,10 +347,10 @@ extern "C" const char* mb_noalloc_last_error(void) { return g_noalloc_err; }
 extern "C" int mb_paged_decode_attention_noalloc(const void* q, const void* k_cache, const void* v_cache,
                                                  const int* block_table, const int* seq_lens, void* out, int B, int Hq,
                                                  int Hk, int page_size, int max_pages, int num_splits, float scale,
-                                                 cudaStream_t stream) {
+                                                 long long num_slots, int* status, cudaStream_t stream) {
   if (!q || !k_cache || !v_cache || !block_table || !seq_lens || !out)
     return noalloc_fail(MB_NOALLOC_ERR_BAD_ARG, "null pointer argument");
-  if (B <= 0 || Hq <= 0 || Hk <= 0 || page_size <= 0 || max_pages <= 0 || num_splits <= 0)
+  if (B <= 0 || Hq <= 0 || Hk <= 0 || page_size <= 0 || max_pages <= 0 || num_splits <= 0 || num_slots <= 0)
     return noalloc_fail(MB_NOALLOC_ERR_BAD_ARG, "extents must be positive");
   if (Hq % Hk != 0) return noalloc_fail(MB_NOALLOC_ERR_BAD_ARG, "Hq must be a multiple of Hk");
   const int G = Hq / Hk;
@@ -432,11 +366,12 @@ extern "C" int mb_paged_decode_attention_noalloc(const void* q, const void* k_ca
   float* scratch = nullptr;
   const int rc = noalloc_scratch_for_current_device(&scratch);
   if (rc != MB_NOALLOC_OK) return rc;
-  mb::paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, out, scratch, B, Hq, Hk, page_size, max_pages,
-                             num_splits, scale, stream);
-  const cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) {
-    snprintf(g_noalloc_err, sizeof(g_noalloc_err), "kernel launch failed: %s", cudaGetErrorString(e));
+  // the launcher reports the result of its own launches; an error some earlier, unrelated call left in the
+  // runtime's "last error" slot is neither read nor cleared here
+  const int e = mb::paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, out, scratch, B, Hq, Hk, page_size,
+                                           max_pages, num_splits, scale, stream, num_slots, status);
+  if (e != 0) {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err), "kernel launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(e)));
     return MB_NOALLOC_ERR_CUDA;
   }
   return MB_NOALLOC_OK;

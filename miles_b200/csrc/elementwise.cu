@@ -514,6 +514,55 @@ __global__ void split_master_cut_kernel(const float* __restrict__ master, bf16* 
   }
 }
 
+// ------------------------------------------------------------------ counter-based normal initialisation
+// out[i] = std * N(key, first + i): Philox4x32-10 keyed by `key`, counter = element index / 4, Box-Muller on the four
+// 32-bit outputs. The value of an element depends only on (key, its index in the logical tensor), so any sharding
+// of the tensor (expert parallel, tensor parallel, pipeline stages) draws the same model, and a 30 B parameter
+// model is filled at memory speed instead of through thousands of generator calls.
+__device__ __forceinline__ void philox4x32_10(unsigned long long key, unsigned long long ctr, unsigned (&r)[4]) {
+  unsigned c0 = static_cast<unsigned>(ctr), c1 = static_cast<unsigned>(ctr >> 32), c2 = 0x9E3779B9u, c3 = 0xBB67AE85u;
+  unsigned k0 = static_cast<unsigned>(key), k1 = static_cast<unsigned>(key >> 32);
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const unsigned hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const unsigned hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const unsigned n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  r[0] = c0; r[1] = c1; r[2] = c2; r[3] = c3;
+}
+__device__ __forceinline__ void normal4(unsigned long long key, unsigned long long ctr, float std, float (&o)[4]) {
+  unsigned r[4];
+  philox4x32_10(key, ctr, r);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float u1 = (static_cast<float>(r[2 * j] >> 8) + 1.0f) * (1.0f / 16777216.0f);  // (0, 1]
+    const float u2 = static_cast<float>(r[2 * j + 1] >> 8) * (1.0f / 16777216.0f);       // [0, 1)
+    const float rad = std * sqrtf(-2.0f * __logf(u1));
+    float sn, cs;
+    __sincosf(6.283185307179586f * u2, &sn, &cs);
+    o[2 * j] = rad * cs;
+    o[2 * j + 1] = rad * sn;
+  }
+}
+template <typename T>
+__global__ void init_normal_kernel(T* __restrict__ out, long long n, unsigned long long key, long long first, float std) {
+  // one thread per group of four consecutive logical elements (aligned to four in the logical index space)
+  const long long g0 = first / 4, g1 = (first + n + 3) / 4;
+  for (long long g = g0 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; g < g1;
+       g += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float v[4];
+    normal4(key, static_cast<unsigned long long>(g), std, v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const long long i = g * 4 + j - first;
+      if (i >= 0 && i < n) out[i] = static_cast<T>(v[j]);
+    }
+  }
+}
+
 // Sum of squares of a flat buffer into a single fp32 accumulator (for the global grad norm).
 template <typename GT>
 __global__ void sumsq_kernel(const GT* __restrict__ g, long long n, float* __restrict__ out) {
@@ -618,6 +667,13 @@ void split_master_join(const void* p, const void* lo, float* out, long long n, c
 void split_master_cut(const float* master, void* p, void* lo, long long n, cudaStream_t s) {
   if (n <= 0) return;
   split_master_cut_kernel<<<grid_for(n, 256), 256, 0, s>>>(master, static_cast<bf16*>(p), static_cast<short*>(lo), n);
+}
+
+void init_normal(void* out, bool fp32, long long n, unsigned long long key, long long first, float std, cudaStream_t s) {
+  if (n <= 0) return;
+  const int grid = grid_for((n + 3) / 4 + 1, 256, 148 * 16);
+  if (fp32) init_normal_kernel<float><<<grid, 256, 0, s>>>(static_cast<float*>(out), n, key, first, std);
+  else init_normal_kernel<bf16><<<grid, 256, 0, s>>>(static_cast<bf16*>(out), n, key, first, std);
 }
 
 void sumsq(const void* g, bool g_fp32, long long n, float* out, cudaStream_t s) {

@@ -29,6 +29,8 @@ void adam_step(void* p, float* master, void* lo, const void* g, bool g_fp32, voi
 void split_master_join(const void* p, const void* lo, float* out, long long n, cudaStream_t s);
 void split_master_cut(const float* master, void* p, void* lo, long long n, cudaStream_t s);
 void sumsq(const void* g, bool g_fp32, long long n, float* out, cudaStream_t s);
+// out[i] = std * N(key, first + i), a counter-based generator: independent of how the logical tensor is sharded.
+void init_normal(void* out, bool fp32, long long n, unsigned long long key, long long first, float std, cudaStream_t s);
 
 // ---- moe.cu
 // Router: softmax over E experts (fp32 logits), top-k, optional renormalisation of the k weights.
@@ -76,9 +78,12 @@ void sample_rows(const void* logits, bool fp32, int T, int V, long long ld, cons
                  cudaStream_t s);
 
 // ---- attention.cu
-void paged_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                            const int* seq_lens, void* out, float* scratch, int B, int Hq, int Hk, int page_size,
-                            int max_pages, int num_splits, float scale, cudaStream_t s);
+// Returns the CUDA error code of its own launches (0 = ok). `num_slots` = rows of the cache (0: unchecked page ids),
+// `status` (device int or null) receives 8 / 9 for a length / page id outside the tables.
+int paged_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                           const int* seq_lens, void* out, float* scratch, int B, int Hq, int Hk, int page_size,
+                           int max_pages, int num_splits, float scale, cudaStream_t s, long long num_slots = 0,
+                           int* status = nullptr);
 
 // ---- attention_fwd.cu
 // Causal variable-length attention forward on tcgen05. q/k/v are bf16 [rows, heads, 128] views with row pitches

@@ -20,6 +20,11 @@
 //     part of it has to start at zero: each call overwrites every partial slot before it reads it. Two
 //     calls whose kernels may overlap on the GPU (different streams, no ordering) race on the array;
 //     order them on one stream or with events.
+//   * seq_lens and block_table are read on the device and are not trusted: a length below zero or beyond
+//     max_pages * page_size is clamped (status 8), and a page id that is negative or whose last row lies
+//     beyond num_slots is treated as a page of zeros instead of being read (status 9). `status` is an
+//     optional device int the kernel writes the first such code into (pass NULL to ignore); the host
+//     decides when to read it.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -38,11 +43,13 @@ enum {
 
 // q [B, Hq, 128] bf16; k_cache / v_cache [slots, Hk, 128] bf16 with slot = page * page_size + offset;
 // block_table [B, max_pages] int32; seq_lens [B] int32; out [B, Hq, 128] bf16. Hq / Hk in {1, 2, 4, 8}.
+// num_slots = rows of k_cache / v_cache (pages * page_size); status = device int or NULL (see above).
 // Asynchronous on `stream`. Returns MB_NOALLOC_OK or one of the codes above;
 // mb_noalloc_last_error() describes the most recent failure of the calling thread.
 __attribute__((visibility("default"))) int mb_paged_decode_attention_noalloc(
     const void* q, const void* k_cache, const void* v_cache, const int* block_table, const int* seq_lens, void* out,
-    int B, int Hq, int Hk, int page_size, int max_pages, int num_splits, float scale, cudaStream_t stream);
+    int B, int Hq, int Hk, int page_size, int max_pages, int num_splits, float scale, long long num_slots, int* status,
+    cudaStream_t stream);
 
 __attribute__((visibility("default"))) const char* mb_noalloc_last_error(void);
 

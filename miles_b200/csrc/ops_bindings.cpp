@@ -154,6 +154,14 @@ void split_master_cut(const at::Tensor& master, at::Tensor& p, at::Tensor& lo) {
   mb::split_master_cut(master.data_ptr<float>(), p.data_ptr(), lo.data_ptr(), p.numel(), cur_stream());
 }
 
+void init_normal(at::Tensor& out, int64_t key, double std, int64_t first) {
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous(), "init_normal needs a contiguous CUDA tensor");
+  TORCH_CHECK(out.scalar_type() == at::kFloat || out.scalar_type() == at::kBFloat16, "init_normal fills fp32 or bf16");
+  const c10::cuda::CUDAGuard guard(out.device());
+  mb::init_normal(out.data_ptr(), out.scalar_type() == at::kFloat, out.numel(), static_cast<unsigned long long>(key), first,
+                  static_cast<float>(std), cur_stream());
+}
+
 void sumsq(const at::Tensor& g, at::Tensor& out) {
   TORCH_CHECK(g.is_cuda() && g.is_contiguous(), "bad gradient");
   CHECK_F32(out);
@@ -279,6 +287,7 @@ void register_elementwise(pybind11::module_& m) {
   m.def("split_master_join", &split_master_join);
   m.def("split_master_cut", &split_master_cut);
   m.def("sumsq", &sumsq);
+  m.def("init_normal", &init_normal, pybind11::arg("out"), pybind11::arg("key"), pybind11::arg("std"), pybind11::arg("first") = 0);
   m.def("moe_router_topk", &moe_router_topk);
   m.def("moe_router_bwd", &moe_router_bwd);
   m.def("moe_build_permutation", &moe_build_permutation);

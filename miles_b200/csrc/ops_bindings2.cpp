@@ -38,7 +38,7 @@ void sample_rows(const at::Tensor& logits, const c10::optional<at::Tensor>& temp
 // q [B, Hq, 128]; caches [slots, Hk, 128]; block_table [B, max_pages]; out [B, Hq, 128]; scratch fp32.
 void paged_decode_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
                             const at::Tensor& block_table, const at::Tensor& seq_lens, at::Tensor& out, at::Tensor& scratch,
-                            int64_t page_size, int64_t num_splits, double scale) {
+                            int64_t page_size, int64_t num_splits, double scale, const c10::optional<at::Tensor>& status) {
   CHECK_BF16(q); CHECK_BF16(k_cache); CHECK_BF16(v_cache); CHECK_I32(block_table); CHECK_I32(seq_lens); CHECK_BF16(out); CHECK_F32(scratch);
   const int B = q.size(0), Hq = q.size(1), Hk = k_cache.size(1);
   TORCH_CHECK(q.size(2) == 128 && k_cache.size(2) == 128, "head_dim must be 128");
@@ -46,9 +46,15 @@ void paged_decode_attention(const at::Tensor& q, const at::Tensor& k_cache, cons
   TORCH_CHECK(Hq % Hk == 0 && (G == 1 || G == 2 || G == 4 || G == 8), "unsupported GQA group size");
   TORCH_CHECK(scratch.numel() >= static_cast<int64_t>(B) * Hq * num_splits * 130, "scratch too small");
   const c10::cuda::CUDAGuard guard(q.device());
-  mb::paged_decode_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr<int>(),
-                             seq_lens.data_ptr<int>(), out.data_ptr(), scratch.data_ptr<float>(), B, Hq, Hk, page_size,
-                             block_table.size(1), num_splits, scale, cur_stream());
+  int* st = nullptr;
+  if (status.has_value() && status->defined()) {
+    CHECK_I32((*status));
+    st = status->data_ptr<int>();
+  }
+  const int e = mb::paged_decode_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr<int>(),
+                                           seq_lens.data_ptr<int>(), out.data_ptr(), scratch.data_ptr<float>(), B, Hq, Hk,
+                                           page_size, block_table.size(1), num_splits, scale, cur_stream(), k_cache.size(0), st);
+  TORCH_CHECK(e == 0, "paged_decode_attention launch failed: ", cudaGetErrorString(static_cast<cudaError_t>(e)));
 }
 
 // q [Tq, Hq, 128], k/v [Tkv, Hk, 128] (last dim contiguous, arbitrary row pitch); tiles int32 [n, 4].
@@ -212,7 +218,9 @@ void register_more(pybind11::module_& m) {
   register_comm(m);
   register_mx(m);
   m.def("sample_rows", &sample_rows);
-  m.def("paged_decode_attention", &paged_decode_attention);
+  m.def("paged_decode_attention", &paged_decode_attention, pybind11::arg("q"), pybind11::arg("k_cache"), pybind11::arg("v_cache"),
+        pybind11::arg("block_table"), pybind11::arg("seq_lens"), pybind11::arg("out"), pybind11::arg("scratch"),
+        pybind11::arg("page_size"), pybind11::arg("num_splits"), pybind11::arg("scale"), pybind11::arg("status") = pybind11::none());
   m.def("flash_attn_fwd", &flash_attn_fwd);
   m.def("small_gemv", &small_gemv);
   m.def("router_small", &router_small);

@@ -362,10 +362,16 @@ class Engine:
             idx = torch.arange(n)
             slots.append(pg[idx // ps] * ps + idx % ps)
             cu.append(cu[-1] + n)
-        tokens = torch.tensor(toks, dtype=torch.int32, device=dev)
-        positions = torch.tensor(pos, dtype=torch.int32, device=dev)
-        slot_mapping = torch.cat(slots).to(torch.int32).to(dev)
-        cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+        # one pinned host staging buffer per prefill: tokens | positions | slot mapping | cu_seqlens, one H2D copy
+        n_tok = len(toks)
+        host = torch.empty(3 * n_tok + len(cu), dtype=torch.int32, pin_memory=self.on_gpu)
+        host[:n_tok] = torch.tensor(toks, dtype=torch.int32)
+        host[n_tok:2 * n_tok] = torch.tensor(pos, dtype=torch.int32)
+        host[2 * n_tok:3 * n_tok] = torch.cat(slots).to(torch.int32)
+        host[3 * n_tok:] = torch.tensor(cu, dtype=torch.int32)
+        staged = host.to(dev, non_blocking=True)
+        tokens, positions, slot_mapping, cu_t = (staged[:n_tok], staged[n_tok:2 * n_tok], staged[2 * n_tok:3 * n_tok],
+                                                 staged[3 * n_tok:])
         max_len = max(b - a for a, b in zip(cu[:-1], cu[1:]))
         meta = InferMeta(True, cu_t, max_len, slot_mapping, page_size=ps)
         want_routes = any(r.return_routed_experts for r in batch) and self.cfg.is_moe

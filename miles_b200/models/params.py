@@ -204,10 +204,32 @@ class ParamStore:
     # ------------------------------------------------------------------ init / access
     @torch.no_grad()
     def init_weights(self, std: float = 0.02, seed: int = 1234) -> None:
-        gen = torch.Generator(device=self.device)
-        if self.tp_size > 1:
-            self._gshapes = {g.name: g.shape for g in build_specs(self.global_cfg, self.ep_size)}
+        """N(0, std) for matrices, ones for norm weights, zeros for biases. Every value is a function of
+        (seed, parameter name, global expert index, element index in the unsharded tensor): any expert-, tensor- or
+        pipeline-parallel factorisation builds the same model. On a CUDA device the values come from the extension's
+        counter-based generator (one launch per tensor); on the CPU from seeded ``torch.Generator`` streams."""
+        C = None
+        if self.device.type == "cuda":
+            from ..ops import _ext
+
+            C = _ext.load(required=False)
+        gen = torch.Generator(device=self.device) if C is None else None
+        gshapes = {g.name: g.shape for g in build_specs(self.global_cfg, self.ep_size)} if self.tp_size > 1 else {}
         el = self.cfg.num_experts // self.ep_size if self.cfg.is_moe else 0
+
+        def draw(dst: torch.Tensor, key: str) -> None:
+            """Fill the contiguous view ``dst`` (a whole logical tensor) with N(0, std) under ``key``."""
+            k = _seed_for(seed, key)
+            if C is not None:
+                C.init_normal(dst, k, std)
+                return
+            gen.manual_seed(k)
+            flat = dst.view(-1)
+            chunk = 1 << 26
+            for a in range(0, flat.numel(), chunk):
+                b = min(a + chunk, flat.numel())
+                flat[a:b].copy_(torch.empty(b - a, dtype=torch.float32, device=self.device).normal_(0.0, std, generator=gen))
+
         for s in self.specs:
             p = self.params[s.name]
             if s.init == "ones":
@@ -217,32 +239,15 @@ class ParamStore:
             elif s.group == "expert":
                 # one stream per *global* expert so that any EP factorisation builds the same model
                 for le in range(el):
-                    ge = self.ep_rank * el + le
-                    gen.manual_seed(_seed_for(seed, f"{s.name}:{ge}"))
-                    p[le].copy_(torch.empty(p[le].shape, dtype=torch.float32, device=self.device).normal_(0.0, std, generator=gen))
+                    draw(p[le], f"{s.name}:{self.ep_rank * el + le}")
             elif self.tp_size > 1 and is_tp_sharded(s.name):
-                # draw the full tensor of the global model and keep this rank's shard: any TP factorisation builds
-                # the same model
-                gshape = next(g.shape for g in build_specs(self.global_cfg, self.ep_size) if g.name == s.name) \
-                    if not hasattr(self, "_gshapes") else self._gshapes[s.name]
-                gen.manual_seed(_seed_for(seed, s.name))
-                n = 1
-                for d in gshape:
-                    n *= d
-                full = torch.empty(n, dtype=torch.float32, device=self.device)
-                chunk = 1 << 26
-                for a in range(0, n, chunk):
-                    b = min(a + chunk, n)
-                    full[a:b].normal_(0.0, std, generator=gen)
-                p.copy_(tp_slice(self.global_cfg, s.name, full.view(gshape), self.tp_size, self.tp_rank))
+                # draw the full tensor of the global model and keep this rank's shard
+                full = torch.empty(gshapes[s.name], dtype=torch.float32, device=self.device)
+                draw(full, s.name)
+                p.copy_(tp_slice(self.global_cfg, s.name, full, self.tp_size, self.tp_rank))
                 del full
             else:
-                gen.manual_seed(_seed_for(seed, s.name))
-                chunk = 1 << 26
-                flat = p.view(-1)
-                for a in range(0, flat.numel(), chunk):
-                    b = min(a + chunk, flat.numel())
-                    flat[a:b].copy_(torch.empty(b - a, dtype=torch.float32, device=self.device).normal_(0.0, std, generator=gen))
+                draw(p, s.name)
 
     def __getitem__(self, name: str) -> torch.Tensor:
         return self.params[name]

@@ -27,7 +27,7 @@ def _lib():
     lib = ctypes.CDLL(str(_build.TARGET))
     fn = lib.mb_paged_decode_attention_noalloc
     fn.restype = ctypes.c_int
-    fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 6 + [ctypes.c_float, ctypes.c_void_p]
+    fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 6 + [ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p]
     lib.mb_noalloc_last_error.restype = ctypes.c_char_p
     return lib, fn
 
@@ -58,13 +58,24 @@ def test_no_alloc_entry_point_matches_regular_path_twice(ext):
         scratch = torch.empty(B * Hq * splits * 130, dtype=torch.float32, device=q.device)
         ext.paged_decode_attention(q, kc, vc, bt, sl, want, scratch, ps, splits, 128 ** -0.5)
         got = torch.full_like(q, float("nan"))
-        before = torch.cuda.memory_allocated()
-        rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), sl.data_ptr(), got.data_ptr(), B, Hq, Hk, ps,
-                max_pages, splits, ctypes.c_float(128 ** -0.5), ctypes.c_void_p(stream))
+        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+
+        def call():
+            return fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), sl.data_ptr(), got.data_ptr(), B, Hq, Hk, ps,
+                      max_pages, splits, ctypes.c_float(128 ** -0.5), kc.shape[0], status.data_ptr(), ctypes.c_void_p(stream))
+
+        rc = call()  # also the warm-up: the first call on a device looks up the scratch address
         assert rc == 0, lib.mb_noalloc_last_error().decode()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
-        assert torch.isfinite(got.float()).all()
+        # neither torch's allocator nor the driver may hand out memory during a call: the caching allocator's
+        # counter cannot see a raw cudaMalloc, the driver's free-byte count can
+        before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
+        got.fill_(float("nan"))
+        rc = call()
+        assert rc == 0, lib.mb_noalloc_last_error().decode()
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == before and torch.cuda.mem_get_info()[0] == free_before
+        assert torch.isfinite(got.float()).all() and status.item() == 0
         assert (got.float() - want.float()).abs().max().item() < 2e-2
 
 
@@ -74,9 +85,37 @@ def test_no_alloc_entry_point_rejects_oversized_requests(ext):
     out = torch.zeros_like(q)
     splits = SCRATCH_FLOATS // (130 * 2 * 32) + 1
     rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), sl.data_ptr(), out.data_ptr(), 2, 32, 4, ps, max_pages,
-            splits, ctypes.c_float(0.1), ctypes.c_void_p(0))
+            splits, ctypes.c_float(0.1), kc.shape[0], None, ctypes.c_void_p(0))
     assert rc == -2 and b"exceed" in lib.mb_noalloc_last_error()
     torch.cuda.synchronize()
     assert out.abs().sum().item() == 0
     assert fn(None, kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), sl.data_ptr(), out.data_ptr(), 2, 32, 4, ps, max_pages, 1,
-              ctypes.c_float(0.1), ctypes.c_void_p(0)) == -1
+              ctypes.c_float(0.1), kc.shape[0], None, ctypes.c_void_p(0)) == -1
+
+
+def test_no_alloc_entry_point_does_not_follow_bad_tables(ext):
+    """Lengths and page ids come from device memory a C host filled. A length past the block-table row is clamped and
+    a page id outside the cache reads as zeros; the kernel records which happened and touches no address outside the
+    cache (the call returns normally and the next call works)."""
+    lib, fn = _lib()
+    q, kc, vc, bt, sl, ps, max_pages = _case(4, 2, [200, 300])
+    out = torch.zeros_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), sl.data_ptr(), out.data_ptr(), 2, 32, 4, ps, max_pages,
+                4, ctypes.c_float(128 ** -0.5), kc.shape[0], status.data_ptr(), ctypes.c_void_p(stream))
+        torch.cuda.synchronize()
+        return rc
+
+    good_bt = bt.clone()
+    bt[1, 2] = 10 ** 6  # far outside the cache
+    assert call() == 0 and status.item() == 9 and torch.isfinite(out.float()).all()
+    bt.copy_(good_bt)
+    status.zero_()
+    sl[0] = max_pages * ps + 5000  # longer than its block-table row
+    assert call() == 0 and status.item() == 8 and torch.isfinite(out.float()).all()
+    sl[0] = 200
+    status.zero_()
+    assert call() == 0 and status.item() == 0
