@@ -149,7 +149,10 @@ def main() -> None:
         "--rollout-max-prompt-len", str(ns.prompt_len), "--rollout-max-response-len", str(ns.max_response_len),
         "--rollout-temperature", "1.0", "--rm-type", "parity", "--advantage-estimator", "grpo",
         "--eps-clip", "0.2", "--eps-clip-high", "0.28", "--lr", "1e-6", "--weight-decay", "0.1", "--adam-beta1", "0.9",
-        "--adam-beta2", "0.98", "--clip-grad", "1.0", "--use-dynamic-batch-size", "--max-tokens-per-gpu", str(ns.max_tokens_per_gpu),
+        "--adam-beta2", "0.98", "--clip-grad", "1.0",
+        # fp32 master weights with 16-bit moments (the reference's precision-aware optimizer): the one optimizer
+        # format that fits this model at every GPU count of the run, down to a single 192 GB device
+        "--use-precision-aware-optimizer", "--exp-avg-dtype", "bf16", "--exp-avg-sq-dtype", "bf16", "--use-dynamic-batch-size", "--max-tokens-per-gpu", str(ns.max_tokens_per_gpu),
         "--actor-num-nodes", "1", "--actor-num-gpus-per-node", str(world), "--colocate",
         "--expert-model-parallel-size", str(world if (ns.tp == 1 and ns.pp == 1) else 1), "--tensor-model-parallel-size", str(ns.tp),
         "--pipeline-model-parallel-size", str(ns.pp),
@@ -224,9 +227,9 @@ def main() -> None:
     h2d0, d2h0 = copied()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     cfg = loop.actor.cfg
-    dtype = ("bf16 compute; fp32 master weights (bf16 weight + 16-bit remainder), fp32 Adam moments, "
-             "fp32 dense / bf16 expert gradient accumulation")
-    if loop.actor.plan.get("state") != "fp32" or not loop.actor.plan.get("master"):
+    dtype = ("bf16 compute; fp32 master weights (bf16 weight + 16-bit remainder), bf16 Adam moments (precision-aware "
+             "optimizer), fp32 dense / bf16 expert gradient accumulation")
+    if loop.actor.plan.get("state") != "bf16" or not loop.actor.plan.get("master"):
         dtype = f"bf16 compute; optimizer plan {loop.actor.plan.get('name')}"
     if ns.rollout_quantization != "none":
         dtype += f"; {ns.rollout_quantization} rollout GEMMs"

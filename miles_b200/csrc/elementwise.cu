@@ -563,18 +563,35 @@ __global__ void init_normal_kernel(T* __restrict__ out, long long n, unsigned lo
   }
 }
 
-// Sum of squares of a flat buffer into a single fp32 accumulator (for the global grad norm).
+// Sum of squares of a flat buffer, added to a single fp32 accumulator (for the global grad norm), in two
+// stages with a fixed summation order: every block writes its partial sum, one block adds the partials in index
+// order. The same gradients therefore always give the same norm bits (an atomicAdd per block would not), which
+// keeps the clip coefficient, and with it a whole training step, reproducible.
 template <typename GT>
-__global__ void sumsq_kernel(const GT* __restrict__ g, long long n, float* __restrict__ out) {
+__global__ void sumsq_partial_kernel(const GT* __restrict__ g, long long n, float* __restrict__ partial) {
   __shared__ float red[32];
   float s = 0.f;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const float x = static_cast<float>(g[i]);
+  const long long n8 = n / 8;
+  for (long long i8 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i8 < n8;
+       i8 += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float x[8];
+    adam_load8<GT>(g + i8 * 8, x);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += x[j] * x[j];
+  }
+  if (blockIdx.x == 0 && threadIdx.x < n - n8 * 8) {
+    const float x = static_cast<float>(g[n8 * 8 + threadIdx.x]);
     s += x * x;
   }
   s = block_sum<256>(s, red);
-  if (threadIdx.x == 0) atomicAdd(out, s);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+__global__ void sumsq_final_kernel(const float* __restrict__ partial, int n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += 256) s += partial[i];
+  s = block_sum<256>(s, red);
+  if (threadIdx.x == 0) *out += s;
 }
 
 int grid_for(long long work_items, int threads, int cap = 148 * 8) {
@@ -676,11 +693,15 @@ void init_normal(void* out, bool fp32, long long n, unsigned long long key, long
   else init_normal_kernel<bf16><<<grid, 256, 0, s>>>(static_cast<bf16*>(out), n, key, first, std);
 }
 
-void sumsq(const void* g, bool g_fp32, long long n, float* out, cudaStream_t s) {
+int sumsq_num_partials(long long n) { return grid_for((n + 7) / 8, 256, 148 * 4); }
+
+// `partial`: fp32 scratch of sumsq_num_partials(n) elements; g must be 16-byte aligned.
+void sumsq(const void* g, bool g_fp32, long long n, float* partial, float* out, cudaStream_t s) {
   if (n <= 0) return;
-  const int grid = grid_for(n, 256, 148 * 8);
-  if (g_fp32) sumsq_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(g), n, out);
-  else sumsq_kernel<bf16><<<grid, 256, 0, s>>>(static_cast<const bf16*>(g), n, out);
+  const int grid = sumsq_num_partials(n);
+  if (g_fp32) sumsq_partial_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(g), n, partial);
+  else sumsq_partial_kernel<bf16><<<grid, 256, 0, s>>>(static_cast<const bf16*>(g), n, partial);
+  sumsq_final_kernel<<<1, 256, 0, s>>>(partial, grid, out);
 }
 
 }  // namespace mb

@@ -28,7 +28,8 @@ void adam_step(void* p, float* master, void* lo, const void* g, bool g_fp32, voi
                const float* skip_flag, cudaStream_t s);
 void split_master_join(const void* p, const void* lo, float* out, long long n, cudaStream_t s);
 void split_master_cut(const float* master, void* p, void* lo, long long n, cudaStream_t s);
-void sumsq(const void* g, bool g_fp32, long long n, float* out, cudaStream_t s);
+int sumsq_num_partials(long long n);
+void sumsq(const void* g, bool g_fp32, long long n, float* partial, float* out, cudaStream_t s);
 // out[i] = std * N(key, first + i), a counter-based generator: independent of how the logical tensor is sharded.
 void init_normal(void* out, bool fp32, long long n, unsigned long long key, long long first, float std, cudaStream_t s);
 

@@ -166,7 +166,10 @@ void sumsq(const at::Tensor& g, at::Tensor& out) {
   TORCH_CHECK(g.is_cuda() && g.is_contiguous(), "bad gradient");
   CHECK_F32(out);
   const c10::cuda::CUDAGuard guard(g.device());
-  mb::sumsq(g.data_ptr(), g.scalar_type() == at::kFloat, g.numel(), out.data_ptr<float>(), cur_stream());
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(g.data_ptr()) & 15) == 0, "sumsq needs a 16-byte aligned buffer");
+  TORCH_CHECK(g.scalar_type() == at::kFloat || g.scalar_type() == at::kBFloat16, "sumsq takes fp32 or bf16");
+  at::Tensor partial = at::empty({mb::sumsq_num_partials(g.numel())}, out.options());
+  mb::sumsq(g.data_ptr(), g.scalar_type() == at::kFloat, g.numel(), partial.data_ptr<float>(), out.data_ptr<float>(), cur_stream());
 }
 
 // ---------------------------------------------------------------- MoE

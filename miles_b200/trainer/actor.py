@@ -43,29 +43,62 @@ def replica_wanted(args, ep_size: int) -> bool:
     return bool(v)
 
 
-def choose_memory_plan(total_bytes: int, dense_params: int, expert_params: int, reserve_frac: float = 0.22,
-                       extra_resident_bytes: int = 0, kv_bytes: int = 0, dp_size: int = 1) -> dict:
-    """Where the optimizer state of the expert group lives. The numerics are the same at every size:
-    bf16 weights whose fp32 master is kept as (bf16 weight, signed 16-bit remainder), fp32 Adam moments, fp32
-    gradient accumulation for the replicated parameters and bf16 for the experts (that buffer shares its bytes
-    with the KV cache of the colocated engine). Per expert parameter that is 2 B of weight on the device and 10 B
-    of optimizer state; the plan keeps the share of those 10 B that fits next to everything else on the device
-    and streams the rest through pinned host memory every optimizer step.
+def choose_memory_plan(total_bytes: int, dense_params: int, expert_params: int, reserve_frac: float = 0.16,
+                       extra_resident_bytes: int = 0, kv_bytes: int = 0, dp_size: int = 1, state: str = "fp32",
+                       host_bytes: Optional[int] = None) -> dict:
+    """Where the optimizer state of the expert group lives. The numerics do not depend on the placement:
+    bf16 weights whose fp32 master is kept as (bf16 weight, signed 16-bit remainder), Adam moments in ``state``
+    precision (fp32 like the reference's default optimizer, or bf16 like its precision-aware optimizer), fp32
+    gradient accumulation for the replicated parameters and bf16 for the experts (that buffer shares its bytes with
+    the KV cache of the colocated engine). Per expert parameter that is 2 B of weight on the device and 2 + 2 x
+    moment-size bytes of optimizer state; the plan keeps the share of the state that fits next to everything else
+    on the device and streams the rest through pinned host memory every optimizer step.
 
     ``reserve_frac`` of the device is left for activations, exchange buffers and the allocator;
     ``extra_resident_bytes`` is whatever else will stay resident (e.g. a full expert replica for the engine);
     ``kv_bytes`` the KV pool the engine will want (it shares the expert-gradient arena, so the larger of the two
-    counts); the replicated parameters' state is partitioned over ``dp_size`` ranks."""
-    state = expert_params * 10
-    dense = dense_params * (2 + 4) + dense_params * 10 // max(dp_size, 1)
+    counts); the replicated parameters' state is partitioned over ``dp_size`` ranks; ``host_bytes`` is the pinned
+    host memory this rank may take (None: unknown, not checked). Raises when device plus host cannot hold the state:
+    nothing is silently degraded."""
+    msize = 4 if state == "fp32" else 2
+    bpp = 2 + 2 * msize
+    state_bytes = expert_params * bpp
+    dense = dense_params * (2 + 4) + dense_params * bpp // max(dp_size, 1)
     resident = dense + expert_params * 2 + max(int(kv_bytes), expert_params * 2) + int(extra_resident_bytes)
     room = int(total_bytes * (1.0 - reserve_frac)) - resident
-    plan = dict(expert_grad="bf16", state="fp32", master=True, offload=False, resident_frac=1.0, name="fp32-master")
-    if state > room:
-        frac = max(0.0, min(1.0, room / max(state, 1)))
+    plan = dict(expert_grad="bf16", state=state, master=True, offload=False, resident_frac=1.0,
+                name=f"fp32 master, {state} moments")
+    if state_bytes > room:
+        frac = max(0.0, min(1.0, room / max(state_bytes, 1)))
         frac = int(frac * 64) / 64.0  # whole chunks, rounded down
-        plan.update(offload=True, resident_frac=frac, name="fp32-master, %d%% of the expert state streamed from host" % round(100 * (1 - frac)))
+        on_host = int(state_bytes * (1 - frac))
+        if host_bytes is not None and on_host > host_bytes:
+            raise MemoryError(
+                f"optimizer state of {state_bytes / 1e9:.0f} GB ({bpp} B per expert parameter, {state} moments): "
+                f"{state_bytes * frac / 1e9:.0f} GB fit on the device, the remaining {on_host / 1e9:.0f} GB exceed the "
+                f"{host_bytes / 1e9:.0f} GB of host memory this rank may pin. Use more GPUs"
+                + (", or --use-precision-aware-optimizer --exp-avg-dtype bf16 --exp-avg-sq-dtype bf16" if state == "fp32" else ""))
+        plan.update(offload=True, resident_frac=frac, name=plan["name"] + ", %d%% of the expert state streamed from host" % round(100 * (1 - frac)))
     return plan
+
+
+def host_memory_per_rank(local_world: int) -> Optional[int]:
+    """Pinned host bytes one rank may take: 80 % of what is available now (the cgroup limit if that is lower),
+    divided among the ranks of this node. None when it cannot be read."""
+    try:
+        import psutil
+
+        avail = psutil.virtual_memory().available
+    except Exception:
+        return None
+    try:
+        txt = open("/sys/fs/cgroup/memory.max").read().strip()
+        if txt.isdigit():
+            cur = int(open("/sys/fs/cgroup/memory.current").read().strip())
+            avail = min(avail, int(txt) - cur)
+    except Exception:
+        pass
+    return int(avail * 0.8) // max(local_world, 1)
 
 
 def wanted_kv_bytes(args, cfg, n_rep: int) -> int:
@@ -189,13 +222,15 @@ class TrainActor:
             if colocated:
                 kv = min(wanted_kv_bytes(a, self.cfg, self.ps.dp_cp.size * self.ps.pp.size),
                          int(total * float(getattr(a, "sglang_mem_fraction_static", 0.7))))
-            plan = choose_memory_plan(total, dense, expert, extra_resident_bytes=extra, kv_bytes=kv, dp_size=self.ps.dp_cp.size)
+            # moments: fp32 unless the precision-aware optimizer flags ask for 16 bits
+            state = "fp32"
+            if getattr(a, "use_precision_aware_optimizer", False) or a.exp_avg_dtype != "fp32" or a.exp_avg_sq_dtype != "fp32":
+                state = a.exp_avg_dtype if a.exp_avg_dtype in ("bf16", "fp32") else "bf16"
+            local_world = int(os.environ.get("LOCAL_WORLD_SIZE", self.ps.world_size))
+            plan = choose_memory_plan(total, dense, expert, extra_resident_bytes=extra, kv_bytes=kv, dp_size=self.ps.dp_cp.size,
+                                      state=state, host_bytes=host_memory_per_rank(local_world))
         else:
             plan = dict(expert_grad="fp32", state="fp32", master=False, offload=False, resident_frac=1.0, name="cpu")
-        # explicit flags override the automatic plan
-        if getattr(a, "use_precision_aware_optimizer", False) or a.exp_avg_dtype != "fp32" or a.exp_avg_sq_dtype != "fp32":
-            plan["state"] = a.exp_avg_dtype if a.exp_avg_dtype in _DT else "bf16"
-            plan["name"] += f", {plan['state']} moments"
         if getattr(a, "main_params_dtype", "fp32") != "fp32":
             plan["master"] = False
             plan["name"] += ", no fp32 master"

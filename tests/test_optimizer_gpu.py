@@ -91,7 +91,8 @@ def test_split_master_roundtrip_and_skip_flag(ext):
 
 def test_flat_adam_streamed_state_equals_resident(ext):
     """FlatAdam with the expert group's state streamed through pinned host memory (partly resident) must produce
-    the same bits as the all-resident optimizer."""
+    the same bits as the all-resident optimizer (the gradient norm is reduced in a fixed order, so the clip
+    coefficient is reproducible too)."""
     from miles_b200.models import ParamStore, get_config
     from miles_b200.trainer.optimizer import FlatAdam, OptimConfig
 
