@@ -149,6 +149,31 @@ void ep_row_ptrs(const int* row_src, const int* meta, const EpPeers& peers, int 
 void ep_return(const void* yp, const int* recv_dest_row, const int* meta, const int* counts, const EpPeers& peers, int me,
                int nranks, int cap, int H, unsigned long long* ctrl, int* status, cudaStream_t s);
 
+// ---- ep_decode.cu (low-latency expert-parallel exchange for decode steps)
+struct EpLLPeers {
+  char* base[kMaxPeers];  // every rank's mapping of the symmetric region (own rank included)
+};
+struct EpLLLayout {       // identical on all ranks; offsets in bytes from the region base
+  int R, Bm, H, K;        // ranks, max rows per rank and step, hidden size, experts per token
+  long long off_xg;       // [R][Bm][H] bf16   gathered (normalised) rows, by source rank
+  long long off_ig;       // [R][Bm][K] int32  their expert ids (-1: padding row)
+  long long off_wg;       // [R][Bm][K] fp32   their gate weights
+  long long off_yb;       // [R][Bm][H] bf16   partial sums returned by each owner rank for this rank's rows
+  long long off_flag_a;   // [R] u64 (epoch << 32 | rows)  arrival of a source's rows
+  long long off_flag_b;   // [R] u64 (epoch << 32)         arrival of an owner's partial sums
+};
+size_t ep_ll_plan_smem(const EpLLLayout& L, int E);
+int ep_ll_send(const void* x, const void* ln_w, float eps, const float* logits, const int* active, const EpLLPeers& peers,
+               const EpLLLayout& L, int me, int T, int E, bool renorm, int* ids_out, float* w_out, unsigned long long* ctrl,
+               cudaStream_t s);
+int ep_ll_plan(char* local, const EpLLLayout& L, int me, int E, int max_rows, int max_tiles, int align, int* src_rows,
+               int* counts, int* offsets, int* dest_row, int* row_src, int* tiles, int* totals, unsigned long long* ctrl,
+               unsigned long long wait_ns, int* status, cudaStream_t s);
+void ep_ll_return(const void* yp, const int* dest_row, const int* src_rows, const EpLLPeers& peers, const EpLLLayout& L, int me,
+                  int rows_hint, unsigned long long* ctrl, cudaStream_t s);
+void ep_ll_combine(const char* local, const EpLLLayout& L, const int* ids, const int* active, const void* residual, void* out,
+                   int T, int E, unsigned long long* ctrl, unsigned long long wait_ns, int* status, cudaStream_t s);
+
 // ---- dp_adam.cu (gradient reduce-scatter + partitioned Adam + parameter all-gather over peer memory)
 struct DpPeers {
   void* grad[kMaxPeers];                  // fp32 flat gradient buffers of all data-parallel ranks
