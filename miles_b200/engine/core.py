@@ -311,12 +311,23 @@ class Engine:
         before = set(self.finished)
         admitted = [] if self.paused else self._admit()
         local = 2 if admitted else (1 if ((self.running and not self.paused) or self._pending is not None) else 0)
-        mode = self.sync.agree(local) if self.sync is not None else local
+        bucket = None
+        if self.sync is not None:
+            # one host agreement per iteration: the kind of iteration and, for a decode step, the row bound every rank
+            # pads its batch to (the expert-parallel exchange needs the same bound everywhere)
+            want = self._bucket(max(len(self.running), 1)) if (local == 1 and not self.paused) else 0
+            mode, bucket = self.sync.agree(local, want)
+            bucket = max(bucket, 1)
+        else:
+            mode = local
         self.last_mode = mode
         if mode == 2:
             self._prefill(admitted)
         elif mode == 1:
-            self._decode()
+            if self.sync is not None:
+                self._decode_lockstep(bucket)
+            else:
+                self._decode()
         return [self.finished[r] for r in self.finished if r not in before]
 
     def drain(self) -> None:
@@ -500,7 +511,7 @@ class Engine:
         return True
 
     @torch.no_grad()
-    def _launch_decode(self, lookahead: int) -> Optional[dict]:
+    def _launch_decode(self, lookahead: int, bucket: Optional[int] = None) -> Optional[dict]:
         """Enqueue one decode step for the running set and the copies of its results into pinned host buffers.
         ``lookahead = 1``: the step *after* the one still in flight (same batch, device-side state already advances
         inside the captured step), launched before the host has looked at the previous step's tokens."""
@@ -513,7 +524,7 @@ class Engine:
         if not reqs and self.sync is None:
             return None
         n = len(reqs)
-        B = self._bucket(max(n, 1))
+        B = self._bucket(max(n, 1)) if bucket is None else max(int(bucket), self._bucket(max(n, 1)))
         same = (self._rows_B == B and len(self._rows) == n and all(a is b for a, b in zip(self._rows, reqs)))
         if not same:
             assert lookahead == 0, "a look-ahead step never changes the batch"
@@ -523,6 +534,11 @@ class Engine:
                 for j in range(before_pages.get(r.rid, 0), len(r.pages)):
                     self.d_block_table[i, j] = r.pages[j]
         want_routes = self.cfg.is_moe and any(r.return_routed_experts for r in reqs)
+        ll = getattr(self.ep_decode, "low_latency", False)
+        if ll:
+            # every rank replays the same graph for a row bound: routing is always recorded, padding rows are masked
+            want_routes = self.cfg.is_moe
+            self.ep_decode.set_step(B, self.d_active)
         saved_ep = getattr(self.model, "ep", None)
         if self.ep_decode is not None:
             self.model.ep = self.ep_decode
@@ -585,6 +601,59 @@ class Engine:
             if len(r.output_ids) + 1 >= limit or r.seq_len + 2 >= self.max_seq_len:
                 return False
         return True
+
+    def _can_launch_ahead(self, pend: dict, bucket: int) -> bool:
+        """Lockstep engines: may the next step be launched before the host has seen the step in flight? Only when
+        nothing about the batch can change: same requests, same row bound, nobody certain to stop, pages at hand."""
+        if not self.overlap_decode or self.paused or self.waiting or bucket != self._rows_B:
+            return False
+        reqs = pend["reqs"]
+        if len(reqs) != len(self.running) or any(a is not b for a, b in zip(reqs, self.running)):
+            return False
+        for r in reqs:
+            p = r.params
+            limit = p.max_new_tokens if p.forced_length is None else min(p.forced_length, p.max_new_tokens)
+            if len(r.output_ids) + 1 >= limit or r.seq_len + 2 >= self.max_seq_len:
+                return False
+        return self._grow_pages_ahead(1)
+
+    @torch.no_grad()
+    def _decode_lockstep(self, bucket: int) -> None:
+        """One decode iteration of a lockstep (expert-parallel) engine: exactly one step is launched per call on
+        every rank, with ``bucket`` rows (a rank without requests launches padding rows only), so that the ranks'
+        exchanges stay aligned; the step launched by the previous call is read back after the new launch whenever
+        the batch cannot have changed, which hides the host work and the agreement behind the GPU."""
+        prev, self._pending = self._pending, None
+        ahead = prev is not None and self._can_launch_ahead(prev, bucket)
+        if prev is not None and not ahead:
+            self._process_decode(prev)
+            prev = None
+        new = self._launch_decode(1 if ahead else 0, bucket=bucket)
+        if prev is not None:
+            self._process_decode(prev)
+        self._pending = new
+
+    def warm_up_decode_graphs(self) -> None:
+        """Capture the decode graph of every row bound now (all ranks of a lockstep group call this at the same
+        point): capturing runs a step twice, which a rank must not do on its own in the middle of a rollout."""
+        if not (self.use_cuda_graph and self.on_gpu) or self.kv_cache is None:
+            return
+        buckets = sorted({self._bucket(n) for n in range(1, self.max_running + 1)})
+        ll = getattr(self.ep_decode, "low_latency", False)
+        saved_ep = getattr(self.model, "ep", None)
+        for B in buckets:
+            self._upload_rows([], B)
+            if ll:
+                self.ep_decode.set_step(B, self.d_active)
+            if self.ep_decode is not None:
+                self.model.ep = self.ep_decode
+            try:
+                self._run_decode(B, self.cfg.is_moe if ll else False)
+            finally:
+                if self.ep_decode is not None:
+                    self.model.ep = saved_ep
+        torch.cuda.synchronize()
+        self._rows, self._rows_B = [], 0
 
     def _drain_pending(self) -> None:
         if self._pending is not None:
@@ -685,9 +754,10 @@ class LockstepSync:
 
         self.dist = dist
         self.group = group
-        self.buf = torch.zeros(1, dtype=torch.int32)
+        self.buf = torch.zeros(2, dtype=torch.int32)
 
-    def agree(self, mode: int) -> int:
-        self.buf[0] = mode
+    def agree(self, mode: int, bucket: int = 0) -> tuple:
+        """MAX over the ranks of (kind of iteration, rows wanted for a decode step)."""
+        self.buf[0], self.buf[1] = mode, bucket
         self.dist.all_reduce(self.buf, op=self.dist.ReduceOp.MAX, group=self.group)
-        return int(self.buf[0])
+        return int(self.buf[0]), int(self.buf[1])

@@ -158,7 +158,13 @@ class RLLoop:
             from .parallel.expert_parallel import ExpertParallel
 
             sync = LockstepSync(self.ps.gloo_world if self.ps.backend != "gloo" else None)
-            ep_decode = ExpertParallel(cfg, self.ps, fused=getattr(a, "fused_comm", True), max_tokens=max(max_running, 16))
+            if self.actor.on_gpu and getattr(a, "fused_comm", True) and max_running <= 256 and not self.actor.is_torch:
+                # decode steps: gather / partial-sum exchange with in-kernel flags (csrc/ep_decode.cu)
+                from .parallel.ep_decode import EpDecodeLL
+
+                ep_decode = EpDecodeLL(cfg, self.ps, max_rows=max(max_running, 8))
+            else:
+                ep_decode = ExpertParallel(cfg, self.ps, fused=getattr(a, "fused_comm", True), max_tokens=max(max_running, 16))
         quant = getattr(a, "rollout_quantization", "none")
         if quant != "none" and self.actor.on_gpu and not self.actor.is_torch:
             if engine_model is self.actor.model:
@@ -171,6 +177,8 @@ class RLLoop:
                              max_prefill_tokens=getattr(a, "engine_max_prefill_tokens", 16384), kv_mem_bytes=kv_bytes,
                              use_cuda_graph=not getattr(a, "sglang_disable_cuda_graph", False) and self.actor.on_gpu,
                              eos_token_id=getattr(self.tokenizer, "eos_token_id", None), kv_storage=kv_storage)
+        if sync is not None:
+            self.engine.warm_up_decode_graphs()  # lockstep ranks capture their decode graphs together
         self.client = EngineClient([self.engine], self.tokenizer)
         self.actor.connect_rollout_engines([self.engine])
         if self.actor.on_gpu and self.actor.opt is not None and self.actor.plan.get("offload"):

@@ -275,6 +275,8 @@ class B200Qwen3:
                 return self._layer_forward_small(i, x, positions, meta, kv_cache, record)
             # expert-parallel MoE: the attention half still takes the light kernels, the experts go through the exchange
             x2 = self._attn_small(i, x, positions, meta, kv_cache)
+            if getattr(self.ep, "low_latency", False):
+                return self.ep.moe_decode(self, i, x2, None, record)
             h2, _ = C.rmsnorm_fwd(x2, None, P[p + "ln2.weight"], cfg.rms_eps)
             self.launches += 1
             y, _ = self.moe_forward(i, h2, replay_ids, record, keep=False, residual=x2)
@@ -296,6 +298,9 @@ class B200Qwen3:
             att, _ = self.attention(q, k, self._v_view(qkv), cu)
         h2, _, x2 = self._o_proj_ln2(i, att.view(att.shape[0], -1), x)
         if cfg.layer_is_moe(i):
+            if (meta is not None and not meta.is_prefill and replay_ids is None and getattr(self.ep, "low_latency", False)
+                    and x.shape[0] <= self.ep.rows):
+                return self.ep.moe_decode(self, i, x2, h2, record)
             y, _ = self.moe_forward(i, h2, replay_ids, record, keep=False, residual=x2)
             return y
         gu = self.linear(h2, P[p + "mlp.gate_up.weight"])

@@ -24,3 +24,17 @@ def test_expert_parallel_matches_single_rank(mode):
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     _run(mode, 2)
+
+
+def test_low_latency_expert_parallel_decode():
+    """The decode exchange (gather rows at the expert owners, partial sums back): one layer against the single-rank
+    layer, then lockstep rollouts with uneven request counts checked by log-prob recomputation."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29733", os.path.join(here, "mp_ep_decode_check.py"), "check"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "EP_DECODE_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
