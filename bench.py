@@ -252,6 +252,10 @@ def main() -> None:
         dev_s, wall = float(t[0]), float(t[1])
         est = max(est * 0.5, dev_s / timed)
         note(f"timed step {timed - 1}: rollout {last.get('perf/rollout_time', 0):.1f}s train {last.get('perf/train_time', 0):.1f}s")
+        if loop.engine is not None and loop.engine.bucket_time:
+            note("decode ms/step by row bucket: " + ", ".join(f"{b}: {1e3 * t / max(n, 1):.2f} x{n}"
+                                                               for b, (t, n) in sorted(loop.engine.bucket_time.items())))
+            loop.engine.bucket_time = {}
         stop = timed >= ns.steps or (timed >= 2 and agree(float(left() < est * 1.1)) > 0)
         h2d, d2h = copied()
         if rank == 0:

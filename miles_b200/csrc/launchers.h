@@ -96,6 +96,15 @@ int flash_attn_fwd(const void* q, long long q_ld, const void* k, long long k_ld,
                    void* out, float* lse, const int* tiles, int num_tiles, long long Tq, long long Tkv, int Hq, int Hk,
                    int head_dim, float scale, int* status, cudaStream_t stream);
 const char* flash_attn_last_error();
+// attention_bwd.cu: causal varlen backward for self-attention over packed sequences (keys = queries' own tokens).
+// q, o, d_o [T, Hq, 128] (o and d_o contiguous), k, v [T, Hk, 128] (row pitches in elements); lse fp32 [Hq, T] from the
+// forward; blocks int32 [n, 4] = {first key row, keys (<= 128), position of the first key in its sequence, row one past
+// the sequence}; scratch fp32 [T*Hq*128 + 2*Hq*T]; dq [T, Hq, 128], dk / dv [T, Hk, 128] bf16 contiguous.
+int flash_attn_bwd(const void* q, long long q_ld, const void* k, long long k_ld, const void* v, long long v_ld, const void* o,
+                   const void* d_o, long long do_ld, const float* lse, const int* blocks, int num_blocks, long long T, int Hq,
+                   int Hk, int head_dim, float scale, float* scratch, void* dq, void* dk, void* dv, int* status,
+                   cudaStream_t stream);
+const char* flash_attn_bwd_last_error();
 
 // ---- decode_stream.cu / decode_small.cu (at most 8 tokens: persistent weight-streaming mma.sync kernel fed by
 // bulk asynchronous copies, RMSNorm folded in; `status` receives a code if a bounded wait gives up)

@@ -80,6 +80,34 @@ std::vector<at::Tensor> flash_attn_fwd(const at::Tensor& q, const at::Tensor& k,
   return {out, lse};
 }
 
+// Backward of the causal self-attention over packed sequences. Returns {dq, dk, dv}.
+std::vector<at::Tensor> flash_attn_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o,
+                                       const at::Tensor& d_o, const at::Tensor& lse, const at::Tensor& blocks, double scale,
+                                       const c10::optional<at::Tensor>& status) {
+  CHECK_I32(blocks);
+  for (const at::Tensor* t : {&q, &k, &v, &o, &d_o})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kBFloat16 && t->dim() == 3 && t->size(2) == 128 && t->stride(2) == 1 &&
+                    t->stride(1) == 128, "q/k/v/o/d_o must be bf16 [rows, heads, 128] with heads packed along each row");
+  TORCH_CHECK(o.is_contiguous() && d_o.is_contiguous(), "o and d_o must be contiguous");
+  CHECK_F32(lse);
+  const int64_t T = q.size(0), Hq = q.size(1), Hk = k.size(1);
+  TORCH_CHECK(k.size(0) == T && v.size(0) == T && o.size(0) == T && d_o.size(0) == T && o.size(1) == Hq && d_o.size(1) == Hq &&
+                  v.size(1) == Hk && lse.size(0) == Hq && lse.size(1) == T, "shape mismatch");
+  TORCH_CHECK(blocks.is_contiguous() && blocks.dim() == 2 && blocks.size(1) == 4, "blocks must be contiguous [n, 4]");
+  const c10::cuda::CUDAGuard guard(q.device());
+  at::Tensor dq = at::empty({T, Hq, 128}, q.options());
+  at::Tensor dk = at::empty({T, Hk, 128}, q.options()), dv = at::empty({T, Hk, 128}, q.options());
+  at::Tensor scratch = at::empty({T * Hq * 128 + 2 * Hq * T}, q.options().dtype(at::kFloat));
+  int* st = nullptr;
+  if (status.has_value()) { CHECK_I32((*status)); st = status->data_ptr<int>(); }
+  const int rc = mb::flash_attn_bwd(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), o.data_ptr(),
+                                    d_o.data_ptr(), d_o.stride(0), lse.data_ptr<float>(), blocks.data_ptr<int>(), blocks.size(0),
+                                    T, Hq, Hk, 128, scale, scratch.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                    st, cur_stream());
+  TORCH_CHECK(rc == 0, mb::flash_attn_bwd_last_error());
+  return {dq, dk, dv};
+}
+
 // ---- small-batch decode kernels (T <= 8)
 void small_gemv(const at::Tensor& x, const c10::optional<at::Tensor>& norm_w, double eps, const at::Tensor& W,
                 const c10::optional<at::Tensor>& residual, at::Tensor& out, const c10::optional<at::Tensor>& status) {
@@ -224,6 +252,7 @@ void register_more(pybind11::module_& m) {
         pybind11::arg("block_table"), pybind11::arg("seq_lens"), pybind11::arg("out"), pybind11::arg("scratch"),
         pybind11::arg("page_size"), pybind11::arg("num_splits"), pybind11::arg("scale"), pybind11::arg("status") = pybind11::none());
   m.def("flash_attn_fwd", &flash_attn_fwd);
+  m.def("flash_attn_bwd", &flash_attn_bwd);
   m.def("small_gemv", &small_gemv);
   m.def("router_small", &router_small);
   m.def("moe_small_up", &moe_small_up);

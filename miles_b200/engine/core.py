@@ -134,6 +134,10 @@ class Engine:
         self._graphs: dict = {}
         self._alloc_decode_buffers()
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "retracted": 0}
+        # host wall time and count of decode iterations per row bucket (the GPU is the bottleneck of a decode
+        # iteration, so this is the step latency by batch size): {bucket: [seconds, steps]}
+        self.bucket_time: dict = {}
+        self._t_last_decode = None
         self.d2h_bytes = 0  # bytes read back from the device (sampled tokens, log-probs, routing)
         self.h2d_bytes = 0
 
@@ -551,7 +555,7 @@ class Engine:
             return None
         par = self._parity
         self._parity ^= 1
-        pend = {"reqs": reqs, "n": n, "parity": par, "event": None, "routes": None}
+        pend = {"reqs": reqs, "n": n, "parity": par, "event": None, "routes": None, "bucket": B}
         if self.on_gpu:
             self.h_out[par, :n].copy_(self.d_out_tokens[:n], non_blocking=True)
             self.h_lp[par, :n].copy_(self.d_out_logprobs[:n], non_blocking=True)
@@ -576,6 +580,14 @@ class Engine:
         retracted or aborted after the step was launched ignores its row)."""
         if pend["event"] is not None:
             pend["event"].synchronize()
+        now = time.perf_counter()
+        if self._t_last_decode is not None and pend.get("bucket"):
+            bt = self.bucket_time.setdefault(pend["bucket"], [0.0, 0])
+            dt = now - self._t_last_decode
+            if dt < 0.5:  # a gap that long is a prefill or an idle period, not a decode step
+                bt[0] += dt
+                bt[1] += 1
+        self._t_last_decode = now
         n, par = pend["n"], pend["parity"]
         tok_l, lp_l = self.h_out[par, :n].tolist(), self.h_lp[par, :n].tolist()
         routes_c = pend["routes"]

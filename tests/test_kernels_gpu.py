@@ -251,3 +251,33 @@ def test_small_gemv_token_groups_vs_fp32(ext, T):
         ext.small_gemv(x, None, 0.0, W, res, out32, status)
         assert _rel(out32, ref + res.float()) < 2e-3
     assert status.item() == 0
+
+
+@pytest.mark.parametrize("lens,Hq,Hk", [([128], 4, 4), ([64], 2, 1), ([1, 7, 129, 300], 8, 2), ([1000, 24, 513], 4, 1),
+                                        ([2048, 777], 16, 2)])
+def test_flash_attention_bwd_vs_fp32(ext, lens, Hq, Hk):
+    """dQ / dK / dV of the tcgen05 backward against fp32 autograd of plain attention, element by element."""
+    from miles_b200.ops.attention import attention_backward_reference, build_bwd_blocks, build_tiles
+
+    torch.manual_seed(11)
+    T = sum(lens)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q = (torch.randn(T, Hq, 128, device=DEV) * 0.7).bfloat16()
+    # k and v as views of one fused buffer (the layout the model hands over): rows have a pitch beyond Hk * 128
+    kv = (torch.randn(T, 2 * Hk, 128, device=DEV) * 0.7).bfloat16()
+    k, v = kv[:, :Hk], kv[:, Hk:]
+    d_o = (torch.randn(T, Hq, 128, device=DEV) * 0.5).bfloat16()
+    scale = 128 ** -0.5
+    out, lse = ext.flash_attn_fwd(q, k, v, build_tiles(lens).to(DEV), scale, status)
+    dq, dk, dv = ext.flash_attn_bwd(q, k, v, out, d_o, lse, build_bwd_blocks(lens).to(DEV), scale, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    rq, rk, rv = attention_backward_reference(q, k, v, d_o, lens, scale)
+    for name, got, ref in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+        assert torch.isfinite(got.float()).all(), name
+        # bf16 P / dS operands: a few 1e-3 of the gradient's scale per element, never a wrong tile
+        tol = 2e-2 * ref.abs().max().item()
+        err = (got.float() - ref).abs()
+        assert err.max().item() < tol, (name, err.max().item(), tol)
+        rel = err.norm().item() / ref.norm().item()
+        assert rel < 1e-2, (name, rel)
