@@ -2,13 +2,18 @@
 the return transfer fused into the grouped-GEMM epilogue.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29555 \
-        -m miles_b200.parallel.bench_ep --tokens 8192
+        benchmarks/bench_ep.py --tokens 8192
 
 Times one MoE block (router, dispatch, grouped GEMMs, return, combine) forward and forward+backward with CUDA
 events, max over ranks, after warm-up; inputs are far larger than L2. The roofline printed for the fused path is
 max(FLOPs / measured bf16 peak, bytes over NVLink / 770 GB/s per direction).
 """
 from __future__ import annotations
+
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import argparse
 import json

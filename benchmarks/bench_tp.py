@@ -2,12 +2,17 @@
 local GEMM followed by NCCL all-reduce.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29556 \
-        -m miles_b200.parallel.bench_tp --tokens 8192
+        benchmarks/bench_tp.py --tokens 8192
 
 Shapes default to Qwen3-4B under TP = world size (o projection and MLP down projection). CUDA events, max over
 ranks, after warm-up; operands exceed L2. Roofline = max(FLOPs / measured bf16 peak, bytes over NVLink / 770 GB/s).
 """
 from __future__ import annotations
+
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import argparse
 import json

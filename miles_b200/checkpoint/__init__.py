@@ -41,10 +41,22 @@ def latest_iteration(base: str) -> Optional[int]:
     return int(txt) if txt.isdigit() else None
 
 
-def save_checkpoint(actor, base: str, iteration: int) -> str:
-    d = iter_dir(base, iteration)
-    os.makedirs(d, exist_ok=True)
-    rank = actor.ps.rank
+_ASYNC: dict = {"thread": None, "error": None}
+
+
+def wait_for_async_save() -> None:
+    """Block until a background save (``--async-save``) has finished; re-raise what it raised."""
+    t = _ASYNC["thread"]
+    if t is not None:
+        t.join()
+        _ASYNC["thread"] = None
+    if _ASYNC["error"] is not None:
+        err, _ASYNC["error"] = _ASYNC["error"], None
+        raise RuntimeError("asynchronous checkpoint save failed") from err
+
+
+def _snapshot_state(actor, iteration: int) -> dict:
+    """Host copies of everything a rank saves (the device is free to move on once this returns)."""
     state = {
         "flat": {g: t.detach().cpu() for g, t in actor.store.flat.items()},
         "version": actor.store.version,
@@ -59,19 +71,93 @@ def save_checkpoint(actor, base: str, iteration: int) -> str:
                                   if isinstance(v, dict) else v) for k, v in sd.items()}
     if getattr(actor, "_value_head", None) is not None:
         state["value_head"] = actor._value_head.detach().cpu()
+    return state
+
+
+def _write_state(actor, base: str, d: str, iteration: int, state: dict, checksums: Optional[dict]) -> None:
+    rank = actor.ps.rank
     tmp = os.path.join(d, f"rank_{rank:05d}.pt.tmp")
     torch.save(state, tmp)
     os.replace(tmp, os.path.join(d, f"rank_{rank:05d}.pt"))
-    from ..utils.ci_checks import save_model_hashes
+    if checksums is not None:
+        with open(os.path.join(d, f"weight_checksum_rank_{rank:05d}.json"), "w") as f:
+            json.dump(checksums, f)
 
-    save_model_hashes(actor.args, actor.store, actor.ps, iteration)
-    if dist.is_initialized():
-        dist.barrier()
-    if rank == 0:
+
+def _finish_save(actor, base: str, d: str, iteration: int) -> None:
+    """After every rank has written its file: metadata, the latest pointer, retention, the post-save hook."""
+    args = actor.args
+    if actor.ps.rank == 0:
         with open(os.path.join(d, "meta.json"), "w") as f:
             json.dump({"iteration": iteration, "world_size": actor.ps.world_size, "model": actor.cfg.to_dict()}, f, default=str)
         with open(os.path.join(base, LATEST), "w") as f:
             f.write(str(iteration))
+        prune_checkpoints(base, iteration, getattr(args, "save_interval", None), getattr(args, "save_retain_interval", None))
+    hook = getattr(args, "custom_megatron_post_save_hook_path", None)
+    if hook:
+        from ..utils.misc import load_function
+
+        load_function(hook)(args, actor, iteration, d)
+
+
+def prune_checkpoints(base: str, newest: int, save_interval: Optional[int], retain_interval: Optional[int]) -> list:
+    """``--save-retain-interval R``: of the checkpoints older than the newest keep those whose step (rollout id + 1) is
+    a multiple of R and delete the rest (reference: miles/backends/megatron_utils/checkpoint.py). Returns what was
+    deleted."""
+    if not retain_interval:
+        return []
+    gone = []
+    for name in sorted(os.listdir(base)):
+        if not name.startswith("iter_") or not name[5:].isdigit():
+            continue
+        it = int(name[5:])
+        if it >= newest or (it + 1) % retain_interval == 0:
+            continue
+        shutil.rmtree(os.path.join(base, name), ignore_errors=True)
+        gone.append(it)
+    return gone
+
+
+def save_checkpoint(actor, base: str, iteration: int) -> str:
+    """One file per rank under ``<base>/iter_%07d``. With ``--async-save`` the device-to-host snapshot happens here and
+    the file write, metadata, retention and hooks run in a background thread (the next save, or the end of the run,
+    waits for it); ranks then synchronise through the files themselves instead of a barrier."""
+    wait_for_async_save()
+    d = iter_dir(base, iteration)
+    os.makedirs(d, exist_ok=True)
+    state = _snapshot_state(actor, iteration)
+    checksums = None
+    if getattr(actor.args, "save_local_weight_checksum", False):
+        checksums = {g: float(t.double().abs().sum()) for g, t in state["flat"].items()}
+    from ..utils.ci_checks import save_model_hashes
+
+    save_model_hashes(actor.args, actor.store, actor.ps, iteration)
+    if getattr(actor.args, "async_save", False):
+        import threading
+        import time
+
+        def work():
+            try:
+                _write_state(actor, base, d, iteration, state, checksums)
+                if actor.ps.rank == 0:  # every rank's file must exist before the checkpoint is announced
+                    deadline = time.time() + 600
+                    want = [os.path.join(d, f"rank_{r:05d}.pt") for r in range(actor.ps.world_size)]
+                    while not all(os.path.exists(w) for w in want):
+                        if time.time() > deadline:
+                            raise TimeoutError(f"rank files missing under {d}")
+                        time.sleep(0.05)
+                _finish_save(actor, base, d, iteration)
+            except BaseException as e:  # noqa: BLE001 - surfaced by wait_for_async_save
+                _ASYNC["error"] = e
+
+        t = threading.Thread(target=work, name="miles-b200-async-save", daemon=False)
+        _ASYNC["thread"] = t
+        t.start()
+        return d
+    _write_state(actor, base, d, iteration, state, checksums)
+    if dist.is_initialized():
+        dist.barrier()
+    _finish_save(actor, base, d, iteration)
     return d
 
 

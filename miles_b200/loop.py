@@ -82,6 +82,9 @@ class RLLoop:
         self.start_rollout_id = self._resume()
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        from .utils.ci_checks import metric_checker_from_args
+
+        self.metric_checker = metric_checker_from_args(args)
         self.tracker = None
         try:
             from .utils.tracking import init_tracking
@@ -315,6 +318,14 @@ class RLLoop:
         if self.engine is not None:
             self.engine.drain()  # expert-parallel ranks keep serving dummy iterations until all are done
         samples = flatten_groups(out.samples if hasattr(out, "samples") else out)
+        if getattr(a, "ci_inject_rollout_data_path", None):
+            from .utils.ci_checks import inject_rollout_data
+
+            samples = inject_rollout_data(a, rollout_id, samples, self.rep, self.n_rep)
+        if getattr(a, "rollout_data_postprocess_path", None):
+            # user hook on the generated samples before they become training data (reference signature: fn(args, samples))
+            res = load_function(a.rollout_data_postprocess_path)(a, samples)
+            samples = res if res is not None else samples
         samples = postprocess_rollout_data(self.local_args, samples)
         # the ranks of a context-parallel group and the stages of a pipeline train on the same samples: each of
         # them generated a share with its own engine, now they pool them
@@ -403,8 +414,12 @@ class RLLoop:
         if a.offload_train:
             self.actor.wake_up()
         metrics.update(self.train(rollout_id, samples))
+        if getattr(a, "ci_test", False):
+            from .utils.ci_checks import check_rollout_logprobs
+
+            check_rollout_logprobs(a, metrics)
         t2 = time.perf_counter()
-        if should_run_periodic_action(rollout_id, a.save_interval, None, a.num_rollout):
+        if should_run_periodic_action(rollout_id, a.save_interval, None, a.num_rollout) or self._save_triggered():
             self.actor.save_model(rollout_id)
             self.data_source.save(rollout_id)
         if a.offload_train:
@@ -426,11 +441,31 @@ class RLLoop:
             self.tracker.log(metrics, step=rollout_id)
         return metrics
 
+    def _save_triggered(self) -> bool:
+        """``--save-trigger-sentinel PATH``: an operator touches the file to ask for a checkpoint at the next save point;
+        the file is removed once seen (every rank takes the first rank's answer)."""
+        path = getattr(self.args, "save_trigger_sentinel", None)
+        if not path:
+            return False
+        hit = [False]
+        if self.ps.rank == 0 and os.path.exists(path):
+            hit[0] = True
+            try:
+                os.remove(path)
+            except OSError:
+                pass
+        if self.ps.world_size > 1:
+            dist.broadcast_object_list(hit, src=0)
+        return bool(hit[0])
+
     def evaluate(self, rollout_id: int) -> dict:
         out = self.rollout_fn(RolloutFnEvalInput(rollout_id))
         if asyncio.iscoroutine(out):
             out = asyncio.run(out)
-        return dict(getattr(out, "metrics", {}) or {})
+        metrics = dict(getattr(out, "metrics", {}) or {})
+        if self.metric_checker is not None:
+            self.metric_checker.update(metrics)
+        return metrics
 
     def run(self) -> list:
         a = self.args
@@ -448,4 +483,9 @@ class RLLoop:
                 print(f"[rollout {rid}] " + " ".join(f"{k.split('/')[-1] if k.count('/')==1 else k}={m[k]:.5g}" for k in keys if k in m), flush=True)
             if getattr(a, "debug_exit_after_rollout", None) is not None and rid >= a.debug_exit_after_rollout:
                 break
+        from .checkpoint import wait_for_async_save
+
+        wait_for_async_save()  # a background save must be complete before the job ends
+        if self.metric_checker is not None:
+            self.metric_checker.finalize()
         return history

@@ -24,14 +24,6 @@ from .params import ParamStore
 from .torch_impl import InferMeta
 
 
-def _flash_attn_bwd():
-    # The attention backward still comes from the flash-attn library; it consumes the output and the
-    # log-sum-exp written by this package's tcgen05 forward kernel.
-    from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
-
-    return _flash_attn_varlen_backward
-
-
 @dataclass
 class MoeCtx:
     ids: torch.Tensor
@@ -62,12 +54,20 @@ class B200Qwen3:
         self._tiles = TileCache()
         self._ident: Optional[torch.Tensor] = None
         self.small_decode = True  # weight-streaming kernels for decode steps of at most SMALL_T rows
+        self.lm_chunk = 2048      # rows of the LM head per pass (--log-probs-chunk-size)
 
     def attention(self, q, k, v, cu):
         """Causal attention over packed sequences: returns (out [T, Hq, 128], lse [Hq, T])."""
         out, lse = self.C.flash_attn_fwd(q, k, v, self._tiles.get(cu), self.cfg.head_dim ** -0.5, self.status)
         self.launches += 1
         return out, lse
+
+    def attention_backward(self, q, k, v, out, d_out, lse, cu):
+        """dQ, dK, dV of :meth:`attention` from its output and log-sum-exp (tcgen05 kernel, csrc/attention_bwd.cu)."""
+        dq, dk, dv = self.C.flash_attn_bwd(q, k, v, out, d_out.contiguous(), lse, self._tiles.get_bwd(cu),
+                                           self.cfg.head_dim ** -0.5, self.status)
+        self.launches += 3
+        return dq, dk, dv
 
     # ------------------------------------------------------------------ GEMM helpers
     def _gemm(self, a, b, out, a_mn=False, b_mn=False, acc=False):
@@ -441,9 +441,7 @@ class B200Qwen3:
         # ---- attention output projection
         datt = self.linear_dgrad(dx2, P[p + "attn.o.weight"])
         self.linear_wgrad(dx2, att2, G[p + "attn.o.weight"])
-        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty(k.shape, dtype=k.dtype, device=k.device)
-        _flash_attn_bwd()(datt.view_as(att), q, k, v, att, lse, dq, dk, dv, cu, cu, max_seqlen, max_seqlen, 0.0, scale,
-                          True, -1, -1, 0.0, None, False, None, False)
+        dq, dk, dv = self.attention_backward(q, k, v, att, datt.view_as(att), lse, cu)
         dqkv = C.qk_norm_rope_bwd(dq, dk, dv, qkv, P.get(p + "attn.q_norm.weight"),
                                   P.get(p + "attn.k_norm.weight"), positions, qr, kr, G.get(p + "attn.q_norm.weight"),
                                   G.get(p + "attn.k_norm.weight"), cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta)
@@ -539,8 +537,9 @@ class B200Qwen3:
         return self.linear(hidden_rows.contiguous(), self.store.lm_head(), out_dtype)
 
     @torch.no_grad()
-    def logprobs_entropy(self, hidden_rows, targets, inv_temp: float, chunk: int = 2048, keep_stats: bool = False):
+    def logprobs_entropy(self, hidden_rows, targets, inv_temp: float, chunk: int = 0, keep_stats: bool = False):
         C = self.C
+        chunk = chunk or self.lm_chunk
         n = hidden_rows.shape[0]
         lp = torch.empty(n, dtype=torch.float32, device=self.dev)
         ent = torch.empty_like(lp)
@@ -564,12 +563,13 @@ class B200Qwen3:
         return self.logprobs_entropy(h[row_index.long()], targets, inv_temp)
 
     def forward_backward(self, tokens, positions, cu_seqlens, row_index, targets, inv_temp, loss_fn, replay=None,
-                         max_seqlen: int = 0, chunk: int = 2048, x_in: Optional[torch.Tensor] = None):
+                         max_seqlen: int = 0, chunk: int = 0, x_in: Optional[torch.Tensor] = None):
         """One micro-batch: forward, ``loss_fn(logprobs, entropy) -> (loss, metrics)``, backward into the grad buffers.
         On the last pipeline stage ``x_in`` is the activation received from the previous stage and ``self.last_dx_in``
         afterwards holds the gradient to send back."""
         cfg, P, G, C = self.cfg, self.store.params, self.store.grads, self.C
         assert G, "allocate_grads() must be called before training"
+        chunk = chunk or self.lm_chunk
         if not max_seqlen:
             max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
         inputs: list[torch.Tensor] = []

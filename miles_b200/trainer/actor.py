@@ -189,6 +189,8 @@ class TrainActor:
             # the rollout id the checkpoint was written after (None: weights only, start from rollout 0);
             # load_checkpoint restores global_step (optimizer steps) itself
             self.loaded_rollout_id = load_checkpoint(self, args.load, getattr(args, "ckpt_step", None))
+            if getattr(args, "reset_optimizer_states", False) and self.opt is not None:
+                self.opt.reset_state()  # keep the weights (and their fp32 master), restart the moments and the schedule
         need_ref = (args.kl_coef != 0 or args.use_kl_loss) and role == "actor"
         if need_ref:
             self.backup_weights("ref")
@@ -246,12 +248,18 @@ class TrainActor:
         self.plan = plan
         self._expert_grad_dtype = torch.bfloat16 if (plan["expert_grad"] == "bf16" and self.store.dtype == torch.bfloat16) else torch.float32
         self.store.allocate_grads(torch.float32, self._expert_grad_dtype)
+        warmup = a.lr_warmup_iters or 0
+        if getattr(a, "lr_warmup_fraction", None) and (a.lr_decay_iters or 0) > 0:
+            warmup = int(a.lr_warmup_fraction * a.lr_decay_iters)  # Megatron: a fraction of the decay horizon
+        if self.role == "critic" and getattr(a, "critic_lr_warmup_iters", 0):
+            warmup = a.critic_lr_warmup_iters
         oc = OptimConfig(lr=a.lr if self.role == "actor" else (a.critic_lr or a.lr), beta1=a.adam_beta1, beta2=a.adam_beta2,
                          eps=a.adam_eps, weight_decay=a.weight_decay, clip_grad=a.clip_grad, state_dtype=_DT[plan["state"]],
                          master_weights=plan["master"], offload_states=plan["offload"],
                          offload_resident_frac=plan.get("resident_frac", 0.0) if plan["offload"] else 0.0,
                          lr_decay_style=a.lr_decay_style,
-                         lr_warmup_iters=a.lr_warmup_iters or 0, lr_decay_iters=a.lr_decay_iters or 0, min_lr=a.min_lr,
+                         lr_warmup_iters=warmup, lr_decay_iters=a.lr_decay_iters or 0, min_lr=a.min_lr,
+                         skip_nonfinite=not getattr(a, "no_check_for_nan_in_loss_and_grad", False),
                          lr_wsd_decay_iters=a.lr_wsd_decay_iters or 0)
         if getattr(a, "optimizer", "adam") == "muon":
             from .muon import Muon, MuonConfig
@@ -322,6 +330,9 @@ class TrainActor:
     def _forward_logprobs(self, mb: MicroBatch, replay=None, record=None):
         inv_t = 1.0 / self.args.rollout_temperature
         self._set_cp(mb)
+        chunk = getattr(self.args, "log_probs_chunk_size", -1) or -1
+        if chunk > 0 and hasattr(self.model, "lm_chunk"):
+            self.model.lm_chunk = int(chunk)  # rows of the LM head (logits -> log-prob / entropy) computed at a time
         if self.is_torch:
             return self.model.forward_logprobs(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t,
                                                replay=replay, record=record)
@@ -578,6 +589,9 @@ class TrainActor:
                 self.compute_log_probs(mbs, "ref_log_probs")
         for k in ("train_log_probs", "train_fwd_bwd", "train_optimizer"):
             T.reset(k)
+        if getattr(a, "custom_megatron_before_log_prob_hook_path", None):
+            # reference signature: hook(args, model, store_prefix)
+            load_function(a.custom_megatron_before_log_prob_hook_path)(a, self.model, "")
         if need_old:
             with T.context("log_probs"), T.cuda_span("train_log_probs"):
                 self.compute_log_probs(mbs, "log_probs", with_entropy=getattr(a, "use_rollout_entropy", False))
@@ -598,6 +612,9 @@ class TrainActor:
                 if not chunk:
                     continue
                 self.store.zero_grads()
+                if getattr(a, "custom_megatron_before_train_step_hook_path", None):
+                    # reference signature: hook(args, rollout_id, step_id, model, optimizer, opt_param_scheduler)
+                    load_function(a.custom_megatron_before_train_step_hook_path)(a, rollout_id, s, self.model, self.opt, None)
                 if a.calculate_per_token_loss:
                     tok = torch.stack([mb.loss_mask.sum() for mb in chunk]).sum()
                     if self.ps.dp_cp.size > 1:  # a size-1 axis has no group object, and None would mean the whole world

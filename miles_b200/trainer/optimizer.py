@@ -45,6 +45,7 @@ class OptimConfig:
     lr_decay_iters: int = 0
     min_lr: float = 0.0
     lr_wsd_decay_iters: int = 0
+    skip_nonfinite: bool = True           # a non-finite gradient norm skips the step (--no-check-for-nan-in-loss-and-grad: apply anyway)
 
 
 def lr_at(cfg: OptimConfig, step: int) -> float:
@@ -184,7 +185,10 @@ class FlatAdam:
     def _prepare_scale(self, extra_scale: float) -> None:
         norm = self.compute_grad_norm()
         finite = torch.isfinite(norm)
-        self.skip_flag.copy_((~finite).float().reshape(1))
+        if self.cfg.skip_nonfinite:
+            self.skip_flag.copy_((~finite).float().reshape(1))
+        else:
+            self.skip_flag.zero_()
         if self.cfg.clip_grad and self.cfg.clip_grad > 0:
             coef = torch.clamp(self.cfg.clip_grad / (norm * extra_scale + 1e-6), max=1.0)
         else:

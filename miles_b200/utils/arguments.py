@@ -241,10 +241,24 @@ def _default(ns, name: str, value: Any) -> None:
         setattr(ns, name, value)
 
 
+_DEFAULTS: dict = {}
+
+
+def parser_defaults() -> dict:
+    """dest -> default of every flag of the parser (cached)."""
+    if not _DEFAULTS:
+        _DEFAULTS.update({a.dest: a.default for a in build_parser()._actions})
+    return _DEFAULTS
+
+
 def validate_args(args: argparse.Namespace) -> argparse.Namespace:
     for attr, what in _UNBUILT.items():
         if getattr(args, attr, False):
             raise NotImplementedError(f"--{attr.replace('_', '-')}: {what} is not built in this framework yet")
+    from . import flag_policy
+
+    # flags of features that are not built raise; flags of components that do not exist here warn once
+    flag_policy.apply(args, parser_defaults())
     if getattr(args, "custom_config_path", None):
         import yaml
 

@@ -70,7 +70,7 @@ def check_model_hashes(args, store, ps, iteration: int) -> None:
 
 
 def check_first_step_kl(args, metrics: dict, step_in_rollout: int, global_step: int) -> None:
-    if not getattr(args, "ci_test", False):
+    if not getattr(args, "ci_test", False) or getattr(args, "ci_disable_kl_checker", False):
         return
     if step_in_rollout == 0 and "train/ppo_kl" in metrics and "train/pg_clipfrac" in metrics:
         tol = 1e-8 if getattr(args, "lora_rank", 0) else 1e-9
@@ -91,3 +91,53 @@ def check_grad_norm(args, grad_norm: float, rollout_id: int, step_id: int, role:
     elif load:
         want = float(torch.load(load.format(role=role, rollout_id=rollout_id, step_id=step_id), weights_only=False))
         assert math.isclose(float(grad_norm), want, rel_tol=0.03, abs_tol=0.03), f"gradient norm {grad_norm} != recorded {want}"
+
+
+def check_rollout_logprobs(args, metrics: dict) -> None:
+    """Trainer-vs-rollout log-prob gate of a CI run (reference: training_utils/log_utils.py:262-298): the mean
+    absolute difference must stay below 0.03; ``--ci-disable-logprobs-checker`` turns it off."""
+    if not getattr(args, "ci_test", False) or getattr(args, "ci_disable_logprobs_checker", False):
+        return
+    d = metrics.get("train/train_rollout_logprob_abs_diff")
+    if d is not None:
+        assert d <= 0.03, f"trainer and rollout log-probs differ by {d} on average (limit 0.03)"
+
+
+def metric_checker_from_args(args):
+    """``--ci-metric-checker-key K --ci-metric-checker-threshold X`` (with ``--ci-test``): some evaluation of the run
+    must reach ``metrics[K] >= X``; the loop calls ``finalize`` at the end of the run (reference:
+    miles/utils/metric_checker.py:6-28)."""
+    if getattr(args, "ci_test", False) and getattr(args, "ci_metric_checker_key", None) is not None:
+        from .metric_utils import MetricChecker
+
+        thr = args.ci_metric_checker_threshold if args.ci_metric_checker_threshold is not None else 0.0
+        return MetricChecker(args.ci_metric_checker_key, float(thr))
+    return None
+
+
+def inject_rollout_data(args, rollout_id: int, generated: list, rep: int, n_rep: int) -> list:
+    """``--ci-inject-rollout-data-path`` (CI comparison runs): from ``--ci-inject-rollout-data-start-rollout-id`` on the
+    samples just generated are replaced by a recording written with ``--save-debug-rollout-data``, after checking that
+    the recording and the generation agree on at least ``--ci-inject-rollout-data-min-match-ratio`` of the response
+    tokens (a lower ratio means the engine is not running the weights the recording was made with)."""
+    path = getattr(args, "ci_inject_rollout_data_path", None)
+    start = getattr(args, "ci_inject_rollout_data_start_rollout_id", None)
+    if not path or (start is not None and rollout_id < start):
+        return generated
+    from .types import Sample
+
+    blob = torch.load(path.format(rollout_id=rollout_id), weights_only=False)
+    recorded = [Sample.from_dict(d) for d in blob["samples"]]
+    recorded = recorded[rep::n_rep] if n_rep > 1 else recorded
+    n = min(len(recorded), len(generated))
+    if n:
+        ratios = []
+        for a, b in zip(recorded[:n], generated[:n]):
+            ra, rb = list(a.tokens[-a.response_length:]) if a.response_length else [], \
+                list(b.tokens[-b.response_length:]) if b.response_length else []
+            m = min(len(ra), len(rb))
+            ratios.append(sum(x == y for x, y in zip(ra[:m], rb[:m])) / max(max(len(ra), len(rb)), 1))
+        mean = sum(ratios) / len(ratios)
+        assert mean >= float(getattr(args, "ci_inject_rollout_data_min_match_ratio", 0.9)), \
+            f"generated responses match the recording on {mean:.3f} of the tokens only"
+    return recorded

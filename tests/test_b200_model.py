@@ -67,10 +67,12 @@ def test_forward_backward_matches_autograd(name):
         got = store.grads[s.name].float()
         want = ref_store.flat[s.group].grad[s.offset:s.offset + s.numel].view(s.shape)
         denom = want.abs().max().item() + 1e-6
-        rel = (got - want).abs().max().item() / denom
+        rel = (got - want).abs().max().item() / denom            # worst element against the gradient's scale
+        l2 = (got - want).norm().item() / (want.norm().item() + 1e-12)
         cos = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0).item() if want.abs().sum() > 0 else 1.0
-        if cos < 0.99:
-            bad.append((s.name, rel, cos))
+        # bf16 activations against an fp32 autograd reference: direction, overall size and the worst element
+        if cos < 0.99 or l2 > 0.12 or rel > 0.25:
+            bad.append((s.name, round(rel, 4), round(l2, 4), round(cos, 5)))
     assert not bad, bad
 
 

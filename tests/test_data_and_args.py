@@ -120,3 +120,61 @@ def test_hf_validate_args_reports_all_mismatches():
         hf_validate_args(bad, hf)
     msg = str(e.value)
     assert "num_hidden_layers" in msg and "rope_theta" in msg and "tie_word_embeddings" in msg
+
+
+def _package_source() -> str:
+    """Every line of the package and the drivers that could read a flag: the flag tables themselves and the policy
+    lists are left out, so that being listed does not count as being read."""
+    import os
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = []
+    for base, _, files in os.walk(os.path.join(root, "miles_b200")):
+        for f in files:
+            if not f.endswith(".py") or f in ("flag_table.py", "flag_policy.py"):
+                continue
+            txt = open(os.path.join(base, f)).read()
+            if f == "arguments.py" and base.endswith("utils"):
+                txt = txt[:txt.index("TRAINER_FLAGS = [")] + txt[txt.index("_UNBUILT"):]
+            src.append(txt)
+    for f in ("train.py", "train_async.py", "train_multi_lora_async.py"):
+        src.append(open(os.path.join(root, f)).read())
+    return "\n".join(src)
+
+
+def test_every_flag_is_read_rejected_or_declared_inert():
+    """A parsed flag must do something, refuse to start, or be declared inert with a reason: walking the parser
+    catches a flag that is accepted and silently dropped."""
+    import re
+
+    from miles_b200.utils import flag_policy
+    from miles_b200.utils.arguments import build_parser
+
+    src = _package_source()
+    dests = sorted({a.dest for a in build_parser()._actions if a.dest != "help"})
+    assert len(dests) > 400
+    both = set(flag_policy.REJECT) & set(flag_policy.IGNORED)
+    assert not both, f"listed as rejected and as inert: {sorted(both)}"
+    stale = [d for d in list(flag_policy.REJECT) + list(flag_policy.IGNORED) if d not in dests]
+    assert not stale, f"policy entries for flags the parser does not have: {stale}"
+    orphans = []
+    for d in dests:
+        if d in flag_policy.REJECT or d in flag_policy.IGNORED:
+            continue
+        if not re.search(r"\b" + re.escape(d) + r"\b", src):
+            orphans.append(d)
+    assert not orphans, f"{len(orphans)} flags are parsed but neither read, rejected nor declared inert: {orphans}"
+
+
+def test_unbuilt_features_refuse_to_start():
+    base = ["--num-rollout", "1", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--model-preset", "qwen3-tiny"]
+    for extra in (["--fp8-format", "e4m3", "--fp8-recipe", "mxfp8"], ["--moe-router-score-function", "sigmoid"],
+                  ["--moe-shared-expert-intermediate-size", "512"], ["--attention-output-gate"], ["--train-backend", "fsdp"],
+                  ["--true-on-policy-mode"], ["--virtual-pipeline-model-parallel-size", "2"], ["--hidden-dropout", "0.1"]):
+        with pytest.raises(NotImplementedError):
+            parse_args(base + extra)
+    # the reference's own model script for this family passes these with their default meaning: accepted
+    parse_args(base + ["--moe-router-score-function", "softmax", "--moe-token-drop-policy", "probs", "--moe-router-dtype", "fp32",
+                       "--moe-aux-loss-coeff", "0", "--attention-dropout", "0.0", "--hidden-dropout", "0.0", "--rotary-percent", "1.0",
+                       "--normalization", "RMSNorm", "--position-embedding-type", "rope", "--moe-grouped-gemm", "--moe-permute-fusion"])
