@@ -85,6 +85,11 @@ class RLLoop:
         from .utils.ci_checks import metric_checker_from_args
 
         self.metric_checker = metric_checker_from_args(args)
+        self.ft = None
+        if getattr(args, "use_fault_tolerance", False):
+            from .ft.runtime import FTRuntime
+
+            self.ft = FTRuntime(self, args)
         self.tracker = None
         try:
             from .utils.tracking import init_tracking
@@ -310,6 +315,10 @@ class RLLoop:
             from .utils.types import Sample
 
             samples = [Sample.from_dict(d) for d in blob["samples"]]
+            ratio = getattr(a, "load_debug_rollout_data_subsample", None)
+            if ratio is not None:  # keep the head and the tail of the recording (reference: ray/rollout/debug_data.py:93-99)
+                k = int(len(samples) * ratio)
+                samples = samples[:k // 2] + samples[len(samples) - (k - k // 2):]
             samples = samples[self.rep::self.n_rep] if self.n_rep > 1 else samples
             return samples, {}
         out = self.rollout_fn(RolloutFnTrainInput(rollout_id))
@@ -334,7 +343,12 @@ class RLLoop:
                 samples = self._pool_samples(samples, axis)
         dt = time.perf_counter() - t0
         metrics = dict(getattr(out, "metrics", {}) or {})
-        metrics.update(compute_rollout_metrics(a, samples, dt))
+        hook = getattr(a, "custom_rollout_log_function_path", None)
+        # a user log function may take over (it returns True to suppress the built-in rollout metrics)
+        if not (hook and load_function(hook)(rollout_id, a, samples, metrics, dt)):
+            metrics.update(compute_rollout_metrics(a, samples, dt))
+        if getattr(a, "save_debug_trajectory_data", None):
+            self._save_trajectories(rollout_id, samples, evaluation=False)
         if getattr(a, "save_debug_rollout_data", None):
             p = a.save_debug_rollout_data.format(rollout_id=rollout_id)
             os.makedirs(os.path.dirname(p) or ".", exist_ok=True)
@@ -345,6 +359,26 @@ class RLLoop:
             if self.ps.rank == 0:
                 torch.save({"rollout_id": rollout_id, "samples": [d for g in gathered for d in g]}, p)
         return samples, metrics
+
+    def _save_trajectories(self, rollout_id: int, samples: list, evaluation: bool) -> None:
+        """``--save-debug-trajectory-data TEMPLATE``: one JSON line per sample that carries a conversation
+        (``metadata['messages']``), written next to the rollout dump; the messages then leave the sample."""
+        import json
+
+        rows = []
+        for s in samples:
+            msgs = (s.metadata or {}).get("messages")
+            if msgs:
+                rows.append({"index": s.index, "group_index": s.group_index, "reward": s.reward, "messages": msgs})
+        if not rows:
+            return
+        p = self.args.save_debug_trajectory_data.format(rollout_id=("eval_" if evaluation else "") + str(rollout_id), rank=self.ps.rank)
+        os.makedirs(os.path.dirname(p) or ".", exist_ok=True)
+        with open(p, "w") as f:
+            f.write("".join(json.dumps(r, default=str, separators=(",", ":")) + "\n" for r in rows))
+        for s in samples:
+            if s.metadata:
+                s.metadata.pop("messages", None)
 
     def _pool_samples(self, samples: list, axis) -> list:
         from .utils.types import Sample
@@ -376,6 +410,12 @@ class RLLoop:
     def train(self, rollout_id: int, samples: list) -> dict:
         a = self.args
         data = convert_samples_to_train_data(a, samples)
+        if self.ft is not None and "train" in self.ft.components:
+            return self.ft.train(rollout_id, data)  # through the cell group: retries, suspended cells, scripted faults
+        return self._train_once(rollout_id, data)
+
+    def _train_once(self, rollout_id: int, data: dict) -> dict:
+        a = self.args
         local = copy.copy(self.actor.args)
         metrics = {}
         # every rank already holds exactly its own share: train on it without a DP re-split
@@ -437,6 +477,8 @@ class RLLoop:
                         "perf/grpo_tokens_per_s": float(tot.item()) / max(t3 - t0, 1e-9)})
         if a.eval_interval is not None and should_run_periodic_action(rollout_id, a.eval_interval, None, a.num_rollout):
             metrics.update(self.evaluate(rollout_id))
+        if self.ft is not None:
+            self.ft.after_rollout(rollout_id)
         if self.tracker is not None:
             self.tracker.log(metrics, step=rollout_id)
         return metrics
@@ -463,6 +505,9 @@ class RLLoop:
         if asyncio.iscoroutine(out):
             out = asyncio.run(out)
         metrics = dict(getattr(out, "metrics", {}) or {})
+        hook = getattr(self.args, "custom_eval_rollout_log_function_path", None)
+        if hook:  # reference signature: fn(rollout_id, args, data, extra_metrics) -> bool
+            load_function(hook)(rollout_id, self.args, getattr(out, "data", None), metrics)
         if self.metric_checker is not None:
             self.metric_checker.update(metrics)
         return metrics
@@ -486,6 +531,15 @@ class RLLoop:
         from .checkpoint import wait_for_async_save
 
         wait_for_async_save()  # a background save must be complete before the job ends
+        if self.ft is not None:
+            self.ft.stop()
         if self.metric_checker is not None:
             self.metric_checker.finalize()
+        if getattr(a, "enable_event_analyzer", False) and self.actor.events is not None:
+            # every replica reported the same weights per step, every sample was trained exactly once
+            from .utils.audit import analyze, read_events
+
+            evs = read_events(a.save_debug_event_data) if getattr(a, "save_debug_event_data", None) else self.actor.events.events
+            problems = analyze(evs)
+            assert not problems, "event analyzer: " + "; ".join(problems[:5])
         return history

@@ -150,6 +150,28 @@ def compute_rollout_metrics(args, samples: Sequence[Sample], rollout_time: float
     m["perf/rollout_time"] = rollout_time
     if rollout_time > 0:
         m["perf/tokens_per_gpu_per_sec"] = sum(resp) / rollout_time / max(num_gpus, 1)
+    cat_key = getattr(args, "log_reward_category", None)
+    if cat_key:
+        # share of samples per value of one field of a dict-valued reward (e.g. an error category)
+        cats: dict = defaultdict(int)
+        for s in samples:
+            if isinstance(s.reward, dict) and cat_key in s.reward:
+                cats[s.reward[cat_key]] += 1
+        for c, n in cats.items():
+            m[f"rollout/error_cat/{c}"] = n / max(len(samples), 1)
+    if getattr(args, "log_multi_turn", False):
+        # responses of tool / multi-turn rollouts contain observation tokens the model did not write (loss mask 0)
+        own = [float(sum(s.loss_mask)) if s.loss_mask is not None else float(s.response_length) for s in samples]
+        m.update({f"rollout/{k}": v for k, v in _stats(own, "wo_obs_response_length").items()})
+        m["rollout/raw_response_length/clip_ratio"] = sum(r >= args.rollout_max_response_len for r in resp) / max(len(resp), 1)
+        rounds = [float((s.metadata or {}).get("round_number", (s.metadata or {}).get("num_turns", 0)) or 0) for s in samples]
+        if any(rounds):
+            m.update({f"rollout/{k}": v for k, v in _stats(rounds, "multi_turn_metric/round_number").items()})
+    if getattr(args, "log_correct_samples", False) and rewards:
+        # response-length statistics of the samples that earned the full reward
+        ok = [float(s.response_length) for s in samples if s.reward is not None and s.get_reward_value(key) >= 1.0]
+        m["rollout/correct_samples/ratio"] = len(ok) / max(len(samples), 1)
+        m.update({f"rollout/{k}": v for k, v in _stats(ok, "correct_samples/response_len").items()})
     cached = sum(s.prefix_cache_info.get("cached_tokens", 0) for s in samples)
     total_p = sum(s.prefix_cache_info.get("total_prompt_tokens", 0) for s in samples)
     if total_p:

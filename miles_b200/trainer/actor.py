@@ -171,6 +171,32 @@ class TrainActor:
         self.d2h_bytes = 0
         self._value_head = None
         self.cell_group = None  # ft.indep_dp.ReconfigurableGroup when this trainer is one cell of several
+        # audit trail (--enable-witness / --save-debug-event-data): every trained sample id is counted through the same
+        # commit / discard boundary as the optimizer step, and steps are logged with a weight checksum
+        self.witness = None
+        self.events = None
+        if getattr(args, "enable_witness", False) or getattr(args, "save_debug_event_data", None) or getattr(args, "enable_event_analyzer", False):
+            from ..utils.audit import EventLogger, Witness
+
+            self.events = EventLogger(getattr(args, "save_debug_event_data", None), role, self.ps.rank)
+            if getattr(args, "enable_witness", False):
+                self.witness = Witness(int(getattr(args, "witness_buffer_size", 1 << 20) or (1 << 20)))
+        self.dumper = None
+        if getattr(args, "dumper_enable", False):
+            from ..utils.dumper import Dumper
+
+            self.dumper = Dumper(getattr(args, "dumper_dir", None) or "/tmp/dumper", self.ps.rank)
+            # a phase is dumped when its flag is given, or when none of the three is (dump everything)
+            chosen = {"inference": getattr(args, "dumper_inference", None), "fwd_only": getattr(args, "dumper_fwd_only", None),
+                      "fwd_bwd": getattr(args, "dumper_fwd_bwd", None)}
+            self.dumper.phases = {k for k, v in chosen.items() if v} or set(chosen)
+        if getattr(args, "deterministic_mode", False):
+            # reproducible kernels where a choice exists: torch ops, cuBLAS workspaces, fixed-order gradient reductions
+            # (the attention backward still accumulates dQ with atomics, the one order-dependent sum of this trainer)
+            os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+            os.environ.setdefault("NCCL_ALGO", "Ring")
+            torch.use_deterministic_algorithms(True, warn_only=True)
+            args.debug_deterministic_collective = True
         if role == "critic":
             self._init_value_head()
         self._setup_optimizer()
@@ -357,6 +383,9 @@ class TrainActor:
             record = [] if (self.cfg.is_moe and self.args.use_routing_replay and not self.args.use_rollout_routing_replay
                             and key == "log_probs") else None
             lp, ent = self._forward_logprobs(mb, self._replay_for(mb, "logprob"), record)
+            if self.dumper is not None and "fwd_only" in self.dumper.phases:
+                self.dumper.configure("fwd_only", self.global_step)
+                self.dumper.dump(f"{key}_mb{mbs.index(mb)}", lp, samples=mb.sample_indices)
             mb.extras[key] = lp
             if with_entropy:
                 mb.extras["entropy"] = ent
@@ -581,6 +610,7 @@ class TrainActor:
         with T.context("data_preprocess"):
             mbs = self._stage(data)
         n_tokens_local = sum(mb.num_tokens for mb in mbs)
+        self._last_seq_lens = [int(x) for mb in mbs for x in (mb.cu_seqlens[1:] - mb.cu_seqlens[:-1]).tolist()]
         need_old = not (a.use_rollout_logprobs or a.skip_actor_forward_only) or a.use_routing_replay and not a.use_rollout_routing_replay
         if a.loss_type == "sft_loss":
             need_old = False
@@ -639,7 +669,11 @@ class TrainActor:
                         if not cross_cell_grad_sync(self, self.cell_group):
                             self.discarded_steps = getattr(self, "discarded_steps", 0) + 1
                             self.store.zero_grads()
+                            if self.witness is not None:
+                                self.witness.discard()
                             continue
+                if self.witness is not None:
+                    self.witness.touch(i for mb in chunk for i in mb.sample_indices)
                 with T.cuda_span("train_optimizer"):
                     if self.lora is not None:
                         self.lora.grads_from_weight_grads()
@@ -651,6 +685,17 @@ class TrainActor:
 
                     check_grad_norm(a, float(grad_norm), rollout_id, s, self.role, self.ps.rank)
                 self.global_step += 1
+                if self.witness is not None:
+                    self.witness.commit()
+                if self.events is not None:
+                    ids = [i for mb in chunk for i in mb.sample_indices]
+                    self.events.log("train_step", rollout_id=rollout_id, step=self.global_step, samples=len(ids))
+                    if self.witness is not None:
+                        self.events.log("witness", rollout_id=rollout_id, counts={str(i): 1 for i in ids})
+                    if getattr(a, "enable_event_analyzer", False):
+                        ck = self.store.checksum()
+                        self.events.log("weight_checksum", step=self.global_step, version=self.store.version,
+                                        checksum=f"{ck.get('dense', 0.0):.6e}")
         if self.on_gpu:
             torch.cuda.synchronize()
         elapsed = time.perf_counter() - t_start
@@ -683,8 +728,11 @@ class TrainActor:
             self.model.accumulate_autograd_grads()
             self.model.set_requires_grad(False)
             return m
-        _, m, _, _ = self.model.forward_backward(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t, fn,
-                                                 replay=replay, max_seqlen=mb.max_seqlen)
+        _, m, lp, _ = self.model.forward_backward(mb.tokens, mb.positions, mb.cu_seqlens, mb.rows, mb.targets, inv_t, fn,
+                                                  replay=replay, max_seqlen=mb.max_seqlen)
+        if self.dumper is not None and "fwd_bwd" in self.dumper.phases:
+            self.dumper.configure("fwd_bwd", self.global_step)
+            self.dumper.dump(f"log_probs_s{mb.sample_indices[0]}", lp, samples=mb.sample_indices)
         return m
 
     def _reduce_grads(self) -> None:
@@ -708,10 +756,16 @@ class TrainActor:
             if ge is not None:
                 ge.copy_(buf)
         g = self.store.grad
+        reduce = dist.all_reduce
+        if getattr(self.args, "debug_deterministic_collective", False):
+            # gather + fixed-order tree sum instead of the library's ring / tree of the day (--debug-deterministic-collective)
+            from ..utils.det_collectives import det_all_reduce
+
+            reduce = det_all_reduce
         if self.ps.dp_cp.size > 1 and g["dense"] is not None and g["dense"].numel() and getattr(self, "dense_shard", None) is None:
-            dist.all_reduce(g["dense"], group=self.ps.dp_cp.group)  # with the partitioned optimizer the step itself reduces
+            reduce(g["dense"], group=self.ps.dp_cp.group)  # with the partitioned optimizer the step itself reduces
         if self.ps.expert_dp.size > 1 and g["expert"] is not None and g["expert"].numel():
-            dist.all_reduce(g["expert"], group=self.ps.expert_dp.group)
+            reduce(g["expert"], group=self.ps.expert_dp.group)
 
     def _finalize_metrics(self, acc: dict, grad_norm, n_tokens_local: int, elapsed: float, n_mb: int) -> dict:
         keys = sorted(acc)
@@ -736,6 +790,13 @@ class TrainActor:
         out["train/step"] = self.global_step
         out["perf/actor_train_time"] = elapsed
         out["perf/actor_train_tok_per_s"] = float(extra[0]) / max(elapsed, 1e-9)
+        lens = getattr(self, "_last_seq_lens", None)
+        if lens and elapsed > 0:
+            from ..utils.metric_utils import perf_metrics
+
+            # per-GPU TFLOP/s and MFU of this rank's share (reference: miles/utils/train_metric_utils.py:36-48)
+            pm = perf_metrics(self.cfg, lens, elapsed, 1, peak_tflops=getattr(self.args, "mfu_peak_tflops", None))
+            out.update({k: v for k, v in pm.items() if k != "perf/actor_train_tok_per_s"})
         out["perf/num_micro_batches"] = n_mb
         return out
 

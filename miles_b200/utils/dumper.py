@@ -17,6 +17,7 @@ class Dumper:
     def __init__(self, directory: Optional[str], rank: int = 0, enabled: bool = True):
         self.dir, self.rank, self.enabled = directory, rank, bool(enabled and directory)
         self.phase, self.step = "fwd_only", 0
+        self.phases = {"inference", "fwd_only", "fwd_bwd"}
 
     def configure(self, phase: str, step: int) -> None:
         self.phase, self.step = phase, step

@@ -251,3 +251,37 @@ def test_control_server_and_router_over_http():
     assert rc.post("/add_worker", params={"url": "http://w0"}).status_code == 200
     r = rc.post("/generate", json={"input_ids": [1, 2]})
     assert r.status_code == 200 and r.json() == {"echo": "/generate"}
+
+
+def test_fault_tolerance_runtime_in_the_loop(tmp_path):
+    """--use-fault-tolerance: training goes through the cell group; a scripted crash before the gradient reduction is
+    retried, a scripted stop drops a rollout's training and a scripted start brings the cell back; the control server
+    lists the cell."""
+    import json
+    import socket
+    import urllib.request
+
+    from miles_b200.loop import RLLoop
+    from miles_b200.utils.arguments import parse_args
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    actions = [{"at_rollout": 0, "action": "crash_before_allreduce", "cell_index": 0},
+               {"at_rollout": 1, "action": "stop_cell_at_end", "cell_index": -1},
+               {"at_rollout": 2, "action": "start_cell_at_end", "cell_index": 0}]
+    args = parse_args(["--model-preset", "qwen3-tiny", "--num-rollout", "4", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2",
+                       "--rollout-max-response-len", "8", "--rm-type", "parity", "--advantage-estimator", "grpo", "--lr", "1e-4",
+                       "--colocate", "--actor-num-gpus-per-node", "1", "--use-fault-tolerance", "--control-server-port", str(port),
+                       "--mini-ft-controller-enable", "--ci-ft-test-actions", json.dumps(actions)])
+    loop = RLLoop(args)
+    cells = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/api/v1/cells", timeout=5).read())
+    assert [c["metadata"]["name"] for c in cells["items"]] == ["cell-0"]
+    hist = loop.run()
+    assert len(hist) == 4
+    events = loop.ft.group.events
+    assert any(e[0] == "cell_error" for e in events), events        # rollout 0: the injected crash was seen ...
+    assert ("step_ok", 0, 1) in events                              # ... and the step succeeded on the retry
+    assert "train/grad_norm" in hist[0] and "train/grad_norm" in hist[1]
+    assert hist[2].get("train/skipped_suspended") == 1.0            # stopped at the end of rollout 1
+    assert "train/grad_norm" in hist[3]                             # started again at the end of rollout 2
