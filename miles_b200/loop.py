@@ -85,6 +85,10 @@ class RLLoop:
         from .utils.ci_checks import metric_checker_from_args
 
         self.metric_checker = metric_checker_from_args(args)
+        self.session_urls: list = []
+        if getattr(args, "use_session_server", False) and self.ps.rank == 0:
+            self.session_urls = self._start_session_servers()
+            args.session_server_urls = self.session_urls  # generate functions hand these to their agent frameworks
         self.ft = None
         if getattr(args, "use_fault_tolerance", False):
             from .ft.runtime import FTRuntime
@@ -237,11 +241,38 @@ class RLLoop:
         self.client = RemoteEngineClient([router] if router else urls, self.tokenizer)
         self.rollout_store = None
         sender = self.ps.rank == 0
-        if sender or self.actor.store.ep_size > 1:
+        if getattr(self.args, "update_weight_transfer_mode", None) == "disk-delta":
+            from .weight_sync.disk_delta import DiskDeltaUpdater
+
+            self.weight_updater = DiskDeltaUpdater(
+                self.actor, [HttpEngineHandle(u) for u in urls] if sender else [], self.args.update_weight_disk_dir,
+                encoding=getattr(self.args, "update_weight_delta_encoding", "xor"),
+                checksum_kind=getattr(self.args, "update_weight_delta_checksum", "xxh3-128"))
+        elif sender or self.actor.store.ep_size > 1:
             handles = [HttpEngineHandle(u) for u in urls] if sender else []
             self.weight_updater = BroadcastWeightUpdater(
                 self.actor, handles, buffer_bytes=int(getattr(self.args, "update_weight_buffer_size", None) or (512 << 20)),
                 is_sender=sender)
+
+    def _start_session_servers(self) -> list:
+        """The standalone token-in-token-out session servers (``--use-session-server``): they forward to engines that are
+        reached over HTTP, so they need ``--rollout-engine-urls`` / a launched fleet (rollouts on the in-process engine
+        use the in-process session of ``rollout.generate_hub.agentic`` instead)."""
+        from .rollout.session.server import start_session_servers
+
+        if self.engine is not None:
+            raise ValueError("--use-session-server needs engines reached over HTTP (--rollout-engine-urls or "
+                             "--launch-rollout-fleet); with the in-process engine use the agentic generate function")
+        client = self.client
+
+        def generate(input_ids: list, sampling_params: dict) -> dict:
+            out = asyncio.run(client.generate({"input_ids": list(input_ids), "sampling_params": dict(sampling_params),
+                                               "return_logprob": True}))
+            meta = out.get("meta_info", {})
+            return {"output_ids": out["output_ids"], "output_token_logprobs": [lp for lp, _ in meta.get("output_token_logprobs", [])],
+                    "finish_reason": meta.get("finish_reason", {}).get("type", "stop"), "weight_version": meta.get("weight_version")}
+
+        return start_session_servers(self.args, self.tokenizer, generate)
 
     def _replica_bytes(self) -> int:
         cfg = self.actor.cfg
@@ -500,7 +531,72 @@ class RLLoop:
             dist.broadcast_object_list(hit, src=0)
         return bool(hit[0])
 
+    # ------------------------------------------------------------------ checkpoint evaluation in the background
+    def _checkpoint_eval(self, rollout_id: int, fn_cls) -> dict:
+        """``--eval-function-path`` names a :class:`CheckpointEvalFn`: the weights are exported as an HF snapshot under
+        ``--eval-hf-dir`` and scored in the background while training goes on (``--eval-max-in-flight``,
+        ``--eval-overflow-policy``, ``--eval-keep-snapshots``; ``--eval-num-gpus`` / ``--eval-num-gpus-per-engine`` are
+        handed to the evaluator, which owns its engines). Results arrive in the metrics of a later step."""
+        import threading
+
+        from .rollout.eval_dispatch import EvalDispatcher
+
+        a = self.args
+        if getattr(self, "_eval_rt", None) is None:
+            evaluator = fn_cls(a)
+            evaluator.num_gpus = int(getattr(a, "eval_num_gpus", 0) or 0)
+            evaluator.num_gpus_per_engine = int(getattr(a, "eval_num_gpus_per_engine", 1) or 1)
+            ev_loop = asyncio.new_event_loop()
+            threading.Thread(target=ev_loop.run_forever, name="eval-dispatch", daemon=True).start()
+            box: list = []
+
+            async def export(rid: int, d: str) -> None:
+                pass  # the snapshot is written by the training thread before dispatch (it owns the device)
+
+            disp = EvalDispatcher(evaluator, export_fn=export, on_result=lambda rid, m: box.append((rid, m)),
+                                  max_in_flight=int(getattr(a, "eval_max_in_flight", 2) or 1),
+                                  overflow_policy=getattr(a, "eval_overflow_policy", "backpressure"),
+                                  keep_snapshots=int(getattr(a, "eval_keep_snapshots", 2) or 0))
+            self._eval_rt = (ev_loop, disp, box, evaluator)
+        ev_loop, disp, box, _ = self._eval_rt
+        base = getattr(a, "eval_hf_dir", None) or os.path.join(getattr(a, "save", None) or ".", "eval_snapshots")
+        d = os.path.join(base, f"rollout_{rollout_id}")
+        from .checkpoint import export_hf
+
+        export_hf(self.actor, d)  # every rank takes part; the first rank writes
+        if self.ps.rank == 0:
+            asyncio.run_coroutine_threadsafe(disp.dispatch(rollout_id, d), ev_loop).result()
+        out: dict = {}
+        while box:  # whatever has settled since the last call
+            rid, m = box.pop(0)
+            out.update({(k if k.startswith(("eval/", "perf/")) else f"eval/{k}"): v for k, v in m.items()})
+            out["eval/scored_rollout_id"] = rid
+        return out
+
+    def drain_evaluations(self) -> dict:
+        rt = getattr(self, "_eval_rt", None)
+        if rt is None or self.ps.rank != 0:
+            return {}
+        ev_loop, disp, box, evaluator = rt
+        asyncio.run_coroutine_threadsafe(disp.drain(), ev_loop).result()
+        evaluator.dispose()
+        out: dict = {}
+        while box:
+            rid, m = box.pop(0)
+            out.update({(k if k.startswith(("eval/", "perf/")) else f"eval/{k}"): v for k, v in m.items()})
+        return out
+
     def evaluate(self, rollout_id: int) -> dict:
+        fn_path = getattr(self.args, "eval_function_path", None)
+        if fn_path:
+            from .rollout.eval_dispatch import is_checkpoint_eval_fn
+
+            obj = load_function(fn_path)
+            if is_checkpoint_eval_fn(obj):
+                metrics = self._checkpoint_eval(rollout_id, obj)
+                if self.metric_checker is not None and metrics:
+                    self.metric_checker.update(metrics)
+                return metrics
         out = self.rollout_fn(RolloutFnEvalInput(rollout_id))
         if asyncio.iscoroutine(out):
             out = asyncio.run(out)
@@ -531,6 +627,11 @@ class RLLoop:
         from .checkpoint import wait_for_async_save
 
         wait_for_async_save()  # a background save must be complete before the job ends
+        tail = self.drain_evaluations()
+        if tail and history:
+            history[-1].update(tail)
+            if self.metric_checker is not None:
+                self.metric_checker.update(tail)
         if self.ft is not None:
             self.ft.stop()
         if self.metric_checker is not None:

@@ -51,25 +51,39 @@ def is_checkpoint_eval_fn(obj) -> bool:
 
 
 class EvalDispatcher:
+    """``max_in_flight`` evaluations may run at once (``--eval-max-in-flight``); a request beyond that waits for the
+    oldest one (``overflow_policy="backpressure"``) or is dropped and recorded in ``skipped`` (``"skip"``,
+    ``--eval-overflow-policy``). ``keep_snapshots`` newest export directories stay on disk after their evaluation
+    (``--eval-keep-snapshots``; 0 deletes each one as soon as it is scored)."""
+
     def __init__(self, eval_fn: Callable[..., Awaitable[dict]], export_fn: Optional[Callable[[int, str], Awaitable[None]]] = None,
-                 on_result: Optional[Callable[[int, dict], None]] = None, keep_exports: bool = False):
+                 on_result: Optional[Callable[[int, dict], None]] = None, keep_exports: bool = False, max_in_flight: int = 1,
+                 overflow_policy: str = "backpressure", keep_snapshots: int = 0):
+        assert overflow_policy in ("backpressure", "skip")
         self.eval_fn, self.export_fn, self.on_result = eval_fn, export_fn, on_result
         self.keep_exports = keep_exports
-        self._task: Optional[asyncio.Task] = None
+        self.max_in_flight, self.overflow_policy, self.keep_snapshots = max(1, int(max_in_flight)), overflow_policy, int(keep_snapshots)
+        self._tasks: list = []
+        self._kept: list = []
         self.results: list = []
         self.skipped: list = []
 
+    def _prune(self) -> None:
+        self._tasks = [t for t in self._tasks if not t.done()]
+
     @property
     def busy(self) -> bool:
-        return self._task is not None and not self._task.done()
+        self._prune()
+        return len(self._tasks) >= self.max_in_flight
 
     async def dispatch(self, rollout_id: int, export_dir: Optional[str] = None, force: bool = False) -> bool:
         """Returns True if an evaluation was started."""
         if self.busy:
-            if not force:
+            if not force and self.overflow_policy == "skip":
                 self.skipped.append(rollout_id)
                 return False
-            await self.drain()
+            await self._tasks[0]  # backpressure: the oldest evaluation has to settle first
+            self._prune()
         exported = None
         t_export = 0.0
         if self.export_fn is not None and export_dir is not None:
@@ -77,7 +91,7 @@ class EvalDispatcher:
             await self.export_fn(rollout_id, export_dir)  # the only part the training loop waits for
             t_export = time.perf_counter() - t0
             exported = export_dir
-        self._task = asyncio.ensure_future(self._settle(rollout_id, exported, t_export))
+        self._tasks.append(asyncio.ensure_future(self._settle(rollout_id, exported, t_export)))
         return True
 
     async def _settle(self, rollout_id: int, exported: Optional[str], t_export: float) -> None:
@@ -88,7 +102,9 @@ class EvalDispatcher:
             metrics = {"eval/skipped": 1.0, "eval/skip_reason": e.reason}
         finally:
             if exported is not None and not self.keep_exports:
-                shutil.rmtree(exported, ignore_errors=True)
+                self._kept.append(exported)
+                while len(self._kept) > self.keep_snapshots:
+                    shutil.rmtree(self._kept.pop(0), ignore_errors=True)
         metrics["perf/eval_time"] = time.perf_counter() - t0
         metrics["perf/eval_export_time"] = t_export
         self.results.append((rollout_id, metrics))
@@ -96,6 +112,6 @@ class EvalDispatcher:
             self.on_result(rollout_id, metrics)
 
     async def drain(self) -> None:
-        if self._task is not None:
-            await self._task
-            self._task = None
+        for t in list(self._tasks):
+            await t
+        self._tasks = []

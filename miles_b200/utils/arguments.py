@@ -140,6 +140,8 @@ def _add(group, flag: str, kind: str, default: Any, extra: dict) -> None:
             kw["choices"] = extra["choices"]
         if "nargs" in extra:
             kw["nargs"] = extra["nargs"]
+            if extra["nargs"] == "?":
+                kw["const"] = extra.get("const", True)  # the bare flag switches the feature on
         group.add_argument(*names, type=_KIND[kind], default=default, **kw)
 
 

@@ -24,7 +24,14 @@ def _bytes(t: torch.Tensor) -> bytes:
 
 
 def checksum(b: bytes, kind: str = "sha1") -> str:
-    return hashlib.blake2b(b, digest_size=16).hexdigest() if kind == "blake2" else hashlib.sha1(b).hexdigest()
+    """Per-tensor checksum of a published delta. The reference's flag names xxh3-128 / blake3 / adler32
+    (``--update-weight-delta-checksum``); xxhash and blake3 are not in this image, so the 128-bit kinds map to
+    blake2b-128 from hashlib, ``adler32`` is zlib's."""
+    if kind == "adler32":
+        return f"{zlib.adler32(b) & 0xffffffff:08x}"
+    if kind in ("blake2", "blake3", "xxh3-128"):
+        return hashlib.blake2b(b, digest_size=16).hexdigest()
+    return hashlib.sha1(b).hexdigest()
 
 
 class DiskDeltaWriter:
@@ -117,3 +124,34 @@ def apply_delta_dir(store, path: str) -> int:
         reader = DiskDeltaReader(os.path.dirname(path))
         store._delta_reader = reader
     return reader.apply(version, store.params)
+
+
+class DiskDeltaUpdater:
+    """Trainer side of ``--update-weight-transfer-mode disk-delta``: every weight update publishes a version directory
+    of per-tensor deltas (``--update-weight-delta-encoding xor | overwrite``, checksummed with
+    ``--update-weight-delta-checksum``) under ``--update-weight-disk-dir`` and tells each engine to pull it
+    (``POST /pull_weights``). Engines that fall behind apply the versions in order. Reference:
+    miles/backends/megatron_utils/update_weight/ (disk-delta transfer)."""
+
+    def __init__(self, actor, handles: list, directory: str, encoding: str = "xor", checksum_kind: str = "xxh3-128"):
+        self.actor, self.handles = actor, list(handles)
+        self.writer = DiskDeltaWriter(directory, encoding=encoding, checksum_kind=checksum_kind, rank=actor.ps.rank,
+                                      world=actor.ps.world_size)
+
+    def update(self) -> dict:
+        import time
+
+        import torch.distributed as dist
+
+        t0 = time.perf_counter()
+        version = self.actor.store.version
+        idx = self.writer.write(((n, p) for n, p in self.actor.store.params.items()), version)
+        if dist.is_initialized() and self.actor.ps.world_size > 1:
+            dist.barrier()  # every rank's file is in place before an engine reads the directory
+        vdir = os.path.join(self.writer.dir, f"v{version:08d}")
+        futs = [h.post_async("/pull_weights", {"path": vdir, "weight_version": version}) for h in self.handles]
+        for f in futs:
+            f.result()
+        dt = time.perf_counter() - t0
+        return {"perf/update_weights_time": dt, "perf/update_weights_total_time": dt, "perf/update_weights_bytes": idx["compressed_bytes"],
+                "perf/update_weights_raw_bytes": idx["raw_bytes"], "weight_version": version}

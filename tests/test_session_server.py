@@ -57,3 +57,46 @@ def test_rewritten_history_is_rejected():
     c.post("/sessions/s/v1/chat/completions", json={"messages": [{"role": "user", "content": "a"}]})
     bad = [{"role": "user", "content": "changed"}, {"role": "assistant", "content": "r1"}, {"role": "user", "content": "b"}]
     assert c.post("/sessions/s/v1/chat/completions", json={"messages": bad}).status_code == 409
+
+
+def test_tree_sessions_branch_pick_and_postprocess():
+    """Tree-serving sessions (--use-session-server v2): a request that rewrites history branches instead of being
+    refused, retried turns are dropped by the default picker, shared prefix tokens are trained once."""
+    from miles_b200.rollout.session.hooks import match_loose_tool_call, match_strict, resolve_matcher
+    from miles_b200.rollout.session.server import SessionStore
+
+    class Tok:
+        def encode(self, text, add_special_tokens=False):
+            return [ord(c) % 251 for c in text]
+
+        def decode(self, ids, skip_special_tokens=True):
+            return "".join(chr(97 + (i % 26)) for i in ids)
+
+    calls = []
+
+    def generate(ids, sp):
+        calls.append(list(ids))
+        out = [(len(ids) * 7 + k) % 200 for k in range(3)]
+        return {"output_ids": out, "output_token_logprobs": [-0.5] * 3, "finish_reason": "stop"}
+
+    store = SessionStore(Tok(), generate, tree=True)
+    sys_user = [{"role": "system", "content": "s"}, {"role": "user", "content": "q1"}]
+    r1 = store.chat("a", sys_user, {})
+    hist = sys_user + [{"role": "assistant", "content": r1["text"]}, {"role": "user", "content": "q2"}]
+    r2 = store.chat("a", hist, {})
+    assert calls[1][:len(calls[0])] == calls[0]                      # the second turn extends the first lineage
+    # the agent retries the second turn with an edited question: a branch after the first assistant message
+    hist_b = sys_user + [{"role": "assistant", "content": r1["text"]}, {"role": "user", "content": "q2 edited"}]
+    store.chat("a", hist_b, {})
+    assert calls[2][:len(calls[0]) + 3] == calls[1][:len(calls[0]) + 3] and calls[2] != calls[1]
+    tree = store._trees["a"]
+    assert len(tree.leaves()) == 2
+    samples = store.samples("a")
+    assert len(samples) == 2
+    # tokens of the shared first turn carry loss in one sample only
+    first_turn = sum(s["loss_mask"][:3] == [1, 1, 1] for s in samples)
+    assert first_turn == 1
+    assert match_strict({"role": "user", "content": "x"}, {"role": "user", "content": "x"})
+    tc = lambda i, a: {"role": "assistant", "content": None, "tool_calls": [{"id": i, "function": {"name": "f", "arguments": a}}]}
+    assert not match_strict(tc("1", '{"a": 1}'), tc("2", '{"a":1}')) and match_loose_tool_call(tc("1", '{"a": 1}'), tc("2", '{"a":1}'))
+    assert resolve_matcher("role_content_only")(tc("1", "{}"), {"role": "assistant", "content": None})
