@@ -13,7 +13,6 @@
 #include <stdint.h>
 
 #include "launchers.h"
-#include "pdl.cuh"
 
 namespace mb {
 namespace {
@@ -30,8 +29,6 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int num_splits) {
-  pdl_launch_dependents();  // chained launches (pdl.cuh)
-  pdl_wait();
   const long long bh = blockIdx.x;  // b * Hq + head
   const int d = threadIdx.x;
   float gm = -FLT_MAX;
@@ -83,8 +80,6 @@ decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
                   float* __restrict__ part_ml, bf16* __restrict__ out, int Hq, int Hk, int page_size, int max_pages,
                   int num_splits, float scale, long long num_slots, int* __restrict__ status) {
   extern __shared__ __align__(16) unsigned char dsm[];
-  pdl_launch_dependents();  // chained launches (pdl.cuh): q, the cache rows and the tables all come from predecessors
-  pdl_wait();
   bf16* Ks = reinterpret_cast<bf16*>(dsm);            // [2][TOK][LDS]
   bf16* Vs = Ks + 2 * STAGE_ELEMS;                    // [2][TOK][LDS]
   const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
@@ -289,25 +284,12 @@ int paged_decode_attention(const void* q, const void* k_cache, const void* v_cac
   // call rather than remembered per process (a second device would otherwise launch with the 48 KB default).
   cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
   if (e != cudaSuccess) return static_cast<int>(e);
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(WARPS * 32);
-  cfg.dynamicSmemBytes = SMEM;
-  cfg.stream = s;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  e = cudaLaunchKernelExC(&cfg, fn, args);
+  e = cudaLaunchKernel(fn, grid, dim3(WARPS * 32), args, SMEM, s);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (num_splits > 1) {
     const float *po = part_o, *pm = part_ml;
     void* margs[] = {&po, &pm, &op, &num_splits};
-    cfg.gridDim = dim3(B * Hq);
-    cfg.blockDim = dim3(D);
-    cfg.dynamicSmemBytes = 0;
-    e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(&decode_merge_kernel), margs);
+    e = cudaLaunchKernel(reinterpret_cast<const void*>(&decode_merge_kernel), dim3(B * Hq), dim3(D), margs, 0, s);
   }
   return static_cast<int>(e);
 }

@@ -17,7 +17,6 @@
 #include <stdint.h>
 
 #include "launchers.h"
-#include "pdl.cuh"
 
 namespace mb {
 namespace {
@@ -128,11 +127,6 @@ __global__ void __launch_bounds__(1024) small_gemv_kernel(const bf16* __restrict
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int r = lane >> 2, c = lane & 3;
   const int n0 = blockIdx.x * 16;
-  // chained launches (pdl.cuh): pull this CTA's 16 weight rows towards L2 while the preceding kernel finishes
-  pdl_launch_dependents();
-  for (long long i = static_cast<long long>(threadIdx.x) * 64; i < 16ll * K; i += static_cast<long long>(blockDim.x) * 64)
-    prefetch_l2(W + static_cast<long long>(n0) * K + i);
-  pdl_wait();
   int k_begin, k_end;
   k_range(K, warp, nwarps, k_begin, k_end);
   const bool live = r < T;
@@ -182,10 +176,6 @@ __global__ void __launch_bounds__(256) small_gemv_multi_kernel(const bf16* __res
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int r = lane >> 2, c = lane & 3;
   const int n0 = blockIdx.x * 16;
-  pdl_launch_dependents();
-  for (long long i = static_cast<long long>(threadIdx.x) * 64; i < 16ll * K; i += static_cast<long long>(blockDim.x) * 64)
-    prefetch_l2(W + static_cast<long long>(n0) * K + i);
-  pdl_wait();
   int k_begin, k_end;
   k_range(K, warp, nwarps, k_begin, k_end);
   float acc[G][4];
@@ -258,8 +248,6 @@ __global__ void __launch_bounds__(256) router_small_kernel(const float* __restri
                                                            int* __restrict__ pair_count, int* __restrict__ pair_list) {
   __shared__ int ids_s[TOK][32];
   __shared__ int cnt_s[1024];
-  pdl_launch_dependents();
-  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (warp < T) {
     const float* lg = logits + static_cast<long long>(warp) * E;
@@ -338,26 +326,25 @@ void small_gemv_direct(const void* x, int T, const void* norm_w, float eps, cons
     const bf16* wb = static_cast<const bf16*>(W);
     const bf16* rb = static_cast<const bf16*>(residual);
     const int f32 = out_fp32 ? 1 : 0;
-    if (T <= 16) launch_pdl(small_gemv_multi_kernel<2>, dim3(N / 16), dim3(32 * warps), 0, s, xb, T, wb, N, K, rb, out, f32);
-    else if (T <= 32) launch_pdl(small_gemv_multi_kernel<4>, dim3(N / 16), dim3(32 * warps), 0, s, xb, T, wb, N, K, rb, out, f32);
-    else launch_pdl(small_gemv_multi_kernel<8>, dim3(N / 16), dim3(32 * warps), 0, s, xb, T, wb, N, K, rb, out, f32);
+    if (T <= 16) small_gemv_multi_kernel<2><<<N / 16, 32 * warps, 0, s>>>(xb, T, wb, N, K, rb, out, f32);
+    else if (T <= 32) small_gemv_multi_kernel<4><<<N / 16, 32 * warps, 0, s>>>(xb, T, wb, N, K, rb, out, f32);
+    else small_gemv_multi_kernel<8><<<N / 16, 32 * warps, 0, s>>>(xb, T, wb, N, K, rb, out, f32);
     return;
   }
   const int threads = 32 * (warps_for(K) < 4 ? 4 : warps_for(K));  // the epilogue needs 128 threads
-  const bf16* nul = nullptr;
   if (norm_w)
-    launch_pdl(small_gemv_kernel<true>, dim3(N / 16), dim3(threads), 0, s, static_cast<const bf16*>(x), T,
-               static_cast<const bf16*>(norm_w), eps, static_cast<const bf16*>(W), N, K, static_cast<const bf16*>(residual), out,
-               out_fp32 ? 1 : 0);
+    small_gemv_kernel<true><<<N / 16, threads, 0, s>>>(static_cast<const bf16*>(x), T, static_cast<const bf16*>(norm_w),
+                                                       eps, static_cast<const bf16*>(W), N, K,
+                                                       static_cast<const bf16*>(residual), out, out_fp32 ? 1 : 0);
   else
-    launch_pdl(small_gemv_kernel<false>, dim3(N / 16), dim3(threads), 0, s, static_cast<const bf16*>(x), T, nul, eps,
-               static_cast<const bf16*>(W), N, K, static_cast<const bf16*>(residual), out, out_fp32 ? 1 : 0);
+    small_gemv_kernel<false><<<N / 16, threads, 0, s>>>(static_cast<const bf16*>(x), T, nullptr, eps,
+                                                        static_cast<const bf16*>(W), N, K,
+                                                        static_cast<const bf16*>(residual), out, out_fp32 ? 1 : 0);
 }
 
 void router_small(const float* logits, int T, int E, int K, bool renorm, int* topk_ids, float* topk_w, int* active,
                   int* pair_count, int* pair_list, cudaStream_t s) {
-  launch_pdl(router_small_kernel, dim3(1), dim3(256), 0, s, logits, T, E, K, renorm ? 1 : 0, topk_ids, topk_w, active, pair_count,
-             pair_list);
+  router_small_kernel<<<1, 256, 0, s>>>(logits, T, E, K, renorm ? 1 : 0, topk_ids, topk_w, active, pair_count, pair_list);
 }
 
 }  // namespace mb

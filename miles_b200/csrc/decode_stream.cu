@@ -27,7 +27,6 @@
 #include <stdint.h>
 
 #include "launchers.h"
-#include "pdl.cuh"
 #include "ptx.cuh"
 
 namespace mb {
@@ -127,10 +126,6 @@ __global__ void __launch_bounds__(THREADS, 1) stream_kernel(const StreamArgs a) 
     fence_barrier_init();
   }
   __syncthreads();
-  // Chained launches (pdl.cuh): the expert lists of the MoE forms come from the preceding router kernel, so those
-  // wait here; the dense form lets its producer warp start streaming weights at once and only the consumers wait.
-  pdl_launch_dependents();
-  if (a.active) pdl_wait();
   const int n_groups = a.active ? a.active[0] : 1;
   const int tiles = a.rows / (ROWS * RT);
   const int total = n_groups * tiles;
@@ -179,7 +174,6 @@ __global__ void __launch_bounds__(THREADS, 1) stream_kernel(const StreamArgs a) 
     }
   } else {
     // ------------------------------------------------------------------ consumers
-    if (!a.active) pdl_wait();  // activations (and the output buffer) belong to the preceding kernels
     const int cw = warp - 1;
     const int r = lane >> 2, c = lane & 3;
     const int ct = threadIdx.x - 32;             // 0..255
@@ -316,9 +310,13 @@ __global__ void __launch_bounds__(THREADS, 1) stream_kernel(const StreamArgs a) 
 template <int CPW, int RT, bool EXACT>
 int launch_variant(const StreamArgs& a, int grid, int smem, cudaStream_t s) {
   auto kern = stream_kernel<CPW, RT, EXACT>;
-  // per (function, device): cheap enough to set on every launch
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES + 1024) != cudaSuccess) return -1;
-  return launch_pdl(kern, dim3(grid), dim3(THREADS), static_cast<size_t>(smem), s, a) == cudaSuccess ? 0 : -1;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES + 1024) != cudaSuccess) return -1;
+    attr_set = true;
+  }
+  kern<<<grid, THREADS, smem, s>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 int g_sms = 0;

@@ -9,7 +9,6 @@
 #include <stdint.h>
 
 #include "launchers.h"
-#include "pdl.cuh"
 
 namespace mb {
 namespace {
@@ -71,8 +70,6 @@ __global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __res
                                    const bf16* __restrict__ w, bf16* __restrict__ y, bf16* __restrict__ res_out,
                                    float* __restrict__ rstd, int H, float eps) {
   __shared__ float red[32];
-  pdl_launch_dependents();  // chained launches (pdl.cuh): nothing to prefetch here, the inputs are the predecessor's
-  pdl_wait();
   const long long row = blockIdx.x;
   const bf16* xr = x + row * H;
   float ss = 0.f;
@@ -174,8 +171,6 @@ __global__ void qk_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16
                                         const int* __restrict__ slot_mapping, int T, int Hq, int Hk,
                                         float theta, float eps, int use_norm) {
   constexpr int D = 128;
-  pdl_launch_dependents();
-  pdl_wait();
   const int warps_per_block = blockDim.x >> 5;
   const long long gw = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -610,8 +605,9 @@ int grid_for(long long work_items, int threads, int cap = 148 * 8) {
 void rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, float* rstd, int T, int H,
                  float eps, cudaStream_t s) {
   if (T <= 0) return;
-  launch_pdl(rmsnorm_fwd_kernel<256>, dim3(T), dim3(256), 0, s, static_cast<const bf16*>(x), static_cast<const bf16*>(res),
-             static_cast<const bf16*>(w), static_cast<bf16*>(y), static_cast<bf16*>(res_out), rstd, H, eps);
+  rmsnorm_fwd_kernel<256><<<T, 256, 0, s>>>(static_cast<const bf16*>(x), static_cast<const bf16*>(res),
+                                            static_cast<const bf16*>(w), static_cast<bf16*>(y),
+                                            static_cast<bf16*>(res_out), rstd, H, eps);
 }
 
 int rmsnorm_bwd_num_partials(int T) { return T < 296 ? (T < 1 ? 1 : T) : 296; }
@@ -633,10 +629,10 @@ void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int
   const long long warps = static_cast<long long>(T) * (Hq + 2 * Hk);
   const int wpb = 8;
   const long long blocks = (warps + wpb - 1) / wpb;
-  launch_pdl(qk_norm_rope_fwd_kernel, dim3(static_cast<unsigned>(blocks)), dim3(wpb * 32), 0, s,
-             static_cast<const bf16*>(qkv), static_cast<const bf16*>(qw), static_cast<const bf16*>(kw), pos,
-             static_cast<bf16*>(q_out), static_cast<bf16*>(k_out), q_rstd, k_rstd, static_cast<bf16*>(k_cache),
-             static_cast<bf16*>(v_cache), slot_mapping, T, Hq, Hk, theta, eps, use_norm ? 1 : 0);
+  qk_norm_rope_fwd_kernel<<<static_cast<unsigned>(blocks), wpb * 32, 0, s>>>(
+      static_cast<const bf16*>(qkv), static_cast<const bf16*>(qw), static_cast<const bf16*>(kw), pos,
+      static_cast<bf16*>(q_out), static_cast<bf16*>(k_out), q_rstd, k_rstd, static_cast<bf16*>(k_cache),
+      static_cast<bf16*>(v_cache), slot_mapping, T, Hq, Hk, theta, eps, use_norm ? 1 : 0);
 }
 
 void qk_norm_rope_bwd(const void* dq, const void* dk, const void* dv, const void* qkv, const void* qw, const void* kw,

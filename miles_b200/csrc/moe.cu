@@ -20,7 +20,6 @@
 #include <stdint.h>
 
 #include "launchers.h"
-#include "pdl.cuh"
 
 namespace mb {
 namespace {
@@ -418,8 +417,6 @@ __device__ __forceinline__ uint4 pack8(const float (&a)[8]) {
 __global__ void combine_kernel(const bf16* __restrict__ y_perm, const int* __restrict__ dest_row,
                                const float* __restrict__ topk_w, const bf16* __restrict__ residual,
                                bf16* __restrict__ out, int T, int K, int H) {
-  pdl_launch_dependents();  // chained launches (pdl.cuh)
-  pdl_wait();
   const int vec_per_row = H / 8;
   const long long total = static_cast<long long>(T) * vec_per_row;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
@@ -531,8 +528,8 @@ void moe_permute(const void* x, const int* row_src, const int* num_m_tiles, void
 void moe_combine(const void* y_perm, const int* dest_row, const float* topk_w, const void* residual, void* out, int T,
                  int K, int H, cudaStream_t s) {
   if (T <= 0) return;
-  launch_pdl(combine_kernel, dim3(grid_for(static_cast<long long>(T) * (H / 8), 256)), dim3(256), 0, s,
-             static_cast<const bf16*>(y_perm), dest_row, topk_w, static_cast<const bf16*>(residual), static_cast<bf16*>(out), T, K, H);
+  combine_kernel<<<grid_for(static_cast<long long>(T) * (H / 8), 256), 256, 0, s>>>(
+      static_cast<const bf16*>(y_perm), dest_row, topk_w, static_cast<const bf16*>(residual), static_cast<bf16*>(out), T, K, H);
 }
 
 void moe_unpermute_sum(const void* dx_perm, const int* dest_row, void* dx, int T, int K, int H, cudaStream_t s) {

@@ -6,7 +6,7 @@ import pytest
 from miles_b200.models import get_config
 from miles_b200.utils import http_utils, lifecycle
 from miles_b200.utils.eval_config import build_eval_configs
-from miles_b200.utils.metric_utils import device_peak_tflops, forward_flops, mfu, train_step_flops
+from miles_b200.utils.flops_utils import device_peak_tflops, forward_flops, mfu, train_step_flops
 
 
 def test_http_retries_then_succeeds_and_gives_up_on_client_errors():
