@@ -85,7 +85,7 @@ def main() -> None:
         floor_ms = (ns.layers * layer_bytes + head_bytes) / (hbm * 1e9) * 1e3
         print(json.dumps({"what": "decode_step", "model": ns.model, "layers": ns.layers, "batch": B, "ctx": ns.ctx, "ms_per_step": ms,
                           "us_per_layer": (ms - head_bytes / (hbm * 1e9) * 1e3) * 1e3 / ns.layers, "layer_mbytes": layer_bytes / 1e6,
-                          "hbm_floor_ms": floor_ms, "frac_of_measured_hbm": floor_ms / ms, "pdl": os.environ.get("MILES_B200_PDL", "1"),
+                          "hbm_floor_ms": floor_ms, "frac_of_measured_hbm": floor_ms / ms,
                           "clocks": clocks}), flush=True)
 
 

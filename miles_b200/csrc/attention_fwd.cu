@@ -402,12 +402,8 @@ int flash_attn_fwd(const void* q, long long q_ld, const void* k, long long k_ld,
   if (fa_make_map(&mq, q, Tq, static_cast<long long>(Hq) * HD, q_ld)) return -1;
   if (fa_make_map(&mk, k, Tkv, static_cast<long long>(Hk) * HD, k_ld)) return -1;
   if (fa_make_map(&mv, v, Tkv, static_cast<long long>(Hk) * HD, v_ld)) return -1;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM) != cudaSuccess)
-      return fa_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed for attention");
-    attr_set = true;
-  }
+  if (cudaFuncSetAttribute(fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM) != cudaSuccess)  // per device
+    return fa_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed for attention");
   FaArgs a;
   a.tiles = reinterpret_cast<const int4*>(tiles);
   a.num_tiles = num_tiles;

@@ -310,11 +310,8 @@ __global__ void __launch_bounds__(THREADS, 1) stream_kernel(const StreamArgs a) 
 template <int CPW, int RT, bool EXACT>
 int launch_variant(const StreamArgs& a, int grid, int smem, cudaStream_t s) {
   auto kern = stream_kernel<CPW, RT, EXACT>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES + 1024) != cudaSuccess) return -1;
-    attr_set = true;
-  }
+  // the attribute belongs to the (function, device) pair: set on every launch rather than once per process
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES + 1024) != cudaSuccess) return -1;
   kern<<<grid, THREADS, smem, s>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -566,12 +566,8 @@ int launch(const GemmProblem& p, const KArgs& ka, cudaStream_t stream) {
   if (make_map(&ma, p.a, A_MN ? BLOCK_K : BLOCK_M)) return -1;
   if (make_map(&mb_, p.b, B_MN ? BLOCK_K : BLOCK_N)) return -1;
   auto kern = gemm_bf16_kernel<BLOCK_N, A_MN, B_MN, STAGES>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
-      return fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
-    attr_set = true;
-  }
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)  // per (function, device)
+    return fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -427,12 +427,8 @@ int launch_mx(const MxGemmProblem& q, cudaStream_t stream) {
   if (make_byte_map(&ma, q.a, q.a_rows, kbytes, q.a_pitch_bytes, BM)) return -1;
   if (make_byte_map(&mb_, q.b, q.b_rows, kbytes, q.b_pitch_bytes, BN)) return -1;
   auto kern = gemm_mx_kernel<KIND, BN, STAGES>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
-      return mx_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
-    attr_set = true;
-  }
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)  // per (function, device)
+    return mx_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
   MxArgs ka;
   memset(&ka, 0, sizeof(ka));
   ka.mode = q.mode;

@@ -95,12 +95,17 @@ class Fleet:
                     raise TimeoutError(f"{len(pending)} engines did not come up within {wait_s:.0f} s")
                 time.sleep(0.3)
 
-    def start_router(self, port: int, model: Optional[str] = None, policy: str = "least_inflight", wait_s: float = 60.0) -> str:
+    def start_router(self, port: int, model: Optional[str] = None, policy: str = "least_inflight", wait_s: float = 60.0,
+                     failure_threshold: Optional[int] = None, timeout: Optional[float] = None,
+                     max_connections: Optional[int] = None) -> str:
         """One router process in front of the engines of ``model`` (all engines if None); returns its URL. Generation
         requests go through it, weight updates still address the engines themselves."""
         cmd = [sys.executable, "-m", "miles_b200.router.router", "--port", str(port), "--policy", policy]
         for u in self.urls(model):
             cmd += ["--worker", u]
+        for flag, v in (("--failure-threshold", failure_threshold), ("--timeout", timeout), ("--max-connections", max_connections)):
+            if v is not None:
+                cmd += [flag, str(v)]
         proc = subprocess.Popen(cmd, env=dict(os.environ, **self.env))
         self.__dict__.setdefault("routers", []).append(proc)
         url = f"http://127.0.0.1:{port}"

@@ -47,6 +47,17 @@ def register_extra(app, engine, state: dict) -> None:
             engine.update_weight_version(b["weight_version"])
         return {"success": True, "num_tensors": n}
 
+    @app.post("/requantize_weights")
+    async def requantize_weights(req: Request):
+        """Serve the projections and experts from block-scaled copies (``mxfp8`` / ``nvfp4``) of the weights the engine
+        holds now; called by the trainer after a weight update when ``--weight-sync-quant`` is set."""
+        b = await req.json()
+        fmt = b.get("format", "none")
+        fn = getattr(engine.model, "enable_block_scaled", None)
+        if fmt in ("mxfp8", "nvfp4") and fn is not None:
+            return {"success": True, "num_tensors": await asyncio.to_thread(fn, fmt)}
+        return {"success": False, "reason": f"format {fmt!r} is not served by this engine"}
+
     @app.get("/parallelism_config")
     async def parallelism_config():
         st = engine.store

@@ -224,7 +224,10 @@ class RLLoop:
             box[0] = ",".join(self.fleet.updatable_urls() or self.fleet.urls())
             if getattr(a, "use_miles_router", False):
                 # generation goes through one router process; weight updates still address the engines themselves
-                box.append(self.fleet.start_router(a.rollout_fleet_base_port + len(self.fleet.engines) + 1))
+                box.append(self.fleet.start_router(
+                    a.rollout_fleet_base_port + len(self.fleet.engines) + 1,
+                    failure_threshold=getattr(a, "miles_router_health_check_failure_threshold", None),
+                    timeout=getattr(a, "miles_router_timeout", None), max_connections=getattr(a, "miles_router_max_connections", None)))
         if self.ps.world_size > 1:
             box = box + [None] * (2 - len(box))
             dist.broadcast_object_list(box, src=0)
@@ -432,7 +435,11 @@ class RLLoop:
 
     def offload_rollout(self) -> None:
         if self.engine is not None and self.args.offload_rollout:
-            self.engine.release_memory_occupation(("kv_cache", "cuda_graph"))
+            # --offload-rollout-level: "kv_cache" frees the cache (and the graphs that point into it); "weight" is
+            # meaningful for engines with weights of their own (a colocated engine reads the trainer's)
+            level = getattr(self.args, "offload_rollout_level", None) or ["kv_cache", "weight"]
+            tags = tuple(t for t in ("kv_cache",) if t in level) + ("cuda_graph",)
+            self.engine.release_memory_occupation(tags)
 
     def onload_rollout(self) -> None:
         if self.engine is not None and self.args.offload_rollout:
@@ -447,6 +454,9 @@ class RLLoop:
 
     def _train_once(self, rollout_id: int, data: dict) -> dict:
         a = self.args
+        if getattr(self, "_remerge_before_train", False):
+            self.actor.lora.merge()
+            self._remerge_before_train = False
         local = copy.copy(self.actor.args)
         metrics = {}
         # every rank already holds exactly its own share: train on it without a DP re-split
@@ -454,6 +464,9 @@ class RLLoop:
         self.actor._local_data = True
         if self.critic is not None:
             metrics.update({k.replace("train/", "train/critic_"): v for k, v in self.critic.train_critic(rollout_id, data).items()})
+            if rollout_id < int(getattr(a, "num_critic_only_steps", 0) or 0):
+                metrics["train/actor_frozen"] = 1.0  # value-function warm-up: the actor does not train yet
+                return metrics
         metrics.update(self.actor.train(rollout_id, data))
         self.h2d_bytes += self.actor.h2d_bytes
         return metrics
@@ -461,8 +474,31 @@ class RLLoop:
     def update_weights(self) -> dict:
         if getattr(self.args, "debug_skip_weight_update", False):
             return {}
+        lora = getattr(self.actor, "lora", None)
+        if lora is not None and getattr(self.args, "lora_train_only", False):
+            # --lora-train-only: the engines keep serving the frozen base policy; the merged adapter is taken out of the
+            # live weights for the hand-off and put back for the next training step
+            for n, b in lora.base.items():
+                self.actor.store.params[n].copy_(b)
+            try:
+                return self._update_weights()
+            finally:
+                if self.engine is None or self.engine.store is not self.actor.store:
+                    lora.merge()
+                else:
+                    self._remerge_before_train = True  # shared weights: merge again right before training
+        return self._update_weights()
+
+    def _update_weights(self) -> dict:
         if getattr(self.args, "rollout_engine_urls", None):
             out = self.weight_updater.update() if self.weight_updater is not None else {}
+            fmt = getattr(self.args, "weight_sync_quant", "none")
+            if fmt != "none" and self.ps.rank == 0:
+                # --weight-sync-quant: the engines re-quantise what just arrived and serve from the block-scaled copies
+                from .weight_sync.broadcast import HttpEngineHandle
+
+                for u in [x for x in self.args.rollout_engine_urls.split(",") if x]:
+                    HttpEngineHandle(u).post("/requantize_weights", {"format": fmt})
             if self.ps.world_size > 1:
                 dist.barrier()  # nobody generates with the old weights while the first rank is still sending
             return out

@@ -118,6 +118,23 @@ class LoRAManager:
             w.add_((self.scale * (b @ a)).to(w.dtype))
 
     @torch.no_grad()
+    def check_merged(self, params: Optional[dict] = None, atol: float = 2e-2) -> None:
+        """``--check-lora-weight-equal``: every targeted weight the rollout engine serves (``params``, default the
+        trainer's own live weights) must equal ``base + scale * B @ A`` of the adapter just trained (up to the
+        rounding of the weight dtype); a missing tensor or a mismatch raises."""
+        params = params if params is not None else self.store.params
+        want = {n: b.detach().float().clone() for n, b in self.base.items()}
+        for t, a, b in zip(self.targets, self.A, self.B):
+            self._slice(want[t.native], t).add_(self.scale * (b @ a))
+        for n, w in want.items():
+            if n not in params:
+                raise AssertionError(f"adapter sync check: the engine has no tensor {n}")
+            got = params[n].detach().float()
+            err = (got - w.to(got.device)).abs().max().item()
+            tol = atol * max(w.abs().max().item(), 1e-6)
+            assert err <= tol, f"adapter sync check: {n} differs from base + scale*B@A by {err} (tolerance {tol})"
+
+    @torch.no_grad()
     def grads_from_weight_grads(self) -> None:
         """Project the full weight gradients (already accumulated by the backward GEMMs) onto the adapters."""
         for t, a, b in zip(self.targets, self.A, self.B):

@@ -41,8 +41,12 @@ class AdapterSpec:
 
 
 class AdapterRegistry:
-    def __init__(self, max_slots: int = 8):
+    def __init__(self, max_slots: int = 8, max_adapter_batch: Optional[int] = None, samples_per_prompt: int = 1):
+        """``max_adapter_batch``: upper bound on an adapter's samples per optimizer step (its ``rollout_batch_size`` x
+        ``samples_per_prompt``), checked when the adapter registers (``--multi-lora-max-adapter-global-batch-size``,
+        default four times the global batch size)."""
         self.max_slots = max_slots
+        self.max_adapter_batch, self.samples_per_prompt = max_adapter_batch, max(1, samples_per_prompt)
         self._lock = threading.Lock()
         self._adapters: dict = {}
         self.version = 0  # bumped on every change; the service loop compares it with its last snapshot
@@ -54,6 +58,10 @@ class AdapterRegistry:
                 raise ValueError(f"adapter {spec.name!r} is already registered")
             if len(live) >= self.max_slots:
                 raise RuntimeError(f"all {self.max_slots} adapter slots are in use")
+            if self.max_adapter_batch and spec.rollout_batch_size:
+                n = spec.rollout_batch_size * self.samples_per_prompt
+                if n > self.max_adapter_batch:
+                    raise ValueError(f"adapter {spec.name!r} asks for {n} samples per step, more than the bound {self.max_adapter_batch}")
             used = {a.slot for a in live}
             spec.slot = next(i for i in range(self.max_slots) if i not in used)
             spec.state = AdapterState.REGISTERED

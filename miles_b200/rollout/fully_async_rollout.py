@@ -151,9 +151,21 @@ class FullyAsyncRolloutFn:
         target = self.args.rollout_batch_size
         data: list = []
         t0 = time.perf_counter()
+        # multi-adapter service: train on what is ready once ``rollout_coalesce_wait_s`` have passed since the first group
+        # arrived; fail if not a single group arrives within ``rollout_empty_wait_s`` (0 = wait for the full batch forever)
+        coalesce = float(getattr(self.args, "rollout_coalesce_wait_s", 0.0) or 0.0)
+        empty_wait = float(getattr(self.args, "rollout_empty_wait_s", 0.0) or 0.0)
+        t_first = None
         while len(data) < target:
             data += self.buffer.get(target - len(data), self.state.client.weight_version())
+            if data and t_first is None:
+                t_first = time.perf_counter()
             if len(data) < target:
+                now = time.perf_counter()
+                if coalesce and t_first is not None and now - t_first >= coalesce:
+                    break
+                if empty_wait and not data and now - t0 >= empty_wait:
+                    raise TimeoutError(f"no finished rollout group within {empty_wait:.0f} s")
                 await asyncio.sleep(0.001)
         data.sort(key=lambda g: g[0].index or 0)
         m = {f"rollout/async_buffer/{k}": v for k, v in self.buffer.stats.items()}

@@ -20,6 +20,16 @@ class GenerateState:
             max_new_tokens=args.rollout_max_response_len, stop_token_ids=list(args.rollout_stop_token_ids or []),
             skip_special_tokens=getattr(args, "rollout_skip_special_tokens", False),
         )
+        # --rollout-stop: stop words. A word that is one token becomes a stop token id (the engine stops on it); a longer
+        # one is matched on the decoded response afterwards and the response is cut after its first occurrence.
+        self.stop_strings: list = []
+        for word in (getattr(args, "rollout_stop", None) or []):
+            ids = tokenizer.encode(word, add_special_tokens=False) if tokenizer is not None else []
+            if len(ids) == 1:
+                self.sampling_params["stop_token_ids"].append(int(ids[0]))
+            else:
+                assert tokenizer is not None, "--rollout-stop with words needs a tokenizer (--hf-checkpoint); use --rollout-stop-token-ids"
+                self.stop_strings.append(word)
         self.aborted = False
 
     def eval_sampling_params(self) -> dict:
@@ -69,6 +79,16 @@ def update_sample_from_response(state: GenerateState, sample: Sample, input_ids:
     meta = output["meta_info"]
     new_ids = list(output["output_ids"])
     lps = [lp for lp, _ in meta.get("output_token_logprobs", [])]
+    if getattr(state, "stop_strings", None) and state.tokenizer is not None and new_ids:
+        # cut after the first stop word: the shortest token prefix whose decoding contains it
+        text = state.tokenizer.decode(new_ids, skip_special_tokens=False)
+        hit = min((text.find(w) + len(w) for w in state.stop_strings if w in text), default=-1)
+        if hit >= 0:
+            k = next((k for k in range(1, len(new_ids) + 1)
+                      if len(state.tokenizer.decode(new_ids[:k], skip_special_tokens=False)) >= hit), len(new_ids))
+            new_ids, lps = new_ids[:k], lps[:k]
+            output = dict(output, text=state.tokenizer.decode(new_ids, skip_special_tokens=True))
+            meta = dict(meta, finish_reason={"type": "stop"})
     if not sample.tokens or sample.response_length == 0:
         sample.tokens = list(input_ids)
     sample.tokens = sample.tokens + new_ids

@@ -53,7 +53,7 @@ def convert_samples_to_train_data(args, samples: Sequence[Sample]) -> dict:
             raw, [s.group_index if s.group_index is not None else i for i, s in enumerate(samples)],
             [s.effective_rollout_id if s.effective_rollout_id is not None else i for i, s in enumerate(samples)],
             advantage_estimator=args.advantage_estimator,
-            normalize=not getattr(args, "disable_rewards_normalization", False),
+            normalize=getattr(args, "rewards_normalization", True) is not False,  # --disable-rewards-normalization
             std_normalization=getattr(args, "grpo_std_normalization", True) and not getattr(args, "disable_grpo_std_normalization", False),
         )
     loss_masks = []

@@ -159,8 +159,11 @@ def main(argv=None) -> None:
     ap.add_argument("--policy", default="least_inflight", choices=["least_inflight", "round_robin", "consistent_hashing"])
     ap.add_argument("--failure-threshold", type=int, default=3)
     ap.add_argument("--health-interval", type=float, default=5.0)
+    ap.add_argument("--timeout", type=float, default=600.0, help="seconds a forwarded request may take")
+    ap.add_argument("--max-connections", type=int, default=1024)
     ns = ap.parse_args(argv)
-    router = MilesRouter(failure_threshold=ns.failure_threshold, health_interval=ns.health_interval, policy=ns.policy)
+    router = MilesRouter(timeout=ns.timeout, max_connections=ns.max_connections, failure_threshold=ns.failure_threshold,
+                         health_interval=ns.health_interval, policy=ns.policy)
     for w in ns.worker:
         router.add_worker(w)
     uvicorn.run(build_router_app(router), host=ns.host, port=ns.port, log_level="warning")

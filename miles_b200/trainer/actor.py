@@ -217,6 +217,14 @@ class TrainActor:
             self.loaded_rollout_id = load_checkpoint(self, args.load, getattr(args, "ckpt_step", None))
             if getattr(args, "reset_optimizer_states", False) and self.opt is not None:
                 self.opt.reset_state()  # keep the weights (and their fp32 master), restart the moments and the schedule
+        if getattr(args, "use_opd", False) and getattr(args, "opd_type", None) == "megatron" and role == "actor" \
+                and getattr(args, "opd_teacher_load", None):
+            # on-policy distillation against a teacher the trainer itself evaluates: its weights live in a pinned host
+            # copy and are swapped in for one log-prob pass per rollout (--opd-teacher-load / --opd-teacher-ckpt-step)
+            from ..checkpoint import load_weights_into_backup
+
+            self.backup_weights("teacher")
+            load_weights_into_backup(self, "teacher", args.opd_teacher_load, getattr(args, "opd_teacher_ckpt_step", None))
         need_ref = (args.kl_coef != 0 or args.use_kl_loss) and role == "actor"
         if need_ref:
             self.backup_weights("ref")
@@ -287,6 +295,21 @@ class TrainActor:
                          lr_warmup_iters=warmup, lr_decay_iters=a.lr_decay_iters or 0, min_lr=a.min_lr,
                          skip_nonfinite=not getattr(a, "no_check_for_nan_in_loss_and_grad", False),
                          lr_wsd_decay_iters=a.lr_wsd_decay_iters or 0)
+        if getattr(a, "stream_optimizer_state_to_disk", False) or getattr(a, "offload_train_target", "cpu") == "disk":
+            # optimizer state in files on a local disk, streamed through the device bucket by bucket
+            # (--stream-optimizer-state-to-disk, or --offload-train-target disk): for models whose state fits neither
+            # in device nor in host memory
+            from .nvme_optimizer import NvmeStreamedAdam
+
+            d = getattr(a, "offload_train_disk_dir", None) or os.path.join(getattr(a, "save", None) or "/tmp", "optimizer_stream")
+            mdt = getattr(a, "stream_optimizer_state_moment_dtype", "fp32")
+            assert mdt in ("fp32", "bf16", "fp16"), "--stream-optimizer-state-moment-dtype: fp8 moments are not built"
+            self.dense_shard = None
+            self.opt = NvmeStreamedAdam(self.store, os.path.join(d, f"rank_{self.ps.rank:05d}"), lr=oc.lr,
+                                        betas=(oc.beta1, oc.beta2), eps=oc.eps, weight_decay=oc.weight_decay,
+                                        bucket_elems=max(1, int(getattr(a, "offload_train_disk_chunk_mb", 256)) * (1 << 20) // 4),
+                                        moment_dtype=mdt, clip_grad=oc.clip_grad)
+            return
         if getattr(a, "optimizer", "adam") == "muon":
             from .muon import Muon, MuonConfig
 
@@ -538,7 +561,11 @@ class TrainActor:
                 t = torch.tensor([n_mb], dtype=torch.int64, device=self.device)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 n_mb = int(t.item())
-            if self.ps.world_size > 1:
+            if getattr(a, "balance_by_flops", False):
+                # partition by estimated FLOPs (linear + quadratic attention term) instead of token counts: sequences of
+                # very different lengths then cost the micro-batches about the same time
+                kw["weights"] = "flops"
+            if self.ps.world_size > 1 or getattr(a, "balance_by_flops", False):
                 mbs = build_micro_batches(data, num_micro_batches=max(n_mb, 1), **kw)
             else:
                 mbs = build_micro_batches(data, max_tokens_per_gpu=a.max_tokens_per_gpu, **kw)
@@ -617,6 +644,11 @@ class TrainActor:
         if "ref" in self.weights_backup and a.loss_type == "policy_loss":
             with T.context("ref_log_probs"), self.with_weights("ref"):
                 self.compute_log_probs(mbs, "ref_log_probs")
+        if "teacher" in self.weights_backup and a.loss_type == "policy_loss":
+            with T.context("teacher_log_probs"), self.with_weights("teacher"):
+                self.compute_log_probs(mbs, "teacher_log_probs")
+            for mb in mbs:
+                mb.teacher_log_probs = mb.extras["teacher_log_probs"]
         for k in ("train_log_probs", "train_fwd_bwd", "train_optimizer"):
             T.reset(k)
         if getattr(a, "custom_megatron_before_log_prob_hook_path", None):

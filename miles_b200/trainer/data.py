@@ -150,12 +150,18 @@ def pack_samples(data: dict, idxs: Sequence[int], pin: bool = False, num_moe_lay
 
 def build_micro_batches(data: dict, *, max_tokens_per_gpu: Optional[int] = None, micro_batch_size: Optional[int] = None,
                         num_micro_batches: Optional[int] = None, pin: bool = False, num_moe_layers: int = 0,
-                        top_k: int = 0, sample_ids: Optional[Sequence[int]] = None) -> list[MicroBatch]:
-    """Dynamic (token-capped, first-fit) or fixed-size micro-batches over the local samples."""
+                        top_k: int = 0, sample_ids: Optional[Sequence[int]] = None, weights: str = "tokens",
+                        flops_quadratic: float = 1.0 / 12288.0) -> list[MicroBatch]:
+    """Dynamic (token-capped, first-fit) or fixed-size micro-batches over the local samples. With
+    ``num_micro_batches`` the samples are spread over that many bins by balanced partitioning of their cost:
+    token counts, or with ``weights="flops"`` an estimate ``n * (1 + n * flops_quadratic)`` in which the causal
+    attention term grows with the square of the length (the default ratio is that of a 2048-wide model with 48
+    heads-times-dim per layer; only the relative size of the two terms matters)."""
     ids = list(range(len(data["tokens"]))) if sample_ids is None else list(sample_ids)
     lens = [len(data["tokens"][i]) for i in ids]
     if num_micro_batches is not None:
-        bins = balanced_bins(lens, num_micro_batches)
+        cost = lens if weights != "flops" else [int(n * (1.0 + n * flops_quadratic)) + 1 for n in lens]
+        bins = balanced_bins(cost, num_micro_batches)
     elif max_tokens_per_gpu:
         bins = first_fit_pack(lens, max_tokens_per_gpu)
     else:

@@ -145,6 +145,19 @@ IGNORED = {
     "custom_update_weight_post_write_path": "no weight files are written during an in-memory update",
     "update_weight_local_checkpoint_dir": "disk-delta updates write under --update-weight-disk-dir",
     "low_memory_resume": "resume loads one rank file at a time already",
+    # batching / scheduling details of the reference's Ray pipeline
+    "allow_partial_train_step": "trailing samples of a rollout always train as a smaller last step",
+    "data_pad_size_multiplier": "packed micro-batches are not padded (the kernels take any token count)",
+    "delay_split_train_data_by_dp": "a rank trains on the samples its own engine generated: there is no split to delay",
+    "fetch_trajectory_retry_times": "the reference does not read it either",
+    "min_batch_collection_ratio": "the reference does not read it either",
+    "rollout_task_type": "the reference does not read it either",
+    "dumper_source_patcher_config_inference": "the source patcher rewrites Megatron / SGLang sources, which do not exist here",
+    "dumper_source_patcher_config_train": "the source patcher rewrites Megatron / SGLang sources, which do not exist here",
+    "mtp_loss_scaling_factor": "multi-token prediction is rejected (--mtp-num-layers)",
+    "opd_top_k_strategy": "read by top-k distillation only, which is rejected (--opd-log-prob-top-k)",
+    "opd_reward_weight_mode": "read by top-k distillation only, which is rejected (--opd-log-prob-top-k)",
+    "opd_teacher_key": "routes between remote teachers, which are rejected (--opd-teacher-urls)",
 }
 
 

@@ -45,6 +45,18 @@ def forward_flops(cfg, seq_lens: Sequence[int]) -> float:
     return tokens * per_tok + attn
 
 
+def train_step_flops(cfg, seq_lens: Sequence[int], recompute: bool = True, extra_forwards: int = 1) -> float:
+    """Forward + backward (2x) + recomputed forward, plus ``extra_forwards`` log-prob passes (old / reference policy)."""
+    return forward_flops(cfg, seq_lens) * (3.0 + (1.0 if recompute else 0.0) + extra_forwards)
+
+
+def mfu(flops: float, seconds: float, n_gpus: int = 1, peak_tflops: Optional[float] = None) -> float:
+    peak = device_peak_tflops(override=peak_tflops)
+    if peak <= 0 or seconds <= 0:
+        return 0.0
+    return flops / seconds / (peak * 1e12 * n_gpus)
+
+
 def perf_metrics(cfg, seq_lens: Sequence[int], train_time: float, num_gpus: int = 1, log_prob_time: float = 0.0,
                  ref_time: float = 0.0, peak_tflops: Optional[float] = None) -> dict:
     f = forward_flops(cfg, seq_lens)

@@ -72,10 +72,37 @@ def sync_weights(actor, engines: Sequence, mode: str | None = None) -> dict:
         e.continue_generation()
     t1 = time.perf_counter()
     if getattr(args, "check_weight_update_equal", False):
+        check_engines_hold_trainer_weights(actor, engines)
+    if getattr(args, "check_lora_weight_equal", False) and getattr(actor, "lora", None) is not None:
         for e in engines:
+            actor.lora.check_merged(e.store.params)
+    return {"perf/update_weights_time": t1 - t_paused, "perf/update_weights_total_time": t1 - t0,
+            "perf/update_weights_bytes": moved, "weight_version": version}
+
+
+def check_engines_hold_trainer_weights(actor, engines: Sequence) -> None:
+    """``--check-weight-update-equal``: after an update every engine parameter of the same shape must equal the
+    trainer's. ``--check-weight-update-skip-list`` (regular expressions over parameter names) leaves tensors out,
+    ``--check-weight-update-selector`` picks the model (``target``/``all``: the policy; ``draft`` has nothing to check:
+    no speculative draft model is served), ``--check-weight-update-allow-quant-error`` widens the tolerance to what a
+    block-scaled copy of the weights may differ by."""
+    import re
+
+    args = actor.args
+    if getattr(args, "check_weight_update_selector", "all") == "draft":
+        return
+    skip = [re.compile(p) for p in (getattr(args, "check_weight_update_skip_list", None) or [])]
+    rtol = 6e-2 if getattr(args, "check_weight_update_allow_quant_error", False) else 1e-3
+    for e in engines:
+        if not skip:
             a, b = actor.store.checksum(), e.store.checksum()
             for g in a:
                 if e.store.flat[g].numel() == actor.store.flat[g].numel():
-                    assert abs(a[g] - b[g]) <= 1e-3 * max(1.0, abs(a[g])), f"weight update mismatch in group {g}: {a[g]} vs {b[g]}"
-    return {"perf/update_weights_time": t1 - t_paused, "perf/update_weights_total_time": t1 - t0,
-            "perf/update_weights_bytes": moved, "weight_version": version}
+                    assert abs(a[g] - b[g]) <= rtol * max(1.0, abs(a[g])), f"weight update mismatch in group {g}: {a[g]} vs {b[g]}"
+            continue
+        for name, p in actor.store.params.items():
+            q = e.store.params.get(name)
+            if q is None or q.shape != p.shape or any(r.search(name) for r in skip):
+                continue
+            sa, sb = float(p.float().abs().sum()), float(q.float().abs().sum())
+            assert abs(sa - sb) <= rtol * max(1.0, abs(sa)), f"weight update mismatch in {name}: {sa} vs {sb}"

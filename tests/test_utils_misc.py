@@ -6,7 +6,7 @@ import pytest
 from miles_b200.models import get_config
 from miles_b200.utils import http_utils, lifecycle
 from miles_b200.utils.eval_config import build_eval_configs
-from miles_b200.utils.flops_utils import device_peak_tflops, forward_flops, mfu, train_step_flops
+from miles_b200.utils.metric_utils import device_peak_tflops, forward_flops, mfu, train_step_flops
 
 
 def test_http_retries_then_succeeds_and_gives_up_on_client_errors():
@@ -184,7 +184,7 @@ def test_eval_dispatcher_runs_in_background_and_skips_when_busy(tmp_path):
     seen = []
 
     async def main():
-        disp = EvalDispatcher(MyEval(None), export_fn=export, on_result=lambda r, m: seen.append((r, m)))
+        disp = EvalDispatcher(MyEval(None), export_fn=export, on_result=lambda r, m: seen.append((r, m)), overflow_policy="skip")
         assert await disp.dispatch(1, str(tmp_path / "e1"))
         assert disp.busy
         assert not await disp.dispatch(2, str(tmp_path / "e2"))          # one evaluation at a time
@@ -197,6 +197,22 @@ def test_eval_dispatcher_runs_in_background_and_skips_when_busy(tmp_path):
     assert [r for r, _ in seen] == [1, 3, 7] and disp.skipped == [2]
     assert seen[0][1]["eval/score"] == 1.0 and seen[2][1]["eval/skipped"] == 1.0
     assert not os.path.exists(tmp_path / "e1")  # snapshots are removed once evaluated
+
+    # back-pressure with two evaluations in flight and the newest snapshot kept
+    seen.clear()
+
+    async def main2():
+        disp = EvalDispatcher(MyEval(None), export_fn=export, on_result=lambda r, m: seen.append((r, m)), max_in_flight=2,
+                              overflow_policy="backpressure", keep_snapshots=1)
+        for rid in (11, 12, 13):
+            assert await disp.dispatch(rid, str(tmp_path / f"b{rid}"))   # the third waits for the first, none is dropped
+        await disp.drain()
+        return disp
+
+    disp = asyncio.run(main2())
+    assert sorted(r for r, _ in seen) == [11, 12, 13] and disp.skipped == []
+    kept = [rid for rid in (11, 12, 13) if os.path.exists(tmp_path / f"b{rid}")]
+    assert len(kept) == 1
 
 
 def test_ci_checks_hashes_kl_gate_and_grad_norm(tmp_path):

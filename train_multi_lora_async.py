@@ -33,7 +33,14 @@ def main(argv=None) -> None:
 
     args = parse_args(argv)
     loop = RLLoop(args)
-    registry = AdapterRegistry(max_slots=getattr(args, "multi_lora_n_adapters", 0) or 8)
+    gbs = args.global_batch_size or args.rollout_batch_size * args.n_samples_per_prompt
+    registry = AdapterRegistry(max_slots=getattr(args, "multi_lora_n_adapters", 0) or 8,
+                               max_adapter_batch=getattr(args, "multi_lora_max_adapter_global_batch_size", None) or 4 * gbs,
+                               samples_per_prompt=args.n_samples_per_prompt)
+    # an adapter's step starts once its batch is full, or after the coalesce wait on what is ready; a generate call that
+    # sees no finished group at all within the empty wait fails instead of blocking the other adapters
+    args.rollout_coalesce_wait_s = float(getattr(args, "multi_lora_max_coalesce_wait_s", 0.5) or 0.0)
+    args.rollout_empty_wait_s = float(getattr(args, "multi_lora_max_empty_wait_s", 30.0) or 0.0)
     ctl = MultiLoRAController(loop.actor, registry, save_dir=getattr(args, "save", None))
     for name, path in getattr(args, "multi_lora_adapters", None) or []:
         registry.register(AdapterSpec(name=name, rank=getattr(args, "lora_rank", 16) or 16, alpha=getattr(args, "lora_alpha", 32) or 32,
