@@ -88,8 +88,13 @@ def _finish_save(actor, base: str, d: str, iteration: int) -> None:
     """After every rank has written its file: metadata, the latest pointer, retention, the post-save hook."""
     args = actor.args
     if actor.ps.rank == 0:
-        with open(os.path.join(d, "meta.json"), "w") as f:
-            json.dump({"iteration": iteration, "world_size": actor.ps.world_size, "model": actor.cfg.to_dict()}, f, default=str)
+        meta = {}
+        mp = os.path.join(d, "meta.json")
+        if os.path.exists(mp):  # the reshardable format has already written its own fields
+            meta = json.load(open(mp))
+        meta.update({"iteration": iteration, "world_size": actor.ps.world_size, "model": actor.cfg.to_dict()})
+        with open(mp, "w") as f:
+            json.dump(meta, f, default=str)
         with open(os.path.join(base, LATEST), "w") as f:
             f.write(str(iteration))
         prune_checkpoints(base, iteration, getattr(args, "save_interval", None), getattr(args, "save_retain_interval", None))
@@ -118,6 +123,38 @@ def prune_checkpoints(base: str, newest: int, save_interval: Optional[int], reta
     return gone
 
 
+def _save_dist(actor, base: str, d: str, iteration: int) -> str:
+    """``--ckpt-format torch_dist`` (default): a reshardable ``torch.distributed.checkpoint`` directory (dist_ckpt.py);
+    RNG state and the value head, which are per rank, go next to it."""
+    from . import dist_ckpt
+    from ..utils.ci_checks import save_model_hashes
+
+    save_model_hashes(actor.args, actor.store, actor.ps, iteration)
+    side = {"rng": {"cpu": torch.get_rng_state(), "cuda": torch.cuda.get_rng_state() if actor.on_gpu else None}}
+    if getattr(actor, "_value_head", None) is not None:
+        side["value_head"] = actor._value_head.detach().cpu()
+    torch.save(side, os.path.join(d, f"side_rank_{actor.ps.rank:05d}.pt"))
+    fut = dist_ckpt.save(actor, d, iteration, async_save=bool(getattr(actor.args, "async_save", False)))
+    if fut is not None:
+        import threading
+
+        def work():
+            try:
+                fut.result()
+                _finish_save(actor, base, d, iteration)
+            except BaseException as e:  # noqa: BLE001 - surfaced by wait_for_async_save
+                _ASYNC["error"] = e
+
+        t = threading.Thread(target=work, name="miles-b200-async-save", daemon=False)
+        _ASYNC["thread"] = t
+        t.start()
+        return d
+    if dist.is_initialized():
+        dist.barrier()
+    _finish_save(actor, base, d, iteration)
+    return d
+
+
 def save_checkpoint(actor, base: str, iteration: int) -> str:
     """One file per rank under ``<base>/iter_%07d``. With ``--async-save`` the device-to-host snapshot happens here and
     the file write, metadata, retention and hooks run in a background thread (the next save, or the end of the run,
@@ -125,6 +162,8 @@ def save_checkpoint(actor, base: str, iteration: int) -> str:
     wait_for_async_save()
     d = iter_dir(base, iteration)
     os.makedirs(d, exist_ok=True)
+    if getattr(actor.args, "ckpt_format", "torch_dist") == "torch_dist":
+        return _save_dist(actor, base, d, iteration)
     state = _snapshot_state(actor, iteration)
     checksums = None
     if getattr(actor.args, "save_local_weight_checksum", False):
@@ -169,6 +208,10 @@ def load_checkpoint(actor, path: str, step: Optional[int] = None) -> Optional[in
     if is_native_checkpoint(path):
         it = step if step is not None else latest_iteration(path)
         d = iter_dir(path, it) if it is not None else path
+        from . import dist_ckpt
+
+        if dist_ckpt.is_dist_checkpoint(d):
+            return _load_dist(actor, d, it)
         f = os.path.join(d, f"rank_{actor.ps.rank:05d}.pt")
         state = torch.load(f, map_location="cpu", weights_only=False)
         with torch.no_grad():
@@ -198,6 +241,31 @@ def load_checkpoint(actor, path: str, step: Optional[int] = None) -> Optional[in
             actor.opt.sync_master_from_params()
         return None
     raise FileNotFoundError(f"checkpoint {path} not found")
+
+
+def _load_dist(actor, d: str, it: Optional[int]) -> Optional[int]:
+    from . import dist_ckpt
+    from ..utils.ci_checks import check_model_hashes
+
+    with_opt = actor.opt is not None and not getattr(actor.args, "no_load_optim", False)
+    meta = dist_ckpt.load(actor, d, with_optimizer=with_opt)
+    actor.store.version = int(meta.get("version", 0) or 0)
+    if actor.opt is not None and not with_opt:
+        actor.opt.sync_master_from_params()
+    side_p = os.path.join(d, f"side_rank_{actor.ps.rank:05d}.pt")
+    if os.path.exists(side_p):  # same layout as the run that saved: per-rank extras apply
+        side = torch.load(side_p, map_location="cpu", weights_only=False)
+        if not getattr(actor.args, "no_load_rng", False) and side.get("rng"):
+            torch.set_rng_state(side["rng"]["cpu"])
+        if getattr(actor, "_value_head", None) is not None and "value_head" in side:
+            actor._value_head.data.copy_(side["value_head"])
+    if it is not None:
+        check_model_hashes(actor.args, actor.store, actor.ps, it)
+    if getattr(actor.args, "finetune", False):
+        return None
+    actor.global_step = int(meta.get("global_step", 0) or 0)
+    rid = meta.get("rollout_id", it)
+    return int(rid) if rid is not None else None
 
 
 def load_weights_into_backup(actor, tag: str, path: str, step: Optional[int] = None) -> None:

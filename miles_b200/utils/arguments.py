@@ -98,6 +98,7 @@ TRAINER_FLAGS = [
     ("--recompute-granularity", "s", "full", {"choices": ["full", "selective", "none"]}),
     ("--recompute-method", "s", "uniform", {}), ("--recompute-num-layers", "i", 1, {}),
     # checkpoint / misc
+    ("--ckpt-format", "s", "torch_dist", {"choices": ["torch_dist", "torch"]}),
     ("--load", "s", None, {}), ("--save", "s", None, {}), ("--save-interval", "i", None, {}), ("--ckpt-step", "i", None, {}),
     ("--save-retain-interval", "i", None, {}), ("--async-save", "b", False, {}), ("--no-save-optim", "b", False, {}),
     ("--no-load-optim", "b", False, {}), ("--no-load-rng", "b", False, {}), ("--finetune", "b", False, {}),

@@ -281,3 +281,63 @@ def test_flash_attention_bwd_vs_fp32(ext, lens, Hq, Hk):
         assert err.max().item() < tol, (name, err.max().item(), tol)
         rel = err.norm().item() / ref.norm().item()
         assert rel < 1e-2, (name, rel)
+
+
+def test_bounded_peer_wait_expires_and_the_context_stays_usable(ext):
+    """A wait on a flag that no peer ever raises must give up after its budget, report it in the status word and
+    return, and the next launches must work: two expert-parallel "ranks" are emulated on one device (both map the same
+    region), only rank 0 sends, so rank 0's plan kernel waits in vain for rank 1."""
+    import time
+
+    R, Bm, H, K, E = 2, 8, 512, 4, 16
+
+    def al(x):
+        return (x + 255) // 256 * 256
+
+    off, lay = 0, {}
+    for name, nb in (("xg", R * Bm * H * 2), ("ig", R * Bm * K * 4), ("wg", R * Bm * K * 4), ("yb", R * Bm * H * 2),
+                     ("fa", R * 8), ("fb", R * 8)):
+        lay[name] = off
+        off = al(off + nb)
+
+    def fresh():
+        region = torch.zeros(off, dtype=torch.uint8, device=DEV)
+        layout = [R, Bm, H, K, lay["xg"], lay["ig"], lay["wg"], lay["yb"], lay["fa"], lay["fb"]]
+        return region, layout, [region.data_ptr()] * R
+
+    torch.manual_seed(3)
+    T = 5
+    x = (torch.randn(T, H, device=DEV) * 0.5).bfloat16()
+    ln = torch.ones(H, device=DEV, dtype=torch.bfloat16)
+    logits = torch.randn(T, E, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ids, w = torch.empty(T, K, dtype=torch.int32, device=DEV), torch.empty(T, K, device=DEV)
+
+    region, layout, bases = fresh()
+    ctrl0 = torch.zeros(8, dtype=torch.int64, device=DEV)
+    ext.ep_ll_send(x, ln, 1e-6, logits, None, bases, layout, 0, True, ids, w, ctrl0)
+    t0 = time.perf_counter()
+    src_rows, counts, offsets, dest, row_src, tiles, totals = ext.ep_ll_plan(region.data_ptr(), layout, 0, E, Bm, 1, ctrl0,
+                                                                             50_000_000, status)  # 50 ms budget
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert status.item() == 5, "the expired wait must be reported (5 = a source rank's rows never arrived)"
+    assert 0.04 < waited < 2.0, waited
+    assert src_rows.tolist() == [T, 0]           # what did arrive is still planned; the silent peer counts as empty
+    local = (ids // (E // R)) == 0
+    assert int(counts.sum()) == int(local.sum())
+    # the context is intact: an ordinary kernel runs, and a complete exchange on fresh buffers works
+    status.zero_()
+    a = torch.randn(128, 64, device=DEV, dtype=torch.bfloat16)
+    c = torch.empty(128, 128, device=DEV, dtype=torch.bfloat16)
+    ext.gemm(a, a, c, False, False, False, 0, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and torch.isfinite(c.float()).all()
+    region, layout, bases = fresh()
+    ctrls = [torch.zeros(8, dtype=torch.int64, device=DEV) for _ in range(R)]
+    for me in range(R):
+        ext.ep_ll_send(x, ln, 1e-6, logits, None, bases, layout, me, True, ids, w, ctrls[me])
+    out = ext.ep_ll_plan(region.data_ptr(), layout, 1, E, Bm, 1, ctrls[1], 50_000_000, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and out[0].tolist() == [T, T]
+    assert int(out[1].sum()) == 2 * int(((ids // (E // R)) == 1).sum())   # both sources' picks of rank 1's experts
