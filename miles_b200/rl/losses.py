@@ -141,7 +141,9 @@ def policy_loss(
             drop = (adv < 0) & (seq_kl.detach()[seg] > cfg.opsm_delta)
             opsm_mask = 1.0 - drop.float()
             counts = torch.zeros(reducer.num_samples, device=mask.device).index_add_(0, seg, mask)
-            metrics["opsm_clipfrac"] = ((drop.float() * mask) / counts.clamp_min(1.0)[seg]).sum()
+            # per sample: dropped tokens over trainable tokens, summed over samples (the reference counts every token of a
+            # dropped sequence in the numerator, miles/backends/training_utils/loss_hub/math_utils.py:182-222)
+            metrics["opsm_clipfrac"] = (drop.float() / counts.clamp_min(1.0)[seg]).sum()
 
     if cfg.advantage_estimator == "gspo":
         ppo_kl = seq_kl[seg]

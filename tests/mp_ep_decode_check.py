@@ -63,7 +63,7 @@ def rollout_check(cfg, ps, store, model, ref, ll, dev):
     g = torch.Generator().manual_seed(50 + ps.rank)
     n_req = 5 if ps.rank == 0 else 2
     prompts = [torch.randint(0, cfg.vocab_size, (20 + 9 * j + 3 * ps.rank,), generator=g).tolist() for j in range(n_req)]
-    params = [SamplingParams(temperature=1.0, max_new_tokens=64, forced_length=12 + 11 * j + 20 * (ps.rank == 0), ignore_eos=True,
+    params = [SamplingParams(temperature=1.0, max_new_tokens=96, forced_length=12 + 11 * j + 20 * (ps.rank == 0), ignore_eos=True,
                              sampling_seed=7 + j) for j in range(n_req)]
     res = eng.generate(prompts, params, return_routed_experts=True)
     eng.drain()

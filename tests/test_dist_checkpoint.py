@@ -64,3 +64,38 @@ def test_missing_atoms_are_reported(tmp_path):
     full = ParamStore(get_config("qwen3-tiny"), "cpu", torch.float32, seed=2)
     with pytest.raises(KeyError, match="lacks"):
         dist_ckpt.load(_actor(full), out, with_optimizer=False)
+
+
+@pytest.mark.parametrize("name", ["qwen3-tiny", "qwen3-tiny-moe"])
+def test_hf_to_torch_dist_and_back(tmp_path, name):
+    """HF safetensors -> torch_dist -> (expert-parallel slice loads it) -> HF safetensors: every tensor survives."""
+    from safetensors import safe_open
+    from miles_b200.checkpoint import export_hf
+    from miles_b200.tools import convert_hf_to_torch_dist, convert_torch_dist_to_hf
+    cfg = get_config(name)
+    src = ParamStore(cfg, "cpu", torch.bfloat16, seed=21)
+    one = NS(size=1, rank=0, group=None)
+    actor = NS(store=src, opt=None, args=NS(hf_checkpoint=None), cfg=cfg, global_step=0, ps=NS(rank=0, world_size=1, tp=one, pp=one, dp_cp=one))
+    hf0 = str(tmp_path / "hf0")
+    export_hf(actor, hf0)
+    d = convert_hf_to_torch_dist.convert(hf0, str(tmp_path / "dist"))
+    assert dist_ckpt.is_dist_checkpoint(d)
+    if cfg.is_moe:
+        part = ParamStore(cfg, "cpu", torch.bfloat16, seed=3, ep_size=2, ep_rank=1)
+        dist_ckpt.load(_actor(part), d, with_optimizer=False)
+        want = ParamStore(cfg, "cpu", torch.bfloat16, seed=21, ep_size=2, ep_rank=1)
+        for n in want.params:
+            assert torch.equal(part.params[n], want.params[n]), n
+    hf1 = convert_torch_dist_to_hf.convert(str(tmp_path / "dist"), str(tmp_path / "hf1"))
+
+    def tensors(path):
+        out = {}
+        for f in sorted(os.listdir(path)):
+            if f.endswith(".safetensors"):
+                with safe_open(os.path.join(path, f), framework="pt") as h:
+                    out.update({k: h.get_tensor(k) for k in h.keys()})
+        return out
+    a, b = tensors(hf0), tensors(hf1)
+    assert a.keys() == b.keys() and len(a) > 10
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
