@@ -96,6 +96,22 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     from torch.utils import cpp_extension
 
     OBJ.mkdir(parents=True, exist_ok=True)
+    import fcntl
+
+    # ranks of one job may all find the library stale at once: one compiles, the others wait and then find it fresh
+    lock = open(OBJ / ".build.lock", "w")
+    fcntl.flock(lock, fcntl.LOCK_EX)
+    try:
+        return _build_locked(verbose, force)
+    finally:
+        fcntl.flock(lock, fcntl.LOCK_UN)
+        lock.close()
+
+
+def _build_locked(verbose: bool, force: bool) -> Path:
+    import torch
+    from torch.utils import cpp_extension
+
     cu, cpp = sources()
     hdr_t = _newest_header()
     jobs: list[list[str]] = []

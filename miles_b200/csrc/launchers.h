@@ -203,4 +203,31 @@ int symm_open(const char* handle64, void** ptr);
 int symm_close(void* ptr);
 int symm_free(void* ptr);
 
+// ---- trainer -> engine weight push (weight_push.cu). The tables are int64 rows so that the host builds them as tensors.
+struct WeightPushSeg {      // one 2-D slab of the local shard
+  long long src_off;        // element offset in the source buffer (multiple of 8)
+  long long rows, cols;     // cols % 8 == 0 (bf16), % 128 (MXFP8), % 64 (NVFP4)
+  long long src_ld;         // source leading dimension in elements (multiple of 8)
+  long long tensor;         // row of the tensor table
+  long long dst_row0, dst_col0;  // position of the slab inside the destination tensor
+  long long peer_mask;      // ranks that receive the slab
+};
+struct WeightPushTensor {   // one destination tensor, at the same offsets inside every rank's symmetric region
+  long long val_off;        // byte offset of the values
+  long long sf_off;         // byte offset of the scale-factor atoms (quantised modes)
+  long long ld;             // destination leading dimension in elements (= K for the quantised modes)
+  long long mode;           // 0 bf16, 1 MXFP8, 2 NVFP4
+  long long amax_slot;      // NVFP4: index of the per-tensor amax
+  long long pad[3];
+};
+struct WeightPushPeers {
+  char* base[8];
+  long long flag_off;       // byte offset of the 8 arrival flags (u64) inside every region
+};
+int weight_push(const void* src, const WeightPushSeg* segs, int nseg, const WeightPushTensor* tensors, const float* amax,
+                const WeightPushPeers& peers, int me, unsigned flag_mask, unsigned long long version, unsigned int* counter,
+                long long total_vecs, cudaStream_t s);
+void weight_push_wait(const unsigned long long* flags, unsigned src_mask, unsigned long long version, double wait_ms, int* status,
+                      cudaStream_t s);
+
 }  // namespace mb

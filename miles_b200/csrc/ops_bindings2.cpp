@@ -242,11 +242,13 @@ std::vector<at::Tensor> fake_int4_quant(const at::Tensor& x, int64_t gr, int64_t
 void register_comm(pybind11::module_& m);  // ops_bindings3.cpp
 void register_mx(pybind11::module_& m);    // ops_bindings4.cpp
 void register_ep_ll(pybind11::module_& m); // ops_bindings5.cpp
+void register_weight_push(pybind11::module_& m); // ops_bindings6.cpp
 
 void register_more(pybind11::module_& m) {
   register_comm(m);
   register_mx(m);
   register_ep_ll(m);
+  register_weight_push(m);
   m.def("sample_rows", &sample_rows);
   m.def("paged_decode_attention", &paged_decode_attention, pybind11::arg("q"), pybind11::arg("k_cache"), pybind11::arg("v_cache"),
         pybind11::arg("block_table"), pybind11::arg("seq_lens"), pybind11::arg("out"), pybind11::arg("scratch"),

@@ -148,6 +148,7 @@ class RLLoop:
         sync = ep_decode = None
         engine_model = self.actor.model
         self.rollout_store = None
+        self.weight_pusher = None
         if replicate:
             # Rollout on a full replica of the experts: decode is bound by the weights it streams, not by capacity,
             # and a B200 holds all experts of this model many times over. Every rank then generates independently
@@ -155,8 +156,23 @@ class RLLoop:
             # expert parallel, and the weight update all-gathers the updated expert shares into the replica.
             from .models import ParamStore, build_model
 
-            self.rollout_store = ParamStore(cfg, self.actor.device, self.actor.store.dtype, ep_size=1, init=False,
-                                            share_dense=self.actor.store)
+            ep = self.ps.ep
+            if (getattr(a, "fused_comm", True) and self.actor.store.dtype == torch.bfloat16 and ep.size <= 8
+                    and getattr(a, "update_weight_transfer_mode", "broadcast") != "broadcast-nccl"):
+                # the replica's experts live in a peer-mapped region: every rank stores its updated expert shard
+                # straight into all replicas with one kernel (csrc/weight_push.cu) instead of an all-gather per tensor
+                from .weight_sync.p2p_push import Layout, PushTarget, WeightPusher
+
+                target = PushTarget.create(cfg, ep.group, ep.rank, ep.size, self.actor.device, groups=("expert",),
+                                           share_dense=self.actor.store)
+                self.rollout_store = target.store
+                self.weight_pusher = WeightPusher(cfg, self.actor.store, target, ep.rank,
+                                                  [Layout(ep_size=ep.size, ep_rank=r) for r in range(ep.size)],
+                                                  [Layout() for _ in range(ep.size)], skip_groups=("dense",), amax_group=ep.group)
+                self.rollout_store.weight_pusher = self.weight_pusher
+            else:
+                self.rollout_store = ParamStore(cfg, self.actor.device, self.actor.store.dtype, ep_size=1, init=False,
+                                                share_dense=self.actor.store)
             engine_model = build_model(cfg, self.rollout_store, "b200")
         elif pipelined:
             # the trainer's stage holds part of the layers; the engine decodes on a copy of the whole model that the

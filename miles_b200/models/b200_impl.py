@@ -96,7 +96,15 @@ class B200Qwen3:
             self.mx[w.data_ptr()] = quantize_operand(w2, kind)
         return len(self.mx)
 
+    def use_block_scaled(self, kind: str, operands: dict) -> None:
+        """Serve from block-scaled copies that something else keeps up to date (``{parameter name: MxOperand}``, e.g.
+        the buffers a peer-memory weight push quantises into)."""
+        self.mx_kind, self.mx_external = kind, True
+        self.mx = {self.store.params[n].data_ptr(): op for n, op in operands.items() if n in self.store.params}
+
     def refresh_block_scaled(self) -> None:
+        if getattr(self, "mx_external", False):
+            return
         if getattr(self, "mx", None):
             self.enable_block_scaled(self.mx_kind)
 

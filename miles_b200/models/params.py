@@ -166,8 +166,10 @@ class ParamStore:
                  ep_size: int = 1, ep_rank: int = 0, init_std: float = 0.02, seed: int = 1234, init: bool = True,
                  meta: bool = False, tp_size: int = 1, tp_rank: int = 0, share_dense: Optional["ParamStore"] = None,
                  pp_size: int = 1, pp_rank: int = 0, pp_first_layers: Optional[int] = None,
-                 pp_last_layers: Optional[int] = None):
-        """``cfg`` is the global model; with ``tp_size > 1`` the store holds this rank's shard (``self.cfg`` becomes
+                 pp_last_layers: Optional[int] = None, flat_override: Optional[dict] = None):
+        """``flat_override``: ``{group: flat tensor}`` to use instead of allocating (e.g. views of a peer-mapped
+        symmetric region that other ranks write weight updates into).
+        ``cfg`` is the global model; with ``tp_size > 1`` the store holds this rank's shard (``self.cfg`` becomes
         the local view, ``self.global_cfg`` keeps the full model for conversions). With ``pp_size > 1`` it holds the
         decoder layers ``self.layer_range`` of pipeline stage ``pp_rank`` (plus embedding / head on the end stages)."""
         self.global_cfg = cfg
@@ -190,7 +192,11 @@ class ParamStore:
         # all experts next to a trainer that holds its expert-parallel share)
         if share_dense is not None:
             assert share_dense.sizes["dense"] == self.sizes["dense"] and share_dense.dtype == dtype
-        self.flat = {g: (share_dense.flat[g] if (share_dense is not None and g == "dense") else torch.zeros(n, dtype=dtype, device=dev))
+        flat_override = flat_override or {}
+        for g, t in flat_override.items():
+            assert t.numel() == self.sizes[g] and t.dtype == dtype and t.is_contiguous(), f"flat_override[{g}] has the wrong size or type"
+        self.flat = {g: (flat_override[g] if g in flat_override else share_dense.flat[g] if (share_dense is not None and g == "dense")
+                         else torch.zeros(n, dtype=dtype, device=dev))
                      for g, n in self.sizes.items()}
         self.grad: dict[str, Optional[torch.Tensor]] = {"dense": None, "expert": None}
         self.params: "OrderedDict[str, torch.Tensor]" = OrderedDict()

@@ -30,6 +30,7 @@ def sync_weights(actor, engines: Sequence, mode: str | None = None) -> dict:
     t0 = time.perf_counter()
     pause_mode = getattr(args, "pause_generation_mode", "retract")
     moved = 0
+    pushers = []
     for e in engines:
         e.pause_generation(pause_mode)
         if pause_mode != "in_place":
@@ -43,6 +44,12 @@ def sync_weights(actor, engines: Sequence, mode: str | None = None) -> dict:
                 from .reshard import gather_stages_into
 
                 moved += gather_stages_into(actor.store, e.store, actor.ps.pp)
+                continue
+            pusher = getattr(e.store, "weight_pusher", None)
+            if pusher is not None:
+                # reshard (+ quantise) + peer-memory stores + version flag in one kernel per flat buffer
+                moved += pusher.push()
+                pushers.append(pusher)
                 continue
             for g, t in e.store.flat.items():
                 src = actor.store.flat[g]
@@ -66,6 +73,8 @@ def sync_weights(actor, engines: Sequence, mode: str | None = None) -> dict:
             refresh()  # engines that serve MXFP8 / NVFP4 copies re-quantise from the weights that just arrived
     if actor.on_gpu:
         torch.cuda.synchronize()
+    for p in pushers:
+        p.check_status()  # a source that never arrived: raise rather than serve stale weights
     version = actor.store.version
     for e in engines:
         e.update_weight_version(version)

@@ -38,3 +38,18 @@ def test_low_latency_expert_parallel_decode():
            "--master-port", "29733", os.path.join(here, "mp_ep_decode_check.py"), "check"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "EP_DECODE_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_weight_push_reshards_and_quantises_into_peer_memory():
+    """The peer-memory weight update (reshard + quantise + store + flag in one kernel): expert-parallel trainer ->
+    replicas (bf16, MXFP8, NVFP4, bitwise against the stand-alone quantisers), tensor-parallel trainer -> unsharded
+    engine, replicated trainer -> tensor-parallel engine, and a source that never arrives (the bounded wait gives up)."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29735", os.path.join(here, "mp_weight_push_check.py"), "check"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "WEIGHT_PUSH_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
