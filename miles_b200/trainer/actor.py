@@ -251,9 +251,9 @@ class TrainActor:
             colocated = self.role == "actor" and not getattr(a, "debug_train_only", False) and not getattr(a, "rollout_engine_urls", None)
             if (self.cfg.is_moe and self.ps.ep.size > 1 and colocated and self.ps.tp.size == 1
                     and replica_wanted(a, self.ps.ep.size)):
-                # the colocated engine will hold all experts (see RLLoop._build_engine): leave room for the part this
-                # rank does not train
-                extra = (expert * self.ps.ep.size - expert) * 2
+                # the colocated engine will hold all experts in a buffer of its own (see RLLoop._build_engine; this
+                # rank's share is stored twice: the trainer's flat shard and its slice of every replica tensor)
+                extra = expert * self.ps.ep.size * 2
             kv = 0
             if colocated:
                 kv = min(wanted_kv_bytes(a, self.cfg, self.ps.dp_cp.size * self.ps.pp.size),

@@ -55,10 +55,11 @@ def layer_check(cfg, ps, model, ref, ll, dev):
     dist.barrier()
 
 
-def rollout_check(cfg, ps, store, model, ref, ll, dev):
+def rollout_check(cfg, ps, store, model, ref, ll, dev, use_graph=True, overlap=True, report=False):
     world = ps.world_size
     sync = LockstepSync(ps.gloo_world)
-    eng = Engine(model, sync=sync, ep_decode=ll, max_running=8, page_size=64, max_seq_len=512, use_cuda_graph=True)
+    eng = Engine(model, sync=sync, ep_decode=ll, max_running=8, page_size=64, max_seq_len=512, use_cuda_graph=use_graph)
+    eng.overlap_decode = overlap
     eng.warm_up_decode_graphs()
     g = torch.Generator().manual_seed(50 + ps.rank)
     n_req = 5 if ps.rank == 0 else 2
@@ -86,6 +87,15 @@ def rollout_check(cfg, ps, store, model, ref, ll, dev):
     lp_ref, _ = ref.forward_logprobs(t(toks), t(pos), t(cu), t(rows, torch.int64), t(tgts), 1.0,
                                      replay=torch.cat(routes).contiguous().to(dev))
     diff = (lp_ref - torch.tensor(lps, device=dev)).abs()
+    if report:
+        first = torch.tensor([sum(len(r["output_ids"]) for r in res[:j]) for j in range(len(res))], device=dev)
+        per_req = [round(float(diff[a:a + len(r["output_ids"])].mean()), 4) for a, r in zip(first.tolist(), res)]
+        worst = int(diff.argmax())
+        print(f"[rank {ps.rank}] graph={use_graph} overlap={overlap} ll={getattr(ll, 'low_latency', False)} mean={diff.mean().item():.4f} "
+              f"max={diff.max().item():.3f} at flat index {worst} first-token mean={diff[first].mean().item():.4f} per-request={per_req} "
+              f"lens={[len(r['output_ids']) for r in res]}", flush=True)
+        dist.barrier()
+        return diff.mean().item(), 0
     assert diff.mean().item() < 2e-2 and diff.max().item() < 0.3, (diff.mean().item(), diff.max().item())
     steps = torch.tensor([eng.stats["decode_steps"]], device=dev)
     dist.all_reduce(steps, op=dist.ReduceOp.MAX)
@@ -158,6 +168,14 @@ def main():
         ref_store = ParamStore(cfg, dev, torch.bfloat16, init_std=0.05, seed=5)
         ref = build_model(cfg, ref_store, "b200")
         layer_check(cfg, ps, model, ref, ll, dev)
+        if mode == "diagnose":
+            for kw in (dict(use_graph=True, overlap=True), dict(use_graph=False, overlap=False), dict(use_graph=False, overlap=True),
+                       dict(use_graph=True, overlap=False)):
+                rollout_check(cfg, ps, store, model, ref, ll, dev, report=True, **kw)
+            rollout_check(cfg, ps, store, model, ref, ep, dev, report=True, use_graph=False, overlap=False)
+            dist.barrier()
+            dist.destroy_process_group()
+            return
         mean_diff, steps = rollout_check(cfg, ps, store, model, ref, ll, dev)
         if ps.rank == 0:
             print(f"EP_DECODE_CHECK_OK world={world} logprob_diff={mean_diff:.5f} lockstep_decode_steps={steps}")
