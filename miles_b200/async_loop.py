@@ -12,9 +12,9 @@ Two modes, selected like in the reference (train_async.py:22-129, miles/utils/ar
 With engines in other processes (``--rollout-engine-urls`` / ``--launch-rollout-fleet``) the next rollout is generated
 on a background thread while the current one trains, and is collected before the weights change.
 
-On one process per GPU the producer is advanced cooperatively: the trainer yields to the rollout
-function between micro-batches (``pump``), which interleaves engine iterations with training kernels on
-the same device; samples generated under older weights are corrected by TIS when enabled.
+On one process per GPU the fully-asynchronous producer is advanced cooperatively: ``pump`` is called once per step
+before training (engine iterations and training kernels do not interleave on one device); samples generated under
+older weights are corrected by TIS when enabled.
 """
 from __future__ import annotations
 

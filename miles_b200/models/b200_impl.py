@@ -52,22 +52,67 @@ class B200Qwen3:
         self.launches = 0  # number of this library's kernels launched (reported by the benchmark)
         self._decode_scratch: Optional[torch.Tensor] = None
         self._tiles = TileCache()
+        self.cp_ctx = None  # (sample lengths, cp size, cp rank, group, comm, layout) while a context-parallel micro-batch runs
         self._ident: Optional[torch.Tensor] = None
         self.small_decode = True  # weight-streaming kernels for decode steps of at most SMALL_T rows
         self.lm_chunk = 2048      # rows of the LM head per pass (--log-probs-chunk-size)
 
     def attention(self, q, k, v, cu):
-        """Causal attention over packed sequences: returns (out [T, Hq, 128], lse [Hq, T])."""
+        """Causal attention over packed sequences: returns (out [T, Hq, 128], lse [Hq, T]).
+
+        Under context parallelism (``cp_ctx`` set by the trainer: the rows are this rank's shard of every sequence)
+        the sequence shard is traded for a head shard with one all-to-all per tensor, the kernel attends over whole
+        sequences with ``Hq / cp`` query heads, and the output is traded back; what the backward needs in that layout
+        travels in the second return value. NVSwitch gives the all-to-all full bandwidth between every pair, so this
+        layout, not a ring of K/V blocks, is the one built for this path."""
+        if self.cp_ctx is not None:
+            return self._attention_cp(q, k, v)
         out, lse = self.C.flash_attn_fwd(q, k, v, self._tiles.get(cu), self.cfg.head_dim ** -0.5, self.status)
         self.launches += 1
         return out, lse
 
     def attention_backward(self, q, k, v, out, d_out, lse, cu):
         """dQ, dK, dV of :meth:`attention` from its output and log-sum-exp (tcgen05 kernel, csrc/attention_bwd.cu)."""
+        if isinstance(lse, tuple):
+            return self._attention_cp_backward(d_out, lse)
         dq, dk, dv = self.C.flash_attn_bwd(q, k, v, out, d_out.contiguous(), lse, self._tiles.get_bwd(cu),
                                            self.cfg.head_dim ** -0.5, self.status)
         self.launches += 3
         return dq, dk, dv
+
+    def _cp_full_cu(self, lens):
+        key = tuple(lens)
+        if getattr(self, "_cp_cu_key", None) != key:
+            self._cp_cu = torch.tensor([0] + list(torch.tensor(list(lens)).cumsum(0).tolist()), dtype=torch.int32, device=self.dev)
+            self._cp_cu_key = key
+        return self._cp_cu
+
+    def _attention_cp(self, q, k, v):
+        from ..parallel.context_parallel import heads_to_sequence, sequence_to_heads
+
+        lens, cp, rank, group = self.cp_ctx[:4]
+        layout = self.cp_ctx[5] if len(self.cp_ctx) > 5 else "zigzag"
+        cfg = self.cfg
+        assert cfg.num_kv_heads % cp == 0, (f"context parallelism on this path shards the {cfg.num_kv_heads} key / value heads "
+                                            f"over the {cp} ranks (all-to-all layout)")
+        qf, kf, vf = (heads_to_sequence(t.contiguous(), lens, cp, rank, group, layout).contiguous() for t in (q, k, v))
+        cu = self._cp_full_cu(lens)
+        out_f, lse_f = self.C.flash_attn_fwd(qf, kf, vf, self._tiles.get(cu), cfg.head_dim ** -0.5, self.status)
+        self.launches += 1
+        out = sequence_to_heads(out_f, lens, cp, rank, group, layout)
+        return out, (lse_f, qf, kf, vf, out_f, cu)
+
+    def _attention_cp_backward(self, d_out, saved):
+        from ..parallel.context_parallel import heads_to_sequence, sequence_to_heads
+
+        lens, cp, rank, group = self.cp_ctx[:4]
+        layout = self.cp_ctx[5] if len(self.cp_ctx) > 5 else "zigzag"
+        lse_f, qf, kf, vf, out_f, cu = saved
+        do_f = heads_to_sequence(d_out.contiguous(), lens, cp, rank, group, layout).contiguous()
+        dqf, dkf, dvf = self.C.flash_attn_bwd(qf, kf, vf, out_f, do_f, lse_f, self._tiles.get_bwd(cu), self.cfg.head_dim ** -0.5,
+                                              self.status)
+        self.launches += 3
+        return tuple(sequence_to_heads(t, lens, cp, rank, group, layout) for t in (dqf, dkf, dvf))
 
     # ------------------------------------------------------------------ GEMM helpers
     def _gemm(self, a, b, out, a_mn=False, b_mn=False, acc=False):

@@ -152,8 +152,15 @@ class TrainActor:
             max_tok = max(getattr(args, "max_tokens_per_gpu", None) or 0, getattr(args, "engine_max_prefill_tokens", 16384),
                           (getattr(args, "rollout_max_context_len", None) or 0), 4096)
             self.ep_dispatcher = ExpertParallel(self.cfg, self.ps, fused=getattr(args, "fused_comm", True), max_tokens=max_tok)
-        self.model = build_model(self.cfg, store, "b200" if want_b200 else "torch", ep=self.ep_dispatcher, tp=self.tp_exchange)
-        self.is_torch = not want_b200
+        provider = getattr(args, "custom_model_provider_path", None)
+        if provider:
+            # a plug-in builds the model (see miles_b200/plugins): it says itself whether it runs under autograd
+            self.model = load_function(provider)(args=args, cfg=self.cfg, store=store, ep=self.ep_dispatcher, tp=self.tp_exchange,
+                                                 role=role)
+            self.is_torch = bool(getattr(self.model, "uses_autograd", not want_b200))
+        else:
+            self.model = build_model(self.cfg, store, "b200" if want_b200 else "torch", ep=self.ep_dispatcher, tp=self.tp_exchange)
+            self.is_torch = not want_b200
         self.loss_cfg = LossConfig.from_args(args)
         if getattr(args, "custom_tis_function_path", None):
             self.loss_cfg.custom_tis_fn = load_function(args.custom_tis_function_path)
@@ -371,9 +378,9 @@ class TrainActor:
             if hasattr(self.model, "cp_ctx"):
                 self.model.cp_ctx = None
             return
-        if not self.is_torch:
-            raise NotImplementedError("training under context parallelism runs on the PyTorch model path; the sm_100a "
-                                      "path has the context-parallel attention forward only")
+        if not self.is_torch and self.cfg.num_kv_heads % cp[1] != 0:
+            raise NotImplementedError(f"context parallelism on the sm_100a path trades sequence shards for head shards: the "
+                                      f"{self.cfg.num_kv_heads} key / value heads must divide by the context-parallel size {cp[1]}")
         self.model.cp_ctx = (cp[0], cp[1], cp[2], self.ps.cp.group, getattr(self.ps, "cp_comm_type", "p2p"), cp[3])
 
     def _forward_logprobs(self, mb: MicroBatch, replay=None, record=None):

@@ -80,7 +80,6 @@ REJECT = {
     "experts_shared_outer_loras": "LoRA on experts",
     "multi_lora_backend_path": "pluggable multi-LoRA backends",
     "multi_lora_http_server_path": "pluggable multi-LoRA servers",
-    "custom_model_provider_path": "model provider plugins",
     "custom_megatron_init_path": "Megatron initialisation hooks",
     "opd_teacher_urls": "on-policy distillation against remote teacher servers",
     "opd_log_prob_top_k": "top-k on-policy distillation",

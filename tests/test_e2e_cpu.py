@@ -220,3 +220,17 @@ def test_ci_checks_run_inside_the_loop(tmp_path):
     hashes[0].write_text(json.dumps(h))
     with pytest.raises(AssertionError):
         RLLoop(parse_args(common + ["--num-rollout", "2", "--load", str(tmp_path / "ckpt")]))
+
+
+def test_model_provider_plugin_builds_the_trainer_and_engine_model():
+    """--custom-model-provider-path: the plug-in's model trains and (shared with the colocated engine) generates: the
+    trainer / rollout log-probs still agree, which they would not if only one side used the plug-in."""
+    from miles_b200.loop import RLLoop
+    from miles_b200.plugins.example_provider import SoftCappedQwen3
+
+    args = parse_args(BASE + ["--num-rollout", "1", "--actor-num-gpus-per-node", "1",
+                              "--custom-model-provider-path", "miles_b200.plugins.example_provider.provider"])
+    loop = RLLoop(args)
+    assert isinstance(loop.actor.model, SoftCappedQwen3) and loop.engine.model is loop.actor.model
+    m = loop.run()[0]
+    assert m["train/train_rollout_logprob_abs_diff"] < 1e-5 and m["train/grad_norm"] > 0

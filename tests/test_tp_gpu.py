@@ -63,3 +63,16 @@ def test_pipeline_parallel_model_matches_single_rank():
            "--master-port", "29749", os.path.join(here, "mp_pp_check.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "PP_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_context_parallel_training_step_on_the_sm100_path():
+    """Sequence shards are traded for head shards around the attention forward / backward kernels: log-probs and the
+    summed gradients of a 2-rank context-parallel step equal the single-rank step (dense and MoE smoke models)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29749", os.path.join(here, "mp_cp_train_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "CP_TRAIN_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
