@@ -498,6 +498,8 @@ class Engine:
         self.d_temperature[:B] = d_f[:, 0]
         self.d_top_p[:B] = d_f[:, 1]
         self.d_seeds[:B] = h_s.to(self.dev)
+        for r in reqs:
+            r.dev_pages = len(r.pages)
         self._rows = list(reqs)
         self._rows_B = B
 
@@ -519,7 +521,6 @@ class Engine:
         """Enqueue one decode step for the running set and the copies of its results into pinned host buffers.
         ``lookahead = 1``: the step *after* the one still in flight (same batch, device-side state already advances
         inside the captured step), launched before the host has looked at the previous step's tokens."""
-        before_pages = {r.rid: len(r.pages) for r in self.running}
         if lookahead == 0:
             self._grow_pages()
         elif not self._grow_pages_ahead(lookahead):
@@ -534,9 +535,10 @@ class Engine:
             assert lookahead == 0, "a look-ahead step never changes the batch"
             self._upload_rows(reqs, B)
         else:
-            for i, r in enumerate(reqs):  # pages appended since the last step
-                for j in range(before_pages.get(r.rid, 0), len(r.pages)):
+            for i, r in enumerate(reqs):  # pages appended since the device-side table was last written (wherever they
+                for j in range(getattr(r, "dev_pages", 0), len(r.pages)):  # were obtained: here or by a look-ahead check)
                     self.d_block_table[i, j] = r.pages[j]
+                r.dev_pages = len(r.pages)
         want_routes = self.cfg.is_moe and any(r.return_routed_experts for r in reqs)
         ll = getattr(self.ep_decode, "low_latency", False)
         if ll:

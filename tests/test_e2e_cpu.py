@@ -156,8 +156,11 @@ def _cp_worker(rank: int, world: int, port: int, out_dir: str, comm: str = "p2p"
     # the context-parallel step is the single-process step: same loss terms, same gradient norm, same new weights
     for k in ("train/pg_loss", "train/grad_norm", "train/train_rollout_logprob_abs_diff"):
         assert abs(m[k] - m0[k]) <= 1e-5 * max(1.0, abs(m0[k])), (k, m[k], m0[k])
+    # (the first Adam step moves every weight by lr * g / (|g| + eps): an element whose gradient is rounding noise around
+    # zero may move the other way in the other summation order, so a handful of elements may differ by up to 2 lr)
     for g in solo.store.flat:
-        assert torch.allclose(solo.store.flat[g], loop.actor.store.flat[g], atol=1e-6), g
+        d = (solo.store.flat[g] - loop.actor.store.flat[g]).abs()
+        assert d.max().item() <= 2.2 * args.lr and (d > 1e-6).float().mean().item() < 1e-3, (g, d.max().item())
     assert m["train/train_rollout_logprob_abs_diff"] < 1e-5
     dist.barrier()
     dist.destroy_process_group()
