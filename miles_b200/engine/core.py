@@ -58,6 +58,10 @@ class Request:
     pages: list = field(default_factory=list)
     slot: int = -1  # row in the running batch
     seed: int = 0
+    nodes: list = field(default_factory=list)  # prefix-cache nodes behind the first len(nodes) pages (shared, read only)
+    prefill_cached: int = 0                    # tokens of the current prefill that came from the prefix cache
+    cache_epoch: int = -1
+    routes_tokens: int = 0                     # token positions covered by routed_experts so far
     t_submit: float = 0.0
     cached_tokens: int = 0
 
@@ -82,6 +86,16 @@ class Request:
         return {"output_ids": list(self.output_ids), "meta_info": meta}
 
 
+def _common_pages(a: list, b: list, ps: int, limit: int) -> int:
+    """Number of leading full pages (of ``ps`` tokens, within the first ``limit`` tokens of ``a``) on which two token
+    lists agree."""
+    n = min(limit, len(b)) // ps
+    k = 0
+    while k < n and a[k * ps:(k + 1) * ps] == b[k * ps:(k + 1) * ps]:
+        k += 1
+    return k
+
+
 def PagePool(num_pages: int):
     """KV page pool: the C++ free-list allocator of ``csrc/native/engine_core.cpp`` (page 0 is reserved as the
     dummy page of padded batch rows; ``alloc(n)`` returns a list of page ids or ``None``, ``release(pages)``,
@@ -95,8 +109,14 @@ class Engine:
     def __init__(self, model, *, max_running: int = 64, num_pages: Optional[int] = None, page_size: int = 64,
                  max_seq_len: int = 16384, max_prefill_tokens: int = 16384, kv_mem_bytes: Optional[int] = None,
                  use_cuda_graph: Optional[bool] = None, eos_token_id: Optional[int] = None, kv_dtype=None,
-                 sync=None, ep_decode=None, kv_storage: Optional[torch.Tensor] = None, overlap_decode: bool = True):
+                 sync=None, ep_decode=None, kv_storage: Optional[torch.Tensor] = None, overlap_decode: bool = True,
+                 prefix_cache: bool = False):
         self.model = model
+        self.prefix = None
+        if prefix_cache:
+            from .prefix_cache import PrefixCache
+
+            self.prefix = PrefixCache(page_size)
         self.overlap_decode = overlap_decode  # keep one decode step in flight while the host reads the previous one
         self.kv_storage = kv_storage  # caller-owned uint8 device buffer to carve the KV cache from (None = allocate)
         self.sync = sync            # lockstep agreement across expert-parallel ranks (None = independent engine)
@@ -196,6 +216,8 @@ class Engine:
             self._graphs.clear()
         if "kv_cache" in tags:
             self.kv_cache = None
+            if self.prefix is not None:
+                self.pool.release(self.prefix.clear())  # the cached keys / values are gone with the memory
             self._graphs.clear()  # graphs hold raw cache pointers
         if self.on_gpu:
             torch.cuda.empty_cache()
@@ -207,9 +229,24 @@ class Engine:
 
     def flush_cache(self) -> bool:
         if self.running:
+            if self.prefix is not None:
+                # requests in flight keep the pages they use; everything else is forgotten (weights changed)
+                self.pool.release(self.prefix.clear())
             return False
         self.pool = PagePool(self.num_pages)
+        if self.prefix is not None:
+            self.prefix.clear()
         return True
+
+    def _alloc(self, n: int):
+        """``n`` pages from the pool; when it runs dry, unreferenced prefix-cache pages are evicted first."""
+        pages = self.pool.alloc(n)
+        if pages is None and self.prefix is not None and self.prefix.num_pages:
+            freed = self.prefix.evict(n - self.pool.num_free)
+            if freed:
+                self.pool.release(freed)
+                pages = self.pool.alloc(n)
+        return pages
 
     # ------------------------------------------------------------------ request API
     def add_request(self, input_ids: Sequence[int], params: SamplingParams | dict | None = None, rid: Optional[str] = None,
@@ -272,23 +309,47 @@ class Engine:
         return (n_tokens + self.page_size - 1) // self.page_size
 
     def _retract(self, req: Request) -> None:
-        self._release(req)
+        self._release(req, offer=True)
         self.running.remove(req)
         self.waiting.appendleft(req)
         self.stats["retracted"] += 1
 
-    def _release(self, req: Request) -> None:
+    def _release(self, req: Request, offer: bool = False) -> None:
+        """Give the request's pages back. ``offer``: its full pages (prompt and generated tokens) are offered to the
+        prefix cache first, so a follow-up request that starts with this conversation finds them."""
         if req.pages:
-            self.pool.release(req.pages)
+            own = req.pages[len(req.nodes):]
+            if self.prefix is not None:
+                if offer and req.cache_epoch == self.prefix.epoch:
+                    ids = req.input_ids + req.output_ids
+                    # the last sampled token was never fed: keys / values exist for len(ids) - 1 positions
+                    ids = ids[:len(ids) - 1]
+                    payloads = self._page_payloads(req, len(ids) // self.page_size)
+                    taken, dup = self.prefix.insert(ids, req.pages, payloads, skip=len(req.nodes))
+                    keep = {n.page for n in taken[len(req.nodes):]}
+                    own = [p for p in own if p not in keep or p in dup]
+                own = own + self.prefix.unlock(req.nodes)
+                req.nodes = []
+            if own:
+                self.pool.release(own)
             req.pages = []
         if req.slot >= 0:
             self.slot_req[req.slot] = None
             self.slots_free.append(req.slot)
             req.slot = -1
 
+    def _page_payloads(self, req: Request, n_pages: int):
+        """Routed experts of the request's first ``n_pages`` full pages (what routing replay needs when a later request
+        takes those pages from the prefix cache), or None when the request did not record them."""
+        if not (req.return_routed_experts and self.cfg.is_moe and req.routed_experts):
+            return None
+        allr = torch.cat(req.routed_experts, 0)
+        ps = self.page_size
+        return [allr[p * ps:(p + 1) * ps].clone() if (p + 1) * ps <= allr.shape[0] else None for p in range(n_pages)]
+
     def _finish(self, req: Request, reason: str) -> None:
         req.finish_reason = reason
-        self._release(req)
+        self._release(req, offer=True)
         if req in self.running:
             self.running.remove(req)
         self.finished[req.rid] = req
@@ -345,20 +406,55 @@ class Engine:
 
     def _admit(self) -> list:
         batch, tokens = [], 0
-        while self.waiting and self.slots_free:
-            req = self.waiting[0]
-            n = req.seq_len
-            if batch and tokens + n > self.max_prefill_tokens:
+        if self.prefix is None:
+            while self.waiting and self.slots_free:
+                req = self.waiting[0]
+                n = req.seq_len
+                if batch and tokens + n > self.max_prefill_tokens:
+                    break
+                pages = self._alloc(self._pages_needed(n + 1))
+                if pages is None:
+                    break
+                self.waiting.popleft()
+                req.pages = pages
+                req.slot = self.slots_free.pop()
+                self.slot_req[req.slot] = req
+                batch.append(req)
+                tokens += n
+            return batch
+        # with a prefix cache: a request that shares more full pages with one admitted in this very batch than the cache
+        # holds yet is left for the next iteration, when those pages exist (the samples of one prompt then compute the
+        # prompt once); the others keep their order
+        ps = self.page_size
+        admitted_ids: list = []
+        for req in list(self.waiting):
+            if not self.slots_free:
                 break
-            pages = self.pool.alloc(self._pages_needed(n + 1))
+            ids = req.input_ids + req.output_ids
+            n = len(ids)
+            nodes = self.prefix.match(ids, n - 1, need_payload=req.return_routed_experts and self.cfg.is_moe)
+            if any(_common_pages(ids, other, ps, n - 1) > len(nodes) for other in admitted_ids):
+                continue
+            new_tokens = n - len(nodes) * ps
+            if batch and tokens + new_tokens > self.max_prefill_tokens:
+                break
+            self.prefix.lock(nodes)  # before allocating: the eviction that may run now must not take them
+            pages = self._alloc(self._pages_needed(n + 1) - len(nodes))
             if pages is None:
+                self.pool.release(self.prefix.unlock(nodes))
                 break
-            self.waiting.popleft()
-            req.pages = pages
+            self.waiting.remove(req)
+            req.nodes, req.pages = list(nodes), [nd.page for nd in nodes] + pages
+            req.prefill_cached, req.cache_epoch = len(nodes) * ps, self.prefix.epoch
+            req.cached_tokens += req.prefill_cached  # reported as meta_info.cached_tokens
+            if req.return_routed_experts and self.cfg.is_moe and req.routes_tokens < req.prefill_cached:
+                req.routed_experts = [nd.payload for nd in nodes]
+                req.routes_tokens = req.prefill_cached
             req.slot = self.slots_free.pop()
             self.slot_req[req.slot] = req
             batch.append(req)
-            tokens += n
+            admitted_ids.append(ids)
+            tokens += new_tokens
         return batch
 
     # ------------------------------------------------------------------ prefill
@@ -368,15 +464,19 @@ class Engine:
         toks, pos, slots, cu = [], [], [], [0]
         if not batch:  # lockstep dummy: one token written to the reserved page 0
             toks, pos, slots, cu = [0], [0], [torch.zeros(1, dtype=torch.int64)], [0, 1]
+        prefix_lens, pre_slots = [], []
         for req in batch:
             ids = req.input_ids + req.output_ids
-            n = len(ids)
-            toks.extend(ids)
-            pos.extend(range(n))
+            n, c = len(ids), req.prefill_cached
+            toks.extend(ids[c:])
+            pos.extend(range(c, n))
             pg = torch.tensor(req.pages, dtype=torch.int64)
             idx = torch.arange(n)
-            slots.append(pg[idx // ps] * ps + idx % ps)
-            cu.append(cu[-1] + n)
+            sl = pg[idx // ps] * ps + idx % ps
+            slots.append(sl[c:])
+            pre_slots.append(sl[:c])
+            prefix_lens.append(c)
+            cu.append(cu[-1] + n - c)
         # one pinned host staging buffer per prefill: tokens | positions | slot mapping | cu_seqlens, one H2D copy
         n_tok = len(toks)
         host = torch.empty(3 * n_tok + len(cu), dtype=torch.int32, pin_memory=self.on_gpu)
@@ -389,6 +489,13 @@ class Engine:
                                                  staged[3 * n_tok:])
         max_len = max(b - a for a, b in zip(cu[:-1], cu[1:]))
         meta = InferMeta(True, cu_t, max_len, slot_mapping, page_size=ps)
+        if any(prefix_lens):
+            # part of every sequence is already in the KV cache: the attention reads those keys / values from their
+            # pages (prefix slots) next to the ones this pass computes
+            from ..models.torch_impl import PrefixInfo
+
+            meta.prefix = PrefixInfo.build(prefix_lens, [b - a for a, b in zip(cu[:-1], cu[1:])], torch.cat(pre_slots), dev)
+            self.stats["cached_tokens"] = self.stats.get("cached_tokens", 0) + sum(prefix_lens)
         want_routes = any(r.return_routed_experts for r in batch) and self.cfg.is_moe
         record = [] if want_routes else None
         kw = {"max_seqlen": max_len} if self.on_gpu and hasattr(self.model, "launches") else {}
@@ -404,8 +511,24 @@ class Engine:
         self.h2d_bytes += 12 * len(toks) + 4 * len(cu)
         self.stats["prefill_tokens"] += len(toks)
         for i, req in enumerate(batch):
-            if routes is not None and req.return_routed_experts and not req.routed_experts:
-                req.routed_experts.append(routes[cu[i]:cu[i + 1]])
+            if routes is not None and req.return_routed_experts:
+                # this pass covered positions [cached, n): keep what is not recorded yet (after a retraction only the
+                # position of the token that had been sampled but not fed is new)
+                n_i = req.prefill_cached + (cu[i + 1] - cu[i])
+                start = max(req.routes_tokens, req.prefill_cached)
+                if start < n_i:
+                    req.routed_experts.append(routes[cu[i] + (start - req.prefill_cached):cu[i + 1]])
+                    req.routes_tokens = n_i
+            if self.prefix is not None and req.cache_epoch == self.prefix.epoch:
+                # the full pages this pass completed join the prefix tree at once (the other samples of the prompt are
+                # waiting for exactly these); the request keeps using them through references
+                ids = req.input_ids + req.output_ids
+                if len(ids) // ps > len(req.nodes):
+                    nodes, _ = self.prefix.insert(ids, req.pages, self._page_payloads(req, len(ids) // ps), skip=len(req.nodes),
+                                                  stop_at_duplicate=True)
+                    self.prefix.lock(nodes[len(req.nodes):])
+                    req.nodes = list(nodes)
+            req.prefill_cached = 0
             self.running.append(req)
             self._append_token(req, int(tok_l[i]), float(lp_l[i]))
 
@@ -455,7 +578,7 @@ class Engine:
                 continue
             need = self._pages_needed(req.seq_len)
             while len(req.pages) < need:
-                pg = self.pool.alloc(1)
+                pg = self._alloc(1)
                 if pg is None:
                     victim = self.running[-1]
                     self._retract(victim)
@@ -510,7 +633,7 @@ class Engine:
         for req in self.running:
             need = self._pages_needed(req.seq_len + lookahead)
             while len(req.pages) < need:
-                pg = self.pool.alloc(1)
+                pg = self._alloc(1)
                 if pg is None:
                     return False
                 req.pages.extend(pg)
@@ -600,6 +723,7 @@ class Engine:
                 continue
             if routes_c is not None and r.return_routed_experts:
                 r.routed_experts.append(routes_c[i:i + 1].clone())
+                r.routes_tokens += 1
             self.stats["decode_tokens"] += 1
             self._append_token(r, int(tok_l[i]), float(lp_l[i]))
 

@@ -195,6 +195,7 @@ def main(argv=None) -> None:
     ap.add_argument("--mem-fraction-static", type=float, default=0.85)
     ap.add_argument("--quantization", default="none", choices=["none", "mxfp8", "nvfp4"])
     ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--disable-radix-cache", action="store_true", help="turn the prefix (radix) cache off")
     ns = ap.parse_args(argv)
     cfg = get_config(ns.model_preset or ns.hf_checkpoint)
     on_gpu = ns.device.startswith("cuda")
@@ -215,7 +216,8 @@ def main(argv=None) -> None:
         free, total = torch.cuda.mem_get_info()
         kv_bytes = max(int(free - (1.0 - ns.mem_fraction_static) * total), 1 << 28)
     engine = Engine(model, max_running=ns.max_running_requests, page_size=ns.page_size, max_seq_len=ns.context_length,
-                    kv_mem_bytes=kv_bytes, use_cuda_graph=on_gpu, eos_token_id=getattr(tokenizer, "eos_token_id", None))
+                    kv_mem_bytes=kv_bytes, use_cuda_graph=on_gpu, eos_token_id=getattr(tokenizer, "eos_token_id", None),
+                    prefix_cache=not ns.disable_radix_cache)
     serve(engine, ns.host, ns.port, tokenizer, ns.hf_checkpoint or ns.model_preset or "")
 
 

@@ -204,7 +204,10 @@ class RLLoop:
         self.engine = Engine(engine_model, sync=sync, ep_decode=ep_decode, max_running=max_running, page_size=page, max_seq_len=max_ctx,
                              max_prefill_tokens=getattr(a, "engine_max_prefill_tokens", 16384), kv_mem_bytes=kv_bytes,
                              use_cuda_graph=not getattr(a, "sglang_disable_cuda_graph", False) and self.actor.on_gpu,
-                             eos_token_id=getattr(self.tokenizer, "eos_token_id", None), kv_storage=kv_storage)
+                             eos_token_id=getattr(self.tokenizer, "eos_token_id", None), kv_storage=kv_storage,
+                             # prefix (radix) cache: on unless --sglang-disable-radix-cache, as in the reference's engines;
+                             # lockstep expert-parallel engines keep it off (their ranks must run the same iterations)
+                             prefix_cache=not getattr(a, "sglang_disable_radix_cache", False) and sync is None)
         if sync is not None:
             self.engine.warm_up_decode_graphs()  # lockstep ranks capture their decode graphs together
         self.client = EngineClient([self.engine], self.tokenizer)

@@ -347,6 +347,12 @@ class B200Qwen3:
             C.paged_decode_attention(q, kc, vc, meta.block_table, meta.seq_lens, att, self._decode_scratch, meta.page_size,
                                      splits, scale)
             self.launches += 2
+        elif meta is not None and getattr(meta, "prefix", None) is not None:
+            # prefill behind a cached prefix: the keys / values of the cached tokens come from their pages, the tile
+            # table gives every query tile its sequence's key range and the position of its first query
+            kf, vf = meta.prefix.full_kv(k, self._v_view(qkv), *kv_cache[i])
+            att, _ = self.C.flash_attn_fwd(q, kf, vf, meta.prefix.tiles, scale, self.status)
+            self.launches += 5
         else:
             att, _ = self.attention(q, k, self._v_view(qkv), cu)
         h2, _, x2 = self._o_proj_ln2(i, att.view(att.shape[0], -1), x)

@@ -33,6 +33,44 @@ class InferMeta:
     seq_lens: Optional[torch.Tensor] = None
     page_size: int = 16
     cu_list: list = field(default_factory=list)
+    prefix: Optional["PrefixInfo"] = None  # prefill only: part of every sequence is already in the KV cache
+
+
+@dataclass
+class PrefixInfo:
+    """Prefill over sequences whose first ``prefix_lens[i]`` tokens are cached: the pass computes only the remaining
+    ``new_lens[i]`` tokens, and the attention reads keys / values of the cached part from the cache slots ``pre_slots``.
+    ``pre_dst`` / ``new_dst`` place both parts in one packed key / value tensor per layer (sequence i: its cached rows,
+    then its new rows), which is what the attention kernel's tile table (``tiles``) indexes."""
+    prefix_lens: list
+    new_lens: list
+    pre_slots: torch.Tensor
+    pre_dst: torch.Tensor
+    new_dst: torch.Tensor
+    total: int
+    tiles: Optional[torch.Tensor] = None
+
+    @classmethod
+    def build(cls, prefix_lens, new_lens, pre_slots: torch.Tensor, device) -> "PrefixInfo":
+        pre_dst, new_dst, start = [], [], 0
+        for c, n in zip(prefix_lens, new_lens):
+            pre_dst.append(torch.arange(start, start + c))
+            new_dst.append(torch.arange(start + c, start + c + n))
+            start += c + n
+        from ..ops.attention import build_tiles
+
+        return cls(list(prefix_lens), list(new_lens), pre_slots.to(device=device, dtype=torch.int64),
+                   torch.cat(pre_dst).to(device), torch.cat(new_dst).to(device), start,
+                   build_tiles(new_lens, prefix_lens).to(device))
+
+    def full_kv(self, k_new: torch.Tensor, v_new: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor):
+        """Packed keys / values of every sequence: cached rows gathered from the cache, then the rows of this pass."""
+        kf = k_new.new_empty((self.total,) + tuple(k_new.shape[1:]))
+        vf = v_new.new_empty((self.total,) + tuple(v_new.shape[1:]))
+        kf[self.new_dst], vf[self.new_dst] = k_new, v_new
+        kf[self.pre_dst] = kc[self.pre_slots].to(k_new.dtype)
+        vf[self.pre_dst] = vc[self.pre_slots].to(v_new.dtype)
+        return kf, vf
 
 
 class TorchQwen3:
@@ -73,6 +111,15 @@ class TorchQwen3:
                 else:
                     kf, vf = gather_kv_autograd(k, v, lens, cp, rank, group, layout)
                     att = attention_zigzag(q, kf, vf, lens, cp, rank, scale, layout)
+            elif meta is not None and meta.prefix is not None:
+                # prefill behind a cached prefix: every sequence's new queries attend to its cached + new keys
+                pf = meta.prefix
+                kf, vf = pf.full_kv(k, v, *kv_cache[i])
+                outs, q0, s0 = [], 0, 0
+                for c, n in zip(pf.prefix_lens, pf.new_lens):
+                    outs.append(R.attention_prefix(q[q0:q0 + n], kf[s0:s0 + c + n], vf[s0:s0 + c + n], c, scale))
+                    q0, s0 = q0 + n, s0 + c + n
+                att = torch.cat(outs, 0)
             else:
                 att = R.attention_varlen(q, k, v, cu, scale)
         else:

@@ -194,3 +194,62 @@ def test_remote_client_balances_and_fans_out():
 
     asyncio.run(main())
     assert sum(u.endswith("/pause_generation") for _, u in calls) == 2
+
+
+def _logprob_parity(m, prompts, res, atol=1e-4):
+    for p, r in zip(prompts, res):
+        ids = p + r["output_ids"]
+        tok, pos, cu = torch.tensor(ids), torch.arange(len(ids)), torch.tensor([0, len(ids)])
+        lp, _ = m.forward_logprobs(tok, pos, cu, torch.arange(len(p) - 1, len(ids) - 1), tok[len(p):], 1.0)
+        elp = torch.tensor([x[0] for x in r["meta_info"]["output_token_logprobs"]])
+        assert torch.allclose(lp, elp, atol=atol)
+
+
+@pytest.mark.parametrize("name", ["qwen3-tiny", "qwen3-tiny-moe"])
+def test_prefix_cache_shares_prompt_pages_and_changes_nothing(name):
+    """Eight samples of one prompt (the GRPO group), a second prompt, and a follow-up turn that re-sends a finished
+    conversation: with the prefix cache the shared tokens are computed once, and tokens, log-probs and routed experts
+    equal those of an engine without it."""
+    cfg, m, plain = _engine(name, max_running=8, page_size=8, max_seq_len=160)
+    _, _, cached = _engine(name, max_running=8, page_size=8, max_seq_len=160, prefix_cache=True)
+    cached.model = m
+    p0, p1 = _prompts(cfg, [37, 21], seed=3)
+    prompts = [p0] * 4 + [p1] * 2
+    sps = [SamplingParams(max_new_tokens=6 + i, sampling_seed=i) for i in range(len(prompts))]
+    moe = cfg.is_moe
+    a = plain.generate(prompts, sps, return_routed_experts=moe)
+    b = cached.generate(prompts, sps, return_routed_experts=moe)
+    for ra, rb in zip(a, b):
+        assert ra["output_ids"] == rb["output_ids"]
+        la = torch.tensor([x[0] for x in ra["meta_info"]["output_token_logprobs"]])
+        lb = torch.tensor([x[0] for x in rb["meta_info"]["output_token_logprobs"]])
+        assert torch.allclose(la, lb, atol=1e-5)
+        if moe:
+            assert torch.equal(ra["meta_info"]["routed_experts"], rb["meta_info"]["routed_experts"])
+    _logprob_parity(m, prompts, b)
+    # samples 2..4 of the first prompt found its four full pages (32 of 37 tokens), the second sample of the other its two
+    assert [r["meta_info"]["cached_tokens"] for r in b] == [0, 32, 32, 32, 0, 16]
+    assert cached.stats["prefill_tokens"] < plain.stats["prefill_tokens"]
+    assert not cached.running and cached.pool.num_free + cached.prefix.num_pages == cached.num_pages - 1
+    # a follow-up turn: the whole first conversation plus a few new tokens
+    turn2 = p0 + b[0]["output_ids"] + _prompts(cfg, [5], seed=9)[0]
+    ra = plain.generate([turn2], SamplingParams(max_new_tokens=5, sampling_seed=40), return_routed_experts=moe)[0]
+    rb = cached.generate([turn2], SamplingParams(max_new_tokens=5, sampling_seed=40), return_routed_experts=moe)[0]
+    assert ra["output_ids"] == rb["output_ids"] and rb["meta_info"]["cached_tokens"] >= 40
+    if moe:
+        assert torch.equal(ra["meta_info"]["routed_experts"], rb["meta_info"]["routed_experts"])
+    # a weight update forgets everything
+    assert cached.flush_cache() and cached.prefix.num_pages == 0 and cached.pool.num_free == cached.num_pages - 1
+    rc = cached.generate([turn2], SamplingParams(max_new_tokens=5, sampling_seed=40))[0]
+    assert rc["meta_info"]["cached_tokens"] == 0 and rc["output_ids"] == ra["output_ids"]
+
+
+def test_prefix_cache_gives_pages_back_under_pressure():
+    """A pool too small to keep everything cached: unreferenced cached pages are evicted, nothing leaks, results hold."""
+    cfg, m, eng = _engine(max_running=2, page_size=8, max_seq_len=64, num_pages=14, prefix_cache=True)
+    prompts = _prompts(cfg, [30, 28, 33, 31, 29, 27], seed=5)
+    sps = [SamplingParams(max_new_tokens=10, sampling_seed=i) for i in range(len(prompts))]
+    res = eng.generate(prompts, sps)
+    assert [len(r["output_ids"]) for r in res] == [10] * 6
+    _logprob_parity(m, prompts, res)
+    assert eng.pool.num_free + eng.prefix.num_pages == eng.num_pages - 1
