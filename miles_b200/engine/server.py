@@ -82,8 +82,11 @@ def build_app(engine: Engine, tokenizer=None, model_path: str = ""):
         from ..weight_sync.registry import take_bucket
 
         n = 0
+        from ..models.hf_mapping import param_or_hf_view
+
         for name, tensor in take_bucket(body["bucket_id"]):
-            engine.store.params[name].copy_(tensor.to(engine.store.params[name].dtype))
+            dst = param_or_hf_view(engine.cfg, engine.store, name)  # native or HuggingFace tensor name
+            dst.copy_(tensor.to(dst.dtype))
             n += 1
         if body.get("weight_version") is not None:
             engine.update_weight_version(body["weight_version"])

@@ -83,6 +83,29 @@ def hf_names(cfg: ModelConfig, store, tp_group=None) -> Iterator[tuple]:
             yield item
 
 
+def param_or_hf_view(cfg: ModelConfig, store, name: str) -> torch.Tensor:
+    """The destination of a weight that arrives under ``name``: a native parameter name, or a HuggingFace tensor name,
+    which maps to a view of the (possibly fused) native parameter. Because HF pieces land in views (q / k / v rows of
+    the fused QKV, gate / up rows of the fused first MLP matrix, one expert's rows of the stacked expert tensors), a
+    sender may deliver them in any order and split them over buckets as it likes: no group of tensors has to arrive in
+    one call (the reference needs such atomic groups for loaders that fuse on arrival,
+    miles/backends/megatron_utils/update_weight/common.py:21-131)."""
+    if name in store.params:
+        return store.params[name]
+    views = getattr(store, "_hf_views", None)
+    if views is None:
+        assert getattr(store, "tp_size", 1) == 1, "HF-named updates address unsharded parameters"
+        el = cfg.num_experts // store.ep_size if cfg.is_moe else 0
+        views = {}
+        for pname, dst in store.named_parameters():
+            for hf_name, view in to_hf(getattr(store, "global_cfg", cfg), pname, dst, expert_offset=store.ep_rank * el):
+                views[hf_name] = view
+        store._hf_views = views
+    if name not in views:
+        raise KeyError(f"{name} is neither a parameter of this model nor one of its HuggingFace tensor names")
+    return views[name]
+
+
 def from_hf(cfg: ModelConfig, store, get_tensor, strict: bool = True) -> int:
     """Fill ``store`` from HF tensors; ``get_tensor(hf_name) -> tensor | None``. Returns #tensors loaded."""
     from .params import build_specs, is_tp_sharded, tp_slice

@@ -23,6 +23,8 @@ from typing import Iterable, Optional, Sequence
 import torch
 import torch.distributed as dist
 
+from ..models.hf_mapping import param_or_hf_view
+
 _GROUPS: dict = {}
 
 
@@ -105,7 +107,7 @@ def receive_bucket(header: dict, store, device=None) -> int:
     for name, dt, shape in zip(header["names"], header["dtypes"], header["shapes"]):
         buf = torch.empty(shape, dtype=_DT[dt], device=dev)
         dist.broadcast(buf, src=0, group=pg)
-        dst = store.params[name]
+        dst = param_or_hf_view(store.global_cfg, store, name)  # native or HuggingFace tensor name
         if tuple(dst.shape) != tuple(buf.shape):
             raise ValueError(f"{name}: received shape {tuple(buf.shape)} but the engine holds {tuple(dst.shape)}")
         dst.copy_(buf.to(dst.dtype))

@@ -369,3 +369,28 @@ def test_async_loop_overlaps_generation_with_training_on_remote_engines():
         if loop.weight_updater is not None and loop.weight_updater.connected:
             loop.weight_updater.disconnect()
         loop.fleet.stop()
+
+
+def test_hf_named_pieces_update_fused_parameters_in_any_order():
+    """Weights may arrive under HuggingFace tensor names, in any order and split over buckets anyhow: every piece is
+    copied into its view of the fused native parameter (so no group of tensors has to arrive atomically)."""
+    import random
+
+    import pytest
+    import torch
+
+    from miles_b200.models import ParamStore, get_config
+    from miles_b200.models.hf_mapping import hf_names, param_or_hf_view
+
+    for name in ("qwen3-tiny", "qwen3-tiny-moe"):
+        cfg = get_config(name)
+        src = ParamStore(cfg, "cpu", torch.float32, seed=1)
+        dst = ParamStore(cfg, "cpu", torch.float32, seed=2)
+        items = list(hf_names(cfg, src))
+        random.Random(0).shuffle(items)
+        for n, t in items:
+            param_or_hf_view(cfg, dst, n).copy_(t)
+        assert all(torch.equal(src.params[k], dst.params[k]) for k in src.params)
+        assert param_or_hf_view(cfg, dst, "final_norm.weight") is dst.params["final_norm.weight"]
+        with pytest.raises(KeyError):
+            param_or_hf_view(cfg, dst, "model.layers.0.no_such.weight")
