@@ -107,3 +107,42 @@ def test_sampling_kernel_distribution(ext):
     sp, si = p.sort(descending=True)
     nucleus = set(si[: int((sp.cumsum(0) < 0.5).sum().item()) + 1].tolist())
     assert set(out.tolist()) <= nucleus
+
+
+@pytest.mark.parametrize("name", ["qwen3-smoke", "qwen3-smoke-moe"])
+def test_prefix_cache_on_the_sm100_path(name):
+    """The samples of one prompt share its pages (prefill of the later samples attends to cached keys / values through
+    the tile table's key ranges), a follow-up turn finds the finished conversation; the log-probs the engine reports
+    still match a recomputation with routing replay, and the routed experts of cached tokens come from the cache."""
+    dev = torch.device("cuda")
+    cfg = get_config(name)
+    st = ParamStore(cfg, dev, torch.bfloat16, init_std=0.02)
+    m = build_model(cfg, st, "b200")
+    eng = Engine(m, max_running=8, page_size=64, max_seq_len=1024, use_cuda_graph=True, prefix_cache=True)
+    g = torch.Generator().manual_seed(1)
+    p0 = torch.randint(0, cfg.vocab_size, (300,), generator=g).tolist()
+    p1 = torch.randint(0, cfg.vocab_size, (150,), generator=g).tolist()
+    prompts = [p0] * 4 + [p1] * 2
+    sps = [SamplingParams(temperature=1.0, max_new_tokens=30 + 7 * i, sampling_seed=i) for i in range(len(prompts))]
+    res = eng.generate(prompts, sps, return_routed_experts=True)
+    assert [r["meta_info"]["cached_tokens"] for r in res] == [0, 256, 256, 256, 0, 128]
+    turn2 = p0 + res[0]["output_ids"] + torch.randint(0, cfg.vocab_size, (40,), generator=g).tolist()
+    r2 = eng.generate([turn2], SamplingParams(temperature=1.0, max_new_tokens=20, sampling_seed=9), return_routed_experts=True)[0]
+    assert r2["meta_info"]["cached_tokens"] >= 320
+    m.check_status()
+    for p, r in list(zip(prompts, res)) + [(turn2, r2)]:
+        ids = p + r["output_ids"]
+        tok = torch.tensor(ids, dtype=torch.int32, device=dev)
+        pos = torch.arange(len(ids), dtype=torch.int32, device=dev)
+        cu = torch.tensor([0, len(ids)], dtype=torch.int32, device=dev)
+        rows = torch.arange(len(p) - 1, len(ids) - 1, device=dev)
+        replay = None
+        if cfg.is_moe:
+            re = r["meta_info"]["routed_experts"].to(dev)
+            assert re.shape[0] == len(ids) - 1
+            replay = torch.cat([re, re[-1:]], 0)
+        lp, _ = m.forward_logprobs(tok, pos, cu, rows, tok[len(p):], 1.0, replay=replay)
+        elp = torch.tensor([x[0] for x in r["meta_info"]["output_token_logprobs"]], device=dev)
+        d = (lp - elp).abs()
+        assert d.mean().item() < 2e-2 and d.max().item() < 0.25, (d.mean().item(), d.max().item())
+    assert not eng.running and eng.pool.num_free + eng.prefix.num_pages == eng.num_pages - 1
