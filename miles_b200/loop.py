@@ -58,6 +58,14 @@ class RLLoop:
         self.rep = self.ps.dp_cp.rank * self.ps.pp.size + self.ps.pp.rank
         torch.manual_seed(args.seed + self.rep)
         self.tokenizer = _load_tokenizer(args)
+        if self.ps.rank == 0 and os.environ.get("MILES_B200_ENV_REPORT", "1") != "0":
+            # library versions, GPUs, collective-steering environment and git state as one marked JSON line in the log
+            from .utils.env_report import collect_and_print
+
+            try:
+                collect_and_print()
+            except Exception as e:  # noqa: BLE001  (a report must never stop a run)
+                print(f"[miles_b200] environment report failed: {e!r}", flush=True)
         self.actor = TrainActor(args, "actor", self.ps)
         self.critic = None
         if getattr(args, "use_critic", False):
@@ -466,7 +474,16 @@ class RLLoop:
 
     def train(self, rollout_id: int, samples: list) -> dict:
         a = self.args
-        data = convert_samples_to_train_data(a, samples)
+        # the batch travels from the rollout side to the trainer through the object store (in-process by default;
+        # --object-store-backend file with --dump-details keeps every batch on disk in the ragged encoding)
+        if getattr(self, "object_store", None) is None:
+            from .utils.object_store import init_instance
+
+            self.object_store = init_instance(a)
+        ref = self.object_store.put(convert_samples_to_train_data(a, samples))
+        data = self.object_store.get(ref)
+        if not getattr(a, "dump_details", None):
+            self.object_store.delete(ref)
         if self.ft is not None and "train" in self.ft.components:
             return self.ft.train(rollout_id, data)  # through the cell group: retries, suspended cells, scripted faults
         return self._train_once(rollout_id, data)
@@ -670,7 +687,14 @@ class RLLoop:
             self.update_weights()  # engines start from the trainer's weights
         if a.eval_interval is not None and not getattr(a, "skip_eval_before_train", False) and self.start_rollout_id == 0:
             self.evaluate(-1)
+        profiler = None
+        if getattr(a, "use_pytorch_profiler", False) or getattr(a, "memory_snapshot_dir", None):
+            from .utils.profile_utils import TrainProfiler
+
+            profiler = TrainProfiler(a, self.ps.rank)  # torch profiler trace of steps [start, end), memory snapshot
         for rid in range(self.start_rollout_id, a.num_rollout):
+            if profiler is not None:
+                profiler.step(rid - 1)
             m = self.step(rid)
             history.append(m)
             if self.ps.rank == 0:
@@ -679,6 +703,8 @@ class RLLoop:
                 print(f"[rollout {rid}] " + " ".join(f"{k.split('/')[-1] if k.count('/')==1 else k}={m[k]:.5g}" for k in keys if k in m), flush=True)
             if getattr(a, "debug_exit_after_rollout", None) is not None and rid >= a.debug_exit_after_rollout:
                 break
+        if profiler is not None:
+            profiler.step(a.num_rollout - 1)  # closes a trace that runs to the last step
         from .checkpoint import wait_for_async_save
 
         wait_for_async_save()  # a background save must be complete before the job ends

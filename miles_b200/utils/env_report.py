@@ -58,11 +58,14 @@ def collect(packages=("torch", "numpy", "transformers", "flash_attn", "safetenso
     import importlib
 
     rep = NodeEnvReport(socket.gethostname(), sys.version.split()[0], platform.platform())
+    from importlib import metadata
+
     for p in packages:
-        try:
-            rep.packages[p] = getattr(importlib.import_module(p), "__version__", "?")
+        try:  # the installed version from the package metadata: nothing is imported for the report
+            rep.packages[p] = metadata.version(p.replace("_", "-"))
         except Exception:
-            rep.packages[p] = None
+            mod = sys.modules.get(p)
+            rep.packages[p] = getattr(mod, "__version__", None) if mod is not None else None
     try:
         import torch
 
