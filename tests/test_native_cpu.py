@@ -22,20 +22,6 @@ def test_page_pool_all_or_nothing_and_double_free(N):
         p.release([0])  # reserved page
 
 
-def test_scheduler_admission_growth_and_retraction(N):
-    s = N.Scheduler(num_pages=8, page_size=4, max_running=3, max_prefill_tokens=20)
-    adm = s.admit([(10, 7), (11, 4), (12, 9), (13, 1)])
-    assert [r for r, _ in adm] == [10, 11, 12] and s.num_running == 3  # slot limit stops request 13
-    assert [len(p) for _, p in adm] == [2, 2, 3] and s.num_free_pages == 0
-    for rid in (10, 11, 12):
-        s.advance(rid)
-    grown, retracted = s.grow_for_decode()  # request 10 now has 8 tokens and needs a third page: newest is retracted
-    assert retracted == [12] and (10, grown[0][1]) == grown[0] and s.running_ids() == [10, 11]
-    s.finish(10)
-    assert s.running_ids() == [11] and s.num_free_pages == 7 - 2
-    assert s.admit([(12, 9)])[0][0] == 12  # the retracted request comes back when pages are free
-
-
 def test_quorum_changes_on_timeout_join_and_evict(N):
     q = N.QuorumStore(timeout_s=10.0)
     q.heartbeat("cell-0", 0.0)
