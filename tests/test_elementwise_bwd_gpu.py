@@ -93,7 +93,7 @@ def test_logprob_entropy_forward_and_backward(ext, T, V, dtype):
     inv_t = 1.0 / 0.8
     logits = (torch.randn(T, V, device=DEV) * 3).to(dtype)
     tg = torch.randint(0, V, (T,), device=DEV, dtype=torch.int32)
-    lf = logits.float().requires_grad_(True)
+    lf = logits.detach().clone().float().requires_grad_(True)   # a leaf of its own (fp32 logits: .float() is no copy)
     lp_ref, ent_ref = R.logprob_entropy(lf, tg, inv_t)
     lp, ent, lse, px = ext.logprob_entropy_fwd(logits, tg, inv_t)
     torch.testing.assert_close(lp, lp_ref.detach(), rtol=1e-4, atol=2e-4)
@@ -106,6 +106,6 @@ def test_logprob_entropy_forward_and_backward(ext, T, V, dtype):
     # bf16 output: half a unit in the third significant digit of each element
     _close(dl, lf.grad, 1e-2, 1e-6, frac=2e-3)
     # only the log-prob gradient (no entropy term)
-    lf2 = logits.float().requires_grad_(True)
+    lf2 = logits.detach().clone().float().requires_grad_(True)
     (R.logprob_entropy(lf2, tg, inv_t)[0] * dlp).sum().backward()
     _close(ext.logprob_entropy_bwd(logits.clone(), tg, lse, px, dlp, None, inv_t), lf2.grad, 1e-2, 1e-6, frac=2e-3)
