@@ -1,5 +1,15 @@
-"""FastAPI app of the dashboard: ``/api/streams``, ``/api/{stream}?since=&limit=``, ``/api/advisories`` and ``/`` (one
-static page that polls the JSON endpoints and draws the step metrics as tables)."""
+"""FastAPI app of the dashboard.
+
+* ``/`` one static page that polls the JSON endpoints and draws the step metrics;
+* ``/api/meta`` what the run is (streams, steps seen, rollout dumps at hand), ``/api/streams``, ``/api/{stream}?since=&limit=``,
+  ``/api/advisories``;
+* ``/api/timeline/phases`` seconds per phase (rollout, log-probs, forward/backward, optimizer, weight update, wait) for
+  every step, ``/api/timeline/bubbles`` the share of each step in which the trainer waited, ``/api/timeline/gpu`` the
+  sampled GPU series per device, ``/api/timeline/engines`` the scraped engine gauges;
+* ``/api/rollout/{id}/summary|groups``, ``/api/rollout/{id}/sample/{i}/tokens|messages`` the rollout inspector over the
+  run's rollout dumps (``dump_reader.DumpReader``).
+
+Reference counterpart: miles/dashboard/server.py:76-309."""
 from .collector import advisories
 from .store import EventStore
 
@@ -31,8 +41,9 @@ refresh(); setInterval(refresh, 5000);
 </script>"""
 
 
-def build_dashboard_app(store: EventStore):
-    from fastapi import FastAPI
+def build_dashboard_app(store: EventStore, dumps=None):
+    """``dumps``: a ``dump_reader.DumpReader`` over the run's rollout dumps (None: the rollout inspector answers 404)."""
+    from fastapi import FastAPI, HTTPException
     from fastapi.responses import HTMLResponse
 
     app = FastAPI(title="miles_b200 dashboard")
@@ -48,6 +59,69 @@ def build_dashboard_app(store: EventStore):
     @app.get("/api/advisories")
     async def adv():
         return advisories(store)
+
+    PHASES = ("perf/rollout_time", "perf/train_log_probs_time", "perf/train_fwd_bwd_time", "perf/train_optimizer_time",
+              "perf/update_weights_time", "perf/train_wait_time", "perf/step_time")
+
+    @app.get("/api/meta")
+    async def meta():
+        ms = store.tail("metrics", 1)
+        return {"streams": store.streams(), "last_step": ms[-1].get("step") if ms else None,
+                "rollout_dumps": dumps.rollout_ids() if dumps is not None else [], "has_tokenizer": bool(dumps and dumps.tokenizer)}
+
+    @app.get("/api/timeline/phases")
+    async def phases(limit: int = 500):
+        return [{"step": m.get("step"), "t": m.get("t"), **{k.split("/", 1)[1]: m[k] for k in PHASES if k in m}}
+                for m in store.tail("metrics", limit)]
+
+    @app.get("/api/timeline/bubbles")
+    async def bubbles(limit: int = 500):
+        """Per step: the seconds not accounted for by rollout + training + weight update (host gaps, evaluation,
+        checkpoint writes) and the share of the step the trainer spent waiting for samples."""
+        out = []
+        for m in store.tail("metrics", limit):
+            st = m.get("perf/step_time")
+            if not st:
+                continue
+            busy = sum(m.get(k, 0.0) for k in ("perf/rollout_time", "perf/train_time", "perf/update_weights_time"))
+            out.append({"step": m.get("step"), "step_time": st, "unaccounted_s": max(st - busy, 0.0),
+                        "wait_ratio": m.get("perf/wait_time_ratio", (m.get("perf/train_wait_time", 0.0)) / st)})
+        return out
+
+    @app.get("/api/timeline/gpu")
+    async def gpu(since: float = 0.0, limit: int = 2000):
+        series: dict = {}
+        for r in list(store.read("gpus", since=since))[-limit:]:
+            series.setdefault(str(r.get("gpu")), []).append({k: r.get(k) for k in ("t", "util", "mem_used", "power_w", "sm_mhz")})
+        return series
+
+    @app.get("/api/timeline/engines")
+    async def engines(since: float = 0.0, limit: int = 2000):
+        series: dict = {}
+        for r in list(store.read("engines", since=since))[-limit:]:
+            series.setdefault(r.get("engine"), []).append({k: v for k, v in r.items() if k != "engine"})
+        return series
+
+    def _or_404(v):
+        if v is None:
+            raise HTTPException(404, "no such rollout dump or sample (run with --save-debug-rollout-data / --dump-details)")
+        return v
+
+    @app.get("/api/rollout/{rollout_id}/summary")
+    async def rollout_summary(rollout_id: int):
+        return _or_404(dumps.summary(rollout_id) if dumps is not None else None)
+
+    @app.get("/api/rollout/{rollout_id}/groups")
+    async def rollout_groups(rollout_id: int):
+        return _or_404(dumps.groups(rollout_id) if dumps is not None else None)
+
+    @app.get("/api/rollout/{rollout_id}/sample/{index}/tokens")
+    async def sample_tokens(rollout_id: int, index: int):
+        return _or_404(dumps.sample_tokens(rollout_id, index) if dumps is not None else None)
+
+    @app.get("/api/rollout/{rollout_id}/sample/{index}/messages")
+    async def sample_messages(rollout_id: int, index: int):
+        return _or_404(dumps.sample_messages(rollout_id, index) if dumps is not None else None)
 
     @app.get("/api/{stream}")
     async def read(stream: str, since: float = 0.0, limit: int = 200):

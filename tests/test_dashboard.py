@@ -56,3 +56,47 @@ def test_engine_scrape_and_advisories(tmp_path):
     assert col.scrape_engines_once(fetch) == 1
     rules = {a["rule"] for a in advisories(st)}
     assert {"engine_down", "engine_queue"} <= rules
+
+
+def test_timeline_and_rollout_inspector_endpoints(tmp_path):
+    import os
+
+    import torch
+    from fastapi.testclient import TestClient
+
+    from miles_b200.dashboard.serve import build
+    from miles_b200.utils.types import Sample
+
+    root = str(tmp_path)
+    s = EventStore(os.path.join(root, "dashboard"))
+    c = Collector(s, gpu_sampler=lambda: [{"gpu": g, "util": 50 + g, "mem_used": 1, "mem_total": 2, "power_w": 500.0, "sm_mhz": 1900} for g in (0, 1)])
+    for i in range(3):
+        c.log_metrics({"perf/rollout_time": 6.0, "perf/train_time": 3.0, "perf/train_fwd_bwd_time": 2.0, "perf/update_weights_time": 0.1,
+                       "perf/step_time": 10.0, "perf/train_wait_time": 0.5}, step=i)
+    c.sample_gpus_once()
+    os.makedirs(os.path.join(root, "rollout_data"))
+    samples = []
+    for g in range(2):
+        for k in range(3):
+            sm = Sample(index=g * 3 + k, group_index=g, prompt="what is 2+2?", tokens=[5, 6, 7, 10 + k, 11 + k], response="four", response_length=2,
+                        reward=float(k % 2) if g == 0 else 1.0, rollout_log_probs=[-0.5, -0.25], loss_mask=[1, 0], weight_versions=[3])
+            sm.status = Sample.Status.COMPLETED
+            samples.append(sm.to_dict())
+    torch.save({"rollout_id": 0, "samples": samples}, os.path.join(root, "rollout_data", "0.pt"))
+    app = TestClient(build(root))
+    meta = app.get("/api/meta").json()
+    assert meta["rollout_dumps"] == [0] and meta["last_step"] == 2 and "metrics" in meta["streams"]
+    ph = app.get("/api/timeline/phases").json()
+    assert len(ph) == 3 and ph[0]["rollout_time"] == 6.0 and ph[0]["train_fwd_bwd_time"] == 2.0
+    bub = app.get("/api/timeline/bubbles").json()
+    assert abs(bub[0]["unaccounted_s"] - 0.9) < 1e-9 and abs(bub[0]["wait_ratio"] - 0.05) < 1e-9
+    assert set(app.get("/api/timeline/gpu").json()) == {"0", "1"}
+    summ = app.get("/api/rollout/0/summary").json()
+    assert summ["num_samples"] == 6 and summ["num_groups"] == 2 and summ["weight_versions"] == [3] and summ["response_len_max"] == 2
+    groups = app.get("/api/rollout/0/groups").json()
+    assert [g["all_equal"] for g in groups] == [False, True] and groups[0]["rewards"] == [0.0, 1.0, 0.0]
+    toks = app.get("/api/rollout/0/sample/4/tokens").json()
+    assert toks["prompt_tokens"] == 3 and [t["id"] for t in toks["tokens"]] == [11, 12] and toks["tokens"][1]["loss_mask"] == 0
+    msgs = app.get("/api/rollout/0/sample/1/messages").json()["messages"]
+    assert msgs[0]["role"] == "user" and msgs[-1] == {"role": "assistant", "content": "four"}
+    assert app.get("/api/rollout/7/summary").status_code == 404 and app.get("/api/rollout/0/sample/99/tokens").status_code == 404
