@@ -99,7 +99,7 @@ class B200Qwen3:
         cu = self._cp_full_cu(lens)
         out_f, lse_f = self.C.flash_attn_fwd(qf, kf, vf, self._tiles.get(cu), cfg.head_dim ** -0.5, self.status)
         self.launches += 1
-        out = sequence_to_heads(out_f, lens, cp, rank, group, layout)
+        out = sequence_to_heads(out_f, lens, cp, rank, group, layout).contiguous()  # (a view when a rank holds one head)
         return out, (lse_f, qf, kf, vf, out_f, cu)
 
     def _attention_cp_backward(self, d_out, saved):
@@ -112,7 +112,7 @@ class B200Qwen3:
         dqf, dkf, dvf = self.C.flash_attn_bwd(qf, kf, vf, out_f, do_f, lse_f, self._tiles.get_bwd(cu), self.cfg.head_dim ** -0.5,
                                               self.status)
         self.launches += 3
-        return tuple(sequence_to_heads(t, lens, cp, rank, group, layout) for t in (dqf, dkf, dvf))
+        return tuple(sequence_to_heads(t, lens, cp, rank, group, layout).contiguous() for t in (dqf, dkf, dvf))
 
     # ------------------------------------------------------------------ GEMM helpers
     def _gemm(self, a, b, out, a_mn=False, b_mn=False, acc=False):
