@@ -14,6 +14,14 @@ def _rel(got, ref):
     return (got.float() - ref.float()).abs().max().item() / (ref.float().abs().max().item() + 1e-6)
 
 
+def _each(got, ref, rtol, atol):
+    """Every element within ``rtol * |ref| + atol`` (a wrong element inside a large tile cannot hide behind the largest
+    magnitude of the tensor)."""
+    err = (got.float() - ref.float()).abs()
+    bad = err > rtol * ref.float().abs() + atol
+    assert not bad.any(), (int(bad.sum()), err[bad].max().item(), ref.float()[bad].abs().min().item())
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (1000, 776, 520), (64, 5120, 2048), (8, 2048, 4096), (300, 151936, 512)])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
 def test_gemm_majors_and_tails(ext, M, N, K, a_mn, b_mn):
@@ -29,9 +37,12 @@ def test_gemm_majors_and_tails(ext, M, N, K, a_mn, b_mn):
     c = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
     ext.gemm(a, b, c, a_mn, b_mn, False, 0, status)
     assert _rel(c, ref) < 1e-2 and status.item() == 0
+    rms = ref.pow(2).mean().sqrt().item()
+    _each(c, ref, 1.6e-2, 4e-3 * rms)          # bf16 output: two ulps of the element plus accumulation-order noise
     c32 = torch.ones(M, N, device=DEV, dtype=torch.float32)
     ext.gemm(a, b, c32, a_mn, b_mn, True, 0, status)
     assert _rel(c32, ref + 1) < 1e-3
+    _each(c32, ref + 1, 1e-3, 1e-3 * rms)      # fp32 accumulate-into output
 
 
 @pytest.mark.parametrize("T,E,K,align", [(512, 16, 8, 64), (4096, 128, 8, 64), (64, 128, 8, 1), (1, 8, 2, 1)])
@@ -160,6 +171,8 @@ def test_flash_attention_fwd_vs_fp32(ext, lens, Hq, Hk):
     assert status.item() == 0
     assert torch.isfinite(out.float()).all()
     assert _rel(out, ref) < 2e-2
+    # P travels to the second MMA as bf16: at most 2^-9 * sum p|v| <= 0.002 * max|v| per element, plus the output rounding
+    _each(out, ref, 1.6e-2, 5e-3 * v.float().abs().max().item())
     assert (lse - ref_lse).abs().max().item() < 2e-2
     # increasing scores along the sequence force a rescale at every block
     k2 = k.clone()
