@@ -67,6 +67,12 @@ class RLLoop:
             except Exception as e:  # noqa: BLE001  (a report must never stop a run)
                 print(f"[miles_b200] environment report failed: {e!r}", flush=True)
         self.actor = TrainActor(args, "actor", self.ps)
+        if self.ps.rank == 0 and os.environ.get("MILES_B200_ENV_REPORT", "1") != "0":
+            # which clauses of the trainer / rollout numerical contract this configuration keeps: says where a
+            # train / rollout log-prob difference may come from before the first step shows one
+            from .true_on_policy import check, explain
+
+            print(explain(check(args, self.actor.cfg)), flush=True)
         self.critic = None
         if getattr(args, "use_critic", False):
             cargs = copy.copy(args)

@@ -39,7 +39,12 @@ async def generate_and_rm(state: GenerateState, sample, sampling_params: dict, e
         sample.status = Sample.Status.ABORTED
         return sample
     fn = _resolve_generate_fn(args, sample)
-    out = await fn(GenerateFnInput(state, sample, dict(sampling_params), evaluation))
+    try:
+        out = await fn(GenerateFnInput(state, sample, dict(sampling_params), evaluation))
+    finally:
+        pacer = getattr(state, "pacer", None)
+        if pacer is not None and not evaluation:
+            pacer.sample_finished()  # --rollout-submission-granularity sample: this sample's slot is free again
     result = out.samples if hasattr(out, "samples") else out
     if getattr(args, "group_rm", False) and not evaluation:
         return result
@@ -93,14 +98,24 @@ class InferenceRolloutFn:
         drop_reasons: Counter = Counter()
         t0 = time.perf_counter()
 
+        # pacing of the submissions (rollout/submission.py): by group (a slot frees when a whole prompt group is back) or by
+        # sample (every finished sample frees its slot, so the engine's batch stays full behind a group's stragglers)
+        from .submission import make_pacer
+
+        pacer = state.pacer = make_pacer(args)
+
         def submit(n_groups: int) -> None:
-            for group in self.data_source.get_samples(n_groups):
+            groups = self.data_source.get_samples(n_groups)
+            pacer.submitted(groups)
+            for group in groups:
                 pending.add(asyncio.ensure_future(generate_and_rm_group(state, group, state.sampling_params)))
 
         while len(data) < target:
-            if len(data) + len(pending) < target:
+            if pacer.may_submit(len(pending), target - len(data)):
                 submit(args.over_sampling_batch_size)
-            done, pending = await asyncio.wait(pending, return_when=asyncio.FIRST_COMPLETED)
+            if not pending:
+                continue
+            done, pending = await pacer.wait(pending)
             for task in done:
                 group = task.result()
                 all_groups.append(group)

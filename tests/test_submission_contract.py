@@ -42,3 +42,23 @@ def test_contract_names_what_breaks_bit_equality():
     assert "routing" in {c.key for c in check(A(), get_config("qwen3-30B-A3B")).satisfied}
     assert "routing" in {c.key for c in check(A(), get_config("qwen3-4B")).satisfied}
     assert "broken: attention" in explain(rep)
+
+
+def test_rollout_loop_paces_by_sample_and_by_group():
+    """The whole loop under both granularities: same batch, same rewards; by sample the pacer's in-flight count returns
+    to zero and new groups were admitted while others were still generating."""
+    from miles_b200.loop import RLLoop
+    from miles_b200.utils.arguments import parse_args
+
+    base = ["--model-preset", "qwen3-tiny", "--rollout-batch-size", "4", "--n-samples-per-prompt", "4", "--rollout-max-response-len", "8",
+            "--rollout-max-prompt-len", "16", "--rm-type", "parity", "--lr", "1e-5", "--micro-batch-size", "8", "--colocate",
+            "--num-rollout", "1", "--actor-num-gpus-per-node", "1", "--over-sampling-batch-size", "4"]
+    outs = {}
+    for g in ("group", "sample"):
+        loop = RLLoop(parse_args(base + ["--rollout-submission-granularity", g]))
+        samples, _ = loop.generate(0)
+        assert len(samples) == 16
+        outs[g] = sorted((s.index, tuple(s.tokens), s.reward) for s in samples)
+        pacer = loop.rollout_fn.state.pacer
+        assert pacer.by_sample == (g == "sample") and pacer.samples_in_flight == 0
+    assert outs["group"] == outs["sample"]
