@@ -110,8 +110,18 @@ class Engine:
                  max_seq_len: int = 16384, max_prefill_tokens: int = 16384, kv_mem_bytes: Optional[int] = None,
                  use_cuda_graph: Optional[bool] = None, eos_token_id: Optional[int] = None, kv_dtype=None,
                  sync=None, ep_decode=None, kv_storage: Optional[torch.Tensor] = None, overlap_decode: bool = True,
-                 prefix_cache: bool = False):
+                 prefix_cache: bool = False, memory_saver: bool = False):
         self.model = model
+        # KV cache in the tagged virtual-memory arena (utils/memory_saver.py): releasing it gives the physical memory
+        # back but keeps the addresses, so captured decode graphs survive a release / resume cycle
+        self._saver = None
+        self._kv_tag = f"kv_cache_{id(self):x}"
+        self._kv_paused = False
+        if memory_saver and kv_storage is None and model.store.device.type == "cuda":
+            from ..utils.memory_saver import MemorySaver
+
+            saver = MemorySaver()
+            self._saver = saver if saver.available else None
         self.prefix = None
         if prefix_cache:
             from .prefix_cache import PrefixCache
@@ -176,9 +186,12 @@ class Engine:
             views = [flat[i * per:(i + 1) * per].view(slots, cfg.num_kv_heads, cfg.head_dim) for i in range(2 * cfg.num_layers)]
             self.kv_cache = [(views[2 * i], views[2 * i + 1]) for i in range(cfg.num_layers)]
             return
-        self.kv_cache = [(torch.zeros(slots, cfg.num_kv_heads, cfg.head_dim, dtype=self.kv_dtype, device=self.dev),
-                          torch.zeros(slots, cfg.num_kv_heads, cfg.head_dim, dtype=self.kv_dtype, device=self.dev))
-                         for _ in range(cfg.num_layers)]
+        import contextlib
+
+        with (self._saver.region(self._kv_tag) if self._saver is not None else contextlib.nullcontext()):
+            self.kv_cache = [(torch.zeros(slots, cfg.num_kv_heads, cfg.head_dim, dtype=self.kv_dtype, device=self.dev),
+                              torch.zeros(slots, cfg.num_kv_heads, cfg.head_dim, dtype=self.kv_dtype, device=self.dev))
+                             for _ in range(cfg.num_layers)]
 
     def _alloc_decode_buffers(self) -> None:
         B, dev = self.max_running, self.dev
@@ -215,15 +228,25 @@ class Engine:
         if "cuda_graph" in tags:
             self._graphs.clear()
         if "kv_cache" in tags:
-            self.kv_cache = None
             if self.prefix is not None:
                 self.pool.release(self.prefix.clear())  # the cached keys / values are gone with the memory
-            self._graphs.clear()  # graphs hold raw cache pointers
+            if self._saver is not None and self.kv_cache is not None:
+                if not self._kv_paused:
+                    torch.cuda.synchronize(self.dev)
+                    self._saver.pause(self._kv_tag)  # physical memory released, addresses (and graphs) stay valid
+                    self._kv_paused = True
+            else:
+                self.kv_cache = None
+                self._graphs.clear()  # graphs hold raw cache pointers
         if self.on_gpu:
             torch.cuda.empty_cache()
 
     def resume_memory_occupation(self, tags: Sequence[str] = ("kv_cache",)) -> None:
-        if "kv_cache" in tags and self.kv_cache is None:
+        if "kv_cache" in tags and self._kv_paused:
+            self._saver.resume(self._kv_tag)
+            self._kv_paused = False
+            self.pool = PagePool(self.num_pages)
+        elif "kv_cache" in tags and self.kv_cache is None:
             self._alloc_kv()
             self.pool = PagePool(self.num_pages)
 
@@ -371,7 +394,7 @@ class Engine:
 
         With ``sync`` every expert-parallel rank agrees on the kind of iteration (2 prefill, 1 decode, 0 idle);
         ranks without matching work run a one-token dummy forward so that the MoE exchanges stay aligned."""
-        if self.kv_cache is None:
+        if self.kv_cache is None or self._kv_paused:
             return []
         before = set(self.finished)
         admitted = [] if self.paused else self._admit()

@@ -221,7 +221,10 @@ class RLLoop:
                              eos_token_id=getattr(self.tokenizer, "eos_token_id", None), kv_storage=kv_storage,
                              # prefix (radix) cache: on unless --sglang-disable-radix-cache, as in the reference's engines;
                              # lockstep expert-parallel engines keep it off (their ranks must run the same iterations)
-                             prefix_cache=not getattr(a, "sglang_disable_radix_cache", False) and sync is None)
+                             prefix_cache=not getattr(a, "sglang_disable_radix_cache", False) and sync is None,
+                             # a KV cache of its own that --offload-rollout releases: tagged virtual memory keeps the
+                             # addresses (captured graphs stay valid across release / resume)
+                             memory_saver=kv_storage is None and bool(getattr(a, "offload_rollout", False)))
         if sync is not None:
             self.engine.warm_up_decode_graphs()  # lockstep ranks capture their decode graphs together
         self.client = EngineClient([self.engine], self.tokenizer)
