@@ -39,6 +39,8 @@ class EngineClient:
         if ids is None:
             assert self.tokenizer is not None, "text prompts need a tokenizer"
             ids = self.tokenizer(payload["text"], add_special_tokens=False)["input_ids"]
+        if int((payload.get("sampling_params") or {}).get("max_new_tokens", 1) or 0) == 0:
+            return self._score(ids, payload)
         sp = SamplingParams.from_dict(payload.get("sampling_params") or {})
         rid = payload.get("rid") or f"c{next(self._rid)}"
         i = self._pick()
@@ -60,6 +62,22 @@ class EngineClient:
         else:
             res["text"] = ""
         return res
+
+    def _score(self, ids: list, payload: dict) -> dict:
+        """``max_new_tokens = 0``: score the input instead of generating (the request a distillation teacher gets,
+        reference: miles/rollout/on_policy_distillation.py:104-125). ``meta_info.input_token_logprobs`` holds
+        ``[logprob, token]`` per input token from ``logprob_start_len`` on (the first token of a sequence has none);
+        ``top_logprobs_num = k`` adds ``input_top_logprobs``: per position the k ``[logprob, token]`` pairs."""
+        start = int(payload.get("logprob_start_len", 0) or 0)
+        k = int(payload.get("top_logprobs_num", 0) or 0)
+        out = self.engines[self._pick()].score(ids, temperature=1.0, top_k=k)
+        meta = {"prompt_tokens": len(ids), "completion_tokens": 0, "finish_reason": {"type": "length"},
+                "input_token_logprobs": [[lp, t] for lp, t in zip(out["logprobs"], ids)][start:],
+                "output_token_logprobs": [], "weight_version": self.engines[0].weight_version}
+        if k:
+            meta["input_top_logprobs"] = [None if tp is None else [[l, t] for l, t in zip(tp["logprobs"], tp["ids"])]
+                                          for tp in out["top"]][start:]
+        return {"output_ids": [], "text": "", "meta_info": meta}
 
     def _ensure_pump(self) -> None:
         if self._pump_task is None or self._pump_task.done():

@@ -888,6 +888,36 @@ class Engine:
             self.model.launches += per_replay
         return out
 
+    # ------------------------------------------------------------------ scoring
+    @torch.no_grad()
+    def score(self, input_ids: Sequence[int], temperature: float = 1.0, top_k: int = 0) -> dict:
+        """Log-probs this model gives to a token sequence (no generation, no KV cache): ``logprobs[i]`` is the log-prob
+        of token ``i`` given the tokens before it (``None`` for the first). With ``top_k`` also the ``top_k`` most likely
+        tokens and their log-probs at every position (``top[i]`` predicts token ``i``). The scoring endpoint of a
+        teacher in on-policy distillation (``/generate`` with ``max_new_tokens = 0``)."""
+        ids = [int(t) for t in input_ids]
+        n = len(ids)
+        if n < 2:
+            return {"logprobs": [None] * n, "top": [None] * n}
+        dev = self.dev
+        tok = torch.tensor(ids, dtype=torch.int32, device=dev)
+        pos = torch.arange(n, dtype=torch.int32, device=dev)
+        cu = torch.tensor([0, n], dtype=torch.int32, device=dev)
+        rows = torch.arange(0, n - 1, dtype=torch.int64, device=dev)
+        kw = {"max_seqlen": n} if self.on_gpu and hasattr(self.model, "launches") else {}
+        inv_t = 1.0 / max(float(temperature), 1e-6)
+        top = [None] * n
+        if top_k > 0:
+            h = self.model.forward_hidden(tok, pos, cu, **kw)
+            ls = torch.log_softmax(self.model.logits(h[rows]).float() * inv_t, dim=-1)
+            lp = ls.gather(1, tok[1:].long()[:, None])[:, 0]
+            tv, ti = ls.topk(min(top_k, ls.shape[1]), dim=-1)
+            top = [None] + [{"ids": ti[i].tolist(), "logprobs": tv[i].tolist()} for i in range(n - 1)]
+        else:
+            lp, _ = self.model.forward_logprobs(tok, pos, cu, rows, tok[1:], inv_t, **kw)
+        self.stats["scored_tokens"] = self.stats.get("scored_tokens", 0) + n
+        return {"logprobs": [None] + [float(x) for x in lp.tolist()], "top": top}
+
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams] | dict | None = None,
                  return_routed_experts: bool = False) -> list:

@@ -49,8 +49,19 @@ async def generate_and_rm(state: GenerateState, sample, sampling_params: dict, e
     if getattr(args, "group_rm", False) and not evaluation:
         return result
     items = result if isinstance(result, list) else [result]
+    opd = getattr(args, "use_opd", False) and getattr(args, "opd_type", None) == "sglang" and not evaluation
     for s in items:
+        if opd and s.teacher_log_probs is None:
+            # on-policy distillation against a teacher server: its log-probs of the sampled tokens travel with the sample
+            from .on_policy_distillation import fetch_teacher_log_probs
+
+            await fetch_teacher_log_probs(args, s, post=getattr(state, "teacher_post", None),
+                                          vocab_size=getattr(getattr(state.client, "engines", [None])[0], "cfg", None).vocab_size
+                                          if getattr(state.client, "engines", None) else None)
         if s.status == Sample.Status.ABORTED or s.reward is not None:
+            continue
+        if opd and getattr(args, "rm_type", None) is None and not getattr(args, "custom_rm_path", None):
+            s.reward = 0.0  # pure distillation: the signal is the per-token penalty, there is no task reward
             continue
         s.reward = await async_rm(args, s)
     return result

@@ -296,6 +296,21 @@ def validate_args(args: argparse.Namespace) -> argparse.Namespace:
             raise ValueError("--opd-type must be given with --use-opd")
         if args.opd_type == "megatron" and args.opd_teacher_load is None:
             raise ValueError("--opd-teacher-load is required with --opd-type megatron")
+        if args.opd_type == "sglang":
+            # teacher servers score the samples during the rollout (rollout/on_policy_distillation.py)
+            from ..rollout.on_policy_distillation import parse_teacher_urls
+
+            if args.opd_teacher_load is not None:
+                raise ValueError("--opd-teacher-load belongs to --opd-type megatron; with sglang the teacher is a server")
+            if not parse_teacher_urls(getattr(args, "opd_teacher_urls", None)) and not getattr(args, "rm_url", None):
+                raise ValueError("--opd-type sglang needs --opd-teacher-urls NAME=URL ... or --rm-url")
+            if int(getattr(args, "opd_log_prob_top_k", 0) or 0) > 0 and getattr(args, "opd_top_k_strategy", "only-student") != "only-teacher":
+                raise NotImplementedError("--opd-log-prob-top-k is built for --opd-top-k-strategy only-teacher (the teacher's top-k "
+                                          "per position); strategies that need the student's top-k are not")
+        elif int(getattr(args, "opd_log_prob_top_k", 0) or 0) > 0 or getattr(args, "opd_teacher_urls", None):
+            raise ValueError("--opd-log-prob-top-k / --opd-teacher-urls need --opd-type sglang")
+    elif getattr(args, "opd_teacher_urls", None):
+        raise ValueError("--opd-teacher-urls is set but --use-opd is not")
     # ---- batching
     if args.use_dynamic_batch_size:
         assert args.max_tokens_per_gpu is not None, "--use-dynamic-batch-size needs --max-tokens-per-gpu"

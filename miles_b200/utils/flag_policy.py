@@ -81,9 +81,7 @@ REJECT = {
     "multi_lora_backend_path": "pluggable multi-LoRA backends",
     "multi_lora_http_server_path": "pluggable multi-LoRA servers",
     "custom_megatron_init_path": "Megatron initialisation hooks",
-    "opd_teacher_urls": "on-policy distillation against remote teacher servers",
-    "opd_log_prob_top_k": "top-k on-policy distillation",
-    "opd_topk_per_position": "top-k on-policy distillation",
+    "opd_topk_per_position": "per-position token lists in teacher scoring requests",
 }
 
 # dest -> why nothing needs to happen
@@ -154,9 +152,7 @@ IGNORED = {
     "dumper_source_patcher_config_inference": "the source patcher rewrites Megatron / SGLang sources, which do not exist here",
     "dumper_source_patcher_config_train": "the source patcher rewrites Megatron / SGLang sources, which do not exist here",
     "mtp_loss_scaling_factor": "multi-token prediction is rejected (--mtp-num-layers)",
-    "opd_top_k_strategy": "read by top-k distillation only, which is rejected (--opd-log-prob-top-k)",
-    "opd_reward_weight_mode": "read by top-k distillation only, which is rejected (--opd-log-prob-top-k)",
-    "opd_teacher_key": "routes between remote teachers, which are rejected (--opd-teacher-urls)",
+    "opd_reward_weight_mode": "weights the per-token terms of multi-token (student-side top-k) distillation, which is not built",
 }
 
 
@@ -174,7 +170,7 @@ def apply(args, defaults: dict) -> None:
             continue
         if dest in ("moe_aux_loss_coeff", "moe_router_bias_update_rate") and float(v) == 0.0:
             continue
-        if dest in ("num_layers_at_start_in_bf16", "num_layers_at_end_in_bf16", "opd_log_prob_top_k") and int(v) == 0:
+        if dest in ("num_layers_at_start_in_bf16", "num_layers_at_end_in_bf16") and int(v) == 0:
             continue
         if dest == "expert_tensor_parallel_size" and int(v) == 1:
             continue
