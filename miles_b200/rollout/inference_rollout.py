@@ -50,6 +50,11 @@ async def generate_and_rm(state: GenerateState, sample, sampling_params: dict, e
         return result
     items = result if isinstance(result, list) else [result]
     opd = getattr(args, "use_opd", False) and getattr(args, "opd_type", None) == "sglang" and not evaluation
+    if getattr(args, "recompute_logprobs_via_prefill", False) and not evaluation:
+        from .generate_hub.prefill_logprobs import recompute_rollout_logprobs_via_prefill
+
+        for s in items:
+            await recompute_rollout_logprobs_via_prefill(args, state, s)
     for s in items:
         if opd and s.teacher_log_probs is None:
             # on-policy distillation against a teacher server: its log-probs of the sampled tokens travel with the sample

@@ -75,7 +75,6 @@ REJECT = {
     "qkv_format": "padded [batch, seq] batches (sequences are always packed)",
     "rollout_external": "rollout engines managed outside the job (pass their URLs with --rollout-engine-urls)",
     "rollout_external_engine_addrs": "rollout engines managed outside the job (pass their URLs with --rollout-engine-urls)",
-    "recompute_logprobs_via_prefill": "log-prob recomputation through the engine's prefill",
     "lora_type": "canonical LoRA",
     "experts_shared_outer_loras": "LoRA on experts",
     "multi_lora_backend_path": "pluggable multi-LoRA backends",

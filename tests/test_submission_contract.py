@@ -62,3 +62,22 @@ def test_rollout_loop_paces_by_sample_and_by_group():
         pacer = loop.rollout_fn.state.pacer
         assert pacer.by_sample == (g == "sample") and pacer.samples_in_flight == 0
     assert outs["group"] == outs["sample"]
+
+
+def test_rollout_logprobs_recomputed_through_the_engines_prefill():
+    """--recompute-logprobs-via-prefill: the recorded rollout log-probs are the engine's one-pass scores of the finished
+    sequence; in fp32 they equal the ones recorded while decoding and the trainer's."""
+    from miles_b200.loop import RLLoop
+    from miles_b200.utils.arguments import parse_args
+
+    base = ["--model-preset", "qwen3-tiny", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2", "--rollout-max-response-len", "8",
+            "--rollout-max-prompt-len", "16", "--rm-type", "parity", "--lr", "1e-5", "--micro-batch-size", "8", "--colocate",
+            "--num-rollout", "1", "--actor-num-gpus-per-node", "1"]
+    plain = RLLoop(parse_args(base)).generate(0)[0]
+    loop = RLLoop(parse_args(base + ["--recompute-logprobs-via-prefill"]))
+    scored = loop.generate(0)[0]
+    assert loop.engine.stats.get("scored_tokens", 0) > 0
+    for a, b in zip(sorted(plain, key=lambda s: s.index), sorted(scored, key=lambda s: s.index)):
+        assert a.tokens == b.tokens and b.metadata["rollout_log_probs_source"] == "prefill_recompute"
+        assert len(b.rollout_log_probs) == b.response_length
+        assert max(abs(x - y) for x, y in zip(a.rollout_log_probs, b.rollout_log_probs)) < 1e-4
