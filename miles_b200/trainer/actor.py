@@ -117,6 +117,10 @@ class TrainActor:
         self.args = args
         self.role = role
         self.ps = ps or get_parallel_state()
+        if getattr(args, "custom_megatron_init_path", None):
+            # a user hook that runs once per trainer process after the parallel groups exist and before the model is
+            # built (the reference calls it at the end of its Megatron initialisation): fn(args)
+            load_function(args.custom_megatron_init_path)(args)
         self.cfg = model_config_from_args(args)
         self.device = self.ps.device
         self.on_gpu = self.device.type == "cuda"

@@ -353,6 +353,17 @@ def validate_args(args: argparse.Namespace) -> argparse.Namespace:
         args.save_debug_train_data = f"{args.dump_details}/train_data/{{rollout_id}}_{{rank}}.pt"
     if args.ci_test and not args.debug_rollout_only and not args.debug_train_only and not args.ci_disable_weight_update_checker:
         args.check_weight_update_equal = True
+    if getattr(args, "rollout_external", False):
+        # engines somebody else started (--rollout-external --rollout-external-engine-addrs host:port ...): the same
+        # path as --rollout-engine-urls
+        addrs = getattr(args, "rollout_external_engine_addrs", None) or []
+        assert addrs, "--rollout-external needs --rollout-external-engine-addrs host:port ..."
+        assert not getattr(args, "sglang_config", None) and not getattr(args, "launch_rollout_fleet", False), \
+            "--rollout-external engines are not launched by the job: drop --sglang-config / --launch-rollout-fleet"
+        args.rollout_engine_urls = ",".join(a if a.startswith("http") else "http://" + a for a in addrs)
+        args.colocate = False
+    elif getattr(args, "rollout_external_engine_addrs", None):
+        raise ValueError("--rollout-external-engine-addrs is set but --rollout-external is not")
     if args.update_weight_transfer_mode in ("p2p", "disk-delta"):
         assert not args.colocate, f"--update-weight-transfer-mode {args.update_weight_transfer_mode} is not compatible with --colocate"
     if args.update_weight_transfer_mode == "disk-delta":

@@ -73,13 +73,10 @@ REJECT = {
     "virtual_pipeline_model_parallel_size": "interleaved pipeline stages",
     "expert_tensor_parallel_size": "tensor parallelism inside experts",
     "qkv_format": "padded [batch, seq] batches (sequences are always packed)",
-    "rollout_external": "rollout engines managed outside the job (pass their URLs with --rollout-engine-urls)",
-    "rollout_external_engine_addrs": "rollout engines managed outside the job (pass their URLs with --rollout-engine-urls)",
     "lora_type": "canonical LoRA",
     "experts_shared_outer_loras": "LoRA on experts",
     "multi_lora_backend_path": "pluggable multi-LoRA backends",
     "multi_lora_http_server_path": "pluggable multi-LoRA servers",
-    "custom_megatron_init_path": "Megatron initialisation hooks",
     "opd_topk_per_position": "per-position token lists in teacher scoring requests",
 }
 

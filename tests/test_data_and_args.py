@@ -178,3 +178,30 @@ def test_unbuilt_features_refuse_to_start():
     parse_args(base + ["--moe-router-score-function", "softmax", "--moe-token-drop-policy", "probs", "--moe-router-dtype", "fp32",
                        "--moe-aux-loss-coeff", "0", "--attention-dropout", "0.0", "--hidden-dropout", "0.0", "--rotary-percent", "1.0",
                        "--normalization", "RMSNorm", "--position-embedding-type", "rope", "--moe-grouped-gemm", "--moe-permute-fusion"])
+
+
+def test_external_engines_and_init_hook_flags():
+    from miles_b200.utils.arguments import parse_args
+
+    base = ["--model-preset", "qwen3-tiny", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--rm-type", "parity",
+            "--actor-num-gpus-per-node", "1", "--num-rollout", "1"]
+    a = parse_args(base + ["--rollout-external", "--rollout-external-engine-addrs", "10.0.0.1:30000", "http://10.0.0.2:30000"])
+    assert a.rollout_engine_urls == "http://10.0.0.1:30000,http://10.0.0.2:30000" and not a.colocate
+    import pytest
+    with pytest.raises(ValueError):
+        parse_args(base + ["--rollout-external-engine-addrs", "10.0.0.1:30000"])
+
+
+def init_hook(args):
+    args.init_hook_saw_seed = args.seed  # (the hook is imported under another module name: leave the trace on args)
+
+
+def test_custom_init_hook_runs_before_the_model_is_built():
+    from miles_b200.trainer.actor import TrainActor
+    from miles_b200.parallel.state import ParallelState
+    from miles_b200.utils.arguments import parse_args
+
+    a = parse_args(["--model-preset", "qwen3-tiny", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--rm-type", "parity",
+                    "--actor-num-gpus-per-node", "1", "--num-rollout", "1", "--custom-megatron-init-path", "tests.test_data_and_args.init_hook"])
+    TrainActor(a, "actor", ParallelState())
+    assert a.init_hook_saw_seed == a.seed
