@@ -394,3 +394,30 @@ def test_hf_named_pieces_update_fused_parameters_in_any_order():
         assert param_or_hf_view(cfg, dst, "final_norm.weight") is dst.params["final_norm.weight"]
         with pytest.raises(KeyError):
             param_or_hf_view(cfg, dst, "model.layers.0.no_such.weight")
+
+
+def test_generate_endpoint_scores_when_no_token_is_asked_for():
+    """POST /generate with max_new_tokens = 0: the engine scores the input (what a distillation teacher and the prefill
+    log-prob recomputation ask for) and the prefix cache and request slots are untouched."""
+    import torch
+    from fastapi.testclient import TestClient
+
+    from miles_b200.engine import Engine
+    from miles_b200.engine.server import build_app
+    from miles_b200.models import ParamStore, build_model, get_config
+
+    cfg = get_config("qwen3-tiny")
+    m = build_model(cfg, ParamStore(cfg, "cpu", torch.float32, seed=11))
+    eng = Engine(m, max_running=2, page_size=8, max_seq_len=64, prefix_cache=True)
+    c = TestClient(build_app(eng))
+    ids = list(range(3, 20))
+    r = c.post("/generate", json={"input_ids": ids, "sampling_params": {"max_new_tokens": 0, "temperature": 0}, "return_logprob": True,
+                                  "logprob_start_len": 9, "top_logprobs_num": 2}).json()
+    meta = r["meta_info"]
+    assert r["output_ids"] == [] and meta["completion_tokens"] == 0 and meta["prompt_tokens"] == 17
+    assert [e[1] for e in meta["input_token_logprobs"]] == ids[9:] and all(e[0] < 0 for e in meta["input_token_logprobs"])
+    assert len(meta["input_top_logprobs"]) == 8 and len(meta["input_top_logprobs"][0]) == 2
+    tok, pos, cu = torch.tensor(ids), torch.arange(17), torch.tensor([0, 17])
+    lp, _ = m.forward_logprobs(tok, pos, cu, torch.arange(8, 16), tok[9:], 1.0)
+    assert torch.allclose(torch.tensor([e[0] for e in meta["input_token_logprobs"]]), lp, atol=1e-5)
+    assert not eng.running and eng.prefix.num_pages == 0 and eng.pool.num_free == eng.num_pages - 1
