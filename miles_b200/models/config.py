@@ -203,6 +203,16 @@ PRESETS: dict[str, ModelConfig] = {
                          rope_theta=1e6, rms_eps=1e-5, hf_architecture="MistralForCausalLM"),
     "llama-3.1-8B": _dense("llama-3.1-8B", 32, 4096, 32, 8, 14336, False, vocab=128256, qk_norm=False,
                            rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+    # names of the reference's per-model argument files (scripts/models/*.py) for shapes already covered above
+    "qwen3-4B-Instruct-2507": _dense("qwen3-4B-Instruct-2507", 36, 2560, 32, 8, 9728, True, rope_theta=5e6),
+    "qwen3-30B-A3B-5layer": _moe("qwen3-30B-A3B-5layer", 5, 2048, 32, 4, 128, 8, 768),
+    "llama3.1-8B-Instruct": _dense("llama3.1-8B-Instruct", 32, 4096, 32, 8, 14336, False, vocab=128256, qk_norm=False,
+                                   rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+    "llama3.2-3B-Instruct": _dense("llama3.2-3B-Instruct", 28, 3072, 24, 8, 8192, True, vocab=128256, qk_norm=False,
+                                   rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+    # MiMo-7B-RL: a Qwen2-style dense model (QKV bias, no QK norm); its multi-token-prediction layer is not trained here
+    "mimo-7B-rl": _dense("mimo-7B-rl", 36, 4096, 32, 8, 11008, False, vocab=151680, qk_norm=False, qkv_bias=True,
+                         rope_theta=640000.0, rms_eps=1e-5, hf_architecture="Qwen2ForCausalLM"),
 }
 
 
