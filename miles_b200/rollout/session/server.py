@@ -1,6 +1,8 @@
 """OpenAI-compatible session proxy: ``POST /sessions/{id}/v1/chat/completions`` keeps the exact token sequence of
 an agent conversation across turns (token in, token out) and ``GET /sessions/{id}/sample`` returns the assembled
-training sample (tokens, loss mask, rollout log-probs).
+training sample (tokens, loss mask, rollout log-probs). ``POST /sessions`` creates a session, ``GET /sessions/{id}`` describes
+it, ``GET /sessions/{id}/samples?max_seq_len=`` collects its samples, ``DELETE /sessions/{id}`` closes it, ``GET /health``;
+``"stream": true`` answers as server-sent events. Errors map to HTTP statuses through ``errors.py``.
 
 An agent framework talks to this endpoint as if it were a chat model. Each request carries the whole conversation
 so far; the server renders only the messages it has not seen yet (through the tokenizer's chat template, as a
@@ -16,6 +18,7 @@ import time
 import uuid
 from typing import Callable, Optional
 
+from .errors import MessageValidationError
 from .trajectory import LinearTrajectory
 
 
@@ -142,13 +145,13 @@ class SessionStore:
             return self._chat_tree(sid, messages, sampling_params)
         traj = self.get(sid)
         if len(messages) < traj.num_messages:
-            raise ValueError("the request holds fewer messages than the session: a session only moves forward")
+            raise MessageValidationError("the request holds fewer messages than the session: a session only moves forward")
         if getattr(self, "tito", None) is not None:
             return self._chat_tito(traj, messages, sampling_params)
         full = self._render(messages, add_generation_prompt=True)
         seen = self._rendered[sid]
         if not full.startswith(seen):
-            raise ValueError("the conversation does not extend the session's history (token-in-token-out would break)")
+            raise MessageValidationError("the conversation does not extend the session's history (token-in-token-out would break)")
         delta = full[len(seen):]
         new_ids = self._encode(delta)
         if new_ids:
@@ -166,32 +169,107 @@ class SessionStore:
         return {"text": text, "ids": ids, "finish_reason": out.get("finish_reason", "stop")}
 
 
-def build_session_app(store: SessionStore, model_name: str = "policy"):
+def build_session_app(store: SessionStore, model_name: str = "policy", created_only: bool = False):
+    """``created_only``: chat requests are accepted only for sessions made with ``POST /sessions`` (default: a session
+    comes into being with its first request, which agent frameworks that pick their own ids rely on)."""
     from fastapi import FastAPI, HTTPException, Request
 
     app = FastAPI(title="miles_b200 session server")
 
+    from .errors import MessageValidationError, SessionError, SessionNotFoundError, UpstreamResponseError
+
     async def _chat(sid: str, req: Request):
+        import json as _json
+
+        from fastapi.responses import StreamingResponse
+
         body = await req.json()
+        messages = body.get("messages")
+        if not isinstance(messages, list) or not all(isinstance(m, dict) and "role" in m for m in messages):
+            raise HTTPException(MessageValidationError.status_code, "messages must be a list of {role, content} objects")
+        if created_only and sid not in store.sessions and sid not in store._trees:
+            raise HTTPException(SessionNotFoundError.status_code, f"unknown session {sid}: create it with POST /sessions")
         sp = {"temperature": body.get("temperature", 1.0), "top_p": body.get("top_p", 1.0),
               "max_new_tokens": body.get("max_tokens") or body.get("max_completion_tokens") or 1024}
         if body.get("stop"):
             sp["stop"] = body["stop"]
         try:
-            out = store.chat(sid, body.get("messages", []), sp)
+            out = store.chat(sid, messages, sp)
+        except SessionError as e:
+            raise HTTPException(e.status_code, str(e))
         except ValueError as e:
             raise HTTPException(409, str(e))
+        except KeyError as e:
+            raise HTTPException(UpstreamResponseError.status_code, f"the engine's answer lacks {e}")
         except RuntimeError as e:
             raise HTTPException(503, str(e))
         fr = out["finish_reason"]
         fr = fr.get("type") if isinstance(fr, dict) else fr
-        return {"id": "chatcmpl-" + uuid.uuid4().hex[:24], "object": "chat.completion", "created": int(time.time()),
-                "model": body.get("model", model_name),
-                "choices": [{"index": 0, "message": {"role": "assistant", "content": out["text"]},
-                             "finish_reason": "length" if fr == "length" else "stop"}],
+        fr = "length" if fr == "length" else "stop"
+        cid, now, model = "chatcmpl-" + uuid.uuid4().hex[:24], int(time.time()), body.get("model", model_name)
+        if body.get("stream"):
+            # server-sent events for clients that only speak the streaming protocol: the turn is generated whole (the
+            # trajectory needs its exact tokens) and sent as one content chunk, a final chunk and [DONE]
+            def events():
+                first = {"id": cid, "object": "chat.completion.chunk", "created": now, "model": model,
+                         "choices": [{"index": 0, "delta": {"role": "assistant", "content": out["text"]}, "finish_reason": None}]}
+                last = {"id": cid, "object": "chat.completion.chunk", "created": now, "model": model,
+                        "choices": [{"index": 0, "delta": {}, "finish_reason": fr}], "usage": {"completion_tokens": len(out["ids"])}}
+                yield "data: " + _json.dumps(first) + "\n\n"
+                yield "data: " + _json.dumps(last) + "\n\n"
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(events(), media_type="text/event-stream")
+        return {"id": cid, "object": "chat.completion", "created": now, "model": model,
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": out["text"]}, "finish_reason": fr}],
                 "usage": {"completion_tokens": len(out["ids"])}}
 
     app.post("/sessions/{sid}/v1/chat/completions")(_chat)
+
+    @app.get("/health")
+    async def health():
+        return {"status": "ok", "sessions": len(store.sessions) + len(store._trees), "mode": "tree" if store.tree else "linear"}
+
+    @app.post("/sessions")
+    async def create_session():
+        sid = uuid.uuid4().hex
+        if store.tree:
+            store._lineage.setdefault(sid, [])
+        else:
+            store.get(sid)
+        return {"session_id": sid}
+
+    def _meta(sid: str) -> dict:
+        if store.tree:
+            tree = store._trees.get(sid)
+            if tree is None and sid not in store._lineage:
+                raise HTTPException(SessionNotFoundError.status_code, f"unknown session {sid}")
+            leaves = tree.to_sample_dicts() if tree is not None else []
+            return {"session_id": sid, "mode": "tree", "num_leaves": len(leaves), "num_requests": len(store._lineage.get(sid, [])),
+                    "num_tokens": max((len(l["tokens"]) for l in leaves), default=0)}
+        t = store.sessions.get(sid)
+        if t is None:
+            raise HTTPException(SessionNotFoundError.status_code, f"unknown session {sid}")
+        return {"session_id": sid, "mode": "linear", "num_messages": t.num_messages, "num_tokens": len(t.tokens),
+                "num_turns": len(t.turns), "prompt_tokens": t.prompt_length, "finish_reason": t.finish_reason,
+                "weight_versions": list(t.weight_versions)}
+
+    @app.get("/sessions/{sid}")
+    async def get_session(sid: str):
+        return _meta(sid)
+
+    @app.get("/sessions/{sid}/samples")
+    async def collect_samples(sid: str, max_seq_len: Optional[int] = None):
+        """The session's training samples; a sample longer than ``max_seq_len`` tokens is cut there and marked truncated."""
+        _meta(sid)
+        out = []
+        for smp in store.samples(sid):
+            if max_seq_len is not None and len(smp["tokens"]) > max_seq_len:
+                cut = len(smp["tokens"]) - max_seq_len
+                keep = max(smp["response_length"] - cut, 0)
+                smp = dict(smp, tokens=smp["tokens"][:max_seq_len], response_length=keep, loss_mask=smp["loss_mask"][:keep],
+                           rollout_log_probs=smp["rollout_log_probs"][:keep], status="truncated")
+            out.append(smp)
+        return {"session_id": sid, "samples": out}
 
     @app.get("/sessions/{sid}/sample")
     async def sample(sid: str):

@@ -56,7 +56,7 @@ def test_rewritten_history_is_rejected():
     c = TestClient(build_session_app(store))
     c.post("/sessions/s/v1/chat/completions", json={"messages": [{"role": "user", "content": "a"}]})
     bad = [{"role": "user", "content": "changed"}, {"role": "assistant", "content": "r1"}, {"role": "user", "content": "b"}]
-    assert c.post("/sessions/s/v1/chat/completions", json={"messages": bad}).status_code == 409
+    assert c.post("/sessions/s/v1/chat/completions", json={"messages": bad}).status_code == 400  # messages are not append-only
 
 
 def test_tree_sessions_branch_pick_and_postprocess():
@@ -100,3 +100,30 @@ def test_tree_sessions_branch_pick_and_postprocess():
     tc = lambda i, a: {"role": "assistant", "content": None, "tool_calls": [{"id": i, "function": {"name": "f", "arguments": a}}]}
     assert not match_strict(tc("1", '{"a": 1}'), tc("2", '{"a":1}')) and match_loose_tool_call(tc("1", '{"a": 1}'), tc("2", '{"a":1}'))
     assert resolve_matcher("role_content_only")(tc("1", "{}"), {"role": "assistant", "content": None})
+
+
+def test_session_lifecycle_endpoints_streaming_and_length_cap():
+    import json
+
+    from fastapi.testclient import TestClient
+
+    store, calls = _store()
+    c = TestClient(build_session_app(store))
+    assert c.get("/health").json()["status"] == "ok"
+    sid = c.post("/sessions").json()["session_id"]
+    assert c.get(f"/sessions/{sid}").json()["num_tokens"] == 0 and c.get("/sessions/nope").status_code == 404
+    m1 = [{"role": "user", "content": "hello"}]
+    r = c.post(f"/sessions/{sid}/v1/chat/completions", json={"messages": m1, "stream": True})
+    assert r.headers["content-type"].startswith("text/event-stream")
+    events = [l[len("data: "):] for l in r.text.splitlines() if l.startswith("data: ")]
+    assert events[-1] == "[DONE]" and json.loads(events[0])["choices"][0]["delta"]["content"] == "r1"
+    assert json.loads(events[1])["choices"][0]["finish_reason"] == "stop"
+    meta = c.get(f"/sessions/{sid}").json()
+    assert meta["num_turns"] == 2 and meta["weight_versions"] == [3] and meta["num_tokens"] == len(store.sessions[sid].tokens)
+    full = c.get(f"/sessions/{sid}/samples").json()["samples"][0]
+    assert full["status"] == "completed" and full["response_length"] == 2
+    cut = c.get(f"/sessions/{sid}/samples?max_seq_len={len(full['tokens']) - 1}").json()["samples"][0]
+    assert cut["status"] == "truncated" and cut["response_length"] == 1 and len(cut["loss_mask"]) == 1 and len(cut["tokens"]) == len(full["tokens"]) - 1
+    assert c.post(f"/sessions/{sid}/v1/chat/completions", json={"messages": "not a list"}).status_code == 400
+    strict = TestClient(build_session_app(store, created_only=True))
+    assert strict.post("/sessions/unknown/v1/chat/completions", json={"messages": m1}).status_code == 404
