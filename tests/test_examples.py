@@ -8,6 +8,7 @@ from miles_b200.utils.arguments import build_parser
 LAUNCHER_FLAGS = {"--nnodes", "--nproc-per-node", "--master-addr", "--master-port"}
 SERVER_FLAGS = {"--port", "--device", "--max-running-requests", "--page-size", "--context-length", "--host", "--quantization",
                 "--mem-fraction-static"}
+TOOL_FLAGS = {"--format", "--output"}  # the converter tools of examples/convert_checkpoints.sh (miles_b200/tools)
 
 
 def test_example_flags_are_known():
@@ -19,5 +20,5 @@ def test_example_flags_are_known():
     assert len(files) >= 8
     for f in files:
         flags = set(re.findall(r"(?<![\w-])(--[a-z][a-z0-9-]+)", open(f).read()))
-        unknown = sorted(x for x in flags - known - LAUNCHER_FLAGS - SERVER_FLAGS if not x.startswith("--sglang-"))
+        unknown = sorted(x for x in flags - known - LAUNCHER_FLAGS - SERVER_FLAGS - TOOL_FLAGS if not x.startswith("--sglang-"))
         assert not unknown, (os.path.basename(f), unknown)
