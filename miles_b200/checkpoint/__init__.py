@@ -71,7 +71,25 @@ def _snapshot_state(actor, iteration: int) -> dict:
                                   if isinstance(v, dict) else v) for k, v in sd.items()}
     if getattr(actor, "_value_head", None) is not None:
         state["value_head"] = actor._value_head.detach().cpu()
+    state["audit"] = _audit_state(actor)
     return state
+
+
+def _audit_state(actor) -> dict:
+    """Witness table / allocator and the event log's sequence number: a resumed run keeps counting where it stopped."""
+    out = {}
+    if getattr(actor, "witness", None) is not None:
+        out["witness"] = actor.witness.state_dict()
+    if getattr(actor, "events", None) is not None:
+        out["events"] = actor.events.state_dict()
+    return out
+
+
+def _load_audit_state(actor, state: dict) -> None:
+    if getattr(actor, "witness", None) is not None and state.get("witness") is not None:
+        actor.witness.load_state_dict(state["witness"])
+    if getattr(actor, "events", None) is not None and state.get("events") is not None:
+        actor.events.load_state_dict(state["events"])
 
 
 def _write_state(actor, base: str, d: str, iteration: int, state: dict, checksums: Optional[dict]) -> None:
@@ -133,6 +151,7 @@ def _save_dist(actor, base: str, d: str, iteration: int) -> str:
     side = {"rng": {"cpu": torch.get_rng_state(), "cuda": torch.cuda.get_rng_state() if actor.on_gpu else None}}
     if getattr(actor, "_value_head", None) is not None:
         side["value_head"] = actor._value_head.detach().cpu()
+    side["audit"] = _audit_state(actor)
     torch.save(side, os.path.join(d, f"side_rank_{actor.ps.rank:05d}.pt"))
     fut = dist_ckpt.save(actor, d, iteration, async_save=bool(getattr(actor.args, "async_save", False)))
     if fut is not None:
@@ -226,6 +245,7 @@ def load_checkpoint(actor, path: str, step: Optional[int] = None) -> Optional[in
             torch.set_rng_state(state["rng"]["cpu"])
         if getattr(actor, "_value_head", None) is not None and "value_head" in state:
             actor._value_head.data.copy_(state["value_head"])
+        _load_audit_state(actor, state.get("audit") or {})
         from ..utils.ci_checks import check_model_hashes
 
         if it is not None:
@@ -259,6 +279,7 @@ def _load_dist(actor, d: str, it: Optional[int]) -> Optional[int]:
             torch.set_rng_state(side["rng"]["cpu"])
         if getattr(actor, "_value_head", None) is not None and "value_head" in side:
             actor._value_head.data.copy_(side["value_head"])
+        _load_audit_state(actor, side.get("audit") or {})
     if it is not None:
         check_model_hashes(actor.args, actor.store, actor.ps, it)
     if getattr(actor.args, "finetune", False):

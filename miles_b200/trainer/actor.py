@@ -676,6 +676,17 @@ class TrainActor:
             self._advantages(mbs)
         metrics_acc: dict = {}
         grad_norm = torch.zeros((), device=self.device)
+        wid_of: dict = {}
+        if self.witness is not None:
+            # a slot of the witness ring for every sample this rank trains in this rollout (the same slots again when a
+            # failed attempt of the rollout is retried)
+            from ..utils.audit import ev_witness_allocate
+
+            sids = sorted({int(i) for mb in mbs for i in mb.sample_indices})
+            wids, stale = self.witness.allocate(rollout_id, sids)
+            wid_of = dict(zip(sids, wids))
+            if self.events is not None:
+                self.events.log(ev_witness_allocate(rollout_id, sids, wids, stale))
         with T.context("actor_train"):
             steps = a.num_steps_per_rollout or 1
             per_step = max(1, math.ceil(len(mbs) / steps))
@@ -714,9 +725,14 @@ class TrainActor:
                             self.store.zero_grads()
                             if self.witness is not None:
                                 self.witness.discard()
+                            if self.events is not None:
+                                from ..utils.audit import ev_train_step
+
+                                ids = [i for mb in chunk for i in mb.sample_indices]
+                                self.events.log(ev_train_step(rollout_id, self.global_step, len(ids), "discarded", ids))
                             continue
                 if self.witness is not None:
-                    self.witness.touch(i for mb in chunk for i in mb.sample_indices)
+                    self.witness.touch(wid_of[i] for mb in chunk for i in mb.sample_indices)
                 with T.cuda_span("train_optimizer"):
                     if self.lora is not None:
                         self.lora.grads_from_weight_grads()
@@ -731,14 +747,16 @@ class TrainActor:
                 if self.witness is not None:
                     self.witness.commit()
                 if self.events is not None:
+                    from ..utils.audit import ev_train_step, ev_weight_checksum, ev_witness_snapshot
+
                     ids = [i for mb in chunk for i in mb.sample_indices]
-                    self.events.log("train_step", rollout_id=rollout_id, step=self.global_step, samples=len(ids))
+                    self.events.log(ev_train_step(rollout_id, self.global_step, len(ids), "normal", ids))
                     if self.witness is not None:
-                        self.events.log("witness", rollout_id=rollout_id, counts={str(i): 1 for i in ids})
+                        # what the table holds for this step's samples now (read back, not assumed)
+                        self.events.log(ev_witness_snapshot(rollout_id, self.global_step, self.witness.counts(wid_of[i] for i in ids)))
                     if getattr(a, "enable_event_analyzer", False):
                         ck = self.store.checksum()
-                        self.events.log("weight_checksum", step=self.global_step, version=self.store.version,
-                                        checksum=f"{ck.get('dense', 0.0):.6e}")
+                        self.events.log(ev_weight_checksum(self.global_step, self.store.version, f"{ck.get('dense', 0.0):.6e}"))
         if self.on_gpu:
             torch.cuda.synchronize()
         elapsed = time.perf_counter() - t_start
