@@ -337,7 +337,10 @@ class RLLoop:
         return bool(ok.item() > 0)
 
     def _build_data_source(self):
-        a = self.args
+        return self._build_data_source_for(self.args)
+
+    def _build_data_source_for(self, a):
+        """The prompt stream described by ``a`` (the run's arguments, or a copy with another dataset: multi-LoRA adapters)."""
         path = getattr(a, "data_source_path", None) or "miles_b200.rollout.data_source.RolloutDataSourceWithBuffer"
         path = path.replace("miles.rollout.data_source", "miles_b200.rollout.data_source")
         if not getattr(a, "prompt_data", None) and "Synthetic" not in path and getattr(a, "rollout_global_dataset", True):

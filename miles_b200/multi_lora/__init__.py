@@ -7,3 +7,5 @@ sizes), train_multi_lora_async.py:35-101 (the service loop).
 """
 from .registry import AdapterSpec, AdapterState, AdapterRegistry  # noqa: F401
 from .controller import MultiLoRAController, build_control_app  # noqa: F401
+from .data_source import AdapterDataSources  # noqa: F401
+from .service import run_service, train_adapter_step  # noqa: F401

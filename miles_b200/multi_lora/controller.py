@@ -80,11 +80,14 @@ class MultiLoRAController:
         self.actor.lora = m
         return m
 
-    def after_train(self, name: str, rollout_id: int, save_interval: Optional[int] = None) -> None:
-        self.registry.bump_steps(name)
+    def after_train(self, name: str, rollout_id: int, save_interval: Optional[int] = None) -> bool:
+        """Counts the step and writes the periodic adapter checkpoint. Returns True when the adapter has reached its
+        ``num_step`` (the caller deregisters it)."""
+        done = self.registry.bump_steps(name)
         a = self.registry.get(name)
         if self.save_dir and save_interval and a.steps % save_interval == 0:
             self.managers[name].save(os.path.join(self.save_dir, name, f"step_{a.steps}"))
+        return done
 
 
 def build_control_app(registry: AdapterRegistry, on_change: Optional[Callable[[], None]] = None):
@@ -103,7 +106,7 @@ def build_control_app(registry: AdapterRegistry, on_change: Optional[Callable[[]
         body = await req.json()
         try:
             spec = registry.register(AdapterSpec(**{k: v for k, v in body.items() if k in AdapterSpec.__dataclass_fields__
-                                                    and k not in ("state", "slot", "steps")}))
+                                                    and k not in ("state", "slot", "steps", "registration_id")}))
         except (ValueError, RuntimeError, TypeError) as e:
             raise HTTPException(409, str(e))
         if on_change:

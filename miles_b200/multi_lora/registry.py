@@ -27,8 +27,14 @@ class AdapterSpec:
     lr: float = 1e-4
     target_modules: object = "all-linear"
     rollout_batch_size: Optional[int] = None   # prompts per step for this adapter (None: the service default)
-    prompt_data: Optional[str] = None          # its own dataset, if any
+    prompt_data: Optional[str] = None          # its own dataset, if any (None: the service's --prompt-data)
+    input_key: Optional[str] = None            # dataset columns of its own dataset (None: the service's)
+    label_key: Optional[str] = None
+    rm_type: Optional[str] = None              # its reward function (None: the service's --rm-type)
+    num_step: Optional[int] = None             # retire (save + remove) after this many optimizer steps
+    num_epoch: Optional[float] = None          # ... or after this many passes over its dataset (resolved to num_step)
     load: Optional[str] = None                 # PEFT directory to start from
+    registration_id: str = ""                  # unique per registration: a re-registered name is a new tenant
     state: AdapterState = AdapterState.REGISTERED
     steps: int = 0
     slot: int = -1
@@ -65,6 +71,9 @@ class AdapterRegistry:
             used = {a.slot for a in live}
             spec.slot = next(i for i in range(self.max_slots) if i not in used)
             spec.state = AdapterState.REGISTERED
+            import uuid
+
+            spec.registration_id = uuid.uuid4().hex[:12]
             self._adapters[spec.name] = spec
             self.version += 1
             return spec
@@ -100,6 +109,19 @@ class AdapterRegistry:
         with self._lock:
             return self._adapters[name]
 
-    def bump_steps(self, name: str) -> None:
+    def bump_steps(self, name: str) -> bool:
+        """One more optimizer step trained. Returns True when the adapter has now reached its ``num_step`` (the caller
+        deregisters it: it is saved and removed at the next reconciliation)."""
         with self._lock:
-            self._adapters[name].steps += 1
+            a = self._adapters[name]
+            a.steps += 1
+            return a.num_step is not None and a.steps >= a.num_step
+
+    def resolve_num_step(self, name: str, dataset_len: int, default_batch: int) -> Optional[int]:
+        """``num_epoch`` -> ``num_step`` once the (filtered) dataset length is known."""
+        with self._lock:
+            a = self._adapters[name]
+            if a.num_step is None and a.num_epoch is not None and dataset_len > 0:
+                per = max(1, a.rollout_batch_size or default_batch)
+                a.num_step = max(1, int(-(-a.num_epoch * dataset_len // per)))
+            return a.num_step

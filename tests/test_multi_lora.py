@@ -72,3 +72,56 @@ def test_http_control_api():
     assert [a["name"] for a in c.get("/adapters").json()["adapters"]] == ["m"]
     assert c.delete("/adapters/m").json()["state"] == "removed"
     assert c.delete("/adapters/nope").status_code == 404
+
+
+def test_service_trains_each_adapter_on_its_own_data_batch_and_lifetime(tmp_path):
+    """Two adapters on one base model: different prompt files, batch sizes and reward types; one retires after its
+    num_step (derived from num_epoch for the other), both are saved, and the base weights are back afterwards."""
+    import json
+
+    from miles_b200.loop import RLLoop
+    from miles_b200.multi_lora import AdapterDataSources, run_service, train_adapter_step
+    from miles_b200.utils.arguments import parse_args
+
+    def prompts(path, first_token, n):
+        with open(path, "w") as f:
+            for i in range(n):
+                f.write(json.dumps({"input": [first_token, 10 + i, 11 + i, 12 + i], "label": "1"}) + "\n")
+
+    prompts(tmp_path / "a.jsonl", 100, 8)
+    prompts(tmp_path / "b.jsonl", 200, 4)
+    args = parse_args(["--model-preset", "qwen3-tiny", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2", "--rollout-max-response-len", "6",
+                       "--rollout-max-prompt-len", "16", "--rm-type", "parity", "--lr", "1e-4", "--micro-batch-size", "8", "--colocate",
+                       "--num-rollout", "10", "--actor-num-gpus-per-node", "1", "--save", str(tmp_path / "out"), "--input-key", "input",
+                       "--label-key", "label"])
+    loop = RLLoop(args)
+    base = {n: p.clone() for n, p in loop.actor.store.params.items()}
+    reg = AdapterRegistry(max_slots=4, samples_per_prompt=2)
+    ctl = MultiLoRAController(loop.actor, reg, save_dir=str(tmp_path / "out"))
+    reg.register(AdapterSpec("a", rank=4, prompt_data=str(tmp_path / "a.jsonl"), rollout_batch_size=4, rm_type="random", num_step=3))
+    reg.register(AdapterSpec("b", rank=2, prompt_data=str(tmp_path / "b.jsonl"), rollout_batch_size=2, num_epoch=1.0))
+    sources = AdapterDataSources(args, loop.tokenizer, lambda a, tok: loop._build_data_source_for(a), reg, default_batch=args.rollout_batch_size)
+    assert ctl.reconcile() == ["a", "b"]
+    sources.reconcile(reg.snapshot()[1])
+    assert reg.get("b").num_step == 2 and reg.get("a").registration_id != reg.get("b").registration_id   # 4 prompts / 2 per step
+    seen = {"a": [], "b": []}
+    orig_train = loop.train
+
+    def spy(rid, samples):
+        seen[samples[0].metadata["adapter"]].append(samples)
+        return orig_train(rid, samples)
+
+    loop.train = spy
+    logs = []
+    n = run_service(loop, ctl, sources, max_rollouts=10, can_register=False, log=logs.append)
+    assert n == 5 and [len(v) for v in seen.values()] == [3, 2]              # a: 3 steps, b: 2 steps, then nobody is left
+    assert all(len(s) == 8 for s in seen["a"]) and all(len(s) == 4 for s in seen["b"])   # 4 x 2 and 2 x 2 samples per step
+    assert all(s.tokens[0] == 100 and s.metadata["rm_type"] == "random" for step in seen["a"] for s in step)
+    assert all(s.tokens[0] == 200 and "rm_type" not in s.metadata for step in seen["b"] for s in step)
+    assert reg.snapshot()[1] == [] and not ctl.managers
+    assert (tmp_path / "out" / "a" / "final_step_3" / "adapter_model.safetensors").exists()
+    assert (tmp_path / "out" / "b" / "final_step_2" / "adapter_model.safetensors").exists()
+    assert any("(retired)" in l for l in logs)
+    for name, p in loop.actor.store.params.items():
+        assert torch.allclose(p, base[name], atol=1e-6), name                # the base model never moved
+    assert loop.actor.args.global_batch_size == args.global_batch_size and loop.rollout_fn.args.rollout_batch_size == 4

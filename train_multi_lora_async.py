@@ -7,8 +7,10 @@
 ``--multi-lora-adapter NAME PATH`` (repeatable) registers adapters at start-up (PATH: a PEFT directory or "none");
 ``--multi-lora-disable-service-mode`` runs without the HTTP API and stops when no adapter is left.
 
-Loop: snapshot of the registry -> reconcile (create / retire adapter tensors) -> for every active adapter:
-activate (merged weights become live for trainer and engine) -> generate -> train -> periodic adapter save.
+Loop (``miles_b200/multi_lora/service.py``): snapshot of the registry -> reconcile (create / retire adapter tensors and
+prompt streams) -> for every active adapter: activate (merged weights become live for trainer and engine) -> generate its
+batch from its own prompt stream (``prompt_data``, ``rollout_batch_size``, ``rm_type`` of the adapter's registration) ->
+train -> periodic adapter save; an adapter that reaches its ``num_step`` / ``num_epoch`` is saved and removed.
 Reference: train_multi_lora_async.py:35-101.
 """
 from __future__ import annotations
@@ -49,31 +51,12 @@ def main(argv=None) -> None:
     port = getattr(args, "multi_lora_api_port", None) if service else None
     if port and loop.ps.rank == 0:
         _serve(build_control_app(registry), int(port))
-    rollout_id = loop.start_rollout_id
-    idle_sleep = float(getattr(args, "multi_lora_idle_poll_s", 1.0) or 1.0)
-    max_rollouts = args.num_rollout
-    while max_rollouts is None or rollout_id < max_rollouts:
-        active = ctl.reconcile()
-        if not active:
-            time.sleep(idle_sleep)
-            if max_rollouts is not None and port is None:
-                break  # nothing registered and nobody can register: do not spin forever
-            continue
-        for name in active:
-            ctl.activate(name)
-            loop.update_weights()
-            samples, _ = loop.generate(rollout_id)
-            for s in samples:
-                s.metadata = dict(s.metadata or {}, adapter=name)
-            metrics = loop.train(rollout_id, samples)
-            ctl.after_train(name, rollout_id, getattr(args, "save_interval", None))
-            if loop.ps.rank == 0:
-                print(f"[multi-lora] rollout {rollout_id} adapter {name}: "
-                      f"loss {metrics.get('train/pg_loss', float('nan')):.4f} grad_norm {metrics.get('train/grad_norm', 0):.3f}", flush=True)
-            rollout_id += 1
-            if max_rollouts is not None and rollout_id >= max_rollouts:
-                break
-    ctl.reconcile()
+    from miles_b200.multi_lora import AdapterDataSources, run_service
+
+    sources = AdapterDataSources(args, loop.tokenizer, lambda a, tok: loop._build_data_source_for(a), registry,
+                                 default_batch=args.rollout_batch_size)
+    run_service(loop, ctl, sources, max_rollouts=args.num_rollout, idle_sleep=float(getattr(args, "multi_lora_idle_poll_s", 1.0) or 1.0),
+                can_register=port is not None)
 
 
 if __name__ == "__main__":
