@@ -22,7 +22,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Callable, Iterator, Optional
+from typing import Iterator, Optional
 
 import torch
 import torch.distributed as dist

@@ -3,7 +3,6 @@ sink) and periodic GPU samples (utilisation, memory, power, SM clock through NVM
 from __future__ import annotations
 
 import threading
-import time
 from typing import Callable, Optional
 
 from .store import EventStore

@@ -11,7 +11,6 @@ server needs no scheduler or detokenizer subprocesses.
 """
 import asyncio
 import time
-from typing import Any, Optional
 
 from .client import EngineClient
 from .core import Engine

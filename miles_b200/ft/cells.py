@@ -14,8 +14,8 @@ Actors are plain Python objects behind a factory, so the logic is testable with 
 from __future__ import annotations
 
 import enum
-from dataclasses import dataclass, field
-from typing import Any, Callable, Optional, Sequence
+from dataclasses import dataclass
+from typing import Any, Callable, Optional
 
 
 class CellState(enum.Enum):

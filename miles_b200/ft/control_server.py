@@ -8,7 +8,7 @@ back-off.  Reference: miles/utils/ft_utils/control_server/server.py:1-156, mini_
 flags ``--control-server-port``, ``--mini-ft-controller-*``.
 """
 import time
-from typing import Callable, Optional
+from typing import Callable
 
 from .cells import CellState, TrainGroup
 

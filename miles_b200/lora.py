@@ -17,7 +17,6 @@ from __future__ import annotations
 import json
 import math
 import os
-import re
 from dataclasses import dataclass
 from typing import Optional, Sequence
 

@@ -10,7 +10,7 @@ conversion is pure slicing without reshuffles).
 from __future__ import annotations
 
 import re
-from typing import Iterator, Optional
+from typing import Iterator
 
 import torch
 

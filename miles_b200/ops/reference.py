@@ -5,7 +5,6 @@ configuration.  Shapes and conventions are identical to the CUDA kernels in ``mi
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

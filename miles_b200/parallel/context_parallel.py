@@ -22,7 +22,7 @@ data.py:198-235 (all-gather mode).
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Sequence
 
 import torch
 import torch.distributed as dist

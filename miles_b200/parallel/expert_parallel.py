@@ -14,7 +14,6 @@ Reference: Megatron's alltoall token dispatcher (scripts/models/qwen3-30B-A3B.py
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -7,7 +7,6 @@ TMA multicast, no library collectives).  Sub-buffers are carved out at identical
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -15,7 +15,7 @@ import json
 import os
 import random
 from abc import ABC, abstractmethod
-from typing import Any, Optional
+from typing import Optional
 
 import torch
 

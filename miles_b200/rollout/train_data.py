@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import math
 from collections import defaultdict
-from typing import Optional, Sequence
+from typing import Sequence
 
 from ..rl.rewards import normalize_group_rewards
 from ..utils.misc import load_function

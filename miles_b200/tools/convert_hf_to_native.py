@@ -9,7 +9,6 @@ tools/convert_hf_to_torch_dist.py.
 import argparse
 import json
 import os
-import sys
 
 
 import torch

@@ -7,7 +7,6 @@ Counterpart of the reference's tools/convert_torch_dist_to_hf.py.
 import argparse
 import json
 import os
-import sys
 
 
 import torch

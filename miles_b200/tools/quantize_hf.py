@@ -11,14 +11,12 @@ import argparse
 import json
 import os
 import shutil
-import sys
 
 
 import torch
 from safetensors import safe_open
 from safetensors.torch import save_file
 
-from miles_b200.ops import reference as R
 from miles_b200.weight_sync.quantize import quantize_tensor
 
 

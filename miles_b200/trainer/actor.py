@@ -12,7 +12,7 @@ from __future__ import annotations
 import math
 import os
 import time
-from typing import Any, Optional
+from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -12,7 +12,7 @@ and total length n, logits at packed positions ``[p-1, n-1)`` predict tokens ``[
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 

@@ -13,7 +13,7 @@ import socket
 import subprocess
 import sys
 from dataclasses import asdict, dataclass, field
-from typing import Any, Optional
+from typing import Optional
 
 MARK = "MILES_B200_ENV_REPORT "
 ENV_PREFIXES = ("NCCL_", "CUDA_", "TORCH_", "MILES_", "OMP_", "MASTER_", "WORLD_SIZE", "RANK", "LOCAL_RANK")

@@ -5,7 +5,7 @@ import importlib
 import importlib.util
 import os
 import sys
-from typing import Any, Callable, Optional
+from typing import Any, Optional
 
 
 def load_function(path: str) -> Any:

@@ -13,7 +13,6 @@ import faulthandler
 import os
 import sys
 import threading
-from typing import Optional
 
 import torch
 

@@ -14,7 +14,6 @@ import hashlib
 import json
 import os
 import zlib
-from typing import Optional
 
 import torch
 

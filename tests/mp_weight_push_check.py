@@ -56,8 +56,6 @@ def check(ps, dev):
                     assert torch.allclose(torch.as_tensor(op.decode_scale).float().cpu(), torch.as_tensor(ref.decode_scale).float().cpu())
         if quant != "none":
             assert len(tgt.mx) >= 4, len(tgt.mx)
-        for p, f in zip(src.params.values(), full.params.values()):
-            pass
         src = ParamStore(cfg, dev, torch.bfloat16, ep_size=world, ep_rank=rank, seed=5)
         full = ParamStore(cfg, dev, torch.bfloat16, seed=5)
         dist.barrier()
