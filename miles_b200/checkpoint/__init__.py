@@ -256,7 +256,11 @@ def load_checkpoint(actor, path: str, step: Optional[int] = None) -> Optional[in
         rid = state.get("rollout_id", it)
         return int(rid) if rid is not None else None
     if os.path.isdir(path):
-        load_hf(actor.cfg, actor.store, path)
+        import contextlib
+
+        # a sharded store keeps what is written into its per-unit views only inside writing()
+        with (actor.store.writing(gather=False) if getattr(actor.store, "is_fsdp", False) else contextlib.nullcontext()):
+            load_hf(actor.cfg, actor.store, path)
         if actor.opt is not None:
             actor.opt.sync_master_from_params()
         return None
@@ -331,6 +335,8 @@ def export_hf(actor, out_dir: str, max_shard_bytes: int = 5 << 30, tokenizer_dir
     shards, cur, size = [], {}, 0
     for hf_name, t in hf_names(cfg, store, tp_group=ps.tp.group if ps.tp.size > 1 else None):
         is_expert = ".experts." in hf_name
+        if getattr(store, "is_fsdp", False) and ps.rank != 0:
+            continue  # every rank of a sharded trainer sees the same gathered tensors: the first one writes them
         if ps.tp.size > 1 and ps.tp.rank != 0:
             continue  # the gathered tensors are identical on every tensor-parallel rank
         if not is_expert and ps.dp_cp.rank != 0:
@@ -342,6 +348,8 @@ def export_hf(actor, out_dir: str, max_shard_bytes: int = 5 << 30, tokenizer_dir
             shards.append(cur)
             cur, size = {}, 0
         cur[hf_name] = t.detach().contiguous().cpu()
+        if getattr(store, "is_fsdp", False) and cur[hf_name].device == t.device:
+            cur[hf_name] = cur[hf_name].clone()  # the unit buffers are reused: keep a copy, not a view
         size += nb
     if cur:
         shards.append(cur)

@@ -108,14 +108,20 @@ def save(actor, directory: str, iteration: int, async_save: bool = False):
 
     os.makedirs(directory, exist_ok=True)
     with_opt = not getattr(actor.args, "no_save_optim", False)
-    sd = {k: v.detach() for k, v in state_atoms(actor, with_opt).items()}
-    if async_save:
-        sd = {k: v.cpu().clone() for k, v in sd.items()}  # the device may move on: the writer thread owns host copies
+    if getattr(actor.store, "is_fsdp", False):
+        from ..fsdp.checkpoint import gathered_atoms
+
+        # a sharded store: units are gathered and every rank keeps host copies of the atoms of the units it owns
+        sd = gathered_atoms(actor, with_opt)
+    else:
+        sd = {k: v.detach() for k, v in state_atoms(actor, with_opt).items()}
+        if async_save:
+            sd = {k: v.cpu().clone() for k, v in sd.items()}  # the device may move on: the writer thread owns host copies
     opt = getattr(actor, "opt", None)
     extra = {"iteration": iteration, "global_step": actor.global_step, "rollout_id": iteration, "version": actor.store.version,
              "optimizer_step": getattr(opt, "step_count", 0) if opt is not None else 0, "model": actor.cfg.to_dict(),
              "saved_layout": {"tp": actor.store.tp_size, "ep": actor.store.ep_size, "pp": actor.store.pp_size,
-                              "world": actor.ps.world_size}}
+                              "world": actor.ps.world_size, "fsdp_shards": getattr(actor.store, "shard_size", 0)}}
     if actor.ps.rank == 0:
         with open(os.path.join(directory, "meta.json"), "w") as f:
             json.dump(extra, f, default=str)
@@ -137,6 +143,14 @@ def load(actor, directory: str, with_optimizer: bool = True) -> dict:
     # resident optimizer state is handed out as the live tensors; state kept in pinned host chunks as concatenated host
     # copies, which are loaded here and written back through load_state_dict below
     osd = opt.state_dict() if (with_optimizer and opt is not None and hasattr(opt, "state_dict")) else {}
+    if getattr(actor.store, "is_fsdp", False):
+        from ..fsdp.checkpoint import load_units
+
+        if load_units(actor, directory, meta_keys, with_optimizer, osd or None):
+            opt.load_state_dict(osd)
+        else:
+            osd = {}
+        return _finish_load(actor, directory, bool(osd))
     want = state_atoms(actor, with_optimizer, osd or None)
     sd = {}
     for k, v in want.items():
@@ -152,14 +166,20 @@ def load(actor, directory: str, with_optimizer: bool = True) -> dict:
         for k, v in want.items():  # non-contiguous views were loaded into contiguous copies
             if k in sd and sd[k].data_ptr() != v.data_ptr():
                 v.copy_(sd[k])
-    if osd and any(k.startswith("optim.") for k in sd):
+    got_optim = bool(osd) and any(k.startswith("optim.") for k in sd)
+    if got_optim:
         # state_dict() hands out the live tensors for resident state; offloaded chunks were concatenated into copies
         opt.load_state_dict(osd)
+    return _finish_load(actor, directory, got_optim)
+
+
+def _finish_load(actor, directory: str, got_optim: bool) -> dict:
+    opt = getattr(actor, "opt", None)
     meta = {}
     p = os.path.join(directory, "meta.json")
     if os.path.exists(p):
         meta = json.load(open(p))
-    if osd and any(k.startswith("optim.") for k in sd) and hasattr(opt, "step_count"):
+    if got_optim and hasattr(opt, "step_count"):
         opt.step_count = int(meta.get("optimizer_step", opt.step_count))
     return meta
 

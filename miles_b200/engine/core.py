@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import itertools
 import time
+import zlib
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
@@ -281,7 +282,7 @@ class Engine:
         if len(ids) + 1 > self.max_seq_len:
             ids = ids[-(self.max_seq_len - 1):]
         req = Request(rid, ids, params, return_routed_experts)
-        req.seed = params.sampling_seed if params.sampling_seed is not None else (hash(rid) & 0x7FFFFFFF)
+        req.seed = params.sampling_seed if params.sampling_seed is not None else (zlib.crc32(rid.encode()) & 0x7FFFFFFF)
         req.t_submit = time.time()
         self.waiting.append(req)
         return rid

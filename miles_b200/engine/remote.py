@@ -11,6 +11,7 @@ miles/backends/sglang_utils/sglang_engine.py:126-693.
 from __future__ import annotations
 
 import asyncio
+import zlib
 from typing import Optional, Sequence
 
 from ..utils import http_utils
@@ -29,7 +30,7 @@ class RemoteEngineClient:
     # ------------------------------------------------------------------ data plane
     def _pick(self, routing_key: Optional[str] = None) -> str:
         if routing_key is not None:  # requests of one session stay on one engine (its KV cache holds their prefix)
-            return self.urls[hash(routing_key) % len(self.urls)]
+            return self.urls[zlib.crc32(str(routing_key).encode()) % len(self.urls)]  # the same engine from any process
         low = min(self.inflight.values())
         cands = [u for u in self.urls if self.inflight[u] == low]
         self._rr += 1

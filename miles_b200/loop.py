@@ -130,6 +130,8 @@ class RLLoop:
             total = torch.cuda.get_device_properties(self.actor.device).total_memory
             frac = float(getattr(a, "sglang_mem_fraction_static", 0.7))
             budget = int(total * frac) - self.actor.store.nbytes()
+            if getattr(self.actor, "fsdp", False):
+                budget -= sum(self.actor.store.full_sizes.values()) * 2  # the engine's own whole copy of the model
             per_tok = 2 * cfg.num_layers * cfg.num_kv_heads * cfg.head_dim * 2
             want = max_running * (max_ctx + page) * per_tok
             # what is really free once weights, gradients and resident optimizer states are placed, keeping
@@ -142,14 +144,15 @@ class RLLoop:
             room = free_now + lend - total // 7
             kv_bytes = max(min(budget, want, room), per_tok * page * 4)
         pipelined = self.ps.pp.size > 1
+        sharded = getattr(self.actor, "fsdp", False)
         replicate = not pipelined and self.actor.ep_dispatcher is not None and self._replicate_experts_fits(kv_bytes)
         if replicate:
             # the worst case (every sequence at the full context length) almost never happens and the engine retracts
             # requests when the pool runs dry: with the replica resident, size the pool for 65 % of that worst case
             kv_bytes = max(min(kv_bytes, room - self._replica_bytes(), int(0.65 * want)), per_tok * page * 4)
-        if pipelined:
+        if pipelined or sharded:
             assert self.actor.ep_dispatcher is None and self.ps.tp.size == 1, \
-                "the colocated engine of a pipelined trainer is built for tp = ep = 1"
+                "the colocated engine of a pipelined or sharded trainer is built for tp = ep = 1"
             from .models import build_specs
 
             full_bytes = sum(sp.numel for sp in build_specs(cfg)) * 2
@@ -188,6 +191,15 @@ class RLLoop:
                 self.rollout_store = ParamStore(cfg, self.actor.device, self.actor.store.dtype, ep_size=1, init=False,
                                                 share_dense=self.actor.store)
             engine_model = build_model(cfg, self.rollout_store, "b200")
+        elif sharded:
+            # the trainer holds one slice of every unit: the engine decodes on a whole copy that the weight update fills
+            # with one all-gather per unit, straight into its flat buffers (miles_b200/fsdp/store.py)
+            from .fsdp.store import FsdpWeightGather
+            from .models import ParamStore, build_model
+
+            self.rollout_store = ParamStore(cfg, self.actor.device, self.actor.store.dtype, init=False)
+            self.rollout_store.weight_pusher = FsdpWeightGather(self.actor.store, self.rollout_store)
+            engine_model = build_model(cfg, self.rollout_store, "b200" if not self.actor.is_torch else "torch")
         elif pipelined:
             # the trainer's stage holds part of the layers; the engine decodes on a copy of the whole model that the
             # weight update fills stage by stage (broadcasts inside the pipeline group)

@@ -522,6 +522,9 @@ class B200Qwen3:
         ``tokens``, later stages continue from ``x_in``; every stage but the last returns the raw hidden states that
         the next stage consumes, the last one applies the final norm."""
         cfg, P, C = self.cfg, self.store.params, self.C
+        begin = getattr(self.store, "begin_pass", None)
+        if begin is not None:
+            begin()  # a sharded store materialises units per pass
         lo, hi = self.store.layer_range
         x = P["embed.weight"][tokens.long()] if self.store.is_first_stage else x_in
         if not max_seqlen and cu_seqlens is not None:

@@ -159,6 +159,9 @@ class TorchQwen3:
         pipeline parallelism this runs the stage's layers: later stages start from ``x_in``, every stage but the last
         returns the raw hidden states for the next one."""
         cfg, P = self.cfg, self.store.params
+        begin = getattr(self.store, "begin_pass", None)
+        if begin is not None:
+            begin()
         lo, hi = getattr(self.store, "layer_range", (0, cfg.num_layers))
         x = F.embedding(tokens.long(), P["embed.weight"]) if getattr(self.store, "is_first_stage", True) else x_in
         moe_idx = sum(cfg.layer_is_moe(j) for j in range(lo))
@@ -198,6 +201,10 @@ class TorchQwen3:
             return self.logprobs_entropy(hidden[row_index.long()], targets, inv_temp)
 
     def set_requires_grad(self, flag: bool) -> None:
+        hook = getattr(self.store, "on_requires_grad", None)
+        if hook is not None:
+            hook(flag)  # a sharded store: the leaves are its shard buffers, full parameters are gathered under autograd
+            return
         for t in self.store.flat.values():
             t.requires_grad_(flag)
         # views were created before requires_grad was set; rebuild them so autograd tracks them

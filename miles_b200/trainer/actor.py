@@ -129,6 +129,20 @@ class TrainActor:
         self.dtype = torch.bfloat16 if want_b200 else (torch.float32 if not self.on_gpu else torch.bfloat16)
         ep = self.ps.ep.size if self.cfg.is_moe else 1
         tp = self.ps.tp.size
+        # --train-backend fsdp: pure data parallelism with parameters, master weights and moments sharded per unit
+        # over the data-parallel ranks (miles_b200/fsdp)
+        self.fsdp = getattr(args, "train_backend", "megatron") == "fsdp"
+        if self.fsdp and store is None:
+            from ..fsdp import FsdpParamStore, build_mesh
+
+            if tp > 1 or self.ps.pp.size > 1 or self.ps.ep.size > 1:
+                raise ValueError("--train-backend fsdp is data parallel only (optionally with context parallelism): "
+                                 "tensor / pipeline / expert parallel sizes must be 1")
+            if getattr(args, "lora_rank", 0):
+                raise NotImplementedError("--lora-rank with --train-backend fsdp is not built")
+            self.mesh = build_mesh(self.ps, int(getattr(args, "dp_replicate_size", 1) or 1))
+            store = FsdpParamStore(self.cfg, self.device, self.dtype, self.mesh, init_std=getattr(args, "init_std", 0.02),
+                                   seed=args.seed, num_buffers=int(getattr(args, "fsdp_num_unit_buffers", 2) or 2))
         if store is None:
             store = ParamStore(self.cfg, self.device, self.dtype, ep_size=ep, ep_rank=self.ps.ep.rank if ep > 1 else 0,
                                init_std=getattr(args, "init_std", 0.02), seed=args.seed, tp_size=tp, tp_rank=self.ps.tp.rank,
@@ -260,7 +274,10 @@ class TrainActor:
             total = torch.cuda.get_device_properties(self.device).total_memory
             extra = 0
             colocated = self.role == "actor" and not getattr(a, "debug_train_only", False) and not getattr(a, "rollout_engine_urls", None)
-            if (self.cfg.is_moe and self.ps.ep.size > 1 and colocated and self.ps.tp.size == 1
+            if self.fsdp and colocated:
+                # the colocated engine holds a whole copy of the model next to this rank's shards, plus the unit buffers
+                extra = sum(self.store.full_sizes.values()) * 2 + sum(self.store.max_padded.values()) * 12
+            elif (self.cfg.is_moe and self.ps.ep.size > 1 and colocated and self.ps.tp.size == 1
                     and replica_wanted(a, self.ps.ep.size)):
                 # the colocated engine will hold all experts in a buffer of its own (see RLLoop._build_engine; this
                 # rank's share is stored twice: the trainer's flat shard and its slice of every replica tensor)
@@ -281,6 +298,8 @@ class TrainActor:
         if getattr(a, "main_params_dtype", "fp32") != "fp32":
             plan["master"] = False
             plan["name"] += ", no fp32 master"
+        if self.fsdp and getattr(a, "fsdp_cpu_offload", False):
+            plan["offload"], plan["resident_frac"] = True, 0.0
         if getattr(a, "optimizer_cpu_offload", False) or getattr(a, "offload_optimizer_states", False):
             plan["offload"], plan["resident_frac"] = True, 0.0
         if getattr(a, "accumulate_allreduce_grads_in_fp32", False) and self.on_gpu and self.cfg.is_moe:
@@ -306,6 +325,15 @@ class TrainActor:
                          lr_warmup_iters=warmup, lr_decay_iters=a.lr_decay_iters or 0, min_lr=a.min_lr,
                          skip_nonfinite=not getattr(a, "no_check_for_nan_in_loss_and_grad", False),
                          lr_wsd_decay_iters=a.lr_wsd_decay_iters or 0)
+        if self.fsdp:
+            if getattr(a, "stream_optimizer_state_to_disk", False) or getattr(a, "optimizer", "adam") != "adam":
+                raise NotImplementedError("--train-backend fsdp steps with Adam on the resident or host-offloaded shards")
+            if not getattr(a, "keep_fp32_master", True):
+                oc.master_weights = False
+            self.dense_shard = None
+            # gradients arrive reduced over the shard group; every rank's slice counts once in the global norm
+            self.opt = FlatAdam(self.store, oc, shard_group=self.store.group)
+            return
         if getattr(a, "stream_optimizer_state_to_disk", False) or getattr(a, "offload_train_target", "cpu") == "disk":
             # optimizer state in files on a local disk, streamed through the device bucket by bucket
             # (--stream-optimizer-state-to-disk, or --offload-train-target disk): for models whose state fits neither
@@ -798,6 +826,10 @@ class TrainActor:
 
     def _reduce_grads(self) -> None:
         """Sum dense gradients over dp x cp and expert gradients over the experts' own data-parallel group."""
+        if self.fsdp:
+            # each unit was reduce-scattered as the backward left it: flush the last one (and sum over replicas)
+            self.store.finish_grads()
+            return
         if self.ps.world_size <= 1:
             return
         if self.ps.tp.size > 1:
@@ -941,6 +973,12 @@ class TrainActor:
         engine (KV cache) while rolling out. The two uses never overlap in the synchronous loop, the
         addresses stay fixed (captured decode graphs remain valid), and nothing is freed or reallocated
         between phases. Returns the uint8 buffer (at least ``min_bytes`` long)."""
+        if self.fsdp:
+            # sharded gradients are small and the unit buffers come and go with sleep / wake: the arena is the cache's own
+            if self.arena is None or self.arena.numel() < int(min_bytes):
+                self.arena = None
+                self.arena = torch.empty(max(int(min_bytes), 256), dtype=torch.uint8, device=self.device)
+            return self.arena
         n = self.store.sizes.get("expert", 0) * torch.empty((), dtype=self._expert_grad_dtype).element_size()
         size = max(int(min_bytes), n, 256)
         if self.arena is None or self.arena.numel() < size:
@@ -956,6 +994,11 @@ class TrainActor:
         """Release trainer-only device memory (gradients) so that the rollout engine can use it. With a lent
         arena the gradients already share their bytes with the KV cache and nothing has to move."""
         with Timer().context("sleep"):
+            if self.fsdp:
+                self.store.release_buffers()  # the full-unit buffers; the gradient shards stay
+                if self.on_gpu:
+                    torch.cuda.empty_cache()
+                return
             if self.arena is not None:
                 return
             self.store.free_grads()

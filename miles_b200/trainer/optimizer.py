@@ -69,9 +69,10 @@ def lr_at(cfg: OptimConfig, step: int) -> float:
 
 class FlatAdam:
     def __init__(self, store: ParamStore, cfg: OptimConfig, dp_group=None, ep_group=None, tp_group=None, dense_shard=None,
-                 pp_group=None):
+                 pp_group=None, shard_group=None):
         self.store, self.cfg = store, cfg
         self.dp_group, self.ep_group = dp_group, ep_group
+        self.shard_group = shard_group  # a sharded store: every rank holds a different slice of every gradient
         self.tp_group = tp_group  # tensor-parallel shards count once each in the global gradient norm
         self.pp_group = pp_group  # pipeline stages hold disjoint layers: their squared norms add up
         self.dev = store.device
@@ -126,7 +127,10 @@ class FlatAdam:
             self.state[g] = st
         # weight decay applies to matrices only (norm weights and biases are exempt)
         self.segments = {g: [] for g in store.flat}
-        for s in store.specs:
+        custom = getattr(store, "decay_segments", None)
+        if custom is not None:
+            self.segments = custom(cfg.weight_decay)  # a sharded store knows which of its elements are matrices
+        for s in (store.specs if custom is None else ()):
             wd = cfg.weight_decay if len(s.shape) >= 2 else 0.0
             segs = self.segments[s.group]
             if segs and segs[-1][2] == wd and segs[-1][1] == s.offset:
@@ -178,6 +182,8 @@ class FlatAdam:
             self.norm_buf[0:1] += total_sharded - sharded
         if self.pp_group is not None and dist.is_initialized() and dist.get_world_size(self.pp_group) > 1:
             dist.all_reduce(self.norm_buf, group=self.pp_group)
+        if self.shard_group is not None and dist.is_initialized() and dist.get_world_size(self.shard_group) > 1:
+            dist.all_reduce(self.norm_buf, group=self.shard_group)
         total = self.norm_buf.sum().sqrt()
         self.last_grad_norm = total
         return total

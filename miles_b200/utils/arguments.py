@@ -109,6 +109,10 @@ TRAINER_FLAGS = [
     ("--padded-vocab-size", "i", None, {}), ("--wandb-project", "s", None, {}), ("--deterministic-mode", "b", False, {}),
     ("--no-check-for-nan-in-loss-and-grad", "b", False, {}), ("--log-interval", "i", 1, {}),
     ("--tokenizer-type", "s", "HuggingFaceTokenizer", {}), ("--tokenizer-model", "s", None, {}),
+    # sharded data-parallel backend (--train-backend fsdp); names of the reference's fsdp_utils/arguments.py:10-66
+    ("--dp-replicate-size", "i", 1, {}), ("--fsdp-cpu-offload", "b", False, {}), ("--keep-fp32-master", "B", True, {}),
+    ("--gradient-checkpointing", "b", False, {}), ("--fsdp-state-dict-cpu-offload", "B", True, {}),
+    ("--config", "s", None, {}), ("--fsdp-num-unit-buffers", "i", 2, {}),
     # native extensions of this framework
     ("--model-preset", "s", None, {}), ("--model-backend", "s", "auto", {"choices": ["auto", "b200", "torch"]}),
     ("--init-std", "f", 0.02, {}), ("--engine-page-size", "i", 64, {}), ("--engine-max-prefill-tokens", "i", 16384, {}),
@@ -268,6 +272,33 @@ def validate_args(args: argparse.Namespace) -> argparse.Namespace:
         with open(args.custom_config_path) as f:
             for k, v in (yaml.safe_load(f) or {}).items():
                 setattr(args, k, v)
+    if getattr(args, "config", None):
+        # the sharded backend's YAML file: keys are flag names with underscores; unknown keys are an error, not a no-op
+        # (reference: fsdp_utils/arguments.py:100-123)
+        import yaml
+
+        with open(args.config) as f:
+            data = yaml.safe_load(f) or {}
+        unknown = sorted(k for k in data if not hasattr(args, k))
+        if unknown:
+            raise ValueError(f"unknown key(s) in the YAML config {args.config}: {', '.join(unknown)}")
+        for k, v in data.items():
+            setattr(args, k, v)
+    if getattr(args, "train_backend", "megatron") == "fsdp":
+        for flag in ("tensor_model_parallel_size", "pipeline_model_parallel_size", "expert_model_parallel_size"):
+            if int(getattr(args, flag, 1) or 1) != 1:
+                raise ValueError(f"--train-backend fsdp is data parallel only: --{flag.replace('_', '-')} must be 1")
+        for flag, what in (("lora_rank", "LoRA"), ("rollout_engine_urls", "engines in other processes"),
+                           ("use_fault_tolerance", "independent data-parallel cells"),
+                           ("stream_optimizer_state_to_disk", "optimizer state on disk")):
+            if getattr(args, flag, None):
+                raise NotImplementedError(f"--train-backend fsdp with {what} (--{flag.replace('_', '-')}) is not built")
+        if getattr(args, "update_weight_transfer_mode", "broadcast") == "disk-delta":
+            raise NotImplementedError("--train-backend fsdp updates engines by all-gather, not through disk deltas")
+        if int(getattr(args, "dp_replicate_size", 1) or 1) < 1:
+            raise ValueError("--dp-replicate-size must be at least 1")
+    elif int(getattr(args, "dp_replicate_size", 1) or 1) != 1 or getattr(args, "fsdp_cpu_offload", False):
+        raise ValueError("--dp-replicate-size / --fsdp-cpu-offload belong to --train-backend fsdp")
     # ---- algorithm
     assert not (args.kl_coef != 0 and args.kl_loss_coef != 0), "only one of --kl-coef and --kl-loss-coef can be set"
     if args.advantage_estimator in ("reinforce_plus_plus", "reinforce_plus_plus_baseline"):

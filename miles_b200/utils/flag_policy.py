@@ -69,7 +69,6 @@ REJECT = {
     "true_on_policy_mode": "bit-identical trainer / rollout numerics",
     "moe_router_dtype": "router precision other than fp32",
     # topology / backends that are not built
-    "train_backend": "the FSDP trainer backend (use --model-backend torch for the PyTorch autograd path)",
     "virtual_pipeline_model_parallel_size": "interleaved pipeline stages",
     "expert_tensor_parallel_size": "tensor parallelism inside experts",
     "qkv_format": "padded [batch, seq] batches (sequences are always packed)",
@@ -82,6 +81,9 @@ REJECT = {
 
 # dest -> why nothing needs to happen
 IGNORED = {
+    # sharded backend: activations are always recomputed per layer; checkpoints stage through host copies per unit
+    "gradient_checkpointing": "layer inputs are the only activations kept: every layer is recomputed in the backward",
+    "fsdp_state_dict_cpu_offload": "checkpoint and export copies are always staged in host memory, unit by unit",
     # Megatron / TransformerEngine kernel and fusion switches: one fused sm_100a path exists here
     "attention_backend": "one attention implementation (tcgen05 flash attention)",
     "attention_softmax_in_fp32": "softmax statistics are always fp32",

@@ -14,8 +14,10 @@ end -> continue_generation``.  Modes here:
   for weight updates; buckets announced over HTTP, tensors broadcast from the trainer's source rank).
 * **disk**      — ``disk_delta``: versioned XOR / overwrite deltas that engines pull.
 
-Writing the trainer's shards straight into the buffers of engines on other GPUs of the box from inside a kernel
-(peer stores over NVLink) is not built; the broadcast mode covers those engines.
+* **push**      — an engine store that carries a ``weight_pusher``: the replica of an expert-parallel trainer is filled by
+  one kernel per flat buffer that reshards, optionally quantises and stores into every GPU's replica over NVLink
+  (``p2p_push.WeightPusher``, ``csrc/weight_push.cu``); the engine of a sharded (``--train-backend fsdp``) trainer by one
+  all-gather per unit straight into its flat buffers (``fsdp.store.FsdpWeightGather``).
 """
 from __future__ import annotations
 

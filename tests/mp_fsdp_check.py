@@ -1,0 +1,105 @@
+"""Helper launched by torchrun (2+ GPUs): the sharded data-parallel store under the sm_100a model path. Every rank runs
+forward + backward on micro-batches of its own through (a) an unsharded store followed by a gradient all-reduce and (b) the
+sharded store (all-gather per unit on the communication stream with prefetch, reduce-scatter per unit in the backward).
+Log-probs must be equal bit for bit (same kernels, same weights) and every rank's gradient shard must match its slice of
+the all-reduced gradients; then one Adam step on both and the gathered weights are compared, and the engine-side gather is
+checked against the unsharded weights."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+from miles_b200.fsdp import FsdpParamStore, build_mesh
+from miles_b200.models import ParamStore, build_model, get_config
+from miles_b200.parallel.state import init_parallel_state
+from miles_b200.trainer.optimizer import FlatAdam, OptimConfig
+
+
+def main():
+    ps = init_parallel_state()
+    dev, rank, world = ps.device, ps.rank, ps.world_size
+    mesh = build_mesh(ps, 1)
+    for preset in ("qwen3-smoke", "qwen3-smoke-moe"):
+        cfg = get_config(preset)
+        ref_store = ParamStore(cfg, dev, torch.bfloat16, init_std=0.05, seed=5)
+        ref_store.allocate_grads(torch.float32)
+        ref = build_model(cfg, ref_store, "b200")
+        store = FsdpParamStore(cfg, dev, torch.bfloat16, mesh, init_std=0.05, seed=5)
+        store.allocate_grads(torch.float32)
+        model = build_model(cfg, store, "b200")
+        full = ParamStore(cfg, dev, torch.bfloat16, init=False)
+        store.gather_into(full)
+        for g in full.flat:
+            assert torch.equal(full.flat[g], ref_store.flat[g]), f"{preset}: initial shards do not gather to the same model ({g})"
+        oc = OptimConfig(lr=1e-3, weight_decay=0.01, clip_grad=1.0, master_weights=True)
+        opt_ref = FlatAdam(ref_store, oc)
+        opt = FlatAdam(store, oc, shard_group=store.group)
+        gen = torch.Generator().manual_seed(11 + rank)
+        for step in range(2):
+            ref_store.zero_grads()
+            store.zero_grads()
+            for mb in range(2):
+                lens = [300 + 17 * rank + 5 * mb, 129, 700]
+                T = sum(lens)
+                tokens = torch.randint(0, cfg.vocab_size, (T,), generator=gen).int().to(dev)
+                pos = torch.cat([torch.arange(n) for n in lens]).int().to(dev)
+                cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32).to(dev)
+                rows = torch.cat([torch.arange(a + 5, a + n - 1) for a, n in zip(cu[:-1].tolist(), lens)]).to(dev)
+                targets = tokens[(rows + 1).long()]
+                coef = torch.randn(rows.numel(), generator=gen).to(dev)
+                denom = float(rows.numel())
+
+                def loss(lp, ent, c=coef, d=denom):
+                    return (lp * c).sum() / d + 0.01 * ent.sum() / d, {}
+
+                rec = []
+                ref.forward_logprobs(tokens, pos, cu, rows, targets, 1.0, record=rec)
+                replay = torch.stack(rec, 1) if rec else None
+                _, _, lp_ref, _ = ref.forward_backward(tokens, pos, cu, rows, targets, 1.0, loss, replay=replay)
+                lp_nograd, _ = model.forward_logprobs(tokens, pos, cu, rows, targets, 1.0, replay=replay)
+                _, _, lp, _ = model.forward_backward(tokens, pos, cu, rows, targets, 1.0, loss, replay=replay)
+                model.check_status()
+                assert torch.equal(lp, lp_ref) and torch.equal(lp_nograd, lp_ref), (preset, (lp - lp_ref).abs().max().item())
+            store.finish_grads()
+            for g in ("dense", "expert"):
+                gr = ref_store.grad[g]
+                if gr is None or not gr.numel():
+                    continue
+                dist.all_reduce(gr)
+                for u in store.units:
+                    n = u.piece(g, world)
+                    if not n:
+                        continue
+                    a = u.lo[g] + rank * n
+                    b = min(a + n, u.hi[g])
+                    if b <= a:
+                        continue
+                    got = store.grad[g][u.shard_off[g]:u.shard_off[g] + b - a]
+                    want = gr[a:b]
+                    err = (got - want).abs().max().item()
+                    # dQ is accumulated with atomics: the two backward passes differ by fp32 summation order only
+                    assert err <= 2e-3 * max(want.abs().max().item(), 1e-3) + 1e-6, (preset, g, u.name, err, want.abs().max().item())
+            n_ref = opt_ref.step(1.0)
+            n_fs = opt.step(1.0)
+            assert abs(float(n_ref) - float(n_fs)) <= 1e-3 * float(n_ref), (float(n_ref), float(n_fs))
+            store.gather_into(full)
+            for g in full.flat:
+                d = (full.flat[g].float() - ref_store.flat[g].float()).abs()
+                # a bf16 weight may round the other way where the two gradients differ in the last bits
+                assert d.max().item() <= 2.5e-3 and (d > 0).float().mean().item() < 0.02, (preset, g, d.max().item(), (d > 0).float().mean().item())
+                ref_store.flat[g].copy_(full.flat[g])  # keep both sides on identical weights for the next step
+            opt_ref.sync_master_from_params()
+        if rank == 0:
+            print(f"fsdp {preset}: gathers {store.gathers} reduce-scatters {store.reduce_scatters} grad norm {float(n_fs):.4f}", flush=True)
+        dist.barrier()
+    if rank == 0:
+        print(f"FSDP_CHECK_OK world={world}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

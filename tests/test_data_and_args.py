@@ -170,7 +170,7 @@ def test_every_flag_is_read_rejected_or_declared_inert():
 def test_unbuilt_features_refuse_to_start():
     base = ["--num-rollout", "1", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--model-preset", "qwen3-tiny"]
     for extra in (["--fp8-format", "e4m3", "--fp8-recipe", "mxfp8"], ["--moe-router-score-function", "sigmoid"],
-                  ["--moe-shared-expert-intermediate-size", "512"], ["--attention-output-gate"], ["--train-backend", "fsdp"],
+                  ["--moe-shared-expert-intermediate-size", "512"], ["--attention-output-gate"],
                   ["--true-on-policy-mode"], ["--virtual-pipeline-model-parallel-size", "2"], ["--hidden-dropout", "0.1"]):
         with pytest.raises(NotImplementedError):
             parse_args(base + extra)

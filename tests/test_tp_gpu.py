@@ -76,3 +76,16 @@ def test_context_parallel_training_step_on_the_sm100_path():
            "--master-port", "29749", os.path.join(here, "mp_cp_train_check.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "CP_TRAIN_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_sharded_data_parallel_store_on_the_sm100_path():
+    """--train-backend fsdp under the hand-written forward / backward: per-unit all-gather with prefetch on a side stream,
+    per-unit reduce-scatter in the backward, Adam on the shards; against an unsharded store + gradient all-reduce."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29751", os.path.join(here, "mp_fsdp_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "FSDP_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
