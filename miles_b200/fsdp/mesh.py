@@ -8,8 +8,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-import torch.distributed as dist
-
+from ..parallel.reloadable_groups import registry
 from ..parallel.state import GroupInfo, ParallelState
 
 
@@ -40,11 +39,11 @@ def build_mesh(ps: ParallelState, replicate_size: int = 1) -> FsdpMesh:
     shard_groups, repl_groups = mesh_ranks(ranks, replicate_size)
     mine_s = mine_r = None
     for rk in shard_groups:
-        g = dist.new_group(rk) if len(rk) > 1 else None
+        g = registry().new_group(rk) if len(rk) > 1 else None
         if ps.rank in rk:
             mine_s = GroupInfo(rk.index(ps.rank), len(rk), g, rk)
     for rk in repl_groups:
-        g = dist.new_group(rk) if len(rk) > 1 else None
+        g = registry().new_group(rk) if len(rk) > 1 else None
         if ps.rank in rk:
             mine_r = GroupInfo(rk.index(ps.rank), len(rk), g, rk)
     return FsdpMesh(mine_s, mine_r)

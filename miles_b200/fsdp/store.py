@@ -91,8 +91,13 @@ def build_units(specs: list, shard_size: int) -> list:
 def _all_gather(out: torch.Tensor, piece: torch.Tensor, group, size: int) -> None:
     if size == 1:
         out.copy_(piece)
-    else:
-        dist.all_gather_into_tensor(out, piece.contiguous(), group=group)
+        return
+    piece = piece.contiguous()
+    if piece.dtype in (torch.int16, torch.uint16):
+        # a gather only moves bytes, and not every backend knows 16-bit integers (the remainder words of the split
+        # fp32 master weights): send them as bytes
+        out, piece = out.view(torch.uint8), piece.view(torch.uint8)
+    dist.all_gather_into_tensor(out, piece, group=group)
 
 
 def _reduce_scatter(out: torch.Tensor, full: torch.Tensor, group, size: int) -> None:

@@ -406,11 +406,16 @@ class RLLoop:
                 samples = samples[:k // 2] + samples[len(samples) - (k - k // 2):]
             samples = samples[self.rep::self.n_rep] if self.n_rep > 1 else samples
             return samples, {}
+        released = self._release_groups_for_rollout()
         out = self.rollout_fn(RolloutFnTrainInput(rollout_id))
         if asyncio.iscoroutine(out):
             out = asyncio.run(out)
         if self.engine is not None:
             self.engine.drain()  # expert-parallel ranks keep serving dummy iterations until all are done
+        if released:
+            from .parallel.reloadable_groups import registry
+
+            registry().reload()
         samples = flatten_groups(out.samples if hasattr(out, "samples") else out)
         if getattr(a, "ci_inject_rollout_data_path", None):
             from .utils.ci_checks import inject_rollout_data
@@ -444,6 +449,21 @@ class RLLoop:
             if self.ps.rank == 0:
                 torch.save({"rollout_id": rollout_id, "samples": [d for g in gathered for d in g]}, p)
         return samples, metrics
+
+    def _release_groups_for_rollout(self) -> bool:
+        """``--reload-process-groups``: while this rank's engine generates on its own (no lockstep with other ranks) the
+        trainer's communicators only pin device memory: destroy them for the rollout and build them again before the
+        first collective of the training phase (parallel/reloadable_groups.py)."""
+        a = self.args
+        if not getattr(a, "reload_process_groups", False) or self.ps.world_size <= 1 or self.engine is None:
+            return False
+        if getattr(self.engine, "sync", None) is not None or getattr(self.engine, "ep_decode", None) is not None:
+            return False  # expert-parallel engines talk to each other while they generate
+        from .parallel.reloadable_groups import registry
+
+        freed = registry().release(include_host_groups=self.ps.backend == "gloo")
+        self.last_group_release_bytes = freed
+        return True
 
     def _save_trajectories(self, rollout_id: int, samples: list, evaluation: bool) -> None:
         """``--save-debug-trajectory-data TEMPLATE``: one JSON line per sample that carries a conversation

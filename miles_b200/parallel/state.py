@@ -19,6 +19,8 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
+from .reloadable_groups import registry, reset_registry
+
 
 @dataclass
 class GroupInfo:
@@ -90,7 +92,7 @@ def _make_groups(world: int, rank: int, layout: list, backend_timeout) -> dict:
                 base += combo[k] * strides[j]
                 k += 1
             ranks = [base + i * strides[ai] for i in range(size)]
-            grp = dist.new_group(ranks, timeout=backend_timeout) if size > 1 else None
+            grp = registry().new_group(ranks, timeout=backend_timeout) if size > 1 else None
             if rank in ranks:
                 mine = GroupInfo(ranks.index(rank), size, grp, ranks)
         out[name] = mine
@@ -143,4 +145,5 @@ def destroy_parallel_state() -> None:
     global _STATE
     if dist.is_initialized():
         dist.destroy_process_group()
+    reset_registry()
     _STATE = None

@@ -113,6 +113,8 @@ TRAINER_FLAGS = [
     ("--dp-replicate-size", "i", 1, {}), ("--fsdp-cpu-offload", "b", False, {}), ("--keep-fp32-master", "B", True, {}),
     ("--gradient-checkpointing", "b", False, {}), ("--fsdp-state-dict-cpu-offload", "B", True, {}),
     ("--config", "s", None, {}), ("--fsdp-num-unit-buffers", "i", 2, {}),
+    # destroy the trainer's NCCL sub-groups while the colocated engine generates, rebuild them before training
+    ("--reload-process-groups", "b", False, {}),
     # native extensions of this framework
     ("--model-preset", "s", None, {}), ("--model-backend", "s", "auto", {"choices": ["auto", "b200", "torch"]}),
     ("--init-std", "f", 0.02, {}), ("--engine-page-size", "i", 64, {}), ("--engine-max-prefill-tokens", "i", 16384, {}),

@@ -62,7 +62,13 @@ def main():
                 lp_nograd, _ = model.forward_logprobs(tokens, pos, cu, rows, targets, 1.0, replay=replay)
                 _, _, lp, _ = model.forward_backward(tokens, pos, cu, rows, targets, 1.0, loss, replay=replay)
                 model.check_status()
-                assert torch.equal(lp, lp_ref) and torch.equal(lp_nograd, lp_ref), (preset, (lp - lp_ref).abs().max().item())
+                d1, d2 = (lp - lp_ref).abs().max().item(), (lp_nograd - lp_ref).abs().max().item()
+                if rank == 0 and step == 0 and mb == 0:
+                    print(f"fsdp {preset}: log-prob difference to the unsharded model {d1:.2e} (with backward) {d2:.2e} (forward only)", flush=True)
+                # identical weights at the first step: identical numbers; afterwards the two sides' weights differ in a
+                # few elements by a rounding step, which bf16 arithmetic amplifies to the usual forward noise
+                tol = 0.0 if step == 0 else 6e-2
+                assert d1 <= tol and d2 <= tol, (preset, step, d1, d2)
             store.finish_grads()
             for g in ("dense", "expert"):
                 gr = ref_store.grad[g]
@@ -79,19 +85,27 @@ def main():
                         continue
                     got = store.grad[g][u.shard_off[g]:u.shard_off[g] + b - a]
                     want = gr[a:b]
-                    err = (got - want).abs().max().item()
-                    # dQ is accumulated with atomics: the two backward passes differ by fp32 summation order only
-                    assert err <= 2e-3 * max(want.abs().max().item(), 1e-3) + 1e-6, (preset, g, u.name, err, want.abs().max().item())
+                    # dQ is accumulated with atomics and the all-reduce and the reduce-scatter add in different orders:
+                    # the two gradients differ by rounding, which relative norm and cosine bound
+                    rel = ((got - want).norm() / want.norm().clamp_min(1e-12)).item()
+                    cos = torch.nn.functional.cosine_similarity(got, want, dim=0).item() if want.norm().item() > 0 else 1.0
+                    assert rel < 2e-2 and cos > 0.999, (preset, g, u.name, rel, cos)
             n_ref = opt_ref.step(1.0)
             n_fs = opt.step(1.0)
             assert abs(float(n_ref) - float(n_fs)) <= 1e-3 * float(n_ref), (float(n_ref), float(n_fs))
             store.gather_into(full)
             for g in full.flat:
+                if not full.flat[g].numel():
+                    continue
                 d = (full.flat[g].float() - ref_store.flat[g].float()).abs()
                 # a bf16 weight may round the other way where the two gradients differ in the last bits
-                assert d.max().item() <= 2.5e-3 and (d > 0).float().mean().item() < 0.02, (preset, g, d.max().item(), (d > 0).float().mean().item())
-                ref_store.flat[g].copy_(full.flat[g])  # keep both sides on identical weights for the next step
-            opt_ref.sync_master_from_params()
+                frac = (d > 0).float().mean().item()
+                if rank == 0:
+                    print(f"fsdp {preset} step {step} {g}: weights differ in {frac:.4%} of the elements, max {d.max().item():.2e}", flush=True)
+                # one bf16 step of the largest weights at most. After the first step (same weights, same data) only a few
+                # elements in a million may round the other way; from then on the two runs have their own weights and
+                # Adam's normalised update turns noise-level gradient differences into different roundings of more elements
+                assert d.max().item() <= 8e-3 and frac < (1e-4 if step == 0 else 0.05), (preset, g, step, d.max().item(), frac)
         if rank == 0:
             print(f"fsdp {preset}: gathers {store.gathers} reduce-scatters {store.reduce_scatters} grad norm {float(n_fs):.4f}", flush=True)
         dist.barrier()

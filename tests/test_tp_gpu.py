@@ -89,3 +89,15 @@ def test_sharded_data_parallel_store_on_the_sm100_path():
            "--master-port", "29751", os.path.join(here, "mp_fsdp_check.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "FSDP_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_nccl_groups_are_released_and_rebuilt():
+    """--reload-process-groups: destroy the NCCL sub-groups, build them again, collectives and holders keep working."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29753", os.path.join(here, "mp_reload_groups_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "RELOAD_GROUPS_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
