@@ -163,13 +163,15 @@ __global__ void colsum_kernel(const float* __restrict__ part, float* __restrict_
 // partner d+64 lives in lane l+16, so pairs are exchanged with a shuffle).
 // Outputs: q_out [T, Hq, D], k_out [T, Hk, D] (v is consumed in place by the attention kernels).
 // When kv_cache pointers are given, K and V rows are also scattered to slot_mapping[t] of the paged cache.
+// inv_freq_tab (64 floats, or null): inverse frequencies of a model with scaled rotary embeddings (Llama-3.1 style or
+// linear scaling); null means theta^(-d/64).
 __global__ void qk_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
                                         const bf16* __restrict__ kw, const int* __restrict__ pos,
                                         bf16* __restrict__ q_out, bf16* __restrict__ k_out,
                                         float* __restrict__ q_rstd, float* __restrict__ k_rstd,
                                         bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                                         const int* __restrict__ slot_mapping, int T, int Hq, int Hk,
-                                        float theta, float eps, int use_norm) {
+                                        float theta, float eps, int use_norm, const float* __restrict__ inv_freq_tab) {
   constexpr int D = 128;
   const int warps_per_block = blockDim.x >> 5;
   const long long gw = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
@@ -221,7 +223,7 @@ __global__ void qk_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16
   for (int i = 0; i < 4; ++i) {
     const float partner = __shfl_xor_sync(0xffffffffu, f[i], 16);
     const int d = (lane & 15) * 4 + i;  // frequency index in [0, 64)
-    const float inv_freq = powf(theta, -static_cast<float>(d) / 64.f);
+    const float inv_freq = inv_freq_tab ? inv_freq_tab[d] : powf(theta, -static_cast<float>(d) / 64.f);
     float s, c;
     sincosf(p * inv_freq, &s, &c);
     o[i] = lane < 16 ? f[i] * c - partner * s : f[i] * c + partner * s;
@@ -249,7 +251,7 @@ __global__ void qk_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16*
                                         const int* __restrict__ pos, const float* __restrict__ q_rstd,
                                         const float* __restrict__ k_rstd, bf16* __restrict__ dqkv,
                                         float* __restrict__ dqw, float* __restrict__ dkw, int T, int Hq, int Hk,
-                                        float theta, int use_norm) {
+                                        float theta, int use_norm, const float* __restrict__ inv_freq_tab) {
   constexpr int D = 128;
   __shared__ float wacc[2][D];
   for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&wacc[0][0])[i] = 0.f;
@@ -285,7 +287,7 @@ __global__ void qk_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16*
     for (int i = 0; i < 4; ++i) {
       const float partner = __shfl_xor_sync(0xffffffffu, g[i], 16);
       const int d = (lane & 15) * 4 + i;
-      const float inv_freq = powf(theta, -static_cast<float>(d) / 64.f);
+      const float inv_freq = inv_freq_tab ? inv_freq_tab[d] : powf(theta, -static_cast<float>(d) / 64.f);
       float s, c;
       sincosf(p * inv_freq, &s, &c);
       dn[i] = lane < 16 ? g[i] * c + partner * s : g[i] * c - partner * s;
@@ -624,7 +626,7 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
 
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* q_out, void* k_out,
                       float* q_rstd, float* k_rstd, void* k_cache, void* v_cache, const int* slot_mapping, int T,
-                      int Hq, int Hk, float theta, float eps, bool use_norm, cudaStream_t s) {
+                      int Hq, int Hk, float theta, float eps, bool use_norm, cudaStream_t s, const float* inv_freq) {
   if (T <= 0) return;
   const long long warps = static_cast<long long>(T) * (Hq + 2 * Hk);
   const int wpb = 8;
@@ -632,12 +634,12 @@ void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int
   qk_norm_rope_fwd_kernel<<<static_cast<unsigned>(blocks), wpb * 32, 0, s>>>(
       static_cast<const bf16*>(qkv), static_cast<const bf16*>(qw), static_cast<const bf16*>(kw), pos,
       static_cast<bf16*>(q_out), static_cast<bf16*>(k_out), q_rstd, k_rstd, static_cast<bf16*>(k_cache),
-      static_cast<bf16*>(v_cache), slot_mapping, T, Hq, Hk, theta, eps, use_norm ? 1 : 0);
+      static_cast<bf16*>(v_cache), slot_mapping, T, Hq, Hk, theta, eps, use_norm ? 1 : 0, inv_freq);
 }
 
 void qk_norm_rope_bwd(const void* dq, const void* dk, const void* dv, const void* qkv, const void* qw, const void* kw,
                       const int* pos, const float* q_rstd, const float* k_rstd, void* dqkv, float* dqw, float* dkw,
-                      int T, int Hq, int Hk, float theta, bool use_norm, cudaStream_t s) {
+                      int T, int Hq, int Hk, float theta, bool use_norm, cudaStream_t s, const float* inv_freq) {
   if (T <= 0) return;
   const long long warps = static_cast<long long>(T) * (Hq + 2 * Hk);
   const int wpb = 8;
@@ -646,7 +648,7 @@ void qk_norm_rope_bwd(const void* dq, const void* dk, const void* dv, const void
   qk_norm_rope_bwd_kernel<<<static_cast<unsigned>(blocks), wpb * 32, 0, s>>>(
       static_cast<const bf16*>(dq), static_cast<const bf16*>(dk), static_cast<const bf16*>(dv),
       static_cast<const bf16*>(qkv), static_cast<const bf16*>(qw), static_cast<const bf16*>(kw), pos, q_rstd, k_rstd,
-      static_cast<bf16*>(dqkv), dqw, dkw, T, Hq, Hk, theta, use_norm ? 1 : 0);
+      static_cast<bf16*>(dqkv), dqw, dkw, T, Hq, Hk, theta, use_norm ? 1 : 0, inv_freq);
 }
 
 void swiglu_fwd(const void* in, void* out, long long T, int I, cudaStream_t s) {

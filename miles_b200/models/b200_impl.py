@@ -307,11 +307,25 @@ class B200Qwen3:
             kc, vc = kv_cache[i]
             slots = meta.slot_mapping
         write_k = meta is None or meta.is_prefill
-        q, k, qr, kr = C.qk_norm_rope_fwd(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"), positions,
-                                          cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps, kc, vc, slots,
-                                          write_k)
+        if cfg.rope_scaling:
+            q, k, qr, kr = C.qk_norm_rope_fwd_scaled(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"),
+                                                     positions, cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps,
+                                                     kc, vc, slots, write_k, self._rope_table())
+        else:
+            q, k, qr, kr = C.qk_norm_rope_fwd(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"), positions,
+                                              cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps, kc, vc, slots,
+                                              write_k)
         self.launches += 2
         return h1, rstd1, qkv, q, k, qr, kr
+
+    def _rope_table(self) -> torch.Tensor:
+        """The 64 inverse frequencies of a model with scaled rotary embeddings (fp32, on the device)."""
+        t = getattr(self, "_inv_freq", None)
+        if t is None:
+            from ..ops.reference import rope_inv_freq
+
+            t = self._inv_freq = rope_inv_freq(self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling, self.dev).contiguous()
+        return t
 
     def _v_view(self, qkv):
         cfg = self.cfg
@@ -408,9 +422,14 @@ class B200Qwen3:
         if cfg.qkv_bias:
             qkv += P[p + "attn.qkv.bias"]
         kc, vc = kv_cache[i]
-        q, _, _, _ = C.qk_norm_rope_fwd(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"), positions,
-                                        cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps, kc, vc,
-                                        meta.slot_mapping, False)
+        if cfg.rope_scaling:
+            q, _, _, _ = C.qk_norm_rope_fwd_scaled(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"),
+                                                   positions, cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps,
+                                                   kc, vc, meta.slot_mapping, False, self._rope_table())
+        else:
+            q, _, _, _ = C.qk_norm_rope_fwd(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"), positions,
+                                            cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps, kc, vc,
+                                            meta.slot_mapping, False)
         att = torch.empty_like(q)
         splits = self._decode_splits(T, meta)
         need = T * cfg.num_q_heads * splits * 130
@@ -501,9 +520,15 @@ class B200Qwen3:
         datt = self.linear_dgrad(dx2, P[p + "attn.o.weight"])
         self.linear_wgrad(dx2, att2, G[p + "attn.o.weight"])
         dq, dk, dv = self.attention_backward(q, k, v, att, datt.view_as(att), lse, cu)
-        dqkv = C.qk_norm_rope_bwd(dq, dk, dv, qkv, P.get(p + "attn.q_norm.weight"),
-                                  P.get(p + "attn.k_norm.weight"), positions, qr, kr, G.get(p + "attn.q_norm.weight"),
-                                  G.get(p + "attn.k_norm.weight"), cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta)
+        if cfg.rope_scaling:
+            dqkv = C.qk_norm_rope_bwd_scaled(dq, dk, dv, qkv, P.get(p + "attn.q_norm.weight"),
+                                             P.get(p + "attn.k_norm.weight"), positions, qr, kr, G.get(p + "attn.q_norm.weight"),
+                                             G.get(p + "attn.k_norm.weight"), cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta,
+                                             self._rope_table())
+        else:
+            dqkv = C.qk_norm_rope_bwd(dq, dk, dv, qkv, P.get(p + "attn.q_norm.weight"),
+                                      P.get(p + "attn.k_norm.weight"), positions, qr, kr, G.get(p + "attn.q_norm.weight"),
+                                      G.get(p + "attn.k_norm.weight"), cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta)
         self.launches += 1
         if cfg.qkv_bias:
             G[p + "attn.qkv.bias"].add_(dqkv.float().sum(0).to(G[p + "attn.qkv.bias"].dtype))

@@ -10,7 +10,7 @@ from __future__ import annotations
 import json
 from dataclasses import asdict, dataclass, field
 from pathlib import Path
-from typing import Any
+from typing import Any, Optional
 
 
 @dataclass
@@ -36,6 +36,9 @@ class ModelConfig:
     moe_layer_freq: int = 1  # every n-th layer is MoE (1 = all)
     first_dense_layers: int = 0
     max_position_embeddings: int = 40960
+    # scaled rotary embeddings: None, {"rope_type": "llama3", "factor", "low_freq_factor", "high_freq_factor",
+    # "original_max_position_embeddings"} or {"rope_type": "linear", "factor"}
+    rope_scaling: Optional[dict] = None
     hf_architecture: str = "Qwen3ForCausalLM"
     extra: dict[str, Any] = field(default_factory=dict)
 
@@ -86,10 +89,15 @@ class ModelConfig:
         return asdict(self)
 
     # ------------------------------------------------------------------ HF interop
+    @property
+    def family(self) -> str:
+        """The HuggingFace ``model_type`` of this architecture (decides config keys and tensor names)."""
+        return HF_FAMILIES.get(self.hf_architecture, "qwen3_moe" if self.is_moe else "qwen3")
+
     def to_hf_config(self) -> dict:
         cfg = {
             "architectures": [self.hf_architecture],
-            "model_type": "qwen3_moe" if self.is_moe else "qwen3",
+            "model_type": self.family,
             "hidden_size": self.hidden_size,
             "num_hidden_layers": self.num_layers,
             "num_attention_heads": self.num_q_heads,
@@ -104,7 +112,12 @@ class ModelConfig:
             "max_position_embeddings": self.max_position_embeddings,
             "torch_dtype": "bfloat16",
         }
-        if self.is_moe:
+        if self.rope_scaling:
+            cfg["rope_scaling"] = dict(self.rope_scaling)
+        if self.family == "mixtral":
+            cfg.update({"num_local_experts": self.num_experts, "num_experts_per_tok": self.moe_top_k,
+                        "intermediate_size": self.moe_ffn_hidden_size, "sliding_window": None})
+        elif self.is_moe:
             cfg.update({
                 "num_experts": self.num_experts,
                 "num_experts_per_tok": self.moe_top_k,
@@ -125,8 +138,29 @@ class ModelConfig:
         arch = (cfg.get("architectures") or ["Qwen3ForCausalLM"])[0]
         heads = cfg["num_attention_heads"]
         head_dim = cfg.get("head_dim") or cfg["hidden_size"] // heads
-        is_qwen3 = "qwen3" in cfg.get("model_type", "qwen3").lower()
+        mtype = (cfg.get("model_type") or HF_FAMILIES.get(arch, "qwen3")).lower()
+        if arch not in HF_FAMILIES:
+            raise NotImplementedError(f"{arch} ({mtype}) is not one of the architectures this package implements: "
+                                      f"{', '.join(sorted(HF_FAMILIES))}")
+        is_qwen3 = "qwen3" in mtype
         mlp_only = cfg.get("mlp_only_layers") or []
+        n_experts = cfg.get("num_experts", 0) or cfg.get("num_local_experts", 0) or 0
+        moe_ffn = cfg.get("moe_intermediate_size", 0) or (cfg.get("intermediate_size", 0) if mtype == "mixtral" else 0)
+        if cfg.get("sliding_window") and cfg.get("use_sliding_window", mtype != "qwen2" and not is_qwen3) \
+                and cfg["sliding_window"] < cfg.get("max_position_embeddings", 0):
+            raise NotImplementedError("sliding-window attention is not built: this checkpoint would be served with full attention")
+        scaling = cfg.get("rope_scaling") or None
+        if scaling is None and isinstance(cfg.get("rope_parameters"), dict) and cfg["rope_parameters"].get("rope_type") not in (None, "default"):
+            scaling = {k: v for k, v in cfg["rope_parameters"].items() if k != "rope_theta"}
+        if scaling:
+            kind = scaling.get("rope_type") or scaling.get("type") or "default"
+            if kind == "default":
+                scaling = None
+            elif kind in ("llama3", "linear"):
+                scaling = dict(scaling, rope_type=kind)
+                scaling.pop("type", None)
+            else:
+                raise NotImplementedError(f"rope scaling of type {kind!r} is not built (llama3 and linear are)")
         return cls(
             name=name or cfg.get("_name_or_path", arch),
             num_layers=cfg["num_hidden_layers"],
@@ -137,19 +171,29 @@ class ModelConfig:
             ffn_hidden_size=cfg.get("intermediate_size", 0),
             vocab_size=cfg["vocab_size"],
             rms_eps=cfg.get("rms_norm_eps", 1e-6),
-            rope_theta=float(cfg.get("rope_theta", 1e6)),
+            # newer HuggingFace configs keep the base inside "rope_parameters"; 10000 is the library-wide default
+            rope_theta=float(cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta") or 10000.0),
             qk_norm=is_qwen3,
-            qkv_bias=bool(cfg.get("attention_bias", not is_qwen3 and "qwen2" in cfg.get("model_type", ""))),
+            qkv_bias=bool(cfg.get("attention_bias", not is_qwen3 and "qwen2" in mtype)),
             tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
-            num_experts=cfg.get("num_experts", 0) or 0,
-            moe_top_k=cfg.get("num_experts_per_tok", 0) or 0,
-            moe_ffn_hidden_size=cfg.get("moe_intermediate_size", 0) or 0,
-            norm_topk_prob=bool(cfg.get("norm_topk_prob", True)),
+            num_experts=n_experts,
+            moe_top_k=(cfg.get("num_experts_per_tok", 0) or 0) if n_experts else 0,
+            moe_ffn_hidden_size=moe_ffn,
+            # Mixtral takes the softmax over the chosen experts only, which equals renormalising the full softmax
+            norm_topk_prob=True if mtype == "mixtral" else bool(cfg.get("norm_topk_prob", True)),
             moe_layer_freq=cfg.get("decoder_sparse_step", 1) or 1,
             first_dense_layers=(max(mlp_only) + 1) if mlp_only else 0,
             max_position_embeddings=cfg.get("max_position_embeddings", 40960),
+            rope_scaling=scaling,
             hf_architecture=arch,
         )
+
+
+# architectures this package implements -> HuggingFace model_type
+HF_FAMILIES = {
+    "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3_moe", "Qwen2ForCausalLM": "qwen2", "LlamaForCausalLM": "llama",
+    "MistralForCausalLM": "mistral", "MixtralForCausalLM": "mixtral", "MiMoForCausalLM": "mimo",
+}
 
 
 def _dense(name, L, H, q, kv, ffn, tie, vocab=151936, hd=128, **kw) -> ModelConfig:
@@ -171,6 +215,14 @@ PRESETS: dict[str, ModelConfig] = {
     # a small GPU smoke model with head_dim 128 (the kernels' native head size)
     "qwen3-smoke": _dense("qwen3-smoke", 2, 512, 4, 2, 1024, False, vocab=4096),
     "qwen3-smoke-moe": _moe("qwen3-smoke-moe", 2, 512, 8, 2, 16, 4, 256, vocab=4096),
+    # the same size in the other families' conventions: no QK norm, scaled rotary embedding / Mixtral expert naming
+    "llama3-smoke": _dense("llama3-smoke", 2, 512, 4, 2, 1024, False, vocab=4096, qk_norm=False, rope_theta=5e5, rms_eps=1e-5,
+                           hf_architecture="LlamaForCausalLM", max_position_embeddings=131072,
+                           rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                         "original_max_position_embeddings": 8192}),
+    "mixtral-smoke": ModelConfig(name="mixtral-smoke", num_layers=2, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                                 ffn_hidden_size=256, vocab_size=4096, rms_eps=1e-5, qk_norm=False, num_experts=8, moe_top_k=2,
+                                 moe_ffn_hidden_size=256, hf_architecture="MixtralForCausalLM"),
     "qwen3-0.6B": _dense("qwen3-0.6B", 28, 1024, 16, 8, 3072, True),
     "qwen3-1.7B": _dense("qwen3-1.7B", 28, 2048, 16, 8, 6144, True),
     "qwen3-4B": _dense("qwen3-4B", 36, 2560, 32, 8, 9728, True),
@@ -194,22 +246,37 @@ PRESETS: dict[str, ModelConfig] = {
     "qwen2.5-72B": _dense("qwen2.5-72B", 80, 8192, 64, 8, 29568, False, vocab=152064, qk_norm=False, qkv_bias=True, rope_theta=1e6,
                           hf_architecture="Qwen2ForCausalLM"),
     "llama-3.2-1B": _dense("llama-3.2-1B", 16, 2048, 32, 8, 8192, True, vocab=128256, hd=64, qk_norm=False,
-                           rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+                           rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM",
+                           rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}, max_position_embeddings=131072),
     "llama-3.2-3B": _dense("llama-3.2-3B", 28, 3072, 24, 8, 8192, True, vocab=128256, qk_norm=False,
-                           rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+                           rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM",
+                           rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}, max_position_embeddings=131072),
     "llama-3.1-70B": _dense("llama-3.1-70B", 80, 8192, 64, 8, 28672, False, vocab=128256, qk_norm=False,
-                            rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+                            rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM",
+                           rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}, max_position_embeddings=131072),
     "mistral-7B": _dense("mistral-7B", 32, 4096, 32, 8, 14336, False, vocab=32768, qk_norm=False,
                          rope_theta=1e6, rms_eps=1e-5, hf_architecture="MistralForCausalLM"),
     "llama-3.1-8B": _dense("llama-3.1-8B", 32, 4096, 32, 8, 14336, False, vocab=128256, qk_norm=False,
-                           rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+                           rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM",
+                           rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}, max_position_embeddings=131072),
+    # Mixtral: 8 experts, top-2, the softmax taken over the chosen experts (= renormalised top-k of the full softmax)
+    "mixtral-8x7B": ModelConfig(name="mixtral-8x7B", num_layers=32, hidden_size=4096, num_q_heads=32, num_kv_heads=8, head_dim=128,
+                                ffn_hidden_size=14336, vocab_size=32000, rms_eps=1e-5, rope_theta=1e6, qk_norm=False, num_experts=8,
+                                moe_top_k=2, moe_ffn_hidden_size=14336, max_position_embeddings=32768,
+                                hf_architecture="MixtralForCausalLM"),
+    "mixtral-8x22B": ModelConfig(name="mixtral-8x22B", num_layers=56, hidden_size=6144, num_q_heads=48, num_kv_heads=8, head_dim=128,
+                                 ffn_hidden_size=16384, vocab_size=32768, rms_eps=1e-5, rope_theta=1e6, qk_norm=False, num_experts=8,
+                                 moe_top_k=2, moe_ffn_hidden_size=16384, max_position_embeddings=65536,
+                                 hf_architecture="MixtralForCausalLM"),
     # names of the reference's per-model argument files (scripts/models/*.py) for shapes already covered above
     "qwen3-4B-Instruct-2507": _dense("qwen3-4B-Instruct-2507", 36, 2560, 32, 8, 9728, True, rope_theta=5e6),
     "qwen3-30B-A3B-5layer": _moe("qwen3-30B-A3B-5layer", 5, 2048, 32, 4, 128, 8, 768),
     "llama3.1-8B-Instruct": _dense("llama3.1-8B-Instruct", 32, 4096, 32, 8, 14336, False, vocab=128256, qk_norm=False,
-                                   rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+                                   rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM",
+                           rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}, max_position_embeddings=131072),
     "llama3.2-3B-Instruct": _dense("llama3.2-3B-Instruct", 28, 3072, 24, 8, 8192, True, vocab=128256, qk_norm=False,
-                                   rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM"),
+                                   rope_theta=5e5, rms_eps=1e-5, hf_architecture="LlamaForCausalLM",
+                           rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}, max_position_embeddings=131072),
     # MiMo-7B-RL: a Qwen2-style dense model (QKV bias, no QK norm); its multi-token-prediction layer is not trained here
     "mimo-7B-rl": _dense("mimo-7B-rl", 36, 4096, 32, 8, 11008, False, vocab=151680, qk_norm=False, qkv_bias=True,
                          rope_theta=640000.0, rms_eps=1e-5, hf_architecture="Qwen2ForCausalLM"),

@@ -1,4 +1,4 @@
-"""Native parameter layout <-> HuggingFace names (Qwen3 / Qwen3-MoE / Qwen2 / Llama conventions).
+"""Native parameter layout <-> HuggingFace names (Qwen3 / Qwen3-MoE / Qwen2 / Llama / Mistral / Mixtral conventions).
 
 ``to_hf`` splits the fused tensors (q|k|v rows, gate|up rows, stacked experts) into the per-projection
 tensors an HF checkpoint or an external engine expects; ``from_hf`` is the inverse.  This is the role of
@@ -49,16 +49,22 @@ def to_hf(cfg: ModelConfig, name: str, t: torch.Tensor, expert_offset: int = 0) 
         return [(p + "mlp.gate_proj.weight", t[:I]), (p + "mlp.up_proj.weight", t[I:])]
     if rest == "mlp.down.weight":
         return [(p + "mlp.down_proj.weight", t)]
+    mixtral = getattr(cfg, "family", "") == "mixtral"  # block_sparse_moe.{gate, experts.N.w1 (gate) / w3 (up) / w2 (down)}
     if rest == "moe.router.weight":
-        return [(p + "mlp.gate.weight", t)]
+        return [(p + ("block_sparse_moe.gate.weight" if mixtral else "mlp.gate.weight"), t)]
     if rest == "moe.w1":
         I = t.shape[1] // 2
         out = []
         for e in range(t.shape[0]):
             ge = expert_offset + e
-            out += [(p + f"mlp.experts.{ge}.gate_proj.weight", t[e, :I]), (p + f"mlp.experts.{ge}.up_proj.weight", t[e, I:])]
+            if mixtral:
+                out += [(p + f"block_sparse_moe.experts.{ge}.w1.weight", t[e, :I]), (p + f"block_sparse_moe.experts.{ge}.w3.weight", t[e, I:])]
+            else:
+                out += [(p + f"mlp.experts.{ge}.gate_proj.weight", t[e, :I]), (p + f"mlp.experts.{ge}.up_proj.weight", t[e, I:])]
         return out
     if rest == "moe.w2":
+        if mixtral:
+            return [(p + f"block_sparse_moe.experts.{expert_offset + e}.w2.weight", t[e]) for e in range(t.shape[0])]
         return [(p + f"mlp.experts.{expert_offset + e}.down_proj.weight", t[e]) for e in range(t.shape[0])]
     raise KeyError(name)
 

@@ -88,8 +88,13 @@ class TorchQwen3:
         p = f"layers.{i}."
         h = R.rmsnorm(x, P[p + "ln1.weight"], cfg.rms_eps)
         qkv = F.linear(h, P[p + "attn.qkv.weight"], P.get(p + "attn.qkv.bias"))
+        inv_freq = None
+        if cfg.rope_scaling:
+            if getattr(self, "_inv_freq", None) is None or self._inv_freq.device != qkv.device:
+                self._inv_freq = R.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling, qkv.device)
+            inv_freq = self._inv_freq
         q, k, v = R.qk_norm_rope(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"), positions,
-                                 cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rope_theta, cfg.rms_eps)
+                                 cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rope_theta, cfg.rms_eps, inv_freq)
         scale = cfg.head_dim ** -0.5
         if meta is None or meta.is_prefill:
             if kv_cache is not None:

@@ -17,9 +17,33 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return y.to(x.dtype)
 
 
-def rope_cos_sin(pos: torch.Tensor, dim: int, theta: float):
-    inv = theta ** (-torch.arange(dim // 2, device=pos.device, dtype=torch.float32) / (dim // 2))
-    ang = pos.float()[:, None] * inv[None, :]
+def rope_inv_freq(dim: int, theta: float, scaling: Optional[dict] = None, device=None) -> torch.Tensor:
+    """The ``dim / 2`` inverse frequencies of the rotary embedding. ``scaling``: None; ``{"rope_type": "linear",
+    "factor"}`` (every frequency divided by the factor); or ``{"rope_type": "llama3", "factor", "low_freq_factor",
+    "high_freq_factor", "original_max_position_embeddings"}``: wavelengths beyond ``original / low_freq_factor`` are
+    stretched by the factor, those below ``original / high_freq_factor`` are kept, the band between is interpolated
+    (the published Llama-3.1 recipe)."""
+    import math
+
+    inv = theta ** (-torch.arange(dim // 2, device=device, dtype=torch.float32) / (dim // 2))
+    if not scaling:
+        return inv
+    kind = scaling.get("rope_type") or scaling.get("type")
+    factor = float(scaling["factor"])
+    if kind == "linear":
+        return inv / factor
+    assert kind == "llama3", f"rope scaling {kind!r} is not built"
+    low, high = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+    orig = float(scaling.get("original_max_position_embeddings", 8192))
+    wavelen = 2 * math.pi / inv
+    smooth = ((orig / wavelen - low) / (high - low)).clamp(0.0, 1.0)
+    mixed = (1 - smooth) * inv / factor + smooth * inv
+    return torch.where(wavelen > orig / low, inv / factor, torch.where(wavelen < orig / high, inv, mixed))
+
+
+def rope_cos_sin(pos: torch.Tensor, dim: int, theta: float, inv_freq: Optional[torch.Tensor] = None):
+    inv = inv_freq if inv_freq is not None else theta ** (-torch.arange(dim // 2, device=pos.device, dtype=torch.float32) / (dim // 2))
+    ang = pos.float()[:, None] * inv.to(pos.device)[None, :]
     return ang.cos(), ang.sin()
 
 
@@ -33,15 +57,15 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
 
 
 def qk_norm_rope(qkv: torch.Tensor, qw: Optional[torch.Tensor], kw: Optional[torch.Tensor], pos: torch.Tensor,
-                 Hq: int, Hk: int, D: int, theta: float, eps: float):
-    """qkv [T, (Hq+2Hk)*D] -> q [T,Hq,D], k [T,Hk,D], v [T,Hk,D]."""
+                 Hq: int, Hk: int, D: int, theta: float, eps: float, inv_freq: Optional[torch.Tensor] = None):
+    """qkv [T, (Hq+2Hk)*D] -> q [T,Hq,D], k [T,Hk,D], v [T,Hk,D]. ``inv_freq``: see :func:`rope_inv_freq`."""
     T = qkv.shape[0]
     v3 = qkv.view(T, Hq + 2 * Hk, D)
     q, k, v = v3[:, :Hq], v3[:, Hq:Hq + Hk], v3[:, Hq + Hk:]
     if qw is not None:
         q = rmsnorm(q, qw, eps)
         k = rmsnorm(k, kw, eps)
-    cos, sin = rope_cos_sin(pos, D, theta)
+    cos, sin = rope_cos_sin(pos, D, theta, inv_freq)
     return apply_rope(q, cos, sin), apply_rope(k, cos, sin), v
 
 

@@ -485,4 +485,8 @@ def model_config_from_args(args):
         num_experts=args.num_experts or 0, moe_top_k=args.moe_router_topk if moe else 0,
         moe_ffn_hidden_size=(args.moe_ffn_hidden_size or 0) if moe else 0,
         hf_architecture="Qwen3MoeForCausalLM" if moe else "Qwen3ForCausalLM",
+        # Megatron's --use-rope-scaling is the Llama-3.1 recipe with --rotary-scaling-factor (default 8)
+        rope_scaling=({"rope_type": "llama3", "factor": float(args.rotary_scaling_factor or 8.0), "low_freq_factor": 1.0,
+                       "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}
+                      if getattr(args, "use_rope_scaling", False) else None),
     )

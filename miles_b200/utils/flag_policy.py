@@ -28,8 +28,6 @@ REJECT = {
     "position_embedding_type": "position embeddings other than rotary",
     "no_position_embedding": "models without rotary position embedding",
     "rotary_percent": "partial rotary embedding",
-    "use_rope_scaling": "rope scaling",
-    "rotary_scaling_factor": "rope scaling",
     "original_max_position_embeddings": "YaRN rope scaling",
     "beta_fast": "YaRN rope scaling",
     "beta_slow": "YaRN rope scaling",

@@ -75,6 +75,30 @@ def test_qk_norm_rope_forward_and_backward(ext, T, Hq, Hk, use_norm):
         _close(dkw, kwf.grad, 2e-2, 3e-2 * (T * Hk) ** 0.5)
 
 
+@pytest.mark.parametrize("scaling", [{"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                      "original_max_position_embeddings": 8192}, {"rope_type": "linear", "factor": 4.0}])
+def test_scaled_rotary_embedding_forward_and_backward(ext, scaling):
+    """Llama-3.1 style and linear rope scaling: the kernels read the 64 inverse frequencies from a table."""
+    torch.manual_seed(3)
+    T, Hq, Hk, D, theta, eps = 257, 8, 2, 128, 5e5, 1e-5
+    inv = R.rope_inv_freq(D, theta, scaling, DEV).contiguous()
+    assert not torch.allclose(inv, R.rope_inv_freq(D, theta, None, DEV))
+    qkv = torch.randn(T, (Hq + 2 * Hk) * D, device=DEV).bfloat16()
+    pos = torch.randint(0, 9000, (T,), device=DEV, dtype=torch.int32)
+    q, k, _, _ = ext.qk_norm_rope_fwd_scaled(qkv, None, None, pos, Hq, Hk, theta, eps, None, None, None, True, inv)
+    qkv_f = qkv.float().requires_grad_(True)
+    q_ref, k_ref, v_ref = R.qk_norm_rope(qkv_f, None, None, pos, Hq, Hk, D, theta, eps, inv)
+    _close(q, q_ref, 2e-2, 2e-2)
+    _close(k, k_ref, 2e-2, 2e-2)
+    q_plain, _, _, _ = ext.qk_norm_rope_fwd(qkv, None, None, pos, Hq, Hk, theta, eps, None, None, None, True)
+    assert (q.float() - q_plain.float()).abs().max().item() > 0.1, "the table must change the rotation"
+    dq, dk = torch.randn_like(q), torch.randn_like(k)
+    dv = torch.randn(T, Hk, D, device=DEV).bfloat16()
+    (q_ref * dq.float()).sum().add((k_ref * dk.float()).sum()).add((v_ref * dv.float()).sum()).backward()
+    dqkv = ext.qk_norm_rope_bwd_scaled(dq, dk, dv, qkv, None, None, pos, None, None, None, None, Hq, Hk, theta, inv)
+    _close(dqkv, qkv_f.grad, 2e-2, 3e-2)
+
+
 @pytest.mark.parametrize("T,I", [(1, 768), (333, 768), (257, 9728)])
 def test_swiglu_backward(ext, T, I):
     torch.manual_seed(I)

@@ -1,0 +1,108 @@
+"""Numerical parity with the HuggingFace implementations of every architecture family this package serves: a tiny randomly
+initialised HF model is saved as safetensors, read through ``ModelConfig.from_hf_config`` + ``load_hf``, and the logits of
+the PyTorch model path must equal the HF forward; then the weights are exported again and HF must load them back to the
+same logits. Covers the name mapping (fused QKV / gate-up, stacked experts), rotary convention and scaling, QK norm, biases,
+tied embeddings and the routers' top-k semantics."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from miles_b200.checkpoint import load_hf  # noqa: E402
+from miles_b200.models import ParamStore, build_model  # noqa: E402
+from miles_b200.models.config import ModelConfig  # noqa: E402
+from miles_b200.models.hf_mapping import hf_names  # noqa: E402
+
+COMMON = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              vocab_size=256, max_position_embeddings=4096)
+LLAMA3_SCALING = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                  "original_max_position_embeddings": 64}
+
+
+def _case(name):
+    T = transformers
+    if name == "qwen3":
+        return T.Qwen3Config(**COMMON, head_dim=16, rope_theta=1e6, tie_word_embeddings=False), T.Qwen3ForCausalLM
+    if name == "qwen3-tied":
+        return T.Qwen3Config(**COMMON, head_dim=32, rope_theta=1e6, tie_word_embeddings=True), T.Qwen3ForCausalLM
+    if name == "qwen3_moe":
+        return T.Qwen3MoeConfig(**COMMON, head_dim=16, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
+                                norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[]), T.Qwen3MoeForCausalLM
+    if name == "qwen3_moe-raw-topk":
+        return T.Qwen3MoeConfig(**COMMON, head_dim=16, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
+                                norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[0]), T.Qwen3MoeForCausalLM
+    if name == "qwen2":
+        return T.Qwen2Config(**COMMON, rope_theta=1e6, tie_word_embeddings=False), T.Qwen2ForCausalLM
+    if name == "llama":
+        return T.LlamaConfig(**COMMON, rope_theta=5e5, rms_norm_eps=1e-5), T.LlamaForCausalLM
+    if name == "llama-rope-llama3":
+        return T.LlamaConfig(**COMMON, rope_theta=5e5, rms_norm_eps=1e-5, rope_scaling=dict(LLAMA3_SCALING)), T.LlamaForCausalLM
+    if name == "llama-rope-linear":
+        return T.LlamaConfig(**COMMON, rope_theta=1e4, rope_scaling={"rope_type": "linear", "factor": 4.0}), T.LlamaForCausalLM
+    if name == "mistral":
+        return T.MistralConfig(**COMMON, rope_theta=1e6, sliding_window=None), T.MistralForCausalLM
+    if name == "mixtral":
+        return T.MixtralConfig(**COMMON, rope_theta=1e6, num_local_experts=4, num_experts_per_tok=2, sliding_window=None), T.MixtralForCausalLM
+    raise KeyError(name)
+
+
+CASES = ["qwen3", "qwen3-tied", "qwen3_moe", "qwen3_moe-raw-topk", "qwen2", "llama", "llama-rope-llama3", "llama-rope-linear",
+         "mistral", "mixtral"]
+
+
+def _my_logits(cfg: ModelConfig, store, tokens):
+    model = build_model(cfg, store, "torch")
+    lens = [len(tokens)]
+    with torch.no_grad():
+        h = model.forward_hidden(tokens.int(), torch.arange(lens[0]).int(), torch.tensor([0, lens[0]], dtype=torch.int32))
+        return model.logits(h)
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_logits_match_huggingface_both_ways(name, tmp_path):
+    torch.manual_seed(0)
+    hf_cfg, cls = _case(name)
+    hf = cls(hf_cfg).float().eval()
+    with torch.no_grad():  # HF initialises norms to one and biases to zero: make them matter
+        for n, p in hf.named_parameters():
+            if n.endswith("norm.weight") or n.endswith(".bias"):
+                p.add_(torch.randn_like(p) * 0.1)
+    src = tmp_path / "hf"
+    hf.save_pretrained(src, safe_serialization=True)
+    cfg = ModelConfig.from_hf_config(str(src))
+    assert cfg.hf_architecture == cls.__name__
+    store = ParamStore(cfg, "cpu", torch.float32, init=False)
+    n_loaded = load_hf(cfg, store, str(src))
+    assert n_loaded >= len(list(hf.state_dict())) - (1 if hf_cfg.tie_word_embeddings else 0) - 2
+    tokens = torch.randint(0, 256, (200,))  # longer than the scaled-rope "original" length, so scaling matters
+    with torch.no_grad():
+        ref = hf(tokens[None]).logits[0]
+    out = _my_logits(cfg, store, tokens)
+    assert torch.allclose(out, ref, atol=2e-4, rtol=1e-4), (name, (out - ref).abs().max().item())
+    # ... and back: export under HF names, load with HF, same logits
+    from safetensors.torch import save_file
+    import json
+
+    dst = tmp_path / "export"
+    dst.mkdir()
+    save_file({k: v.detach().clone().contiguous() for k, v in hf_names(cfg, store)}, str(dst / "model.safetensors"), metadata={"format": "pt"})
+    (dst / "config.json").write_text(json.dumps(cfg.to_hf_config()))
+    back = transformers.AutoModelForCausalLM.from_pretrained(str(dst), torch_dtype=torch.float32).eval()
+    assert type(back).__name__ == cls.__name__
+    with torch.no_grad():
+        again = back(tokens[None]).logits[0]
+    assert torch.allclose(again, ref, atol=2e-4, rtol=1e-4), (name, (again - ref).abs().max().item())
+
+
+def test_unsupported_checkpoints_are_refused():
+    with pytest.raises(NotImplementedError):
+        ModelConfig.from_hf_config({"architectures": ["DeepseekV3ForCausalLM"], "model_type": "deepseek_v3", "num_attention_heads": 4,
+                                    "hidden_size": 64, "num_hidden_layers": 1, "vocab_size": 10})
+    base = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_attention_heads": 4, "hidden_size": 64,
+            "num_hidden_layers": 1, "vocab_size": 10, "intermediate_size": 8}
+    with pytest.raises(NotImplementedError):
+        ModelConfig.from_hf_config(dict(base, rope_scaling={"rope_type": "yarn", "factor": 4.0}))
+    with pytest.raises(NotImplementedError):
+        ModelConfig.from_hf_config(dict(base, architectures=["MistralForCausalLM"], model_type="mistral", sliding_window=128,
+                                        max_position_embeddings=4096))
+    assert ModelConfig.from_hf_config(dict(base, rope_scaling=LLAMA3_SCALING)).rope_scaling["rope_type"] == "llama3"
