@@ -171,7 +171,8 @@ __global__ void qk_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16
                                         float* __restrict__ q_rstd, float* __restrict__ k_rstd,
                                         bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                                         const int* __restrict__ slot_mapping, int T, int Hq, int Hk,
-                                        float theta, float eps, int use_norm, const float* __restrict__ inv_freq_tab) {
+                                        float theta, float eps, int use_norm, const float* __restrict__ inv_freq_tab,
+                                        int rot_half) {
   constexpr int D = 128;
   const int warps_per_block = blockDim.x >> 5;
   const long long gw = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
@@ -220,13 +221,20 @@ __global__ void qk_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16
   const float p = static_cast<float>(pos[t]);
   float o[4];
 #pragma unroll
+  // rot_half = 64: the whole head rotates (dimension d pairs with d + 64). rot_half = 32: only the first 64 dimensions
+  // do (d pairs with d + 32), the rest passes through (partial rotary embedding).
+  const int hl = rot_half >> 2;  // lanes per half
   for (int i = 0; i < 4; ++i) {
-    const float partner = __shfl_xor_sync(0xffffffffu, f[i], 16);
-    const int d = (lane & 15) * 4 + i;  // frequency index in [0, 64)
-    const float inv_freq = inv_freq_tab ? inv_freq_tab[d] : powf(theta, -static_cast<float>(d) / 64.f);
+    const float partner = __shfl_xor_sync(0xffffffffu, f[i], hl);
+    if (lane >= 2 * hl) {
+      o[i] = f[i];
+      continue;
+    }
+    const int d = (lane & (hl - 1)) * 4 + i;  // frequency index in [0, rot_half)
+    const float inv_freq = inv_freq_tab ? inv_freq_tab[d] : powf(theta, -static_cast<float>(d) / static_cast<float>(rot_half));
     float s, c;
     sincosf(p * inv_freq, &s, &c);
-    o[i] = lane < 16 ? f[i] * c - partner * s : f[i] * c + partner * s;
+    o[i] = (lane & hl) == 0 ? f[i] * c - partner * s : f[i] * c + partner * s;
   }
   uint2 outv;
   outv.x = pack2(o[0], o[1]);
@@ -251,7 +259,7 @@ __global__ void qk_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16*
                                         const int* __restrict__ pos, const float* __restrict__ q_rstd,
                                         const float* __restrict__ k_rstd, bf16* __restrict__ dqkv,
                                         float* __restrict__ dqw, float* __restrict__ dkw, int T, int Hq, int Hk,
-                                        float theta, int use_norm, const float* __restrict__ inv_freq_tab) {
+                                        float theta, int use_norm, const float* __restrict__ inv_freq_tab, int rot_half) {
   constexpr int D = 128;
   __shared__ float wacc[2][D];
   for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&wacc[0][0])[i] = 0.f;
@@ -284,13 +292,18 @@ __global__ void qk_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16*
     const float p = static_cast<float>(pos[t]);
     float dn[4];
 #pragma unroll
+    const int hl = rot_half >> 2;  // lanes per half (see the forward kernel)
     for (int i = 0; i < 4; ++i) {
-      const float partner = __shfl_xor_sync(0xffffffffu, g[i], 16);
-      const int d = (lane & 15) * 4 + i;
-      const float inv_freq = inv_freq_tab ? inv_freq_tab[d] : powf(theta, -static_cast<float>(d) / 64.f);
+      const float partner = __shfl_xor_sync(0xffffffffu, g[i], hl);
+      if (lane >= 2 * hl) {
+        dn[i] = g[i];
+        continue;
+      }
+      const int d = (lane & (hl - 1)) * 4 + i;
+      const float inv_freq = inv_freq_tab ? inv_freq_tab[d] : powf(theta, -static_cast<float>(d) / static_cast<float>(rot_half));
       float s, c;
       sincosf(p * inv_freq, &s, &c);
-      dn[i] = lane < 16 ? g[i] * c + partner * s : g[i] * c - partner * s;
+      dn[i] = (lane & hl) == 0 ? g[i] * c + partner * s : g[i] * c - partner * s;
     }
     float o[4];
     if (use_norm) {
@@ -626,7 +639,8 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
 
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* q_out, void* k_out,
                       float* q_rstd, float* k_rstd, void* k_cache, void* v_cache, const int* slot_mapping, int T,
-                      int Hq, int Hk, float theta, float eps, bool use_norm, cudaStream_t s, const float* inv_freq) {
+                      int Hq, int Hk, float theta, float eps, bool use_norm, cudaStream_t s, const float* inv_freq,
+                      int rotary_dim) {
   if (T <= 0) return;
   const long long warps = static_cast<long long>(T) * (Hq + 2 * Hk);
   const int wpb = 8;
@@ -634,12 +648,13 @@ void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int
   qk_norm_rope_fwd_kernel<<<static_cast<unsigned>(blocks), wpb * 32, 0, s>>>(
       static_cast<const bf16*>(qkv), static_cast<const bf16*>(qw), static_cast<const bf16*>(kw), pos,
       static_cast<bf16*>(q_out), static_cast<bf16*>(k_out), q_rstd, k_rstd, static_cast<bf16*>(k_cache),
-      static_cast<bf16*>(v_cache), slot_mapping, T, Hq, Hk, theta, eps, use_norm ? 1 : 0, inv_freq);
+      static_cast<bf16*>(v_cache), slot_mapping, T, Hq, Hk, theta, eps, use_norm ? 1 : 0, inv_freq, rotary_dim / 2);
 }
 
 void qk_norm_rope_bwd(const void* dq, const void* dk, const void* dv, const void* qkv, const void* qw, const void* kw,
                       const int* pos, const float* q_rstd, const float* k_rstd, void* dqkv, float* dqw, float* dkw,
-                      int T, int Hq, int Hk, float theta, bool use_norm, cudaStream_t s, const float* inv_freq) {
+                      int T, int Hq, int Hk, float theta, bool use_norm, cudaStream_t s, const float* inv_freq,
+                      int rotary_dim) {
   if (T <= 0) return;
   const long long warps = static_cast<long long>(T) * (Hq + 2 * Hk);
   const int wpb = 8;
@@ -648,7 +663,7 @@ void qk_norm_rope_bwd(const void* dq, const void* dk, const void* dv, const void
   qk_norm_rope_bwd_kernel<<<static_cast<unsigned>(blocks), wpb * 32, 0, s>>>(
       static_cast<const bf16*>(dq), static_cast<const bf16*>(dk), static_cast<const bf16*>(dv),
       static_cast<const bf16*>(qkv), static_cast<const bf16*>(qw), static_cast<const bf16*>(kw), pos, q_rstd, k_rstd,
-      static_cast<bf16*>(dqkv), dqw, dkw, T, Hq, Hk, theta, use_norm ? 1 : 0, inv_freq);
+      static_cast<bf16*>(dqkv), dqw, dkw, T, Hq, Hk, theta, use_norm ? 1 : 0, inv_freq, rotary_dim / 2);
 }
 
 void swiglu_fwd(const void* in, void* out, long long T, int I, cudaStream_t s) {

@@ -15,10 +15,12 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
                  float* dw_partial, float* dw, bool accumulate_dw, int T, int H, cudaStream_t s);
 void qk_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, void* q_out, void* k_out,
                       float* q_rstd, float* k_rstd, void* k_cache, void* v_cache, const int* slot_mapping, int T,
-                      int Hq, int Hk, float theta, float eps, bool use_norm, cudaStream_t s, const float* inv_freq = nullptr);
+                      int Hq, int Hk, float theta, float eps, bool use_norm, cudaStream_t s, const float* inv_freq = nullptr,
+                      int rotary_dim = 128);
 void qk_norm_rope_bwd(const void* dq, const void* dk, const void* dv, const void* qkv, const void* qw, const void* kw,
                       const int* pos, const float* q_rstd, const float* k_rstd, void* dqkv, float* dqw, float* dkw,
-                      int T, int Hq, int Hk, float theta, bool use_norm, cudaStream_t s, const float* inv_freq = nullptr);
+                      int T, int Hq, int Hk, float theta, bool use_norm, cudaStream_t s, const float* inv_freq = nullptr,
+                      int rotary_dim = 128);
 void swiglu_fwd(const void* in, void* out, long long T, int I, cudaStream_t s);
 void swiglu_bwd(const void* dout, const void* in, void* din, long long T, int I, cudaStream_t s);
 // Fused Adam(W) on a bf16 flat buffer. The fp32 master is `master` (fp32 array), or the pair (p, lo) with `lo` a

@@ -54,11 +54,13 @@ std::vector<at::Tensor> qk_norm_rope_fwd(const at::Tensor& qkv, const c10::optio
                                          const c10::optional<at::Tensor>& kw, const at::Tensor& pos, int64_t Hq, int64_t Hk,
                                          double theta, double eps, const c10::optional<at::Tensor>& k_cache,
                                          const c10::optional<at::Tensor>& v_cache, const c10::optional<at::Tensor>& slot_mapping,
-                                         bool write_k_out, const c10::optional<at::Tensor>& inv_freq) {
+                                         bool write_k_out, const c10::optional<at::Tensor>& inv_freq, int64_t rotary_dim) {
   CHECK_BF16(qkv); CHECK_I32(pos);
+  TORCH_CHECK(rotary_dim == 128 || rotary_dim == 64, "rotary_dim must be 128 (whole head) or 64 (half of it)");
   if (inv_freq.has_value())
-    TORCH_CHECK(inv_freq->is_cuda() && inv_freq->scalar_type() == at::kFloat && inv_freq->numel() == 64 && inv_freq->is_contiguous(),
-                "inv_freq must be 64 contiguous fp32 values on the device");
+    TORCH_CHECK(inv_freq->is_cuda() && inv_freq->scalar_type() == at::kFloat && inv_freq->numel() == rotary_dim / 2 &&
+                    inv_freq->is_contiguous(),
+                "inv_freq must be rotary_dim / 2 contiguous fp32 values on the device");
   const c10::cuda::CUDAGuard guard(qkv.device());
   const int T = qkv.size(0);
   TORCH_CHECK(qkv.size(1) == (Hq + 2 * Hk) * 128, "qkv must be [T, (Hq+2Hk)*128]");
@@ -71,7 +73,7 @@ std::vector<at::Tensor> qk_norm_rope_fwd(const at::Tensor& qkv, const c10::optio
                        write_k_out ? k.data_ptr() : nullptr, use_norm ? qr.data_ptr<float>() : nullptr,
                        use_norm ? kr.data_ptr<float>() : nullptr, opt_ptr<void>(k_cache), opt_ptr<void>(v_cache),
                        opt_ptr<int>(slot_mapping), T, Hq, Hk, static_cast<float>(theta), static_cast<float>(eps), use_norm,
-                       cur_stream(), opt_ptr<float>(inv_freq));
+                       cur_stream(), opt_ptr<float>(inv_freq), static_cast<int>(rotary_dim));
   return {q, k, qr, kr};
 }
 
@@ -80,25 +82,27 @@ std::vector<at::Tensor> qk_norm_rope_fwd_plain(const at::Tensor& qkv, const c10:
                                                double theta, double eps, const c10::optional<at::Tensor>& k_cache,
                                                const c10::optional<at::Tensor>& v_cache,
                                                const c10::optional<at::Tensor>& slot_mapping, bool write_k_out) {
-  return qk_norm_rope_fwd(qkv, qw, kw, pos, Hq, Hk, theta, eps, k_cache, v_cache, slot_mapping, write_k_out, c10::nullopt);
+  return qk_norm_rope_fwd(qkv, qw, kw, pos, Hq, Hk, theta, eps, k_cache, v_cache, slot_mapping, write_k_out, c10::nullopt, 128);
 }
 
 at::Tensor qk_norm_rope_bwd(const at::Tensor& dq, const at::Tensor& dk, const at::Tensor& dv, const at::Tensor& qkv,
                             const c10::optional<at::Tensor>& qw, const c10::optional<at::Tensor>& kw, const at::Tensor& pos,
                             const c10::optional<at::Tensor>& q_rstd, const c10::optional<at::Tensor>& k_rstd,
                             const c10::optional<at::Tensor>& dqw, const c10::optional<at::Tensor>& dkw, int64_t Hq, int64_t Hk,
-                            double theta, const c10::optional<at::Tensor>& inv_freq) {
+                            double theta, const c10::optional<at::Tensor>& inv_freq, int64_t rotary_dim) {
   CHECK_BF16(dq); CHECK_BF16(dk); CHECK_BF16(dv); CHECK_BF16(qkv);
+  TORCH_CHECK(rotary_dim == 128 || rotary_dim == 64, "rotary_dim must be 128 (whole head) or 64 (half of it)");
   if (inv_freq.has_value())
-    TORCH_CHECK(inv_freq->is_cuda() && inv_freq->scalar_type() == at::kFloat && inv_freq->numel() == 64 && inv_freq->is_contiguous(),
-                "inv_freq must be 64 contiguous fp32 values on the device");
+    TORCH_CHECK(inv_freq->is_cuda() && inv_freq->scalar_type() == at::kFloat && inv_freq->numel() == rotary_dim / 2 &&
+                    inv_freq->is_contiguous(),
+                "inv_freq must be rotary_dim / 2 contiguous fp32 values on the device");
   const c10::cuda::CUDAGuard guard(qkv.device());
   const int T = qkv.size(0);
   at::Tensor dqkv = at::empty_like(qkv);
   mb::qk_norm_rope_bwd(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), qkv.data_ptr(), opt_ptr<void>(qw), opt_ptr<void>(kw),
                        pos.data_ptr<int>(), opt_ptr<float>(q_rstd), opt_ptr<float>(k_rstd), dqkv.data_ptr(),
                        opt_ptr<float>(dqw), opt_ptr<float>(dkw), T, Hq, Hk, static_cast<float>(theta), qw.has_value(),
-                       cur_stream(), opt_ptr<float>(inv_freq));
+                       cur_stream(), opt_ptr<float>(inv_freq), static_cast<int>(rotary_dim));
   return dqkv;
 }
 
@@ -107,7 +111,7 @@ at::Tensor qk_norm_rope_bwd_plain(const at::Tensor& dq, const at::Tensor& dk, co
                                   const c10::optional<at::Tensor>& q_rstd, const c10::optional<at::Tensor>& k_rstd,
                                   const c10::optional<at::Tensor>& dqw, const c10::optional<at::Tensor>& dkw, int64_t Hq,
                                   int64_t Hk, double theta) {
-  return qk_norm_rope_bwd(dq, dk, dv, qkv, qw, kw, pos, q_rstd, k_rstd, dqw, dkw, Hq, Hk, theta, c10::nullopt);
+  return qk_norm_rope_bwd(dq, dk, dv, qkv, qw, kw, pos, q_rstd, k_rstd, dqw, dkw, Hq, Hk, theta, c10::nullopt, 128);
 }
 
 at::Tensor swiglu_fwd(const at::Tensor& in) {
@@ -304,7 +308,7 @@ void register_elementwise(pybind11::module_& m) {
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd_plain);
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd_plain);
-  m.def("qk_norm_rope_fwd_scaled", &qk_norm_rope_fwd);  // + inv_freq [64] fp32: scaled rotary embeddings
+  m.def("qk_norm_rope_fwd_scaled", &qk_norm_rope_fwd);  // + optional inv_freq table (scaled rotary embeddings), rotary_dim
   m.def("qk_norm_rope_bwd_scaled", &qk_norm_rope_bwd);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);

@@ -189,9 +189,18 @@ class B200Qwen3:
             raise RuntimeError(f"a miles_b200 kernel reported error status {code} (bounded wait expired)")
 
     # ------------------------------------------------------------------ MoE block
-    def _route(self, h2, router_w, replay_ids):
+    def _route(self, h2, router_w, replay_ids, bias=None):
         cfg, C = self.cfg, self.C
         logits = self.linear(h2, router_w, torch.float32)
+        if cfg.router_score == "sigmoid":
+            # GLM-4.5 / DeepSeek-V3 routing: a [T, E] problem, done with framework ops (ops/reference.py); what the
+            # backward needs is the logits, kept in the place of the softmax probabilities
+            from ..ops.reference import router_sigmoid_topk
+
+            ids, w, _ = router_sigmoid_topk(logits, cfg.moe_top_k, cfg.norm_topk_prob, bias, cfg.routed_scaling_factor,
+                                            cfg.n_group, cfg.topk_group, replay_ids)
+            self.launches += 8
+            return ids.contiguous(), w.contiguous(), logits
         rid = replay_ids.contiguous() if replay_ids is not None else None
         ids, w, probs = C.moe_router_topk(logits, rid, cfg.moe_top_k, cfg.norm_topk_prob, True)
         self.launches += 1
@@ -236,9 +245,15 @@ class B200Qwen3:
     def moe_forward(self, i, h2, replay_ids=None, record=None, keep=False, residual=None):
         cfg, P, C = self.cfg, self.store.params, self.C
         p = f"layers.{i}.moe."
-        ids, w, probs = self._route(h2, P[p + "router.weight"], replay_ids)
+        ids, w, probs = self._route(h2, P[p + "router.weight"], replay_ids, P.get(p + "router.bias"))
         if record is not None:
             record.append(ids)
+        if cfg.shared_expert_ffn and not (keep and residual is None):  # (the backward's recompute does not need the output)
+            # the shared expert sees every token: its output joins the residual that the combine adds
+            sh_gu = self.linear(h2, P[p + "shared.gate_up.weight"])
+            sh_y = self.linear(C.swiglu_fwd(sh_gu), P[p + "shared.down.weight"])
+            residual = sh_y.add_(residual) if residual is not None else sh_y
+            self.launches += 3
         if self.ep is not None:
             return self.ep.moe_forward(self, i, h2, ids, w, probs, keep, residual)
         use_mx = bool(getattr(self, "mx", None)) and not keep and h2.shape[0] > 32
@@ -258,7 +273,8 @@ class B200Qwen3:
         cfg, P, G, C = self.cfg, self.store.params, self.store.grads, self.C
         p = f"layers.{i}.moe."
         if self.ep is not None:
-            return self.ep.moe_backward(self, i, h2, dy, saved)
+            dh2 = self.ep.moe_backward(self, i, h2, dy, saved)
+            return self._shared_expert_bwd(i, h2, dy, dh2)
         plan, xp, gu, act, yp = saved
         w1, w2 = P[p + "w1"], P[p + "w2"]
         dyp, dw = C.moe_combine_bwd(dy, yp, plan.src, plan.num_tiles, plan.w)
@@ -266,6 +282,24 @@ class B200Qwen3:
         dh2 = C.moe_combine(dxp, plan.dest, None, h2.shape[0], cfg.moe_top_k)
         self.launches += 2
         dh2 = self._router_bwd(i, h2, dh2, plan.probs, plan.ids, plan.w, dw)
+        return self._shared_expert_bwd(i, h2, dy, dh2)
+
+    def _shared_expert_bwd(self, i, h2, dy, dh2):
+        """The shared expert's part of the MoE backward (recomputed from ``h2``): weight gradients, and its input gradient
+        added to ``dh2``."""
+        cfg, P, G, C = self.cfg, self.store.params, self.store.grads, self.C
+        if not cfg.shared_expert_ffn:
+            return dh2
+        p = f"layers.{i}.moe.shared."
+        wgu, wd = P[p + "gate_up.weight"], P[p + "down.weight"]
+        dyb = dy if dy.dtype == torch.bfloat16 else dy.to(torch.bfloat16)
+        gu = self.linear(h2, wgu)
+        act = C.swiglu_fwd(gu)
+        self.linear_wgrad(dyb, act, G[p + "down.weight"])
+        dgu = C.swiglu_bwd(self.linear_dgrad(dyb, wd), gu)
+        self.linear_wgrad(dgu, h2, G[p + "gate_up.weight"])
+        self._gemm(dgu, wgu, dh2, False, True, True)  # dh2 += dgu . W
+        self.launches += 7
         return dh2
 
     def _experts_bwd(self, dyp, xp, gu, act, plan, w1, w2, gw1, gw2, scatter=None):
@@ -288,7 +322,18 @@ class B200Qwen3:
     def _router_bwd(self, i, h2, dh2, probs, ids, w, dw):
         cfg, P, G, C = self.cfg, self.store.params, self.store.grads, self.C
         p = f"layers.{i}.moe."
-        dlogits = C.moe_router_bwd(probs, ids, w, dw, cfg.norm_topk_prob).to(torch.bfloat16)
+        if cfg.router_score == "sigmoid":
+            # ``probs`` holds the router logits (see _route): differentiate the [T, E] routing function with autograd
+            from ..ops.reference import router_sigmoid_topk
+
+            with torch.enable_grad():
+                lg = probs.detach().requires_grad_(True)
+                _, w2, _ = router_sigmoid_topk(lg, cfg.moe_top_k, cfg.norm_topk_prob, None, cfg.routed_scaling_factor, 1, 1, ids)
+                (dlogits,) = torch.autograd.grad(w2, lg, dw.to(w2.dtype))
+            dlogits = dlogits.to(torch.bfloat16)
+            self.launches += 10
+        else:
+            dlogits = C.moe_router_bwd(probs, ids, w, dw, cfg.norm_topk_prob).to(torch.bfloat16)
         self._gemm(dlogits, P[p + "router.weight"], dh2, False, True, True)
         self.linear_wgrad(dlogits, h2, G[p + "router.weight"])
         self.launches += 1
@@ -307,10 +352,10 @@ class B200Qwen3:
             kc, vc = kv_cache[i]
             slots = meta.slot_mapping
         write_k = meta is None or meta.is_prefill
-        if cfg.rope_scaling:
+        if cfg.rope_scaling or cfg.rotary_dim:
             q, k, qr, kr = C.qk_norm_rope_fwd_scaled(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"),
                                                      positions, cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps,
-                                                     kc, vc, slots, write_k, self._rope_table())
+                                                     kc, vc, slots, write_k, self._rope_table(), cfg.rotary_dim or cfg.head_dim)
         else:
             q, k, qr, kr = C.qk_norm_rope_fwd(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"), positions,
                                               cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps, kc, vc, slots,
@@ -318,13 +363,17 @@ class B200Qwen3:
         self.launches += 2
         return h1, rstd1, qkv, q, k, qr, kr
 
-    def _rope_table(self) -> torch.Tensor:
-        """The 64 inverse frequencies of a model with scaled rotary embeddings (fp32, on the device)."""
+    def _rope_table(self) -> Optional[torch.Tensor]:
+        """The inverse frequencies of a model with scaled rotary embeddings (fp32, on the device); None without scaling
+        (the kernels then compute theta^(-d / half) themselves)."""
+        if not self.cfg.rope_scaling:
+            return None
         t = getattr(self, "_inv_freq", None)
         if t is None:
             from ..ops.reference import rope_inv_freq
 
-            t = self._inv_freq = rope_inv_freq(self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling, self.dev).contiguous()
+            t = self._inv_freq = rope_inv_freq(self.cfg.rotary_dim or self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling,
+                                               self.dev).contiguous()
         return t
 
     def _v_view(self, qkv):
@@ -338,11 +387,13 @@ class B200Qwen3:
         p = f"layers.{i}."
         if (meta is not None and not meta.is_prefill and x.shape[0] <= self.SMALL_T and replay_ids is None
                 and self.small_decode and self.tp is None):
-            if self.ep is None or not cfg.layer_is_moe(i):
+            # the fused few-row MoE kernels serve plain softmax routers whose expert count fits their 16-column tiles
+            plain_moe = cfg.router_score == "softmax" and not cfg.shared_expert_ffn and cfg.num_experts % 16 == 0
+            if (self.ep is None and plain_moe) or not cfg.layer_is_moe(i):
                 return self._layer_forward_small(i, x, positions, meta, kv_cache, record)
             # expert-parallel MoE: the attention half still takes the light kernels, the experts go through the exchange
             x2 = self._attn_small(i, x, positions, meta, kv_cache)
-            if getattr(self.ep, "low_latency", False):
+            if getattr(self.ep, "low_latency", False) and plain_moe:
                 return self.ep.moe_decode(self, i, x2, None, record)
             h2, _ = C.rmsnorm_fwd(x2, None, P[p + "ln2.weight"], cfg.rms_eps)
             self.launches += 1
@@ -372,7 +423,7 @@ class B200Qwen3:
         h2, _, x2 = self._o_proj_ln2(i, att.view(att.shape[0], -1), x)
         if cfg.layer_is_moe(i):
             if (meta is not None and not meta.is_prefill and replay_ids is None and getattr(self.ep, "low_latency", False)
-                    and x.shape[0] <= self.ep.rows):
+                    and x.shape[0] <= self.ep.rows and cfg.router_score == "softmax" and not cfg.shared_expert_ffn):
                 return self.ep.moe_decode(self, i, x2, h2, record)
             y, _ = self.moe_forward(i, h2, replay_ids, record, keep=False, residual=x2)
             return y
@@ -422,10 +473,11 @@ class B200Qwen3:
         if cfg.qkv_bias:
             qkv += P[p + "attn.qkv.bias"]
         kc, vc = kv_cache[i]
-        if cfg.rope_scaling:
+        if cfg.rope_scaling or cfg.rotary_dim:
             q, _, _, _ = C.qk_norm_rope_fwd_scaled(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"),
                                                    positions, cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps,
-                                                   kc, vc, meta.slot_mapping, False, self._rope_table())
+                                                   kc, vc, meta.slot_mapping, False, self._rope_table(),
+                                                   cfg.rotary_dim or cfg.head_dim)
         else:
             q, _, _, _ = C.qk_norm_rope_fwd(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"), positions,
                                             cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta, cfg.rms_eps, kc, vc,
@@ -520,11 +572,11 @@ class B200Qwen3:
         datt = self.linear_dgrad(dx2, P[p + "attn.o.weight"])
         self.linear_wgrad(dx2, att2, G[p + "attn.o.weight"])
         dq, dk, dv = self.attention_backward(q, k, v, att, datt.view_as(att), lse, cu)
-        if cfg.rope_scaling:
+        if cfg.rope_scaling or cfg.rotary_dim:
             dqkv = C.qk_norm_rope_bwd_scaled(dq, dk, dv, qkv, P.get(p + "attn.q_norm.weight"),
                                              P.get(p + "attn.k_norm.weight"), positions, qr, kr, G.get(p + "attn.q_norm.weight"),
                                              G.get(p + "attn.k_norm.weight"), cfg.num_q_heads, cfg.num_kv_heads, cfg.rope_theta,
-                                             self._rope_table())
+                                             self._rope_table(), cfg.rotary_dim or cfg.head_dim)
         else:
             dqkv = C.qk_norm_rope_bwd(dq, dk, dv, qkv, P.get(p + "attn.q_norm.weight"),
                                       P.get(p + "attn.k_norm.weight"), positions, qr, kr, G.get(p + "attn.q_norm.weight"),

@@ -35,6 +35,18 @@ class ModelConfig:
     norm_topk_prob: bool = True
     moe_layer_freq: int = 1  # every n-th layer is MoE (1 = all)
     first_dense_layers: int = 0
+    # router variants (GLM-4.5 / DeepSeek-V3 style): scores = sigmoid(logits); experts are chosen by score + a per-expert
+    # bias (not trained by gradients), optionally inside the best ``topk_group`` of ``n_group`` expert groups; the
+    # weights are the chosen scores (renormalised when norm_topk_prob) times ``routed_scaling_factor``
+    router_score: str = "softmax"  # "softmax" | "sigmoid"
+    router_bias: bool = False
+    routed_scaling_factor: float = 1.0
+    n_group: int = 1
+    topk_group: int = 1
+    # a dense SwiGLU expert of this width that every token passes through, added to the routed experts' output
+    shared_expert_ffn: int = 0
+    # rotary embedding on the first ``rotary_dim`` dimensions of every head only (0 = all of them)
+    rotary_dim: int = 0
     max_position_embeddings: int = 40960
     # scaled rotary embeddings: None, {"rope_type": "llama3", "factor", "low_freq_factor", "high_freq_factor",
     # "original_max_position_embeddings"} or {"rope_type": "linear", "factor"}
@@ -70,8 +82,9 @@ class ModelConfig:
             if self.qkv_bias:
                 n += self.qkv_dim
             if self.layer_is_moe(i):
-                n += self.num_experts * self.hidden_size
+                n += self.num_experts * self.hidden_size + (self.num_experts if self.router_bias else 0)
                 n += self.num_experts * 3 * self.moe_ffn_hidden_size * self.hidden_size
+                n += 3 * self.shared_expert_ffn * self.hidden_size
             else:
                 n += 3 * self.ffn_hidden_size * self.hidden_size
         return n
@@ -114,7 +127,14 @@ class ModelConfig:
         }
         if self.rope_scaling:
             cfg["rope_scaling"] = dict(self.rope_scaling)
-        if self.family == "mixtral":
+        if self.family == "glm4_moe":
+            cfg.update({"n_routed_experts": self.num_experts, "num_experts_per_tok": self.moe_top_k,
+                        "moe_intermediate_size": self.moe_ffn_hidden_size, "norm_topk_prob": self.norm_topk_prob,
+                        "n_shared_experts": self.shared_expert_ffn // max(self.moe_ffn_hidden_size, 1),
+                        "routed_scaling_factor": self.routed_scaling_factor, "n_group": self.n_group, "topk_group": self.topk_group,
+                        "first_k_dense_replace": self.first_dense_layers, "use_qk_norm": self.qk_norm,
+                        "partial_rotary_factor": (self.rotary_dim or self.head_dim) / self.head_dim})
+        elif self.family == "mixtral":
             cfg.update({"num_local_experts": self.num_experts, "num_experts_per_tok": self.moe_top_k,
                         "intermediate_size": self.moe_ffn_hidden_size, "sliding_window": None})
         elif self.is_moe:
@@ -144,7 +164,11 @@ class ModelConfig:
                                       f"{', '.join(sorted(HF_FAMILIES))}")
         is_qwen3 = "qwen3" in mtype
         mlp_only = cfg.get("mlp_only_layers") or []
-        n_experts = cfg.get("num_experts", 0) or cfg.get("num_local_experts", 0) or 0
+        n_experts = cfg.get("num_experts", 0) or cfg.get("num_local_experts", 0) or cfg.get("n_routed_experts", 0) or 0
+        glm = mtype == "glm4_moe"
+        prf = cfg.get("partial_rotary_factor") or (cfg.get("rope_parameters") or {}).get("partial_rotary_factor") or 1.0
+        if not glm and float(prf) != 1.0:
+            raise NotImplementedError(f"partial rotary embedding is wired for glm4_moe only (got {prf} for {mtype})")
         moe_ffn = cfg.get("moe_intermediate_size", 0) or (cfg.get("intermediate_size", 0) if mtype == "mixtral" else 0)
         if cfg.get("sliding_window") and cfg.get("use_sliding_window", mtype != "qwen2" and not is_qwen3) \
                 and cfg["sliding_window"] < cfg.get("max_position_embeddings", 0):
@@ -173,7 +197,7 @@ class ModelConfig:
             rms_eps=cfg.get("rms_norm_eps", 1e-6),
             # newer HuggingFace configs keep the base inside "rope_parameters"; 10000 is the library-wide default
             rope_theta=float(cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta") or 10000.0),
-            qk_norm=is_qwen3,
+            qk_norm=bool(cfg.get("use_qk_norm", False)) if glm else is_qwen3,
             qkv_bias=bool(cfg.get("attention_bias", not is_qwen3 and "qwen2" in mtype)),
             tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
             num_experts=n_experts,
@@ -182,7 +206,12 @@ class ModelConfig:
             # Mixtral takes the softmax over the chosen experts only, which equals renormalising the full softmax
             norm_topk_prob=True if mtype == "mixtral" else bool(cfg.get("norm_topk_prob", True)),
             moe_layer_freq=cfg.get("decoder_sparse_step", 1) or 1,
-            first_dense_layers=(max(mlp_only) + 1) if mlp_only else 0,
+            first_dense_layers=int(cfg.get("first_k_dense_replace", 0) or 0) if glm else ((max(mlp_only) + 1) if mlp_only else 0),
+            router_score="sigmoid" if glm else "softmax", router_bias=glm,
+            routed_scaling_factor=float(cfg.get("routed_scaling_factor", 1.0) or 1.0) if glm else 1.0,
+            n_group=int(cfg.get("n_group", 1) or 1) if glm else 1, topk_group=int(cfg.get("topk_group", 1) or 1) if glm else 1,
+            shared_expert_ffn=(int(cfg.get("n_shared_experts", 0) or 0) * moe_ffn) if glm else 0,
+            rotary_dim=int(round(head_dim * float(prf))) if float(prf) != 1.0 else 0,
             max_position_embeddings=cfg.get("max_position_embeddings", 40960),
             rope_scaling=scaling,
             hf_architecture=arch,
@@ -193,6 +222,7 @@ class ModelConfig:
 HF_FAMILIES = {
     "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3_moe", "Qwen2ForCausalLM": "qwen2", "LlamaForCausalLM": "llama",
     "MistralForCausalLM": "mistral", "MixtralForCausalLM": "mixtral", "MiMoForCausalLM": "mimo",
+    "Glm4MoeForCausalLM": "glm4_moe",
 }
 
 
@@ -268,6 +298,25 @@ PRESETS: dict[str, ModelConfig] = {
                                  ffn_hidden_size=16384, vocab_size=32768, rms_eps=1e-5, rope_theta=1e6, qk_norm=False, num_experts=8,
                                  moe_top_k=2, moe_ffn_hidden_size=16384, max_position_embeddings=65536,
                                  hf_architecture="MixtralForCausalLM"),
+    # GLM-4.5: sigmoid router with a selection bias, one shared expert, rotary embedding on half of every head, a dense
+    # first layer (their multi-token-prediction layer is not trained here)
+    "glm4.5-106B-A12B": ModelConfig(name="glm4.5-106B-A12B", num_layers=46, hidden_size=4096, num_q_heads=96, num_kv_heads=8,
+                                    head_dim=128, ffn_hidden_size=10944, vocab_size=151552, rms_eps=1e-5, rope_theta=1e6,
+                                    qk_norm=False, qkv_bias=True, num_experts=128, moe_top_k=8, moe_ffn_hidden_size=1408,
+                                    first_dense_layers=1, router_score="sigmoid", router_bias=True, routed_scaling_factor=1.0,
+                                    shared_expert_ffn=1408, rotary_dim=64, max_position_embeddings=131072,
+                                    hf_architecture="Glm4MoeForCausalLM"),
+    "glm4.5-355B-A32B": ModelConfig(name="glm4.5-355B-A32B", num_layers=92, hidden_size=5120, num_q_heads=96, num_kv_heads=8,
+                                    head_dim=128, ffn_hidden_size=12288, vocab_size=151552, rms_eps=1e-5, rope_theta=1e6,
+                                    qk_norm=True, qkv_bias=True, num_experts=160, moe_top_k=8, moe_ffn_hidden_size=1536,
+                                    first_dense_layers=3, router_score="sigmoid", router_bias=True, routed_scaling_factor=2.5,
+                                    shared_expert_ffn=1536, rotary_dim=64, max_position_embeddings=131072,
+                                    hf_architecture="Glm4MoeForCausalLM"),
+    "glm4moe-smoke": ModelConfig(name="glm4moe-smoke", num_layers=3, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                                 ffn_hidden_size=1024, vocab_size=4096, rms_eps=1e-5, rope_theta=1e6, qk_norm=True, qkv_bias=True,
+                                 num_experts=16, moe_top_k=4, moe_ffn_hidden_size=256, first_dense_layers=1, router_score="sigmoid",
+                                 router_bias=True, routed_scaling_factor=2.5, shared_expert_ffn=256, rotary_dim=64,
+                                 hf_architecture="Glm4MoeForCausalLM"),
     # names of the reference's per-model argument files (scripts/models/*.py) for shapes already covered above
     "qwen3-4B-Instruct-2507": _dense("qwen3-4B-Instruct-2507", 36, 2560, 32, 8, 9728, True, rope_theta=5e6),
     "qwen3-30B-A3B-5layer": _moe("qwen3-30B-A3B-5layer", 5, 2048, 32, 4, 128, 8, 768),

@@ -14,6 +14,7 @@ Native parameter names::
     layers.i.attn.q_norm.weight [D]           layers.i.attn.k_norm.weight [D]
     layers.i.mlp.gate_up.weight [2I,H]        layers.i.mlp.down.weight [H,I]
     layers.i.moe.router.weight [E,H]          layers.i.moe.w1 [E_local,2I,H]   layers.i.moe.w2 [E_local,H,I]
+    layers.i.moe.router.bias [E] (sigmoid routers)     layers.i.moe.shared.gate_up.weight [2Is,H]   ...shared.down.weight [H,Is]
 
 The fused layouts (q|k|v rows, gate|up rows) are what the fused kernels consume; ``hf_mapping`` converts
 to and from HuggingFace names, the role that megatron_to_hf/qwen3moe.py:6-117 plays in the reference.
@@ -76,6 +77,12 @@ def build_specs(cfg: ModelConfig, ep_size: int = 1, layers: Optional[tuple] = No
             el = cfg.num_experts // ep_size
             I = cfg.moe_ffn_hidden_size
             specs.append(ParamSpec(p + "moe.router.weight", (cfg.num_experts, H), "dense", "normal"))
+            if getattr(cfg, "router_bias", False):
+                specs.append(ParamSpec(p + "moe.router.bias", (cfg.num_experts,), "dense", "zeros"))  # selection only: no gradient
+            if getattr(cfg, "shared_expert_ffn", 0):
+                Is = cfg.shared_expert_ffn
+                specs.append(ParamSpec(p + "moe.shared.gate_up.weight", (2 * Is, H), "dense", "normal"))
+                specs.append(ParamSpec(p + "moe.shared.down.weight", (H, Is), "dense", "normal"))
             specs.append(ParamSpec(p + "moe.w1", (el, 2 * I, H), "expert", "normal"))
             specs.append(ParamSpec(p + "moe.w2", (el, H, I), "expert", "normal"))
         else:

@@ -89,12 +89,13 @@ class TorchQwen3:
         h = R.rmsnorm(x, P[p + "ln1.weight"], cfg.rms_eps)
         qkv = F.linear(h, P[p + "attn.qkv.weight"], P.get(p + "attn.qkv.bias"))
         inv_freq = None
+        rdim = getattr(cfg, "rotary_dim", 0)
         if cfg.rope_scaling:
             if getattr(self, "_inv_freq", None) is None or self._inv_freq.device != qkv.device:
-                self._inv_freq = R.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling, qkv.device)
+                self._inv_freq = R.rope_inv_freq(rdim or cfg.head_dim, cfg.rope_theta, cfg.rope_scaling, qkv.device)
             inv_freq = self._inv_freq
         q, k, v = R.qk_norm_rope(qkv, P.get(p + "attn.q_norm.weight"), P.get(p + "attn.k_norm.weight"), positions,
-                                 cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rope_theta, cfg.rms_eps, inv_freq)
+                                 cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rope_theta, cfg.rms_eps, inv_freq, rdim)
         scale = cfg.head_dim ** -0.5
         if meta is None or meta.is_prefill:
             if kv_cache is not None:
@@ -148,10 +149,16 @@ class TorchQwen3:
         h = R.rmsnorm(x, P[p + "ln2.weight"], cfg.rms_eps)
         if cfg.layer_is_moe(i):
             logits = F.linear(h.float(), P[p + "moe.router.weight"].float())
-            ids, w, _ = R.router_topk(logits, cfg.moe_top_k, cfg.norm_topk_prob, replay_ids)
+            if getattr(cfg, "router_score", "softmax") == "sigmoid":
+                ids, w, _ = R.router_sigmoid_topk(logits, cfg.moe_top_k, cfg.norm_topk_prob, P.get(p + "moe.router.bias"),
+                                                  cfg.routed_scaling_factor, cfg.n_group, cfg.topk_group, replay_ids)
+            else:
+                ids, w, _ = R.router_topk(logits, cfg.moe_top_k, cfg.norm_topk_prob, replay_ids)
             if record is not None:
                 record.append(ids)
             y = R.moe_experts(h, ids, w.to(h.dtype) if h.dtype != torch.float32 else w, P[p + "moe.w1"], P[p + "moe.w2"])
+            if getattr(cfg, "shared_expert_ffn", 0):
+                y = y + F.linear(R.swiglu(F.linear(h, P[p + "moe.shared.gate_up.weight"])), P[p + "moe.shared.down.weight"])
         else:
             y = F.linear(R.swiglu(F.linear(h, P[p + "mlp.gate_up.weight"])), P[p + "mlp.down.weight"])
         return x + y

@@ -48,7 +48,11 @@ def rope_cos_sin(pos: torch.Tensor, dim: int, theta: float, inv_freq: Optional[t
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """x: [T, H, D]; rotate-half convention (first half pairs with second half)."""
+    """x: [T, H, D]; rotate-half convention (first half pairs with second half). When ``cos`` covers fewer than D / 2
+    frequencies only the first ``2 * cos.shape[-1]`` dimensions of every head are rotated (partial rotary embedding)."""
+    if 2 * cos.shape[-1] < x.shape[-1]:
+        r = 2 * cos.shape[-1]
+        return torch.cat([apply_rope(x[..., :r], cos, sin), x[..., r:]], dim=-1)
     d = x.shape[-1] // 2
     xf = x.float()
     x1, x2 = xf[..., :d], xf[..., d:]
@@ -57,15 +61,17 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
 
 
 def qk_norm_rope(qkv: torch.Tensor, qw: Optional[torch.Tensor], kw: Optional[torch.Tensor], pos: torch.Tensor,
-                 Hq: int, Hk: int, D: int, theta: float, eps: float, inv_freq: Optional[torch.Tensor] = None):
-    """qkv [T, (Hq+2Hk)*D] -> q [T,Hq,D], k [T,Hk,D], v [T,Hk,D]. ``inv_freq``: see :func:`rope_inv_freq`."""
+                 Hq: int, Hk: int, D: int, theta: float, eps: float, inv_freq: Optional[torch.Tensor] = None,
+                 rotary_dim: int = 0):
+    """qkv [T, (Hq+2Hk)*D] -> q [T,Hq,D], k [T,Hk,D], v [T,Hk,D]. ``inv_freq``: see :func:`rope_inv_freq`;
+    ``rotary_dim``: rotate only the first ``rotary_dim`` dimensions of every head (0 = all)."""
     T = qkv.shape[0]
     v3 = qkv.view(T, Hq + 2 * Hk, D)
     q, k, v = v3[:, :Hq], v3[:, Hq:Hq + Hk], v3[:, Hq + Hk:]
     if qw is not None:
         q = rmsnorm(q, qw, eps)
         k = rmsnorm(k, kw, eps)
-    cos, sin = rope_cos_sin(pos, D, theta, inv_freq)
+    cos, sin = rope_cos_sin(pos, rotary_dim or D, theta, inv_freq)
     return apply_rope(q, cos, sin), apply_rope(k, cos, sin), v
 
 
@@ -124,6 +130,31 @@ def router_topk(logits: torch.Tensor, K: int, renorm: bool, replay_ids: Optional
     if renorm:
         w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
     return ids.to(torch.int32), w, probs
+
+
+def router_sigmoid_topk(logits: torch.Tensor, K: int, renorm: bool, bias: Optional[torch.Tensor] = None, scaling: float = 1.0,
+                        n_group: int = 1, topk_group: int = 1, replay_ids: Optional[torch.Tensor] = None):
+    """GLM-4.5 / DeepSeek-V3 routing. fp32 logits [T,E] -> ids int32 [T,K], weights fp32 [T,K], scores [T,E].
+    ``scores = sigmoid(logits)``; experts are *chosen* by ``scores + bias`` (inside the ``topk_group`` groups whose two
+    best biased scores add up highest, when ``n_group > 1``); the *weights* are the unbiased scores of the chosen experts,
+    renormalised to sum to one when ``renorm``, times ``scaling``. Differentiable in ``logits`` through the weights."""
+    scores = torch.sigmoid(logits.float())
+    if replay_ids is not None:
+        ids = replay_ids.long().clamp(0, logits.shape[1] - 1)
+    else:
+        with torch.no_grad():
+            choice = scores + bias.float() if bias is not None else scores.clone()
+            if n_group > 1:
+                T, E = choice.shape
+                grouped = choice.view(T, n_group, E // n_group)
+                best = grouped.topk(2, dim=-1)[0].sum(-1)
+                keep = torch.zeros_like(best).scatter_(1, best.topk(topk_group, dim=-1)[1], 1.0)
+                choice = choice.masked_fill(~keep.bool()[:, :, None].expand_as(grouped).reshape(T, E), 0.0)
+            ids = torch.topk(choice, K, dim=-1, sorted=True)[1]
+    w = scores.gather(1, ids)
+    if renorm:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return ids.to(torch.int32), w * scaling, scores
 
 
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, w: torch.Tensor, W1: torch.Tensor, W2: torch.Tensor) -> torch.Tensor:

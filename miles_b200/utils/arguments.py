@@ -125,7 +125,6 @@ TRAINER_FLAGS = [
 
 _UNBUILT = {
     "multi_latent_attention": "multi-latent attention models (DeepSeek / Kimi / GLM-5 families)",
-    "moe_router_enable_expert_bias": "aux-loss-free expert-bias routing",
 }
 
 
@@ -425,6 +424,9 @@ def validate_args(args: argparse.Namespace) -> argparse.Namespace:
     _default(args, "sglang_mem_fraction_static", 0.7 if args.colocate else 0.85)
     _default(args, "sglang_max_running_requests", None)
     _default(args, "sglang_server_concurrency", 512)
+    if getattr(args, "model_preset", None) or (getattr(args, "hf_checkpoint", None)
+                                               and os.path.exists(os.path.join(args.hf_checkpoint, "config.json"))):
+        model_config_from_args(args)  # fails now, not after the cluster is up, when the flags and the model disagree
     return args
 
 
@@ -459,18 +461,61 @@ def hf_validate_args(args, hf_config: dict) -> None:
         raise AssertionError("model shape flags contradict the HF checkpoint: " + "; ".join(errors))
 
 
+def _first_dense_layers(freq, num_layers: int) -> int:
+    """Megatron's ``--moe-layer-freq`` as a pattern (``"[0]*1+[1]*45"`` or a list): how many leading layers are dense."""
+    if isinstance(freq, str) and "[" in freq:
+        pattern = eval(freq, {"__builtins__": {}})  # noqa: S307 - an arithmetic list expression from the launch script
+    elif isinstance(freq, (list, tuple)):
+        pattern = list(freq)
+    else:
+        return 0
+    n = 0
+    for v in pattern[:num_layers]:
+        if v:
+            break
+        n += 1
+    assert all(pattern[n:num_layers]), "--moe-layer-freq: dense layers are supported at the start of the stack only"
+    return n
+
+
+def _check_architecture_flags(args, cfg):
+    """The model comes from a preset or a checkpoint: architecture flags that were given and say something else would
+    otherwise be dropped without a word (and the job would train another model than the command line describes)."""
+    moe = cfg.is_moe
+    given = [("moe_router_score_function", cfg.router_score if moe else "softmax", "softmax"),
+             ("moe_router_enable_expert_bias", bool(cfg.router_bias), False),
+             ("moe_shared_expert_intermediate_size", cfg.shared_expert_ffn or None, None),
+             ("moe_router_topk_scaling_factor", cfg.routed_scaling_factor if cfg.routed_scaling_factor != 1.0 else None, None),
+             ("moe_router_num_groups", cfg.n_group if cfg.n_group != 1 else None, None),
+             ("moe_router_group_topk", cfg.topk_group if cfg.n_group != 1 else None, None),
+             ("rotary_percent", (cfg.rotary_dim or cfg.head_dim) / cfg.head_dim, 1.0),
+             ("use_rope_scaling", bool(cfg.rope_scaling), False)]
+    bad = []
+    for flag, have, default in given:
+        v = getattr(args, flag, default)
+        if v in (None, default) or v == have:
+            continue
+        if isinstance(v, float) and have is not None and abs(float(v) - float(have)) < 1e-9:
+            continue
+        bad.append(f"--{flag.replace('_', '-')} {v!r} (the model has {have!r})")
+    if bad:
+        raise NotImplementedError(f"model {cfg.name!r} does not match the architecture flags: " + "; ".join(bad) +
+                                  ". The flags describe a model only together with the --num-layers / --hidden-size / ... shape flags")
+    return cfg
+
+
 def model_config_from_args(args):
     """Build a ``ModelConfig`` from a preset, an HF checkpoint dir, or Megatron-style shape flags."""
     from ..models.config import ModelConfig, get_config
 
     if getattr(args, "model_preset", None):
-        return get_config(args.model_preset)
+        return _check_architecture_flags(args, get_config(args.model_preset))
     if getattr(args, "hf_checkpoint", None) and os.path.exists(os.path.join(args.hf_checkpoint, "config.json")):
         import json
 
         with open(os.path.join(args.hf_checkpoint, "config.json")) as f:
             hf_validate_args(args, json.load(f))
-        return ModelConfig.from_hf_config(args.hf_checkpoint)
+        return _check_architecture_flags(args, ModelConfig.from_hf_config(args.hf_checkpoint))
     assert args.num_layers and args.hidden_size and args.num_attention_heads, \
         "model shape needs --model-preset, --hf-checkpoint or the --num-layers/--hidden-size/... flags"
     heads = args.num_attention_heads
@@ -484,7 +529,17 @@ def model_config_from_args(args):
         qkv_bias=bool(args.add_qkv_bias), tie_embeddings=not args.untie_embeddings_and_output_weights,
         num_experts=args.num_experts or 0, moe_top_k=args.moe_router_topk if moe else 0,
         moe_ffn_hidden_size=(args.moe_ffn_hidden_size or 0) if moe else 0,
-        hf_architecture="Qwen3MoeForCausalLM" if moe else "Qwen3ForCausalLM",
+        hf_architecture=("Glm4MoeForCausalLM" if getattr(args, "moe_router_score_function", "softmax") == "sigmoid"
+                         else "Qwen3MoeForCausalLM") if moe else "Qwen3ForCausalLM",
+        # GLM-4.5 / DeepSeek-V3 style routing and shared experts (Megatron flag names)
+        router_score=getattr(args, "moe_router_score_function", "softmax") if moe else "softmax",
+        router_bias=bool(getattr(args, "moe_router_enable_expert_bias", False)) and moe,
+        routed_scaling_factor=float(getattr(args, "moe_router_topk_scaling_factor", None) or 1.0),
+        n_group=int(getattr(args, "moe_router_num_groups", None) or 1), topk_group=int(getattr(args, "moe_router_group_topk", None) or 1),
+        shared_expert_ffn=int(getattr(args, "moe_shared_expert_intermediate_size", None) or 0) if moe else 0,
+        first_dense_layers=_first_dense_layers(getattr(args, "moe_layer_freq", "1"), args.num_layers) if moe else 0,
+        rotary_dim=(int(round((args.kv_channels or args.hidden_size // heads) * float(args.rotary_percent)))
+                    if float(getattr(args, "rotary_percent", 1.0) or 1.0) != 1.0 else 0),
         # Megatron's --use-rope-scaling is the Llama-3.1 recipe with --rotary-scaling-factor (default 8)
         rope_scaling=({"rope_type": "llama3", "factor": float(args.rotary_scaling_factor or 8.0), "low_freq_factor": 1.0,
                        "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}

@@ -27,7 +27,6 @@ REJECT = {
     "normalization": "normalisation other than RMSNorm",
     "position_embedding_type": "position embeddings other than rotary",
     "no_position_embedding": "models without rotary position embedding",
-    "rotary_percent": "partial rotary embedding",
     "original_max_position_embeddings": "YaRN rope scaling",
     "beta_fast": "YaRN rope scaling",
     "beta_slow": "YaRN rope scaling",
@@ -38,16 +37,11 @@ REJECT = {
     "qk_head_dim": "multi-latent attention",
     "qk_pos_emb_head_dim": "multi-latent attention",
     "v_head_dim": "multi-latent attention",
-    "moe_router_score_function": "router score functions other than softmax",
     "moe_router_pre_softmax": "softmax before the top-k over all experts is the only router order built",
-    "moe_router_group_topk": "group-limited routing",
-    "moe_router_num_groups": "group-limited routing",
-    "moe_router_topk_scaling_factor": "scaled top-k routing weights",
-    "moe_router_bias_update_rate": "aux-loss-free expert-bias routing",
+    "moe_router_bias_update_rate": "updating the router's selection bias from the expert load (the bias is loaded and kept)",
     "moe_router_load_balancing_type": "router load-balancing losses",
     "moe_aux_loss_coeff": "router auxiliary loss",
-    "moe_shared_expert_intermediate_size": "shared experts",
-    "moe_shared_expert_gate": "shared experts",
+    "moe_shared_expert_gate": "a gate on the shared expert's output (Qwen2-MoE style)",
     "moe_latent_size": "latent MoE",
     "moe_token_drop_policy": "token dropping (the dispatch here is dropless)",
     "mtp_num_layers": "multi-token-prediction layers",

@@ -85,7 +85,7 @@ def test_scaled_rotary_embedding_forward_and_backward(ext, scaling):
     assert not torch.allclose(inv, R.rope_inv_freq(D, theta, None, DEV))
     qkv = torch.randn(T, (Hq + 2 * Hk) * D, device=DEV).bfloat16()
     pos = torch.randint(0, 9000, (T,), device=DEV, dtype=torch.int32)
-    q, k, _, _ = ext.qk_norm_rope_fwd_scaled(qkv, None, None, pos, Hq, Hk, theta, eps, None, None, None, True, inv)
+    q, k, _, _ = ext.qk_norm_rope_fwd_scaled(qkv, None, None, pos, Hq, Hk, theta, eps, None, None, None, True, inv, 128)
     qkv_f = qkv.float().requires_grad_(True)
     q_ref, k_ref, v_ref = R.qk_norm_rope(qkv_f, None, None, pos, Hq, Hk, D, theta, eps, inv)
     _close(q, q_ref, 2e-2, 2e-2)
@@ -95,8 +95,39 @@ def test_scaled_rotary_embedding_forward_and_backward(ext, scaling):
     dq, dk = torch.randn_like(q), torch.randn_like(k)
     dv = torch.randn(T, Hk, D, device=DEV).bfloat16()
     (q_ref * dq.float()).sum().add((k_ref * dk.float()).sum()).add((v_ref * dv.float()).sum()).backward()
-    dqkv = ext.qk_norm_rope_bwd_scaled(dq, dk, dv, qkv, None, None, pos, None, None, None, None, Hq, Hk, theta, inv)
+    dqkv = ext.qk_norm_rope_bwd_scaled(dq, dk, dv, qkv, None, None, pos, None, None, None, None, Hq, Hk, theta, inv, 128)
     _close(dqkv, qkv_f.grad, 2e-2, 3e-2)
+
+
+@pytest.mark.parametrize("use_norm", [True, False])
+def test_partial_rotary_embedding_forward_and_backward(ext, use_norm):
+    """Rotary embedding on the first 64 dimensions of every head only (GLM-4.5): d pairs with d + 32, the rest passes."""
+    torch.manual_seed(5)
+    T, Hq, Hk, D, theta, eps = 301, 8, 2, 128, 1e6, 1e-5
+    qkv = torch.randn(T, (Hq + 2 * Hk) * D, device=DEV).bfloat16()
+    pos = torch.randint(0, 9000, (T,), device=DEV, dtype=torch.int32)
+    qw = (torch.randn(D, device=DEV) * 0.1 + 1).bfloat16() if use_norm else None
+    kw = (torch.randn(D, device=DEV) * 0.1 + 1).bfloat16() if use_norm else None
+    q, k, qr, kr = ext.qk_norm_rope_fwd_scaled(qkv, qw, kw, pos, Hq, Hk, theta, eps, None, None, None, True, None, 64)
+    qkv_f = qkv.float().requires_grad_(True)
+    qwf = qw.float().requires_grad_(True) if use_norm else None
+    kwf = kw.float().requires_grad_(True) if use_norm else None
+    q_ref, k_ref, v_ref = R.qk_norm_rope(qkv_f, qwf, kwf, pos, Hq, Hk, D, theta, eps, None, 64)
+    _close(q, q_ref, 2e-2, 2e-2)
+    _close(k, k_ref, 2e-2, 2e-2)
+    if not use_norm:  # the upper half of every head passes through untouched
+        assert torch.equal(q[..., 64:], qkv.view(T, Hq + 2 * Hk, D)[:, :Hq, 64:])
+    dq, dk = torch.randn_like(q), torch.randn_like(k)
+    dv = torch.randn(T, Hk, D, device=DEV).bfloat16()
+    (q_ref * dq.float()).sum().add((k_ref * dk.float()).sum()).add((v_ref * dv.float()).sum()).backward()
+    dqw = torch.zeros(D, device=DEV) if use_norm else None
+    dkw = torch.zeros(D, device=DEV) if use_norm else None
+    dqkv = ext.qk_norm_rope_bwd_scaled(dq, dk, dv, qkv, qw, kw, pos, qr if use_norm else None, kr if use_norm else None, dqw, dkw,
+                                       Hq, Hk, theta, None, 64)
+    _close(dqkv, qkv_f.grad, 2e-2, 3e-2)
+    if use_norm:
+        _close(dqw, qwf.grad, 2e-2, 3e-2 * (T * Hq) ** 0.5)
+        _close(dkw, kwf.grad, 2e-2, 3e-2 * (T * Hk) ** 0.5)
 
 
 @pytest.mark.parametrize("T,I", [(1, 768), (333, 768), (257, 9728)])

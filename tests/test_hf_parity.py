@@ -43,10 +43,20 @@ def _case(name):
         return T.MistralConfig(**COMMON, rope_theta=1e6, sliding_window=None), T.MistralForCausalLM
     if name == "mixtral":
         return T.MixtralConfig(**COMMON, rope_theta=1e6, num_local_experts=4, num_experts_per_tok=2, sliding_window=None), T.MixtralForCausalLM
+    if name == "glm4_moe":
+        return T.Glm4MoeConfig(**COMMON, head_dim=16, partial_rotary_factor=0.5, n_routed_experts=8, num_experts_per_tok=2,
+                               moe_intermediate_size=32, n_shared_experts=1, first_k_dense_replace=1, routed_scaling_factor=2.5,
+                               norm_topk_prob=True, use_qk_norm=True, attention_bias=True, n_group=1, topk_group=1,
+                               rope_theta=1e4), T.Glm4MoeForCausalLM
+    if name == "glm4_moe-groups":
+        return T.Glm4MoeConfig(**COMMON, head_dim=16, partial_rotary_factor=0.5, n_routed_experts=8, num_experts_per_tok=2,
+                               moe_intermediate_size=32, n_shared_experts=2, first_k_dense_replace=0, routed_scaling_factor=1.0,
+                               norm_topk_prob=False, use_qk_norm=False, attention_bias=False, n_group=4, topk_group=2,
+                               rope_theta=1e4), T.Glm4MoeForCausalLM
     raise KeyError(name)
 
 
-CASES = ["qwen3", "qwen3-tied", "qwen3_moe", "qwen3_moe-raw-topk", "qwen2", "llama", "llama-rope-llama3", "llama-rope-linear",
+CASES = ["glm4_moe", "glm4_moe-groups", "qwen3", "qwen3-tied", "qwen3_moe", "qwen3_moe-raw-topk", "qwen2", "llama", "llama-rope-llama3", "llama-rope-linear",
          "mistral", "mixtral"]
 
 
@@ -67,6 +77,9 @@ def test_logits_match_huggingface_both_ways(name, tmp_path):
         for n, p in hf.named_parameters():
             if n.endswith("norm.weight") or n.endswith(".bias"):
                 p.add_(torch.randn_like(p) * 0.1)
+        for n, b in hf.named_buffers():
+            if n.endswith("e_score_correction_bias"):
+                b.add_(torch.randn_like(b) * 0.3)  # a selection bias that changes which experts win
     src = tmp_path / "hf"
     hf.save_pretrained(src, safe_serialization=True)
     cfg = ModelConfig.from_hf_config(str(src))
@@ -106,3 +119,24 @@ def test_unsupported_checkpoints_are_refused():
         ModelConfig.from_hf_config(dict(base, architectures=["MistralForCausalLM"], model_type="mistral", sliding_window=128,
                                         max_position_embeddings=4096))
     assert ModelConfig.from_hf_config(dict(base, rope_scaling=LLAMA3_SCALING)).rope_scaling["rope_type"] == "llama3"
+
+
+def test_megatron_style_flags_describe_a_glm45_like_model():
+    from miles_b200.utils.arguments import model_config_from_args, parse_args
+
+    a = parse_args(["--num-rollout", "1", "--rollout-batch-size", "2", "--num-layers", "3", "--hidden-size", "512",
+                    "--num-attention-heads", "8", "--num-query-groups", "2", "--kv-channels", "128", "--ffn-hidden-size", "1024",
+                    "--vocab-size", "4096", "--num-experts", "16", "--moe-router-topk", "4", "--moe-ffn-hidden-size", "256",
+                    "--moe-router-score-function", "sigmoid", "--moe-router-enable-expert-bias", "--moe-router-topk-scaling-factor", "2.5",
+                    "--moe-shared-expert-intermediate-size", "256", "--moe-layer-freq", "[0]*1+[1]*2", "--rotary-percent", "0.5",
+                    "--qk-layernorm", "--add-qkv-bias", "--untie-embeddings-and-output-weights"])
+    cfg = model_config_from_args(a)
+    assert (cfg.router_score, cfg.router_bias, cfg.routed_scaling_factor, cfg.shared_expert_ffn) == ("sigmoid", True, 2.5, 256)
+    assert cfg.first_dense_layers == 1 and cfg.rotary_dim == 64 and cfg.family == "glm4_moe"
+    assert [cfg.layer_is_moe(i) for i in range(3)] == [False, True, True]
+    from miles_b200.models import get_config
+
+    ref = get_config("glm4moe-smoke")
+    store_a = ParamStore(cfg, "cpu", torch.float32, meta=True, init=False)
+    store_b = ParamStore(ref, "cpu", torch.float32, meta=True, init=False)
+    assert [(s.name, s.shape) for s in store_a.specs] == [(s.name, s.shape) for s in store_b.specs]
