@@ -262,6 +262,71 @@ class Engine:
             self.prefix.clear()
         return True
 
+    # ------------------------------------------------------------------ prefill / decode disaggregation
+    @torch.no_grad()
+    def export_prefix(self, tokens: Sequence[int], to_cpu: bool = True) -> Optional[dict]:
+        """The keys / values this engine's prefix cache holds for the longest cached prefix of ``tokens`` (whole pages):
+        what a prefill engine hands to the decode engine that continues the request. ``kv`` is
+        ``[layers, 2, cached_tokens, kv_heads, head_dim]``. None when nothing is cached."""
+        if self.prefix is None or self.kv_cache is None or self._kv_paused:
+            return None
+        self._drain_pending()
+        nodes = self.prefix.match([int(t) for t in tokens])
+        if not nodes:
+            return None
+        ps = self.page_size
+        pages = torch.tensor([n.page for n in nodes], dtype=torch.int64, device=self.dev)
+        slots = (pages[:, None] * ps + torch.arange(ps, device=self.dev)[None, :]).reshape(-1)
+        kv = torch.stack([torch.stack((kc[slots], vc[slots])) for kc, vc in self.kv_cache])
+        payloads = [n.payload for n in nodes]
+        return {"tokens": [int(t) for t in tokens[:len(nodes) * ps]], "kv": kv.cpu() if to_cpu else kv, "page_size": ps,
+                "weight_version": self.weight_version,
+                "routed_experts": torch.cat(payloads, 0).cpu() if all(p is not None for p in payloads) else None}
+
+    @torch.no_grad()
+    def import_prefix(self, blob: Optional[dict]) -> int:
+        """Put exported keys / values into this engine's prefix cache, so that a request starting with those tokens
+        prefills only what follows them. Pages already cached here are kept as they are. Returns the number of tokens the
+        cache now holds for the sequence (0: refused because the page size or the weight version differs, the cache is off,
+        or the pool has no room)."""
+        if (blob is None or self.prefix is None or self.kv_cache is None or self._kv_paused
+                or int(blob["page_size"]) != self.page_size or int(blob["weight_version"]) != self.weight_version):
+            return 0
+        self._drain_pending()
+        ps = self.page_size
+        tokens = [int(t) for t in blob["tokens"]]
+        n_pages = len(tokens) // ps
+        kv = blob["kv"]
+        assert kv.shape[0] == len(self.kv_cache) and kv.shape[2] >= n_pages * ps, "exported keys / values of another model"
+        have = self.prefix.match(tokens)
+        self.prefix.lock(have)  # an eviction for the new pages must not take the pages we build upon
+        try:
+            need = n_pages - len(have)
+            if need <= 0:
+                return n_pages * ps
+            new_pages = self._alloc(need)
+            if new_pages is None:
+                return len(have) * ps
+            pg = torch.as_tensor(list(new_pages), dtype=torch.int64, device=self.dev)
+            slots = (pg[:, None] * ps + torch.arange(ps, device=self.dev)[None, :]).reshape(-1)
+            a = len(have) * ps
+            part = kv[:, :, a:n_pages * ps].to(self.dev)
+            for layer, (kc, vc) in enumerate(self.kv_cache):
+                kc[slots] = part[layer, 0].to(kc.dtype)
+                vc[slots] = part[layer, 1].to(vc.dtype)
+            payloads = None
+            if blob.get("routed_experts") is not None:
+                re = blob["routed_experts"]
+                payloads = [re[p * ps:(p + 1) * ps].clone() for p in range(n_pages)]
+            nodes, dup = self.prefix.insert(tokens, [n.page for n in have] + list(new_pages), payloads, skip=len(have))
+            if dup:
+                self.pool.release(dup)
+            return len(nodes) * ps
+        finally:
+            freed = self.prefix.unlock(have)
+            if freed:
+                self.pool.release(freed)
+
     def _alloc(self, n: int):
         """``n`` pages from the pool; when it runs dry, unreferenced prefix-cache pages are evicted first."""
         pages = self.pool.alloc(n)

@@ -18,8 +18,15 @@ from ..utils import http_utils
 
 
 class RemoteEngineClient:
-    def __init__(self, urls: Sequence[str], tokenizer=None, transport=None, max_retries: int = 3):
-        self.urls = [u.rstrip("/") for u in urls]
+    def __init__(self, urls: Sequence[str], tokenizer=None, transport=None, max_retries: int = 3,
+                 prefill_urls: Sequence[str] = ()):
+        """``prefill_urls``: prefill / decode disaggregation. Those engines only prefill; ``urls`` minus them decode, and
+        every request's prompt pages are handed from one to the other before it is submitted (engine/pd.py)."""
+        self.prefill_urls = [u.rstrip("/") for u in prefill_urls]
+        self.all_urls = [u.rstrip("/") for u in urls]
+        self.urls = [u for u in self.all_urls if u not in self.prefill_urls]  # the engines that answer /generate
+        self._prefill_rr = 0
+        self.transferred_tokens = 0
         if not self.urls:
             raise ValueError("at least one engine URL is required")
         self.tokenizer = tokenizer
@@ -42,14 +49,37 @@ class RemoteEngineClient:
         url = self._pick(payload.get("routing_key"))
         self.inflight[url] += 1
         try:
+            if self.prefill_urls and "input_ids" in payload:
+                await self._hand_over(payload, url)
             return await http_utils.post(url + "/generate", payload, max_retries=self._retries, transport=self._transport)
         finally:
             self.inflight[url] -= 1
 
+    async def _hand_over(self, payload: dict, decode_url: str) -> None:
+        """Prefill the prompt on a prefill engine and move its cached pages into the decode engine's prefix cache. A
+        failure here costs only the saving: the decode engine then prefills the whole prompt itself."""
+        from .pd import PDClient
+
+        self._prefill_rr += 1
+        pu = self.prefill_urls[self._prefill_rr % len(self.prefill_urls)]
+        try:
+            pd = PDClient([pu], [decode_url], transport=self._transport)
+            warm = {"input_ids": payload["input_ids"], "return_logprob": False,
+                    "sampling_params": {"max_new_tokens": 1, "temperature": 0.0, "ignore_eos": True},
+                    "return_routed_experts": bool(payload.get("return_routed_experts"))}
+            await pd._call(pu + "/generate", warm)
+            blob = await pd._call(pu + "/export_prefix", {"input_ids": payload["input_ids"]}, raw=True)
+            got = await pd._call(decode_url + "/import_prefix", blob)
+            if isinstance(got, dict):
+                self.transferred_tokens += int(got.get("cached_tokens", 0))
+        except Exception:  # noqa: BLE001 - the request itself still runs
+            pass
+
     # ------------------------------------------------------------------ control plane (all engines)
     async def _all(self, path: str, payload: Optional[dict] = None, method: str = "POST") -> list:
+        targets = self.all_urls if getattr(self, "all_urls", None) else self.urls
         return await asyncio.gather(*[http_utils.request(method, u + path, payload, max_retries=self._retries,
-                                                         transport=self._transport) for u in self.urls])
+                                                         transport=self._transport) for u in targets])
 
     async def abort_all(self) -> None:
         await self._all("/abort_request", {"abort_all": True})

@@ -94,6 +94,23 @@ def register_extra(app, engine, state: dict) -> None:
         return {"success": True, "loaded_adapters": sorted(state["adapters"])}
 
     # ------------------------------------------------------------------ profiling
+    @app.post("/export_prefix")
+    async def export_prefix(req: Request):
+        """Prefill / decode disaggregation: the cached keys / values of the longest cached prefix of ``input_ids`` as one
+        binary message (engine/pd.py)."""
+        from fastapi.responses import Response
+
+        from .pd import pack_blob
+
+        body = await req.json()
+        return Response(content=pack_blob(engine.export_prefix(body["input_ids"])), media_type="application/octet-stream")
+
+    @app.post("/import_prefix")
+    async def import_prefix(req: Request):
+        from .pd import unpack_blob
+
+        return {"cached_tokens": engine.import_prefix(unpack_blob(await req.body()))}
+
     @app.post("/start_profile")
     async def start_profile(req: Request):
         b = await req.json() if await req.body() else {}

@@ -270,16 +270,20 @@ class RLLoop:
                                first_gpu=0 if (dev or "").startswith("cpu") else self.ps.world_size).start()
             atexit.register(self.fleet.stop)
             box[0] = ",".join(self.fleet.updatable_urls() or self.fleet.urls())
-            if getattr(a, "use_miles_router", False):
+            # prefill / decode disaggregation: these engines only prefill; the client hands their pages to the decoders
+            box.append(",".join(self.fleet.urls(worker_type="prefill")))
+            box.append(None)
+            if getattr(a, "use_miles_router", False) and not box[1]:
                 # generation goes through one router process; weight updates still address the engines themselves
-                box.append(self.fleet.start_router(
+                box[2] = (self.fleet.start_router(
                     a.rollout_fleet_base_port + len(self.fleet.engines) + 1,
                     failure_threshold=getattr(a, "miles_router_health_check_failure_threshold", None),
                     timeout=getattr(a, "miles_router_timeout", None), max_connections=getattr(a, "miles_router_max_connections", None)))
+        box = box + [None] * (3 - len(box))
         if self.ps.world_size > 1:
-            box = box + [None] * (2 - len(box))
             dist.broadcast_object_list(box, src=0)
-        self.router_url = box[1] if len(box) > 1 else None
+        self.prefill_urls = [u for u in (box[1] or "").split(",") if u]
+        self.router_url = box[2]
         return box[0]
 
     def _connect_remote_engines(self, urls: list) -> None:
@@ -289,7 +293,8 @@ class RLLoop:
         from .weight_sync.broadcast import BroadcastWeightUpdater, HttpEngineHandle
 
         router = getattr(self, "router_url", None) or getattr(self.args, "rollout_router_url", None)
-        self.client = RemoteEngineClient([router] if router else urls, self.tokenizer)
+        prefill = list(getattr(self, "prefill_urls", None) or [u for u in (getattr(self.args, "rollout_prefill_urls", None) or "").split(",") if u])
+        self.client = RemoteEngineClient([router] if (router and not prefill) else urls, self.tokenizer, prefill_urls=prefill)
         self.rollout_store = None
         sender = self.ps.rank == 0
         if getattr(self.args, "update_weight_transfer_mode", None) == "disk-delta":

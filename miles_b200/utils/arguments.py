@@ -74,7 +74,7 @@ TRAINER_FLAGS = [
     ("--beta-fast", "f", None, {}), ("--beta-slow", "f", None, {}), ("--no-position-embedding", "b", False, {}),
     # optimizer / schedule
     ("--rollout-quantization", "s", "none", {"choices": ["none", "mxfp8", "nvfp4"]}),
-    ("--rollout-engine-urls", "s", None, {}), ("--launch-rollout-fleet", "b", False, {}), ("--rollout-router-url", "s", None, {}), ("--sglang-config", "s", None, {}), ("--rollout-fleet-device", "s", None, {}),
+    ("--rollout-engine-urls", "s", None, {}), ("--rollout-prefill-urls", "s", None, {}), ("--launch-rollout-fleet", "b", False, {}), ("--rollout-router-url", "s", None, {}), ("--sglang-config", "s", None, {}), ("--rollout-fleet-device", "s", None, {}),
     ("--rollout-fleet-base-port", "i", 30000, {}),
     ("--custom-agent-function-path", "s", None, {}), ("--tito-family", "s", None, {"choices": ["chatml", "qwen3", "llama3", "generic"]}),
     ("--muon-momentum", "f", 0.95, {}), ("--muon-num-ns-steps", "i", 5, {}), ("--muon-extra-scale-factor", "f", 1.0, {}),

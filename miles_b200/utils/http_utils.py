@@ -70,3 +70,26 @@ async def post(url: str, payload: Optional[dict] = None, **kw) -> Any:
 
 async def get(url: str, **kw) -> Any:
     return await request("GET", url, None, **kw)
+
+
+async def post_bytes(url: str, body: bytes, expect_bytes: bool = False, content_type: str = "application/octet-stream",
+                     max_retries: int = 3, base_delay: float = 0.5) -> Any:
+    """POST a raw body (binary hand-over messages); returns the raw response body, or its JSON when ``expect_bytes`` is
+    false. A JSON request that expects a binary answer passes ``content_type="application/json"``."""
+    last: Optional[BaseException] = None
+    for attempt in range(max_retries + 1):
+        try:
+            r = await client().post(url, content=body, headers={"content-type": content_type})
+            if r.status_code >= 500:
+                raise RuntimeError(f"POST {url} -> HTTP {r.status_code}")
+            if r.status_code >= 400:
+                raise ValueError(f"POST {url} -> HTTP {r.status_code}: {r.text[:200]}")
+            return r.content if expect_bytes else (r.json() if r.content else None)
+        except ValueError:
+            raise
+        except Exception as e:  # noqa: BLE001
+            last = e
+            if attempt == max_retries:
+                break
+            await asyncio.sleep(base_delay * (2 ** attempt) * (0.5 + random.random() / 2))
+    raise last if last is not None else RuntimeError("request failed")
