@@ -146,3 +146,46 @@ def test_prefix_cache_on_the_sm100_path(name):
         d = (lp - elp).abs()
         assert d.mean().item() < 2e-2 and d.max().item() < 0.25, (d.mean().item(), d.max().item())
     assert not eng.running and eng.pool.num_free + eng.prefix.num_pages == eng.num_pages - 1
+
+
+@pytest.mark.parametrize("name", ["qwen3-smoke", "qwen3-smoke-moe"])
+def test_prefill_decode_hand_over_on_the_sm100_path(name):
+    """Two engines on one model: the prompt's pages (and routed experts) move from the prefill engine's prefix cache to the
+    decode engine's; the decode engine prefills only the tail, and the log-probs it reports match a recomputation."""
+    from miles_b200.engine.pd import PDPair, pack_blob, unpack_blob
+
+    dev = torch.device("cuda")
+    cfg = get_config(name)
+    st = ParamStore(cfg, dev, torch.bfloat16, init_std=0.02)
+    m = build_model(cfg, st, "b200")
+    prefill = Engine(m, max_running=4, page_size=64, max_seq_len=1024, use_cuda_graph=False, prefix_cache=True)
+    decode = Engine(m, max_running=4, page_size=64, max_seq_len=1024, use_cuda_graph=True, prefix_cache=True)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (300, 130)]
+    sp = SamplingParams(temperature=1.0, max_new_tokens=24, sampling_seed=4)
+    pair = PDPair(prefill, decode)
+    res = pair.generate(prompts, sp, return_routed_experts=True)
+    m.check_status()
+    assert pair.transferred_tokens == 256 + 128
+    assert [r["meta_info"]["cached_tokens"] for r in res] == [256, 128]
+    assert decode.stats["prefill_tokens"] == (300 - 256) + (130 - 128)
+    blob = prefill.export_prefix(prompts[0])
+    back = unpack_blob(pack_blob(blob))                       # the byte form engines in other processes exchange
+    assert torch.equal(back["kv"], blob["kv"]) and back["kv"].dtype == torch.bfloat16
+    for p, r in zip(prompts, res):
+        ids = p + r["output_ids"]
+        tok = torch.tensor(ids, dtype=torch.int32, device=dev)
+        pos = torch.arange(len(ids), dtype=torch.int32, device=dev)
+        cu = torch.tensor([0, len(ids)], dtype=torch.int32, device=dev)
+        rows = torch.arange(len(p) - 1, len(ids) - 1, device=dev)
+        replay = None
+        if cfg.is_moe:
+            re = r["meta_info"]["routed_experts"].to(dev)
+            assert re.shape[0] == len(ids) - 1
+            replay = torch.cat([re, re[-1:]], 0)
+        lp, _ = m.forward_logprobs(tok, pos, cu, rows, tok[len(p):], 1.0, replay=replay)
+        elp = torch.tensor([x[0] for x in r["meta_info"]["output_token_logprobs"]], device=dev)
+        d = (lp - elp).abs()
+        assert d.mean().item() < 2e-2 and d.max().item() < 0.25, (d.mean().item(), d.max().item())
+    for e in (prefill, decode):
+        assert not e.running and e.pool.num_free + e.prefix.num_pages == e.num_pages - 1
