@@ -174,8 +174,10 @@ class RLLoop:
             from .models import ParamStore, build_model
 
             ep = self.ps.ep
-            if (getattr(a, "fused_comm", True) and self.actor.store.dtype == torch.bfloat16 and ep.size <= 8
-                    and getattr(a, "update_weight_transfer_mode", "broadcast") != "broadcast-nccl"):
+            from .parallel.topology import peer_memory_ok
+
+            if (peer_memory_ok(ep.group, ep.size, getattr(a, "fused_comm", True)) and self.actor.store.dtype == torch.bfloat16
+                    and ep.size <= 8 and getattr(a, "update_weight_transfer_mode", "broadcast") != "broadcast-nccl"):
                 # the replica's experts live in a peer-mapped region: every rank stores its updated expert shard
                 # straight into all replicas with one kernel (csrc/weight_push.cu) instead of an all-gather per tensor
                 from .weight_sync.p2p_push import Layout, PushTarget, WeightPusher
@@ -212,13 +214,16 @@ class RLLoop:
             from .parallel.expert_parallel import ExpertParallel
 
             sync = LockstepSync(self.ps.gloo_world if self.ps.backend != "gloo" else None)
-            if self.actor.on_gpu and getattr(a, "fused_comm", True) and max_running <= 256 and not self.actor.is_torch:
+            from .parallel.topology import peer_memory_ok
+
+            one_node = peer_memory_ok(self.ps.ep.group, self.ps.ep.size, getattr(a, "fused_comm", True))
+            if self.actor.on_gpu and one_node and max_running <= 256 and not self.actor.is_torch:
                 # decode steps: gather / partial-sum exchange with in-kernel flags (csrc/ep_decode.cu)
                 from .parallel.ep_decode import EpDecodeLL
 
                 ep_decode = EpDecodeLL(cfg, self.ps, max_rows=max(max_running, 8))
             else:
-                ep_decode = ExpertParallel(cfg, self.ps, fused=getattr(a, "fused_comm", True), max_tokens=max(max_running, 16))
+                ep_decode = ExpertParallel(cfg, self.ps, fused=one_node, max_tokens=max(max_running, 16))
         quant = getattr(a, "rollout_quantization", "none")
         if quant != "none" and self.actor.on_gpu and not self.actor.is_torch:
             if engine_model is self.actor.model:

@@ -161,15 +161,21 @@ class TrainActor:
 
             assert want_b200, "tensor parallelism needs the sm_100a model path"
             max_tok = max(getattr(args, "max_tokens_per_gpu", None) or 0, getattr(args, "engine_max_prefill_tokens", 16384), 4096)
+            from ..parallel.topology import peer_memory_ok
+
+            # peer-memory kernels need every rank of the group on this node; a group across nodes reduces with NCCL
             self.tp_exchange = TensorParallel(self.ps.tp.group, self.ps.tp.rank, tp, self.device, self.cfg.hidden_size, max_tok,
-                                              fused=getattr(args, "fused_comm", True))
+                                              fused=peer_memory_ok(self.ps.tp.group, tp, getattr(args, "fused_comm", True)))
         self.ep_dispatcher = None
         if ep > 1:
             from ..parallel.expert_parallel import ExpertParallel
 
             max_tok = max(getattr(args, "max_tokens_per_gpu", None) or 0, getattr(args, "engine_max_prefill_tokens", 16384),
                           (getattr(args, "rollout_max_context_len", None) or 0), 4096)
-            self.ep_dispatcher = ExpertParallel(self.cfg, self.ps, fused=getattr(args, "fused_comm", True), max_tokens=max_tok)
+            from ..parallel.topology import peer_memory_ok
+
+            self.ep_dispatcher = ExpertParallel(self.cfg, self.ps, max_tokens=max_tok,
+                                                fused=peer_memory_ok(self.ps.ep.group, ep, getattr(args, "fused_comm", True)))
         provider = getattr(args, "custom_model_provider_path", None)
         if provider:
             # a plug-in builds the model (see miles_b200/plugins): it says itself whether it runs under autograd
@@ -362,7 +368,8 @@ class TrainActor:
             return
         dense_shard = None
         if (self.on_gpu and self.ps.dp_cp.size > 1 and self.ps.tp.size == 1 and self.store.dtype == torch.bfloat16
-                and getattr(a, "fused_comm", True) and getattr(a, "use_distributed_optimizer", True) and self.ps.dp_cp.size <= 8):
+                and getattr(a, "fused_comm", True) and getattr(a, "use_distributed_optimizer", True) and self.ps.dp_cp.size <= 8
+                and self._dp_on_one_node()):
             from ..parallel.dp_optimizer import ShardedDenseAdam
 
             # replicated parameters: reduce-scatter + Adam on the owned range + all-gather as peer-memory kernels
@@ -371,6 +378,11 @@ class TrainActor:
         self.opt = FlatAdam(self.store, oc, dp_group=self.ps.dp_cp.group, ep_group=self.ps.ep.group,
                             tp_group=self.ps.tp.group if self.ps.tp.size > 1 else None, dense_shard=dense_shard,
                             pp_group=self.ps.pp.group if self.ps.pp.size > 1 else None)
+
+    def _dp_on_one_node(self) -> bool:
+        from ..parallel.topology import group_is_single_node
+
+        return group_is_single_node(self.ps.dp_cp.group, self.ps.dp_cp.size)
 
     # ------------------------------------------------------------------ weight tags (ref / old_actor / teacher)
     def backup_weights(self, tag: str) -> None:

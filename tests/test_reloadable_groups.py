@@ -93,3 +93,29 @@ def _loop_worker(rank: int, world: int, port: int, out_dir: str):
 
 def test_training_loop_releases_groups_for_the_rollout(tmp_path):
     mp.spawn(_loop_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+
+
+def _topo_worker(rank: int, world: int, port: int):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    from miles_b200.parallel.state import init_parallel_state
+    from miles_b200.parallel.topology import group_is_single_node, peer_memory_ok
+
+    ps = init_parallel_state(backend="gloo")
+    assert group_is_single_node(ps.dp_cp.group, ps.dp_cp.size), "four local processes are one node"
+    assert peer_memory_ok(ps.dp_cp.group, ps.dp_cp.size, True) and not peer_memory_ok(ps.dp_cp.group, ps.dp_cp.size, False)
+    # ranks {0, 1} and {2, 3} pretend to sit on two nodes: groups inside a node keep peer memory, the group across does not
+    os.environ["MILES_B200_NODE_ID"] = f"node{rank // 2}"
+    from miles_b200.parallel.reloadable_groups import registry
+
+    pairs = [registry().new_group([0, 1]), registry().new_group([2, 3])]
+    across = registry().new_group([0, 1, 2, 3])
+    mine = pairs[rank // 2]
+    assert group_is_single_node(mine, 2)
+    assert not group_is_single_node(across, 4)
+    assert group_is_single_node(None, 1)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_groups_across_nodes_fall_back_from_peer_memory():
+    mp.spawn(_topo_worker, args=(4, _free_port()), nprocs=4, join=True)
