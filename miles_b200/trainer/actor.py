@@ -186,6 +186,7 @@ class TrainActor:
             self.model = build_model(self.cfg, store, "b200" if want_b200 else "torch", ep=self.ep_dispatcher, tp=self.tp_exchange)
             self.is_torch = not want_b200
         self.loss_cfg = LossConfig.from_args(args)
+        self.loss_cfg.args = args  # plug-ins (custom TIS / reducer functions) read their own options from the command line
         if getattr(args, "custom_tis_function_path", None):
             self.loss_cfg.custom_tis_fn = load_function(args.custom_tis_function_path)
         if getattr(args, "custom_pg_loss_reducer_function_path", None):
