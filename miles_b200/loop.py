@@ -309,7 +309,7 @@ class RLLoop:
                 self.actor, [HttpEngineHandle(u) for u in urls] if sender else [], self.args.update_weight_disk_dir,
                 encoding=getattr(self.args, "update_weight_delta_encoding", "xor"),
                 checksum_kind=getattr(self.args, "update_weight_delta_checksum", "xxh3-128"))
-        elif sender or self.actor.store.ep_size > 1:
+        elif sender or self.actor.store.ep_size > 1 or getattr(self.actor, "fsdp", False):
             handles = [HttpEngineHandle(u) for u in urls] if sender else []
             self.weight_updater = BroadcastWeightUpdater(
                 self.actor, handles, buffer_bytes=int(getattr(self.args, "update_weight_buffer_size", None) or (512 << 20)),

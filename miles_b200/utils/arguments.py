@@ -289,8 +289,7 @@ def validate_args(args: argparse.Namespace) -> argparse.Namespace:
         for flag in ("tensor_model_parallel_size", "pipeline_model_parallel_size", "expert_model_parallel_size"):
             if int(getattr(args, flag, 1) or 1) != 1:
                 raise ValueError(f"--train-backend fsdp is data parallel only: --{flag.replace('_', '-')} must be 1")
-        for flag, what in (("lora_rank", "LoRA"), ("rollout_engine_urls", "engines in other processes"),
-                           ("use_fault_tolerance", "independent data-parallel cells"),
+        for flag, what in (("lora_rank", "LoRA"), ("use_fault_tolerance", "independent data-parallel cells"),
                            ("stream_optimizer_state_to_disk", "optimizer state on disk")):
             if getattr(args, flag, None):
                 raise NotImplementedError(f"--train-backend fsdp with {what} (--{flag.replace('_', '-')}) is not built")

@@ -186,11 +186,28 @@ class BroadcastWeightUpdater:
             experts = gathered
         return dense, experts
 
+    def _parts(self):
+        """Lists of ``(name, tensor)`` to send one after the other; a list's tensors stay valid until the next one is asked
+        for. An unsharded store gives two (non-expert pass, expert pass); a sharded (``--train-backend fsdp``) store gives
+        one per unit, whose parameters exist only while the unit is materialised (collective over the shard group: every
+        trainer rank walks the units, the sender alone broadcasts them)."""
+        store = self.actor.store
+        if getattr(store, "is_fsdp", False):
+            store.invalidate()
+            for u in store.units:
+                yield [(sp.name, store.params[sp.name]) for sp in u.specs]
+            store.invalidate()
+            return
+        dense, experts = self._named()
+        yield dense
+        yield experts
+
     def update(self) -> dict:
         import time
 
         if not self.is_sender:
-            self._named()  # take part in the gathers, send nothing
+            for _ in self._parts():  # take part in the gathers, send nothing
+                pass
             return {}
         if not self.connected:
             self.connect()
@@ -202,8 +219,7 @@ class BroadcastWeightUpdater:
                 e.post("/flush_cache", {})
         version = self.actor.store.version
         moved = 0
-        dense, experts = self._named()
-        for part in (dense, experts):  # non-expert pass, then expert pass
+        for part in self._parts():
             for bucket in iter_buckets(part, self.buffer_bytes):
                 hdr = bucket_header(bucket, self.group_name)
                 handles = [e.post_async("/update_weights_from_distributed", hdr) for e in self.engines]

@@ -18,7 +18,9 @@ from miles_b200.utils.arguments import parse_args
 
 BASE = ["--model-preset", "qwen3-tiny-moe", "--rollout-batch-size", "8", "--n-samples-per-prompt", "4", "--rollout-max-response-len", "16",
         "--rollout-max-prompt-len", "32", "--rm-type", "parity", "--lr", "1e-5", "--eps-clip", "0.2", "--micro-batch-size", "4",
-        "--weight-decay", "0.01", "--colocate", "--distributed-backend", "gloo"]
+        "--weight-decay", "0.01", "--colocate", "--distributed-backend", "gloo",
+        # a KL term against reference weights: the reference is a pinned copy of the shards, swapped in for one pass
+        "--use-kl-loss", "--kl-loss-coef", "0.05"]
 
 
 def _free_port() -> int:
@@ -249,3 +251,69 @@ def _explicit_worker(rank: int, world: int, port: int):
 
 def test_explicit_gradient_path_reduce_scatters_units_in_backward_order():
     mp.spawn(_explicit_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def _serve_engine(port, ready):
+    torch.set_num_threads(2)
+    from miles_b200.engine import Engine
+    from miles_b200.engine.server import serve
+    from miles_b200.models import build_model
+
+    cfg = get_config("qwen3-tiny-moe")
+    st = ParamStore(cfg, "cpu", torch.float32, seed=2)  # other weights than the trainer's until the first update
+    ready.set()
+    serve(Engine(build_model(cfg, st), max_running=4, page_size=8, max_seq_len=64), port=port)
+
+
+def _remote_worker(rank: int, world: int, port: int, engine_port: int):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      MILES_B200_ENV_REPORT="0")
+    torch.set_num_threads(2)
+    from miles_b200.loop import RLLoop
+    from miles_b200.weight_sync.broadcast import HttpEngineHandle
+
+    args = parse_args(["--model-preset", "qwen3-tiny-moe", "--train-backend", "fsdp", "--num-rollout", "2", "--rollout-batch-size", "4",
+                       "--n-samples-per-prompt", "2", "--rollout-max-response-len", "8", "--rollout-max-prompt-len", "16",
+                       "--rm-type", "parity", "--lr", "1e-3", "--actor-num-nodes", "1", "--actor-num-gpus-per-node", str(world),
+                       "--rollout-engine-urls", f"http://127.0.0.1:{engine_port}", "--micro-batch-size", "2",
+                       "--distributed-backend", "gloo"])
+    loop = RLLoop(args)
+    assert loop.engine is None and loop.weight_updater is not None, "every rank walks the units; the first one sends"
+    hist = loop.run()
+    assert len(hist) == 2 and all(m["train/train_rollout_logprob_abs_diff"] < 1e-5 for m in hist)
+    want = loop.actor.store.checksum()  # collective: the pieces' sums over the shard group
+    if rank == 0:
+        h = HttpEngineHandle(f"http://127.0.0.1:{engine_port}", timeout_s=60)
+        got = h.post("/weights_checker", {"action": "checksum"})["checksum"]
+        assert all(abs(got[g] - want[g]) <= 1e-3 * max(1.0, abs(want[g])) for g in want), (got, want)
+        assert h.get("/get_weight_version")["weight_version"] == loop.actor.store.version
+        loop.weight_updater.disconnect()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_trainer_updates_an_engine_in_another_process():
+    """--train-backend fsdp with --rollout-engine-urls: the units are gathered one after the other on all trainer ranks and
+    broadcast by the first one; the engine then holds the trainer's weights (on-policy log-prob parity proves it)."""
+    import time
+
+    from miles_b200.weight_sync.broadcast import HttpEngineHandle
+
+    ctx = mp.get_context("spawn")
+    engine_port = _free_port()
+    ready = ctx.Event()
+    srv = ctx.Process(target=_serve_engine, args=(engine_port, ready), daemon=True)
+    srv.start()
+    try:
+        assert ready.wait(120)
+        h = HttpEngineHandle(f"http://127.0.0.1:{engine_port}", timeout_s=60)
+        for _ in range(100):
+            try:
+                h.get("/health")
+                break
+            except Exception:
+                time.sleep(0.2)
+        mp.spawn(_remote_worker, args=(2, _free_port(), engine_port), nprocs=2, join=True)
+    finally:
+        srv.terminate()
+        srv.join(10)
