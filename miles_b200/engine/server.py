@@ -9,7 +9,6 @@
 ``/weights_checker``, ``/metrics``.  The engine loop runs as an asyncio task of the same process, so the
 server needs no scheduler or detokenizer subprocesses.
 """
-import asyncio
 import time
 
 from .client import EngineClient

@@ -15,8 +15,7 @@ from typing import Optional
 
 from ..utils.misc import load_function
 from ..utils.types import Sample
-from .base_types import (GenerateFnInput, RolloutFnConstructorInput, RolloutFnEvalInput, RolloutFnEvalOutput,
-                         RolloutFnTrainInput, RolloutFnTrainOutput)
+from .base_types import GenerateFnInput, RolloutFnConstructorInput, RolloutFnEvalOutput, RolloutFnTrainOutput
 from .generate_hub.common import GenerateState
 from .rm_hub import async_rm, batched_async_rm
 

@@ -23,7 +23,7 @@ from ..rl.advantages import compute_advantages_and_returns
 from ..rl.losses import LossConfig, SegmentReducer, policy_loss, sft_loss, value_loss
 from ..utils.arguments import model_config_from_args
 from ..utils.misc import load_function
-from ..utils.timer import Timer, timer
+from ..utils.timer import Timer
 from .data import MicroBatch, build_micro_batches, split_by_dp
 from .optimizer import FlatAdam, OptimConfig
 

@@ -1,5 +1,4 @@
 """RL mathematics on CPU: GAE (chunked vs loop), KL estimators, reward normalisation, advantages, losses."""
-import math
 
 import pytest
 import torch

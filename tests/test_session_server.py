@@ -1,5 +1,4 @@
 """Token-in-token-out session proxy: exact token history across turns, loss masks, conflict detection."""
-import pytest
 
 from miles_b200.rollout.session import SessionStore, build_session_app
 

@@ -16,7 +16,6 @@ Reference: train_multi_lora_async.py:35-101.
 from __future__ import annotations
 
 import threading
-import time
 
 
 def _serve(app, port: int) -> threading.Thread:
