@@ -602,6 +602,9 @@ class RLLoop:
         T = Timer()
         t0 = time.perf_counter()
         metrics: dict = {}
+        hp = getattr(self, "host_profiler", None)
+        if hp is not None:
+            hp.mark("rollout")
         samples, m = self.generate(rollout_id)
         metrics.update(m)
         t1 = time.perf_counter()
@@ -610,6 +613,8 @@ class RLLoop:
         self.offload_rollout()
         if a.offload_train:
             self.actor.wake_up()
+        if hp is not None:
+            hp.mark("train")
         metrics.update(self.train(rollout_id, samples))
         if getattr(a, "ci_test", False):
             from .utils.ci_checks import check_rollout_logprobs
@@ -622,6 +627,8 @@ class RLLoop:
         if a.offload_train:
             self.actor.sleep()
         self.onload_rollout()
+        if hp is not None:
+            hp.mark("update_weights")
         if (rollout_id + 1) % (a.update_weights_interval or 1) == 0:
             metrics.update(self.update_weights())
         t3 = time.perf_counter()
@@ -746,6 +753,12 @@ class RLLoop:
             from .utils.profile_utils import TrainProfiler
 
             profiler = TrainProfiler(a, self.ps.rank)  # torch profiler trace of steps [start, end), memory snapshot
+        self.host_profiler = None
+        if getattr(a, "profile_host_memory", None) and self.ps.rank == 0:
+            from .tools.host_memory_profiler import HostMemoryProfiler
+
+            # machine-wide and per-process host memory over time, with a mark per phase (tools/host_memory_profiler.py)
+            self.host_profiler = HostMemoryProfiler(a.profile_host_memory, float(getattr(a, "profile_host_memory_interval", 0.5))).start()
         for rid in range(self.start_rollout_id, a.num_rollout):
             if profiler is not None:
                 profiler.step(rid - 1)
@@ -759,6 +772,8 @@ class RLLoop:
                 break
         if profiler is not None:
             profiler.step(a.num_rollout - 1)  # closes a trace that runs to the last step
+        if self.host_profiler is not None:
+            self.host_profiler.stop()
         from .checkpoint import wait_for_async_save
 
         wait_for_async_save()  # a background save must be complete before the job ends

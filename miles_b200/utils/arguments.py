@@ -115,6 +115,8 @@ TRAINER_FLAGS = [
     ("--config", "s", None, {}), ("--fsdp-num-unit-buffers", "i", 2, {}),
     # destroy the trainer's NCCL sub-groups while the colocated engine generates, rebuild them before training
     ("--reload-process-groups", "b", False, {}),
+    # host-memory samples with phase marks, written as CSV by the first rank (tools/host_memory_profiler.py)
+    ("--profile-host-memory", "s", None, {}), ("--profile-host-memory-interval", "f", 0.5, {}),
     # native extensions of this framework
     ("--model-preset", "s", None, {}), ("--model-backend", "s", "auto", {"choices": ["auto", "b200", "torch"]}),
     ("--init-std", "f", 0.02, {}), ("--engine-page-size", "i", 64, {}), ("--engine-max-prefill-tokens", "i", 16384, {}),

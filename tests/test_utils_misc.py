@@ -296,3 +296,43 @@ def test_dp_schedule_balances_by_workload():
     per_rank0 = [sum(cost(lens[i]) for i in p) for p in s0.partitions]
     assert max(per_rank) / min(per_rank) <= max(per_rank0) / min(per_rank0) + 1e-9
     assert all(len(m) == s.num_microbatches[0] for m in s.micro_batches)
+
+
+def test_host_memory_profiler_marks_phases_and_summarises(tmp_path):
+    import time
+
+    from miles_b200.tools.host_memory_profiler import HostMemoryProfiler, main, summarize
+
+    out = tmp_path / "mem" / "profile.csv"
+    p = HostMemoryProfiler(str(out), interval=0.01).start()
+    p.mark("rollout")
+    blob = bytearray(32 << 20)  # something for the resident set to show
+    time.sleep(0.05)
+    p.mark("train")
+    time.sleep(0.05)
+    p.mark("rollout")
+    time.sleep(0.03)
+    recs = p.stop()
+    del blob
+    assert out.exists() and len(recs) >= 8
+    s = summarize(str(out))
+    assert [x["phase"] for x in s] == ["start", "rollout", "train"], "phases pooled by name, in order of first appearance"
+    roll = s[1]
+    assert roll["samples"] >= 4 and roll["seconds"] > 0.05 and roll["peak_process_rss_gib"] > 0.03
+    assert all(x["min_available_gib"] > 0 and x["peak_used_gib"] > 0 for x in s)
+    assert main([str(out)]) == 0 and main([]) == 2
+
+
+def test_training_loop_writes_a_host_memory_profile(tmp_path):
+    from miles_b200.loop import RLLoop
+    from miles_b200.tools.host_memory_profiler import summarize
+    from miles_b200.utils.arguments import parse_args
+
+    out = tmp_path / "host.csv"
+    args = parse_args(["--model-preset", "qwen3-tiny", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2",
+                       "--rollout-max-response-len", "8", "--rollout-max-prompt-len", "16", "--rm-type", "parity", "--lr", "1e-5",
+                       "--micro-batch-size", "4", "--colocate", "--num-rollout", "2", "--actor-num-gpus-per-node", "1",
+                       "--profile-host-memory", str(out), "--profile-host-memory-interval", "0.01"])
+    RLLoop(args).run()
+    phases = [x["phase"] for x in summarize(str(out))]
+    assert phases[:1] == ["start"] and {"rollout", "train", "update_weights"} <= set(phases)
