@@ -386,7 +386,7 @@ class B200Qwen3:
         cfg, P, C = self.cfg, self.store.params, self.C
         p = f"layers.{i}."
         if (meta is not None and not meta.is_prefill and x.shape[0] <= self.SMALL_T and replay_ids is None
-                and self.small_decode and self.tp is None):
+                and self.small_decode and self.tp is None and not cfg.post_norms):
             # the fused few-row MoE kernels serve plain softmax routers whose expert count fits their 16-column tiles
             plain_moe = cfg.router_score == "softmax" and not cfg.shared_expert_ffn and cfg.num_experts % 16 == 0
             if (self.ep is None and plain_moe) or not cfg.layer_is_moe(i):
@@ -429,6 +429,11 @@ class B200Qwen3:
             return y
         gu = self.linear(h2, P[p + "mlp.gate_up.weight"])
         self.launches += 1
+        if cfg.post_norms:
+            y = self.linear(C.swiglu_fwd(gu), P[p + "mlp.down.weight"])
+            yn, _ = C.rmsnorm_fwd(y, None, P[p + "post_mlp_ln.weight"], cfg.rms_eps)
+            self.launches += 2
+            return yn.add_(x2)
         return self._row_parallel(C.swiglu_fwd(gu), P[p + "mlp.down.weight"], x2)
 
     def _row_parallel(self, a, w, residual):
@@ -446,10 +451,18 @@ class B200Qwen3:
         p = f"layers.{i}."
         self.launches += 1
         if self.tp is not None:
+            assert not cfg.post_norms, "models with sandwich norms run without tensor parallelism"
             x2 = self._row_parallel(att2, P[p + "attn.o.weight"], x)
             h2, rstd2 = C.rmsnorm_fwd(x2, None, P[p + "ln2.weight"], cfg.rms_eps)
             return h2, rstd2, x2
         o = self.linear(att2, P[p + "attn.o.weight"])
+        if cfg.post_norms:
+            # sandwich norm (GLM-4 dense): the attention output is normalised before it joins the residual stream; the
+            # backward's recompute picks the un-normalised output and its statistics up from here
+            on, rstd_pa = C.rmsnorm_fwd(o, None, P[p + "post_attn_ln.weight"], cfg.rms_eps)
+            self._post_attn_saved = (o, rstd_pa)
+            self.launches += 1
+            return C.rmsnorm_fwd(on, x, P[p + "ln2.weight"], cfg.rms_eps)
         return C.rmsnorm_fwd(o, x, P[p + "ln2.weight"], cfg.rms_eps)
 
     def _col_parallel_dgrad(self, dy, w):
@@ -547,7 +560,10 @@ class B200Qwen3:
         att, lse = self.attention(q, k, v, cu)
         att2 = att.view(att.shape[0], -1)
         h2, rstd2, x2 = self._o_proj_ln2(i, att2, x)
+        post_attn = getattr(self, "_post_attn_saved", None) if cfg.post_norms else None
+        self._post_attn_saved = None
         is_moe = cfg.layer_is_moe(i)
+        assert not (is_moe and cfg.post_norms), "sandwich norms are wired for dense MLP layers"
         if is_moe:
             _, saved = self.moe_forward(i, h2, replay_ids, None, keep=True)
         else:
@@ -559,8 +575,14 @@ class B200Qwen3:
             dh2 = self.moe_backward(i, h2, dy, saved)
             del saved
         else:
-            dact = self.linear_dgrad(dy, P[p + "mlp.down.weight"])
-            self.linear_wgrad(dy, act, G[p + "mlp.down.weight"])
+            dyy = dy
+            if cfg.post_norms:  # through the norm on the MLP output (its input is recomputed)
+                y = self.linear(act, P[p + "mlp.down.weight"])
+                _, rstd_pm = C.rmsnorm_fwd(y, None, P[p + "post_mlp_ln.weight"], cfg.rms_eps)
+                dyy = C.rmsnorm_bwd(dy, y, P[p + "post_mlp_ln.weight"], rstd_pm, None, G[p + "post_mlp_ln.weight"], True)
+                self.launches += 3
+            dact = self.linear_dgrad(dyy, P[p + "mlp.down.weight"])
+            self.linear_wgrad(dyy, act, G[p + "mlp.down.weight"])
             dgu = C.swiglu_bwd(dact, gu)
             dh2 = self._col_parallel_dgrad(dgu, P[p + "mlp.gate_up.weight"])
             self.linear_wgrad(dgu, h2, G[p + "mlp.gate_up.weight"])
@@ -569,8 +591,13 @@ class B200Qwen3:
         dx2 = C.rmsnorm_bwd(dh2, x2, P[p + "ln2.weight"], rstd2, dy, G[p + "ln2.weight"], True)
         self.launches += 2
         # ---- attention output projection
-        datt = self.linear_dgrad(dx2, P[p + "attn.o.weight"])
-        self.linear_wgrad(dx2, att2, G[p + "attn.o.weight"])
+        do = dx2
+        if cfg.post_norms:  # through the norm on the attention output
+            o, rstd_pa = post_attn
+            do = C.rmsnorm_bwd(dx2, o, P[p + "post_attn_ln.weight"], rstd_pa, None, G[p + "post_attn_ln.weight"], True)
+            self.launches += 1
+        datt = self.linear_dgrad(do, P[p + "attn.o.weight"])
+        self.linear_wgrad(do, att2, G[p + "attn.o.weight"])
         dq, dk, dv = self.attention_backward(q, k, v, att, datt.view_as(att), lse, cu)
         if cfg.rope_scaling or cfg.rotary_dim:
             dqkv = C.qk_norm_rope_bwd_scaled(dq, dk, dv, qkv, P.get(p + "attn.q_norm.weight"),

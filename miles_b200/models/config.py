@@ -47,6 +47,12 @@ class ModelConfig:
     shared_expert_ffn: int = 0
     # rotary embedding on the first ``rotary_dim`` dimensions of every head only (0 = all of them)
     rotary_dim: int = 0
+    # GLM-4 dense: an extra RMSNorm on the attention output and on the MLP output before each joins the residual stream
+    post_norms: bool = False
+    # the checkpoint's query / key rows pair dimension 2i with 2i + 1 (GLM-4 dense); rows are de-interleaved when read and
+    # interleaved again when written, so that the model itself always rotates halves (attention scores do not change
+    # under a permutation applied to queries and keys alike)
+    rope_interleaved: bool = False
     max_position_embeddings: int = 40960
     # scaled rotary embeddings: None, {"rope_type": "llama3", "factor", "low_freq_factor", "high_freq_factor",
     # "original_max_position_embeddings"} or {"rope_type": "linear", "factor"}
@@ -76,7 +82,7 @@ class ModelConfig:
     def num_params(self) -> int:
         n = self.vocab_size * self.hidden_size * (1 if self.tie_embeddings else 2) + self.hidden_size
         for i in range(self.num_layers):
-            n += 2 * self.hidden_size + self.qkv_dim * self.hidden_size + self.q_dim * self.hidden_size
+            n += (4 if self.post_norms else 2) * self.hidden_size + self.qkv_dim * self.hidden_size + self.q_dim * self.hidden_size
             if self.qk_norm:
                 n += 2 * self.head_dim
             if self.qkv_bias:
@@ -127,6 +133,12 @@ class ModelConfig:
         }
         if self.rope_scaling:
             cfg["rope_scaling"] = dict(self.rope_scaling)
+        # token ids and similar keys of the checkpoint this model was read from travel back out unchanged
+        cfg.update(self.extra.get("hf_passthrough", {}))
+        if self.family in ("glm4", "glm4_moe") and "pad_token_id" not in cfg and self.vocab_size <= 151329:
+            cfg["pad_token_id"] = None  # the library's default padding id assumes the full GLM vocabulary
+        if self.family == "glm4":
+            cfg["partial_rotary_factor"] = (self.rotary_dim or self.head_dim) / self.head_dim
         if self.family == "glm4_moe":
             cfg.update({"n_routed_experts": self.num_experts, "num_experts_per_tok": self.moe_top_k,
                         "moe_intermediate_size": self.moe_ffn_hidden_size, "norm_topk_prob": self.norm_topk_prob,
@@ -166,9 +178,10 @@ class ModelConfig:
         mlp_only = cfg.get("mlp_only_layers") or []
         n_experts = cfg.get("num_experts", 0) or cfg.get("num_local_experts", 0) or cfg.get("n_routed_experts", 0) or 0
         glm = mtype == "glm4_moe"
+        glm_dense = mtype == "glm4"
         prf = cfg.get("partial_rotary_factor") or (cfg.get("rope_parameters") or {}).get("partial_rotary_factor") or 1.0
-        if not glm and float(prf) != 1.0:
-            raise NotImplementedError(f"partial rotary embedding is wired for glm4_moe only (got {prf} for {mtype})")
+        if not (glm or glm_dense) and float(prf) != 1.0:
+            raise NotImplementedError(f"partial rotary embedding is wired for the GLM families only (got {prf} for {mtype})")
         moe_ffn = cfg.get("moe_intermediate_size", 0) or (cfg.get("intermediate_size", 0) if mtype == "mixtral" else 0)
         if cfg.get("sliding_window") and cfg.get("use_sliding_window", mtype != "qwen2" and not is_qwen3) \
                 and cfg["sliding_window"] < cfg.get("max_position_embeddings", 0):
@@ -198,7 +211,7 @@ class ModelConfig:
             # newer HuggingFace configs keep the base inside "rope_parameters"; 10000 is the library-wide default
             rope_theta=float(cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta") or 10000.0),
             qk_norm=bool(cfg.get("use_qk_norm", False)) if glm else is_qwen3,
-            qkv_bias=bool(cfg.get("attention_bias", not is_qwen3 and "qwen2" in mtype)),
+            qkv_bias=bool(cfg.get("attention_bias", (not is_qwen3 and "qwen2" in mtype) or glm_dense)),
             tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
             num_experts=n_experts,
             moe_top_k=(cfg.get("num_experts_per_tok", 0) or 0) if n_experts else 0,
@@ -212,6 +225,8 @@ class ModelConfig:
             n_group=int(cfg.get("n_group", 1) or 1) if glm else 1, topk_group=int(cfg.get("topk_group", 1) or 1) if glm else 1,
             shared_expert_ffn=(int(cfg.get("n_shared_experts", 0) or 0) * moe_ffn) if glm else 0,
             rotary_dim=int(round(head_dim * float(prf))) if float(prf) != 1.0 else 0,
+            post_norms=glm_dense, rope_interleaved=glm_dense,
+            extra={"hf_passthrough": {k: cfg[k] for k in ("pad_token_id", "eos_token_id", "bos_token_id") if k in cfg}},
             max_position_embeddings=cfg.get("max_position_embeddings", 40960),
             rope_scaling=scaling,
             hf_architecture=arch,
@@ -222,7 +237,7 @@ class ModelConfig:
 HF_FAMILIES = {
     "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3_moe", "Qwen2ForCausalLM": "qwen2", "LlamaForCausalLM": "llama",
     "MistralForCausalLM": "mistral", "MixtralForCausalLM": "mixtral", "MiMoForCausalLM": "mimo",
-    "Glm4MoeForCausalLM": "glm4_moe",
+    "Glm4MoeForCausalLM": "glm4_moe", "Glm4ForCausalLM": "glm4",
 }
 
 
@@ -312,6 +327,15 @@ PRESETS: dict[str, ModelConfig] = {
                                     first_dense_layers=3, router_score="sigmoid", router_bias=True, routed_scaling_factor=2.5,
                                     shared_expert_ffn=1536, rotary_dim=64, max_position_embeddings=131072,
                                     hf_architecture="Glm4MoeForCausalLM"),
+    # GLM-4 dense (GLM-4-0414 / GLM-Z1): sandwich norms, rotary embedding on half of every head (interleaved in the checkpoint)
+    "glm4-9B": _dense("glm4-9B", 40, 4096, 32, 2, 13696, False, vocab=151552, qk_norm=False, qkv_bias=True, rope_theta=1e4,
+                      rms_eps=1e-5, rotary_dim=64, post_norms=True, rope_interleaved=True, max_position_embeddings=32768,
+                      hf_architecture="Glm4ForCausalLM"),
+    "glm4-32B": _dense("glm4-32B", 61, 6144, 48, 2, 23040, False, vocab=151552, qk_norm=False, qkv_bias=False, rope_theta=1e4,
+                       rms_eps=1e-5, rotary_dim=64, post_norms=True, rope_interleaved=True, max_position_embeddings=32768,
+                       hf_architecture="Glm4ForCausalLM"),
+    "glm4-smoke": _dense("glm4-smoke", 2, 512, 4, 2, 1024, False, vocab=4096, qk_norm=False, qkv_bias=True, rope_theta=1e4,
+                         rms_eps=1e-5, rotary_dim=64, post_norms=True, rope_interleaved=True, hf_architecture="Glm4ForCausalLM"),
     "glm4moe-smoke": ModelConfig(name="glm4moe-smoke", num_layers=3, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
                                  ffn_hidden_size=1024, vocab_size=4096, rms_eps=1e-5, rope_theta=1e6, qk_norm=True, qkv_bias=True,
                                  num_experts=16, moe_top_k=4, moe_ffn_hidden_size=256, first_dense_layers=1, router_score="sigmoid",

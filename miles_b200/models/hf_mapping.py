@@ -34,6 +34,10 @@ def to_hf(cfg: ModelConfig, name: str, t: torch.Tensor, expert_offset: int = 0) 
         return [(p + "input_layernorm.weight", t)]
     if rest == "ln2.weight":
         return [(p + "post_attention_layernorm.weight", t)]
+    if rest == "post_attn_ln.weight":
+        return [(p + "post_self_attn_layernorm.weight", t)]
+    if rest == "post_mlp_ln.weight":
+        return [(p + "post_mlp_layernorm.weight", t)]
     if rest in ("attn.qkv.weight", "attn.qkv.bias"):
         sfx = rest.rsplit(".", 1)[1]
         return [(p + f"self_attn.q_proj.{sfx}", t[:q]), (p + f"self_attn.k_proj.{sfx}", t[q:q + kv]),
@@ -44,6 +48,8 @@ def to_hf(cfg: ModelConfig, name: str, t: torch.Tensor, expert_offset: int = 0) 
         return [(p + "self_attn.k_norm.weight", t)]
     if rest == "attn.o.weight":
         return [(p + "self_attn.o_proj.weight", t)]
+    if rest == "mlp.gate_up.weight" and getattr(cfg, "family", "") == "glm4":
+        return [(p + "mlp.gate_up_proj.weight", t)]  # fused in the checkpoint too: gate rows, then up rows
     if rest == "mlp.gate_up.weight":
         I = t.shape[0] // 2
         return [(p + "mlp.gate_proj.weight", t[:I]), (p + "mlp.up_proj.weight", t[I:])]
@@ -76,6 +82,33 @@ def to_hf(cfg: ModelConfig, name: str, t: torch.Tensor, expert_offset: int = 0) 
     raise KeyError(name)
 
 
+def _rope_rows(cfg: ModelConfig, t: torch.Tensor, heads: int, to_checkpoint: bool) -> torch.Tensor:
+    """Reorder the rotary rows of a query / key projection (weight ``[heads * D, H]`` or bias ``[heads * D]``) between the
+    checkpoint's interleaved pairing (2i with 2i + 1) and the model's halves (i with i + R / 2). Returns a new tensor."""
+    D, R = cfg.head_dim, (cfg.rotary_dim or cfg.head_dim)
+    x = t.reshape(heads, D, *t.shape[1:]).clone()
+    rot = x[:, :R]
+    if to_checkpoint:
+        out = torch.empty_like(rot)
+        out[:, 0::2], out[:, 1::2] = rot[:, :R // 2], rot[:, R // 2:]
+    else:
+        out = torch.cat([rot[:, 0::2], rot[:, 1::2]], dim=1)
+    x[:, :R] = out
+    return x.reshape(t.shape)
+
+
+def _rope_heads(cfg: ModelConfig, hf_name: str) -> int:
+    """How many heads a HuggingFace tensor's rotary rows cover, 0 for tensors without any (models whose checkpoints pair
+    rotary dimensions like the model does need nothing)."""
+    if not getattr(cfg, "rope_interleaved", False):
+        return 0
+    if ".self_attn.q_proj." in hf_name:
+        return cfg.num_q_heads
+    if ".self_attn.k_proj." in hf_name:
+        return cfg.num_kv_heads
+    return 0
+
+
 def hf_names(cfg: ModelConfig, store, tp_group=None) -> Iterator[tuple]:
     """Iterate (hf_name, tensor) over every local parameter of ``store``. Under tensor parallelism the sharded
     tensors are gathered over ``tp_group`` first (a collective: every rank of the group must iterate), which is
@@ -92,8 +125,9 @@ def hf_names(cfg: ModelConfig, store, tp_group=None) -> Iterator[tuple]:
             parts = [torch.empty_like(t) for _ in range(tp)]
             dist.all_gather(parts, t.contiguous(), group=tp_group)
             t = tp_merge(gcfg, name, parts)
-        for item in to_hf(gcfg, name, t, expert_offset=store.ep_rank * el):
-            yield item
+        for hf_name, view in to_hf(gcfg, name, t, expert_offset=store.ep_rank * el):
+            heads = _rope_heads(gcfg, hf_name)
+            yield (hf_name, _rope_rows(gcfg, view, heads, to_checkpoint=True) if heads else view)
 
 
 def param_or_hf_view(cfg: ModelConfig, store, name: str) -> torch.Tensor:
@@ -105,6 +139,9 @@ def param_or_hf_view(cfg: ModelConfig, store, name: str) -> torch.Tensor:
     miles/backends/megatron_utils/update_weight/common.py:21-131)."""
     if name in store.params:
         return store.params[name]
+    if _rope_heads(getattr(store, "global_cfg", cfg), name):
+        raise NotImplementedError(f"{name}: this model's checkpoints interleave rotary rows; send the fused native parameter "
+                                  "(attn.qkv.weight) instead of the HuggingFace piece")
     views = getattr(store, "_hf_views", None)
     if views is None:
         assert getattr(store, "tp_size", 1) == 1, "HF-named updates address unsharded parameters"
@@ -139,7 +176,8 @@ def from_hf(cfg: ModelConfig, store, get_tensor, strict: bool = True) -> int:
                         if strict:
                             raise KeyError(f"missing tensor {hf_name} in checkpoint")
                         continue
-                    view.copy_(src.to(view.dtype))
+                    heads = _rope_heads(gcfg, hf_name)
+                    view.copy_((_rope_rows(gcfg, src, heads, to_checkpoint=False) if heads else src).to(view.dtype))
                     n += 1
                 dst.copy_(tp_slice(gcfg, name, full, tp, store.tp_rank))
                 continue
@@ -152,6 +190,7 @@ def from_hf(cfg: ModelConfig, store, get_tensor, strict: bool = True) -> int:
                         if strict:
                             raise KeyError(f"missing tensor {hf_name} in checkpoint")
                         continue
-                view.copy_(src.to(view.dtype))
+                heads = _rope_heads(gcfg, hf_name)
+                view.copy_((_rope_rows(gcfg, src, heads, to_checkpoint=False) if heads else src).to(view.dtype))
                 n += 1
     return n

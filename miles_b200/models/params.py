@@ -72,6 +72,9 @@ def build_specs(cfg: ModelConfig, ep_size: int = 1, layers: Optional[tuple] = No
             specs.append(ParamSpec(p + "attn.q_norm.weight", (D,), "dense", "ones"))
             specs.append(ParamSpec(p + "attn.k_norm.weight", (D,), "dense", "ones"))
         specs.append(ParamSpec(p + "attn.o.weight", (H, cfg.q_dim), "dense", "normal"))
+        if getattr(cfg, "post_norms", False):
+            specs.append(ParamSpec(p + "post_attn_ln.weight", (H,), "dense", "ones"))
+            specs.append(ParamSpec(p + "post_mlp_ln.weight", (H,), "dense", "ones"))
         specs.append(ParamSpec(p + "ln2.weight", (H,), "dense", "ones"))
         if cfg.layer_is_moe(i):
             el = cfg.num_experts // ep_size

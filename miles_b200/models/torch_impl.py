@@ -141,6 +141,8 @@ class TorchQwen3:
                 outs.append(R.attention_prefix(q[b:b + 1], kc[slots].to(q.dtype), vc[slots].to(q.dtype), L - 1, scale))
             att = torch.cat(outs, 0)
         o = F.linear(att.reshape(att.shape[0], -1), P[p + "attn.o.weight"])
+        if getattr(cfg, "post_norms", False):
+            o = R.rmsnorm(o, P[p + "post_attn_ln.weight"], cfg.rms_eps)
         return x + o
 
     def _mlp_block(self, i, x, replay_ids=None, record=None):
@@ -161,6 +163,8 @@ class TorchQwen3:
                 y = y + F.linear(R.swiglu(F.linear(h, P[p + "moe.shared.gate_up.weight"])), P[p + "moe.shared.down.weight"])
         else:
             y = F.linear(R.swiglu(F.linear(h, P[p + "mlp.gate_up.weight"])), P[p + "mlp.down.weight"])
+        if getattr(cfg, "post_norms", False):
+            y = R.rmsnorm(y, P[p + "post_mlp_ln.weight"], cfg.rms_eps)
         return x + y
 
     # ------------------------------------------------------------------ forward
