@@ -90,6 +90,7 @@ class SessionStore:
         traj.append_generation(ids, lps, out.get("weight_version"), out.get("finish_reason"))
         traj.num_messages = len(messages) + 1
         text = self.tok.decode(ids, skip_special_tokens=True) if hasattr(self.tok, "decode") else ""
+        traj.messages = list(messages) + [{"role": "assistant", "content": text}]  # what /verify renders afresh
         return {"text": text, "ids": ids, "finish_reason": out.get("finish_reason", "stop")}
 
     def _chat_tree(self, sid: str, messages: list, sampling_params: dict) -> dict:
@@ -256,6 +257,20 @@ def build_session_app(store: SessionStore, model_name: str = "policy", created_o
     @app.get("/sessions/{sid}")
     async def get_session(sid: str):
         return _meta(sid)
+
+    @app.get("/sessions/{sid}/verify")
+    async def verify(sid: str):
+        """Token-level sessions: compare the incremental trajectory with a fresh rendering of the conversation, difference
+        by difference (session/compare.py). ``ok`` is false when anything but assistant text differs."""
+        t = store.sessions.get(sid)
+        if t is None:
+            raise HTTPException(SessionNotFoundError.status_code, f"unknown session {sid}")
+        if store.tito is None or not getattr(t, "messages", None):
+            return {"session_id": sid, "checked": False, "ok": True, "mismatches": []}
+        # the fresh rendering ends with a generation header the trajectory does not have yet: compare up to the last turn
+        found = store.tito.diagnose(list(t.tokens) + store.tito.boundary_fix(t.tokens[t.turns[-1].start:t.turns[-1].end])
+                                    + store.tito.header_ids("assistant"), t.messages)
+        return {"session_id": sid, "checked": True, "ok": not any(m.severe for m in found), "mismatches": [m.to_dict() for m in found]}
 
     @app.get("/sessions/{sid}/samples")
     async def collect_samples(sid: str, max_seq_len: Optional[int] = None):

@@ -35,6 +35,10 @@ FAMILIES = {
     "chatml": Family("<|im_end|>", "\n", "<|im_start|>{role}\n"),
     "qwen3": Family("<|im_end|>", "\n", "<|im_start|>{role}\n", rewrites_history=True),  # drops earlier <think> blocks
     "llama3": Family("<|eot_id|>", "", "<|start_header_id|>{role}<|end_header_id|>\n\n"),
+    # GLM-4 / GLM-4.5: roles are special tokens, a turn ends where the next role token starts (no end-of-turn token of its
+    # own: generation stops at <|user|> / <|observation|>, which then open the next turn)
+    "glm4": Family("", "", "<|{role}|>\n", rewrites_history=True),
+    "mistral": Family("</s>", "", "[INST] "),  # user turns are wrapped, assistant text follows " [/INST]" (see header_ids)
     "generic": Family("<|end|>", "", "<|{role}|>"),
 }
 
@@ -46,6 +50,10 @@ def detect_family(tokenizer: Any) -> str:
         return "qwen3" if ("qwen3" in name or "<think>" in tpl) else "chatml"
     if "<|start_header_id|>" in tpl:
         return "llama3"
+    if "<|assistant|>" in tpl and "<|user|>" in tpl:
+        return "glm4"
+    if "[INST]" in tpl:
+        return "mistral"
     return "generic"
 
 
@@ -101,6 +109,29 @@ class TitoTokenizer:
         for m in new_messages:
             ids += self.message_ids(m)
         return ids + self.header_ids("assistant")
+
+    def special_ids(self) -> set:
+        """Ids the tokenizer treats as special (turn openers, end-of-turn tokens, role tokens ...)."""
+        ids = set(getattr(self.tok, "all_special_ids", None) or [])
+        added = getattr(self.tok, "added_tokens_decoder", None) or {}
+        ids.update(int(i) for i, t in added.items() if getattr(t, "special", True))
+        for text in (self.family.turn_end,):
+            e = self._enc(text)
+            if len(e) == 1:
+                ids.add(e[0])
+        extra = getattr(self.tok, "special_token_ids", None)  # simple tokenizers of tests declare theirs like this
+        ids.update(extra or [])
+        return ids
+
+    def diagnose(self, trajectory_ids: Sequence[int], messages: Sequence[dict]) -> list:
+        """Differences between the incremental trajectory and a fresh rendering of the whole conversation, classified
+        (session/compare.py): text of assistant turns may differ harmlessly, anything else is a defect of the incremental
+        path (or of this family's boundary tokens)."""
+        from .compare import compare
+
+        expected = self._enc(self._render(messages, True))
+        dec = (lambda ids: self.tok.decode(list(ids))) if hasattr(self.tok, "decode") else (lambda ids: " ".join(map(str, ids)))
+        return compare(expected, list(trajectory_ids), self.special_ids(), dec)
 
     def consistent_with_template(self, trajectory_ids: Sequence[int], messages: Sequence[dict]) -> Optional[bool]:
         """Whether the incremental ids equal a fresh rendering of the whole conversation; None for families whose

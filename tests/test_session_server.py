@@ -126,3 +126,37 @@ def test_session_lifecycle_endpoints_streaming_and_length_cap():
     assert c.post(f"/sessions/{sid}/v1/chat/completions", json={"messages": "not a list"}).status_code == 400
     strict = TestClient(build_session_app(store, created_only=True))
     assert strict.post("/sessions/unknown/v1/chat/completions", json={"messages": m1}).status_code == 404
+
+
+def test_verify_endpoint_diagnoses_a_token_level_session():
+    """/sessions/{sid}/verify: the incremental trajectory against a fresh rendering; only assistant-text differences are ok."""
+    import sys
+    import os
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from fastapi.testclient import TestClient
+    from test_tito import ToyTokenizer
+
+    tok = ToyTokenizer()
+    tok.special_token_ids = {tok._id(s) for s in tok.SPECIALS}
+    replies = iter(["a|bc<|im_end|>", "d|ef<|im_end|>"])  # "|" marks where the engine split the text its own way
+
+    def generate(input_ids, sp):
+        parts = next(replies).split("|")
+        ids = [t for part in parts for t in tok.encode(part)]
+        return {"output_ids": ids, "output_token_logprobs": [(-0.1, 0)] * len(ids), "finish_reason": {"type": "stop"}, "weight_version": 1}
+
+    store = SessionStore(tok, generate, tito=True, family="chatml")
+    c = TestClient(build_session_app(store))
+    m1 = [{"role": "user", "content": "hello"}]
+    c.post("/sessions/v/v1/chat/completions", json={"messages": m1})
+    m2 = m1 + [{"role": "assistant", "content": "abc"}, {"role": "user", "content": "more"}]
+    c.post("/sessions/v/v1/chat/completions", json={"messages": m2})
+    out = c.get("/sessions/v/verify").json()
+    assert out["checked"] and out["ok"], out
+    assert {m["kind"] for m in out["mismatches"]} <= {"assistant_text"} and len(out["mismatches"]) >= 1
+    # damage a context token: the check names it
+    store.sessions["v"].tokens[2] = tok._id("zz")
+    bad = c.get("/sessions/v/verify").json()
+    assert not bad["ok"] and any(m["kind"] == "context_text" and m["severe"] for m in bad["mismatches"])
+    assert c.get("/sessions/none/verify").status_code == 404

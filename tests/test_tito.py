@@ -164,3 +164,71 @@ def test_agentic_generate_builds_a_masked_multi_turn_sample():
     # the second request continued from the exact tokens of the first turn, and honoured the per-call token cap
     assert seen[1]["input_ids"][:len(seen[0]["input_ids"])] == seen[0]["input_ids"]
     assert seen[1]["sampling_params"]["max_new_tokens"] == 8
+
+
+def _special_ids(tok):
+    return {tok._id(s) for s in tok.SPECIALS}
+
+
+def test_comparator_classifies_differences_by_segment():
+    from miles_b200.rollout.session.compare import compare, segment
+
+    tok = ToyTokenizer()
+    sp = _special_ids(tok)
+    full = "<|im_start|>user\nhello<|im_end|>\n<|im_start|>assistant\nabc<|im_end|>\n"
+    exp = tok.encode(full)
+    segs = segment(exp, sp)
+    assert [s.special for s in segs] == [True, False, True, False, True, False, True, False]
+    assert compare(exp, list(exp), sp, tok.decode) == []
+    # the same assistant text under another token split (generated ids kept as emitted): harmless
+    a_ids = tok.encode("<|im_start|>user\nhello<|im_end|>\n<|im_start|>assistant\n") + tok.encode("a") + tok.encode("bc") + tok.encode("<|im_end|>\n")
+    ms = compare(exp, a_ids, sp, tok.decode)
+    assert [m.kind for m in ms] == ["assistant_text"] and not ms[0].severe and "another token split" in ms[0].detail
+    # other user text: a defect
+    b_ids = tok.encode(full.replace("hello", "hellx"))
+    ms = compare(exp, b_ids, sp, tok.decode)
+    assert [m.kind for m in ms] == ["context_text"] and ms[0].severe and ms[0].expected.endswith("hello") and ms[0].to_dict()["severe"]
+    # a missing end-of-turn token changes the skeleton
+    c_ids = tok.encode(full.replace("abc<|im_end|>", "abc"))
+    ms = compare(exp, c_ids, sp, tok.decode)
+    assert [m.kind for m in ms] == ["structure"] and "4 special tokens expected, 3 found" in ms[0].detail
+    # another special token at the same place
+    d_ids = list(exp)
+    d_ids[0] = tok._id("<|im_end|>")
+    assert [m.kind for m in compare(exp, d_ids, sp, tok.decode)] == ["special_token"]
+
+
+def test_diagnose_reports_only_harmless_differences_for_a_correct_session():
+    tok = ToyTokenizer()
+    tok.special_token_ids = None
+    t = TitoTokenizer(tok, "chatml")
+    tok.special_token_ids = _special_ids(tok)
+    msgs = [{"role": "user", "content": "hello"}]
+    traj = t.initial(msgs)
+    gen = tok.encode("a") + tok.encode("bc") + tok.encode("<|im_end|>")  # the engine split "abc" its own way
+    traj += gen
+    new = [{"role": "user", "content": "more"}]
+    traj += t.continuation(gen, new)
+    msgs2 = msgs + [{"role": "assistant", "content": "abc"}] + new
+    found = t.diagnose(traj, msgs2)
+    assert [m.kind for m in found] == ["assistant_text"] and not any(m.severe for m in found)
+    assert t.consistent_with_template(traj, msgs2) is False  # the plain equality check cannot tell harmless from broken
+    # a corrupted context turn is found and named
+    bad = list(traj)
+    bad[2] = tok._id("zz")
+    assert any(m.kind == "context_text" for m in t.diagnose(bad, msgs2))
+
+
+def test_new_families_are_detected_from_their_templates():
+    from miles_b200.rollout.session.tito import detect_family
+
+    class T:
+        name_or_path = "x"
+
+        def __init__(self, tpl):
+            self.chat_template = tpl
+
+    assert detect_family(T("[gMASK]<sop>{% for m in messages %}<|user|>\n...<|assistant|>")) == "glm4"
+    assert detect_family(T("{{ bos_token }}[INST] {{ m }} [/INST]")) == "mistral"
+    assert detect_family(T("<|start_header_id|>")) == "llama3"
+    assert set(FAMILIES) >= {"chatml", "qwen3", "llama3", "glm4", "mistral", "generic"}
