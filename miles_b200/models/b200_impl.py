@@ -252,6 +252,10 @@ class B200Qwen3:
             # the shared expert sees every token: its output joins the residual that the combine adds
             sh_gu = self.linear(h2, P[p + "shared.gate_up.weight"])
             sh_y = self.linear(C.swiglu_fwd(sh_gu), P[p + "shared.down.weight"])
+            if cfg.shared_expert_gate:  # one sigmoid gate value per token (a [T, H] x [H] product: framework ops)
+                g = torch.sigmoid(h2.float() @ P[p + "shared.gate.weight"].float().t())
+                sh_y = (sh_y.float() * g).to(sh_y.dtype)
+                self.launches += 3
             residual = sh_y.add_(residual) if residual is not None else sh_y
             self.launches += 3
         if self.ep is not None:
@@ -295,6 +299,17 @@ class B200Qwen3:
         dyb = dy if dy.dtype == torch.bfloat16 else dy.to(torch.bfloat16)
         gu = self.linear(h2, wgu)
         act = C.swiglu_fwd(gu)
+        if cfg.shared_expert_gate:
+            # y = g * s with g = sigmoid(h2 . w_g), s the shared expert's output (recomputed): ds = g dy,
+            # d(logit) = (dy . s) g (1 - g), which reaches w_g and h2
+            wg = P[p + "gate.weight"]
+            s = self.linear(act, wd).float()
+            g = torch.sigmoid(h2.float() @ wg.float().t())
+            dlogit = (dy.float() * s).sum(-1, keepdim=True) * g * (1.0 - g)
+            G[p + "gate.weight"].add_((dlogit.t() @ h2.float()).to(G[p + "gate.weight"].dtype))
+            dh2.add_((dlogit @ wg.float()).to(dh2.dtype))
+            dyb = (dy.float() * g).to(torch.bfloat16)
+            self.launches += 8
         self.linear_wgrad(dyb, act, G[p + "down.weight"])
         dgu = C.swiglu_bwd(self.linear_dgrad(dyb, wd), gu)
         self.linear_wgrad(dgu, h2, G[p + "gate_up.weight"])

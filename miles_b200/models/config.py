@@ -45,6 +45,8 @@ class ModelConfig:
     topk_group: int = 1
     # a dense SwiGLU expert of this width that every token passes through, added to the routed experts' output
     shared_expert_ffn: int = 0
+    # Qwen2-MoE: the shared expert's output is scaled per token by sigmoid(hidden . gate vector)
+    shared_expert_gate: bool = False
     # rotary embedding on the first ``rotary_dim`` dimensions of every head only (0 = all of them)
     rotary_dim: int = 0
     # GLM-4 dense: an extra RMSNorm on the attention output and on the MLP output before each joins the residual stream
@@ -90,7 +92,7 @@ class ModelConfig:
             if self.layer_is_moe(i):
                 n += self.num_experts * self.hidden_size + (self.num_experts if self.router_bias else 0)
                 n += self.num_experts * 3 * self.moe_ffn_hidden_size * self.hidden_size
-                n += 3 * self.shared_expert_ffn * self.hidden_size
+                n += 3 * self.shared_expert_ffn * self.hidden_size + (self.hidden_size if self.shared_expert_gate else 0)
             else:
                 n += 3 * self.ffn_hidden_size * self.hidden_size
         return n
@@ -146,6 +148,11 @@ class ModelConfig:
                         "routed_scaling_factor": self.routed_scaling_factor, "n_group": self.n_group, "topk_group": self.topk_group,
                         "first_k_dense_replace": self.first_dense_layers, "use_qk_norm": self.qk_norm,
                         "partial_rotary_factor": (self.rotary_dim or self.head_dim) / self.head_dim})
+        elif self.family == "qwen2_moe":
+            cfg.update({"num_experts": self.num_experts, "num_experts_per_tok": self.moe_top_k,
+                        "moe_intermediate_size": self.moe_ffn_hidden_size, "norm_topk_prob": self.norm_topk_prob,
+                        "shared_expert_intermediate_size": self.shared_expert_ffn, "decoder_sparse_step": self.moe_layer_freq,
+                        "mlp_only_layers": list(range(self.first_dense_layers))})
         elif self.family == "mixtral":
             cfg.update({"num_local_experts": self.num_experts, "num_experts_per_tok": self.moe_top_k,
                         "intermediate_size": self.moe_ffn_hidden_size, "sliding_window": None})
@@ -217,13 +224,15 @@ class ModelConfig:
             moe_top_k=(cfg.get("num_experts_per_tok", 0) or 0) if n_experts else 0,
             moe_ffn_hidden_size=moe_ffn,
             # Mixtral takes the softmax over the chosen experts only, which equals renormalising the full softmax
-            norm_topk_prob=True if mtype == "mixtral" else bool(cfg.get("norm_topk_prob", True)),
+            norm_topk_prob=True if mtype == "mixtral" else bool(cfg.get("norm_topk_prob", mtype != "qwen2_moe")),
             moe_layer_freq=cfg.get("decoder_sparse_step", 1) or 1,
             first_dense_layers=int(cfg.get("first_k_dense_replace", 0) or 0) if glm else ((max(mlp_only) + 1) if mlp_only else 0),
             router_score="sigmoid" if glm else "softmax", router_bias=glm,
             routed_scaling_factor=float(cfg.get("routed_scaling_factor", 1.0) or 1.0) if glm else 1.0,
             n_group=int(cfg.get("n_group", 1) or 1) if glm else 1, topk_group=int(cfg.get("topk_group", 1) or 1) if glm else 1,
-            shared_expert_ffn=(int(cfg.get("n_shared_experts", 0) or 0) * moe_ffn) if glm else 0,
+            shared_expert_ffn=((int(cfg.get("n_shared_experts", 0) or 0) * moe_ffn) if glm
+                               else int(cfg.get("shared_expert_intermediate_size", 0) or 0) if mtype == "qwen2_moe" else 0),
+            shared_expert_gate=mtype == "qwen2_moe",
             rotary_dim=int(round(head_dim * float(prf))) if float(prf) != 1.0 else 0,
             post_norms=glm_dense, rope_interleaved=glm_dense,
             extra={"hf_passthrough": {k: cfg[k] for k in ("pad_token_id", "eos_token_id", "bos_token_id") if k in cfg}},
@@ -237,7 +246,7 @@ class ModelConfig:
 HF_FAMILIES = {
     "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3_moe", "Qwen2ForCausalLM": "qwen2", "LlamaForCausalLM": "llama",
     "MistralForCausalLM": "mistral", "MixtralForCausalLM": "mixtral", "MiMoForCausalLM": "mimo",
-    "Glm4MoeForCausalLM": "glm4_moe", "Glm4ForCausalLM": "glm4",
+    "Glm4MoeForCausalLM": "glm4_moe", "Glm4ForCausalLM": "glm4", "Qwen2MoeForCausalLM": "qwen2_moe",
 }
 
 
@@ -327,6 +336,16 @@ PRESETS: dict[str, ModelConfig] = {
                                     first_dense_layers=3, router_score="sigmoid", router_bias=True, routed_scaling_factor=2.5,
                                     shared_expert_ffn=1536, rotary_dim=64, max_position_embeddings=131072,
                                     hf_architecture="Glm4MoeForCausalLM"),
+    # Qwen2-MoE (Qwen1.5-MoE-A2.7B, Qwen2-57B-A14B): softmax router without renormalisation, a gated shared expert
+    "qwen2-57B-A14B": ModelConfig(name="qwen2-57B-A14B", num_layers=28, hidden_size=3584, num_q_heads=28, num_kv_heads=4, head_dim=128,
+                                  ffn_hidden_size=18944, vocab_size=151936, rms_eps=1e-6, rope_theta=1e6, qk_norm=False, qkv_bias=True,
+                                  num_experts=64, moe_top_k=8, moe_ffn_hidden_size=2560, norm_topk_prob=False,
+                                  shared_expert_ffn=20480, shared_expert_gate=True, max_position_embeddings=32768,
+                                  hf_architecture="Qwen2MoeForCausalLM"),
+    "qwen2moe-smoke": ModelConfig(name="qwen2moe-smoke", num_layers=2, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                                  ffn_hidden_size=1024, vocab_size=4096, rms_eps=1e-6, qk_norm=False, qkv_bias=True, num_experts=16,
+                                  moe_top_k=4, moe_ffn_hidden_size=256, norm_topk_prob=False, shared_expert_ffn=512,
+                                  shared_expert_gate=True, hf_architecture="Qwen2MoeForCausalLM"),
     # GLM-4 dense (GLM-4-0414 / GLM-Z1): sandwich norms, rotary embedding on half of every head (interleaved in the checkpoint)
     "glm4-9B": _dense("glm4-9B", 40, 4096, 32, 2, 13696, False, vocab=151552, qk_norm=False, qkv_bias=True, rope_theta=1e4,
                       rms_eps=1e-5, rotary_dim=64, post_norms=True, rope_interleaved=True, max_position_embeddings=32768,

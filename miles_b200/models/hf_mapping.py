@@ -57,11 +57,14 @@ def to_hf(cfg: ModelConfig, name: str, t: torch.Tensor, expert_offset: int = 0) 
         return [(p + "mlp.down_proj.weight", t)]
     if rest == "moe.router.bias":
         return [(p + "mlp.gate.e_score_correction_bias", t)]
+    shared = "mlp.shared_expert." if getattr(cfg, "family", "") == "qwen2_moe" else "mlp.shared_experts."
     if rest == "moe.shared.gate_up.weight":
         I = t.shape[0] // 2
-        return [(p + "mlp.shared_experts.gate_proj.weight", t[:I]), (p + "mlp.shared_experts.up_proj.weight", t[I:])]
+        return [(p + shared + "gate_proj.weight", t[:I]), (p + shared + "up_proj.weight", t[I:])]
     if rest == "moe.shared.down.weight":
-        return [(p + "mlp.shared_experts.down_proj.weight", t)]
+        return [(p + shared + "down_proj.weight", t)]
+    if rest == "moe.shared.gate.weight":
+        return [(p + "mlp.shared_expert_gate.weight", t)]
     mixtral = getattr(cfg, "family", "") == "mixtral"  # block_sparse_moe.{gate, experts.N.w1 (gate) / w3 (up) / w2 (down)}
     if rest == "moe.router.weight":
         return [(p + ("block_sparse_moe.gate.weight" if mixtral else "mlp.gate.weight"), t)]

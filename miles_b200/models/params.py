@@ -86,6 +86,8 @@ def build_specs(cfg: ModelConfig, ep_size: int = 1, layers: Optional[tuple] = No
                 Is = cfg.shared_expert_ffn
                 specs.append(ParamSpec(p + "moe.shared.gate_up.weight", (2 * Is, H), "dense", "normal"))
                 specs.append(ParamSpec(p + "moe.shared.down.weight", (H, Is), "dense", "normal"))
+                if getattr(cfg, "shared_expert_gate", False):
+                    specs.append(ParamSpec(p + "moe.shared.gate.weight", (1, H), "dense", "normal"))
             specs.append(ParamSpec(p + "moe.w1", (el, 2 * I, H), "expert", "normal"))
             specs.append(ParamSpec(p + "moe.w2", (el, H, I), "expert", "normal"))
         else:

@@ -160,7 +160,10 @@ class TorchQwen3:
                 record.append(ids)
             y = R.moe_experts(h, ids, w.to(h.dtype) if h.dtype != torch.float32 else w, P[p + "moe.w1"], P[p + "moe.w2"])
             if getattr(cfg, "shared_expert_ffn", 0):
-                y = y + F.linear(R.swiglu(F.linear(h, P[p + "moe.shared.gate_up.weight"])), P[p + "moe.shared.down.weight"])
+                sh = F.linear(R.swiglu(F.linear(h, P[p + "moe.shared.gate_up.weight"])), P[p + "moe.shared.down.weight"])
+                if getattr(cfg, "shared_expert_gate", False):
+                    sh = torch.sigmoid(F.linear(h, P[p + "moe.shared.gate.weight"])) * sh
+                y = y + sh
         else:
             y = F.linear(R.swiglu(F.linear(h, P[p + "mlp.gate_up.weight"])), P[p + "mlp.down.weight"])
         if getattr(cfg, "post_norms", False):

@@ -307,6 +307,12 @@ class TrainActor:
             plan["name"] += ", no fp32 master"
         if self.fsdp and getattr(a, "fsdp_cpu_offload", False):
             plan["offload"], plan["resident_frac"] = True, 0.0
+            if not self.store.sizes.get("expert"):
+                import warnings
+
+                # host-resident optimizer state is built for the expert group (where the bulk of a MoE model's state
+                # lives and one weight-decay value covers the whole buffer); a dense model's shards stay on the device
+                warnings.warn("--fsdp-cpu-offload: this model has no expert parameters, its optimizer state shards stay on the device")
         if getattr(a, "optimizer_cpu_offload", False) or getattr(a, "offload_optimizer_states", False):
             plan["offload"], plan["resident_frac"] = True, 0.0
         if getattr(a, "accumulate_allreduce_grads_in_fp32", False) and self.on_gpu and self.cfg.is_moe:

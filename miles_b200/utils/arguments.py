@@ -486,6 +486,7 @@ def _check_architecture_flags(args, cfg):
     given = [("moe_router_score_function", cfg.router_score if moe else "softmax", "softmax"),
              ("moe_router_enable_expert_bias", bool(cfg.router_bias), False),
              ("moe_shared_expert_intermediate_size", cfg.shared_expert_ffn or None, None),
+             ("moe_shared_expert_gate", bool(cfg.shared_expert_gate), False),
              ("moe_router_topk_scaling_factor", cfg.routed_scaling_factor if cfg.routed_scaling_factor != 1.0 else None, None),
              ("moe_router_num_groups", cfg.n_group if cfg.n_group != 1 else None, None),
              ("moe_router_group_topk", cfg.topk_group if cfg.n_group != 1 else None, None),
@@ -538,6 +539,7 @@ def model_config_from_args(args):
         routed_scaling_factor=float(getattr(args, "moe_router_topk_scaling_factor", None) or 1.0),
         n_group=int(getattr(args, "moe_router_num_groups", None) or 1), topk_group=int(getattr(args, "moe_router_group_topk", None) or 1),
         shared_expert_ffn=int(getattr(args, "moe_shared_expert_intermediate_size", None) or 0) if moe else 0,
+        shared_expert_gate=bool(getattr(args, "moe_shared_expert_gate", False)) and moe,
         first_dense_layers=_first_dense_layers(getattr(args, "moe_layer_freq", "1"), args.num_layers) if moe else 0,
         rotary_dim=(int(round((args.kv_channels or args.hidden_size // heads) * float(args.rotary_percent)))
                     if float(getattr(args, "rotary_percent", 1.0) or 1.0) != 1.0 else 0),

@@ -41,7 +41,6 @@ REJECT = {
     "moe_router_bias_update_rate": "updating the router's selection bias from the expert load (the bias is loaded and kept)",
     "moe_router_load_balancing_type": "router load-balancing losses",
     "moe_aux_loss_coeff": "router auxiliary loss",
-    "moe_shared_expert_gate": "a gate on the shared expert's output (Qwen2-MoE style)",
     "moe_latent_size": "latent MoE",
     "moe_token_drop_policy": "token dropping (the dispatch here is dropless)",
     "mtp_num_layers": "multi-token-prediction layers",

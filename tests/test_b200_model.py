@@ -23,7 +23,7 @@ def _batch(cfg, lens, dev, seed=0):
     return tokens.int(), pos.int(), cu, torch.cat(rows).to(dev), torch.cat(tg).to(dev)
 
 
-@pytest.mark.parametrize("name", ["qwen3-smoke", "qwen3-smoke-moe", "llama3-smoke", "mixtral-smoke", "glm4moe-smoke", "glm4-smoke"])
+@pytest.mark.parametrize("name", ["qwen3-smoke", "qwen3-smoke-moe", "llama3-smoke", "mixtral-smoke", "glm4moe-smoke", "glm4-smoke", "qwen2moe-smoke"])
 def test_forward_backward_matches_autograd(name):
     dev = torch.device("cuda")
     cfg = get_config(name)

@@ -12,7 +12,7 @@ from miles_b200.ops import reference as R
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("name", ["qwen3-smoke", "qwen3-smoke-moe", "llama3-smoke", "mixtral-smoke", "glm4moe-smoke", "glm4-smoke"])
+@pytest.mark.parametrize("name", ["qwen3-smoke", "qwen3-smoke-moe", "llama3-smoke", "mixtral-smoke", "glm4moe-smoke", "glm4-smoke", "qwen2moe-smoke"])
 @pytest.mark.parametrize("graph", [False, True])
 def test_engine_trainer_logprob_parity(name, graph):
     dev = torch.device("cuda")

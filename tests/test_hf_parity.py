@@ -53,13 +53,17 @@ def _case(name):
                                moe_intermediate_size=32, n_shared_experts=2, first_k_dense_replace=0, routed_scaling_factor=1.0,
                                norm_topk_prob=False, use_qk_norm=False, attention_bias=False, n_group=4, topk_group=2,
                                rope_theta=1e4), T.Glm4MoeForCausalLM
+    if name == "qwen2_moe":
+        return T.Qwen2MoeConfig(**COMMON, rope_theta=1e6, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
+                                shared_expert_intermediate_size=48, norm_topk_prob=False, decoder_sparse_step=1,
+                                mlp_only_layers=[]), T.Qwen2MoeForCausalLM
     if name == "glm4":
         return T.Glm4Config(**COMMON, head_dim=16, partial_rotary_factor=0.5, attention_bias=True, rope_theta=1e4, pad_token_id=0,
                             eos_token_id=1), T.Glm4ForCausalLM
     raise KeyError(name)
 
 
-CASES = ["glm4", "glm4_moe", "glm4_moe-groups", "qwen3", "qwen3-tied", "qwen3_moe", "qwen3_moe-raw-topk", "qwen2", "llama", "llama-rope-llama3", "llama-rope-linear",
+CASES = ["qwen2_moe", "glm4", "glm4_moe", "glm4_moe-groups", "qwen3", "qwen3-tied", "qwen3_moe", "qwen3_moe-raw-topk", "qwen2", "llama", "llama-rope-llama3", "llama-rope-linear",
          "mistral", "mixtral"]
 
 
