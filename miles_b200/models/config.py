@@ -141,7 +141,7 @@ class ModelConfig:
             cfg["pad_token_id"] = None  # the library's default padding id assumes the full GLM vocabulary
         if self.family == "glm4":
             cfg["partial_rotary_factor"] = (self.rotary_dim or self.head_dim) / self.head_dim
-        if self.family == "glm4_moe":
+        if self.family in ("glm4_moe", "dots1"):
             cfg.update({"n_routed_experts": self.num_experts, "num_experts_per_tok": self.moe_top_k,
                         "moe_intermediate_size": self.moe_ffn_hidden_size, "norm_topk_prob": self.norm_topk_prob,
                         "n_shared_experts": self.shared_expert_ffn // max(self.moe_ffn_hidden_size, 1),
@@ -184,13 +184,20 @@ class ModelConfig:
         is_qwen3 = "qwen3" in mtype
         mlp_only = cfg.get("mlp_only_layers") or []
         n_experts = cfg.get("num_experts", 0) or cfg.get("num_local_experts", 0) or cfg.get("n_routed_experts", 0) or 0
-        glm = mtype == "glm4_moe"
+        dots = mtype == "dots1"        # dots.llm1: the GLM-4.5 router and shared experts with full rotary embedding and QK norm
+        glm = mtype == "glm4_moe" or dots
         glm_dense = mtype == "glm4"
+        if any(t != "full_attention" for t in (cfg.get("layer_types") or [])):
+            raise NotImplementedError("layers with sliding-window or linear attention are not built")
         prf = cfg.get("partial_rotary_factor") or (cfg.get("rope_parameters") or {}).get("partial_rotary_factor") or 1.0
         if not (glm or glm_dense) and float(prf) != 1.0:
             raise NotImplementedError(f"partial rotary embedding is wired for the GLM families only (got {prf} for {mtype})")
         moe_ffn = cfg.get("moe_intermediate_size", 0) or (cfg.get("intermediate_size", 0) if mtype == "mixtral" else 0)
-        if cfg.get("sliding_window") and cfg.get("use_sliding_window", mtype != "qwen2" and not is_qwen3) \
+        if mtype == "ernie4_5" and cfg.get("use_bias"):
+            raise NotImplementedError("biases on every projection (use_bias) are not built")
+        if mtype == "seed_oss" and (cfg.get("attention_out_bias") or cfg.get("mlp_bias")):
+            raise NotImplementedError("biases on the attention output or MLP projections are not built")
+        if cfg.get("sliding_window") and cfg.get("use_sliding_window", mtype not in ("qwen2", "qwen2_moe", "dots1") and not is_qwen3) \
                 and cfg["sliding_window"] < cfg.get("max_position_embeddings", 0):
             raise NotImplementedError("sliding-window attention is not built: this checkpoint would be served with full attention")
         scaling = cfg.get("rope_scaling") or None
@@ -217,8 +224,8 @@ class ModelConfig:
             rms_eps=cfg.get("rms_norm_eps", 1e-6),
             # newer HuggingFace configs keep the base inside "rope_parameters"; 10000 is the library-wide default
             rope_theta=float(cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta") or 10000.0),
-            qk_norm=bool(cfg.get("use_qk_norm", False)) if glm else is_qwen3,
-            qkv_bias=bool(cfg.get("attention_bias", (not is_qwen3 and "qwen2" in mtype) or glm_dense)),
+            qk_norm=True if dots else bool(cfg.get("use_qk_norm", False)) if glm else is_qwen3,
+            qkv_bias=bool(cfg.get("attention_bias", (not is_qwen3 and "qwen2" in mtype) or glm_dense or mtype == "seed_oss")),
             tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
             num_experts=n_experts,
             moe_top_k=(cfg.get("num_experts_per_tok", 0) or 0) if n_experts else 0,
@@ -234,7 +241,7 @@ class ModelConfig:
                                else int(cfg.get("shared_expert_intermediate_size", 0) or 0) if mtype == "qwen2_moe" else 0),
             shared_expert_gate=mtype == "qwen2_moe",
             rotary_dim=int(round(head_dim * float(prf))) if float(prf) != 1.0 else 0,
-            post_norms=glm_dense, rope_interleaved=glm_dense,
+            post_norms=glm_dense, rope_interleaved=glm_dense or mtype == "ernie4_5",
             extra={"hf_passthrough": {k: cfg[k] for k in ("pad_token_id", "eos_token_id", "bos_token_id") if k in cfg}},
             max_position_embeddings=cfg.get("max_position_embeddings", 40960),
             rope_scaling=scaling,
@@ -247,6 +254,7 @@ HF_FAMILIES = {
     "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3_moe", "Qwen2ForCausalLM": "qwen2", "LlamaForCausalLM": "llama",
     "MistralForCausalLM": "mistral", "MixtralForCausalLM": "mixtral", "MiMoForCausalLM": "mimo",
     "Glm4MoeForCausalLM": "glm4_moe", "Glm4ForCausalLM": "glm4", "Qwen2MoeForCausalLM": "qwen2_moe",
+    "Dots1ForCausalLM": "dots1", "SeedOssForCausalLM": "seed_oss", "Ernie4_5ForCausalLM": "ernie4_5",
 }
 
 
@@ -336,6 +344,17 @@ PRESETS: dict[str, ModelConfig] = {
                                     first_dense_layers=3, router_score="sigmoid", router_bias=True, routed_scaling_factor=2.5,
                                     shared_expert_ffn=1536, rotary_dim=64, max_position_embeddings=131072,
                                     hf_architecture="Glm4MoeForCausalLM"),
+    # ERNIE-4.5-0.3B: Llama layout whose checkpoints pair rotary dimensions 2i / 2i + 1
+    "ernie4.5-0.3B": _dense("ernie4.5-0.3B", 18, 1024, 16, 2, 3072, True, vocab=103424, qk_norm=False, rope_theta=5e5, rms_eps=1e-5,
+                            rope_interleaved=True, max_position_embeddings=131072, hf_architecture="Ernie4_5ForCausalLM"),
+    # Seed-OSS-36B: Llama layout with QKV bias; dots.llm1 (142B total, 14B active): GLM-4.5 style router with QK norm
+    "seed-oss-36B": _dense("seed-oss-36B", 64, 5120, 80, 8, 27648, False, vocab=155136, qk_norm=False, qkv_bias=True, rope_theta=1e7,
+                           rms_eps=1e-6, max_position_embeddings=524288, hf_architecture="SeedOssForCausalLM"),
+    "dots-llm1": ModelConfig(name="dots-llm1", num_layers=62, hidden_size=4096, num_q_heads=32, num_kv_heads=32, head_dim=128,
+                             ffn_hidden_size=10944, vocab_size=152064, rms_eps=1e-5, rope_theta=1e7, qk_norm=True, num_experts=128,
+                             moe_top_k=6, moe_ffn_hidden_size=1408, first_dense_layers=1, router_score="sigmoid", router_bias=True,
+                             routed_scaling_factor=2.5, shared_expert_ffn=2816, max_position_embeddings=32768,
+                             hf_architecture="Dots1ForCausalLM"),
     # Qwen2-MoE (Qwen1.5-MoE-A2.7B, Qwen2-57B-A14B): softmax router without renormalisation, a gated shared expert
     "qwen2-57B-A14B": ModelConfig(name="qwen2-57B-A14B", num_layers=28, hidden_size=3584, num_q_heads=28, num_kv_heads=4, head_dim=128,
                                   ffn_hidden_size=18944, vocab_size=151936, rms_eps=1e-6, rope_theta=1e6, qk_norm=False, qkv_bias=True,

@@ -53,6 +53,15 @@ def _case(name):
                                moe_intermediate_size=32, n_shared_experts=2, first_k_dense_replace=0, routed_scaling_factor=1.0,
                                norm_topk_prob=False, use_qk_norm=False, attention_bias=False, n_group=4, topk_group=2,
                                rope_theta=1e4), T.Glm4MoeForCausalLM
+    if name == "ernie4_5":
+        return T.Ernie4_5Config(**COMMON, head_dim=16, rope_theta=5e5, use_bias=False, tie_word_embeddings=True), T.Ernie4_5ForCausalLM
+    if name == "seed_oss":
+        return T.SeedOssConfig(**COMMON, head_dim=16, rope_theta=1e7, attention_bias=True, attention_out_bias=False,
+                               residual_dropout=0.0, attention_dropout=0.0), T.SeedOssForCausalLM
+    if name == "dots1":
+        return T.Dots1Config(**COMMON, head_dim=16, n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
+                             n_shared_experts=2, first_k_dense_replace=1, routed_scaling_factor=2.5, norm_topk_prob=True, n_group=2,
+                             topk_group=1, rope_theta=1e4, layer_types=["full_attention"] * 2, sliding_window=None), T.Dots1ForCausalLM
     if name == "qwen2_moe":
         return T.Qwen2MoeConfig(**COMMON, rope_theta=1e6, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
                                 shared_expert_intermediate_size=48, norm_topk_prob=False, decoder_sparse_step=1,
@@ -63,7 +72,7 @@ def _case(name):
     raise KeyError(name)
 
 
-CASES = ["qwen2_moe", "glm4", "glm4_moe", "glm4_moe-groups", "qwen3", "qwen3-tied", "qwen3_moe", "qwen3_moe-raw-topk", "qwen2", "llama", "llama-rope-llama3", "llama-rope-linear",
+CASES = ["ernie4_5", "seed_oss", "dots1", "qwen2_moe", "glm4", "glm4_moe", "glm4_moe-groups", "qwen3", "qwen3-tied", "qwen3_moe", "qwen3_moe-raw-topk", "qwen2", "llama", "llama-rope-llama3", "llama-rope-linear",
          "mistral", "mixtral"]
 
 
