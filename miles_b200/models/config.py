@@ -190,7 +190,7 @@ class ModelConfig:
         if any(t != "full_attention" for t in (cfg.get("layer_types") or [])):
             raise NotImplementedError("layers with sliding-window or linear attention are not built")
         prf = cfg.get("partial_rotary_factor") or (cfg.get("rope_parameters") or {}).get("partial_rotary_factor") or 1.0
-        if not (glm or glm_dense) and float(prf) != 1.0:
+        if not (glm or glm_dense) and float(prf) != 1.0:  # (Phi-4-mini's 0.75 among them: the kernels rotate 128 or 64 dimensions)
             raise NotImplementedError(f"partial rotary embedding is wired for the GLM families only (got {prf} for {mtype})")
         moe_ffn = cfg.get("moe_intermediate_size", 0) or (cfg.get("intermediate_size", 0) if mtype == "mixtral" else 0)
         if mtype == "ernie4_5" and cfg.get("use_bias"):
@@ -255,6 +255,7 @@ HF_FAMILIES = {
     "MistralForCausalLM": "mistral", "MixtralForCausalLM": "mixtral", "MiMoForCausalLM": "mimo",
     "Glm4MoeForCausalLM": "glm4_moe", "Glm4ForCausalLM": "glm4", "Qwen2MoeForCausalLM": "qwen2_moe",
     "Dots1ForCausalLM": "dots1", "SeedOssForCausalLM": "seed_oss", "Ernie4_5ForCausalLM": "ernie4_5",
+    "Phi3ForCausalLM": "phi3",
 }
 
 
@@ -344,6 +345,9 @@ PRESETS: dict[str, ModelConfig] = {
                                     first_dense_layers=3, router_score="sigmoid", router_bias=True, routed_scaling_factor=2.5,
                                     shared_expert_ffn=1536, rotary_dim=64, max_position_embeddings=131072,
                                     hf_architecture="Glm4MoeForCausalLM"),
+    # Phi-4 (14B): Llama layout with the query / key / value rows and the gate / up rows fused in the checkpoint as well
+    "phi-4": _dense("phi-4", 40, 5120, 40, 10, 17920, False, vocab=100352, qk_norm=False, rope_theta=250000.0, rms_eps=1e-5,
+                    max_position_embeddings=16384, hf_architecture="Phi3ForCausalLM"),
     # ERNIE-4.5-0.3B: Llama layout whose checkpoints pair rotary dimensions 2i / 2i + 1
     "ernie4.5-0.3B": _dense("ernie4.5-0.3B", 18, 1024, 16, 2, 3072, True, vocab=103424, qk_norm=False, rope_theta=5e5, rms_eps=1e-5,
                             rope_interleaved=True, max_position_embeddings=131072, hf_architecture="Ernie4_5ForCausalLM"),

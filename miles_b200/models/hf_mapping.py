@@ -38,6 +38,11 @@ def to_hf(cfg: ModelConfig, name: str, t: torch.Tensor, expert_offset: int = 0) 
         return [(p + "post_self_attn_layernorm.weight", t)]
     if rest == "post_mlp_ln.weight":
         return [(p + "post_mlp_layernorm.weight", t)]
+    fused_names = getattr(cfg, "family", "") == "phi3"  # one qkv_proj and one gate_up_proj tensor, in this package's row order
+    if rest in ("attn.qkv.weight", "attn.qkv.bias") and fused_names:
+        return [(p + f"self_attn.qkv_proj.{rest.rsplit('.', 1)[1]}", t)]
+    if rest == "mlp.gate_up.weight" and fused_names:
+        return [(p + "mlp.gate_up_proj.weight", t)]
     if rest in ("attn.qkv.weight", "attn.qkv.bias"):
         sfx = rest.rsplit(".", 1)[1]
         return [(p + f"self_attn.q_proj.{sfx}", t[:q]), (p + f"self_attn.k_proj.{sfx}", t[q:q + kv]),

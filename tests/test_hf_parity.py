@@ -53,6 +53,8 @@ def _case(name):
                                moe_intermediate_size=32, n_shared_experts=2, first_k_dense_replace=0, routed_scaling_factor=1.0,
                                norm_topk_prob=False, use_qk_norm=False, attention_bias=False, n_group=4, topk_group=2,
                                rope_theta=1e4), T.Glm4MoeForCausalLM
+    if name == "phi3":
+        return T.Phi3Config(**COMMON, rope_theta=250000.0, pad_token_id=0, original_max_position_embeddings=4096), T.Phi3ForCausalLM
     if name == "ernie4_5":
         return T.Ernie4_5Config(**COMMON, head_dim=16, rope_theta=5e5, use_bias=False, tie_word_embeddings=True), T.Ernie4_5ForCausalLM
     if name == "seed_oss":
@@ -72,7 +74,7 @@ def _case(name):
     raise KeyError(name)
 
 
-CASES = ["ernie4_5", "seed_oss", "dots1", "qwen2_moe", "glm4", "glm4_moe", "glm4_moe-groups", "qwen3", "qwen3-tied", "qwen3_moe", "qwen3_moe-raw-topk", "qwen2", "llama", "llama-rope-llama3", "llama-rope-linear",
+CASES = ["phi3", "ernie4_5", "seed_oss", "dots1", "qwen2_moe", "glm4", "glm4_moe", "glm4_moe-groups", "qwen3", "qwen3-tied", "qwen3_moe", "qwen3_moe-raw-topk", "qwen2", "llama", "llama-rope-llama3", "llama-rope-linear",
          "mistral", "mixtral"]
 
 
