@@ -373,7 +373,7 @@ PRESETS: dict[str, ModelConfig] = {
     "glm4-9B": _dense("glm4-9B", 40, 4096, 32, 2, 13696, False, vocab=151552, qk_norm=False, qkv_bias=True, rope_theta=1e4,
                       rms_eps=1e-5, rotary_dim=64, post_norms=True, rope_interleaved=True, max_position_embeddings=32768,
                       hf_architecture="Glm4ForCausalLM"),
-    "glm4-32B": _dense("glm4-32B", 61, 6144, 48, 2, 23040, False, vocab=151552, qk_norm=False, qkv_bias=False, rope_theta=1e4,
+    "glm4-32B": _dense("glm4-32B", 64, 6144, 48, 8, 23040, False, vocab=151552, qk_norm=False, qkv_bias=False, rope_theta=1e4,
                        rms_eps=1e-5, rotary_dim=64, post_norms=True, rope_interleaved=True, max_position_embeddings=32768,
                        hf_architecture="Glm4ForCausalLM"),
     "glm4-smoke": _dense("glm4-smoke", 2, 512, 4, 2, 1024, False, vocab=4096, qk_norm=False, qkv_bias=True, rope_theta=1e4,

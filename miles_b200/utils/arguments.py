@@ -54,6 +54,8 @@ TRAINER_FLAGS = [
     ("--spec", "s", None, {"nargs": "+"}), ("--no-rope-fusion", "b", False, {}), ("--no-masked-softmax-fusion", "b", False, {}),
     ("--no-gradient-accumulation-fusion", "b", False, {}), ("--attention-output-gate", "b", False, {}),
     ("--apply-layernorm-1p", "b", False, {}),
+    # GLM-4 dense: sandwich norms and checkpoints with interleaved rotary rows
+    ("--post-self-attn-layernorm", "b", False, {}), ("--post-mlp-layernorm", "b", False, {}), ("--rotary-interleaved", "b", False, {}),
     # MoE
     ("--num-experts", "i", None, {}), ("--moe-router-topk", "i", 2, {}), ("--moe-ffn-hidden-size", "i", None, {}),
     ("--moe-layer-freq", "s", "1", {}), ("--moe-router-score-function", "s", "softmax", {}),
@@ -462,6 +464,15 @@ def hf_validate_args(args, hf_config: dict) -> None:
         raise AssertionError("model shape flags contradict the HF checkpoint: " + "; ".join(errors))
 
 
+def _sandwich_norms(args) -> bool:
+    a, b = bool(getattr(args, "post_self_attn_layernorm", False)), bool(getattr(args, "post_mlp_layernorm", False))
+    if a != b:
+        raise NotImplementedError("--post-self-attn-layernorm and --post-mlp-layernorm come together (GLM-4 sandwich norms)")
+    if a and getattr(args, "num_experts", None):
+        raise NotImplementedError("sandwich norms are built for dense MLP layers")
+    return a
+
+
 def _first_dense_layers(freq, num_layers: int) -> int:
     """Megatron's ``--moe-layer-freq`` as a pattern (``"[0]*1+[1]*45"`` or a list): how many leading layers are dense."""
     if isinstance(freq, str) and "[" in freq:
@@ -491,7 +502,9 @@ def _check_architecture_flags(args, cfg):
              ("moe_router_num_groups", cfg.n_group if cfg.n_group != 1 else None, None),
              ("moe_router_group_topk", cfg.topk_group if cfg.n_group != 1 else None, None),
              ("rotary_percent", (cfg.rotary_dim or cfg.head_dim) / cfg.head_dim, 1.0),
-             ("use_rope_scaling", bool(cfg.rope_scaling), False)]
+             ("use_rope_scaling", bool(cfg.rope_scaling), False),
+             ("post_self_attn_layernorm", bool(cfg.post_norms), False), ("post_mlp_layernorm", bool(cfg.post_norms), False),
+             ("rotary_interleaved", bool(cfg.rope_interleaved), False)]
     bad = []
     for flag, have, default in given:
         v = getattr(args, flag, default)
@@ -531,8 +544,11 @@ def model_config_from_args(args):
         qkv_bias=bool(args.add_qkv_bias), tie_embeddings=not args.untie_embeddings_and_output_weights,
         num_experts=args.num_experts or 0, moe_top_k=args.moe_router_topk if moe else 0,
         moe_ffn_hidden_size=(args.moe_ffn_hidden_size or 0) if moe else 0,
-        hf_architecture=("Glm4MoeForCausalLM" if getattr(args, "moe_router_score_function", "softmax") == "sigmoid"
-                         else "Qwen3MoeForCausalLM") if moe else "Qwen3ForCausalLM",
+        hf_architecture=(("Glm4MoeForCausalLM" if getattr(args, "moe_router_score_function", "softmax") == "sigmoid"
+                          else "Qwen3MoeForCausalLM") if moe
+                         else "Glm4ForCausalLM" if getattr(args, "post_self_attn_layernorm", False)
+                         else "Qwen3ForCausalLM" if args.qk_layernorm else "Qwen2ForCausalLM" if args.add_qkv_bias else "LlamaForCausalLM"),
+        post_norms=_sandwich_norms(args), rope_interleaved=bool(getattr(args, "rotary_interleaved", False)),
         # GLM-4.5 / DeepSeek-V3 style routing and shared experts (Megatron flag names)
         router_score=getattr(args, "moe_router_score_function", "softmax") if moe else "softmax",
         router_bias=bool(getattr(args, "moe_router_enable_expert_bias", False)) and moe,

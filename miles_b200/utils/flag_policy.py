@@ -43,7 +43,6 @@ REJECT = {
     "moe_aux_loss_coeff": "router auxiliary loss",
     "moe_latent_size": "latent MoE",
     "moe_token_drop_policy": "token dropping (the dispatch here is dropless)",
-    "mtp_num_layers": "multi-token-prediction layers",
     "enable_mtp_training": "multi-token-prediction layers",
     "multimodal_keys": "multimodal inputs",
     "freeze_indexer": "sparse-attention indexer models",
@@ -72,6 +71,7 @@ REJECT = {
 
 # dest -> why nothing needs to happen
 IGNORED = {
+    "mtp_num_layers": "the multi-token-prediction layer is not built: the model trains and serves without it (training it, --enable-mtp-training, is rejected)",
     # sharded backend: activations are always recomputed per layer; checkpoints stage through host copies per unit
     "gradient_checkpointing": "layer inputs are the only activations kept: every layer is recomputed in the backward",
     "fsdp_state_dict_cpu_offload": "checkpoint and export copies are always staged in host memory, unit by unit",
@@ -140,7 +140,7 @@ IGNORED = {
     "rollout_task_type": "the reference does not read it either",
     "dumper_source_patcher_config_inference": "the source patcher rewrites Megatron / SGLang sources, which do not exist here",
     "dumper_source_patcher_config_train": "the source patcher rewrites Megatron / SGLang sources, which do not exist here",
-    "mtp_loss_scaling_factor": "multi-token prediction is rejected (--mtp-num-layers)",
+    "mtp_loss_scaling_factor": "the multi-token-prediction layer is not built, so its loss has no weight to scale",
     "opd_reward_weight_mode": "weights the per-token terms of multi-token (student-side top-k) distillation, which is not built",
 }
 
@@ -163,8 +163,10 @@ def apply(args, defaults: dict) -> None:
             continue
         if dest == "expert_tensor_parallel_size" and int(v) == 1:
             continue
-        if dest == "moe_router_load_balancing_type" and v in ("none", "aux_loss") and float(getattr(args, "moe_aux_loss_coeff", 0.0) or 0.0) == 0.0:
-            continue
+        if dest == "moe_router_load_balancing_type" and float(getattr(args, "moe_aux_loss_coeff", 0.0) or 0.0) == 0.0:
+            continue  # any balancing loss with coefficient zero is no loss at all
+        if dest == "moe_router_pre_softmax":
+            continue  # scores are always computed over all experts before the top-k (the order this flag asks for)
         raise NotImplementedError(f"--{dest.replace('_', '-')} {v!r}: {why} is not built in this framework; "
                                   "the flag is rejected rather than ignored")
     noted = []

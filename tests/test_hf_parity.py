@@ -158,3 +158,72 @@ def test_megatron_style_flags_describe_a_glm45_like_model():
     store_a = ParamStore(cfg, "cpu", torch.float32, meta=True, init=False)
     store_b = ParamStore(ref, "cpu", torch.float32, meta=True, init=False)
     assert [(s.name, s.shape) for s in store_a.specs] == [(s.name, s.shape) for s in store_b.specs]
+
+
+GLM45_AIR_FLAGS = ("--disable-bias-linear --group-query-attention --num-attention-heads 96 --num-query-groups 8 --kv-channels 128 "
+                   "--num-layers 46 --hidden-size 4096 --ffn-hidden-size 10944 --add-qkv-bias --normalization RMSNorm "
+                   "--position-embedding-type rope --rotary-percent 0.5 --swiglu --untie-embeddings-and-output-weights "
+                   "--vocab-size 151552 --rotary-base 1000000 --moe-ffn-hidden-size 1408 --moe-shared-expert-intermediate-size 1408 "
+                   "--moe-router-pre-softmax --moe-router-score-function sigmoid --moe-router-enable-expert-bias "
+                   "--moe-router-bias-update-rate 0 --moe-router-load-balancing-type seq_aux_loss --moe-token-dispatcher-type alltoall "
+                   "--moe-router-topk 8 --moe-layer-freq [0]*1+[1]*45 --num-experts 128 --moe-grouped-gemm --moe-router-dtype fp32 "
+                   "--moe-permute-fusion --moe-aux-loss-coeff 0")
+QWEN3_30B_FLAGS = ("--disable-bias-linear --qk-layernorm --group-query-attention --num-attention-heads 32 --num-query-groups 4 "
+                   "--kv-channels 128 --num-layers 48 --hidden-size 2048 --ffn-hidden-size 6144 --normalization RMSNorm "
+                   "--position-embedding-type rope --norm-epsilon 1e-6 --rotary-percent 1.0 --swiglu "
+                   "--untie-embeddings-and-output-weights --vocab-size 151936 --rotary-base 1000000 --moe-ffn-hidden-size 768 "
+                   "--moe-router-score-function softmax --moe-token-dispatcher-type alltoall --moe-router-topk 8 --moe-layer-freq [1]*48 "
+                   "--num-experts 128 --moe-grouped-gemm --moe-token-drop-policy probs --moe-router-dtype fp32 --moe-permute-fusion "
+                   "--moe-aux-loss-coeff 0")
+
+
+@pytest.mark.parametrize("flags,preset", [(GLM45_AIR_FLAGS, "glm4.5-106B-A12B"), (QWEN3_30B_FLAGS, "qwen3-30B-A3B")])
+def test_reference_model_argument_strings_describe_our_presets(flags, preset):
+    """The Megatron-style argument strings the reference's per-model files pass (scripts/models/glm4.5-106B-A12B.py,
+    qwen3-30B-A3B.py) parse here and give the same parameter layout as the preset of that model."""
+    from miles_b200.models import get_config
+    from miles_b200.utils.arguments import model_config_from_args, parse_args
+
+    a = parse_args(["--num-rollout", "1", "--rollout-batch-size", "2"] + flags.split())
+    cfg, ref = model_config_from_args(a), get_config(preset)
+    sa = ParamStore(cfg, "cpu", torch.float32, meta=True, init=False)
+    sb = ParamStore(ref, "cpu", torch.float32, meta=True, init=False)
+    assert [(s.name, s.shape) for s in sa.specs] == [(s.name, s.shape) for s in sb.specs]
+    for f in ("num_q_heads", "num_kv_heads", "head_dim", "rope_theta", "qk_norm", "qkv_bias", "router_score", "router_bias",
+              "routed_scaling_factor", "norm_topk_prob", "rotary_dim", "first_dense_layers", "moe_top_k", "tie_embeddings"):
+        assert getattr(cfg, f) == getattr(ref, f), (f, getattr(cfg, f), getattr(ref, f))
+
+
+LLAMA31_FLAGS = ("--swiglu --num-layers 32 --hidden-size 4096 --ffn-hidden-size 14336 --num-attention-heads 32 --group-query-attention "
+                 "--num-query-groups 8 --max-position-embeddings 131072 --use-rotary-position-embeddings --disable-bias-linear "
+                 "--normalization RMSNorm --norm-epsilon 1e-5 --rotary-base 500000 --vocab-size 128256 --kv-channels 128 "
+                 "--use-rope-scaling --rotary-scaling-factor 8.0 --untie-embeddings-and-output-weights")
+MIMO_FLAGS = ("--swiglu --num-layers 36 --hidden-size 4096 --ffn-hidden-size 11008 --num-attention-heads 32 --group-query-attention "
+              "--num-query-groups 8 --use-rotary-position-embeddings --disable-bias-linear --add-qkv-bias --normalization RMSNorm "
+              "--norm-epsilon 1e-05 --rotary-base 640000 --vocab-size 151680 --untie-embeddings-and-output-weights "
+              "--max-position-embeddings 32768 --mtp-num-layers 1")
+GLM4_32B_FLAGS = ("--spec miles_plugins.models.glm4 get_glm_spec --swiglu --num-layers 64 --hidden-size 6144 --ffn-hidden-size 23040 "
+                  "--num-attention-heads 48 --max-position-embeddings 32768 --seq-length 32768 --use-rotary-position-embeddings "
+                  "--disable-bias-linear --normalization RMSNorm --norm-epsilon 1e-5 --rotary-base 10000 --group-query-attention "
+                  "--num-query-groups 8 --vocab-size 151552 --post-self-attn-layernorm --post-mlp-layernorm --rotary-interleaved "
+                  "--rotary-percent 0.5 --no-rope-fusion --untie-embeddings-and-output-weights")
+
+
+@pytest.mark.parametrize("flags,preset", [(LLAMA31_FLAGS, "llama3.1-8B-Instruct"), (MIMO_FLAGS, "mimo-7B-rl"), (GLM4_32B_FLAGS, "glm4-32B")])
+def test_more_reference_argument_strings(flags, preset):
+    """scripts/models/{llama3.1-8B-Instruct,mimo-7B-rl,glm4-32B}.py of the reference."""
+    import warnings
+
+    from miles_b200.models import get_config
+    from miles_b200.utils.arguments import model_config_from_args, parse_args
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")  # flags that change nothing here are announced once
+        a = parse_args(["--num-rollout", "1", "--rollout-batch-size", "2"] + flags.split())
+    cfg, ref = model_config_from_args(a), get_config(preset)
+    sa = ParamStore(cfg, "cpu", torch.float32, meta=True, init=False)
+    sb = ParamStore(ref, "cpu", torch.float32, meta=True, init=False)
+    assert [(s.name, s.shape) for s in sa.specs] == [(s.name, s.shape) for s in sb.specs]
+    for f in ("num_q_heads", "num_kv_heads", "head_dim", "rope_theta", "rms_eps", "qk_norm", "qkv_bias", "rotary_dim", "post_norms",
+              "rope_interleaved", "tie_embeddings", "rope_scaling", "family"):
+        assert getattr(cfg, f) == getattr(ref, f), (f, getattr(cfg, f), getattr(ref, f))
