@@ -35,9 +35,16 @@ def _nvml_sampler() -> Optional[Callable[[], list]]:
 
 
 class Collector:
-    def __init__(self, store: EventStore, gpu_interval: float = 5.0, gpu_sampler: Optional[Callable[[], list]] = None):
+    def __init__(self, store: EventStore, gpu_interval: float = 5.0, gpu_sampler: Optional[Callable[[], list]] = None,
+                 engine_interval: Optional[float] = None, engine_metrics: Optional[list] = None, forward: Optional[Callable] = None):
+        """``engine_interval``: scrape cadence of the engines' ``/metrics`` (default: with every GPU sample);
+        ``engine_metrics``: keep only these metric names of an engine's answer; ``forward(name, value, labels)``: also hand
+        every gauge to another sink (the Prometheus backend)."""
         self.store = store
         self.gpu_interval = gpu_interval
+        self.engine_interval = engine_interval
+        self.engine_metrics = set(engine_metrics) if engine_metrics else None
+        self.forward = forward
         self._sampler = gpu_sampler if gpu_sampler is not None else _nvml_sampler()
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
@@ -55,6 +62,10 @@ class Collector:
         rows = self._sampler()
         for r in rows:
             self.store.append("gpus", r)
+            if self.forward is not None:
+                for k, v in r.items():
+                    if isinstance(v, (int, float)) and k not in ("gpu", "index"):
+                        self.forward(f"dashboard_gpu_{k}", float(v), {"gpu": str(r.get("gpu", r.get("index", "")))})
         return len(rows)
 
     def add_engine(self, url: str) -> None:
@@ -70,8 +81,14 @@ class Collector:
                 self.store.append("engines", {"engine": url, "up": 0, "error": repr(e)[:120]})
                 continue
             rec = {"engine": url, "up": 1}
-            rec.update(parse_prometheus(text))
+            vals = parse_prometheus(text)
+            if self.engine_metrics is not None:
+                vals = {k: v for k, v in vals.items() if k in self.engine_metrics}
+            rec.update(vals)
             self.store.append("engines", rec)
+            if self.forward is not None:
+                for k, v in vals.items():
+                    self.forward(f"dashboard_engine_{k}", float(v), {"engine": url})
             n += 1
         return n
 
@@ -81,9 +98,18 @@ class Collector:
             return
 
         def loop():
-            while not self._stop.wait(self.gpu_interval):
-                self.sample_gpus_once()
-                self.scrape_engines_once()
+            import time
+
+            step = min(self.gpu_interval, self.engine_interval or self.gpu_interval)
+            next_gpu = next_eng = time.monotonic()
+            while not self._stop.wait(step):
+                now = time.monotonic()
+                if now >= next_gpu:
+                    self.sample_gpus_once()
+                    next_gpu = now + self.gpu_interval
+                if now >= next_eng:
+                    self.scrape_engines_once()
+                    next_eng = now + (self.engine_interval or self.gpu_interval)
 
         self._thread = threading.Thread(target=loop, daemon=True)
         self._thread.start()

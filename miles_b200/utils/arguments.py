@@ -117,6 +117,11 @@ TRAINER_FLAGS = [
     ("--config", "s", None, {}), ("--fsdp-num-unit-buffers", "i", 2, {}),
     # destroy the trainer's NCCL sub-groups while the colocated engine generates, rebuild them before training
     ("--reload-process-groups", "b", False, {}),
+    # run dashboard (names of the reference's miles/dashboard/args.py); telemetry is collected whenever --dump-details is set
+    ("--use-miles-dashboard", "b", False, {}), ("--dashboard-flush-interval", "f", 5.0, {}),
+    ("--dashboard-gpu-sample-interval", "f", 1.0, {}), ("--dashboard-sglang-scrape-interval", "f", 2.0, {}),
+    ("--dashboard-sglang-scrape-mode", "s", "auto", {"choices": ["auto", "router", "direct"]}),
+    ("--dashboard-sglang-metrics", "s", None, {}), ("--dashboard-forward-prometheus", "b", False, {}),
     # host-memory samples with phase marks, written as CSV by the first rank (tools/host_memory_profiler.py)
     ("--profile-host-memory", "s", None, {}), ("--profile-host-memory-interval", "f", 0.5, {}),
     # native extensions of this framework

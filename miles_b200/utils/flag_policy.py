@@ -71,6 +71,7 @@ REJECT = {
 
 # dest -> why nothing needs to happen
 IGNORED = {
+    "dashboard_flush_interval": "dashboard events are appended to their files as they happen: there is no buffer to flush",
     "mtp_num_layers": "the multi-token-prediction layer is not built: the model trains and serves without it (training it, --enable-mtp-training, is rejected)",
     # sharded backend: activations are always recomputed per layer; checkpoints stage through host copies per unit
     "gradient_checkpointing": "layer inputs are the only activations kept: every layer is recomputed in the backward",

@@ -49,12 +49,34 @@ class DashboardBackend(TrackingBackend):
     read-only GPU samples go to its partitioned JSONL store."""
     name = "dashboard"
 
-    def __init__(self, root: str):
+    # the part of the command line shown in the dashboard's header (written once to <root>/meta.json)
+    SNAPSHOT_KEYS = ("wandb_group", "wandb_project", "colocate", "actor_num_nodes", "actor_num_gpus_per_node", "rollout_num_gpus",
+                     "rollout_num_gpus_per_engine", "rollout_batch_size", "n_samples_per_prompt", "rollout_max_response_len",
+                     "hf_checkpoint", "model_preset", "train_backend", "sglang_max_running_requests", "sglang_mem_fraction_static",
+                     "use_miles_router", "tensor_model_parallel_size", "expert_model_parallel_size", "pipeline_model_parallel_size",
+                     "context_parallel_size")
+
+    def __init__(self, root: str, args=None, forward=None):
+        import json
+
         from ..dashboard import Collector, EventStore
         from . import lifecycle
 
         self.root = root
-        self.collector = Collector(EventStore(root))
+        metrics = getattr(args, "dashboard_sglang_metrics", None)
+        self.collector = Collector(EventStore(root), gpu_interval=float(getattr(args, "dashboard_gpu_sample_interval", None) or 5.0),
+                                   engine_interval=getattr(args, "dashboard_sglang_scrape_interval", None),
+                                   engine_metrics=[m.strip() for m in metrics.split(",") if m.strip()] if metrics else None,
+                                   forward=forward)
+        if args is not None:
+            os.makedirs(root, exist_ok=True)
+            with open(os.path.join(root, "meta.json"), "w") as f:
+                json.dump({k: getattr(args, k) for k in self.SNAPSHOT_KEYS if getattr(args, k, None) is not None}, f, default=str)
+            if getattr(args, "dashboard_sglang_scrape_mode", "auto") != "router":
+                for u in [x for x in (getattr(args, "rollout_engine_urls", None) or "").split(",") if x]:
+                    self.collector.add_engine(u)
+            elif getattr(args, "rollout_router_url", None):
+                self.collector.add_engine(args.rollout_router_url)
         lifecycle.add_sink(self.collector.on_lifecycle)
         self.collector.start()
 
@@ -150,6 +172,16 @@ class PrometheusBackend(TrackingBackend):
                 g = self.gauges[name] = self.Gauge(name, k, ["run"])
             g.labels(run=self.run).set(float(v))
 
+    def set_gauge(self, name: str, value: float, labels: Optional[dict] = None) -> None:
+        """A gauge that is not a step metric (the dashboard collector's GPU and engine samples,
+        ``--dashboard-forward-prometheus``)."""
+        name = "miles_" + "".join(c if c.isalnum() else "_" for c in name)
+        keys = ["run"] + sorted(labels or {})
+        g = self.gauges.get(name)
+        if g is None:
+            g = self.gauges[name] = self.Gauge(name, name, keys)
+        g.labels(run=self.run, **{k: str(v) for k, v in (labels or {}).items()}).set(float(value))
+
 
 class TrackingManager:
     def __init__(self, backends: Optional[list] = None):
@@ -180,8 +212,15 @@ def init_tracking(args, primary: bool = True) -> TrackingManager:
                 backends.append(cls(args))
             except Exception as e:  # noqa: BLE001
                 print(f"[tracking] {cls.name} disabled: {e}")
+    if getattr(args, "use_miles_dashboard", False) and not getattr(args, "dump_details", None):
+        raise ValueError("--use-miles-dashboard writes its telemetry under <dump-details>/dashboard: --dump-details is required")
     if getattr(args, "dump_details", None):
-        backends.append(DashboardBackend(os.path.join(args.dump_details, "dashboard")))
+        forward = None
+        if getattr(args, "dashboard_forward_prometheus", False):
+            prom = next((b for b in backends if getattr(b, "name", "") == "prometheus"), None)
+            if prom is not None and hasattr(prom, "set_gauge"):
+                forward = prom.set_gauge
+        backends.append(DashboardBackend(os.path.join(args.dump_details, "dashboard"), args, forward))
         backends.append(JsonlBackend(os.path.join(args.dump_details, "metrics.jsonl")))
     if os.environ.get("MILES_CI_HISTORY_PATH"):
         backends.append(CIHistoryBackend(os.environ["MILES_CI_HISTORY_PATH"]))

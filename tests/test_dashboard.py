@@ -100,3 +100,35 @@ def test_timeline_and_rollout_inspector_endpoints(tmp_path):
     msgs = app.get("/api/rollout/0/sample/1/messages").json()["messages"]
     assert msgs[0]["role"] == "user" and msgs[-1] == {"role": "assistant", "content": "four"}
     assert app.get("/api/rollout/7/summary").status_code == 404 and app.get("/api/rollout/0/sample/99/tokens").status_code == 404
+
+
+def test_dashboard_flags_configure_the_collector(tmp_path):
+    """--use-miles-dashboard and the --dashboard-* flags of the reference: header snapshot, sampling cadences, engine metric
+    whitelist, forwarding of the collector's gauges."""
+    import json
+
+    import pytest
+
+    from miles_b200.utils.arguments import parse_args
+    from miles_b200.utils.tracking import DashboardBackend, init_tracking
+
+    base = ["--model-preset", "qwen3-tiny", "--num-rollout", "1", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2"]
+    with pytest.raises(ValueError):
+        init_tracking(parse_args(base + ["--use-miles-dashboard"]), primary=True)
+    a = parse_args(base + ["--use-miles-dashboard", "--dump-details", str(tmp_path), "--dashboard-gpu-sample-interval", "0.5",
+                           "--dashboard-sglang-scrape-interval", "0.25", "--dashboard-sglang-metrics", "num_running_reqs,gen_throughput",
+                           "--rollout-engine-urls", "http://127.0.0.1:1"])
+    seen = []
+    b = DashboardBackend(str(tmp_path / "dashboard"), a, forward=lambda n, v, l: seen.append((n, v, l)))
+    try:
+        c = b.collector
+        assert (c.gpu_interval, c.engine_interval, c.engine_metrics) == (0.5, 0.25, {"num_running_reqs", "gen_throughput"})
+        meta = json.load(open(tmp_path / "dashboard" / "meta.json"))
+        assert meta["model_preset"] == "qwen3-tiny" and meta["rollout_batch_size"] == 2
+        n = c.scrape_engines_once(fetch=lambda url: "num_running_reqs 3\nother_metric 9\ngen_throughput{engine=\"0\"} 120.5\n")
+        assert n == 1
+        rows = list(c.store.read("engines"))
+        assert rows[-1]["num_running_reqs"] == 3.0 and rows[-1]["gen_throughput"] == 120.5 and "other_metric" not in rows[-1]
+        assert ("dashboard_engine_gen_throughput", 120.5, {"engine": "http://127.0.0.1:1"}) in seen
+    finally:
+        b.finish()
