@@ -23,6 +23,11 @@ _TOOL_RE = re.compile(r"<tool_call>\s*(\{.*?\})\s*</tool_call>", re.S)
 def add_arguments(parser) -> None:
     parser.add_argument("--generate-max-turns", type=int, default=8)
     parser.add_argument("--generate-tool-module-path", type=str, default=None)
+    # the reference's names: a function ``execute(name, arguments) -> str``, the tool specifications shown to the model,
+    # and the markup its calls are written in (rollout/generate_hub/tool_calls.py)
+    parser.add_argument("--generate-execute-tool-function-path", type=str, default=None)
+    parser.add_argument("--generate-tool-specs-path", type=str, default=None)
+    parser.add_argument("--generate-tool-call-parser", type=str, default=None)
     parser.add_argument("--generate-observation-template", type=str, default="\n<tool_response>\n{result}\n</tool_response>\n")
 
 
@@ -58,6 +63,13 @@ async def generate(inp: GenerateFnInput) -> GenerateFnOutput:
     a = state.args
     assert state.tokenizer is not None, "multi-turn generation needs a tokenizer"
     tool_module = load_function(a.generate_tool_module_path) if getattr(a, "generate_tool_module_path", None) else None
+    execute_one = load_function(a.generate_execute_tool_function_path) if getattr(a, "generate_execute_tool_function_path", None) else None
+    parser = None
+    if execute_one is not None or getattr(a, "generate_tool_call_parser", None):
+        from .tool_calls import create_parser
+
+        specs = load_function(a.generate_tool_specs_path) if getattr(a, "generate_tool_specs_path", None) else None
+        parser = create_parser(getattr(a, "generate_tool_call_parser", None), specs() if callable(specs) else specs)
     max_turns = getattr(a, "generate_max_turns", 8)
     template = getattr(a, "generate_observation_template", "\n<tool_response>\n{result}\n</tool_response>\n")
     budget = inp.sampling_params["max_new_tokens"]
@@ -78,10 +90,20 @@ async def generate(inp: GenerateFnInput) -> GenerateFnOutput:
         sample.metadata["turns"] = turn + 1
         if sample.status != Sample.Status.COMPLETED:
             break
-        calls = parse_tool_calls(out.get("text", ""))
-        if not calls or tool_module is None:
-            break
-        obs = template.format(result=await _run_tools(tool_module, calls))
+        if parser is not None:
+            from .tool_calls import execute_tool_calls
+
+            _, found = parser(out.get("text", ""))
+            if not found or (execute_one is None and tool_module is None):
+                break
+            run = execute_one if execute_one is not None else tool_module.call
+            msgs = await execute_tool_calls(found, run)
+            obs = template.format(result="\n".join(m["content"] for m in msgs))
+        else:
+            calls = parse_tool_calls(out.get("text", ""))
+            if not calls or tool_module is None:
+                break
+            obs = template.format(result=await _run_tools(tool_module, calls))
         obs_ids = state.tokenizer(obs, add_special_tokens=False)["input_ids"]
         if sample.response_length + len(obs_ids) >= budget:
             sample.status = Sample.Status.TRUNCATED
