@@ -336,3 +336,46 @@ def test_training_loop_writes_a_host_memory_profile(tmp_path):
     RLLoop(args).run()
     phases = [x["phase"] for x in summarize(str(out))]
     assert phases[:1] == ["start"] and {"rollout", "train", "update_weights"} <= set(phases)
+
+
+def test_debug_rollout_data_tool_shows_rescoring_and_resending(tmp_path):
+    import asyncio
+    import io
+
+    import torch
+
+    from miles_b200.loop import RLLoop
+    from miles_b200.tools import debug_rollout_data as D
+    from miles_b200.utils.arguments import parse_args
+
+    path = tmp_path / "rollout_{rollout_id}.pt"
+    args = parse_args(["--model-preset", "qwen3-tiny", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2",
+                       "--rollout-max-response-len", "8", "--rollout-max-prompt-len", "16", "--rm-type", "parity", "--lr", "1e-5",
+                       "--micro-batch-size", "4", "--colocate", "--num-rollout", "1", "--actor-num-gpus-per-node", "1",
+                       "--save-debug-rollout-data", str(path)])
+    RLLoop(args).run()
+    samples = D.load_samples(str(tmp_path / "rollout_0.pt"))
+    assert len(samples) == 8
+    buf = io.StringIO()
+    summary = D.show(samples, limit=3, out=buf)
+    text = buf.getvalue()
+    assert text.count("--- sample ") == 3 and "reward_mean=" in text and summary["samples"] == 8 and summary["response_len_max"] <= 8
+    # the same grader gives the same rewards; another grader differs somewhere
+    assert asyncio.run(D.rescore(samples, rm_type="parity", out=io.StringIO())) == []
+    flipped = asyncio.run(D.rescore(samples, custom_rm_path="tests.test_utils_misc._always_two", out=io.StringIO()))
+    assert len(flipped) == 8 and flipped[0][2] == 2.0
+    sent = []
+
+    async def post(url, payload):
+        sent.append((url, payload))
+        return {"output_ids": [1, 2, 3], "text": "abc"}
+
+    outs = asyncio.run(D.send(samples, "http://engine:1/", limit=2, max_new_tokens=5, out=io.StringIO(), post=post))
+    assert len(outs) == 2 and sent[0][0] == "http://engine:1/generate" and sent[0][1]["sampling_params"]["max_new_tokens"] == 5
+    n = samples[0].response_length
+    assert sent[0][1]["input_ids"] == samples[0].tokens[:len(samples[0].tokens) - n], "the saved prompt tokens are sent as they were"
+    assert D.main(["show", str(tmp_path / "rollout_0.pt"), "--limit", "1"]) == 0
+
+
+def _always_two(args, sample, **kw):
+    return 2.0
