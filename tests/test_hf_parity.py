@@ -227,3 +227,29 @@ def test_more_reference_argument_strings(flags, preset):
     for f in ("num_q_heads", "num_kv_heads", "head_dim", "rope_theta", "rms_eps", "qk_norm", "qkv_bias", "rotary_dim", "post_norms",
               "rope_interleaved", "tie_embeddings", "rope_scaling", "family"):
         assert getattr(cfg, f) == getattr(ref, f), (f, getattr(cfg, f), getattr(ref, f))
+
+
+@pytest.mark.parametrize("name", ["qwen3", "qwen3_moe", "llama-rope-llama3", "mixtral", "glm4", "glm4_moe", "qwen2_moe"])
+def test_engine_greedy_decoding_matches_huggingface_generate(name, tmp_path):
+    """The rollout engine (paged KV cache, prefill then one token per step, prefix cache on) against ``model.generate`` of the
+    HuggingFace implementation: same greedy continuation for several prompts of different lengths."""
+    from miles_b200.engine import Engine, SamplingParams
+
+    torch.manual_seed(1)
+    hf_cfg, cls = _case(name)
+    hf = cls(hf_cfg).float().eval()
+    src = tmp_path / "hf"
+    hf.save_pretrained(src, safe_serialization=True)
+    cfg = ModelConfig.from_hf_config(str(src))
+    store = ParamStore(cfg, "cpu", torch.float32, init=False)
+    load_hf(cfg, store, str(src))
+    eng = Engine(build_model(cfg, store, "torch"), max_running=4, page_size=8, max_seq_len=128, prefix_cache=True)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(2, 256, (n,), generator=g).tolist() for n in (5, 19, 33)]
+    prompts.append(prompts[2][:24] + [7, 8, 9])  # shares three pages with the previous prompt
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=10, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        with torch.no_grad():
+            ref = hf.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, pad_token_id=0, eos_token_id=None)[0, len(p):].tolist()
+        assert o["output_ids"] == ref, (name, len(p), o["output_ids"], ref)
+    assert outs[3]["meta_info"]["cached_tokens"] == 24
