@@ -538,6 +538,11 @@ class RLLoop:
         data = self.object_store.get(ref)
         if not getattr(a, "dump_details", None):
             self.object_store.delete(ref)
+        if getattr(a, "balance_data", False) and self.ps.dp.size > 1:
+            from .rollout.train_data import rebalance_across_dp
+
+            # the ranks pool their samples and take length-balanced shares (utils/dp_schedule.py)
+            data = rebalance_across_dp(self.local_args, data, self.ps.dp.group, self.ps.dp.rank, self.ps.dp.size)
         if self.ft is not None and "train" in self.ft.components:
             return self.ft.train(rollout_id, data)  # through the cell group: retries, suspended cells, scripted faults
         return self._train_once(rollout_id, data)

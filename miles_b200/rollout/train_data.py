@@ -177,3 +177,48 @@ def compute_rollout_metrics(args, samples: Sequence[Sample], rollout_time: float
     if total_p:
         m["rollout/prefix_cache_hit_rate"] = cached / total_p
     return m
+
+
+def rebalance_across_dp(args, data: dict, group, rank: int, size: int) -> dict:
+    """``--balance-data``: every data-parallel rank generated its own samples, and their lengths differ; the ranks pool
+    what they have and take the partition a common schedule (``utils/dp_schedule.py``) gives them, so that every rank
+    trains about the same number of tokens (or, with ``--balance-by-flops``, the same estimated cost) and the same number
+    of micro-batches. Rewards and advantages inputs are final per sample at this point, so samples may change ranks freely;
+    the samples of one rollout stay in the same optimizer step. Collective over ``group``.
+    Reference: the rollout-side schedule of miles/utils/dp_schedule.py:31-155 (one process plans for all ranks there)."""
+    import torch.distributed as dist
+
+    from ..utils.dp_schedule import build_dp_schedule
+
+    if size <= 1:
+        return data
+    gathered = [None] * size
+    dist.all_gather_object(gathered, data, group=group)
+    list_keys = [k for k, v in data.items() if isinstance(v, list)]
+    merged = {k: [x for d in gathered for x in d[k]] for k in list_keys}
+    # rollout ids are local to the rank that generated them: make them unique over the pool
+    uniq: dict = {}
+    merged["rollout_ids"] = [uniq.setdefault((r, rid), len(uniq)) for r, d in enumerate(gathered) for rid in d["rollout_ids"]]
+    steps = int(getattr(args, "num_steps_per_rollout", None) or 1)
+    n_roll = len(uniq)
+    if n_roll < size * steps:
+        return data  # too few rollouts to give every rank its share in every step: keep what each rank has
+    workload = None
+    if getattr(args, "balance_by_flops", False):
+        workload = lambda n: float(n) * (1.0 + n / 8192.0)  # noqa: E731 - linear layers plus the quadratic attention term
+    dynamic = bool(getattr(args, "use_dynamic_batch_size", False)) and getattr(args, "max_tokens_per_gpu", None)
+    try:
+        sched = build_dp_schedule(merged["total_lengths"], merged["rollout_ids"], dp_size=size, global_batch_size=n_roll // steps,
+                                  max_tokens_per_gpu=args.max_tokens_per_gpu if dynamic else None,
+                                  micro_batch_size=None if dynamic else 1, cp_size=int(getattr(args, "context_parallel_size", 1) or 1),
+                                  balance=True, allow_partial_step=bool(dynamic), workload_fn=workload)
+    except ValueError:
+        return data  # the pool does not fit the schedule's divisibility rules: keep the local shares
+    mine = sched.partitions[rank]
+    out = {k: [merged[k][i] for i in mine] for k in list_keys}
+    for k, v in data.items():
+        if k not in out:
+            out[k] = v
+    out["num_rollouts"] = len(set(out["rollout_ids"]))
+    out["rebalanced_from"] = {"tokens_before": sum(data["total_lengths"]), "tokens_after": sum(out["total_lengths"])}
+    return out

@@ -379,3 +379,47 @@ def test_debug_rollout_data_tool_shows_rescoring_and_resending(tmp_path):
 
 def _always_two(args, sample, **kw):
     return 2.0
+
+
+def _rebalance_worker(rank: int, world: int, port: int, out_dir: str):
+    import os
+    from types import SimpleNamespace as NS
+
+    import torch
+    import torch.distributed as dist
+
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from miles_b200.rollout.train_data import rebalance_across_dp
+
+    # rank 0 drew long samples, rank 1 short ones; two samples per rollout (a group that must stay in one step)
+    lens = [900, 800, 850, 820] if rank == 0 else [100, 120, 90, 110]
+    data = {"tokens": [[rank] * n for n in lens], "total_lengths": list(lens), "response_lengths": [n // 2 for n in lens],
+            "rewards": [float(rank * 10 + i) for i in range(4)], "rollout_ids": [0, 0, 1, 1], "sample_indices": [rank * 4 + i for i in range(4)],
+            "num_rollouts": 2}
+    args = NS(num_steps_per_rollout=1, use_dynamic_batch_size=True, max_tokens_per_gpu=2000, context_parallel_size=1, balance_by_flops=False)
+    out = rebalance_across_dp(args, data, None, rank, world)
+    assert len(out["tokens"]) == len(out["rewards"]) == len(out["sample_indices"]) and out["num_rollouts"] >= 1
+    assert all(len(t) == n for t, n in zip(out["tokens"], out["total_lengths"])), "fields stay aligned per sample"
+    torch.save({"idx": out["sample_indices"], "tok": sum(out["total_lengths"]), "before": sum(lens)}, os.path.join(out_dir, f"r{rank}.pt"))
+    # too few rollouts for the ranks: the local share is kept
+    small = {k: (v[:1] if isinstance(v, list) else v) for k, v in data.items()}
+    assert rebalance_across_dp(NS(**{**vars(args), "num_steps_per_rollout": 4}), small, None, rank, world) is small
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_balance_data_pools_and_redistributes_samples_across_ranks(tmp_path):
+    import socket
+
+    import torch
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_rebalance_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    a, b = torch.load(tmp_path / "r0.pt"), torch.load(tmp_path / "r1.pt")
+    assert sorted(a["idx"] + b["idx"]) == list(range(8)), "every sample trains exactly once"
+    assert a["before"] == 3370 and b["before"] == 420
+    assert abs(a["tok"] - b["tok"]) < 400 and a["tok"] + b["tok"] == 3790, (a["tok"], b["tok"])
