@@ -131,7 +131,8 @@ def _worker(rank: int, world: int, port: int, out_dir: str, mode: str):
     torch.set_num_threads(2)
     from miles_b200.loop import RLLoop
 
-    extra = {"dp": [], "fsdp": ["--train-backend", "fsdp"], "hsdp": ["--train-backend", "fsdp", "--dp-replicate-size", "2"]}[mode]
+    extra = {"dp": [], "fsdp": ["--train-backend", "fsdp"], "hsdp": ["--train-backend", "fsdp", "--dp-replicate-size", "2"],
+             "cp": ["--context-parallel-size", "2"], "fsdp_cp": ["--train-backend", "fsdp", "--context-parallel-size", "2"]}[mode]
     ckpt = os.path.join(out_dir, f"ckpt_{mode}")
     args = parse_args(BASE + extra + ["--num-rollout", "2", "--actor-num-gpus-per-node", str(world), "--check-weight-update-equal",
                                       "--save", ckpt, "--save-interval", "1"])
@@ -139,7 +140,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str, mode: str):
     hist = loop.run()
     assert all(m["train/train_rollout_logprob_abs_diff"] < 1e-5 for m in hist), "the engine serves the gathered weights"
     full = _full_weights(loop)
-    if mode != "dp":
+    if mode not in ("dp", "cp"):
         st = loop.actor.store
         assert st.gathers > 0 and (st.shard_size == 1 or sum(st.sizes.values()) < sum(st.full_sizes.values()))
         for g, t in loop.rollout_store.flat.items():
@@ -317,3 +318,11 @@ def test_sharded_trainer_updates_an_engine_in_another_process():
     finally:
         srv.terminate()
         srv.join(10)
+
+
+def test_sharded_backend_under_context_parallelism(tmp_path):
+    """Shards over the dp x cp group: the ranks of a context-parallel group hold different pieces of the same samples'
+    gradients, and the per-unit reduce-scatter is the sum the plain backend takes with an all-reduce."""
+    for mode in ("cp", "fsdp_cp"):
+        mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), mode), nprocs=2, join=True)
+    _compare(torch.load(tmp_path / "cp.pt", weights_only=False), torch.load(tmp_path / "fsdp_cp.pt", weights_only=False))
