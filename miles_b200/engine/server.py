@@ -6,7 +6,8 @@
 ``/begin_weight_update``, ``/update_weights_from_tensor`` (flat buckets, in-process handle),
 ``/update_weights_from_disk``, ``/update_weight_version``, ``/end_weight_update``, ``/get_weight_version``,
 ``/model_info``, ``/server_info``, ``/release_memory_occupation``, ``/resume_memory_occupation``,
-``/weights_checker``, ``/metrics``.  The engine loop runs as an asyncio task of the same process, so the
+``/weights_checker``, ``/metrics``, ``/export_prefix`` / ``/import_prefix`` (prefill / decode hand-over) and the OpenAI-compatible
+``/v1/*`` endpoints (``openai_api.py``).  The engine loop runs as an asyncio task of the same process, so the
 server needs no scheduler or detokenizer subprocesses.
 """
 import time
@@ -156,6 +157,9 @@ def build_app(engine: Engine, tokenizer=None, model_path: str = ""):
     from .server_extra import register_extra
 
     register_extra(app, engine, snapshot)
+    from .openai_api import register_openai
+
+    register_openai(app, client, tokenizer, model_path or "policy")
 
     @app.get("/metrics")
     async def metrics():

@@ -421,3 +421,41 @@ def test_generate_endpoint_scores_when_no_token_is_asked_for():
     lp, _ = m.forward_logprobs(tok, pos, cu, torch.arange(8, 16), tok[9:], 1.0)
     assert torch.allclose(torch.tensor([e[0] for e in meta["input_token_logprobs"]]), lp, atol=1e-5)
     assert not eng.running and eng.prefix.num_pages == 0 and eng.pool.num_free == eng.num_pages - 1
+
+
+def test_openai_compatible_endpoints_of_the_engine_server():
+    from fastapi.testclient import TestClient
+
+    from miles_b200.engine import Engine
+    from miles_b200.engine.server import build_app
+    from miles_b200.models import build_model
+
+    class Tok:
+        chat_template = None
+
+        def __call__(self, text, add_special_tokens=False):
+            return {"input_ids": [ord(c) % 250 + 2 for c in text]}
+
+        def decode(self, ids, skip_special_tokens=True):
+            return "".join(chr(97 + int(i) % 26) for i in ids)
+
+    cfg = get_config("qwen3-tiny")
+    eng = Engine(build_model(cfg, ParamStore(cfg, "cpu", torch.float32, seed=3)), max_running=4, page_size=8, max_seq_len=128)
+    with TestClient(build_app(eng, Tok(), "tiny-model")) as c:
+        assert c.get("/v1/models").json()["data"][0]["id"] == "tiny-model"
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "temperature": 0.0,
+                                                 "logprobs": True, "seed": 1}).json()
+        ch = r["choices"][0]
+        assert r["object"] == "chat.completion" and ch["message"]["role"] == "assistant" and len(ch["message"]["content"]) == 6
+        assert ch["finish_reason"] == "length" and len(ch["logprobs"]["content"]) == 6 and r["usage"]["completion_tokens"] == 6
+        two = c.post("/v1/completions", json={"prompt": "abc", "max_tokens": 4, "n": 2, "seed": 5}).json()
+        assert [len(x["token_ids"]) for x in two["choices"]] == [4, 4] and two["usage"]["prompt_tokens"] == 3
+        ids = c.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 3, "temperature": 0.0}).json()
+        direct = c.post("/generate", json={"input_ids": [5, 6, 7], "sampling_params": {"max_new_tokens": 3, "temperature": 0.0}}).json()
+        assert ids["choices"][0]["token_ids"] == direct["output_ids"], "the same engine path as /generate"
+        s = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3, "stream": True})
+        assert s.headers["content-type"].startswith("text/event-stream") and s.text.strip().endswith("data: [DONE]")
+        assert c.post("/v1/chat/completions", json={"messages": []}).status_code == 400
+    with TestClient(build_app(eng, None, "")) as c:
+        assert c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}]}).status_code == 400
+        assert c.post("/v1/completions", json={"prompt": [1, 2], "max_tokens": 2}).status_code == 200
