@@ -37,9 +37,17 @@ class SamplingParams:
     # benchmark hook (reference: rollout/generate_hub/benchmarkers.py): stop exactly at this length
     forced_length: Optional[int] = None
 
+    # parameters of the reference's engines that would change what is sampled and are not built here: a request that sets
+    # one to anything but its neutral value is refused instead of being served from another distribution
+    UNSUPPORTED = {"min_p": 0.0, "repetition_penalty": 1.0, "frequency_penalty": 0.0, "presence_penalty": 0.0, "logit_bias": None,
+                   "regex": None, "json_schema": None, "ebnf": None, "structural_tag": None, "n": 1}
+
     @classmethod
     def from_dict(cls, d: dict) -> "SamplingParams":
         d = dict(d or {})
+        for k, neutral in cls.UNSUPPORTED.items():
+            if d.get(k) not in (None, neutral):
+                raise ValueError(f"sampling parameter {k}={d[k]!r} is not built in this engine (only its neutral value {neutral!r} is accepted)")
         stop = d.pop("stop_token_ids", None) or ()
         kw = {k: v for k, v in d.items() if k in cls.__dataclass_fields__}
         return cls(stop_token_ids=tuple(stop), **kw)

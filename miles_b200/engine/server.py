@@ -41,7 +41,10 @@ def build_app(engine: Engine, tokenizer=None, model_path: str = ""):
         payload = await req.json()
         if "input_ids" not in payload and "text" not in payload:
             raise HTTPException(400, "input_ids or text is required")
-        out = await client.generate(payload)
+        try:
+            out = await client.generate(payload)
+        except ValueError as e:  # a sampling parameter this engine does not implement: the caller's mistake, not a crash
+            raise HTTPException(400, str(e))
         if not payload.get("return_logprob", True):
             out["meta_info"].pop("output_token_logprobs", None)
         return JSONResponse(out)

@@ -253,3 +253,25 @@ def test_prefix_cache_gives_pages_back_under_pressure():
     assert [len(r["output_ids"]) for r in res] == [10] * 6
     _logprob_parity(m, prompts, res)
     assert eng.pool.num_free + eng.prefix.num_pages == eng.num_pages - 1
+
+
+def test_sampling_parameters_that_are_not_built_are_refused_not_dropped():
+    import pytest
+
+    from miles_b200.engine.core import SamplingParams
+
+    ok = SamplingParams.from_dict({"temperature": 0.7, "top_p": 0.9, "skip_special_tokens": True, "repetition_penalty": 1.0, "min_p": 0.0,
+                                   "n": 1, "stop_token_ids": [3]})
+    assert ok.temperature == 0.7 and ok.stop_token_ids == (3,)
+    for bad in ({"repetition_penalty": 1.1}, {"min_p": 0.05}, {"presence_penalty": 0.5}, {"json_schema": "{}"}, {"n": 4}):
+        with pytest.raises(ValueError):
+            SamplingParams.from_dict(bad)
+    from fastapi.testclient import TestClient
+
+    from miles_b200.engine.server import build_app
+
+    cfg, m, eng = _engine()
+    with TestClient(build_app(eng)) as c:
+        r = c.post("/generate", json={"input_ids": [1, 2, 3], "sampling_params": {"max_new_tokens": 2, "min_p": 0.1}})
+        assert r.status_code == 400 and "min_p" in r.text
+        assert c.post("/generate", json={"input_ids": [1, 2, 3], "sampling_params": {"max_new_tokens": 2}}).status_code == 200
