@@ -138,6 +138,9 @@ class Engine:
             self.prefix = PrefixCache(page_size)
         self.overlap_decode = overlap_decode  # keep one decode step in flight while the host reads the previous one
         self.kv_storage = kv_storage  # caller-owned uint8 device buffer to carve the KV cache from (None = allocate)
+        # mixed into the sampling seed of requests that bring none: the loop sets it from --seed and the rank, so that a run
+        # is reproducible, runs with different seeds differ, and the engines of different ranks do not sample in step
+        self.seed_salt = 0
         self.sync = sync            # lockstep agreement across expert-parallel ranks (None = independent engine)
         self.ep_decode = ep_decode  # small expert-parallel exchange used by decode steps (graph friendly)
         self.last_mode = 0
@@ -355,7 +358,7 @@ class Engine:
         if len(ids) + 1 > self.max_seq_len:
             ids = ids[-(self.max_seq_len - 1):]
         req = Request(rid, ids, params, return_routed_experts)
-        req.seed = params.sampling_seed if params.sampling_seed is not None else (zlib.crc32(rid.encode()) & 0x7FFFFFFF)
+        req.seed = params.sampling_seed if params.sampling_seed is not None else (zlib.crc32(f"{self.seed_salt}:{rid}".encode()) & 0x7FFFFFFF)
         req.t_submit = time.time()
         self.waiting.append(req)
         return rid

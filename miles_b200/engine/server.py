@@ -226,6 +226,7 @@ def main(argv=None) -> None:
     engine = Engine(model, max_running=ns.max_running_requests, page_size=ns.page_size, max_seq_len=ns.context_length,
                     kv_mem_bytes=kv_bytes, use_cuda_graph=on_gpu, eos_token_id=getattr(tokenizer, "eos_token_id", None),
                     prefix_cache=not ns.disable_radix_cache, memory_saver=on_gpu)
+    engine.seed_salt = ns.seed * 1000003 + ns.port  # engines of one fleet share --seed and differ by port
     serve(engine, ns.host, ns.port, tokenizer, ns.hf_checkpoint or ns.model_preset or "")
 
 

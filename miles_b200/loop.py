@@ -242,6 +242,7 @@ class RLLoop:
                              # a KV cache of its own that --offload-rollout releases: tagged virtual memory keeps the
                              # addresses (captured graphs stay valid across release / resume)
                              memory_saver=kv_storage is None and bool(getattr(a, "offload_rollout", False)))
+        self.engine.seed_salt = int(getattr(a, "seed", 1234)) * 1000003 + self.ps.rank
         if sync is not None:
             self.engine.warm_up_decode_graphs()  # lockstep ranks capture their decode graphs together
         self.client = EngineClient([self.engine], self.tokenizer)

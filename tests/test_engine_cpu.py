@@ -275,3 +275,18 @@ def test_sampling_parameters_that_are_not_built_are_refused_not_dropped():
         r = c.post("/generate", json={"input_ids": [1, 2, 3], "sampling_params": {"max_new_tokens": 2, "min_p": 0.1}})
         assert r.status_code == 400 and "min_p" in r.text
         assert c.post("/generate", json={"input_ids": [1, 2, 3], "sampling_params": {"max_new_tokens": 2}}).status_code == 200
+
+
+def test_default_sampling_seeds_follow_the_salt_not_the_process():
+    """Requests without a seed draw from (salt, request id): the same salt reproduces a run in any process, another salt
+    (another --seed, another rank) samples differently."""
+    cfg, m, a = _engine()
+    _, _, b = _engine()
+    _, _, c = _engine()
+    a.seed_salt = b.seed_salt = 1234 * 1000003
+    c.seed_salt = 1234 * 1000003 + 1
+    prompts = _prompts(cfg, [12, 9], seed=4)
+    sp = SamplingParams(max_new_tokens=12, temperature=1.0)
+    ra, rb, rc = (e.generate(prompts, sp) for e in (a, b, c))
+    assert [r["output_ids"] for r in ra] == [r["output_ids"] for r in rb]
+    assert [r["output_ids"] for r in ra] != [r["output_ids"] for r in rc]
