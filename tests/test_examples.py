@@ -5,7 +5,7 @@ import re
 
 from miles_b200.utils.arguments import build_parser
 
-LAUNCHER_FLAGS = {"--nnodes", "--nproc-per-node", "--master-addr", "--master-port"}
+LAUNCHER_FLAGS = {"--nnodes", "--nproc-per-node", "--master-addr", "--master-port", "--node-rank"}
 SERVER_FLAGS = {"--port", "--device", "--max-running-requests", "--page-size", "--context-length", "--host", "--quantization",
                 "--mem-fraction-static"}
 TOOL_FLAGS = {"--format", "--output"}  # the converter tools of examples/convert_checkpoints.sh (miles_b200/tools)
