@@ -30,7 +30,7 @@ def main():
     world = int(os.environ["WORLD_SIZE"])
     ps = init_parallel_state(ep=world)
     dev = ps.device
-    cfg = get_config("qwen3-smoke-moe")
+    cfg = get_config(sys.argv[2] if len(sys.argv) > 2 else "qwen3-smoke-moe")  # e.g. glm4moe-smoke: sigmoid router + shared expert
     lens_of = {r: [90 + 13 * r, 41, 150 - 20 * r] for r in range(world)}
     # expert-parallel model
     store = ParamStore(cfg, dev, torch.bfloat16, ep_size=world, ep_rank=ps.ep.rank, init_std=0.05, seed=5)

@@ -9,11 +9,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(mode: str, n: int):
+def _run(mode: str, n: int, preset: str = "qwen3-smoke-moe"):
     here = os.path.dirname(os.path.abspath(__file__))
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", "29731", os.path.join(here, "mp_ep_check.py"), mode]
+           "--master-port", "29731", os.path.join(here, "mp_ep_check.py"), mode, preset]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "EP_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
 
@@ -24,6 +24,14 @@ def test_expert_parallel_matches_single_rank(mode):
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     _run(mode, 2)
+
+
+def test_expert_parallel_with_sigmoid_router_and_shared_expert():
+    """GLM-4.5 style layers under expert parallelism: routing happens before the dispatch, the shared expert's output joins
+    the residual that the combine adds."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    _run("fused", 2, "glm4moe-smoke")
 
 
 def test_low_latency_expert_parallel_decode():
