@@ -22,7 +22,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from .models.params import ParamStore
+from .models.params import ParamStore, _seed_for
 
 ALL_LINEAR = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
 
@@ -34,6 +34,8 @@ class Target:
     row0: int
     row1: int
     expert: Optional[int] = None
+    tp: Optional[str] = None   # under tensor parallelism: "col" (output rows sharded, A replicated), "row" (input columns
+                               # sharded, B replicated), None (not sharded: experts)
 
 
 def _targets(store: ParamStore, modules: Sequence[str]) -> list:
@@ -45,17 +47,17 @@ def _targets(store: ParamStore, modules: Sequence[str]) -> list:
         att = {"q_proj": (0, q), "k_proj": (q, q + kv), "v_proj": (q + kv, q + 2 * kv)}
         for m, (a, b) in att.items():
             if m in modules:
-                out.append(Target(hp + "self_attn." + m, p + "attn.qkv.weight", a, b))
+                out.append(Target(hp + "self_attn." + m, p + "attn.qkv.weight", a, b, tp="col"))
         if "o_proj" in modules:
-            out.append(Target(hp + "self_attn.o_proj", p + "attn.o.weight", 0, cfg.hidden_size))
+            out.append(Target(hp + "self_attn.o_proj", p + "attn.o.weight", 0, cfg.hidden_size, tp="row"))
         if not cfg.layer_is_moe(i):
             I = cfg.ffn_hidden_size
             if "gate_proj" in modules:
-                out.append(Target(hp + "mlp.gate_proj", p + "mlp.gate_up.weight", 0, I))
+                out.append(Target(hp + "mlp.gate_proj", p + "mlp.gate_up.weight", 0, I, tp="col"))
             if "up_proj" in modules:
-                out.append(Target(hp + "mlp.up_proj", p + "mlp.gate_up.weight", I, 2 * I))
+                out.append(Target(hp + "mlp.up_proj", p + "mlp.gate_up.weight", I, 2 * I, tp="col"))
             if "down_proj" in modules:
-                out.append(Target(hp + "mlp.down_proj", p + "mlp.down.weight", 0, cfg.hidden_size))
+                out.append(Target(hp + "mlp.down_proj", p + "mlp.down.weight", 0, cfg.hidden_size, tp="row"))
         else:
             I = cfg.moe_ffn_hidden_size
             el = cfg.num_experts // store.ep_size
@@ -72,22 +74,39 @@ def _targets(store: ParamStore, modules: Sequence[str]) -> list:
 
 
 class LoRAManager:
+    """``tp_group``: the tensor-parallel group of a store that holds a shard (``store.tp_size > 1``). The adapter of a
+    column-parallel projection shards ``B`` by output rows and keeps ``A`` whole on every rank; a row-parallel one shards
+    ``A`` by input columns and keeps ``B`` whole. The whole factor's gradient is a partial sum on each rank and is
+    all-reduced over the group before the step, so the ranks stay equal and the sharded adapter is the unsharded one
+    (the role of the partial-gradient all-reduce in miles/backends/megatron_utils/lora_utils.py)."""
+
     def __init__(self, store: ParamStore, rank: int, alpha: float, target_modules: Sequence[str] | str = "all-linear",
-                 lr: float = 1e-4, weight_decay: float = 0.0, seed: int = 0, betas=(0.9, 0.999), base: Optional[dict] = None):
+                 lr: float = 1e-4, weight_decay: float = 0.0, seed: int = 0, betas=(0.9, 0.999), base: Optional[dict] = None,
+                 tp_group=None):
         assert rank > 0
         mods = ALL_LINEAR if target_modules in ("all-linear", None) else list(target_modules)
         self.store, self.rank, self.alpha = store, rank, float(alpha)
         self.scale = self.alpha / rank
         self.target_modules = mods
         self.targets = _targets(store, mods)
+        self.tp_size, self.tp_rank = getattr(store, "tp_size", 1), getattr(store, "tp_rank", 0)
+        self.tp_group = tp_group
+        assert self.tp_size == 1 or tp_group is not None, "a tensor-parallel store needs the tensor-parallel group"
         dev = store.device
-        g = torch.Generator(device="cpu").manual_seed(seed)
         self.A, self.B = [], []
         for t in self.targets:
             w = self._slice(store.params[t.native], t)
-            a = torch.empty(rank, w.shape[1]).uniform_(-1, 1, generator=g) * math.sqrt(3.0 / w.shape[1])
+            # one generator per module, drawn at the unsharded width: the start does not depend on the layout
+            g = torch.Generator(device="cpu").manual_seed(_seed_for(seed, t.hf_module))
+            cols = w.shape[1] * (self.tp_size if t.tp == "row" else 1)
+            a = torch.empty(rank, cols).uniform_(-1, 1, generator=g) * math.sqrt(3.0 / cols)
+            if t.tp == "row" and self.tp_size > 1:
+                a = a[:, self.tp_rank * w.shape[1]:(self.tp_rank + 1) * w.shape[1]].contiguous()
             self.A.append(a.to(dev).requires_grad_(False))
             self.B.append(torch.zeros(w.shape[0], rank, device=dev))
+        # the factors every tensor-parallel rank holds whole (partial gradients) and the ones it holds a shard of
+        self._whole = [] if self.tp_size == 1 else [a if t.tp == "col" else b for t, a, b in zip(self.targets, self.A, self.B) if t.tp]
+        self._sharded = [] if self.tp_size == 1 else [b if t.tp == "col" else a for t, a, b in zip(self.targets, self.A, self.B) if t.tp]
         # frozen base copies of the targeted tensors only (several adapters on one model share one set: ``base``)
         need = {t.native for t in self.targets}
         self.base = base if base is not None else {}
@@ -97,6 +116,7 @@ class LoRAManager:
         self.opt = torch.optim.AdamW([p for p in self.A + self.B], lr=lr, weight_decay=weight_decay, betas=betas)
         for p in self.A + self.B:
             p.grad = torch.zeros_like(p)
+
 
     @staticmethod
     def _slice(w: torch.Tensor, t: Target) -> torch.Tensor:
@@ -136,13 +156,41 @@ class LoRAManager:
     @torch.no_grad()
     def grads_from_weight_grads(self) -> None:
         """Project the full weight gradients (already accumulated by the backward GEMMs) onto the adapters."""
+        if self.tp_size > 1:
+            part = torch.zeros(sum(p.numel() for p in self._whole), device=self.store.device)
+            views, o = {}, 0
+            for p in self._whole:
+                views[id(p)] = part[o:o + p.numel()].view_as(p)
+                o += p.numel()
         for t, a, b in zip(self.targets, self.A, self.B):
             dw = self._slice(self.store.grads[t.native], t).float()
-            b.grad.add_(self.scale * (dw @ a.t()))
-            a.grad.add_(self.scale * (b.t() @ dw))
+            db, da = self.scale * (dw @ a.t()), self.scale * (b.t() @ dw)
+            if self.tp_size > 1 and t.tp == "col":
+                b.grad.add_(db)
+                views[id(a)].copy_(da)
+            elif self.tp_size > 1 and t.tp == "row":
+                a.grad.add_(da)
+                views[id(b)].copy_(db)
+            else:
+                b.grad.add_(db)
+                a.grad.add_(da)
+        if self.tp_size > 1 and part.numel():
+            import torch.distributed as dist
+
+            dist.all_reduce(part, group=self.tp_group)      # one collective for all partial gradients of the step
+            for p in self._whole:
+                p.grad.add_(views[id(p)])
 
     def grad_norm(self) -> torch.Tensor:
-        return torch.sqrt(sum((p.grad.float() ** 2).sum() for p in self.A + self.B))
+        if self.tp_size == 1:
+            return torch.sqrt(sum((p.grad.float() ** 2).sum() for p in self.A + self.B))
+        import torch.distributed as dist
+
+        sharded = {id(p) for p in self._sharded}
+        sq = sum((p.grad.float() ** 2).sum() for p in self.A + self.B if id(p) in sharded)
+        sq = sq if torch.is_tensor(sq) else torch.zeros((), device=self.store.device)
+        dist.all_reduce(sq, group=self.tp_group)            # shards add up over the group, whole factors count once
+        return torch.sqrt(sq + sum((p.grad.float() ** 2).sum() for p in self.A + self.B if id(p) not in sharded))
 
     @torch.no_grad()
     def step(self, clip_grad: float = 0.0, grad_scale: float = 1.0) -> torch.Tensor:
@@ -161,23 +209,41 @@ class LoRAManager:
         return norm
 
     # ------------------------------------------------------------------ PEFT checkpoint
+    @torch.no_grad()
     def state_dict(self) -> dict:
+        """PEFT-named tensors of the whole adapter. Under tensor parallelism the shards are gathered over the group (a
+        collective: every rank of the group calls it) and every rank returns the unsharded adapter."""
         out = {}
         for t, a, b in zip(self.targets, self.A, self.B):
-            out[f"base_model.model.{t.hf_module}.lora_A.weight"] = a.detach().cpu().contiguous()
-            out[f"base_model.model.{t.hf_module}.lora_B.weight"] = b.detach().cpu().contiguous()
+            a, b = a.detach(), b.detach()
+            if self.tp_size > 1 and t.tp:
+                import torch.distributed as dist
+
+                mine = (b if t.tp == "col" else a).contiguous()
+                parts = [torch.empty_like(mine) for _ in range(self.tp_size)]
+                dist.all_gather(parts, mine, group=self.tp_group)
+                a, b = (a, torch.cat(parts, 0)) if t.tp == "col" else (torch.cat(parts, 1), b)
+            out[f"base_model.model.{t.hf_module}.lora_A.weight"] = a.cpu().contiguous()
+            out[f"base_model.model.{t.hf_module}.lora_B.weight"] = b.cpu().contiguous()
         return out
 
-    def save(self, path: str, base_model_name: str = "") -> None:
+    def _state_file(self) -> str:
+        return "training_state.pt" if self.tp_size == 1 else f"training_state_tp{self.tp_rank}.pt"
+
+    def save(self, path: str, base_model_name: str = "", write_adapter: bool = True) -> None:
+        """Every rank of a tensor-parallel group calls it (the gather is collective); the rank with ``write_adapter``
+        writes the PEFT files, every rank writes the optimizer state of its own shard."""
         from safetensors.torch import save_file
 
+        sd = self.state_dict()
         os.makedirs(path, exist_ok=True)
-        save_file(self.state_dict(), os.path.join(path, "adapter_model.safetensors"), metadata={"format": "pt"})
-        cfg = {"peft_type": "LORA", "r": self.rank, "lora_alpha": self.alpha, "lora_dropout": 0.0, "bias": "none",
-               "target_modules": self.target_modules, "task_type": "CAUSAL_LM", "base_model_name_or_path": base_model_name}
-        with open(os.path.join(path, "adapter_config.json"), "w") as f:
-            json.dump(cfg, f, indent=1)
-        torch.save({"optimizer": self.opt.state_dict()}, os.path.join(path, "training_state.pt"))
+        if write_adapter:
+            save_file(sd, os.path.join(path, "adapter_model.safetensors"), metadata={"format": "pt"})
+            cfg = {"peft_type": "LORA", "r": self.rank, "lora_alpha": self.alpha, "lora_dropout": 0.0, "bias": "none",
+                   "target_modules": self.target_modules, "task_type": "CAUSAL_LM", "base_model_name_or_path": base_model_name}
+            with open(os.path.join(path, "adapter_config.json"), "w") as f:
+                json.dump(cfg, f, indent=1)
+        torch.save({"optimizer": self.opt.state_dict()}, os.path.join(path, self._state_file()))
 
     def load(self, path: str, load_optimizer: bool = True) -> None:
         from safetensors.torch import load_file
@@ -187,9 +253,14 @@ class LoRAManager:
             for t, a, b in zip(self.targets, self.A, self.B):
                 ka = f"base_model.model.{t.hf_module}.lora_A.weight"
                 if ka in sd:
-                    a.copy_(sd[ka])
-                    b.copy_(sd[ka.replace("lora_A", "lora_B")])
-        ts = os.path.join(path, "training_state.pt")
+                    fa, fb = sd[ka], sd[ka.replace("lora_A", "lora_B")]
+                    if self.tp_size > 1 and t.tp == "col":
+                        fb = fb[self.tp_rank * b.shape[0]:(self.tp_rank + 1) * b.shape[0]]
+                    elif self.tp_size > 1 and t.tp == "row":
+                        fa = fa[:, self.tp_rank * a.shape[1]:(self.tp_rank + 1) * a.shape[1]]
+                    a.copy_(fa)
+                    b.copy_(fb)
+        ts = os.path.join(path, self._state_file())
         if load_optimizer and os.path.exists(ts):
             self.opt.load_state_dict(torch.load(ts, weights_only=False)["optimizer"])
         self.merge()

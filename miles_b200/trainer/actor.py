@@ -237,7 +237,8 @@ class TrainActor:
             from ..lora import LoRAManager
 
             self.lora = LoRAManager(self.store, args.lora_rank, args.lora_alpha or args.lora_rank, args.target_modules or "all-linear",
-                                    lr=args.lr, weight_decay=args.weight_decay, seed=args.seed, betas=(args.adam_beta1, args.adam_beta2))
+                                    lr=args.lr, weight_decay=args.weight_decay, seed=args.seed, betas=(args.adam_beta1, args.adam_beta2),
+                                    tp_group=self.ps.tp.group if self.ps.tp.size > 1 else None)
             self.opt = None  # base weights are frozen: only the adapters have optimizer state
             if getattr(args, "lora_adapter_path", None):
                 self.lora.load(args.lora_adapter_path)
@@ -1036,8 +1037,10 @@ class TrainActor:
         with Timer().context("save_model"):
             if getattr(self.args, "save", None):
                 d = save_checkpoint(self, self.args.save, rollout_id)
-                if self.lora is not None and self.ps.rank == 0:
-                    self.lora.save(os.path.join(d, "adapter"), getattr(self.args, "hf_checkpoint", None) or "")
+                if self.lora is not None and (self.ps.rank == 0 or (self.ps.tp.size > 1 and 0 in self.ps.tp.ranks)):
+                    # the ranks of rank 0's tensor-parallel group gather the adapter together; rank 0 writes it
+                    self.lora.save(os.path.join(d, "adapter"), getattr(self.args, "hf_checkpoint", None) or "",
+                                   write_adapter=self.ps.rank == 0)
             if getattr(self.args, "save_hf", None):
                 from ..checkpoint import export_hf
 
